@@ -1,0 +1,167 @@
+"""Kernel micro-benchmarks: device-timed (CUDA events) throughput of the library's hot kernels,
+each next to the stock library call for the same problem (cuBLAS through ``torch.matmul``,
+``scaled_dot_product_attention``), with an L2 flush between timed launches.
+
+    python -m mlperf_training_b200.utils.microbench gemm attention elementwise [--quick]
+
+Prints one JSON object per measurement.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+
+import torch
+
+from ..ops import _lib, kernels
+
+_FLUSH = None
+
+
+def flush_l2() -> None:
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _FLUSH.zero_()
+
+
+def time_ms(fn, iters: int = 10, warmup: int = 3) -> float:
+    """Median device time of ``fn`` in milliseconds, L2 flushed before every timed launch."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush_l2()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def emit(**kw) -> None:
+    print(json.dumps(kw), flush=True)
+
+
+GEMM_SHAPES = [
+    # (M, N, K, a_mn, b_mn, tag)
+    (8192, 6144, 4096, False, False, "llama8b qkv fwd"),
+    (8192, 4096, 4096, False, False, "llama8b proj fwd"),
+    (8192, 28672, 4096, False, False, "llama8b gate_up fwd"),
+    (8192, 4096, 14336, False, False, "llama8b down fwd"),
+    (8192, 4096, 28672, False, True, "llama8b gate_up dgrad"),
+    (28672, 4096, 8192, True, True, "llama8b gate_up wgrad"),
+    (8192, 14336, 4096, False, True, "llama8b down dgrad"),
+    (4096, 14336, 8192, True, True, "llama8b down wgrad"),
+    (8192, 128256, 4096, False, False, "llama8b lm_head fwd"),
+    (8192, 8192, 8192, False, False, "square 8192"),
+]
+
+
+def bench_gemm(quick: bool) -> None:
+    shapes = GEMM_SHAPES[:3] + GEMM_SHAPES[-1:] if quick else GEMM_SHAPES
+    for M, N, K, a_mn, b_mn, tag in shapes:
+        a = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
+        b = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = time_ms(lambda: kernels.gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out=out))
+        am = a.t() if a_mn else a
+        bm = b if b_mn else b.t()
+        ms_ref = time_ms(lambda: torch.matmul(am, bm, out=out))
+        fl = 2.0 * M * N * K
+        emit(kernel="gemm_bf16", tag=tag, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, ms=round(ms, 4),
+             tflops=round(fl / ms / 1e9, 1), cublas_ms=round(ms_ref, 4), cublas_tflops=round(fl / ms_ref / 1e9, 1))
+        _lib.check_status(tag)
+        del a, b, out
+
+
+ATTN_SHAPES = [
+    # B, S, Hq, Hkv, D, causal, window, tag
+    (1, 8192, 32, 8, 128, True, 0, "llama8b"),
+    (1, 8192, 64, 8, 64, True, 0, "gpt-oss full"),
+    (1, 8192, 64, 8, 64, True, 128, "gpt-oss window"),
+    (32, 512, 24, 24, 128, False, 0, "flux joint"),
+]
+
+
+def bench_attention(quick: bool) -> None:
+    for B, S, Hq, Hkv, D, causal, window, tag in (ATTN_SHAPES[:1] if quick else ATTN_SHAPES):
+        q = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+        k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+        v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+        do = torch.randn_like(q)
+        pairs = S * S / 2 if causal else S * S
+        if window:
+            pairs = S * window
+        fl_fwd = 4.0 * B * Hq * pairs * D
+        o, lse = kernels.attention_fwd(q, k, v, causal=causal, window=window)
+        ms_f = time_ms(lambda: kernels.attention_fwd(q, k, v, causal=causal, window=window))
+        ms_b = time_ms(lambda: kernels.attention_bwd(do, q, k, v, o, lse, causal=causal, window=window))
+        ref = {}
+        if not window:
+            qt, kt, vt = (t.transpose(1, 2) for t in (q, k, v))
+            f = lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=causal,
+                                                                         enable_gqa=True)
+            try:
+                ref["sdpa_fwd_ms"] = round(time_ms(f), 4)
+                ref["sdpa_fwd_tflops"] = round(fl_fwd / ref["sdpa_fwd_ms"] / 1e9, 1)
+            except Exception as e:  # library path unavailable for this shape
+                ref["sdpa_error"] = str(e)[:80]
+        emit(kernel="attention", tag=tag, B=B, S=S, Hq=Hq, Hkv=Hkv, D=D, causal=causal, window=window,
+             fwd_ms=round(ms_f, 4), fwd_tflops=round(fl_fwd / ms_f / 1e9, 1), bwd_ms=round(ms_b, 4),
+             bwd_tflops=round(2.5 * fl_fwd / ms_b / 1e9, 1), **ref)
+        _lib.check_status(tag)
+
+
+def bench_elementwise(quick: bool) -> None:
+    T, D, Fh, V = 8192, 4096, 14336, 128256
+    x = torch.randn(T, D, device="cuda").bfloat16()
+    w = torch.ones(D, device="cuda").bfloat16()
+    ms = time_ms(lambda: kernels.norm_fwd(x, w, None, 1e-5))
+    emit(kernel="rmsnorm_fwd", T=T, D=D, ms=round(ms, 4), gbs=round(2 * x.numel() * 2 / ms / 1e6, 1))
+    y, h, mean, rstd = kernels.norm_fwd(x, w, None, 1e-5)
+    ms = time_ms(lambda: kernels.norm_bwd(x, h, w, None, mean, rstd))
+    emit(kernel="rmsnorm_bwd", T=T, D=D, ms=round(ms, 4), gbs=round(3 * x.numel() * 2 / ms / 1e6, 1))
+    gu = torch.randn(T, 2 * Fh, device="cuda").bfloat16()
+    ms = time_ms(lambda: kernels.swiglu_fwd(gu))
+    emit(kernel="swiglu_fwd", T=T, F=Fh, ms=round(ms, 4), gbs=round(3 * T * Fh * 2 / ms / 1e6, 1))
+    da = torch.randn(T, Fh, device="cuda").bfloat16()
+    ms = time_ms(lambda: kernels.swiglu_bwd(da, gu))
+    emit(kernel="swiglu_bwd", T=T, F=Fh, ms=round(ms, 4), gbs=round(5 * T * Fh * 2 / ms / 1e6, 1))
+    logits = torch.randn(T, V, device="cuda").bfloat16()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    ms = time_ms(lambda: kernels.cross_entropy_(logits, labels, 1.0), iters=5)
+    emit(kernel="cross_entropy", T=T, V=V, ms=round(ms, 4), gbs=round(3 * T * V * 2 / ms / 1e6, 1))
+    del logits
+    n = 1 << 28
+    p = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    g = torch.zeros(n, device="cuda", dtype=torch.float32)
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    ms = time_ms(lambda: kernels.adamw_(p, g, m, v, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=1),
+                 iters=5)
+    emit(kernel="adamw", n=n, ms=round(ms, 4), gbs=round(n * (2 + 2 + 4 + 16) / ms / 1e6, 1))
+    _lib.check_status("elementwise")
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", nargs="*", default=["gemm", "attention", "elementwise"])
+    ap.add_argument("--quick", action="store_true")
+    args = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print("microbench needs a CUDA device", file=sys.stderr)
+        return 1
+    for w in args.what:
+        {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise}[w](args.quick)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,107 @@
+"""CPU bodies of the raw operators against autograd / torch built-ins (they are the oracles of
+the GPU tests, so they are checked independently here)."""
+import math
+
+import torch
+import torch.nn.functional as F
+
+from mlperf_training_b200.ops import kernels
+
+
+def test_gemm_cpu_layouts():
+    torch.manual_seed(0)
+    x, w, dy = torch.randn(6, 8).bfloat16(), torch.randn(5, 8).bfloat16(), torch.randn(6, 5).bfloat16()
+    assert torch.allclose(kernels.gemm(x, w).float(), x.float() @ w.float().t(), atol=5e-2)
+    assert torch.allclose(kernels.gemm(dy, w, b_mn_major=True).float(), dy.float() @ w.float(), atol=5e-2)
+    assert torch.allclose(kernels.gemm(dy, x, a_mn_major=True, b_mn_major=True).float(),
+                          dy.float().t() @ x.float(), atol=5e-2)
+
+
+def test_norm_bwd_matches_autograd():
+    torch.manual_seed(1)
+    T, D = 7, 32
+    for layer_norm, swish in ((False, False), (True, False), (True, True)):
+        x = torch.randn(T, D)
+        w = torch.randn(D)
+        b = torch.randn(D) if layer_norm else None
+        dy = torch.randn(T, D)
+        y, h, mean, rstd = kernels.norm_fwd(x, w, b, 1e-5, layer_norm=layer_norm, swish=swish)
+        dx, dw, db = kernels.norm_bwd(dy, h, w, b, mean, rstd, layer_norm=layer_norm, swish=swish)
+        xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        br = None if b is None else b.clone().requires_grad_(True)
+        if layer_norm:
+            n = F.layer_norm(xr, (D,), wr, br, 1e-5)
+        else:
+            n = xr * torch.rsqrt((xr * xr).mean(-1, keepdim=True) + 1e-5) * wr
+        yr = xr * torch.sigmoid(n) if swish else n
+        assert torch.allclose(y, yr, atol=1e-5)
+        yr.backward(dy)
+        assert torch.allclose(dx, xr.grad, atol=1e-4)
+        assert torch.allclose(dw, wr.grad, atol=1e-4)
+        if layer_norm:
+            assert torch.allclose(db, br.grad, atol=1e-4)
+
+
+def test_rope_is_rotation():
+    T, S, H, D = 10, 5, 2, 16
+    x = torch.randn(T, H * D)
+    cos, sin = kernels.rope_tables(S, D, 10000.0, "cpu")
+    y = kernels.rope_(x.clone(), cos, sin, col0=0, n_heads=H, head_dim=D, seq_len=S)
+    assert torch.allclose(y.view(T, H, D).norm(dim=-1), x.view(T, H, D).norm(dim=-1), atol=1e-5)
+    back = kernels.rope_(y.clone(), cos, sin, col0=0, n_heads=H, head_dim=D, seq_len=S, backward=True)
+    assert torch.allclose(back, x, atol=1e-5)
+
+
+def test_swiglu_bwd_matches_autograd():
+    gu = torch.randn(4, 12, requires_grad=True)
+    a = F.silu(gu[:, :6]) * gu[:, 6:]
+    da = torch.randn(4, 6)
+    a.backward(da)
+    assert torch.allclose(kernels.swiglu_bwd(da, gu.detach()), gu.grad, atol=1e-5)
+
+
+def test_cross_entropy_matches_torch():
+    T, V = 9, 40
+    logits = torch.randn(T, V)
+    labels = torch.randint(0, V, (T,))
+    labels[2] = -100
+    ref_in = logits.clone().requires_grad_(True)
+    ref = F.cross_entropy(ref_in, labels, reduction="sum", ignore_index=-100)
+    ref.backward()
+    work = logits.clone()
+    loss = kernels.cross_entropy_(work, labels, 1.0)
+    assert torch.allclose(loss.sum(), ref, atol=1e-4)
+    assert torch.allclose(work, ref_in.grad, atol=1e-5)
+
+
+def test_adamw_matches_torch():
+    torch.manual_seed(2)
+    p = torch.randn(50)
+    ref = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v = torch.zeros(50), torch.zeros(50)
+    mine = p.clone()
+    for step in (1, 2, 3):
+        g = torch.randn(50)
+        ref.grad = g.clone()
+        opt.step()
+        kernels.adamw_(mine, g, m, v, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+    assert torch.allclose(mine, ref.data, atol=1e-5)
+
+
+def test_attention_reference_matches_sdpa_and_sink():
+    torch.manual_seed(3)
+    B, S, Hq, Hkv, D = 2, 16, 4, 2, 8
+    q, k, v = torch.randn(B, S, Hq, D), torch.randn(B, S, Hkv, D), torch.randn(B, S, Hkv, D)
+    o, lse = kernels.attention_reference(q, k, v, scale=1 / math.sqrt(D), causal=True)
+    ref = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2).repeat_interleave(2, 1),
+                                         v.transpose(1, 2).repeat_interleave(2, 1), is_causal=True).transpose(1, 2)
+    assert torch.allclose(o, ref, atol=1e-5)
+    # a very negative sink changes nothing; a large one shrinks the output
+    o2, _ = kernels.attention_reference(q, k, v, scale=1 / math.sqrt(D), causal=True, sink=torch.full((Hq,), -1e4))
+    assert torch.allclose(o2, o, atol=1e-5)
+    o3, _ = kernels.attention_reference(q, k, v, scale=1 / math.sqrt(D), causal=True, sink=torch.full((Hq,), 20.0))
+    assert o3.abs().max() < 1e-3 * max(o.abs().max(), 1.0) + 1e-3
+    # window: each query sees at most `window` keys
+    ow, _ = kernels.attention_reference(q, k, v, scale=1.0, causal=True, window=1)
+    assert torch.allclose(ow, v.repeat_interleave(2, 2), atol=1e-5)
