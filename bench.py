@@ -1,0 +1,231 @@
+"""Headline benchmark: Llama-3.1-8B-architecture pre-training step, train tokens/s.
+
+    python bench.py --gpus N --steps K --warmup W            (N = 1)
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Config (the Llama-3.1-8B row of the benchmark definition): 32 layers, hidden 4096, 32 q / 8 kv
+heads of 128, SwiGLU 14336, vocab 128256, seq 8192, 4 sequences per GPU per step (global batch
+32 at 8 GPUs, weak scaling), synthetic uniform token ids, random-init weights, bf16 compute,
+fp32 gradient accumulation and Adam moments, ZeRO-sharded optimizer over the data-parallel ranks.
+
+Two measurements per run, both K steps after W warm-up steps:
+  * ``value``: device-timed (CUDA events, max over ranks) with the step's tokens already on the
+    device and no host read inside the loop;
+  * ``e2e``: wall-clock around ``PretrainTrainer.train_step`` - the public call - including the
+    pinned-host -> device copy of each step's tokens and the device -> host read of its loss.
+Inputs (token ids) are tiny; the working set per step (16 GB of weights, 32 GB of gradients)
+is far larger than L2, which is what keeps timed iterations cold.
+
+``--impl reference`` would run the unmodified reference; it cannot be installed here (the tree has
+no setup.py / pyproject.toml and its stack is ROCm-only), so that arm prints an ``unavailable``
+line.  ``--impl baseline`` runs the same step with stock PyTorch modules (cuBLAS, SDPA, fused
+torch AdamW, DDP) for comparison on the same box.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "baseline"])
+    ap.add_argument("--model", default="llama3.1-8b")
+    ap.add_argument("--layers", type=int, default=0, help="override depth (debug only; marks the run reduced)")
+    ap.add_argument("--seq-len", type=int, default=0)
+    ap.add_argument("--local-batch", type=int, default=4)
+    ap.add_argument("--micro-batch", type=int, default=1)
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock / throttle reasons of this process's GPU with nvidia-smi while running."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid: str | None):
+        self.uuid = uuid
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        cmd = ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"]
+        if self.uuid:
+            cmd += ["-i", self.uuid]
+        try:
+            self.proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        threading.Thread(target=self._read, daemon=True).start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def main() -> int:
+    args = parse()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "reference is not installable (no setup.py/pyproject.toml; ROCm/HIP-only Primus+Megatron stack pinned by Dockerfiles)"}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device"}))
+        return 1
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if args.gpus != world and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE {world}", file=sys.stderr)
+
+    from mlperf_training_b200.models.gpt import PRESETS
+    from mlperf_training_b200.ops import _lib
+    from mlperf_training_b200.parallel.engine import OptimConfig
+    from mlperf_training_b200.trainer.pretrain import PretrainTrainer, TrainConfig, synthetic_tokens
+
+    cfg = PRESETS[args.model]()
+    reduced = False
+    if args.layers:
+        cfg.n_layers = args.layers; reduced = True
+    if args.seq_len:
+        cfg.seq_len = args.seq_len; reduced = True
+    opt = OptimConfig(lr=8e-4, beta1=0.9, beta2=0.95, eps=1e-5, weight_decay=0.1, clip_grad=1.0)
+    tc = TrainConfig(micro_batch=args.micro_batch, local_batch=args.local_batch, warmup_steps=64, seed=0)
+
+    if args.impl == "baseline":
+        from baseline.torch_gpt import BaselineTrainer
+        trainer = BaselineTrainer(cfg, opt, tc, device)
+    else:
+        trainer = PretrainTrainer(cfg, opt, tc, device)
+
+    K_, W_ = args.steps, args.warmup
+    tokens_per_step = args.local_batch * cfg.seq_len * world
+    host = synthetic_tokens(W_ + 2 * K_, args.local_batch, cfg.seq_len, cfg.vocab_size, seed=0, rank=rank)
+    dev_tokens = host[W_:W_ + K_].to(device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # warm-up through the public call
+    losses = []
+    for i in range(W_):
+        losses.append(trainer.train_step(host[i]))
+    barrier()
+
+    uuid = None
+    try:
+        uuid = "GPU-" + str(torch.cuda.get_device_properties(device).uuid)
+    except Exception:
+        uuid = None
+    sampler = ClockSampler(uuid)
+    sampler.start()
+
+    # (1) device-timed: tokens resident, no host read inside the loop
+    launches0 = _lib.launch_count() if args.impl == "b200" else 0
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    last = None
+    for i in range(K_):
+        last = trainer.train_step_device(dev_tokens[i])
+    ev1.record()
+    barrier()
+    dev_ms = ev0.elapsed_time(ev1)
+    launches = (_lib.launch_count() - launches0) if args.impl == "b200" else 0
+    clocks = sampler.stop()
+
+    # (2) end to end through the public API: H2D of the tokens and D2H of the loss every step
+    e2e = None
+    if not args.no_e2e:
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(K_):
+            losses.append(trainer.train_step(host[W_ + K_ + i]))
+        barrier()
+        e2e_s = time.perf_counter() - t0
+    t = torch.tensor([dev_ms, e2e_s if not args.no_e2e else 0.0], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_s = float(t[0]), float(t[1])
+
+    if args.impl == "b200":
+        _lib.check_status("bench")
+    if rank == 0:
+        ms_per_step = dev_ms / K_
+        value = tokens_per_step / (ms_per_step / 1e3)
+        out = {
+            "metric": "train tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K_,
+            "warmup": W_, "ms_per_step": round(ms_per_step, 2), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids (seed 0), random-init weights",
+            "impl": args.impl,
+            "config": {"model": cfg.name, "layers": cfg.n_layers, "global_batch": args.local_batch * world,
+                       "seq_len": cfg.seq_len, "micro_batch": args.micro_batch,
+                       "parallelism": f"dp{world} (ZeRO-sharded optimizer)",
+                       "l2": "no flush: per-step working set (>48 GB of weights and gradients) exceeds L2",
+                       "reduced": reduced},
+            "clocks": clocks, "gpu_launches": int(launches),
+            "model_tflops_per_gpu": round(cfg.flops_per_token() * tokens_per_step / world / (ms_per_step / 1e3) / 1e12, 1),
+            "loss_first": round(losses[0], 4) if losses else None, "loss_last": round(losses[-1], 4) if losses else None,
+        }
+        if not args.no_e2e:
+            bi = int(host[0].numel() * host[0].element_size())
+            out["e2e"] = {"value": round(tokens_per_step * K_ / e2e_s, 1), "unit": "tokens/s",
+                          "h2d_bytes_per_step": bi, "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_s * 1e3 / K_, 2)}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

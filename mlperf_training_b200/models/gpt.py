@@ -1,0 +1,239 @@
+"""Decoder-only GPT family: Llama-3.1-8B, Llama-2-70B (dense) and GPT-OSS-20B (MoE) architectures.
+
+RMSNorm -> fused QKV GEMM -> RoPE -> flash attention (causal, GQA, optional sliding window and
+learned sink logits) -> output GEMM with the residual add in its epilogue -> RMSNorm -> SwiGLU MLP
+(dense or routed experts) -> residual; final norm, untied vocabulary GEMM and fused cross-entropy.
+
+The reference takes this model from Megatron-Core's ``GPTModel`` through Primus model presets;
+the in-tree YAMLs only override it (small_llm_pretraining/primus/conf/llama3.1_8B-pretrain-fp4.yaml:12,44-45;
+small_llm_moe_pretraining/primus/conf/gpt_oss_20B-MXFP4-deosc-mlperf-pretrain.yaml:19-33,115-167;
+llama2_sft/primus/src/llama2_custom.py:496-500).  Activations are 2-D ``[tokens, features]``
+throughout so every GEMM sees one large M.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field, asdict
+
+import torch
+import torch.nn as nn
+
+from ..ops import functional as F
+from ..ops import kernels as K
+
+
+@dataclass
+class GPTConfig:
+    name: str = "gpt"
+    n_layers: int = 2
+    hidden: int = 256
+    n_heads: int = 8
+    n_kv_heads: int = 2
+    head_dim: int = 32
+    ffn_hidden: int = 512
+    vocab_size: int = 2048
+    seq_len: int = 256
+    rope_theta: float = 10000.0
+    norm_eps: float = 1e-5
+    init_std: float = 0.02
+    # attention variants
+    window: int = 0                 # sliding-window length (0 = full attention)
+    window_layers: str = "none"     # "none" | "even" | "all": which layers use the window
+    sink: bool = False              # learned per-head sink logits
+    # mixture of experts (0 experts = dense MLP)
+    n_experts: int = 0
+    top_k: int = 0
+    moe_ffn_hidden: int = 0
+    router_dtype: str = "fp32"
+    # LoRA (rank 0 = off)
+    lora_rank: int = 0
+    lora_alpha: float = 32.0
+    lora_dropout: float = 0.0
+    lora_targets: tuple = ("qkv", "proj")
+    dtype: str = "bf16"
+
+    def torch_dtype(self) -> torch.dtype:
+        return {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}[self.dtype]
+
+    def layer_window(self, layer: int) -> int:
+        if self.window <= 0 or self.window_layers == "none":
+            return 0
+        if self.window_layers == "all":
+            return self.window
+        return self.window if layer % 2 == 0 else 0
+
+    def num_params(self) -> int:
+        d, hd = self.hidden, self.head_dim
+        attn = d * (self.n_heads + 2 * self.n_kv_heads) * hd + self.n_heads * hd * d
+        if self.n_experts:
+            mlp = self.n_experts * 3 * d * self.moe_ffn_hidden + d * self.n_experts
+        else:
+            mlp = 3 * d * self.ffn_hidden
+        per_layer = attn + mlp + 2 * d + (self.n_heads if self.sink else 0)
+        return self.n_layers * per_layer + 2 * self.vocab_size * d + d
+
+    def flops_per_token(self, seq_len: int | None = None) -> float:
+        """Model FLOPs per trained token (fwd + bwd = 3 x fwd), GEMMs plus causal attention."""
+        s = seq_len or self.seq_len
+        d, hd = self.hidden, self.head_dim
+        attn_proj = d * (self.n_heads + 2 * self.n_kv_heads) * hd + self.n_heads * hd * d
+        mlp = (self.top_k * 3 * d * self.moe_ffn_hidden + d * self.n_experts) if self.n_experts else 3 * d * self.ffn_hidden
+        gemm = 2 * (self.n_layers * (attn_proj + mlp) + self.vocab_size * d)
+        attn = 0.0
+        for layer in range(self.n_layers):
+            w = self.layer_window(layer)
+            keys = min(w, s) if w else s / 2
+            attn += 4 * self.n_heads * hd * keys
+        return 3 * gemm + 3.5 * attn
+
+    def to_dict(self) -> dict:
+        return asdict(self)
+
+
+def llama31_8b(**over) -> GPTConfig:
+    return GPTConfig(name="llama3.1-8b", n_layers=32, hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128,
+                     ffn_hidden=14336, vocab_size=128256, seq_len=8192, rope_theta=500000.0, norm_eps=1e-5,
+                     init_std=0.02, **over)
+
+
+def llama2_70b(**over) -> GPTConfig:
+    return GPTConfig(name="llama2-70b", n_layers=80, hidden=8192, n_heads=64, n_kv_heads=8, head_dim=128,
+                     ffn_hidden=28672, vocab_size=32000, seq_len=8192, rope_theta=10000.0, norm_eps=1e-5,
+                     init_std=0.02, **over)
+
+
+def gpt_oss_20b(**over) -> GPTConfig:
+    return GPTConfig(name="gpt-oss-20b", n_layers=24, hidden=2880, n_heads=64, n_kv_heads=8, head_dim=64,
+                     ffn_hidden=2880, vocab_size=201088, seq_len=8192, rope_theta=150000.0, norm_eps=1e-6,
+                     init_std=0.008, window=128, window_layers="even", sink=True, n_experts=32, top_k=4,
+                     moe_ffn_hidden=2880, **over)
+
+
+def tiny_moe(**over) -> GPTConfig:
+    """The CPU plumbing config: 4 layers, d 256, 8q/2kv heads of 32, 8 experts top-2, vocab 2048."""
+    base = dict(name="tiny-moe", n_layers=4, hidden=256, n_heads=8, n_kv_heads=2, head_dim=32, ffn_hidden=512,
+                vocab_size=2048, seq_len=256, rope_theta=10000.0, init_std=0.02, window=128, window_layers="even",
+                n_experts=8, top_k=2, moe_ffn_hidden=512, dtype="fp32")
+    base.update(over)
+    return GPTConfig(**base)
+
+
+PRESETS = {"llama3.1-8b": llama31_8b, "llama2-70b": llama2_70b, "gpt-oss-20b": gpt_oss_20b, "tiny-moe": tiny_moe}
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float, dtype, device):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device))
+        self.eps = eps
+
+    def forward(self, x):
+        return F.rms_norm(x, self.weight, self.eps)
+
+
+class DenseMLP(nn.Module):
+    """gate/up projection as one GEMM ([2F, D], gate rows first), SwiGLU, down projection."""
+
+    def __init__(self, cfg: GPTConfig, dtype, device):
+        super().__init__()
+        d, f = cfg.hidden, cfg.ffn_hidden
+        self.w_gate_up = nn.Parameter(torch.empty(2 * f, d, dtype=dtype, device=device))
+        self.w_down = nn.Parameter(torch.empty(d, f, dtype=dtype, device=device))
+
+    def forward(self, h, norm_w, eps):
+        gu = F.norm_linear(h, norm_w, self.w_gate_up, eps=eps)
+        return F.swiglu_linear(gu, self.w_down, residual=h)
+
+
+class Block(nn.Module):
+    def __init__(self, cfg: GPTConfig, layer: int, dtype, device, mlp: nn.Module | None = None):
+        super().__init__()
+        self.cfg = cfg
+        self.layer = layer
+        d, hd = cfg.hidden, cfg.head_dim
+        self.attn_norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
+        self.w_qkv = nn.Parameter(torch.empty((cfg.n_heads + 2 * cfg.n_kv_heads) * hd, d, dtype=dtype, device=device))
+        self.w_proj = nn.Parameter(torch.empty(d, cfg.n_heads * hd, dtype=dtype, device=device))
+        self.sink = nn.Parameter(torch.zeros(cfg.n_heads, dtype=torch.float32, device=device)) if cfg.sink else None
+        self.mlp_norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
+        if mlp is not None:
+            self.mlp = mlp
+        elif cfg.n_experts:
+            from .moe import MoEMLP
+            self.mlp = MoEMLP(cfg, dtype, device)
+        else:
+            self.mlp = DenseMLP(cfg, dtype, device)
+        self.lora_qkv = self.lora_proj = None
+        if cfg.lora_rank > 0:
+            from .lora import LoRAAdapter
+            if "qkv" in cfg.lora_targets:
+                self.lora_qkv = LoRAAdapter(d, self.w_qkv.shape[0], cfg.lora_rank, cfg.lora_alpha, cfg.lora_dropout,
+                                            dtype, device)
+            if "proj" in cfg.lora_targets:
+                self.lora_proj = LoRAAdapter(cfg.n_heads * hd, d, cfg.lora_rank, cfg.lora_alpha, cfg.lora_dropout,
+                                             dtype, device)
+
+    def forward(self, x, cos, sin, B, S):
+        cfg = self.cfg
+        if self.lora_qkv is None:
+            qkv = F.norm_linear(x, self.attn_norm, self.w_qkv, eps=cfg.norm_eps)
+        else:
+            xn = F.rms_norm(x, self.attn_norm, cfg.norm_eps)
+            qkv = F.linear(xn, self.w_qkv) + self.lora_qkv(xn)
+        a = F.attention_packed(qkv, B=B, S=S, Hq=cfg.n_heads, Hkv=cfg.n_kv_heads, D=cfg.head_dim, cos=cos, sin=sin,
+                               sink=self.sink, causal=True, window=cfg.layer_window(self.layer))
+        if self.lora_proj is None:
+            h = F.linear(a, self.w_proj, None, x)
+        else:
+            h = F.linear(a, self.w_proj, None, x) + self.lora_proj(a)
+        return self.mlp(h, self.mlp_norm, cfg.norm_eps)
+
+
+class GPT(nn.Module):
+    """``forward(tokens [B,S], labels [B,S]) -> mean cross-entropy`` (labels -100 are ignored)."""
+
+    def __init__(self, cfg: GPTConfig, device="cpu", seed: int = 0):
+        super().__init__()
+        self.cfg = cfg
+        dtype = cfg.torch_dtype()
+        self.embed = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden, dtype=dtype, device=device))
+        self.blocks = nn.ModuleList([Block(cfg, i, dtype, device) for i in range(cfg.n_layers)])
+        self.final_norm = nn.Parameter(torch.ones(cfg.hidden, dtype=dtype, device=device))
+        self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden, dtype=dtype, device=device))
+        self._rope = None
+        self.reset_parameters(seed)
+
+    @torch.no_grad()
+    def reset_parameters(self, seed: int = 0) -> None:
+        """N(0, init_std) for matrices (output projections scaled by 1/sqrt(2 L) as Megatron
+        does), ones for norm weights, zeros for sinks and LoRA B."""
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        std = self.cfg.init_std
+        out_std = std / math.sqrt(2.0 * self.cfg.n_layers)
+        for name, p in self.named_parameters():
+            if p.dim() < 2:
+                continue
+            if "lora" in name:
+                continue
+            s = out_std if (name.endswith("w_proj") or name.endswith("w_down") or name.endswith("w2")) else std
+            if p.device.type == "cpu":
+                p.normal_(0.0, s, generator=gen)
+            else:
+                g = torch.Generator(device=p.device).manual_seed(seed + (hash(name) & 0xFFFF))
+                p.normal_(0.0, s, generator=g)
+
+    def rope(self, device):
+        if self._rope is None or self._rope[0].device != torch.device(device):
+            self._rope = K.rope_tables(self.cfg.seq_len, self.cfg.head_dim, self.cfg.rope_theta, device)
+        return self._rope
+
+    def forward(self, tokens: torch.Tensor, labels: torch.Tensor, n_valid: int | None = None) -> torch.Tensor:
+        B, S = tokens.shape
+        cos, sin = self.rope(tokens.device)
+        if S > cos.shape[0]:
+            raise ValueError(f"sequence {S} longer than the configured {cos.shape[0]}")
+        x = F.embedding(tokens.reshape(-1), self.embed)
+        for blk in self.blocks:
+            x = blk(x, cos, sin, B, S)
+        return F.lm_head_loss(x, self.final_norm, self.lm_head, labels.reshape(-1), eps=self.cfg.norm_eps,
+                              n_valid=n_valid)

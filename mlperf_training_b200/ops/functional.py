@@ -1,0 +1,332 @@
+"""Autograd layer over the raw operators of ``ops.kernels``.
+
+Every Function works on 2-D ``[tokens, features]`` activations.  Weight gradients follow the
+"gradient accumulation fusion" convention of the reference's Megatron configs
+(small_llm_pretraining/primus/conf/llama3.1_8B-pretrain-fp4.yaml:59-61): when a parameter
+carries a ``main_grad`` tensor (fp32 or bf16 view into the flat gradient buffer of the
+optimizer / FSDP engine), the wgrad GEMM adds straight into it from its epilogue and autograd
+receives no gradient for that parameter.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch.autograd import Function
+
+from . import kernels as K
+
+
+def _wgrad(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor):
+    """dW = dy^T x, accumulated into ``weight.main_grad`` when present (returns None then)."""
+    if not weight.requires_grad:
+        return None
+    mg = getattr(weight, "main_grad", None)
+    if mg is not None:
+        K.gemm(dy, x, a_mn_major=True, b_mn_major=True, out=mg, accumulate=True)
+        if hasattr(weight, "grad_added_to_main_grad"):
+            weight.grad_added_to_main_grad = True
+        return None
+    return K.gemm(dy, x, a_mn_major=True, b_mn_major=True, out_dtype=weight.dtype)
+
+
+def _vec_grad(param: torch.Tensor | None, g: torch.Tensor | None):
+    """Route a small (norm weight / bias) gradient to main_grad when present."""
+    if param is None or g is None or not param.requires_grad:
+        return None
+    mg = getattr(param, "main_grad", None)
+    if mg is not None:
+        mg.add_(g.to(mg.dtype))
+        return None
+    return g.to(param.dtype)
+
+
+class LinearFn(Function):
+    """y = x W^T (+ bias) (+ residual), the residual add done in the GEMM epilogue."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual):
+        ctx.save_for_backward(x, weight)
+        ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
+        ctx.bias_ref = bias
+        return K.gemm(x, weight, bias=bias, residual=residual)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = K.gemm(dy, weight, b_mn_major=True) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(dy, x, weight)
+        db = _vec_grad(ctx.bias_ref, dy.float().sum(0)) if ctx.has_bias else None
+        dres = dy if ctx.has_res and ctx.needs_input_grad[3] else None
+        return dx, dw, db, dres
+
+
+def linear(x, weight, bias=None, residual=None):
+    return LinearFn.apply(x, weight, bias, residual)
+
+
+class NormFn(Function):
+    """RMSNorm / LayerNorm / SwishLayerNorm on rows."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps, layer_norm, swish):
+        y, h, mean, rstd = K.norm_fwd(x, weight, bias, eps, layer_norm=layer_norm, swish=swish)
+        ctx.save_for_backward(x, weight, bias, mean, rstd)
+        ctx.cfg = (layer_norm, swish)
+        ctx.refs = (weight, bias)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, bias, mean, rstd = ctx.saved_tensors
+        layer_norm, swish = ctx.cfg
+        dx, dw, db = K.norm_bwd(dy.contiguous(), x, weight, bias, mean, rstd, layer_norm=layer_norm, swish=swish)
+        return dx, _vec_grad(ctx.refs[0], dw), _vec_grad(ctx.refs[1], db), None, None, None
+
+
+def rms_norm(x, weight, eps=1e-5):
+    return NormFn.apply(x, weight, None, eps, False, False)
+
+
+def layer_norm(x, weight, bias, eps=1e-5):
+    return NormFn.apply(x, weight, bias, eps, True, False)
+
+
+def swish_layer_norm(x, weight, bias, eps=1e-5):
+    return NormFn.apply(x, weight, bias, eps, True, True)
+
+
+class NormLinearFn(Function):
+    """y = norm(x) W^T with the normalised activation recomputed in backward instead of saved
+    (the "fused residual + RMSNorm -> GEMM" pairing of the reference's Turbo configs,
+    small_llm_pretraining/primus/config_MI355X_1x8x1.sh:42-51)."""
+
+    @staticmethod
+    def forward(ctx, x, norm_w, norm_b, weight, bias, eps, layer_norm):
+        xn, _, mean, rstd = K.norm_fwd(x, norm_w, norm_b, eps, layer_norm=layer_norm)
+        y = K.gemm(xn, weight, bias=bias)
+        ctx.save_for_backward(x, norm_w, norm_b, weight, mean, rstd)
+        ctx.cfg = (eps, layer_norm)
+        ctx.refs = (norm_w, norm_b, bias)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, norm_w, norm_b, weight, mean, rstd = ctx.saved_tensors
+        eps, layer_norm = ctx.cfg
+        dy = dy.contiguous()
+        xn = K.norm_fwd(x, norm_w, norm_b, eps, layer_norm=layer_norm)[0]
+        dw = _wgrad(dy, xn, weight)
+        del xn
+        dxn = K.gemm(dy, weight, b_mn_major=True)
+        dx, dnw, dnb = K.norm_bwd(dxn, x, norm_w, norm_b, mean, rstd, layer_norm=layer_norm)
+        db = _vec_grad(ctx.refs[2], dy.float().sum(0)) if ctx.refs[2] is not None else None
+        return dx, _vec_grad(ctx.refs[0], dnw), _vec_grad(ctx.refs[1], dnb), dw, db, None, None
+
+
+def norm_linear(x, norm_w, weight, *, norm_b=None, bias=None, eps=1e-5, layer_norm=False):
+    return NormLinearFn.apply(x, norm_w, norm_b, weight, bias, eps, layer_norm)
+
+
+class SwiGLULinearFn(Function):
+    """out = swiglu(gu) W^T + residual, saving only ``gu`` (the activation is recomputed)."""
+
+    @staticmethod
+    def forward(ctx, gu, weight, residual):
+        a = K.swiglu_fwd(gu)
+        out = K.gemm(a, weight, residual=residual)
+        ctx.save_for_backward(gu, weight)
+        ctx.has_res = residual is not None
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        gu, weight = ctx.saved_tensors
+        dy = dy.contiguous()
+        a = K.swiglu_fwd(gu)
+        dw = _wgrad(dy, a, weight)
+        del a
+        da = K.gemm(dy, weight, b_mn_major=True)
+        dgu = K.swiglu_bwd(da, gu)
+        return dgu, dw, (dy if ctx.has_res else None)
+
+
+def swiglu_linear(gu, weight, residual=None):
+    return SwiGLULinearFn.apply(gu, weight, residual)
+
+
+class SwiGLUFn(Function):
+    @staticmethod
+    def forward(ctx, gu):
+        ctx.save_for_backward(gu)
+        return K.swiglu_fwd(gu)
+
+    @staticmethod
+    def backward(ctx, da):
+        (gu,) = ctx.saved_tensors
+        return K.swiglu_bwd(da.contiguous(), gu)
+
+
+def swiglu(gu):
+    return SwiGLUFn.apply(gu)
+
+
+class GeluFn(Function):
+    @staticmethod
+    def forward(ctx, x):
+        ctx.save_for_backward(x)
+        return K.gelu_fwd(x)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        return K.gelu_bwd(dy.contiguous(), x)
+
+
+def gelu(x):
+    return GeluFn.apply(x)
+
+
+class AttentionFn(Function):
+    """Rotary embedding + flash attention on a packed ``[T, (Hq + 2 Hkv) * D]`` QKV buffer
+    (T = B * S).  The rotation is applied in place to the q and k columns; backward produces the
+    packed gradient buffer directly (dk/dv written by the kernel into their columns)."""
+
+    @staticmethod
+    def forward(ctx, qkv, sink, cos, sin, B, S, Hq, Hkv, D, causal, window, scale):
+        qkv = qkv.contiguous()
+        if cos is not None:
+            K.rope_(qkv, cos, sin, col0=0, n_heads=Hq + Hkv, head_dim=D, seq_len=S)
+        v3 = qkv.view(B, S, -1)
+        q = v3[:, :, :Hq * D].unflatten(-1, (Hq, D))
+        k = v3[:, :, Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+        v = v3[:, :, (Hq + Hkv) * D:].unflatten(-1, (Hkv, D))
+        out, lse = K.attention_fwd(q, k, v, scale=scale, causal=causal, window=window, sink=sink)
+        ctx.save_for_backward(qkv, out, lse, sink, cos, sin)
+        ctx.cfg = (B, S, Hq, Hkv, D, causal, window, scale)
+        return out.view(B * S, Hq * D)
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse, sink, cos, sin = ctx.saved_tensors
+        B, S, Hq, Hkv, D, causal, window, scale = ctx.cfg
+        v3 = qkv.view(B, S, -1)
+        q = v3[:, :, :Hq * D].unflatten(-1, (Hq, D))
+        k = v3[:, :, Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+        v = v3[:, :, (Hq + Hkv) * D:].unflatten(-1, (Hkv, D))
+        dqkv = torch.empty_like(qkv)
+        d3 = dqkv.view(B, S, -1)
+        dk = d3[:, :, Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+        dv = d3[:, :, (Hq + Hkv) * D:].unflatten(-1, (Hkv, D))
+        dq, _, _, dsink = K.attention_bwd(dout.contiguous().view(B, S, Hq, D), q, k, v, out, lse, scale=scale,
+                                          causal=causal, window=window, sink=sink, dk_out=dk, dv_out=dv)
+        d3[:, :, :Hq * D].copy_(dq.reshape(B, S, Hq * D))
+        if cos is not None:
+            K.rope_(dqkv, cos, sin, col0=0, n_heads=Hq + Hkv, head_dim=D, seq_len=S, backward=True)
+        if sink is not None and dsink is not None:
+            dsink = dsink.to(sink.dtype)
+        return dqkv, dsink, None, None, None, None, None, None, None, None, None, None
+
+
+def attention_packed(qkv, *, B, S, Hq, Hkv, D, cos=None, sin=None, sink=None, causal=True, window=0, scale=None):
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    return AttentionFn.apply(qkv, sink, cos, sin, B, S, Hq, Hkv, D, causal, window, scale)
+
+
+class AttentionBSHDFn(Function):
+    """Flash attention on separate ``[B, S, H, D]`` tensors (MMDiT joint attention, tests)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, sink, causal, window, scale):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out, lse = K.attention_fwd(q, k, v, scale=scale, causal=causal, window=window, sink=sink)
+        ctx.save_for_backward(q, k, v, out, lse, sink)
+        ctx.cfg = (causal, window, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, sink = ctx.saved_tensors
+        causal, window, scale = ctx.cfg
+        dq, dk, dv, dsink = K.attention_bwd(dout.contiguous(), q, k, v, out, lse, scale=scale, causal=causal,
+                                            window=window, sink=sink)
+        return dq.to(q.dtype), dk, dv, (None if dsink is None else dsink.to(sink.dtype)), None, None, None
+
+
+def attention(q, k, v, *, causal=True, window=0, sink=None, scale=None):
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    return AttentionBSHDFn.apply(q, k, v, sink, causal, window, scale)
+
+
+class EmbeddingFn(Function):
+    @staticmethod
+    def forward(ctx, ids, table):
+        ctx.save_for_backward(ids)
+        ctx.table = table
+        return K.gather_rows(table, ids.view(-1))
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        table = ctx.table
+        mg = getattr(table, "main_grad", None)
+        if mg is not None and mg.dtype == torch.float32:
+            K.scatter_add_rows(mg, ids.view(-1), dy.contiguous())
+            return None, None
+        g = torch.zeros(table.shape, dtype=torch.float32, device=table.device)
+        K.scatter_add_rows(g, ids.view(-1), dy.contiguous())
+        if mg is not None:
+            mg.add_(g.to(mg.dtype))
+            return None, None
+        return None, g.to(table.dtype)
+
+
+def embedding(ids, table):
+    return EmbeddingFn.apply(ids, table)
+
+
+class LMHeadLossFn(Function):
+    """loss = mean CE(norm(x) W^T, labels): final norm, vocabulary GEMM and fused cross-entropy.
+    The logits buffer is overwritten with its own gradient during forward, so backward starts
+    from dlogits without recomputing the softmax."""
+
+    @staticmethod
+    def forward(ctx, x, norm_w, weight, labels, eps, loss_mask_count):
+        xn, _, _, rstd = K.norm_fwd(x, norm_w, None, eps)
+        logits = K.gemm(xn, weight)
+        n_valid = loss_mask_count if loss_mask_count is not None else max(int(labels.numel()), 1)
+        losses = K.cross_entropy_(logits, labels.view(-1), 1.0 / n_valid, write_grad=True)
+        ctx.save_for_backward(x, norm_w, weight, rstd, logits)
+        ctx.eps = eps
+        ctx.refs = (norm_w,)
+        return losses.sum() / n_valid
+
+    @staticmethod
+    def backward(ctx, dloss):
+        x, norm_w, weight, rstd, dlogits = ctx.saved_tensors
+        if dloss.numel() != 1:
+            raise RuntimeError("LMHeadLossFn expects a scalar upstream gradient")
+        xn = K.norm_fwd(x, norm_w, None, ctx.eps)[0]
+        scale = dloss.reshape(())
+        # upstream gradient other than 1 (loss scaling, grad accumulation weights) is applied to dlogits
+        dl = dlogits if _is_one(scale) else (dlogits.float() * scale).to(dlogits.dtype)
+        dw = _wgrad(dl, xn, weight)
+        del xn
+        dxn = K.gemm(dl, weight, b_mn_major=True)
+        dx, dnw, _ = K.norm_bwd(dxn, x, norm_w, None, None, rstd)
+        return dx, _vec_grad(ctx.refs[0], dnw), dw, None, None, None
+
+
+def _is_one(t: torch.Tensor) -> bool:
+    # a host read on CPU only; on CUDA the multiply is always done by the caller's choice below
+    if t.is_cuda:
+        return getattr(_is_one, "assume_unit", True)
+    return float(t) == 1.0
+
+
+def lm_head_loss(x, norm_w, weight, labels, *, eps=1e-5, n_valid=None):
+    return LMHeadLossFn.apply(x, norm_w, weight, labels, eps, n_valid)

@@ -25,7 +25,14 @@ def _row_major(t: torch.Tensor) -> torch.Tensor:
         raise ValueError(f"expected a 2-D tensor, got shape {tuple(t.shape)}")
     esz = t.element_size()
     if t.stride(1) != 1 or (t.stride(0) * esz) % 16 != 0 or t.data_ptr() % 16 != 0 or t.stride(0) < t.shape[1]:
-        t = t.contiguous()
+        per16 = 16 // esz
+        cols = (t.shape[1] + per16 - 1) // per16 * per16
+        if cols == t.shape[1]:
+            t = t.contiguous()
+        else:  # TMA needs a 16-byte row pitch: copy into a padded buffer and view the valid columns
+            buf = torch.zeros((t.shape[0], cols), dtype=t.dtype, device=t.device)
+            buf[:, :t.shape[1]].copy_(t)
+            t = buf[:, :t.shape[1]]
     return t
 
 
@@ -33,7 +40,7 @@ def _row_major(t: torch.Tensor) -> torch.Tensor:
 # GEMM
 # --------------------------------------------------------------------------------------
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
-         out: torch.Tensor | None = None, out_dtype: torch.dtype = BF16, accumulate: bool = False,
+         out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None, accumulate: bool = False,
          bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
          alpha: float = 1.0) -> torch.Tensor:
     """``D[M,N] (+)= alpha * A @ B^T (+ bias[N]) (+ residual[M,N])`` with bf16 operands.
@@ -49,6 +56,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
         raise ValueError(f"gemm: contraction mismatch {K} vs {Kb}")
     if out is not None:
         out_dtype = out.dtype
+    elif out_dtype is None:
+        out_dtype = a.dtype
     if not use_kernels(a):
         am = a.float().t() if a_mn_major else a.float()
         bm = b.float() if b_mn_major else b.float().t()
@@ -436,7 +445,7 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: f
         scale = 1.0 / math.sqrt(D)
     if not use_kernels(q):
         o, lse = attention_reference(q, k, v, scale=scale, causal=causal, window=window, sink=sink)
-        return o.to(q.dtype), lse
+        return o.to(q.dtype).contiguous(), lse
     for t in (q, k, v):
         if t.stride(3) != 1 or t.stride(2) != D:
             raise ValueError("attention_fwd: heads must be contiguous inside a token row")
