@@ -34,11 +34,6 @@ struct BwdParams {
   int* status;
 };
 
-B200_DEVICE float ex2(float x) {
-  float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 B200_DEVICE void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
@@ -183,15 +178,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_commit(sdp_full);
         if (!mbar_wait(pds_full, ph, abort_flag, p.status, 83)) { ok = false; break; }
         tc_fence_after();
-        // dQ = dS K : A = dS [q][key] K-major, B = K [key][d] MN-major (contraction over keys)
-#pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) {
-          const uint32_t ao = (kk / 4) * (128 * 128) + (kk % 4) * 32;
-          const uint32_t bo = kk * (16 * 128);
-          tc_mma_f16_ss(tm_S, umma_desc_sw128(adS + ao, 16, 1024), umma_desc_sw128(aK + bo, 128 * 128, 1024), id_dq,
-                        kk > 0);
-        }
-        tc_commit(dq_full);
         // dV += P^T dO ; dK += dS^T Q : contraction over queries, both operands MN-major
 #pragma unroll
         for (int kk = 0; kk < BQ / 16; ++kk) {
@@ -205,7 +191,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tc_mma_f16_ss(tm_dK, umma_desc_sw128(adS + o, 128 * 128, 1024), umma_desc_sw128(aQ + o, 128 * 128, 1024),
                         id_tt, (it > 0 || kk > 0));
         }
-        tc_commit(qdo_empty);
+        tc_commit(qdo_empty);  // Q_i / dO_i may be overwritten: the next tiles load during the dQ GEMM
+        // dQ = dS K : A = dS [q][key] K-major, B = K [key][d] MN-major (contraction over keys)
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {
+          const uint32_t ao = (kk / 4) * (128 * 128) + (kk % 4) * 32;
+          const uint32_t bo = kk * (16 * 128);
+          tc_mma_f16_ss(tm_S, umma_desc_sw128(adS + ao, 16, 1024), umma_desc_sw128(aK + bo, 128 * 128, 1024), id_dq,
+                        kk > 0);
+        }
+        tc_commit(dq_full);    // also: P / dS shared-memory tiles are free again
       }
       if (ok) tc_commit(acc_done);
     }
@@ -235,7 +230,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!mbar_wait(sdp_full, it & 1, abort_flag, p.status, 90)) { ok = false; break; }
       tc_fence_after();
       // P / dS buffers are free once the previous iteration's MMAs have read them
-      if (it > 0 && !mbar_wait(qdo_empty, (it - 1) & 1, abort_flag, p.status, 91)) { ok = false; break; }
+      if (it > 0 && !mbar_wait(dq_full, (it - 1) & 1, abort_flag, p.status, 91)) { ok = false; break; }
       uint8_t* prow = sP + r * 128;
       uint8_t* drow = sdS + r * 128;
 #pragma unroll 1
@@ -245,15 +240,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_32x32b_x32(tm_dP + lane_base + c * 32, d);
         tc_wait_ld();
         float pv[32], dv[32];
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2);
+        const float2 s2 = make_float2(p.scale, p.scale), nd2 = make_float2(-dl * p.scale, -dl * p.scale);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float pe = ex2(__uint_as_float(s[i]) * p.scale_log2 - lse2);
+        for (int i = 0; i < 32; i += 2) {
+          const float2 a = ffma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, nl2);
+          float p0 = ex2_approx(a.x), p1 = ex2_approx(a.y);
           if (need_mask) {
             const int kp = kv0 + c * 32 + i;
-            if (!row_ok || kp > hi || kp < lo) pe = 0.f;
+            if (!row_ok || kp > hi || kp < lo) p0 = 0.f;
+            if (!row_ok || kp + 1 > hi || kp + 1 < lo) p1 = 0.f;
           }
-          pv[i] = pe;
-          dv[i] = pe * (__uint_as_float(d[i]) - dl) * p.scale;
+          const float2 t2 = ffma2(make_float2(__uint_as_float(d[i]), __uint_as_float(d[i + 1])), s2, nd2);
+          const float2 g2 = fmul2(make_float2(p0, p1), t2);
+          pv[i] = p0; pv[i + 1] = p1;
+          dv[i] = g2.x; dv[i + 1] = g2.y;
         }
         uint8_t* pb = prow + (c / 2) * (BQ * 128);
         uint8_t* db = drow + (c / 2) * (BQ * 128);

@@ -90,6 +90,20 @@ B200_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint (ns): the hardware parks the thread until the phase
+// completes or the hint expires, so a waiting role does not burn issue slots of the warps that
+// share its scheduler.
+B200_DEVICE bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 
 // Bounded wait.  Returns true when the phase completed, false when the wait was given up
 // (time limit reached or another role already raised *abort).  On a time-out it records
@@ -99,8 +113,8 @@ B200_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_f
   uint64_t t0 = 0;
   uint32_t it = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++it & 0xff) == 0) {
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+    if ((++it & 0xf) == 0) {
       if (*abort_flag) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
@@ -287,6 +301,73 @@ B200_DEVICE void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+
+B200_DEVICE void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// packed two-wide fp32 arithmetic (sm_100 f32x2 instructions): one issue slot for two lanes
+B200_DEVICE float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+B200_DEVICE float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+B200_DEVICE float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+B200_DEVICE float ex2_approx(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 2^x for a pair of values without the MUFU unit and without float<->int conversions (which also
+// run on the XU pipe): round to nearest with the 1.5 * 2^23 magic constant, a degree-3 polynomial
+// for 2^f on [-0.5, 0.5] (relative error < 7e-4, below bf16 resolution), and the integer part
+// added to the exponent field.  Used for a share of the softmax exponentials so that the
+// 16/clk/SM MUFU unit is not the only exponent engine.
+B200_DEVICE float2 ex2_poly2(float2 x) {
+  const float magic = 12582912.f;
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = fadd2(x, make_float2(magic, magic));
+  const float2 r = fadd2(t, make_float2(-magic, -magic));
+  const float2 f = fadd2(x, make_float2(-r.x, -r.y));
+  float2 p = ffma2(f, make_float2(0.05550411f, 0.05550411f), make_float2(0.24022651f, 0.24022651f));
+  p = ffma2(p, f, make_float2(0.69314718f, 0.69314718f));
+  p = ffma2(p, f, make_float2(1.0f, 1.0f));
+  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
+                     __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
+}
+template <int N>
+B200_DEVICE void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+B200_DEVICE void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 // ----------------------------------------------------------------------------------
 // UMMA descriptors (sm_100 shared-memory matrix descriptor, version 1)

@@ -27,8 +27,14 @@ def flush_l2() -> None:
     _FLUSH.zero_()
 
 
-def time_ms(fn, iters: int = 10, warmup: int = 3) -> float:
+ITERS = 10
+WARMUP = 3
+
+
+def time_ms(fn, iters: int | None = None, warmup: int | None = None) -> float:
     """Median device time of ``fn`` in milliseconds, L2 flushed before every timed launch."""
+    iters = ITERS if iters is None else min(iters, ITERS)
+    warmup = WARMUP if warmup is None else min(warmup, WARMUP)
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -154,7 +160,11 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("what", nargs="*", default=["gemm", "attention", "elementwise"])
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--iters", type=int, default=10, help="timed launches per measurement")
+    ap.add_argument("--warmup", type=int, default=3, help="untimed launches per measurement")
     args = ap.parse_args(argv)
+    global ITERS, WARMUP
+    ITERS, WARMUP = max(args.iters, 1), max(args.warmup, 0)
     if not torch.cuda.is_available():
         print("microbench needs a CUDA device", file=sys.stderr)
         return 1
