@@ -48,6 +48,8 @@ def parse():
     ap.add_argument("--local-batch", type=int, default=4)
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--precision", default="mxfp8", choices=["mxfp8", "bf16"],
+                    help="GEMM precision of the linears (attention, norms, residual stream stay bf16)")
     return ap.parse_args()
 
 
@@ -137,6 +139,7 @@ def main() -> int:
         cfg.n_layers = args.layers; reduced = True
     if args.seq_len:
         cfg.seq_len = args.seq_len; reduced = True
+    cfg.precision = args.precision if args.impl == "b200" else "bf16"
     opt = OptimConfig(lr=8e-4, beta1=0.9, beta2=0.95, eps=1e-5, weight_decay=0.1, clip_grad=1.0)
     tc = TrainConfig(micro_batch=args.micro_batch, local_batch=args.local_batch, warmup_steps=64, seed=0)
 
@@ -206,7 +209,9 @@ def main() -> int:
         out = {
             "metric": "train tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K_,
             "warmup": W_, "ms_per_step": round(ms_per_step, 2), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids (seed 0), random-init weights",
+            "vs_baseline": None,
+            "dtype": ("mxfp8 linears (e4m3 + e8m0/32 block scales, fp32 accumulate), bf16 attention/norms/residual"
+                      if cfg.precision == "mxfp8" else "bf16"), "data": "synthetic uniform token ids (seed 0), random-init weights",
             "impl": args.impl,
             "config": {"model": cfg.name, "layers": cfg.n_layers, "global_batch": args.local_batch * world,
                        "seq_len": cfg.seq_len, "micro_batch": args.micro_batch,

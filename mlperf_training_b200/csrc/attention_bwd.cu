@@ -402,6 +402,7 @@ int launch_bwd(const CUtensorMap* m, const BwdParams& p, cudaStream_t stream) {
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
     cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
+    if (e != cudaSuccess) cudaGetLastError();  // clear the sticky error before reporting
     if (e != cudaSuccess) return b200::fail(611, "attn_bwd: cannot set %d bytes of shared memory: %s", SM::TOTAL,
                                             cudaGetErrorString(e));
     configured[dev & 63] = true;

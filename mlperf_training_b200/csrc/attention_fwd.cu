@@ -372,6 +372,7 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
+    if (e != cudaSuccess) cudaGetLastError();  // clear the sticky error before reporting
     if (e != cudaSuccess) return b200::fail(601, "attn_fwd: cannot set %d bytes of shared memory: %s", SM::TOTAL,
                                             cudaGetErrorString(e));
     configured[dev & 63] = true;

@@ -298,6 +298,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    if (e != cudaSuccess) cudaGetLastError();  // clear the sticky error before reporting
     if (e != cudaSuccess) return b200::fail(201, "gemm_bf16: cannot set %d bytes of shared memory: %s", C::SMEM,
                                             cudaGetErrorString(e));
     configured[dev & 63] = true;

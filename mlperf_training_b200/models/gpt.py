@@ -51,6 +51,7 @@ class GPTConfig:
     lora_dropout: float = 0.0
     lora_targets: tuple = ("qkv", "proj")
     dtype: str = "bf16"
+    precision: str = "bf16"         # GEMM precision of the linears: "bf16" | "mxfp8"
 
     def torch_dtype(self) -> torch.dtype:
         return {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}[self.dtype]
@@ -137,12 +138,13 @@ class DenseMLP(nn.Module):
     def __init__(self, cfg: GPTConfig, dtype, device):
         super().__init__()
         d, f = cfg.hidden, cfg.ffn_hidden
+        self.precision = cfg.precision
         self.w_gate_up = nn.Parameter(torch.empty(2 * f, d, dtype=dtype, device=device))
         self.w_down = nn.Parameter(torch.empty(d, f, dtype=dtype, device=device))
 
     def forward(self, h, norm_w, eps):
-        gu = F.norm_linear(h, norm_w, self.w_gate_up, eps=eps)
-        return F.swiglu_linear(gu, self.w_down, residual=h)
+        gu = F.norm_linear(h, norm_w, self.w_gate_up, eps=eps, precision=self.precision)
+        return F.swiglu_linear(gu, self.w_down, residual=h, precision=self.precision)
 
 
 class Block(nn.Module):
@@ -176,16 +178,16 @@ class Block(nn.Module):
     def forward(self, x, cos, sin, B, S):
         cfg = self.cfg
         if self.lora_qkv is None:
-            qkv = F.norm_linear(x, self.attn_norm, self.w_qkv, eps=cfg.norm_eps)
+            qkv = F.norm_linear(x, self.attn_norm, self.w_qkv, eps=cfg.norm_eps, precision=cfg.precision)
         else:
             xn = F.rms_norm(x, self.attn_norm, cfg.norm_eps)
-            qkv = F.linear(xn, self.w_qkv) + self.lora_qkv(xn)
+            qkv = F.linear(xn, self.w_qkv, None, None, cfg.precision) + self.lora_qkv(xn)
         a = F.attention_packed(qkv, B=B, S=S, Hq=cfg.n_heads, Hkv=cfg.n_kv_heads, D=cfg.head_dim, cos=cos, sin=sin,
                                sink=self.sink, causal=True, window=cfg.layer_window(self.layer))
         if self.lora_proj is None:
-            h = F.linear(a, self.w_proj, None, x)
+            h = F.linear(a, self.w_proj, None, x, cfg.precision)
         else:
-            h = F.linear(a, self.w_proj, None, x) + self.lora_proj(a)
+            h = F.linear(a, self.w_proj, None, x, cfg.precision) + self.lora_proj(a)
         return self.mlp(h, self.mlp_norm, cfg.norm_eps)
 
 
@@ -236,4 +238,4 @@ class GPT(nn.Module):
         for blk in self.blocks:
             x = blk(x, cos, sin, B, S)
         return F.lm_head_loss(x, self.final_norm, self.lm_head, labels.reshape(-1), eps=self.cfg.norm_eps,
-                              n_valid=n_valid)
+                              n_valid=n_valid, precision=self.cfg.precision)

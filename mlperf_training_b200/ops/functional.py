@@ -15,6 +15,7 @@ import torch
 from torch.autograd import Function
 
 from . import kernels as K
+from . import linear as L
 
 
 def _wgrad(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor):
@@ -45,26 +46,30 @@ class LinearFn(Function):
     """y = x W^T (+ bias) (+ residual), the residual add done in the GEMM epilogue."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, residual):
-        ctx.save_for_backward(x, weight)
-        ctx.has_bias = bias is not None
+    def forward(ctx, x, weight, bias, residual, precision):
+        need_w = weight.requires_grad
+        y, saved = L.forward(x, weight, precision, bias=bias, residual=residual, need_wgrad=need_w)
+        tensors, ctx.meta = L.Saved.pack(saved) if saved is not None else ([], None)
+        ctx.save_for_backward(weight, *tensors)
         ctx.has_res = residual is not None
         ctx.bias_ref = bias
-        return K.gemm(x, weight, bias=bias, residual=residual)
+        ctx.precision = precision
+        return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, weight = ctx.saved_tensors
+        weight, *tensors = ctx.saved_tensors
+        saved = L.Saved.unpack(tensors, ctx.meta) if ctx.meta is not None else None
         dy = dy.contiguous()
-        dx = K.gemm(dy, weight, b_mn_major=True) if ctx.needs_input_grad[0] else None
-        dw = _wgrad(dy, x, weight)
-        db = _vec_grad(ctx.bias_ref, dy.float().sum(0)) if ctx.has_bias else None
+        dx, dw = L.backward(dy, saved, weight, ctx.precision, need_dx=ctx.needs_input_grad[0],
+                            need_dw=weight.requires_grad and saved is not None)
+        db = _vec_grad(ctx.bias_ref, dy.float().sum(0)) if ctx.bias_ref is not None else None
         dres = dy if ctx.has_res and ctx.needs_input_grad[3] else None
-        return dx, dw, db, dres
+        return dx, dw, db, dres, None
 
 
-def linear(x, weight, bias=None, residual=None):
-    return LinearFn.apply(x, weight, bias, residual)
+def linear(x, weight, bias=None, residual=None, precision="bf16"):
+    return LinearFn.apply(x, weight, bias, residual, precision)
 
 
 class NormFn(Function):
@@ -99,62 +104,70 @@ def swish_layer_norm(x, weight, bias, eps=1e-5):
 
 
 class NormLinearFn(Function):
-    """y = norm(x) W^T with the normalised activation recomputed in backward instead of saved
+    """y = norm(x) W^T.  bf16: the normalised activation is recomputed in backward instead of saved
     (the "fused residual + RMSNorm -> GEMM" pairing of the reference's Turbo configs,
-    small_llm_pretraining/primus/config_MI355X_1x8x1.sh:42-51)."""
+    small_llm_pretraining/primus/config_MI355X_1x8x1.sh:42-51).  mxfp8: its transposed fp8 copy,
+    produced by the same quantisation pass that feeds the forward GEMM, is kept instead."""
 
     @staticmethod
-    def forward(ctx, x, norm_w, norm_b, weight, bias, eps, layer_norm):
+    def forward(ctx, x, norm_w, norm_b, weight, bias, eps, layer_norm, precision):
         xn, _, mean, rstd = K.norm_fwd(x, norm_w, norm_b, eps, layer_norm=layer_norm)
-        y = K.gemm(xn, weight, bias=bias)
-        ctx.save_for_backward(x, norm_w, norm_b, weight, mean, rstd)
-        ctx.cfg = (eps, layer_norm)
+        keep = precision == "mxfp8" and L.mx_eligible(x.shape[0], weight.shape[0], weight.shape[1])
+        y, saved = L.forward(xn, weight, precision, bias=bias, need_wgrad=keep and weight.requires_grad)
+        tensors, ctx.meta = L.Saved.pack(saved) if saved is not None else ([], None)
+        ctx.save_for_backward(x, norm_w, norm_b, weight, mean, rstd, *tensors)
+        ctx.cfg = (eps, layer_norm, precision)
         ctx.refs = (norm_w, norm_b, bias)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, norm_w, norm_b, weight, mean, rstd = ctx.saved_tensors
-        eps, layer_norm = ctx.cfg
+        x, norm_w, norm_b, weight, mean, rstd, *tensors = ctx.saved_tensors
+        eps, layer_norm, precision = ctx.cfg
         dy = dy.contiguous()
-        xn = K.norm_fwd(x, norm_w, norm_b, eps, layer_norm=layer_norm)[0]
-        dw = _wgrad(dy, xn, weight)
-        del xn
-        dxn = K.gemm(dy, weight, b_mn_major=True)
+        if ctx.meta is not None:
+            saved = L.Saved.unpack(tensors, ctx.meta)
+        elif weight.requires_grad:
+            saved = K.norm_fwd(x, norm_w, norm_b, eps, layer_norm=layer_norm)[0]
+        else:
+            saved = None
+        dxn, dw = L.backward(dy, saved, weight, precision, need_dx=True,
+                             need_dw=weight.requires_grad and saved is not None)
+        del saved
         dx, dnw, dnb = K.norm_bwd(dxn, x, norm_w, norm_b, mean, rstd, layer_norm=layer_norm)
         db = _vec_grad(ctx.refs[2], dy.float().sum(0)) if ctx.refs[2] is not None else None
-        return dx, _vec_grad(ctx.refs[0], dnw), _vec_grad(ctx.refs[1], dnb), dw, db, None, None
+        return dx, _vec_grad(ctx.refs[0], dnw), _vec_grad(ctx.refs[1], dnb), dw, db, None, None, None
 
 
-def norm_linear(x, norm_w, weight, *, norm_b=None, bias=None, eps=1e-5, layer_norm=False):
-    return NormLinearFn.apply(x, norm_w, norm_b, weight, bias, eps, layer_norm)
+def norm_linear(x, norm_w, weight, *, norm_b=None, bias=None, eps=1e-5, layer_norm=False, precision="bf16"):
+    return NormLinearFn.apply(x, norm_w, norm_b, weight, bias, eps, layer_norm, precision)
 
 
 class SwiGLULinearFn(Function):
     """out = swiglu(gu) W^T + residual, saving only ``gu`` (the activation is recomputed)."""
 
     @staticmethod
-    def forward(ctx, gu, weight, residual):
+    def forward(ctx, gu, weight, residual, precision):
         a = K.swiglu_fwd(gu)
-        out = K.gemm(a, weight, residual=residual)
+        out, _ = L.forward(a, weight, precision, residual=residual, need_wgrad=False)
         ctx.save_for_backward(gu, weight)
         ctx.has_res = residual is not None
+        ctx.precision = precision
         return out
 
     @staticmethod
     def backward(ctx, dy):
         gu, weight = ctx.saved_tensors
         dy = dy.contiguous()
-        a = K.swiglu_fwd(gu)
-        dw = _wgrad(dy, a, weight)
+        a = K.swiglu_fwd(gu) if weight.requires_grad else None
+        da, dw = L.backward(dy, a, weight, ctx.precision, need_dx=True, need_dw=weight.requires_grad)
         del a
-        da = K.gemm(dy, weight, b_mn_major=True)
         dgu = K.swiglu_bwd(da, gu)
-        return dgu, dw, (dy if ctx.has_res else None)
+        return dgu, dw, (dy if ctx.has_res else None), None
 
 
-def swiglu_linear(gu, weight, residual=None):
-    return SwiGLULinearFn.apply(gu, weight, residual)
+def swiglu_linear(gu, weight, residual=None, precision="bf16"):
+    return SwiGLULinearFn.apply(gu, weight, residual, precision)
 
 
 class SwiGLUFn(Function):
@@ -295,30 +308,39 @@ class LMHeadLossFn(Function):
     from dlogits without recomputing the softmax."""
 
     @staticmethod
-    def forward(ctx, x, norm_w, weight, labels, eps, loss_mask_count):
+    def forward(ctx, x, norm_w, weight, labels, eps, loss_mask_count, precision):
         xn, _, _, rstd = K.norm_fwd(x, norm_w, None, eps)
-        logits = K.gemm(xn, weight)
+        keep = precision == "mxfp8" and L.mx_eligible(x.shape[0], weight.shape[0], weight.shape[1])
+        logits, saved = L.forward(xn, weight, precision, need_wgrad=keep and weight.requires_grad)
+        del xn
         n_valid = loss_mask_count if loss_mask_count is not None else max(int(labels.numel()), 1)
         losses = K.cross_entropy_(logits, labels.view(-1), 1.0 / n_valid, write_grad=True)
-        ctx.save_for_backward(x, norm_w, weight, rstd, logits)
-        ctx.eps = eps
+        tensors, ctx.meta = L.Saved.pack(saved) if saved is not None else ([], None)
+        ctx.save_for_backward(x, norm_w, weight, rstd, logits, *tensors)
+        ctx.cfg = (eps, precision)
         ctx.refs = (norm_w,)
         return losses.sum() / n_valid
 
     @staticmethod
     def backward(ctx, dloss):
-        x, norm_w, weight, rstd, dlogits = ctx.saved_tensors
+        x, norm_w, weight, rstd, dlogits, *tensors = ctx.saved_tensors
+        eps, precision = ctx.cfg
         if dloss.numel() != 1:
             raise RuntimeError("LMHeadLossFn expects a scalar upstream gradient")
-        xn = K.norm_fwd(x, norm_w, None, ctx.eps)[0]
         scale = dloss.reshape(())
         # upstream gradient other than 1 (loss scaling, grad accumulation weights) is applied to dlogits
         dl = dlogits if _is_one(scale) else (dlogits.float() * scale).to(dlogits.dtype)
-        dw = _wgrad(dl, xn, weight)
-        del xn
-        dxn = K.gemm(dl, weight, b_mn_major=True)
+        if ctx.meta is not None:
+            saved = L.Saved.unpack(tensors, ctx.meta)
+        elif weight.requires_grad:
+            saved = K.norm_fwd(x, norm_w, None, eps)[0]
+        else:
+            saved = None
+        dxn, dw = L.backward(dl, saved, weight, precision, need_dx=True,
+                             need_dw=weight.requires_grad and saved is not None)
+        del saved
         dx, dnw, _ = K.norm_bwd(dxn, x, norm_w, None, None, rstd)
-        return dx, _vec_grad(ctx.refs[0], dnw), dw, None, None, None
+        return dx, _vec_grad(ctx.refs[0], dnw), dw, None, None, None, None
 
 
 def _is_one(t: torch.Tensor) -> bool:
@@ -328,5 +350,5 @@ def _is_one(t: torch.Tensor) -> bool:
     return float(t) == 1.0
 
 
-def lm_head_loss(x, norm_w, weight, labels, *, eps=1e-5, n_valid=None):
-    return LMHeadLossFn.apply(x, norm_w, weight, labels, eps, n_valid)
+def lm_head_loss(x, norm_w, weight, labels, *, eps=1e-5, n_valid=None, precision="bf16"):
+    return LMHeadLossFn.apply(x, norm_w, weight, labels, eps, n_valid, precision)

@@ -1,0 +1,117 @@
+"""Precision-aware GEMM triple of a linear layer (forward, dgrad, wgrad).
+
+``precision="bf16"`` runs the bf16 tcgen05 GEMM on the tensors as they are (the backward GEMMs read
+the same row-major buffers as MN-major operands).  ``precision="mxfp8"`` runs the block-scaled
+GEMM: activations and gradients are quantised on the fly (one pass gives the row-wise copy for the
+next GEMM and the transposed column-wise copy that the weight-gradient GEMM needs later), weights
+are quantised once per optimizer step in both directions and cached on the parameter.
+
+What is saved for backward is the return value of ``forward`` (a bf16 tensor or the fp8 operand);
+``Saved.pack`` / ``Saved.unpack`` move it through ``ctx.save_for_backward``.
+
+Mirrors the recipe plumbing the reference gets from Transformer Engine (quantised copies of
+weights cached between micro-batches, column-wise copies kept for wgrad;
+llama2_sft/primus/src/llama2_custom.py:1904-1910 pre-quantises frozen base weights once).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import kernels as K
+from . import mxfp8 as MX
+
+# bumped by the optimizer engine after every parameter update: invalidates cached weight copies
+_WEIGHT_EPOCH = 0
+
+
+def bump_weight_epoch() -> None:
+    global _WEIGHT_EPOCH
+    _WEIGHT_EPOCH += 1
+
+
+def mx_eligible(rows: int, n_out: int, n_in: int) -> bool:
+    """MXFP8 needs every GEMM dimension to be a multiple of 128 (tokens, out and in features)."""
+    return rows % 128 == 0 and n_out % 128 == 0 and n_in % 128 == 0
+
+
+def weight_operands(weight: torch.Tensor, need_col: bool = True):
+    """(w_row, w_col) MXFP8 copies of ``weight`` ``[N, K]``: ``w_row`` (rows N, contraction K) is
+    the B operand of forward, ``w_col`` (rows K, contraction N) the B operand of dgrad.  Cached on
+    the tensor until the next optimizer step (or forever for frozen weights)."""
+    cache = getattr(weight, "_mx_cache", None)
+    epoch = _WEIGHT_EPOCH if weight.requires_grad else -1
+    if cache is not None and cache[0] == epoch and (cache[2] is not None or not need_col):
+        return cache[1], cache[2]
+    N, Kd = weight.shape
+    w = weight.detach()
+    if w.dtype != torch.bfloat16 and w.is_cuda:
+        w = w.to(torch.bfloat16)
+    row, col = MX.quantize(w, row_tile=MX.b_tile(N), col_tile=MX.b_tile(Kd) if need_col else None)
+    weight._mx_cache = (epoch, row, col)
+    return row, col
+
+
+class Saved:
+    """The activation copy kept for the weight-gradient GEMM."""
+
+    @staticmethod
+    def pack(obj):
+        if isinstance(obj, MX.MXOperand):
+            return [obj.q, obj.sf], ("mx", obj.rows, obj.k, obj.tile_rows)
+        return [obj], ("t",)
+
+    @staticmethod
+    def unpack(tensors, meta):
+        if meta[0] == "mx":
+            return MX.MXOperand(tensors[0], tensors[1], meta[1], meta[2], meta[3])
+        return tensors[0]
+
+
+def forward(x: torch.Tensor, weight: torch.Tensor, precision: str, *, bias=None, residual=None,
+            need_wgrad: bool = True):
+    """``y = x W^T (+ bias) (+ residual)``.  Returns ``(y, saved)`` where ``saved`` is what
+    ``backward`` needs of ``x`` (None when ``need_wgrad`` is False)."""
+    M, Kd = x.shape
+    N = weight.shape[0]
+    if precision == "mxfp8" and mx_eligible(M, N, Kd):
+        w_row, _ = weight_operands(weight, need_col=False)
+        x_row, x_col = MX.quantize(x, row_tile=MX.A_TILE, col_tile=MX.b_tile(Kd) if need_wgrad else None)
+        y = MX.gemm(x_row, w_row, bias=bias, residual=residual, out_dtype=x.dtype)
+        return y, x_col
+    y = K.gemm(x, weight, bias=bias, residual=residual)
+    return y, (x if need_wgrad else None)
+
+
+def backward(dy: torch.Tensor, saved, weight: torch.Tensor, precision: str, *, need_dx: bool = True,
+             need_dw: bool = True):
+    """Returns ``(dx, dw)``.  ``dw`` is None when it was accumulated into ``weight.main_grad``
+    (or not requested)."""
+    M, N = dy.shape
+    Kd = weight.shape[1]
+    dx = dw = None
+    use_mx = precision == "mxfp8" and mx_eligible(M, N, Kd)
+    if use_mx and need_dw and not isinstance(saved, MX.MXOperand):
+        # the forward ran in bf16 for this call (e.g. recomputed activation): quantise now
+        _, saved = MX.quantize(saved, col_tile=MX.b_tile(Kd))
+    if use_mx:
+        dy_row, dy_col = MX.quantize(dy, row_tile=MX.A_TILE if need_dx else None,
+                                     col_tile=MX.A_TILE if need_dw else None)
+        if need_dx:
+            _, w_col = weight_operands(weight, need_col=True)
+            dx = MX.gemm(dy_row, w_col, out_dtype=dy.dtype)
+        if need_dw:
+            mg = getattr(weight, "main_grad", None)
+            if mg is not None:
+                MX.gemm(dy_col, saved, out=mg, accumulate=True)
+            else:
+                dw = MX.gemm(dy_col, saved, out_dtype=weight.dtype if weight.dtype != torch.float32 else torch.float32)
+        return dx, dw
+    if need_dx:
+        dx = K.gemm(dy, weight, b_mn_major=True)
+    if need_dw:
+        mg = getattr(weight, "main_grad", None)
+        if mg is not None:
+            K.gemm(dy, saved, a_mn_major=True, b_mn_major=True, out=mg, accumulate=True)
+        else:
+            dw = K.gemm(dy, saved, a_mn_major=True, b_mn_major=True, out_dtype=weight.dtype)
+    return dx, dw

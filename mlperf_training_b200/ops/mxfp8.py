@@ -1,0 +1,184 @@
+"""MXFP8 (e4m3 codes + one UE8M0 scale per 32 contraction elements) operands and GEMM.
+
+``quantize`` turns a bf16 matrix into the operand copies a training step needs - the row-wise
+copy (contraction along the columns) and/or the column-wise copy stored transposed (contraction
+along the rows) - in one pass; ``gemm`` multiplies two such operands on the block-scaled tcgen05
+tensor-core path.  On CPU tensors both run an eager emulation with identical rounding, which is the
+oracle of the GPU tests.
+
+The recipe (per-32 power-of-two scales, no amax history, no calibration, no all-reduce) is the
+MX block-scaling family the reference selects for its linears
+(small_llm_pretraining/primus/conf/llama3.1_8B-pretrain-fp4.yaml:108-112 ``fp4_recipe: mxfp4``;
+llama2_sft/primus/src/llama2_custom.py:179-198 ``bf16_with_mxfp4_mixed``) at the MXFP8 width the
+benchmark definition names.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import call, ptr, stream_ptr, use_kernels
+
+A_TILE = 128     # M tile of the GEMM: scale-atom grouping of A operands
+
+
+def b_tile(n_rows: int) -> int:
+    """N tile the GEMM uses for a B operand with ``n_rows`` rows (its scale-atom grouping)."""
+    return 224 if n_rows > 128 else 128
+
+
+@dataclass
+class MXOperand:
+    """K-major MXFP8 operand: ``q`` ``[rows, k]`` e4m3 codes (uint8), ``sf`` scales.
+
+    On CUDA ``sf`` is the flat atom layout for ``tile_rows``; on CPU it is a plain ``[rows, k/32]``
+    uint8 matrix (biased exponents)."""
+    q: torch.Tensor
+    sf: torch.Tensor
+    rows: int
+    k: int
+    tile_rows: int
+
+    @property
+    def is_cuda(self) -> bool:
+        return self.q.is_cuda
+
+
+def _e8m0(amax: torch.Tensor) -> torch.Tensor:
+    """Biased exponent of the smallest power of two s with amax / s <= 448 (0 for amax == 0)."""
+    t = (amax.float() / 448.0)
+    bits = t.view(torch.int32)
+    e = ((bits >> 23) & 0xff) - 127
+    e = e + ((bits & 0x7fffff) != 0).to(torch.int32)
+    e = e.clamp(-127, 127) + 127
+    return torch.where(amax > 0, e, torch.zeros_like(e)).to(torch.uint8)
+
+
+def _quant_rows_cpu(x: torch.Tensor):
+    """Eager row-wise MXFP8: returns (codes uint8 [R, C], sf uint8 [R, C/32])."""
+    R, C = x.shape
+    xb = x.float().view(R, C // 32, 32)
+    sf = _e8m0(xb.abs().amax(-1))
+    inv = torch.exp2(127.0 - sf.float())
+    y = (xb * inv[..., None]).clamp(-448.0, 448.0)
+    q = y.to(torch.float8_e4m3fn).view(torch.uint8).view(R, C)
+    return q, sf
+
+
+def sf_index(rows: int, k: int, tile_rows: int, device) -> torch.Tensor:
+    """Flat byte offsets, shape ``[rows, k/32]``, of every scale in the atom layout."""
+    r = torch.arange(rows, device=device, dtype=torch.int64)[:, None]
+    kc = torch.arange(k // 32, device=device, dtype=torch.int64)[None, :]
+    atoms = (tile_rows + 127) // 128
+    tile = r // tile_rows
+    rr = r - tile * tile_rows
+    atom, ra = rr // 128, rr % 128
+    return ((tile * (k // 128) + kc // 4) * atoms + atom) * 512 + (ra % 32) * 16 + (ra // 32) * 4 + (kc % 4)
+
+
+def sf_bytes(rows: int, k: int, tile_rows: int) -> int:
+    tiles = (rows + tile_rows - 1) // tile_rows
+    return tiles * (k // 128) * ((tile_rows + 127) // 128) * 512
+
+
+def sf_plain(op: MXOperand) -> torch.Tensor:
+    """Scales of ``op`` as a plain ``[rows, k/32]`` uint8 matrix (un-swizzles the CUDA layout)."""
+    if not op.is_cuda:
+        return op.sf
+    return op.sf[sf_index(op.rows, op.k, op.tile_rows, op.sf.device)]
+
+
+def dequantize(op: MXOperand) -> torch.Tensor:
+    """fp32 ``[rows, k]`` value of an operand."""
+    q = op.q.view(torch.float8_e4m3fn).float().view(op.rows, op.k // 32, 32)
+    s = torch.exp2(sf_plain(op).float() - 127.0)
+    return (q * s[..., None]).view(op.rows, op.k)
+
+
+def quantize(x: torch.Tensor, *, row_tile: int | None = None, col_tile: int | None = None):
+    """bf16 ``x`` ``[R, C]`` -> ``(row_op, col_op)``.
+
+    ``row_op`` (when ``row_tile`` is given) has rows = R, contraction = C; ``col_op`` (when
+    ``col_tile`` is given) is the transposed copy with rows = C, contraction = R.  The tile
+    arguments say how the consuming GEMM tiles the operand's rows: ``A_TILE`` for an A operand,
+    ``b_tile(rows)`` for a B operand.  R and C must be multiples of 128."""
+    R, C = x.shape
+    if R % 128 or C % 128:
+        raise ValueError(f"mxfp8.quantize: shape {R}x{C} must be a multiple of 128 in both dims")
+    if not use_kernels(x):
+        row_op = col_op = None
+        if row_tile is not None:
+            q, sf = _quant_rows_cpu(x)
+            row_op = MXOperand(q, sf, R, C, row_tile)
+        if col_tile is not None:
+            q, sf = _quant_rows_cpu(x.t().contiguous())
+            col_op = MXOperand(q, sf, C, R, col_tile)
+        return row_op, col_op
+    if x.dtype != torch.bfloat16:
+        raise TypeError("mxfp8.quantize: bf16 input required")
+    if x.stride(1) != 1 or (x.stride(0) * 2) % 16 or x.data_ptr() % 16:
+        x = x.contiguous()
+    dev = x.device
+    q_row = sf_row = q_col = sf_col = None
+    if row_tile is not None:
+        q_row = torch.empty((R, C), dtype=torch.uint8, device=dev)
+        n = sf_bytes(R, C, row_tile)
+        sf_row = torch.zeros(n, dtype=torch.uint8, device=dev) if row_tile % 128 else torch.empty(n, dtype=torch.uint8, device=dev)
+    if col_tile is not None:
+        q_col = torch.empty((C, R), dtype=torch.uint8, device=dev)
+        n = sf_bytes(C, R, col_tile)
+        sf_col = torch.zeros(n, dtype=torch.uint8, device=dev) if col_tile % 128 else torch.empty(n, dtype=torch.uint8, device=dev)
+    call("b200_quant_mxfp8", ptr(x), x.stride(0), R, C, ptr(q_row), ptr(sf_row), row_tile or 0, ptr(q_col),
+         ptr(sf_col), col_tile or 0, stream_ptr())
+    row_op = MXOperand(q_row, sf_row, R, C, row_tile) if row_tile is not None else None
+    col_op = MXOperand(q_col, sf_col, C, R, col_tile) if col_tile is not None else None
+    return row_op, col_op
+
+
+def gemm(a: MXOperand, b: MXOperand, *, out: torch.Tensor | None = None, out_dtype=torch.bfloat16,
+         accumulate: bool = False, bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+         alpha: float = 1.0) -> torch.Tensor:
+    """``D[M,N] (+)= alpha * deq(a) @ deq(b)^T (+ bias) (+ residual)``."""
+    if a.k != b.k:
+        raise ValueError(f"mxfp8.gemm: contraction mismatch {a.k} vs {b.k}")
+    M, N, Kd = a.rows, b.rows, a.k
+    if out is not None:
+        out_dtype = out.dtype
+    if not a.is_cuda:
+        d = alpha * (dequantize(a) @ dequantize(b).t())
+        if bias is not None:
+            d = d + bias.float()
+        if residual is not None:
+            d = d + residual.float()
+        if out is None:
+            return d.to(out_dtype)
+        if accumulate:
+            out.add_(d.to(out.dtype))
+        else:
+            out.copy_(d.to(out.dtype))
+        return out
+    _lib.require()
+    if a.tile_rows != A_TILE or b.tile_rows != b_tile(N):
+        raise ValueError(f"mxfp8.gemm: operand scale tiling ({a.tile_rows}, {b.tile_rows}) does not match the "
+                         f"kernel tiles ({A_TILE}, {b_tile(N)})")
+    if out is None:
+        if accumulate:
+            raise ValueError("mxfp8.gemm: accumulate needs an output tensor")
+        out = torch.empty((M, N), dtype=out_dtype, device=a.q.device)
+    if out.dtype not in (torch.bfloat16, torch.float32) or out.stride(1) != 1:
+        raise TypeError("mxfp8.gemm: output must be row-major bf16 or fp32")
+    if (out.stride(0) * out.element_size()) % 16 or out.data_ptr() % 16:
+        raise ValueError("mxfp8.gemm: output pitch/base must be 16-byte aligned")
+    if bias is not None:
+        bias = bias.to(torch.bfloat16).contiguous()
+    ldr = 0
+    if residual is not None:
+        if residual.dtype != torch.bfloat16 or residual.stride(1) != 1:
+            residual = residual.to(torch.bfloat16).contiguous()
+        ldr = residual.stride(0)
+    call("b200_gemm_mxfp8", ptr(a.q), ptr(a.sf), ptr(b.q), ptr(b.sf), ptr(out), M, N, Kd, a.q.stride(0),
+         b.q.stride(0), out.stride(0), int(out.dtype == torch.float32), int(accumulate), ptr(bias), ptr(residual),
+         ldr, float(alpha), stream_ptr())
+    return out

@@ -36,6 +36,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from ..ops import kernels as K
+from ..ops.linear import bump_weight_epoch
 
 
 @dataclass
@@ -211,6 +212,7 @@ class ZeroEngine:
                 if b.hi < b.numel:
                     b.grad_buf[b.hi:].zero_()
             self._all_gather(b)
+        bump_weight_epoch()   # cached low-precision weight copies are stale now
 
     def grad_norm(self, grad_scale: float = 1.0) -> float:
         """Global gradient norm of the last step (host read)."""

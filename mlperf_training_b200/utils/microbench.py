@@ -87,6 +87,24 @@ def bench_gemm(quick: bool) -> None:
         del a, b, out
 
 
+def bench_mxfp8(quick: bool) -> None:
+    from ..ops import mxfp8
+    shapes = [(M, N, K, tag) for (M, N, K, a_mn, b_mn, tag) in GEMM_SHAPES if not a_mn and not b_mn]
+    for M, N, K, tag in (shapes[:3] if quick else shapes):
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = torch.randn(N, K, device="cuda").bfloat16()
+        ms_q = time_ms(lambda: mxfp8.quantize(a, row_tile=mxfp8.A_TILE, col_tile=mxfp8.b_tile(K)))
+        a_op, _ = mxfp8.quantize(a, row_tile=mxfp8.A_TILE)
+        b_op, _ = mxfp8.quantize(b, row_tile=mxfp8.b_tile(N))
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = time_ms(lambda: mxfp8.gemm(a_op, b_op, out=out))
+        fl = 2.0 * M * N * K
+        emit(kernel="gemm_mxfp8", tag=tag, M=M, N=N, K=K, ms=round(ms, 4), tflops=round(fl / ms / 1e9, 1),
+             quant_dual_ms=round(ms_q, 4), quant_gbs=round(M * K * 4.06 / ms_q / 1e6, 1))
+        _lib.check_status(tag)
+        del a, b, out, a_op, b_op
+
+
 ATTN_SHAPES = [
     # B, S, Hq, Hkv, D, causal, window, tag
     (1, 8192, 32, 8, 128, True, 0, "llama8b"),
@@ -169,7 +187,7 @@ def main(argv=None) -> int:
         print("microbench needs a CUDA device", file=sys.stderr)
         return 1
     for w in args.what:
-        {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise}[w](args.quick)
+        {"gemm": bench_gemm, "mxfp8": bench_mxfp8, "attention": bench_attention, "elementwise": bench_elementwise}[w](args.quick)
     return 0
 
 

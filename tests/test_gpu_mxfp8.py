@@ -1,0 +1,70 @@
+"""MXFP8 quantiser and block-scaled tcgen05 GEMM against the eager emulation (bit-exact codes and
+scales; GEMM against an fp32 matmul of the dequantised operands)."""
+import pytest
+import torch
+
+from mlperf_training_b200.ops import _lib, mxfp8
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("R,C", [(128, 128), (256, 384), (896, 512)])
+def test_quantize_matches_emulation(R, C):
+    torch.manual_seed(R + C)
+    x = (torch.randn(R, C) * torch.exp(torch.randn(R, 1) * 2)).bfloat16()
+    x[3, 32:64] = 0  # an all-zero block
+    x[5, 0] = 448.0 * 4  # amax exactly on a power-of-two boundary
+    for row_tile, col_tile in ((128, 224), (224, 128)):
+        r_c, c_c = mxfp8.quantize(x, row_tile=row_tile, col_tile=col_tile)
+        r_g, c_g = mxfp8.quantize(x.cuda(), row_tile=row_tile, col_tile=col_tile)
+        torch.cuda.synchronize()
+        for cpu, gpu, what in ((r_c, r_g, "row"), (c_c, c_g, "col")):
+            assert torch.equal(mxfp8.sf_plain(gpu).cpu(), cpu.sf), f"{what} scales"
+            assert torch.equal(gpu.q.cpu(), cpu.q), f"{what} codes"
+        # quantisation error is bounded by the e4m3 step
+        err = (mxfp8.dequantize(r_g).cpu() - x.float()).abs()
+        assert (err <= x.float().abs().view(R, C // 32, 32).amax(-1, keepdim=True).expand(-1, -1, 32).reshape(R, C) * 0.07 + 1e-30).all()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 224, 256), (384, 448, 512), (512, 1000, 384),
+                                   (1024, 4096, 1024), (136, 72, 128)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_mxfp8(M, N, K, out_dtype):
+    torch.manual_seed(M + N + K)
+    Mp, Np = (M + 127) // 128 * 128, (N + 127) // 128 * 128
+    a = torch.randn(Mp, K, device="cuda").bfloat16()
+    b = torch.randn(Np, K, device="cuda").bfloat16()
+    a_op, _ = mxfp8.quantize(a, row_tile=mxfp8.A_TILE)
+    b_op, _ = mxfp8.quantize(b, row_tile=mxfp8.b_tile(Np))
+    d = mxfp8.gemm(a_op, b_op, out_dtype=out_dtype)
+    torch.cuda.synchronize()
+    _lib.check_status("gemm_mxfp8")
+    ref = mxfp8.dequantize(a_op) @ mxfp8.dequantize(b_op).t()
+    err = (d.float() - ref).abs().max().item()
+    tol = (2e-2 if out_dtype == torch.bfloat16 else 1e-3) * ref.abs().max().item()
+    assert err <= tol, f"err {err} tol {tol}"
+    # and the quantised product is close to the bf16 product
+    full = a.float() @ b.float().t()
+    rel = (ref - full).norm() / full.norm()
+    assert rel < 0.06
+
+
+def test_gemm_mxfp8_epilogues():
+    torch.manual_seed(0)
+    M, N, K = 256, 448, 256
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    a_op, _ = mxfp8.quantize(a, row_tile=mxfp8.A_TILE)
+    b_op, _ = mxfp8.quantize(b, row_tile=mxfp8.b_tile(N))
+    ref = mxfp8.dequantize(a_op) @ mxfp8.dequantize(b_op).t()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    d = mxfp8.gemm(a_op, b_op, residual=res, bias=bias, alpha=0.5)
+    acc = torch.ones(M, N, device="cuda")
+    mxfp8.gemm(a_op, b_op, out=acc, accumulate=True)
+    mxfp8.gemm(a_op, b_op, out=acc, accumulate=True)
+    torch.cuda.synchronize()
+    sc = ref.abs().max().item()
+    assert (d.float() - (0.5 * ref + res.float() + bias.float())).abs().max().item() < 2e-2 * sc
+    assert (acc - (2 * ref + 1)).abs().max().item() < 2e-3 * sc
+    _lib.check_status("gemm_mxfp8 epilogues")

@@ -17,7 +17,8 @@ def _cfg(**kw):
     return GPTConfig(**base)
 
 
-@pytest.mark.parametrize("kw", [dict(), dict(head_dim=128, hidden=512), dict(window=128, window_layers="even", sink=True)])
+@pytest.mark.parametrize("kw", [dict(), dict(head_dim=128, hidden=512), dict(window=128, window_layers="even", sink=True),
+                                dict(head_dim=128, hidden=512, precision="mxfp8")])
 def test_loss_and_grads_match_cpu(kw):
     cfg = _cfg(**kw)
     ref = GPT(GPTConfig(**{**cfg.to_dict(), "dtype": "fp32"}), "cpu", seed=1)
@@ -39,11 +40,12 @@ def test_loss_and_grads_match_cpu(kw):
         g_ref, g_dev = p.grad, q.grad.float().cpu()
         denom = g_ref.abs().max().item() + 1e-6
         rel = (g_dev - g_ref).abs().max().item() / denom
-        assert rel < 8e-2, f"{n}: rel err {rel}"
+        assert rel < (0.2 if cfg.precision == "mxfp8" else 8e-2), f"{n}: rel err {rel}"
 
 
-def test_trainer_loss_decreases_and_launches_counted():
-    cfg = _cfg(head_dim=128, hidden=512)
+@pytest.mark.parametrize("precision", ["bf16", "mxfp8"])
+def test_trainer_loss_decreases_and_launches_counted(precision):
+    cfg = _cfg(head_dim=128, hidden=512, precision=precision)
     tr = PretrainTrainer(cfg, OptimConfig(lr=2e-3), TrainConfig(micro_batch=1, local_batch=2, warmup_steps=1), "cuda")
     toks = synthetic_tokens(1, 2, cfg.seq_len, cfg.vocab_size, seed=0)[0]
     n0 = _lib.launch_count()

@@ -105,3 +105,23 @@ def test_attention_reference_matches_sdpa_and_sink():
     # window: each query sees at most `window` keys
     ow, _ = kernels.attention_reference(q, k, v, scale=1.0, causal=True, window=1)
     assert torch.allclose(ow, v.repeat_interleave(2, 2), atol=1e-5)
+
+
+def test_mxfp8_emulation_roundtrip():
+    from mlperf_training_b200.ops import mxfp8
+    torch.manual_seed(5)
+    x = (torch.randn(128, 256) * 3).bfloat16()
+    row, col = mxfp8.quantize(x, row_tile=128, col_tile=224)
+    assert row.q.shape == (128, 256) and col.q.shape == (256, 128)
+    d = mxfp8.dequantize(row)
+    assert (d - x.float()).abs().max() <= x.float().abs().max() * 0.07
+    assert torch.allclose(mxfp8.dequantize(col), mxfp8.dequantize(mxfp8.quantize(x.t().contiguous(), row_tile=224)[0]))
+    # scales are the smallest powers of two that keep the block inside +-448
+    s = torch.exp2(row.sf.float() - 127)
+    amax = x.float().abs().view(128, 8, 32).amax(-1)
+    assert (amax / s <= 448).all() and ((amax / s > 224) | (amax == 0)).all()
+    y = mxfp8.gemm(row, row, out_dtype=torch.float32)
+    assert torch.allclose(y, d @ d.t(), atol=1e-3)
+    # the flat atom layout addresses every scale exactly once
+    idx = mxfp8.sf_index(448, 256, 224, "cpu")
+    assert idx.unique().numel() == idx.numel() and int(idx.max()) < mxfp8.sf_bytes(448, 256, 224)
