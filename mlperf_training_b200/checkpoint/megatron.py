@@ -1,0 +1,176 @@
+"""Megatron / NeMo ``torch_dist`` distributed-checkpoint compatibility for the GPT family.
+
+A Megatron-Bridge checkpoint directory looks like
+``iter_0000000/{__0_0.distcp, __0_1.distcp, common.pt, .metadata, metadata.json, run_config.yaml}``
+plus ``latest_checkpointed_iteration.txt`` next to it (llama2_sft/primus/README.md:53-76); the SFT
+workload loads such a base checkpoint with ``finetune=True, load_optim=False, load_rng=False``
+(llama2_sft/primus/src/llama2_custom.py:711-725).  This module
+
+* maps parameter names between this package's ``GPT`` and Megatron-Core's ``GPTModel`` and converts
+  the fused-QKV layout (Megatron interleaves per KV group: ``[q_0 .. q_{g-1}, k, v]`` for each
+  group; here all query heads come first, then all keys, then all values);
+* writes / reads the ``.distcp`` shards and ``.metadata`` through ``torch.distributed.checkpoint``
+  with one entry per Megatron key, so every rank (tensor/expert/pipeline shard) only touches the
+  slices it owns;
+* writes ``common.pt``, ``metadata.json`` and ``latest_checkpointed_iteration.txt``.
+"""
+from __future__ import annotations
+
+import json
+import re
+from pathlib import Path
+
+import torch
+import torch.distributed.checkpoint as dcp
+
+from ..models.gpt import GPT, GPTConfig
+
+_LAYER = re.compile(r"blocks\.(\d+)\.(.+)")
+
+_BLOCK_MAP = {
+    "attn_norm": "self_attention.linear_qkv.layer_norm_weight",
+    "w_qkv": "self_attention.linear_qkv.weight",
+    "w_proj": "self_attention.linear_proj.weight",
+    "sink": "self_attention.core_attention.softmax_offset",
+    "mlp_norm": "mlp.linear_fc1.layer_norm_weight",
+    "mlp.w_gate_up": "mlp.linear_fc1.weight",
+    "mlp.w_down": "mlp.linear_fc2.weight",
+    "mlp.router": "mlp.router.weight",
+    "mlp.w1": "mlp.experts.linear_fc1.weight",
+    "mlp.w2": "mlp.experts.linear_fc2.weight",
+    "lora_qkv.a": "self_attention.linear_qkv.adapter.linear_in.weight",
+    "lora_qkv.b": "self_attention.linear_qkv.adapter.linear_out.weight",
+    "lora_proj.a": "self_attention.linear_proj.adapter.linear_in.weight",
+    "lora_proj.b": "self_attention.linear_proj.adapter.linear_out.weight",
+}
+_TOP_MAP = {"embed": "embedding.word_embeddings.weight", "final_norm": "decoder.final_layernorm.weight",
+            "lm_head": "output_layer.weight"}
+
+
+def megatron_name(name: str, moe_pre_norm: bool = False) -> str:
+    if name in _TOP_MAP:
+        return _TOP_MAP[name]
+    m = _LAYER.match(name)
+    if not m:
+        raise KeyError(f"no Megatron name for parameter '{name}'")
+    layer, rest = m.group(1), m.group(2)
+    if rest == "mlp_norm" and moe_pre_norm:
+        return f"decoder.layers.{layer}.pre_mlp_layernorm.weight"
+    if rest not in _BLOCK_MAP:
+        raise KeyError(f"no Megatron name for parameter '{name}'")
+    return f"decoder.layers.{layer}.{_BLOCK_MAP[rest]}"
+
+
+def local_name(meg: str) -> str:
+    for k, v in _TOP_MAP.items():
+        if v == meg:
+            return k
+    m = re.match(r"decoder\.layers\.(\d+)\.(.+)", meg)
+    if not m:
+        raise KeyError(meg)
+    if m.group(2) == "pre_mlp_layernorm.weight":
+        return f"blocks.{m.group(1)}.mlp_norm"
+    for k, v in _BLOCK_MAP.items():
+        if v == m.group(2):
+            return f"blocks.{m.group(1)}.{k}"
+    raise KeyError(meg)
+
+
+def qkv_to_megatron(w: torch.Tensor, n_heads: int, n_kv: int, hd: int) -> torch.Tensor:
+    """``[q_all | k_all | v_all]`` rows -> Megatron's per-group interleave."""
+    g = n_heads // n_kv
+    rest = w.shape[1:]
+    q = w[: n_heads * hd].reshape(n_kv, g * hd, *rest)
+    k = w[n_heads * hd:(n_heads + n_kv) * hd].reshape(n_kv, hd, *rest)
+    v = w[(n_heads + n_kv) * hd:].reshape(n_kv, hd, *rest)
+    return torch.cat([q, k, v], dim=1).reshape(-1, *rest)
+
+
+def qkv_from_megatron(w: torch.Tensor, n_heads: int, n_kv: int, hd: int) -> torch.Tensor:
+    g = n_heads // n_kv
+    rest = w.shape[1:]
+    x = w.reshape(n_kv, (g + 2) * hd, *rest)
+    q = x[:, : g * hd].reshape(n_heads * hd, *rest)
+    k = x[:, g * hd:(g + 1) * hd].reshape(n_kv * hd, *rest)
+    v = x[:, (g + 1) * hd:].reshape(n_kv * hd, *rest)
+    return torch.cat([q, k, v], dim=0)
+
+
+def to_megatron_state(model: GPT) -> dict[str, torch.Tensor]:
+    cfg = model.cfg
+    out = {}
+    for name, p in model.named_parameters():
+        t = p.detach()
+        if name.endswith("w_qkv") or name.endswith("lora_qkv.b"):
+            t = qkv_to_megatron(t, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
+        out[megatron_name(name, moe_pre_norm=cfg.n_experts > 0)] = t.contiguous()
+    return out
+
+
+def load_megatron_state(model: GPT, state: dict[str, torch.Tensor], strict: bool = True) -> list[str]:
+    """Copy a (Megatron-named) state dict into ``model``.  Returns the model parameters that were
+    not found (e.g. freshly initialised LoRA adapters when loading a base checkpoint)."""
+    cfg = model.cfg
+    missing = []
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            key = megatron_name(name, moe_pre_norm=cfg.n_experts > 0)
+            if key not in state:
+                missing.append(name)
+                continue
+            t = state[key]
+            if name.endswith("w_qkv") or name.endswith("lora_qkv.b"):
+                t = qkv_from_megatron(t, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
+            if tuple(t.shape) != tuple(p.shape):
+                raise ValueError(f"{key}: checkpoint shape {tuple(t.shape)} vs model {tuple(p.shape)}")
+            p.copy_(t.to(p.dtype))
+    if strict and any("lora" not in m for m in missing):
+        raise KeyError(f"checkpoint lacks parameters: {[m for m in missing if 'lora' not in m]}")
+    return missing
+
+
+def save_torch_dist(model: GPT, root: str, iteration: int = 0, extra_common: dict | None = None) -> Path:
+    """Write ``<root>/iter_<iteration:07d>/`` in the ``torch_dist`` layout.  Collective when a
+    process group is initialised (every rank calls it)."""
+    d = Path(root) / f"iter_{iteration:07d}"
+    rank = torch.distributed.get_rank() if torch.distributed.is_initialized() else 0
+    if rank == 0:
+        d.mkdir(parents=True, exist_ok=True)
+    if torch.distributed.is_initialized():
+        torch.distributed.barrier()
+    state = {f"model.{k}": v for k, v in to_megatron_state(model).items()}
+    dcp.save(state, checkpoint_id=str(d))
+    if rank == 0:
+        common = {"iteration": iteration, "checkpoint_version": 3.0, "args": None, "model_config": model.cfg.to_dict()}
+        common.update(extra_common or {})
+        torch.save(common, d / "common.pt")
+        (d / "metadata.json").write_text(json.dumps({"sharded_backend": "torch_dist", "sharded_backend_version": 1,
+                                                      "common_backend": "torch", "common_backend_version": 1}))
+        (Path(root) / "latest_checkpointed_iteration.txt").write_text(str(iteration))
+    if torch.distributed.is_initialized():
+        torch.distributed.barrier()
+    return d
+
+
+def load_torch_dist(model: GPT, root: str, iteration: int | None = None, strict: bool = True) -> dict:
+    """Load model weights from a ``torch_dist`` checkpoint (finetune semantics: no optimizer state,
+    no RNG).  Architecture fields recorded in ``common.pt`` are asserted against the model."""
+    rootp = Path(root)
+    if iteration is None:
+        f = rootp / "latest_checkpointed_iteration.txt"
+        iteration = int(f.read_text().strip()) if f.exists() else 0
+    d = rootp / f"iter_{iteration:07d}"
+    if not d.exists():
+        raise FileNotFoundError(d)
+    common = torch.load(d / "common.pt", map_location="cpu", weights_only=False) if (d / "common.pt").exists() else {}
+    saved_cfg = common.get("model_config") or {}
+    for k in ("n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "vocab_size"):
+        if k in saved_cfg and saved_cfg[k] != getattr(model.cfg, k):
+            raise ValueError(f"checkpoint {k}={saved_cfg[k]} but model has {getattr(model.cfg, k)}")
+    want = {f"model.{k}": torch.empty_like(v) for k, v in to_megatron_state(model).items()}
+    reader = dcp.FileSystemReader(str(d))
+    present = set(reader.read_metadata().state_dict_metadata.keys())
+    sub = {k: v for k, v in want.items() if k in present}
+    dcp.load(sub, checkpoint_id=str(d))
+    missing = load_megatron_state(model, {k[len("model."):]: v for k, v in sub.items()}, strict=strict)
+    return {"iteration": iteration, "missing": missing, "common": common}

@@ -57,7 +57,7 @@ B200_DEVICE long long sf_offset(long long r, int kc, int tile_rows, int atoms_pe
 }
 
 // grid: (C / 128, R / 128); 256 threads
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, int C, uint8_t* __restrict__ q_row,
                    uint8_t* __restrict__ sf_row, int row_tile, uint8_t* __restrict__ q_col,
                    uint8_t* __restrict__ sf_col, int col_tile) {
