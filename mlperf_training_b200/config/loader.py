@@ -100,7 +100,8 @@ def parse_shell_exports(text: str, env: Mapping[str, str] | None = None) -> dict
             pass
         val = expand(val)
         out[key] = val
-        known[key] = val
+        if key not in (env or {}):   # a pre-set variable keeps its value for later references too
+            known[key] = val
     return out
 
 

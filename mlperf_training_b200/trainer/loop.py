@@ -1,0 +1,230 @@
+"""MLPerf-style training run for the GPT family (pre-training and LoRA SFT).
+
+``run(exp)`` takes a resolved experiment dictionary and performs one timed run:
+
+    cache_clear / init_start -> build model, engine, data -> load checkpoint (resume or finetune base)
+    -> synthetic warm-up with state restoration -> init_stop / run_start (barrier-aligned)
+    -> for step: train_step ; train_loss event ; evaluation every ``eval_interval`` steps
+       (block_stop, eval_start, eval_accuracy, eval_stop, block_start) ; stop when the evaluation
+       loss reaches ``target_eval_loss`` ; checkpoint cadence ; optional fault injection
+    -> run_stop{success|aborted}, run_duration, overall_throughput
+
+which is the event sequence of the reference's ``MLPerfMegatronPretrainTrainer``
+(primus_mllog/mlperf_pre_training.py:100-241 in the bundled wheel) and of its SFT loop
+(llama2_sft/primus/src/llama2_custom.py:1295-1893: evaluation every ``eval_interval`` steps after
+skipping the first ``skip_evals`` ones, sticky early exit below the target loss).
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from ..checkpoint.manager import CheckpointManager, select_checkpoint_reason
+from ..data.indexed import GPTSampleDataset, PackedSFTDataset, SyntheticTokens
+from ..mllog import core as ml
+from ..models.gpt import PRESETS, GPTConfig
+from ..parallel.engine import OptimConfig
+from .pretrain import PretrainTrainer, TrainConfig
+from .warmup import run_synthetic_warmup
+
+
+@dataclass
+class RunConfig:
+    benchmark: str = "llama31_8b"
+    model: dict = field(default_factory=dict)          # preset name under "preset" + field overrides
+    global_batch: int = 32
+    micro_batch: int = 1
+    train_iters: int = 100
+    lr: float = 8e-4
+    min_lr_ratio: float = 0.1
+    lr_warmup_iters: int = 64
+    lr_decay_iters: int = 1_200_000
+    weight_decay: float = 0.1
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.95
+    adam_eps: float = 1e-5
+    clip_grad: float = 1.0
+    seed: int = 0
+    eval_interval: int = 0
+    eval_iters: int = 0
+    skip_evals: int = 0
+    target_eval_loss: float = 0.0
+    warmup_train_steps: int = 2
+    warmup_eval_steps: int = 0
+    data: dict = field(default_factory=lambda: {"kind": "synthetic"})
+    checkpoint_dir: str = ""
+    checkpoint_every: int = 0
+    keep_last: int = 2
+    pretrained_checkpoint: str = ""
+    log_interval: int = 1
+    die_at_step: int = 0                                # fault injection: exit(42) after this step's save
+    mllog_file: str = ""
+    profile_step_start: int = 0
+    profile_step_end: int = 0
+    profile_dir: str = ""
+
+    @staticmethod
+    def from_dict(d: dict) -> "RunConfig":
+        known = {f for f in RunConfig.__dataclass_fields__}
+        return RunConfig(**{k: v for k, v in d.items() if k in known})
+
+
+def build_model_config(spec: dict) -> GPTConfig:
+    spec = dict(spec or {})
+    preset = spec.pop("preset", None)
+    cfg = PRESETS[preset]() if preset else GPTConfig()
+    for k, v in spec.items():
+        if not hasattr(cfg, k):
+            raise KeyError(f"unknown model field '{k}'")
+        if k == "lora_targets" and isinstance(v, list):
+            v = tuple(v)
+        setattr(cfg, k, v)
+    return cfg
+
+
+def build_data(spec: dict, cfg: GPTConfig, seed: int):
+    kind = spec.get("kind", "synthetic")
+    if kind == "synthetic":
+        return SyntheticTokens(cfg.vocab_size, cfg.seq_len, seed=seed, loss_last=int(spec.get("loss_last", 0)))
+    if kind == "indexed":
+        return GPTSampleDataset(list(spec["prefixes"]), spec.get("weights"), cfg.seq_len, seed=seed)
+    if kind == "packed_sft":
+        return PackedSFTDataset(spec["path"], cfg.seq_len, spec.get("metadata"))
+    raise ValueError(f"unknown data kind '{kind}'")
+
+
+def _dist_info():
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(), dist.get_world_size()
+    return 0, 1
+
+
+def run(exp: dict, device: str | None = None, stream=None) -> dict:
+    rc = RunConfig.from_dict(exp)
+    rank, world = _dist_info()
+    device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+    sync = dist.barrier if world > 1 else None
+    resume_mgr = CheckpointManager(rc.checkpoint_dir, rank, world, rc.keep_last, sync) if rc.checkpoint_dir else None
+    resuming = bool(resume_mgr and resume_mgr.present())
+    log = ml.MLLogger(rank=rank, stream=stream or sys.stdout, filename=rc.mllog_file or None, sync=sync,
+                      append=resuming)
+    if not resuming:
+        log.log_init_start()
+        log.log_submission(rc.benchmark, platform=f"1xB200x{world}")
+
+    cfg = build_model_config(rc.model)
+    if rc.global_batch % world:
+        raise ValueError("global_batch must be divisible by the data-parallel size")
+    local_batch = rc.global_batch // world
+    opt = OptimConfig(lr=rc.lr, beta1=rc.adam_beta1, beta2=rc.adam_beta2, eps=rc.adam_eps,
+                      weight_decay=rc.weight_decay, clip_grad=rc.clip_grad)
+    tc = TrainConfig(micro_batch=rc.micro_batch, local_batch=local_batch, warmup_steps=rc.lr_warmup_iters,
+                     decay_steps=rc.lr_decay_iters, min_lr_ratio=rc.min_lr_ratio, seed=rc.seed)
+    trainer = PretrainTrainer(cfg, opt, tc, device)
+    data = build_data(rc.data, cfg, rc.seed)
+    eval_data = build_data(rc.data, cfg, rc.seed + 7919)
+
+    if rc.pretrained_checkpoint and not resuming:
+        from ..checkpoint.megatron import load_torch_dist
+        load_torch_dist(trainer.model, rc.pretrained_checkpoint, strict=True)
+    start_step = 0
+    if resuming:
+        ck = resume_mgr.load()
+        for b, saved in zip(trainer.engine.buckets, ck["dense"]["param_bufs"]):
+            b.param_buf.copy_(saved.to(b.param_buf.device))
+        if ck["optim"] is not None:
+            trainer.engine.load_optimizer_state(ck["optim"])
+        CheckpointManager.restore_rng(ck["rng"])
+        start_step = int(ck["meta"]["step"])
+        trainer.step_idx = start_step
+
+    if not resuming:
+        log.log_hyperparameters({
+            "global_batch_size": rc.global_batch, "seed": rc.seed, "opt_base_learning_rate": rc.lr,
+            "opt_learning_rate_warmup_steps": rc.lr_warmup_iters, "opt_learning_rate_decay_steps": rc.lr_decay_iters,
+            "opt_learning_rate_decay_schedule": "cosine with linear warmup", "opt_adamw_beta_1": rc.adam_beta1,
+            "opt_adamw_beta_2": rc.adam_beta2, "opt_adamw_epsilon": rc.adam_eps,
+            "opt_adamw_weight_decay": rc.weight_decay, "opt_gradient_clip_norm": rc.clip_grad,
+            "gradient_accumulation_steps": trainer.n_micro, "max_sequence_length": cfg.seq_len,
+            "eval_samples": rc.eval_iters * rc.global_batch, "lora_rank": cfg.lora_rank, "lora_alpha": cfg.lora_alpha})
+        run_synthetic_warmup(trainer, rc.warmup_train_steps, rc.warmup_eval_steps)
+        log.log_init_stop_run_start()
+        log.start(ml.EPOCH_START, metadata={"epoch_num": 0})
+        log.start(ml.BLOCK_START, metadata={"samples_count": 0})
+
+    timer = ml.ThroughputTimer(rc.global_batch)
+    t_run0 = time.perf_counter()
+    last_ckpt_t = time.perf_counter()
+    reached, evals_done, last_eval = False, 0, None
+    losses = []
+    prof = None
+    step = start_step
+    for step in range(start_step, rc.train_iters):
+        if rc.profile_step_end > rc.profile_step_start and step == rc.profile_step_start and rank == 0:
+            from ..utils.profiler import StepProfiler
+            prof = StepProfiler(rc.profile_dir or ".", rank)
+            prof.start()
+        timer.step_start()
+        batch = data.batch(step, rank, world, local_batch)
+        if isinstance(batch, tuple):
+            raise NotImplementedError("packed SFT batches go through trainer.sft")
+        loss = trainer.train_step(batch.pin_memory() if torch.cuda.is_available() else batch)
+        timer.step_stop()
+        losses.append(loss)
+        if prof is not None and step + 1 == rc.profile_step_end:
+            prof.stop()
+            prof = None
+        samples = (step + 1) * rc.global_batch
+        if rc.log_interval and (step + 1) % rc.log_interval == 0:
+            log.event(ml.TRAIN_LOSS, loss, metadata={"samples_count": samples, "lr": trainer.lr()})
+        # ---- evaluation ----
+        if rc.eval_interval and (step + 1) % rc.eval_interval == 0:
+            evals_done += 1
+            if evals_done > rc.skip_evals:
+                log.end(ml.BLOCK_STOP, metadata={"samples_count": samples})
+                log.start(ml.EVAL_START, metadata={"samples_count": samples})
+                tot = 0.0
+                for i in range(max(rc.eval_iters, 1)):
+                    eb = eval_data.batch(i, rank, world, local_batch).to(trainer.device)
+                    tot += float(trainer.eval_loss(eb))
+                last_eval = tot / max(rc.eval_iters, 1)
+                log.event(ml.EVAL_ACCURACY, last_eval, metadata={"samples_count": samples})
+                log.end(ml.EVAL_STOP, metadata={"samples_count": samples})
+                if rc.target_eval_loss > 0 and last_eval <= rc.target_eval_loss:
+                    reached = True
+                    break
+                log.start(ml.BLOCK_START, metadata={"samples_count": samples})
+        # ---- checkpoint cadence ----
+        if resume_mgr is not None:
+            reason = select_checkpoint_reason(global_step=step + 1, batch_in_window=0,
+                                              elapsed_since_last_s=time.perf_counter() - last_ckpt_t,
+                                              every_steps=rc.checkpoint_every)
+            if reason or (rc.die_at_step and step + 1 == rc.die_at_step):
+                resume_mgr.save(step + 1,
+                                dense={"param_bufs": [b.param_buf.detach().cpu() for b in trainer.engine.buckets],
+                                       "model_config": cfg.to_dict()},
+                                optim_shard=trainer.engine.optimizer_state(),
+                                meta={"samples": samples, "run_started": True, "window": 0, "batch_idx_in_window": -1})
+                last_ckpt_t = time.perf_counter()
+        if rc.die_at_step and step + 1 == rc.die_at_step:
+            if world > 1:
+                dist.barrier()
+            log.close()
+            sys.exit(42)
+
+    duration = time.perf_counter() - t_run0
+    success = reached or rc.target_eval_loss <= 0
+    if not reached:
+        log.end(ml.BLOCK_STOP, metadata={"samples_count": (step + 1) * rc.global_batch})
+    log.end(ml.EPOCH_STOP, metadata={"epoch_num": 0})
+    log.log_run_stop(success, samples=timer.samples, duration_s=duration)
+    log.event(ml.TRACKED_STATS, {"throughput_samples_per_s": timer.throughput(),
+                                 "tokens_per_s": timer.throughput() * cfg.seq_len}, metadata={"step": step + 1})
+    log.close()
+    return {"steps": step + 1 - start_step, "losses": losses, "eval_loss": last_eval, "reached": reached,
+            "throughput": timer.throughput(), "records": log.lines, "trainer": trainer}

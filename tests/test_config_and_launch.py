@@ -1,0 +1,112 @@
+"""Config system, MLLOG stream and the single-box launch surface (CPU)."""
+import io
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+from mlperf_training_b200.config import loader
+from mlperf_training_b200.mllog import MLLogger, ThroughputTimer, check_compliance, parse_log
+
+REPO = Path(__file__).resolve().parent.parent
+
+
+def test_env_helpers():
+    env = {"A": "3", "B": "0", "C": "x:1,y:2", "D": ""}
+    assert loader.env_int("A", 1, env) == 3 and loader.env_int("Z", 7, env) == 7 and loader.env_int("D", 5, env) == 5
+    assert loader.env_bool("B", True, env) is False and loader.env_bool("A", False, env) is True
+    assert loader.env_str_map("C", "", env) == {"x": "1", "y": "2"}
+    assert loader.env_float("A", 0.0, env) == 3.0
+
+
+def test_shell_defaults_env_wins(tmp_path):
+    f = tmp_path / "config_X.sh"
+    f.write_text('# comment\nexport GBS=32\nexport LR=8e-4 # trailing\nexport NAME="a b"\nexport DER=${GBS}_x\nif true; then :; fi\n')
+    env = {"GBS": "4"}
+    applied = loader.load_shell_defaults(f, env)
+    assert env["GBS"] == "4" and "GBS" not in applied
+    assert env["LR"] == "8e-4" and env["NAME"] == "a b" and env["DER"] == "4_x"
+
+
+def test_yaml_substitution_and_layering(tmp_path):
+    (tmp_path / "base.yaml").write_text("lr: 1.0e-3\nglobal_batch: 8\ndata:\n  kind: synthetic\n")
+    (tmp_path / "m.yaml").write_text("preset: llama3.1-8b\n")
+    (tmp_path / "exp.yaml").write_text(
+        "name: ${NAME:demo}\nmodules:\n  pre_trainer:\n    config: base.yaml\n    model: m.yaml\n    overrides:\n"
+        "      global_batch: ${GBS:32}\n      flag: ${FLAG:true}\n      model:\n        seq_len: ${SEQ:128}\n      text: run_${NAME:demo}\n")
+    cfg = loader.load_experiment(tmp_path / "exp.yaml", env={"GBS": "16"}, overrides=["modules.pre_trainer.resolved.lr=0.5"])
+    r = cfg["modules"]["pre_trainer"]["resolved"]
+    assert r["global_batch"] == 16 and r["flag"] is True and r["lr"] == 0.5
+    assert r["model"] == {"preset": "llama3.1-8b", "seq_len": 128} and r["text"] == "run_demo" and r["data"]["kind"] == "synthetic"
+    with pytest.raises(KeyError):
+        loader.substitute({"x": "${MISSING}"}, env={})
+
+
+def test_shipped_experiments_resolve():
+    for exp in REPO.glob("workloads/*/conf/*.yaml"):
+        cfg = loader.load_experiment(exp, env={})
+        mods = cfg["modules"]
+        assert all("resolved" in m for m in mods.values()), exp
+
+
+def test_mllog_lifecycle_and_compliance():
+    buf = io.StringIO()
+    t = [0.0]
+    log = MLLogger(stream=buf, clock=lambda: t.__setitem__(0, t[0] + 1) or t[0])
+    log.log_init_start()
+    log.log_submission("llama31_8b")
+    log.log_hyperparameters({"global_batch_size": 32, "junk": 1}, env={"MLLOG_SEED": "7"})
+    log.log_init_stop_run_start()
+    log.start("block_start")
+    log.event("eval_accuracy", 3.4)
+    log.end("block_stop")
+    log.log_run_stop(True, samples=64, duration_s=2.0)
+    recs = parse_log(buf.getvalue())
+    assert [r["key"] for r in recs][:2] == ["cache_clear", "init_start"]
+    assert {"seed", "global_batch_size"} <= {r["key"] for r in recs} and "junk" not in {r["key"] for r in recs}
+    assert check_compliance(recs) == []
+    assert any(r["key"] == "overall_throughput" and r["value"] == 32 for r in recs)
+    assert "missing run_stop" in check_compliance(recs[:-3])
+
+
+def test_throughput_timer_counts_only_step_time():
+    t = [0.0]
+    tm = ThroughputTimer(8, clock=lambda: t[0])
+    for _ in range(3):
+        tm.step_start(); t[0] += 2.0; tm.step_stop(); t[0] += 100.0  # eval / checkpoint time in between
+    assert tm.samples == 24 and tm.throughput() == 4.0
+
+
+def test_non_rank0_is_silent_but_syncs():
+    calls = []
+    buf = io.StringIO()
+    log = MLLogger(rank=1, stream=buf, sync=lambda: calls.append(1))
+    log.log_init_stop_run_start()
+    assert buf.getvalue() == "" and len(calls) == 2
+
+
+def test_run_and_time_end_to_end(tmp_path):
+    """The launch surface on CPU: run_and_time.sh -> trainer CLI -> RESULT line + compliant MLLOG."""
+    exp = REPO / "workloads" / "llama31_8b" / "conf" / "_test_tiny.yaml"
+    exp.write_text(
+        "modules:\n  pre_trainer:\n    config: pre_trainer.yaml\n    overrides:\n      benchmark: tiny\n      global_batch: 2\n"
+        "      micro_batch: 1\n      train_iters: 3\n      eval_interval: 2\n      eval_iters: 1\n      warmup_train_steps: 1\n"
+        "      model: {n_layers: 1, hidden: 32, n_heads: 2, n_kv_heads: 1, head_dim: 16, ffn_hidden: 64, vocab_size: 64, seq_len: 16, dtype: fp32}\n")
+    try:
+        env = dict(os.environ, WORKLOAD="llama31_8b", EXP="conf/_test_tiny.yaml", NGPU="1", CUDA_VISIBLE_DEVICES="",
+                   PYTHONPATH=str(REPO))
+        res = subprocess.run(["bash", str(REPO / "workloads/common/run_and_time.sh")], env=env, capture_output=True,
+                             text=True, timeout=300)
+        assert res.returncode == 0, res.stdout + res.stderr
+        assert "STARTING TIMING RUN" in res.stdout and "RESULT,llama31_8b,," in res.stdout
+        recs = parse_log(res.stdout)
+        assert check_compliance(recs) == [] and any(r["key"] == "eval_accuracy" for r in recs)
+        log = tmp_path / "trial.log"
+        log.write_text(res.stdout)
+        chk = subprocess.run([sys.executable, "-m", "mlperf_training_b200.mllog.compliance", str(log)], env=env,
+                             capture_output=True, text=True)
+        assert chk.returncode == 0 and "SUCCESS" in chk.stdout
+    finally:
+        exp.unlink()
