@@ -148,7 +148,7 @@ class DenseMLP(nn.Module):
 
 
 class Block(nn.Module):
-    def __init__(self, cfg: GPTConfig, layer: int, dtype, device, mlp: nn.Module | None = None):
+    def __init__(self, cfg: GPTConfig, layer: int, dtype, device, mlp: nn.Module | None = None, ep_group=None):
         super().__init__()
         self.cfg = cfg
         self.layer = layer
@@ -162,7 +162,7 @@ class Block(nn.Module):
             self.mlp = mlp
         elif cfg.n_experts:
             from .moe import MoEMLP
-            self.mlp = MoEMLP(cfg, dtype, device)
+            self.mlp = MoEMLP(cfg, dtype, device, ep_group=ep_group)
         else:
             self.mlp = DenseMLP(cfg, dtype, device)
         self.lora_qkv = self.lora_proj = None
@@ -194,12 +194,12 @@ class Block(nn.Module):
 class GPT(nn.Module):
     """``forward(tokens [B,S], labels [B,S]) -> mean cross-entropy`` (labels -100 are ignored)."""
 
-    def __init__(self, cfg: GPTConfig, device="cpu", seed: int = 0):
+    def __init__(self, cfg: GPTConfig, device="cpu", seed: int = 0, ep_group=None):
         super().__init__()
         self.cfg = cfg
         dtype = cfg.torch_dtype()
         self.embed = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden, dtype=dtype, device=device))
-        self.blocks = nn.ModuleList([Block(cfg, i, dtype, device) for i in range(cfg.n_layers)])
+        self.blocks = nn.ModuleList([Block(cfg, i, dtype, device, ep_group=ep_group) for i in range(cfg.n_layers)])
         self.final_norm = nn.Parameter(torch.ones(cfg.hidden, dtype=dtype, device=device))
         self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden, dtype=dtype, device=device))
         self._rope = None

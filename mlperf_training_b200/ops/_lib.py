@@ -57,6 +57,12 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_attn_fwd": [P, P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, L, L, L, L, F, I, I, P],
         "b200_quant_mxfp8": [P, L, I, I, P, P, I, P, P, I, P],
         "b200_gemm_mxfp8": [P, P, P, P, P, I, I, I, L, L, L, I, I, P, P, L, F, P],
+        "b200_router_topk": [P, I, I, I, P, P, P, P],
+        "b200_router_plan": [P, P, I, I, I, P, P, I, P, P],
+        "b200_permute_rows": [P, P, I, I, I, P, P, P, P],
+        "b200_unpermute_sum": [P, P, P, I, I, I, P, P],
+        "b200_gemm_grouped_rows": [P, P, P, P, I, I, I, I, L, L, I, I, F, P],
+        "b200_gemm_grouped_wgrad": [P, P, P, P, I, I, I, I, L, L, I, I, F, P],
         "b200_attn_delta": [P, P, P, I, I, I, I, L, L, L, L, P],
         "b200_attn_bwd": [P] * 9 + [I] * 6 + [L] * 12 + [F, I, I, P],
     }

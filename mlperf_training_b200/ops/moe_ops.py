@@ -1,0 +1,269 @@
+"""Mixture-of-experts operators: router top-k, device-side dispatch plan, row permutation and
+grouped expert GEMMs, with autograd.
+
+Everything that depends on the routing result (per-expert counts, padded segment offsets, the
+expert of every 128-row tile, destination rows) stays on the device; the only host-visible size is
+the static upper bound ``max_rows(T * k, E)`` of the padded buffer.  This is the property the
+reference's "sync-free MoE stage" and ``host_sync_free.py`` work for
+(small_llm_moe_pretraining/primus/config_MI355X_1x8x1_tp1pp1ep1_gbs32.sh:156,
+generative_recommenders/dlrm_v4/host_sync_free.py).
+
+Router semantics: fp32 logits, top-k, softmax over the selected logits, no auxiliary loss, no
+capacity / token dropping (small_llm_moe_pretraining/primus/conf/gpt_oss_20B-MXFP4-deosc-mlperf-pretrain.yaml:115-118,130-167).
+"""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+
+from . import kernels as K
+from ._lib import call, ptr, stream_ptr, use_kernels
+
+PAD = 128
+
+
+def max_rows(pairs: int, n_experts: int, pad: int = PAD) -> int:
+    """Static upper bound of the padded, expert-grouped buffer for ``pairs`` (token, slot) pairs."""
+    return (pairs + n_experts * (pad - 1) + pad - 1) // pad * pad
+
+
+# --------------------------------------------------------------------------------------
+# raw ops
+# --------------------------------------------------------------------------------------
+def router_topk(logits: torch.Tensor, k: int):
+    """``logits`` fp32 ``[T, E]`` -> ``(idx int32 [T,k], w fp32 [T,k], counts int32 [E])``."""
+    T, E = logits.shape
+    if not use_kernels(logits):
+        val, idx = torch.topk(logits.float(), k, dim=-1)
+        w = torch.softmax(val, dim=-1)
+        counts = torch.bincount(idx.reshape(-1), minlength=E).to(torch.int32)
+        return idx.to(torch.int32), w, counts
+    logits = logits.float().contiguous()
+    idx = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    counts = torch.zeros(E, dtype=torch.int32, device=logits.device)
+    call("b200_router_topk", ptr(logits), T, E, k, ptr(idx), ptr(w), ptr(counts), stream_ptr())
+    return idx, w, counts
+
+
+def plan(idx: torch.Tensor, counts: torch.Tensor, n_experts: int, pad: int = PAD):
+    """Dispatch plan from the routing result: ``seg [E+1]`` padded segment offsets, ``tile_expert
+    [rows/pad]`` (-1 past the end), ``dest [pairs]`` destination row of every (token, slot) pair in
+    flattened order (stable inside an expert), ``rows`` the static buffer height."""
+    pairs = idx.numel()
+    rows = max_rows(pairs, n_experts, pad)
+    n_tiles = rows // pad
+    if not use_kernels(idx):
+        padded = (counts.long() + pad - 1) // pad * pad
+        seg = torch.zeros(n_experts + 1, dtype=torch.int64)
+        seg[1:] = torch.cumsum(padded, 0)
+        flat = idx.reshape(-1).long()
+        order = torch.argsort(flat, stable=True)
+        rank_in = torch.empty(pairs, dtype=torch.int64)
+        sorted_e = flat[order]
+        start = torch.zeros(n_experts + 1, dtype=torch.int64)
+        start[1:] = torch.cumsum(counts.long(), 0)
+        rank_in[order] = torch.arange(pairs) - start[sorted_e]
+        dest = (seg[flat] + rank_in).to(torch.int32)
+        tile_start = torch.arange(n_tiles) * pad
+        te = torch.searchsorted(seg[1:], tile_start, right=True)
+        te = torch.where(tile_start < seg[-1], te, torch.full_like(te, -1)).to(torch.int32)
+        return seg.to(torch.int32), te, dest, rows
+    dev = idx.device
+    seg = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+    te = torch.empty(n_tiles, dtype=torch.int32, device=dev)
+    dest = torch.empty(pairs, dtype=torch.int32, device=dev)
+    call("b200_router_plan", ptr(counts), ptr(idx.contiguous()), pairs, n_experts, pad, ptr(seg), ptr(te), n_tiles,
+         ptr(dest), stream_ptr())
+    return seg, te, dest, rows
+
+
+def permute_rows(x: torch.Tensor, dest: torch.Tensor, k: int, rows: int) -> torch.Tensor:
+    """``out[dest[p]] = x[p // k]``; rows that no pair maps to are zero."""
+    T, D = x.shape
+    out = torch.zeros((rows, D), dtype=x.dtype, device=x.device)
+    if not use_kernels(x) or x.dtype != torch.bfloat16:
+        out[dest.long()] = x.repeat_interleave(k, dim=0)
+        return out
+    call("b200_permute_rows", ptr(x.contiguous()), ptr(dest), dest.numel(), k, D, ptr(out), None, None, stream_ptr())
+    return out
+
+
+def unpermute_sum(yp: torch.Tensor, dest: torch.Tensor, w: torch.Tensor | None, T: int, k: int) -> torch.Tensor:
+    """``y[t] = sum_j w[t,j] * yp[dest[t*k + j]]`` (``w`` None = plain sum)."""
+    D = yp.shape[1]
+    if not use_kernels(yp) or yp.dtype != torch.bfloat16:
+        g = yp[dest.long()].view(T, k, D).float()
+        if w is not None:
+            g = g * w.view(T, k, 1).float()
+        return g.sum(1).to(yp.dtype)
+    y = torch.empty((T, D), dtype=yp.dtype, device=yp.device)
+    wf = None if w is None else w.float().contiguous()
+    call("b200_unpermute_sum", ptr(yp.contiguous()), ptr(dest), ptr(wf), T, k, D, ptr(y), stream_ptr())
+    return y
+
+
+def grouped_rows(a: torch.Tensor, b: torch.Tensor, tile_expert: torch.Tensor, seg: torch.Tensor, *,
+                 b_mn_major: bool = False) -> torch.Tensor:
+    """``d[r] = a[r] @ op(b[e(r)])^T`` over the padded row buffer.  ``b`` is ``[E, N, K]`` or, with
+    ``b_mn_major``, ``[E, K, N]``."""
+    rows, Kd = a.shape
+    E = b.shape[0]
+    N = b.shape[2] if b_mn_major else b.shape[1]
+    if not use_kernels(a) or a.dtype != torch.bfloat16:
+        out = torch.zeros((rows, N), dtype=a.dtype, device=a.device)
+        s = seg.tolist()
+        for e in range(E):
+            if s[e + 1] > s[e]:
+                w = b[e].float() if b_mn_major else b[e].float().t()
+                out[s[e]:s[e + 1]] = (a[s[e]:s[e + 1]].float() @ w).to(a.dtype)
+        return out
+    out = torch.empty((rows, N), dtype=a.dtype, device=a.device)
+    call("b200_gemm_grouped_rows", ptr(a.contiguous()), ptr(b.contiguous()), ptr(out), ptr(tile_expert), rows, N, Kd, E,
+         a.stride(0), out.stride(0), int(b_mn_major), 0, 1.0, stream_ptr())
+    # tiles past the last segment are not written: their rows are padding and are never read back
+    return out
+
+
+def grouped_wgrad(dy: torch.Tensor, x: torch.Tensor, seg: torch.Tensor, n_experts: int, *,
+                  out: torch.Tensor | None = None, accumulate: bool = False, out_dtype=None) -> torch.Tensor:
+    """``d[e] (+)= dy[seg[e]:seg[e+1]]^T @ x[seg[e]:seg[e+1]]`` -> ``[E, M, N]``."""
+    M, N = dy.shape[1], x.shape[1]
+    if out is None:
+        out = torch.zeros((n_experts, M, N), dtype=out_dtype or dy.dtype, device=dy.device)
+        accumulate = True if use_kernels(dy) else accumulate
+    if not use_kernels(dy) or dy.dtype != torch.bfloat16:
+        s = seg.tolist()
+        for e in range(n_experts):
+            g = dy[s[e]:s[e + 1]].float().t() @ x[s[e]:s[e + 1]].float()
+            if accumulate:
+                out[e] += g.to(out.dtype)
+            else:
+                out[e] = g.to(out.dtype)
+        return out
+    call("b200_gemm_grouped_wgrad", ptr(dy.contiguous()), ptr(x.contiguous()), ptr(out), ptr(seg), dy.shape[0], M, N,
+         n_experts, dy.stride(0), x.stride(0), int(out.dtype == torch.float32), int(accumulate), 1.0, stream_ptr())
+    return out
+
+
+# --------------------------------------------------------------------------------------
+# autograd
+# --------------------------------------------------------------------------------------
+class RouterFn(Function):
+    """top-k + softmax over the selected logits; the gradient flows to the selected logits only."""
+
+    @staticmethod
+    def forward(ctx, logits, k):
+        idx, w, counts = router_topk(logits, k)
+        ctx.save_for_backward(idx, w)
+        ctx.shape = logits.shape
+        ctx.mark_non_differentiable(idx, counts)
+        return idx, w, counts
+
+    @staticmethod
+    def backward(ctx, _gidx, gw, _gc):
+        idx, w = ctx.saved_tensors
+        g = w * (gw - (w * gw).sum(-1, keepdim=True))
+        out = torch.zeros(ctx.shape, dtype=gw.dtype, device=gw.device)
+        out.scatter_(1, idx.long(), g)
+        return out, None
+
+
+class PermuteFn(Function):
+    @staticmethod
+    def forward(ctx, x, dest, k, rows):
+        ctx.save_for_backward(dest)
+        ctx.cfg = (x.shape[0], k)
+        return permute_rows(x, dest, k, rows)
+
+    @staticmethod
+    def backward(ctx, g):
+        (dest,) = ctx.saved_tensors
+        T, k = ctx.cfg
+        return unpermute_sum(g.contiguous(), dest, None, T, k), None, None, None
+
+
+class UnpermuteFn(Function):
+    @staticmethod
+    def forward(ctx, yp, dest, w, T, k):
+        ctx.save_for_backward(yp, dest, w)
+        ctx.cfg = (T, k)
+        return unpermute_sum(yp, dest, w, T, k)
+
+    @staticmethod
+    def backward(ctx, gy):
+        yp, dest, w = ctx.saved_tensors
+        T, k = ctx.cfg
+        D = yp.shape[1]
+        gy = gy.contiguous()
+        gyp = permute_rows(gy, dest, k, yp.shape[0])
+        gw = None
+        if w is not None:
+            # scale the scattered rows by their routing weight; weight gradient = <gy[t], yp[dest]>
+            scale = torch.zeros(yp.shape[0], dtype=torch.float32, device=yp.device)
+            scale[dest.long()] = w.reshape(-1).float()
+            gw = (yp[dest.long()].view(T, k, D).float() * gy.view(T, 1, D).float()).sum(-1).to(w.dtype)
+            gyp = (gyp.float() * scale[:, None]).to(gyp.dtype)
+        return gyp, None, gw, None, None
+
+
+class GroupedMLPFn(Function):
+    """Expert MLP over the padded row buffer: ``swiglu(x W1[e]^T) W2[e]^T`` with the activation
+    recomputed in backward.  ``w1`` ``[E, 2F, D]`` (gate rows first), ``w2`` ``[E, D, F]``.  Weight
+    gradients accumulate into ``main_grad`` when the parameters carry one."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w2, seg, tile_expert):
+        gu = grouped_rows(x, w1, tile_expert, seg)
+        a = K.swiglu_fwd(gu)
+        y = grouped_rows(a, w2, tile_expert, seg)
+        ctx.save_for_backward(x, gu, w1, w2, seg, tile_expert)
+        ctx.refs = (w1, w2)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, gu, w1, w2, seg, tile_expert = ctx.saved_tensors
+        p1, p2 = ctx.refs
+        E = w1.shape[0]
+        gy = _zero_padding(gy.contiguous(), tile_expert)
+        a = K.swiglu_fwd(gu)
+        a = _zero_padding(a, tile_expert)
+        g2 = _wgrad_into(p2, gy, a, seg, E)
+        da = grouped_rows(gy, w2, tile_expert, seg, b_mn_major=True)
+        dgu = K.swiglu_bwd(da, gu)
+        dgu = _zero_padding(dgu, tile_expert)
+        g1 = _wgrad_into(p1, dgu, x, seg, E)
+        dx = grouped_rows(dgu, w1, tile_expert, seg, b_mn_major=True)
+        return dx, g1, g2, None, None
+
+
+def _zero_padding(t: torch.Tensor, tile_expert: torch.Tensor) -> torch.Tensor:
+    """Rows of tiles past the last segment may hold stale memory: zero them so the weight-gradient
+    contraction over whole tiles is exact (rows inside a segment's padding are already zero because
+    they come from zero inputs)."""
+    dead = (tile_expert < 0).repeat_interleave(PAD)
+    if dead.numel() == t.shape[0]:
+        t = t.masked_fill(dead[:, None], 0)
+    return t
+
+
+def _wgrad_into(param, dy, x, seg, E):
+    mg = getattr(param, "main_grad", None)
+    if not param.requires_grad:
+        return None
+    if mg is not None:
+        grouped_wgrad(dy, x, seg, E, out=mg, accumulate=True)
+        return None
+    return grouped_wgrad(dy, x, seg, E, out_dtype=param.dtype)
+
+
+def moe_experts(x, idx, w, counts, w1, w2):
+    """Local (all experts on this rank) MoE expert stage: dispatch by permutation, grouped MLP,
+    weighted combine.  ``x`` ``[T, D]``; returns ``[T, D]``."""
+    T, k = idx.shape
+    E = w1.shape[0]
+    seg, tile_expert, dest, rows = plan(idx, counts, E)
+    xp = PermuteFn.apply(x, dest, k, rows)
+    yp = GroupedMLPFn.apply(xp, w1, w2, seg, tile_expert)
+    return UnpermuteFn.apply(yp, dest, w, T, k)

@@ -135,8 +135,15 @@ class ZeroEngine:
         device = named[0][1].device
         groups: dict[str, list] = {}
         for n, p in named:
-            groups.setdefault(bucket_of(n), []).append((n, p))
-        self.buckets = [Bucket(k, groups[k], self.world, self.rank, opt, device) for k in sorted(groups)]
+            # expert-parallel parameters exist on one rank only: their bucket is not sharded or reduced
+            key = bucket_of(n) + ("_ep" if getattr(p, "expert_parallel", False) else "")
+            groups.setdefault(key, []).append((n, p))
+        self.buckets = []
+        for k in sorted(groups):
+            local = k.endswith("_ep")
+            b = Bucket(k, groups[k], 1 if local else self.world, 0 if local else self.rank, opt, device)
+            b.local_only = local
+            self.buckets.append(b)
         self.device = device
         self.step_count = 0
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=device)
@@ -157,6 +164,11 @@ class ZeroEngine:
     def _reduce_scatter(self, b: Bucket) -> None:
         if self.world == 1:
             return
+        if getattr(b, "local_only", False):
+            # gradients of local experts already contain every rank's contribution (they arrived
+            # through the backward all-to-all); only the 1/world of the global mean is missing
+            b.grad_buf.mul_(1.0 / self.world)
+            return
         if dist.get_backend(self.group) == "gloo":
             dist.all_reduce(b.grad_buf, group=self.group)
             b.grad_buf.div_(self.world)
@@ -164,7 +176,7 @@ class ZeroEngine:
             dist.reduce_scatter_tensor(b.g_shard(), b.grad_buf, op=dist.ReduceOp.AVG, group=self.group)
 
     def _all_gather(self, b: Bucket) -> None:
-        if self.world == 1:
+        if self.world == 1 or getattr(b, "local_only", False):
             return
         if dist.get_backend(self.group) == "gloo":
             parts = [torch.empty_like(b.p_shard()) for _ in range(self.world)]
@@ -205,7 +217,7 @@ class ZeroEngine:
                          weight_decay=o.weight_decay if wd else 0.0, step=self.step_count,
                          master=None if b.master is None else b.master[s:e], grad_scale=grad_scale,
                          sumsq_buf=self.sumsq if clip else None, max_norm=o.clip_grad, zero_grad=True)
-            if self.world > 1:
+            if self.world > 1 and not getattr(b, "local_only", False):
                 # the part of the bucket owned by other ranks still holds this step's gradients
                 if b.lo > 0:
                     b.grad_buf[:b.lo].zero_()

@@ -36,11 +36,11 @@ class TrainConfig:
 
 
 class PretrainTrainer:
-    def __init__(self, model_cfg: GPTConfig, opt: OptimConfig, train: TrainConfig, device, group=None):
+    def __init__(self, model_cfg: GPTConfig, opt: OptimConfig, train: TrainConfig, device, group=None, ep_group=None):
         self.cfg = model_cfg
         self.train_cfg = train
         self.device = torch.device(device)
-        self.model = GPT(model_cfg, device=self.device, seed=train.seed)
+        self.model = GPT(model_cfg, device=self.device, seed=train.seed, ep_group=ep_group)
         self.engine = ZeroEngine(self.model, opt, group=group, comm=train.comm)
         self.step_idx = 0
         if train.local_batch % train.micro_batch != 0:
