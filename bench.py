@@ -48,6 +48,8 @@ def parse():
     ap.add_argument("--local-batch", type=int, default=4)
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
+                    help="data-parallel step: in-kernel NVLink peer loads/stores, or NCCL collectives")
     ap.add_argument("--precision", default="mxfp8", choices=["mxfp8", "bf16"],
                     help="GEMM precision of the linears (attention, norms, residual stream stay bf16)")
     return ap.parse_args()
@@ -141,7 +143,7 @@ def main() -> int:
         cfg.seq_len = args.seq_len; reduced = True
     cfg.precision = args.precision if args.impl == "b200" else "bf16"
     opt = OptimConfig(lr=8e-4, beta1=0.9, beta2=0.95, eps=1e-5, weight_decay=0.1, clip_grad=1.0)
-    tc = TrainConfig(micro_batch=args.micro_batch, local_batch=args.local_batch, warmup_steps=64, seed=0)
+    tc = TrainConfig(micro_batch=args.micro_batch, local_batch=args.local_batch, warmup_steps=64, seed=0, comm=args.comm)
 
     if args.impl == "baseline":
         from baseline.torch_gpt import BaselineTrainer
@@ -215,7 +217,7 @@ def main() -> int:
             "impl": args.impl,
             "config": {"model": cfg.name, "layers": cfg.n_layers, "global_batch": args.local_batch * world,
                        "seq_len": cfg.seq_len, "micro_batch": args.micro_batch,
-                       "parallelism": f"dp{world} (ZeRO-sharded optimizer)",
+                       "parallelism": f"dp{world} (ZeRO-sharded optimizer, {args.comm if world > 1 else 'single GPU'} step)",
                        "l2": "no flush: per-step working set (>48 GB of weights and gradients) exceeds L2",
                        "reduced": reduced},
             "clocks": clocks, "gpu_launches": int(launches),

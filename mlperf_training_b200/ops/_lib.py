@@ -63,6 +63,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_unpermute_sum": [P, P, P, I, I, I, P, P],
         "b200_gemm_grouped_rows": [P, P, P, P, I, I, I, I, L, L, I, I, F, P],
         "b200_gemm_grouped_wgrad": [P, P, P, P, I, I, I, I, L, L, I, I, F, P],
+        "b200_zero_reduce_scatter": [P, I, I, L, L, F, P, P, P],
+        "b200_zero_adamw_all_gather": [P, I, I, L, L, P, P, P, P, F, F, F, F, F, I, F, P, F, I, P],
         "b200_attn_delta": [P, P, P, I, I, I, I, L, L, L, L, P],
         "b200_attn_bwd": [P] * 9 + [I] * 6 + [L] * 12 + [F, I, I, P],
     }
@@ -75,6 +77,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b200_norm_bwd_scratch_elems.argtypes = [I, I]
     lib.b200_norm_bwd_scratch_elems.restype = c_ll
     lib.b200_sumsq_scratch_elems.restype = c_int
+    if hasattr(lib, "b200_zero_grid"):
+        lib.b200_zero_grid.restype = c_int
 
 
 def declare_extra(name: str, argtypes: list, restype=c_int) -> None:

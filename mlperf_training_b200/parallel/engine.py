@@ -66,8 +66,9 @@ def no_weight_decay(name: str, p: torch.Tensor) -> bool:
 
 class Bucket:
     def __init__(self, key: str, params: list[tuple[str, nn.Parameter]], world: int, rank: int, opt: OptimConfig,
-                 device):
+                 device, symmetric_group=None):
         self.key = key
+        self.symm_param = self.symm_grad = None
         # weight-decayed parameters first, so each shard crosses the wd boundary at most once
         wd = [(n, p) for n, p in params if not no_weight_decay(n, p)]
         nowd = [(n, p) for n, p in params if no_weight_decay(n, p)]
@@ -84,8 +85,17 @@ class Bucket:
         self.numel = (cur + align - 1) // align * align
         self.shard = self.numel // world
         self.lo, self.hi = rank * self.shard, (rank + 1) * self.shard
-        self.param_buf = torch.zeros(self.numel, dtype=dtype, device=device)
-        self.grad_buf = torch.zeros(self.numel, dtype=opt.grad_dtype, device=device)
+        if symmetric_group is not None:
+            # peer-mapped buffers: every rank can read / write every rank's copy from inside a kernel
+            from .symm import SymmetricBuffer
+            self.symm_param = SymmetricBuffer(self.numel, dtype, symmetric_group, device)
+            self.symm_grad = SymmetricBuffer(self.numel, opt.grad_dtype, symmetric_group, device)
+            self.param_buf, self.grad_buf = self.symm_param.local, self.symm_grad.local
+            self.param_buf.zero_()
+            self.grad_buf.zero_()
+        else:
+            self.param_buf = torch.zeros(self.numel, dtype=dtype, device=device)
+            self.grad_buf = torch.zeros(self.numel, dtype=opt.grad_dtype, device=device)
         self.m = torch.zeros(self.shard, dtype=torch.float32, device=device)
         self.v = torch.zeros(self.shard, dtype=torch.float32, device=device)
         self.master = None
@@ -141,7 +151,9 @@ class ZeroEngine:
         self.buckets = []
         for k in sorted(groups):
             local = k.endswith("_ep")
-            b = Bucket(k, groups[k], 1 if local else self.world, 0 if local else self.rank, opt, device)
+            fused = comm == "fused" and self.world > 1 and not local and device.type == "cuda"
+            b = Bucket(k, groups[k], 1 if local else self.world, 0 if local else self.rank, opt, device,
+                       symmetric_group=(group if group is not None else dist.group.WORLD) if fused else None)
             b.local_only = local
             self.buckets.append(b)
         self.device = device
@@ -191,6 +203,59 @@ class ZeroEngine:
             b.grad_buf.zero_()
 
     @torch.no_grad()
+    def _step_fused(self, lr: float, grad_scale: float) -> None:
+        """Peer-memory path: reduce-scatter by P2P loads, AdamW + all-gather by P2P stores, both inside
+        this package's kernels; NCCL only carries the scalar of the clipping norm."""
+        from ..ops import _lib
+        o = self.opt
+        lib = _lib.load()
+        order = list(reversed(self.buckets))
+        fused = [b for b in order if b.symm_grad is not None]
+        if fused:
+            fused[0].symm_grad.barrier()          # every rank's gradients are final
+        clip = o.clip_grad > 0
+        grid = lib.b200_zero_grid()
+        first = True
+        for b in order:
+            if b.symm_grad is None:
+                self._reduce_scatter(b)
+                if clip:
+                    K.sumsq(b.g_shard(), self.sumsq, accumulate=not first)
+                    first = False
+                continue
+            if not hasattr(b, "rs_out"):
+                b.rs_out = torch.empty(b.shard, dtype=torch.float32, device=self.device)
+                b.rs_partial = torch.empty(grid, dtype=torch.float32, device=self.device)
+            _lib.call("b200_zero_reduce_scatter", b.symm_grad.ptr_array(), self.world, self.rank, b.lo, b.shard,
+                      1.0 / self.world, _lib.ptr(b.rs_out), _lib.ptr(b.rs_partial) if clip else None, _lib.stream_ptr())
+            if clip:
+                part = b.rs_partial.sum()
+                self.sumsq.copy_(part.view(1) if first else self.sumsq + part)
+                first = False
+        if clip:
+            dist.all_reduce(self.sumsq, group=self.group)
+            self.last_grad_norm = self.sumsq
+        for b in order:
+            if b.symm_grad is None:
+                ps, gs = b.p_shard(), b.g_shard()
+                for s, e, wd in b.segments():
+                    K.adamw_(ps[s:e], gs[s:e], b.m[s:e], b.v[s:e], lr=lr, beta1=o.beta1, beta2=o.beta2, eps=o.eps,
+                             weight_decay=o.weight_decay if wd else 0.0, step=self.step_count,
+                             master=None if b.master is None else b.master[s:e], grad_scale=grad_scale,
+                             sumsq_buf=self.sumsq if clip else None, max_norm=o.clip_grad, zero_grad=True)
+                continue
+            b.g_shard().zero_()                   # own copy of the reduced range (peers were cleared by the kernel)
+            for s, e, wd in b.segments():
+                _lib.call("b200_zero_adamw_all_gather", b.symm_param.ptr_array(), self.world, self.rank, b.lo + s, e - s,
+                          _lib.ptr(b.rs_out[s:e]), _lib.ptr(b.m[s:e]), _lib.ptr(b.v[s:e]),
+                          None if b.master is None else _lib.ptr(b.master[s:e]), float(lr), o.beta1, o.beta2, o.eps,
+                          o.weight_decay if wd else 0.0, self.step_count, float(grad_scale),
+                          _lib.ptr(self.sumsq) if clip else None, float(o.clip_grad), 0, _lib.stream_ptr())
+        if fused:
+            fused[0].symm_param.barrier()         # every rank's parameters have landed
+        bump_weight_epoch()
+
+    @torch.no_grad()
     def step(self, lr: float | None = None, grad_scale: float = 1.0) -> None:
         """Reduce-scatter, clip, AdamW on the local shard, all-gather.  ``grad_scale`` multiplies
         the accumulated gradients (1 / number of micro-batches).  Gradients are zeroed by the
@@ -198,6 +263,8 @@ class ZeroEngine:
         o = self.opt
         lr = o.lr if lr is None else lr
         self.step_count += 1
+        if any(b.symm_grad is not None for b in self.buckets):
+            return self._step_fused(lr, grad_scale)
         order = list(reversed(self.buckets))     # the order backward completes them
         for b in order:
             self._reduce_scatter(b)
