@@ -1,0 +1,65 @@
+"""Synthetic jagged interaction batches for the HSTU workload.
+
+Per user: a history whose length is log-normal (median ``length_median``) clipped to
+``[length_min, length_max]``, followed by one target; item ids Zipf(``zipf_alpha``) over the table;
+increasing timestamps; action bit masks.  The target's positive label depends on the item id so a
+model can learn it (AUC above chance) - used by the convergence tests.  Stands in for the
+reference's synthetic / Yambda loaders (generative_recommenders/dlrm_v4/datasets/dataset.py:1033-1209
+``DLRMv4RandomDataset``, yambda.py) with the same batch structure: jagged values + lengths, one
+storage per batch, pinned for the H2D copy.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+
+class HSTUSyntheticData:
+    def __init__(self, rows: int, batch: int, length_median: int = 512, length_min: int = 16, length_max: int = 4096,
+                 zipf_alpha: float = 1.05, sigma: float = 1.0, seed: int = 0, n_targets: int = 1):
+        self.rows, self.batch = rows, batch
+        self.median, self.lmin, self.lmax = length_median, length_min, length_max
+        self.alpha, self.sigma, self.seed, self.n_targets = zipf_alpha, sigma, seed, n_targets
+
+    def _zipf(self, rng: np.random.Generator, n: int) -> np.ndarray:
+        # inverse-CDF sample of a bounded Zipf: P(k) ~ k^-a on [1, rows]
+        a = self.alpha
+        u = rng.random(n)
+        if abs(a - 1.0) < 1e-9:
+            k = np.exp(u * np.log(self.rows))
+        else:
+            hi = self.rows ** (1.0 - a)
+            k = (1.0 + u * (hi - 1.0)) ** (1.0 / (1.0 - a))
+        return np.clip(k.astype(np.int64) - 1, 0, self.rows - 1)
+
+    def batch_at(self, step: int, rank: int = 0, pin: bool = False) -> dict:
+        rng = np.random.default_rng((self.seed * 1000003 + step) * 4099 + rank)
+        hist = np.clip(np.exp(rng.normal(np.log(self.median), self.sigma, self.batch)), self.lmin,
+                       self.lmax - self.n_targets).astype(np.int64)
+        lens = hist + self.n_targets
+        offsets = np.zeros(self.batch + 1, dtype=np.int32)
+        offsets[1:] = np.cumsum(lens)
+        total = int(offsets[-1])
+        ids = self._zipf(rng, total)
+        ts = np.zeros(total, dtype=np.int64)
+        actions = rng.integers(0, 8, total, dtype=np.int64)
+        for b in range(self.batch):
+            lo, hi = offsets[b], offsets[b + 1]
+            gaps = rng.integers(1, 3600, hi - lo)
+            ts[lo:hi] = 1_600_000_000 + np.cumsum(gaps)
+        tgt = np.concatenate([np.arange(offsets[b + 1] - self.n_targets, offsets[b + 1]) for b in range(self.batch)])
+        # learnable label: "listen-plus" (bit 1) on targets is a noisy function of the item id
+        pos = ((ids[tgt] * 2654435761) >> 7) % 4 < 2
+        flip = rng.random(len(tgt)) < 0.1
+        actions[tgt] = (actions[tgt] & ~1) | (pos ^ flip).astype(np.int64)
+        rows_pad = (total + 127) // 128 * 128
+        out = {"offsets": torch.from_numpy(offsets), "num_targets": torch.full((self.batch,), self.n_targets, dtype=torch.int32),
+               "timestamps": torch.from_numpy(ts), "actions": torch.from_numpy(actions), "item_ids": torch.from_numpy(ids),
+               "total": total, "rows": rows_pad, "lengths": torch.from_numpy(lens)}
+        if pin and torch.cuda.is_available():
+            out = {k: (v.pin_memory() if torch.is_tensor(v) else v) for k, v in out.items()}
+        return out
+
+    @staticmethod
+    def to_device(batch: dict, device) -> dict:
+        return {k: (v.to(device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()}

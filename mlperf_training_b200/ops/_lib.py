@@ -65,6 +65,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_gemm_grouped_wgrad": [P, P, P, P, I, I, I, I, L, L, I, I, F, P],
         "b200_zero_reduce_scatter": [P, I, I, L, L, F, P, P, P],
         "b200_zero_adamw_all_gather": [P, I, I, L, L, P, P, P, P, F, F, F, F, F, I, F, P, F, I, P],
+        "b200_hstu_attn_fwd": [P, P, P, P, P, P, I, L, I, I, I, I, L, L, L, L, F, P],
+        "b200_hstu_attn_bwd": [P, P, P, P, P, P, P, P, P, I, L, I, I, I, I, L, L, L, L, L, L, F, P],
         "b200_attn_delta": [P, P, P, I, I, I, I, L, L, L, L, P],
         "b200_attn_bwd": [P] * 9 + [I] * 6 + [L] * 12 + [F, I, I, P],
     }

@@ -1,0 +1,88 @@
+"""HSTU operators: jagged pointwise-SiLU attention (forward / backward) and its eager oracle.
+
+``hstu_attention(q, k, v, offsets, max_len, alpha, num_targets, contextual)`` works on jagged
+``[L, H, D]`` tensors (views into the fused ``uvqk`` projection buffer are fine: only the head dim
+must be contiguous).  Math and mask follow the reference oracle
+(generative_recommenders/ops/pytorch/pt_hstu_attention.py:33-84 mask, :130-187 attention):
+``O = (silu(alpha Q K^T) / N * mask) V`` with N the static maximum sequence length.
+"""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+
+from ._lib import call, ptr, stream_ptr, use_kernels
+
+
+def valid_mask(length: int, n_targets: int = 0, contextual: int = 0, device="cpu") -> torch.Tensor:
+    """Boolean ``[len, len]`` visibility matrix of one sequence (rows = queries)."""
+    pos = torch.arange(length, device=device)
+    max_id = length - n_targets - max(contextual - 1, 0)
+    ids = (pos - contextual + (1 if contextual > 0 else 0)).clamp(min=0, max=max_id)
+    row, col = ids[:, None], ids[None, :]
+    vis = (pos[:, None] == pos[None, :]) | (row > col)
+    if contextual > 0:
+        vis = vis | ((row == 0) & (pos[None, :] < length - n_targets))
+    return vis
+
+
+def hstu_attention_reference(q, k, v, offsets, max_len: int, alpha: float, num_targets=None, contextual: int = 0):
+    """fp32 eager oracle on jagged inputs; returns ``[L, H, D]`` fp32."""
+    out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+    offs = offsets.tolist()
+    for b in range(len(offs) - 1):
+        lo, hi = offs[b], offs[b + 1]
+        if hi <= lo:
+            continue
+        nt = int(num_targets[b]) if num_targets is not None else 0
+        qb, kb, vb = (t[lo:hi].float().transpose(0, 1) for t in (q, k, v))     # [H, len, D]
+        s = torch.matmul(qb, kb.transpose(-1, -2)) * alpha
+        p = torch.nn.functional.silu(s) / max_len
+        p = p * valid_mask(hi - lo, nt, contextual, q.device)[None]
+        out[lo:hi] = torch.matmul(p, vb).transpose(0, 1)
+    return out
+
+
+class HstuAttentionFn(Function):
+    @staticmethod
+    def forward(ctx, q, k, v, offsets, max_len, alpha, num_targets, contextual):
+        ctx.cfg = (max_len, alpha, contextual)
+        if not use_kernels(q):
+            ctx.save_for_backward(q, k, v, offsets, num_targets)
+            return hstu_attention_reference(q, k, v, offsets, max_len, alpha, num_targets, contextual).to(q.dtype)
+        L, H, D = q.shape
+        for t in (q, k, v):
+            if t.stride(2) != 1 or t.stride(1) != D:
+                raise ValueError("hstu_attention: heads must be contiguous inside a row")
+        offs = offsets.to(torch.int32).contiguous()
+        nt = None if num_targets is None else num_targets.to(torch.int32).contiguous()
+        out = torch.zeros((L, H, D), dtype=q.dtype, device=q.device)
+        call("b200_hstu_attn_fwd", ptr(q), ptr(k), ptr(v), ptr(out), ptr(offs), ptr(nt), offs.numel() - 1, L, H, D,
+             int(max_len), int(contextual), q.stride(0), k.stride(0), v.stride(0), out.stride(0), float(alpha),
+             stream_ptr())
+        ctx.save_for_backward(q, k, v, offs, nt)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, offs, nt = ctx.saved_tensors
+        max_len, alpha, contextual = ctx.cfg
+        if not use_kernels(q):
+            qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+            with torch.enable_grad():
+                o = hstu_attention_reference(qf, kf, vf, offs, max_len, alpha, nt, contextual)
+            dq, dk, dv = torch.autograd.grad(o, (qf, kf, vf), dout.float())
+            return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None, None, None
+        L, H, D = q.shape
+        dout = dout if (dout.stride(2) == 1 and dout.stride(1) == D) else dout.contiguous()
+        dq = torch.zeros((L, H, D), dtype=torch.float32, device=q.device)
+        dk = torch.zeros((L, H, D), dtype=k.dtype, device=q.device)
+        dv = torch.zeros((L, H, D), dtype=v.dtype, device=q.device)
+        call("b200_hstu_attn_bwd", ptr(q), ptr(k), ptr(v), ptr(dout), ptr(dq), ptr(dk), ptr(dv), ptr(offs), ptr(nt),
+             offs.numel() - 1, L, H, D, int(max_len), int(contextual), q.stride(0), k.stride(0), v.stride(0),
+             dout.stride(0), dk.stride(0), dv.stride(0), float(alpha), stream_ptr())
+        return dq.to(q.dtype), dk, dv, None, None, None, None, None
+
+
+def hstu_attention(q, k, v, offsets, max_len: int, alpha: float, num_targets=None, contextual: int = 0):
+    return HstuAttentionFn.apply(q, k, v, offsets, max_len, alpha, num_targets, contextual)

@@ -1,0 +1,140 @@
+"""FLUX.1-schnell MMDiT flow-matching training run.
+
+Constant-with-warm-up LR, AdamW (beta2 0.95, wd 0.1), prompt dropout 0.1, evaluation every
+``eval_every_samples`` samples against a target validation loss, FSDP-sharded optimizer state with
+parameters kept gathered after forward (``reshard_after_forward: 0`` as in the reference's
+submission, flux1/primus/config_common.sh:134).  Event stream and hyper-parameters follow
+flux1/primus/conf/flux.1_schnell_t2i-pretrain.yaml:25-89 and config_MI355X_1x8x32.sh:7-12.
+"""
+from __future__ import annotations
+
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+from ..mllog import core as ml
+from ..models.mmdit import PRESETS, MMDiT, MMDiTConfig
+from ..parallel.engine import OptimConfig, ZeroEngine
+
+
+def flux_bucket_of(name: str) -> str:
+    parts = name.split(".")
+    if parts[0] in ("double_blocks", "single_blocks"):
+        return f"{'d' if parts[0][0] == 'd' else 's'}{int(parts[1]):04d}"
+    return "a_io"
+
+
+class SyntheticFluxData:
+    """Pre-encoded sample stand-ins: latents N(0,1) ``[B, Si, 64]`` (already patchified), T5 states
+    N(0,1) ``[B, St, 4096]``, pooled CLIP N(0,1) ``[B, 768]`` - a pure function of (seed, step, rank)."""
+
+    def __init__(self, cfg: MMDiTConfig, seed: int = 0):
+        self.cfg, self.seed = cfg, seed
+
+    def batch(self, step: int, rank: int, local_batch: int):
+        g = torch.Generator().manual_seed((self.seed * 1000003 + step) * 4099 + rank)
+        c = self.cfg
+        return (torch.randn(local_batch, c.img_tokens, c.in_channels, generator=g),
+                torch.randn(local_batch, c.txt_tokens, c.txt_dim, generator=g),
+                torch.randn(local_batch, c.vec_dim, generator=g))
+
+
+class FluxTrainer:
+    def __init__(self, cfg: MMDiTConfig, opt: OptimConfig, device, local_batch: int, warmup_iters: int = 0,
+                 prompt_dropout: float = 0.1, comm: str = "nccl", seed: int = 0, micro_batch: int | None = None):
+        self.cfg, self.device = cfg, torch.device(device)
+        self.model = MMDiT(cfg, device=self.device, seed=seed)
+        self.engine = ZeroEngine(self.model, opt, bucket_of=flux_bucket_of, comm=comm)
+        self.local_batch = local_batch
+        self.micro_batch = micro_batch or local_batch
+        self.warmup_iters = warmup_iters
+        self.prompt_dropout = prompt_dropout
+        self.step_idx = 0
+        self.gen = torch.Generator(device=self.device).manual_seed(seed + 17)
+
+    def lr(self) -> float:
+        base = self.engine.opt.lr
+        return base * min(1.0, (self.step_idx + 1) / self.warmup_iters) if self.warmup_iters > 0 else base
+
+    def train_step_device(self, latents, txt, pooled) -> torch.Tensor:
+        n_micro = max(self.local_batch // self.micro_batch, 1)
+        total = None
+        for i in range(n_micro):
+            sl = slice(i * self.micro_batch, (i + 1) * self.micro_batch)
+            loss = self.model.loss(latents[sl], txt[sl], pooled[sl], generator=self.gen,
+                                   prompt_dropout=self.prompt_dropout)
+            loss.backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        self.engine.step(self.lr(), grad_scale=1.0 / n_micro)
+        self.step_idx += 1
+        return total / n_micro
+
+    def train_step(self, batch) -> float:
+        dev = [t.to(self.device, non_blocking=True) for t in batch]
+        return float(self.train_step_device(*dev).item())
+
+    @torch.no_grad()
+    def eval_loss(self, batch) -> float:
+        g = torch.Generator(device=self.device).manual_seed(1234)
+        dev = [t.to(self.device) for t in batch]
+        l = self.model.loss(*dev, generator=g, prompt_dropout=0.0)
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(l, op=dist.ReduceOp.AVG)
+        return float(l)
+
+
+def run(exp: dict, device: str | None = None, stream=None) -> dict:
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+    log = ml.MLLogger(rank=rank, stream=stream or sys.stdout, sync=dist.barrier if world > 1 else None)
+    log.log_init_start()
+    log.log_submission(exp.get("benchmark", "flux1"), platform=f"1xB200x{world}")
+    spec = dict(exp.get("model") or {})
+    cfg = PRESETS[spec.pop("preset", "flux1-schnell")]()
+    for k, v in spec.items():
+        setattr(cfg, k, tuple(v) if isinstance(v, list) else v)
+    gbs = int(exp.get("global_batch", 256))
+    local_batch = int(exp.get("local_batch", gbs // world))
+    opt = OptimConfig(lr=float(exp.get("lr", 2.5e-4)), beta1=0.9, beta2=float(exp.get("adam_beta2", 0.95)), eps=1e-8,
+                      weight_decay=float(exp.get("weight_decay", 0.1)), clip_grad=float(exp.get("clip_grad", 1.0)))
+    tr = FluxTrainer(cfg, opt, device, local_batch, warmup_iters=int(exp.get("lr_warmup_iters", 0)),
+                     prompt_dropout=float(exp.get("prompt_dropout", 0.1)),
+                     comm=(exp.get("fsdp") or {}).get("comm", "nccl"), seed=int(exp.get("seed", 0)),
+                     micro_batch=exp.get("micro_batch"))
+    data = SyntheticFluxData(cfg, seed=int(exp.get("seed", 0)))
+    log.log_hyperparameters({"global_batch_size": gbs, "seed": int(exp.get("seed", 0)), "opt_base_learning_rate": opt.lr,
+                             "opt_learning_rate_warmup_steps": tr.warmup_iters, "opt_adamw_beta_2": opt.beta2,
+                             "opt_adamw_weight_decay": opt.weight_decay})
+    log.log_init_stop_run_start()
+    log.start(ml.BLOCK_START, metadata={"samples_count": 0})
+    iters = int(exp.get("train_iters", 10))
+    eval_every = int(exp.get("eval_every_samples", 0))
+    target = float(exp.get("target_eval_loss", 0.0))
+    timer = ml.ThroughputTimer(gbs)
+    t0 = time.perf_counter()
+    losses, reached, last_eval, next_eval = [], False, None, eval_every
+    for step in range(iters):
+        timer.step_start()
+        losses.append(tr.train_step(data.batch(step, rank, local_batch)))
+        timer.step_stop()
+        samples = (step + 1) * gbs
+        log.event(ml.TRAIN_LOSS, losses[-1], metadata={"samples_count": samples})
+        if eval_every and samples >= next_eval:
+            next_eval += eval_every
+            log.end(ml.BLOCK_STOP, metadata={"samples_count": samples})
+            log.start(ml.EVAL_START, metadata={"samples_count": samples})
+            last_eval = tr.eval_loss(data.batch(10**6, rank, local_batch))
+            log.event(ml.EVAL_ACCURACY, last_eval, metadata={"samples_count": samples})
+            log.end(ml.EVAL_STOP, metadata={"samples_count": samples})
+            if target > 0 and last_eval <= target:
+                reached = True
+                break
+            log.start(ml.BLOCK_START, metadata={"samples_count": samples})
+    if not reached:
+        log.end(ml.BLOCK_STOP, metadata={"samples_count": timer.samples})
+    log.log_run_stop(reached or target <= 0, samples=timer.samples, duration_s=time.perf_counter() - t0)
+    return {"losses": losses, "eval_loss": last_eval, "throughput": timer.throughput(), "records": log.lines,
+            "trainer": tr}

@@ -125,3 +125,15 @@ def test_mxfp8_emulation_roundtrip():
     # the flat atom layout addresses every scale exactly once
     idx = mxfp8.sf_index(448, 256, 224, "cpu")
     assert idx.unique().numel() == idx.numel() and int(idx.max()) < mxfp8.sf_bytes(448, 256, 224)
+
+
+def test_hstu_mask_rules():
+    from mlperf_training_b200.ops.hstu_ops import valid_mask
+    m = valid_mask(5).int()
+    assert torch.equal(m, torch.tril(torch.ones(5, 5)).int())                 # plain causal
+    m = valid_mask(6, n_targets=2)                                            # rows 4, 5 are targets
+    assert m[4, :4].all() and m[5, :4].all() and m[4, 4] and m[5, 5] and not m[5, 4] and not m[4, 5]
+    m = valid_mask(7, n_targets=1, contextual=3)                              # rows 0..2 contextual
+    assert m[0, :6].all() and not m[0, 6]                                     # contextual rows see all history
+    assert m[3, :3].all() and m[3, 3] and not m[3, 4]
+    assert m[6, :6].all() and m[6, 6]
