@@ -67,6 +67,9 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_zero_adamw_all_gather": [P, I, I, L, L, P, P, P, P, F, F, F, F, F, I, F, P, F, I, P],
         "b200_hstu_attn_fwd": [P, P, P, P, P, P, I, L, I, I, I, I, L, L, L, L, F, P],
         "b200_hstu_attn_bwd": [P, P, P, P, P, P, P, P, P, I, L, I, I, I, I, L, L, L, L, L, L, F, P],
+        "b200_gather_rows_to_peers": [P, L, P, P, L, I, I, P, P, P],
+        "b200_rowwise_adagrad": [P, P, P, P, L, I, F, F, L, P],
+        "b200_segment_sum_rows": [P, P, L, I, P, P],
         "b200_attn_delta": [P, P, P, I, I, I, I, L, L, L, L, P],
         "b200_attn_bwd": [P] * 9 + [I] * 6 + [L] * 12 + [F, I, I, P],
     }

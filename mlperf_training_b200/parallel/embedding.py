@@ -1,0 +1,164 @@
+"""Row-wise sharded embedding table with a sparse optimizer applied in backward.
+
+Rank ``r`` of ``W`` owns the contiguous rows ``[r * rows_per_rank, (r + 1) * rows_per_rank)`` of the
+table (TorchRec's ROW_WISE sharding; the state dict exposes the shard with its global row offset
+under ``embeddings.<table>.weight`` so a TorchRec-style loader can place it).  A lookup is
+
+    dedup ids -> bucketise by owner -> exchange request counts and ids ->
+    owners read their rows -> rows travel back to the requesters -> expand to the original order
+
+and backward mirrors it: duplicate gradient rows are summed (sorted, fixed order), sent to the
+owners, summed again per unique row there and applied with row-wise Adagrad immediately
+(``apply_optimizer_in_backward`` in the reference, generative_recommenders/dlrm_v4/train/utils.py:1547-1783).
+
+``comm="nccl"`` moves the rows with ``all_to_all_single`` (the TorchRec / RCCL structure of the
+reference and the baseline here).  ``comm="fused"`` is the in-kernel NVLink path: the owner's
+gather kernel stores every requested row straight into the requester's symmetric receive buffer
+(``gather_rows_to_peers``), so the row all-to-all and the lookup are one kernel.  With a single
+rank both reduce to a local gather.
+"""
+from __future__ import annotations
+
+import ctypes
+import itertools
+
+import torch
+import torch.distributed as dist
+from torch.autograd import Function
+
+from ..ops import _lib
+from ..ops import kernels as K
+
+
+class ShardedEmbedding:
+    def __init__(self, rows: int, dim: int, *, group=None, device="cpu", dtype=torch.bfloat16, lr: float = 1e-2,
+                 eps: float = 1e-8, seed: int = 0, init_scale: float | None = None, comm: str = "nccl",
+                 max_requests: int = 1 << 20, name: str = "item"):
+        self.group = group
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.rows, self.dim, self.name = rows, dim, name
+        self.rows_per_rank = (rows + self.world - 1) // self.world
+        self.row_lo = self.rank * self.rows_per_rank
+        self.local_rows = max(min(self.rows_per_rank, rows - self.row_lo), 0)
+        self.device = torch.device(device)
+        g = torch.Generator(device=self.device).manual_seed(seed * 7919 + self.rank)
+        scale = init_scale if init_scale is not None else (1.0 / rows) ** 0.5
+        self.weight = (torch.rand(self.local_rows, dim, generator=g, device=self.device) * 2 - 1).mul_(scale).to(dtype)
+        self.state = torch.zeros(self.local_rows, dtype=torch.float32, device=self.device)   # Adagrad row sums
+        self.lr, self.eps = lr, eps
+        self.comm = comm if (self.world > 1 and self.device.type == "cuda") else "nccl"
+        self.recv = None
+        if self.comm == "fused":
+            from .symm import SymmetricBuffer
+            self.max_requests = max_requests
+            self.recv = SymmetricBuffer(max_requests * dim, dtype, group, self.device)
+
+    # ------------------------------------------------------------------ routing
+    def _route(self, ids: torch.Tensor):
+        """Dedup + bucketise.  Returns ``(uniq_sorted_by_owner, inverse, send_counts [W])``."""
+        uniq, inverse = torch.unique(ids, sorted=True, return_inverse=True)      # sorted ids = sorted by owner
+        owner = torch.clamp(uniq // self.rows_per_rank, max=self.world - 1)
+        send_counts = torch.bincount(owner, minlength=self.world)
+        return uniq, inverse, send_counts
+
+    def _exchange_ids(self, uniq, send_counts):
+        W = self.world
+        if W == 1:
+            return uniq - self.row_lo, send_counts.tolist(), send_counts.tolist(), None
+        counts = torch.empty((W, W), dtype=torch.int64, device=uniq.device)
+        dist.all_gather_into_tensor(counts.view(-1), send_counts.to(torch.int64), group=self.group) \
+            if uniq.is_cuda else dist.all_gather(list(counts.unbind(0)), send_counts.to(torch.int64), group=self.group)
+        counts_h = counts.tolist()                                  # counts_h[s][o]: rank s asks owner o
+        in_splits = counts_h[self.rank]
+        out_splits = [counts_h[s][self.rank] for s in range(W)]
+        recv_ids = torch.empty(sum(out_splits), dtype=torch.int64, device=uniq.device)
+        dist.all_to_all_single(recv_ids, uniq.contiguous(), out_splits, in_splits, group=self.group)
+        return recv_ids - self.row_lo, in_splits, out_splits, counts_h
+
+    # ------------------------------------------------------------------ forward / backward
+    def lookup(self, ids: torch.Tensor) -> torch.Tensor:
+        """``ids`` int64 ``[n]`` (global row ids) -> rows ``[n, dim]``; differentiable."""
+        return _LookupFn.apply(ids, self, torch.empty(0, requires_grad=True, device=ids.device))
+
+    def _forward_rows(self, ids):
+        uniq, inverse, send_counts = self._route(ids)
+        local_idx, in_splits, out_splits, counts_h = self._exchange_ids(uniq, send_counts)
+        W = self.world
+        if W == 1:
+            rows_u = K.gather_rows(self.weight, local_idx)
+        elif self.comm == "fused":
+            n_u = uniq.numel()
+            if n_u > self.max_requests:
+                raise RuntimeError(f"{n_u} unique ids exceed the receive buffer ({self.max_requests})")
+            recv_off = torch.tensor([0] + list(itertools.accumulate(out_splits)), dtype=torch.int64, device=ids.device)
+            # where my segment starts inside requester s's buffer: its requests to owners before me
+            base_rows = (ctypes.c_longlong * W)(*[sum(counts_h[s][:self.rank]) for s in range(W)])
+            self.recv.barrier()                                   # previous consumers are done with the buffers
+            _lib.call("b200_gather_rows_to_peers", _lib.ptr(self.weight), self.local_rows, _lib.ptr(local_idx),
+                      _lib.ptr(recv_off), int(sum(out_splits)), W, self.dim, self.recv.ptr_array(), base_rows,
+                      _lib.stream_ptr())
+            self.recv.barrier()                                   # every owner's rows have landed
+            rows_u = self.recv.local[: n_u * self.dim].view(n_u, self.dim).clone()
+        else:
+            served = K.gather_rows(self.weight, local_idx)
+            rows_u = torch.empty((uniq.numel(), self.dim), dtype=self.weight.dtype, device=ids.device)
+            dist.all_to_all_single(rows_u, served, in_splits, out_splits, group=self.group)
+        return rows_u, (uniq, inverse, local_idx, in_splits, out_splits)
+
+    def _backward_rows(self, grad: torch.Tensor, ctx_state) -> None:
+        uniq, inverse, local_idx, in_splits, out_splits = ctx_state
+        # 1. duplicates of this rank: sum per unique id in sorted (fixed) order
+        g_u = torch.zeros((uniq.numel(), self.dim), dtype=torch.float32, device=grad.device)
+        g_u.index_add_(0, inverse, grad.float())
+        # 2. to the owners
+        if self.world > 1:
+            recv = torch.empty((sum(out_splits), self.dim), dtype=torch.float32, device=grad.device)
+            dist.all_to_all_single(recv, g_u, out_splits, in_splits, group=self.group)
+            g_u = recv
+        # 3. several ranks may have asked for the same row: reduce per local row, then update
+        rows_l, inv_l = torch.unique(local_idx, sorted=True, return_inverse=True)
+        g_l = torch.zeros((rows_l.numel(), self.dim), dtype=torch.float32, device=grad.device)
+        g_l.index_add_(0, inv_l, g_u)
+        self.apply_rowwise_adagrad(rows_l, g_l)
+
+    def apply_rowwise_adagrad(self, rows: torch.Tensor, grads: torch.Tensor) -> None:
+        if rows.numel() == 0:
+            return
+        if self.weight.is_cuda and self.weight.dtype == torch.bfloat16:
+            _lib.call("b200_rowwise_adagrad", _lib.ptr(self.weight), _lib.ptr(self.state), _lib.ptr(rows.contiguous()),
+                      _lib.ptr(grads.contiguous()), rows.numel(), self.dim, float(self.lr), float(self.eps),
+                      self.local_rows, _lib.stream_ptr())
+            return
+        ok = (rows >= 0) & (rows < self.local_rows)
+        rows, grads = rows[ok], grads[ok]
+        st = self.state[rows] + (grads * grads).mean(-1)
+        self.state[rows] = st
+        upd = self.weight[rows].float() - self.lr * grads / (st.sqrt()[:, None] + self.eps)
+        self.weight[rows] = upd.to(self.weight.dtype)
+
+    # ------------------------------------------------------------------ state dict (TorchRec-style shard metadata)
+    def state_dict(self) -> dict:
+        key = f"embeddings.{self.name}.weight"
+        return {key: self.weight, f"{key}.row_offset": self.row_lo, f"{key}.global_rows": self.rows,
+                f"embeddings.{self.name}.rowwise_adagrad.sum": self.state}
+
+    def load_state_dict(self, sd: dict) -> None:
+        key = f"embeddings.{self.name}.weight"
+        if int(sd[f"{key}.row_offset"]) != self.row_lo or int(sd[f"{key}.global_rows"]) != self.rows:
+            raise ValueError("embedding shard layout differs from the checkpoint (resharding is not supported here)")
+        self.weight.copy_(sd[key])
+        self.state.copy_(sd[f"embeddings.{self.name}.rowwise_adagrad.sum"])
+
+
+class _LookupFn(Function):
+    @staticmethod
+    def forward(ctx, ids, table: ShardedEmbedding, _anchor):
+        rows_u, st = table._forward_rows(ids.reshape(-1))
+        ctx.table, ctx.state = table, st
+        return rows_u[st[1]]
+
+    @staticmethod
+    def backward(ctx, grad):
+        ctx.table._backward_rows(grad.contiguous(), ctx.state)
+        return None, None, None

@@ -1,0 +1,245 @@
+"""DLRMv4 / HSTU training run: sharded item-embedding lookup, dense HSTU model under the ZeRO
+engine, sparse row-wise Adagrad in backward, MLLOG events, window-AUC evaluation with a target,
+checkpoint cadence and host-side fault injection.
+
+Step structure (the reference's pipelined step, generative_recommenders/dlrm_v4/train/utils.py:4989-5255):
+
+    batch N+1 built on the host and copied H2D on a side stream  ||  step N on the main stream
+    lookup(ids) -> HSTU forward -> loss -> backward (sparse update applied inside) -> dense AdamW
+
+The train loss is read one step late from a pinned buffer (``PendingScalar``), so no step waits
+for a device-to-host copy; a ``StepFence`` bounds how far the host may run ahead
+(generative_recommenders/dlrm_v4/host_sync_free.py:595-660).
+"""
+from __future__ import annotations
+
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+from ..checkpoint.manager import CheckpointManager
+from ..data.hstu_synth import HSTUSyntheticData
+from ..mllog import core as ml
+from ..models.hstu import HSTU, HSTUConfig
+from ..parallel.embedding import ShardedEmbedding
+from ..parallel.engine import OptimConfig, ZeroEngine
+from ..utils.metrics import BinnedCumulativeAUC, window_auc
+
+
+class PendingScalar:
+    """A device scalar whose value is read on the host one step later from pinned memory."""
+
+    def __init__(self, device):
+        self.cuda = torch.device(device).type == "cuda"
+        self.buf = torch.zeros(1, dtype=torch.float32).pin_memory() if self.cuda else torch.zeros(1)
+        self.event = None
+        self.has = False
+
+    def push(self, t: torch.Tensor) -> float | None:
+        """Start copying ``t``; returns the previous value (None on the first call)."""
+        prev = self.read()
+        self.buf.copy_(t.detach().reshape(1).float(), non_blocking=True)
+        if self.cuda:
+            self.event = torch.cuda.Event()
+            self.event.record()
+        self.has = True
+        return prev
+
+    def read(self) -> float | None:
+        if not self.has:
+            return None
+        if self.event is not None:
+            self.event.synchronize()
+        return float(self.buf[0])
+
+
+class StepFence:
+    """Keeps the host at most ``lag`` steps ahead of the device."""
+
+    def __init__(self, lag: int = 1, enabled: bool = True):
+        self.lag, self.enabled, self.events = lag, enabled and torch.cuda.is_available(), []
+
+    def step(self) -> None:
+        if not self.enabled:
+            return
+        e = torch.cuda.Event()
+        e.record()
+        self.events.append(e)
+        if len(self.events) > self.lag:
+            self.events.pop(0).synchronize()
+
+
+def hstu_bucket_of(name: str) -> str:
+    parts = name.split(".")
+    return f"l{int(parts[1]):04d}" if parts[0] == "layers" else "a_misc"
+
+
+class HSTUTrainer:
+    def __init__(self, cfg: HSTUConfig, table_rows: int, batch_per_gpu: int, device, *, dense_lr=1e-3, sparse_lr=1e-2,
+                 clip_grad=1.0, emb_comm="nccl", dense_comm="nccl", seed=0, data_kw: dict | None = None, group=None):
+        self.cfg, self.device = cfg, torch.device(device)
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.model = HSTU(cfg, device=self.device, seed=seed)
+        opt = OptimConfig(lr=dense_lr, beta1=0.95, beta2=0.999, eps=1e-8, weight_decay=0.0, clip_grad=clip_grad)
+        self.engine = ZeroEngine(self.model, opt, bucket_of=hstu_bucket_of, comm=dense_comm, group=group)
+        self.table = ShardedEmbedding(table_rows, cfg.emb_dim, group=group, device=self.device, dtype=cfg.torch_dtype(),
+                                      lr=sparse_lr, seed=seed, comm=emb_comm, init_scale=0.05)
+        self.data = HSTUSyntheticData(table_rows, batch_per_gpu, seed=seed, **(data_kw or {}))
+        self.batch_per_gpu = batch_per_gpu
+        self.step_idx = 0
+        self.copy_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
+        self._next = None
+
+    # ------------------------------------------------------------------ data prefetch
+    def _stage(self, step: int):
+        host = self.data.batch_at(step, self.rank, pin=self.device.type == "cuda")
+        if self.copy_stream is None:
+            return host, None
+        with torch.cuda.stream(self.copy_stream):
+            dev = HSTUSyntheticData.to_device(host, self.device)
+            ev = torch.cuda.Event()
+            ev.record()
+        return dev, ev
+
+    def _take(self, step: int):
+        if self._next is None or self._next[0] != step:
+            self._next = (step, *self._stage(step))
+        _, batch, ev = self._next
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)       # only this batch's own H2D is awaited
+        self._next = (step + 1, *self._stage(step + 1))      # overlaps with the step below
+        return batch
+
+    # ------------------------------------------------------------------ steps
+    def embed(self, batch):
+        rows = batch["rows"]
+        emb = torch.zeros((rows, self.cfg.emb_dim), dtype=self.cfg.torch_dtype(), device=self.device)
+        emb[: batch["total"]] = self.table.lookup(batch["item_ids"]).to(emb.dtype)
+        return emb
+
+    def train_step_device(self, batch) -> torch.Tensor:
+        self.model.train()
+        loss, _, _ = self.model(batch, self.embed(batch))
+        loss.backward()
+        self.engine.step()
+        self.step_idx += 1
+        return loss.detach()
+
+    def train_step(self, step: int | None = None) -> torch.Tensor:
+        return self.train_step_device(self._take(self.step_idx if step is None else step))
+
+    @torch.no_grad()
+    def eval_batches(self, n_batches: int, start: int = 10**6):
+        self.model.eval()
+        ps, ls = [], []
+        for i in range(n_batches):
+            b = HSTUSyntheticData.to_device(self.data.batch_at(start + i, self.rank), self.device)
+            with torch.enable_grad():       # the lookup Function needs a graph only to skip its backward
+                emb = self.embed(b).detach()
+            _, p, l = self.model(b, emb)
+            ps.append(p)
+            ls.append(l)
+        return torch.cat(ps), torch.cat(ls)
+
+
+def run(exp: dict, device: str | None = None, stream=None) -> dict:
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+    sync = dist.barrier if world > 1 else None
+    ckpt = CheckpointManager(exp["checkpoint_dir"], rank, world, int(exp.get("keep_last", 2)), sync) \
+        if exp.get("checkpoint_dir") else None
+    resuming = bool(ckpt and ckpt.present())
+    log = ml.MLLogger(rank=rank, stream=stream or sys.stdout, sync=sync, append=resuming,
+                      filename=exp.get("mllog_file") or None)
+    if not resuming:
+        log.log_init_start()
+        log.log_submission(exp.get("benchmark", "dlrm_v4_hstu"), platform=f"1xB200x{world}")
+    m = dict(exp.get("model") or {})
+    cfg = HSTUConfig(layers=int(m.get("layers", 8)), dim=int(m.get("dim", 512)), heads=int(m.get("heads", 4)),
+                     d_qk=int(m.get("d_qk", 128)), d_v=int(m.get("d_v", 128)), max_seq_len=int(m.get("max_seq_len", 4096)),
+                     emb_dim=int((exp.get("embedding") or {}).get("dim", 256)), dtype=m.get("dtype", "bf16"),
+                     precision=m.get("precision", "bf16"), mlp_hidden=int(m.get("mlp_hidden", 256)),
+                     num_positions=int(m.get("num_positions", 8192)), num_time_buckets=int(m.get("num_time_buckets", 2048)))
+    emb = exp.get("embedding") or {}
+    d = dict(exp.get("data") or {})
+    data_kw = {k: d[k] for k in ("length_median", "length_min", "length_max", "zipf_alpha") if k in d}
+    bpg = int(exp.get("batch_per_gpu", 128))
+    tr = HSTUTrainer(cfg, int(emb.get("rows", 1_000_000)), bpg, device, dense_lr=float(exp.get("dense_lr", 1e-3)),
+                     sparse_lr=float(exp.get("sparse_lr", 1e-2)), clip_grad=float(exp.get("clip_grad", 1.0)),
+                     emb_comm=exp.get("emb_a2a", "nccl"), seed=int(exp.get("seed", 0)), data_kw=data_kw)
+    start = 0
+    if resuming:
+        ck = ckpt.load()
+        tr.model.load_state_dict(ck["dense"]["model"])
+        tr.table.load_state_dict(torch.load(ck["path"] / "sparse" / f"shard_rank{rank}.pt", weights_only=False))
+        if ck["optim"] is not None:
+            tr.engine.load_optimizer_state(ck["optim"])
+        CheckpointManager.restore_rng(ck["rng"])
+        start = int(ck["meta"]["step"])
+        tr.step_idx = start
+    else:
+        log.log_hyperparameters({"global_batch_size": bpg * world, "seed": int(exp.get("seed", 0)),
+                                 "opt_base_learning_rate": float(exp.get("dense_lr", 1e-3))})
+        log.log_init_stop_run_start()
+        log.start(ml.BLOCK_START, metadata={"samples_count": 0})
+    steps = int(exp.get("train_steps", 10))
+    eval_every = int(exp.get("eval_interval_steps", 0))
+    n_eval = int(exp.get("num_eval_batches", 2))
+    thr = float(exp.get("auc_threshold", 0.0))
+    die_at = int(exp.get("die_at_step", 0))
+    every = int(exp.get("checkpoint_every", 0))
+    timer = ml.ThroughputTimer(bpg * world)
+    pending, fence = PendingScalar(device), StepFence(1)
+    lifetime = BinnedCumulativeAUC(device=device)
+    losses, aucs, reached = [], [], False
+    t0 = time.perf_counter()
+    for step in range(start, steps):
+        timer.step_start()
+        loss = tr.train_step(step)
+        prev = pending.push(loss)
+        fence.step()
+        timer.step_stop()
+        if prev is not None:
+            losses.append(prev)
+            log.event(ml.TRAIN_LOSS, prev, metadata={"samples_count": step * bpg * world})
+        samples = (step + 1) * bpg * world
+        if eval_every and (step + 1) % eval_every == 0:
+            log.end(ml.BLOCK_STOP, metadata={"samples_count": samples})
+            log.start(ml.EVAL_START, metadata={"samples_count": samples})
+            p, l = tr.eval_batches(n_eval)
+            lifetime.update(p, l)
+            auc = window_auc(p, l)
+            aucs.append(auc)
+            log.event(ml.EVAL_ACCURACY, auc, metadata={"samples_count": samples})
+            log.end(ml.EVAL_STOP, metadata={"samples_count": samples})
+            stop = torch.tensor([1.0 if (thr > 0 and auc >= thr) else 0.0], device=device)
+            if world > 1:
+                dist.broadcast(stop, 0)                      # rank 0 decides, everyone leaves together
+            if stop.item() > 0:
+                reached = True
+                break
+            log.start(ml.BLOCK_START, metadata={"samples_count": samples})
+        if ckpt is not None and ((every and (step + 1) % every == 0) or (die_at and step + 1 == die_at)):
+            sd = tr.table.state_dict()
+            ckpt.save(step + 1, dense={"model": tr.model.state_dict()}, optim_shard=tr.engine.optimizer_state(),
+                      meta={"samples": samples, "window": 0, "batch_idx_in_window": step + 1},
+                      sparse_writer=lambda d_: torch.save(sd, d_ / f"shard_rank{rank}.pt"))
+        if die_at and step + 1 == die_at:
+            if world > 1:
+                dist.barrier()
+            log.close()
+            sys.exit(42)
+    last = pending.read()
+    if last is not None:
+        losses.append(last)
+    if not reached:
+        log.end(ml.BLOCK_STOP, metadata={"samples_count": timer.samples})
+    lifetime.sync()
+    log.log_run_stop(reached or thr <= 0, samples=timer.samples, duration_s=time.perf_counter() - t0)
+    log.close()
+    return {"losses": losses, "aucs": aucs, "lifetime_auc": lifetime.compute(), "throughput": timer.throughput(),
+            "records": log.lines, "trainer": tr}

@@ -1,0 +1,103 @@
+"""Recommender evaluation metrics: exact (sort-based) window AUC, additive binned cumulative AUC,
+normalised entropy and accuracy.
+
+``window_auc`` is the target metric of the recommender workload (``EVAL_ACCURACY`` = window AUC of
+the holdout pass, compared against ``AUC_THRESHOLD`` = 0.75;
+generative_recommenders/dlrm_v4/train/mlperf_logging_utils.py:671,731-745,803-826): predictions of
+all ranks are gathered and ranked.  ``BinnedCumulativeAUC`` keeps two float64 histograms of
+positive / negative weight over ``bins`` score bins; its state is additive, so cross-rank
+synchronisation is a sum all-reduce and it can be checkpointed
+(generative_recommenders/dlrm_v4/utils.py:188-280).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def exact_auc(scores: torch.Tensor, labels: torch.Tensor, weights: torch.Tensor | None = None) -> float:
+    """Weighted ROC AUC with ties counted half (0.5 when one class is absent)."""
+    s = scores.double().reshape(-1)
+    y = labels.double().reshape(-1)
+    w = torch.ones_like(s) if weights is None else weights.double().reshape(-1)
+    pos_w, neg_w = (w * y).sum(), (w * (1 - y)).sum()
+    if pos_w <= 0 or neg_w <= 0:
+        return 0.5
+    order = torch.argsort(s, stable=True)
+    s, y, w = s[order], y[order], w[order]
+    # group ties
+    new = torch.ones_like(s, dtype=torch.bool)
+    new[1:] = s[1:] != s[:-1]
+    gid = torch.cumsum(new.long(), 0) - 1
+    n = int(gid[-1]) + 1
+    pos_g = torch.zeros(n, dtype=torch.float64, device=s.device).index_add_(0, gid, w * y)
+    neg_g = torch.zeros(n, dtype=torch.float64, device=s.device).index_add_(0, gid, w * (1 - y))
+    neg_below = torch.cumsum(neg_g, 0) - neg_g
+    return float((pos_g * (neg_below + 0.5 * neg_g)).sum() / (pos_w * neg_w))
+
+
+def gather_all(t: torch.Tensor) -> torch.Tensor:
+    """Concatenate variable-length 1-D tensors of all ranks."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return t
+    n = torch.tensor([t.numel()], dtype=torch.int64, device=t.device)
+    sizes = [torch.zeros_like(n) for _ in range(dist.get_world_size())]
+    dist.all_gather(sizes, n)
+    m = int(max(int(s) for s in sizes))
+    pad = torch.zeros(m, dtype=t.dtype, device=t.device)
+    pad[: t.numel()] = t
+    bufs = [torch.zeros_like(pad) for _ in sizes]
+    dist.all_gather(bufs, pad)
+    return torch.cat([b[: int(s)] for b, s in zip(bufs, sizes)])
+
+
+def window_auc(scores: torch.Tensor, labels: torch.Tensor, weights: torch.Tensor | None = None) -> float:
+    s, y = gather_all(scores.float()), gather_all(labels.float())
+    w = None if weights is None else gather_all(weights.float())
+    return exact_auc(s, y, w)
+
+
+class BinnedCumulativeAUC:
+    def __init__(self, n_tasks: int = 1, bins: int = 100_000, device="cpu"):
+        self.bins = bins
+        self.pos = torch.zeros(n_tasks, bins, dtype=torch.float64, device=device)
+        self.neg = torch.zeros(n_tasks, bins, dtype=torch.float64, device=device)
+
+    def update(self, scores: torch.Tensor, labels: torch.Tensor, weights: torch.Tensor | None = None, task: int = 0):
+        b = (scores.double() * self.bins).long().clamp(0, self.bins - 1)
+        w = torch.ones_like(scores, dtype=torch.float64) if weights is None else weights.double()
+        y = labels.double()
+        self.pos[task].index_add_(0, b, w * y)
+        self.neg[task].index_add_(0, b, w * (1 - y))
+
+    def sync(self) -> None:
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(self.pos)
+            dist.all_reduce(self.neg)
+
+    def compute(self, task: int = 0) -> float:
+        pos, neg = self.pos[task], self.neg[task]
+        denom = pos.sum() * neg.sum()
+        if denom <= 0:
+            return 0.5
+        neg_below = torch.cumsum(neg, 0) - neg
+        return float((pos * (neg_below + 0.5 * neg)).sum() / denom)
+
+    def state_dict(self):
+        return {"pos": self.pos, "neg": self.neg}
+
+    def load_state_dict(self, sd):
+        self.pos.copy_(sd["pos"])
+        self.neg.copy_(sd["neg"])
+
+
+def normalized_entropy(scores: torch.Tensor, labels: torch.Tensor, eps: float = 1e-12) -> float:
+    p = scores.double().clamp(eps, 1 - eps)
+    y = labels.double()
+    ce = -(y * p.log() + (1 - y) * (1 - p).log()).mean()
+    base = y.mean().clamp(eps, 1 - eps)
+    return float(ce / -(base * base.log() + (1 - base) * (1 - base).log()))
+
+
+def accuracy(scores: torch.Tensor, labels: torch.Tensor, threshold: float = 0.5) -> float:
+    return float(((scores >= threshold).float() == labels.float()).float().mean())

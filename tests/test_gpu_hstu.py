@@ -45,3 +45,46 @@ def test_hstu_attention_fwd_bwd(lengths, targets, ctx, via_uvqk):
         g = got.float().cpu()
         s = want.abs().max().item() + 1e-9
         assert (g - want).abs().max().item() < 4e-2 * s + 1e-5, name
+
+
+def test_rowwise_adagrad_and_segment_sum_kernels():
+    from mlperf_training_b200.parallel.embedding import ShardedEmbedding
+    torch.manual_seed(0)
+    t = ShardedEmbedding(4096, 256, device="cuda", dtype=torch.bfloat16, lr=0.05, seed=3)
+    w0 = t.weight.float().clone()
+    ids = torch.randint(0, 4096, (3000,), device="cuda")
+    out = t.lookup(ids)
+    assert torch.equal(out, t.weight[ids])
+    w = torch.randn(3000, 256, device="cuda")
+    (out.float() * w).sum().backward()
+    torch.cuda.synchronize()
+    u, inv = torch.unique(ids, return_inverse=True)
+    g = torch.zeros(u.numel(), 256, device="cuda").index_add_(0, inv, w)
+    st = (g * g).mean(-1)
+    ref = w0.clone()
+    ref[u] = (w0[u] - 0.05 * g / (st.sqrt()[:, None] + t.eps)).bfloat16().float()
+    assert (t.weight.float() - ref).abs().max().item() < 1e-2
+    assert torch.allclose(t.state[u], st, rtol=1e-4, atol=1e-6)
+    # segment sum of sorted duplicate rows
+    src = torch.randn(1000, 256, device="cuda").bfloat16()
+    seg = torch.tensor([0, 1, 5, 5, 400, 1000], device="cuda")
+    o = torch.empty(5, 256, device="cuda")
+    _lib.call("b200_segment_sum_rows", _lib.ptr(src), _lib.ptr(seg), 5, 256, _lib.ptr(o), _lib.stream_ptr())
+    want = torch.stack([src[a:b].float().sum(0) for a, b in zip(seg[:-1].tolist(), seg[1:].tolist())])
+    assert torch.allclose(o, want, rtol=1e-4, atol=1e-3)
+
+
+def test_hstu_train_steps_on_gpu():
+    import io
+    from mlperf_training_b200.trainer.hstu import run
+    before = _lib.launch_count()
+    exp = dict(batch_per_gpu=16, train_steps=30, dense_lr=2e-3, sparse_lr=0.05, eval_interval_steps=15, num_eval_batches=2,
+               model=dict(layers=2, dim=256, heads=2, d_qk=128, d_v=128, max_seq_len=512, dtype="bf16", mlp_hidden=64,
+                          num_positions=512, num_time_buckets=128),
+               embedding=dict(rows=5000, dim=128), data=dict(length_median=100, length_min=8, length_max=400))
+    out = run(exp, device="cuda", stream=io.StringIO())
+    _lib.check_status("hstu run")
+    assert _lib.launch_count() > before
+    assert all(l == l for l in out["losses"])
+    assert sum(out["losses"][-5:]) < sum(out["losses"][:5])
+    assert out["aucs"][-1] > 0.55

@@ -11,11 +11,11 @@ pytestmark = pytest.mark.gpu
 HERE = Path(__file__).resolve().parent
 
 
-def _run(worker: str, nproc: int = 2, timeout: int = 600, extra_env: dict | None = None):
+def _run(worker: str, nproc: int = 2, timeout: int = 600, extra_env: dict | None = None, args=()):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-           "--master-addr", "127.0.0.1", "--master-port", "29611", str(HERE / "multi" / worker)]
+           "--master-addr", "127.0.0.1", "--master-port", "29611", str(HERE / "multi" / worker), *args]
     return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
 
 
@@ -24,3 +24,10 @@ def test_fused_zero_step_matches_nccl():
     res = _run("zero_fused_worker.py")
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "RESULT ok=True" in res.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("comm", ["nccl", "fused"])
+def test_sharded_embedding_two_gpus(comm):
+    res = _run("embedding_worker.py", args=("nccl", comm))
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]

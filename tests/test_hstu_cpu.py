@@ -1,0 +1,92 @@
+"""HSTU workload on CPU: metrics, sharded embedding (single rank + gloo world 2), trainer run with
+MLLOG compliance and a fault-injected resume."""
+import io
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from mlperf_training_b200.mllog import check_compliance
+from mlperf_training_b200.parallel.embedding import ShardedEmbedding
+from mlperf_training_b200.utils.metrics import BinnedCumulativeAUC, exact_auc, normalized_entropy
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _exp(**kw):
+    e = dict(batch_per_gpu=8, train_steps=12, dense_lr=3e-3, sparse_lr=0.1, eval_interval_steps=6, num_eval_batches=2,
+             model=dict(layers=2, dim=32, heads=2, d_qk=16, d_v=16, max_seq_len=48, dtype="fp32", mlp_hidden=16,
+                        num_positions=64, num_time_buckets=32),
+             embedding=dict(rows=200, dim=16), data=dict(length_median=12, length_min=4, length_max=40))
+    e.update(kw)
+    return e
+
+
+def test_auc_matches_pair_counting():
+    g = torch.Generator().manual_seed(0)
+    s = torch.rand(200, generator=g).round(decimals=2)          # ties on purpose
+    y = (torch.rand(200, generator=g) < 0.3).float()
+    pos, neg = s[y == 1], s[y == 0]
+    brute = ((pos[:, None] > neg[None]).double() + 0.5 * (pos[:, None] == neg[None]).double()).mean().item()
+    assert abs(exact_auc(s, y) - brute) < 1e-12
+    b = BinnedCumulativeAUC(bins=100)
+    b.update(s[:100], y[:100])
+    b.update(s[100:], y[100:])
+    assert abs(b.compute() - brute) < 2e-2
+    b2 = BinnedCumulativeAUC(bins=100)
+    b2.load_state_dict(b.state_dict())
+    assert b2.compute() == b.compute()
+    assert exact_auc(s, torch.ones_like(y)) == 0.5
+    assert normalized_entropy(torch.full((100,), float(y.mean())), y[:100]) > 0.9
+
+
+def test_sharded_embedding_single_rank_adagrad():
+    t = ShardedEmbedding(50, 8, dtype=torch.float32, lr=0.5, seed=1)
+    w0 = t.weight.clone()
+    ids = torch.tensor([3, 7, 3, 9])
+    out = t.lookup(ids)
+    assert torch.equal(out, w0[ids])
+    out.sum().backward()
+    g = torch.zeros(50, 8)
+    g[3], g[7], g[9] = 2.0, 1.0, 1.0
+    st = (g * g).mean(-1)
+    ref = w0 - 0.5 * g / (st.sqrt()[:, None] + t.eps)
+    assert torch.allclose(t.weight, ref, atol=1e-6)
+    sd = t.state_dict()
+    assert sd["embeddings.item.weight.row_offset"] == 0
+    t2 = ShardedEmbedding(50, 8, dtype=torch.float32, seed=2)
+    t2.load_state_dict(sd)
+    assert torch.equal(t2.weight, t.weight)
+
+
+def test_sharded_embedding_gloo_world2():
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29631",
+                        os.path.join(ROOT, "tests", "multi", "embedding_worker.py"), "gloo"],
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_hstu_run_learns_and_logs():
+    from mlperf_training_b200.trainer.hstu import run
+    out = run(_exp(train_steps=40, eval_interval_steps=20), device="cpu", stream=io.StringIO())
+    assert out["losses"][-1] < out["losses"][0]
+    assert out["aucs"][-1] > 0.6
+    assert check_compliance(out["records"]) == []
+
+
+def test_hstu_die_and_resume(tmp_path):
+    from mlperf_training_b200.trainer.hstu import run
+    ref = run(_exp(), device="cpu", stream=io.StringIO())
+    e = _exp(checkpoint_dir=str(tmp_path / "ck"), die_at_step=6, mllog_file=str(tmp_path / "ml.log"))
+    with pytest.raises(SystemExit) as ex:
+        run(e, device="cpu", stream=io.StringIO())
+    assert ex.value.code == 42
+    e["die_at_step"] = 0
+    out = run(e, device="cpu", stream=io.StringIO())
+    assert abs(out["losses"][-1] - ref["losses"][-1]) < 1e-5
+    lines = open(tmp_path / "ml.log").read().splitlines()
+    assert sum("run_start" in l for l in lines) == 1 and sum("run_stop" in l for l in lines) == 1
