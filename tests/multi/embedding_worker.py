@@ -32,7 +32,7 @@ def main():
         g = torch.Generator().manual_seed(100 * it + rank)
         ids = torch.randint(0, rows, (300,), generator=g).to(device)
         ids[:20] = ids[20:40]                                   # duplicates inside a rank
-        w = torch.randn(300, dim, generator=g).to(device)
+        w = torch.randn(300, dim, generator=g).to(device).to(dtype).float()
         out = tab.lookup(ids)
         ok &= bool(torch.allclose(out.float(), full[ids], atol=1e-2, rtol=1e-2))
         (out.float() * w).sum().backward()

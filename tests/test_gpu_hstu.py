@@ -55,7 +55,7 @@ def test_rowwise_adagrad_and_segment_sum_kernels():
     ids = torch.randint(0, 4096, (3000,), device="cuda")
     out = t.lookup(ids)
     assert torch.equal(out, t.weight[ids])
-    w = torch.randn(3000, 256, device="cuda")
+    w = torch.randn(3000, 256, device="cuda").bfloat16().float()     # the gradient reaches the table in bf16
     (out.float() * w).sum().backward()
     torch.cuda.synchronize()
     u, inv = torch.unique(ids, return_inverse=True)
