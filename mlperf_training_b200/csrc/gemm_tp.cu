@@ -1,0 +1,601 @@
+// Tensor-parallel GEMMs fused with their collective over NVLink peer memory (bf16, tcgen05).
+//
+//   mode 1  all-gather -> GEMM (rows):  D[T, N] = gather_rows(A)[T, K] * B^T.  Every rank holds the
+//           rows [r*T/W, (r+1)*T/W) of A in its copy of a symmetric buffer.  A few CTAs of the SAME
+//           kernel pull the peers' row blocks into the local buffer with bulk async copies
+//           (global(peer) -> shared -> global(local)) and publish one counter per peer block; the
+//           TMA producer of every GEMM CTA waits on the counter of the block its tile needs.  Tiles
+//           are visited own-block first, then peer rank+1, rank+2, ... - the order the copies land.
+//   mode 2  all-gather -> GEMM (reduction dim):  the gathered dimension is K (weight gradients:
+//           K = tokens).  Same copy CTAs; the producer starts its k loop at the local block and
+//           waits per k block.
+//   mode 3  GEMM -> reduce-scatter:  P = A * B^T is a partial sum [T, N]; rank o owns rows
+//           [o*T/W, ...).  Epilogue warps store each bf16 tile straight into the OWNER's staging
+//           buffer (slot of the sending rank) with peer stores and bump the owner's per-row-tile
+//           counter; reduce work items (8 rows x N) are claimed from a queue by a few dedicated CTAs
+//           and by the GEMM CTAs once their tiles are done: wait for the counter, sum the W slots
+//           in fp32 (+ residual), write the bf16 result.  Tiles are ordered row-tile-major across
+//           owners so row tile j of every owner completes while tile j+1 is being computed.
+//
+// The reference runs these as library collectives around library GEMMs (Megatron tensor / sequence
+// parallel linears; the TransformerEngine userbuffer overlap is switched off in every shipped
+// config: llama2_sft/primus/config_MI355X_1x8x1.sh:115-118).
+//
+// Loads never use cluster multicast.  Every wait is bounded (2 s) and reports into the status block.
+#include "common.cuh"
+#include "runtime.h"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 4;
+constexpr int STG_BYTES = 4096;
+constexpr int MAXW = 16;
+constexpr int COPY_PIECE = 32768;     // bytes per bulk copy
+constexpr int COPY_STAGES = 6;
+constexpr int RS_SPLIT = 16;          // reduce work items per 128-row tile (8 rows each)
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_STAGE = BM * BK * 2;
+  static constexpr int B_STAGE = BN * BK * 2;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int EPI_BYTES = EPI_WARPS * 2 * STG_BYTES;
+  static constexpr int SMEM = STAGES * (A_STAGE + B_STAGE) + EPI_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static_assert(COPY_STAGES * COPY_PIECE + 1024 + 256 <= SMEM, "copy ring must fit the GEMM allocation");
+};
+
+struct Params {
+  int M, N, K;
+  int a_mn_major, b_mn_major;
+  int out_f32, accumulate;
+  int group_m;
+  float alpha;
+  int* status;
+  // ---- tensor-parallel part
+  int mode, W, rank;
+  int rows_per;                    // rows (mode 1, 3) or k elements (mode 2) per rank block
+  int n_aux;                       // copy CTAs (mode 1, 2) / dedicated reduce CTAs (mode 3): blockIdx < n_aux
+  // gather
+  const uint8_t* peer_src[MAXW];   // base of rank c's gather buffer (same layout everywhere)
+  uint8_t* gdst;                   // local gather buffer
+  long long chunk_bytes;           // bytes of one rank block (contiguous)
+  int pieces_per_chunk;
+  int* chunk_flag;                 // [W] local counters, zero at launch
+  // reduce-scatter
+  uint8_t* stage_peer[MAXW];       // rank o's staging buffer [W][rows_per][N] bf16
+  int* flag_peer[MAXW];            // rank o's counters [rows_per / BM], zero at launch
+  int* work_counter;               // local, zero at launch
+  __nv_bfloat16* rs_out;
+  long long ld_out;
+  const __nv_bfloat16* rs_residual;
+  long long ld_res;
+};
+
+B200_DEVICE void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+B200_DEVICE void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+B200_DEVICE void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+B200_DEVICE void red_release_gpu_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+B200_DEVICE void red_release_sys_add(int* p, int v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+B200_DEVICE uint4 ld_cg_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// logical tile index -> (row tile, column tile) with the visiting order of the mode
+B200_DEVICE void tile_coords(int t, int num_m, int num_n, const Params& p, int& mb, int& nb) {
+  const int in_group = p.group_m * num_n;
+  const int g = t / in_group;
+  const int first_m = g * p.group_m;
+  const int gsz = min(num_m - first_m, p.group_m);
+  const int r = t - g * in_group;
+  const int ml = first_m + (r % gsz);
+  nb = r / gsz;
+  if (p.mode == 1) {
+    const int tpc = p.rows_per / BM;
+    mb = ((p.rank + ml / tpc) % p.W) * tpc + (ml % tpc);
+  } else if (p.mode == 3) {
+    const int tpc = p.rows_per / BM;
+    mb = ((p.rank + 1 + ml % p.W) % p.W) * tpc + ml / p.W;
+  } else {
+    mb = ml;
+  }
+}
+
+// ------------------------------ copy CTA (modes 1, 2) ------------------------------
+// One thread drives a ring of bulk copies peer -> shared -> local and publishes a piece two
+// stores after it was issued (its bulk group is then complete).
+B200_DEVICE void copy_cta(const Params& p, uint8_t* smem, uint64_t* bars) {
+  if (threadIdx.x != 0) return;
+  for (int i = 0; i < COPY_STAGES; ++i) mbar_init(&bars[i], 1);
+  mbar_fence_init();
+  const int ppc = p.pieces_per_chunk;
+  const int total = (p.W - 1) * ppc;
+  const int mine = (total - (int)blockIdx.x + p.n_aux - 1) / p.n_aux;   // pieces blockIdx, blockIdx + n_aux, ...
+  volatile int dummy_abort = 0;
+  auto piece_of = [&](int i, int& chunk, long long& off, uint32_t& bytes) {
+    const int g = blockIdx.x + i * p.n_aux;
+    chunk = (p.rank + 1 + g / ppc) % p.W;
+    off = (long long)(g % ppc) * COPY_PIECE;
+    const long long left = p.chunk_bytes - off;
+    bytes = (uint32_t)(left < COPY_PIECE ? left : COPY_PIECE);
+  };
+  auto issue_load = [&](int i) {
+    int c; long long off; uint32_t bytes;
+    piece_of(i, c, off, bytes);
+    const int s = i % COPY_STAGES;
+    mbar_expect_tx(&bars[s], bytes);
+    bulk_g2s(smem + s * COPY_PIECE, p.peer_src[c] + (long long)c * p.chunk_bytes + off, bytes, &bars[s]);
+  };
+  auto publish = [&](int i) {
+    int c; long long off; uint32_t bytes;
+    piece_of(i, c, off, bytes);
+    fence_proxy_async_all();
+    red_release_gpu_add(p.chunk_flag + c, 1);
+  };
+  const int ahead = COPY_STAGES - 2;
+  for (int i = 0; i < mine && i < ahead; ++i) issue_load(i);
+  bool ok = true;
+  for (int i = 0; i < mine; ++i) {
+    const int s = i % COPY_STAGES;
+    if (!mbar_wait(&bars[s], (i / COPY_STAGES) & 1, &dummy_abort, p.status, 40)) { ok = false; break; }
+    int c; long long off; uint32_t bytes;
+    piece_of(i, c, off, bytes);
+    bulk_s2g(p.gdst + (long long)c * p.chunk_bytes + off, smem + s * COPY_PIECE, bytes);
+    tma_store_commit();
+    tma_store_wait_all<2>();                 // stores up to i-2 are complete
+    if (i >= 2) publish(i - 2);
+    if (i + ahead < mine) issue_load(i + ahead);   // stage (i-2) % STAGES: its store has completed
+  }
+  tma_store_wait_all<0>();
+  if (ok) {
+    if (mine >= 2) publish(mine - 2);
+    if (mine >= 1) publish(mine - 1);
+  } else {
+    // loads that never completed may still land: give them time before shared memory is released
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+}
+
+// ------------------------------ reduce work (mode 3) ------------------------------
+// `nthreads` threads (a named barrier `bar_id` among them) claim items until the queue is empty.
+B200_DEVICE void reduce_loop(const Params& p, int num_n, int tid, int nthreads, int bar_id, volatile int* slot,
+                             volatile int* abort_flag) {
+  const int tpc = p.rows_per / BM;
+  const int items = tpc * RS_SPLIT;
+  const int nvec = p.N / 8;
+  const uint8_t* stage = p.stage_peer[p.rank];
+  const int* flags = p.flag_peer[p.rank];
+  while (true) {
+    if (tid == 0) {
+      int it = (abort_flag != nullptr && *abort_flag) ? items : atomicAdd(p.work_counter, 1);
+      if (it < items) {
+        const int want = p.W * num_n * EPI_WARPS;
+        if (!flag_wait_geq(flags + it / RS_SPLIT, want, B200_WAIT_LIMIT_NS, p.status, 50)) it = items;  // give up
+      }
+      *slot = it;
+    }
+    named_bar_sync(bar_id, nthreads);
+    const int it = *slot;
+    named_bar_sync(bar_id, nthreads);      // everyone has read the slot before it is rewritten
+    if (it >= items) break;
+    const int row0 = (it / RS_SPLIT) * BM + (it % RS_SPLIT) * (BM / RS_SPLIT);
+    for (int idx = tid; idx < (BM / RS_SPLIT) * nvec; idx += nthreads) {
+      const int row = row0 + idx / nvec;
+      const int v = idx % nvec;
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      if (p.rs_residual != nullptr) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p.rs_residual + (long long)row * p.ld_res + v * 8);
+        const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+        acc[0] = f0.x; acc[1] = f0.y; acc[2] = f1.x; acc[3] = f1.y; acc[4] = f2.x; acc[5] = f2.y; acc[6] = f3.x; acc[7] = f3.y;
+      }
+      for (int s = 0; s < p.W; ++s) {
+        const uint4 u = ld_cg_u4(stage + (((long long)s * p.rows_per + row) * p.N + v * 8) * 2);
+        const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+      const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                                 pack_bf16x2(acc[6], acc[7]));
+      *reinterpret_cast<uint4*>(p.rs_out + (long long)row * p.ld_out + v * 8) = o;
+    }
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmD, const __grid_constant__ Params p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + C::STAGES * C::A_STAGE;
+  uint8_t* sE = sB + C::STAGES * C::B_STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sE + C::EPI_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + C::STAGES;
+  uint64_t* tfull = bars + 2 * C::STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  volatile int* work_slot = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  // ---------------- auxiliary CTAs: no tensor memory, no GEMM barriers ----------------
+  if ((int)blockIdx.x < p.n_aux) {
+    if (p.mode == 3) reduce_loop(p, num_n, threadIdx.x, NUM_THREADS, 2, work_slot, nullptr);
+    else copy_cta(p, smem, bars);
+    return;
+  }
+  const int cta = blockIdx.x - p.n_aux;
+  const int n_gemm = gridDim.x - p.n_aux;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], EPI_WARPS); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB);
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      uint32_t ready = 1u << p.rank;          // rank blocks known to be in the local buffer
+      const int kb_per = (p.mode == 2) ? p.rows_per / BK : 0;
+      const int kb_start = (p.mode == 2) ? p.rank * kb_per : 0;
+      auto need = [&](int c) -> bool {
+        if (ready & (1u << c)) return true;
+        if (!flag_wait_geq(p.chunk_flag + c, p.pieces_per_chunk, B200_WAIT_LIMIT_NS, p.status, 11)) {
+          *abort_flag = 1;
+          return false;
+        }
+        fence_proxy_async_all();              // the copies were written through the async proxy of another CTA
+        ready |= 1u << c;
+        return true;
+      };
+      for (int t = cta; t < num_tiles && ok; t += n_gemm) {
+        int mb, nb; tile_coords(t, num_m, num_n, p, mb, nb);
+        const int m0 = mb * BM, n0 = nb * BN;
+        if (p.mode == 1 && !need(m0 / p.rows_per)) { ok = false; break; }
+        for (int i = 0; i < num_kb; ++i) {
+          int kb = i;
+          if (p.mode == 2) {
+            kb = kb_start + i;
+            if (kb >= num_kb) kb -= num_kb;
+            if (!need(kb / kb_per)) { ok = false; break; }
+          }
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, 10)) { ok = false; break; }
+          mbar_expect_tx(&full[stage], C::A_STAGE + C::B_STAGE);
+          uint8_t* a_dst = sA + stage * C::A_STAGE;
+          uint8_t* b_dst = sB + stage * C::B_STAGE;
+          const int k0 = kb * BK;
+          if (!p.a_mn_major) {
+            tma_load_2d(a_dst, &tmA, &full[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), &tmA, &full[stage], m0 + 64 * j, k0);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d(b_dst, &tmB, &full[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), &tmB, &full[stage], n0 + 64 * j, k0);
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(1, 1, p.a_mn_major, p.b_mn_major, BM, BN);
+      const uint32_t a_lbo = p.a_mn_major ? BK * 128 : 16;
+      const uint32_t b_lbo = p.b_mn_major ? BK * 128 : 16;
+      const uint32_t a_kstep = p.a_mn_major ? UMMA_K * 128 : UMMA_K * 2;
+      const uint32_t b_kstep = p.b_mn_major ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0; uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = cta; t < num_tiles && ok; t += n_gemm, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag, p.status, 20)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 21)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * C::A_STAGE);
+          const uint32_t b_addr = smem_u32(sB + stage * C::B_STAGE);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t ad = umma_desc_sw128(a_addr + kk * a_kstep, a_lbo, 1024);
+            const uint64_t bd = umma_desc_sw128(b_addr + kk * b_kstep, b_lbo, 1024);
+            tc_mma_f16_ss(d_tmem, ad, bd, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty[stage]);
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit(&tfull[acc]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;
+    const int ew = warp - 2;
+    uint8_t* stg = sE + ew * 2 * STG_BYTES;
+    int buf = 0;
+    int it = 0;
+    bool ok = true;
+    for (int t = cta; t < num_tiles && ok; t += n_gemm, ++it) {
+      int mb, nb; tile_coords(t, num_m, num_n, p, mb, nb);
+      const int m0 = mb * BM, n0 = nb * BN;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, p.status, 30)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+      // mode 3: destination row inside the owner's staging slot of this rank
+      const int owner = (p.mode == 3) ? m0 / p.rows_per : 0;
+      uint8_t* rs_row = nullptr;
+      if (p.mode == 3) {
+        const int row_in = m0 - owner * p.rows_per + q * 32 + lane;
+        rs_row = p.stage_peer[owner] + ((long long)p.rank * p.rows_per + row_in) * p.N * 2;
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tc_wait_ld();
+        const int col0 = n0 + c * 32;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+        if (p.mode == 3) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (col0 + j * 8 < p.N) {
+              const uint4 u = make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
+                                         pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+              *reinterpret_cast<uint4*>(rs_row + (long long)(col0 + j * 8) * 2) = u;
+            }
+          }
+        } else if (p.out_f32) {
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+          uint8_t* sb = stg + buf * STG_BYTES + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 u = make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
+                                 __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
+            *reinterpret_cast<uint4*>(sb + ((j ^ (lane & 7)) << 4)) = u;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (col0 < p.N && m0 + q * 32 < p.M) {
+              if (p.accumulate) tma_reduce_add_2d(&tmD, stg + buf * STG_BYTES, col0, m0 + q * 32);
+              else tma_store_2d(&tmD, stg + buf * STG_BYTES, col0, m0 + q * 32);
+            }
+            tma_store_commit();
+          }
+          buf ^= 1;
+        } else {
+          const int half = c & 1;
+          if (half == 0) {
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+          }
+          uint8_t* sb = stg + buf * STG_BYTES + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 u = make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
+                                 pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+            const int chunk = half * 4 + j;
+            *reinterpret_cast<uint4*>(sb + ((chunk ^ (lane & 7)) << 4)) = u;
+          }
+          if (half == 1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              const int cs = col0 - 32;
+              if (cs < p.N && m0 + q * 32 < p.M) {
+                if (p.accumulate) tma_reduce_add_2d(&tmD, stg + buf * STG_BYTES, cs, m0 + q * 32);
+                else tma_store_2d(&tmD, stg + buf * STG_BYTES, cs, m0 + q * 32);
+              }
+              tma_store_commit();
+            }
+            buf ^= 1;
+          }
+        }
+      }
+      tc_fence_before();
+      if (p.mode == 3) {
+        // every lane's peer stores are ordered before the counter bump that the owner acquires
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) red_release_sys_add(p.flag_peer[owner] + (m0 - owner * p.rows_per) / BM, 1);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+    // tiles done: help with the reduction of the rows this rank owns.  All four warps enter (their
+    // named barrier needs every one of them); after an abort the leader hands out no work.
+    if (p.mode == 3) reduce_loop(p, num_n, threadIdx.x - 64, EPI_WARPS * 32, 1, work_slot, abort_flag);
+  }
+
+  // ------------------------------ teardown ------------------------------
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+template <int BN>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const Params& p, int tiles,
+           cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tp_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return b200::fail(1501, "gemm_tp: cannot set %d bytes of shared memory: %s", C::SMEM, cudaGetErrorString(e));
+    }
+    configured[dev & 63] = true;
+  }
+  // every CTA must be resident at once (GEMM CTAs wait on the auxiliary CTAs): one CTA per SM at most
+  const int sms = b200::sm_count();
+  int n_gemm = sms - p.n_aux;
+  if (tiles < n_gemm) n_gemm = tiles;
+  if (n_gemm < 1) return b200::fail(1502, "gemm_tp: %d auxiliary CTAs leave no SM for the GEMM", p.n_aux);
+  gemm_tp_kernel<BN><<<p.n_aux + n_gemm, NUM_THREADS, C::SMEM, stream>>>(tmA, tmB, tmD, p);
+  b200::count_launch();
+  return b200::check_launch("gemm_tp");
+}
+
+int make_ab_maps(CUtensorMap* tmA, CUtensorMap* tmB, const void* a, const void* b, int M, int N, int K, long long lda,
+                 long long ldb, int a_mn, int b_mn, int BN) {
+  int r;
+  if (!a_mn) r = b200::make_tmap_2d(tmA, b200::DT_BF16, a, K, M, lda * 2, BK, BM, b200::SWZ_128);
+  else r = b200::make_tmap_2d(tmA, b200::DT_BF16, a, M, K, lda * 2, 64, BK, b200::SWZ_128);
+  if (r) return r;
+  if (!b_mn) r = b200::make_tmap_2d(tmB, b200::DT_BF16, b, K, N, ldb * 2, BK, BN, b200::SWZ_128);
+  else r = b200::make_tmap_2d(tmB, b200::DT_BF16, b, N, K, ldb * 2, 64, BK, b200::SWZ_128);
+  return r;
+}
+
+}  // namespace
+
+// All-gather -> GEMM.  `a`, `b`, `d` as in b200_gemm_bf16; the gathered operand lives in the local
+// copy `gbuf_local` of a symmetric buffer whose copies on all ranks are `peer_ptrs[0..W)`; rank c's
+// block is the byte range [c*chunk_bytes, (c+1)*chunk_bytes) and rank `rank` has already written its
+// own block (all ranks: a cross-rank barrier between that write and this launch).
+//   mode 1: the blocks are row blocks of A (rows_per rows each, M = W*rows_per, rows_per % 128 == 0)
+//   mode 2: the blocks are k blocks (rows_per k-elements each, K = W*rows_per, rows_per % 64 == 0)
+// chunk_flags: W ints of local device memory, zero at launch.  n_copy CTAs do the copies.
+B200_API int b200_gemm_tp_gather(const void* a, const void* b, void* d, int M, int N, int K, long long lda,
+                                 long long ldb, long long ldd, int a_mn_major, int b_mn_major, int out_f32,
+                                 int accumulate, float alpha, int mode, const unsigned long long* peer_ptrs, int W,
+                                 int rank, void* gbuf_local, long long chunk_bytes, int rows_per, int* chunk_flags,
+                                 int n_copy, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return b200::fail(1510, "gemm_tp_gather: empty problem %d x %d x %d", M, N, K);
+  if (W < 1 || W > MAXW || rank < 0 || rank >= W) return b200::fail(1511, "gemm_tp_gather: bad world %d / rank %d", W, rank);
+  if (mode == 1 && (rows_per % BM != 0 || (long long)rows_per * W != M))
+    return b200::fail(1512, "gemm_tp_gather: mode 1 needs M = W * rows_per with rows_per %% 128 == 0 (M=%d rows_per=%d)", M, rows_per);
+  if (mode == 2 && (rows_per % BK != 0 || (long long)rows_per * W != K))
+    return b200::fail(1513, "gemm_tp_gather: mode 2 needs K = W * rows_per with rows_per %% 64 == 0 (K=%d rows_per=%d)", K, rows_per);
+  if (mode != 1 && mode != 2) return b200::fail(1514, "gemm_tp_gather: mode %d", mode);
+  if (chunk_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(gbuf_local) & 15))
+    return b200::fail(1515, "gemm_tp_gather: blocks must be 16-byte aligned and sized");
+  const int BN = (N > 128) ? 256 : 128;
+  CUtensorMap tmA, tmB, tmD;
+  int r = make_ab_maps(&tmA, &tmB, a, b, M, N, K, lda, ldb, a_mn_major, b_mn_major, BN);
+  if (r) return r;
+  if (out_f32) r = b200::make_tmap_2d(&tmD, b200::DT_F32, d, N, M, ldd * 4, 32, 32, b200::SWZ_128);
+  else r = b200::make_tmap_2d(&tmD, b200::DT_BF16, d, N, M, ldd * 2, 64, 32, b200::SWZ_128);
+  if (r) return r;
+  Params p{};
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn_major = a_mn_major ? 1 : 0; p.b_mn_major = b_mn_major ? 1 : 0;
+  p.out_f32 = out_f32 ? 1 : 0; p.accumulate = accumulate ? 1 : 0;
+  p.group_m = 16; p.alpha = alpha; p.status = b200::status_ptr();
+  p.mode = mode; p.W = W; p.rank = rank; p.rows_per = rows_per;
+  p.n_aux = (W > 1) ? (n_copy > 0 ? n_copy : 8) : 0;
+  for (int c = 0; c < W; ++c) p.peer_src[c] = reinterpret_cast<const uint8_t*>(peer_ptrs[c]);
+  p.gdst = reinterpret_cast<uint8_t*>(gbuf_local);
+  p.chunk_bytes = chunk_bytes;
+  p.pieces_per_chunk = (int)((chunk_bytes + COPY_PIECE - 1) / COPY_PIECE);
+  p.chunk_flag = chunk_flags;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  if (BN == 256) return launch<256>(tmA, tmB, tmD, p, tiles, (cudaStream_t)stream);
+  return launch<128>(tmA, tmB, tmD, p, tiles, (cudaStream_t)stream);
+}
+
+// GEMM -> reduce-scatter.  P[M, N] = alpha * A * B^T is this rank's partial sum; rank o receives
+// out[rows_per, N] = sum over ranks of P[o*rows_per .. , :] (+ residual), bf16.
+//   stage_ptrs[o]: rank o's staging buffer, W * rows_per * N bf16 (symmetric memory)
+//   flag_ptrs[o] : rank o's counters, rows_per / 128 ints (symmetric memory), zero at launch on every
+//                  rank (zero them, then a cross-rank barrier, then launch)
+//   work_counter : one local int, zero at launch.  n_red CTAs only reduce.
+B200_API int b200_gemm_tp_rs(const void* a, const void* b, int M, int N, int K, long long lda, long long ldb,
+                             int a_mn_major, int b_mn_major, float alpha, const unsigned long long* stage_ptrs,
+                             const unsigned long long* flag_ptrs, int W, int rank, int* work_counter, void* out,
+                             long long ld_out, const void* residual, long long ld_res, int n_red, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return b200::fail(1520, "gemm_tp_rs: empty problem %d x %d x %d", M, N, K);
+  if (W < 1 || W > MAXW || rank < 0 || rank >= W) return b200::fail(1521, "gemm_tp_rs: bad world %d / rank %d", W, rank);
+  if (M % (W * BM) != 0) return b200::fail(1522, "gemm_tp_rs: M=%d must be a multiple of W * 128 = %d", M, W * BM);
+  if (N % 8 != 0 || ld_out % 8 != 0 || (residual != nullptr && ld_res % 8 != 0))
+    return b200::fail(1523, "gemm_tp_rs: N and the output / residual pitches must be multiples of 8");
+  const int BN = (N > 128) ? 256 : 128;
+  const int rows_per = M / W;
+  CUtensorMap tmA, tmB, tmD;
+  int r = make_ab_maps(&tmA, &tmB, a, b, M, N, K, lda, ldb, a_mn_major, b_mn_major, BN);
+  if (r) return r;
+  r = b200::make_tmap_2d(&tmD, b200::DT_BF16, out, N, rows_per, ld_out * 2, 64, 32, b200::SWZ_128);   // not used by mode 3
+  if (r) return r;
+  Params p{};
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn_major = a_mn_major ? 1 : 0; p.b_mn_major = b_mn_major ? 1 : 0;
+  p.group_m = 16; p.alpha = alpha; p.status = b200::status_ptr();
+  p.mode = 3; p.W = W; p.rank = rank; p.rows_per = rows_per;
+  p.n_aux = n_red > 0 ? n_red : 4;
+  for (int o = 0; o < W; ++o) {
+    p.stage_peer[o] = reinterpret_cast<uint8_t*>(stage_ptrs[o]);
+    p.flag_peer[o] = reinterpret_cast<int*>(flag_ptrs[o]);
+  }
+  p.work_counter = work_counter;
+  p.rs_out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.ld_out = ld_out;
+  p.rs_residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.ld_res = ld_res;
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  if (BN == 256) return launch<256>(tmA, tmB, tmD, p, tiles, (cudaStream_t)stream);
+  return launch<128>(tmA, tmB, tmD, p, tiles, (cudaStream_t)stream);
+}

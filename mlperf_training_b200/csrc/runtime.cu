@@ -55,6 +55,14 @@ int sm_count() {
 }
 
 static int ensure_encode() {
+  // Driver entry points need a context current on the calling thread.  A thread that has made no
+  // runtime call yet (an autograd worker whose first op is one of these GEMMs) has none: bind the
+  // primary context of its current device once per thread.
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
   if (g_encode) return 0;
   std::lock_guard<std::mutex> lk(g_mu);
   if (g_encode) return 0;

@@ -13,6 +13,7 @@ throughout so every GEMM sees one large M.
 from __future__ import annotations
 
 import math
+import zlib
 from dataclasses import dataclass, field, asdict
 
 import torch
@@ -122,6 +123,23 @@ def tiny_moe(**over) -> GPTConfig:
 PRESETS = {"llama3.1-8b": llama31_8b, "llama2-70b": llama2_70b, "gpt-oss-20b": gpt_oss_20b, "tiny-moe": tiny_moe}
 
 
+def shard_of(full: torch.Tensor, kind: str, W: int, r: int, cfg: "GPTConfig") -> torch.Tensor:
+    """This rank's slice of a full weight.  ``rows`` / ``cols``: contiguous split of dim 0 / 1;
+    ``rows_2``: two stacked matrices (gate | up), each split; ``qkv``: q | k | v head blocks, each split."""
+    if kind == "rows":
+        return full.chunk(W, 0)[r]
+    if kind == "cols":
+        return full.chunk(W, 1)[r]
+    if kind == "rows_2":
+        g, u = full.chunk(2, 0)
+        return torch.cat([g.chunk(W, 0)[r], u.chunk(W, 0)[r]], 0)
+    if kind == "qkv":
+        hd = cfg.head_dim
+        q, k, v = full.split([cfg.n_heads * hd, cfg.n_kv_heads * hd, cfg.n_kv_heads * hd], 0)
+        return torch.cat([q.chunk(W, 0)[r], k.chunk(W, 0)[r], v.chunk(W, 0)[r]], 0)
+    raise ValueError(kind)
+
+
 class RMSNorm(nn.Module):
     def __init__(self, dim: int, eps: float, dtype, device):
         super().__init__()
@@ -135,48 +153,97 @@ class RMSNorm(nn.Module):
 class DenseMLP(nn.Module):
     """gate/up projection as one GEMM ([2F, D], gate rows first), SwiGLU, down projection."""
 
-    def __init__(self, cfg: GPTConfig, dtype, device):
+    def __init__(self, cfg: GPTConfig, dtype, device, tp=None):
         super().__init__()
         d, f = cfg.hidden, cfg.ffn_hidden
+        self.tp = tp if (tp is not None and tp.world > 1) else None
+        if self.tp is not None:
+            if f % self.tp.world:
+                raise ValueError(f"ffn_hidden {f} is not divisible by the tensor-parallel size {self.tp.world}")
+            f //= self.tp.world
         self.precision = cfg.precision
         self.w_gate_up = nn.Parameter(torch.empty(2 * f, d, dtype=dtype, device=device))
         self.w_down = nn.Parameter(torch.empty(d, f, dtype=dtype, device=device))
+        if self.tp is not None:
+            self.w_gate_up.tensor_parallel = ("rows_2", self.tp.world, self.tp.rank)   # gate rows | up rows, each split
+            self.w_down.tensor_parallel = ("cols", self.tp.world, self.tp.rank)
 
     def forward(self, h, norm_w, eps):
+        if self.tp is not None:
+            from ..parallel import tensor as T
+            gu = T.column_parallel(F.rms_norm(h, norm_w, eps), self.w_gate_up, self.tp)
+            return T.row_parallel(F.swiglu(gu), self.w_down, self.tp, residual=h)
         gu = F.norm_linear(h, norm_w, self.w_gate_up, eps=eps, precision=self.precision)
         return F.swiglu_linear(gu, self.w_down, residual=h, precision=self.precision)
 
 
 class Block(nn.Module):
-    def __init__(self, cfg: GPTConfig, layer: int, dtype, device, mlp: nn.Module | None = None, ep_group=None):
+    def __init__(self, cfg: GPTConfig, layer: int, dtype, device, mlp: nn.Module | None = None, ep_group=None, tp=None):
         super().__init__()
         self.cfg = cfg
         self.layer = layer
         d, hd = cfg.hidden, cfg.head_dim
+        self.tp = tp if (tp is not None and tp.world > 1) else None
+        W = self.tp.world if self.tp is not None else 1
+        if cfg.n_heads % W or cfg.n_kv_heads % W:
+            raise ValueError(f"heads {cfg.n_heads}/{cfg.n_kv_heads} are not divisible by the tensor-parallel size {W}")
+        if self.tp is not None and cfg.n_experts:
+            raise ValueError("tensor parallelism is implemented for dense MLPs; shard experts with expert parallelism")
+        self.hq, self.hkv = cfg.n_heads // W, cfg.n_kv_heads // W
         self.attn_norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
-        self.w_qkv = nn.Parameter(torch.empty((cfg.n_heads + 2 * cfg.n_kv_heads) * hd, d, dtype=dtype, device=device))
-        self.w_proj = nn.Parameter(torch.empty(d, cfg.n_heads * hd, dtype=dtype, device=device))
-        self.sink = nn.Parameter(torch.zeros(cfg.n_heads, dtype=torch.float32, device=device)) if cfg.sink else None
+        self.w_qkv = nn.Parameter(torch.empty((self.hq + 2 * self.hkv) * hd, d, dtype=dtype, device=device))
+        self.w_proj = nn.Parameter(torch.empty(d, self.hq * hd, dtype=dtype, device=device))
+        self.sink = nn.Parameter(torch.zeros(self.hq, dtype=torch.float32, device=device)) if cfg.sink else None
         self.mlp_norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
+        if self.tp is not None:
+            self.w_qkv.tensor_parallel = ("qkv", W, self.tp.rank)
+            self.w_proj.tensor_parallel = ("cols", W, self.tp.rank)
+            if self.sink is not None:
+                self.sink.tensor_parallel = ("rows", W, self.tp.rank)
         if mlp is not None:
             self.mlp = mlp
         elif cfg.n_experts:
             from .moe import MoEMLP
             self.mlp = MoEMLP(cfg, dtype, device, ep_group=ep_group)
         else:
-            self.mlp = DenseMLP(cfg, dtype, device)
+            self.mlp = DenseMLP(cfg, dtype, device, tp=self.tp)
         self.lora_qkv = self.lora_proj = None
         if cfg.lora_rank > 0:
             from .lora import LoRAAdapter
             if "qkv" in cfg.lora_targets:
                 self.lora_qkv = LoRAAdapter(d, self.w_qkv.shape[0], cfg.lora_rank, cfg.lora_alpha, cfg.lora_dropout,
                                             dtype, device)
+                if self.tp is not None:
+                    self.lora_qkv.b.tensor_parallel = ("qkv", W, self.tp.rank)      # A stays replicated
             if "proj" in cfg.lora_targets:
-                self.lora_proj = LoRAAdapter(cfg.n_heads * hd, d, cfg.lora_rank, cfg.lora_alpha, cfg.lora_dropout,
+                self.lora_proj = LoRAAdapter(self.hq * hd, d, cfg.lora_rank, cfg.lora_alpha, cfg.lora_dropout,
                                              dtype, device)
+                if self.tp is not None:
+                    self.lora_proj.a.tensor_parallel = ("cols", W, self.tp.rank)    # B stays replicated
+
+    def _forward_tp(self, x, cos, sin, B, S):
+        """Sequence-parallel forward: ``x`` is this rank's block of token rows ``[T/W, hidden]``."""
+        from ..parallel import tensor as T
+        cfg, tp = self.cfg, self.tp
+        xn = F.rms_norm(x, self.attn_norm, cfg.norm_eps)
+        qkv = T.column_parallel(xn, self.w_qkv, tp)
+        if self.lora_qkv is not None:
+            lo = self.lora_qkv
+            u = T.GatherRows.apply(lo.drop(xn) @ lo.a.t(), tp)
+            qkv = qkv + (u @ lo.b.t()) * lo.scale
+        a = F.attention_packed(qkv, B=B, S=S, Hq=self.hq, Hkv=self.hkv, D=cfg.head_dim, cos=cos, sin=sin,
+                               sink=self.sink, causal=True, window=cfg.layer_window(self.layer))
+        h = T.row_parallel(a, self.w_proj, tp, residual=x)
+        if self.lora_proj is not None:
+            lo = self.lora_proj
+            u = T.ScatterRows.apply(lo.drop(a) @ lo.a.t(), tp)
+            h = h + (u @ lo.b.t()) * lo.scale
+        return self.mlp(h, self.mlp_norm, cfg.norm_eps)
 
     def forward(self, x, cos, sin, B, S):
         cfg = self.cfg
+        if self.tp is not None:
+            return self._forward_tp(x, cos, sin, B, S)
         if self.lora_qkv is None:
             qkv = F.norm_linear(x, self.attn_norm, self.w_qkv, eps=cfg.norm_eps, precision=cfg.precision)
         else:
@@ -194,12 +261,14 @@ class Block(nn.Module):
 class GPT(nn.Module):
     """``forward(tokens [B,S], labels [B,S]) -> mean cross-entropy`` (labels -100 are ignored)."""
 
-    def __init__(self, cfg: GPTConfig, device="cpu", seed: int = 0, ep_group=None):
+    def __init__(self, cfg: GPTConfig, device="cpu", seed: int = 0, ep_group=None, tp=None):
         super().__init__()
         self.cfg = cfg
+        self.tp = tp if (tp is not None and tp.world > 1) else None
         dtype = cfg.torch_dtype()
         self.embed = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden, dtype=dtype, device=device))
-        self.blocks = nn.ModuleList([Block(cfg, i, dtype, device, ep_group=ep_group) for i in range(cfg.n_layers)])
+        self.blocks = nn.ModuleList([Block(cfg, i, dtype, device, ep_group=ep_group, tp=self.tp)
+                                     for i in range(cfg.n_layers)])
         self.final_norm = nn.Parameter(torch.ones(cfg.hidden, dtype=dtype, device=device))
         self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden, dtype=dtype, device=device))
         self._rope = None
@@ -218,10 +287,23 @@ class GPT(nn.Module):
             if "lora" in name:
                 continue
             s = out_std if (name.endswith("w_proj") or name.endswith("w_down") or name.endswith("w2")) else std
-            if p.device.type == "cpu":
+            shard = getattr(p, "tensor_parallel", None)
+            if shard is not None:
+                # draw the full matrix (identical on every rank) and keep this rank's slice, so a
+                # tensor-parallel model starts from the same weights as the unsharded one
+                kind, W, r = shard
+                full_shape = (p.shape[0] * W, p.shape[1]) if kind in ("rows", "rows_2", "qkv") else (p.shape[0], p.shape[1] * W)
+                if p.device.type == "cpu":
+                    full = torch.empty(full_shape, dtype=p.dtype).normal_(0.0, s, generator=gen)
+                else:
+                    g = torch.Generator(device=p.device).manual_seed(seed + (zlib.crc32(name.encode()) & 0xFFFF))
+                    full = torch.empty(full_shape, dtype=p.dtype, device=p.device).normal_(0.0, s, generator=g)
+                p.copy_(shard_of(full, kind, W, r, self.cfg))
+                del full
+            elif p.device.type == "cpu":
                 p.normal_(0.0, s, generator=gen)
             else:
-                g = torch.Generator(device=p.device).manual_seed(seed + (hash(name) & 0xFFFF))
+                g = torch.Generator(device=p.device).manual_seed(seed + (zlib.crc32(name.encode()) & 0xFFFF))
                 p.normal_(0.0, s, generator=g)
 
     def rope(self, device):
@@ -234,8 +316,20 @@ class GPT(nn.Module):
         cos, sin = self.rope(tokens.device)
         if S > cos.shape[0]:
             raise ValueError(f"sequence {S} longer than the configured {cos.shape[0]}")
-        x = F.embedding(tokens.reshape(-1), self.embed)
+        ids, tgt = tokens.reshape(-1), labels.reshape(-1)
+        if self.tp is not None:
+            # sequence parallel: every rank embeds and scores its own block of token rows; the
+            # embedding, the final norm and the head are replicated and their gradients summed over
+            # the tensor-parallel group by the engine.  The returned loss is this rank's share.
+            W, r = self.tp.world, self.tp.rank
+            rows = ids.numel() // W
+            if ids.numel() % W:
+                raise ValueError("the number of tokens must be divisible by the tensor-parallel size")
+            if n_valid is None:
+                n_valid = ids.numel()
+            ids, tgt = ids[r * rows:(r + 1) * rows], tgt[r * rows:(r + 1) * rows]
+        x = F.embedding(ids, self.embed)
         for blk in self.blocks:
             x = blk(x, cos, sin, B, S)
-        return F.lm_head_loss(x, self.final_norm, self.lm_head, labels.reshape(-1), eps=self.cfg.norm_eps,
+        return F.lm_head_loss(x, self.final_norm, self.lm_head, tgt, eps=self.cfg.norm_eps,
                               n_valid=n_valid, precision=self.cfg.precision)

@@ -30,9 +30,11 @@ class LoRAAdapter(nn.Module):
         self.scale = alpha / rank
         self.dropout = dropout
 
+    def drop(self, x):
+        return TF.dropout(x, self.dropout) if (self.dropout > 0 and self.training) else x
+
     def forward(self, x):
-        if self.dropout > 0 and self.training:
-            x = TF.dropout(x, self.dropout)
+        x = self.drop(x)
         # rank-16 GEMMs are far below the tensor-core tile: plain matmuls, bf16
         return (x @ self.a.t()) @ self.b.t() * self.scale
 

@@ -64,6 +64,12 @@ def no_weight_decay(name: str, p: torch.Tensor) -> bool:
     return p.dim() < 2 or "norm" in name or "sink" in name or name.endswith("bias")
 
 
+def _fold_grad(p: torch.Tensor) -> None:
+    if p.grad is not None:
+        p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+        p.grad = None
+
+
 class Bucket:
     def __init__(self, key: str, params: list[tuple[str, nn.Parameter]], world: int, rank: int, opt: OptimConfig,
                  device, symmetric_group=None):
@@ -106,6 +112,10 @@ class Bucket:
             p.data = self.param_buf[o:o + n].view(p.shape)
             p.main_grad = self.grad_buf[o:o + n].view(p.shape)
             p.grad = None
+            if p.requires_grad:
+                # gradients produced by plain autograd ops (not by a wgrad GEMM epilogue) are folded into
+                # the flat buffer as soon as they are complete, and the temporary is dropped
+                p.register_post_accumulate_grad_hook(_fold_grad)
         if opt.master_weights:
             self.master = self.param_buf[self.lo:self.hi].float()
 
@@ -132,13 +142,18 @@ class ZeroEngine:
 
     def __init__(self, model: nn.Module, opt: OptimConfig, *, group: dist.ProcessGroup | None = None,
                  bucket_of: Callable[[str], str] = default_bucket_of, comm: str = "nccl",
-                 trainable_only: bool = True):
+                 trainable_only: bool = True, tp_group: dist.ProcessGroup | None = None):
         self.model = model
         self.opt = opt
         self.group = group
         self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.comm = comm
+        # tensor parallelism: parameters tagged ``tensor_parallel`` hold a different slice on every
+        # rank of ``tp_group``; all others are replicated over it and their gradients (each rank saw
+        # its own block of token rows) are summed over the group before the data-parallel reduction
+        self.tp_group = tp_group
+        self.tp_world = dist.get_world_size(tp_group) if tp_group is not None else 1
         named = [(n, p) for n, p in model.named_parameters() if (p.requires_grad or not trainable_only)]
         if not named:
             raise ValueError("ZeroEngine: the model has no trainable parameters")
@@ -147,6 +162,8 @@ class ZeroEngine:
         for n, p in named:
             # expert-parallel parameters exist on one rank only: their bucket is not sharded or reduced
             key = bucket_of(n) + ("_ep" if getattr(p, "expert_parallel", False) else "")
+            if self.tp_world > 1 and getattr(p, "tensor_parallel", None) is not None:
+                key += "_tp"
             groups.setdefault(key, []).append((n, p))
         self.buckets = []
         for k in sorted(groups):
@@ -155,10 +172,12 @@ class ZeroEngine:
             b = Bucket(k, groups[k], 1 if local else self.world, 0 if local else self.rank, opt, device,
                        symmetric_group=(group if group is not None else dist.group.WORLD) if fused else None)
             b.local_only = local
+            b.tp_sharded = k.endswith("_tp")
             self.buckets.append(b)
         self.device = device
         self.step_count = 0
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=device)
+        self.sumsq_tp = torch.zeros(1, dtype=torch.float32, device=device)
         self.last_grad_norm = None
 
     # ------------------------------------------------------------------ info
@@ -264,18 +283,32 @@ class ZeroEngine:
         lr = o.lr if lr is None else lr
         self.step_count += 1
         if any(b.symm_grad is not None for b in self.buckets):
+            if self.tp_world > 1:
+                raise NotImplementedError("comm='fused' of the optimizer step is not combined with tensor parallelism")
             return self._step_fused(lr, grad_scale)
         order = list(reversed(self.buckets))     # the order backward completes them
         for b in order:
+            if self.tp_world > 1 and not b.tp_sharded:
+                dist.all_reduce(b.grad_buf, group=self.tp_group)
             self._reduce_scatter(b)
         clip = o.clip_grad > 0
         if clip:
-            first = True
+            first = first_tp = True
+            self.sumsq.zero_()
             for b in order:
-                K.sumsq(b.g_shard(), self.sumsq, accumulate=not first)
-                first = False
+                if self.tp_world > 1 and b.tp_sharded:
+                    K.sumsq(b.g_shard(), self.sumsq_tp, accumulate=not first_tp)
+                    first_tp = False
+                else:
+                    K.sumsq(b.g_shard(), self.sumsq, accumulate=not first)
+                    first = False
             if self.world > 1:
                 dist.all_reduce(self.sumsq, group=self.group)
+            if self.tp_world > 1 and not first_tp:
+                if self.world > 1:
+                    dist.all_reduce(self.sumsq_tp, group=self.group)
+                dist.all_reduce(self.sumsq_tp, group=self.tp_group)
+                self.sumsq.add_(self.sumsq_tp)
             self.last_grad_norm = self.sumsq      # squared norm, before grad_scale (device scalar)
         for b in order:
             ps, gs = b.p_shard(), b.g_shard()

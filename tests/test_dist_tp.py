@@ -1,0 +1,35 @@
+"""Tensor + sequence parallel GPT on gloo (world 2): loss and gradient-norm parity with the
+unsharded model, with and without LoRA; mesh arithmetic."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+from mlperf_training_b200.parallel.mesh import MeshSpec, coords, group_ranks
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("extra", [(), ("nccl", "lora")])
+def test_tp_parity_gloo(extra):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29643",
+                        os.path.join(ROOT, "tests", "multi", "tp_worker.py"), "gloo", *extra],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT rank 0 ok=True" in r.stdout
+
+
+def test_mesh_groups_partition_the_world():
+    spec = MeshSpec(tp=2, pp=2, ep=2)
+    g = group_ranks(spec, 16)
+    for dim, lists in g.items():
+        flat = sorted(r for l in lists for r in l)
+        assert flat == list(range(16)), dim
+    assert g["tp"][0] == [0, 1] and g["pp"][0] == [0, 8]
+    assert all(len(l) == 2 for l in g["ep"]) and all(len(l) == 4 for l in g["dp"])
+    assert coords(13, spec, 16) == {"tp": 1, "cp": 0, "dp": 2, "pp": 1}
+    with pytest.raises(ValueError):
+        group_ranks(MeshSpec(tp=3), 16)

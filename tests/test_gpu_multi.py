@@ -31,3 +31,11 @@ def test_fused_zero_step_matches_nccl():
 def test_sharded_embedding_two_gpus(comm):
     res = _run("embedding_worker.py", args=("nccl", comm))
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("comm,lora", [("nccl", False), ("fused", False), ("fused", True)])
+def test_tensor_parallel_gpt_two_gpus(comm, lora):
+    res = _run("tp_worker.py", args=("nccl", comm) + (("lora",) if lora else ()))
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "RESULT rank 0 ok=True" in res.stdout
