@@ -198,26 +198,138 @@ B200_DEVICE void reduce_loop(const Params& p, int num_n, int tid, int nthreads, 
     named_bar_sync(bar_id, nthreads);      // everyone has read the slot before it is rewritten
     if (it >= items) break;
     const int row0 = (it / RS_SPLIT) * BM + (it % RS_SPLIT) * (BM / RS_SPLIT);
-    for (int idx = tid; idx < (BM / RS_SPLIT) * nvec; idx += nthreads) {
-      const int row = row0 + idx / nvec;
-      const int v = idx % nvec;
+    constexpr int U = 4;                   // vectors per thread in flight per source
+    const int total = (BM / RS_SPLIT) * nvec;
+    for (int base = tid; base < total; base += U * nthreads) {
+      float acc[U][8];
+      long long off[U];
+      bool live[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = base + u * nthreads;
+        live[u] = idx < total;
+        const int row = row0 + (live[u] ? idx / nvec : 0);
+        const int v = live[u] ? idx % nvec : 0;
+        off[u] = (long long)row * p.N + v * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
+        if (p.rs_residual != nullptr && live[u]) {
+          const uint4 q = *reinterpret_cast<const uint4*>(p.rs_residual + (long long)row * p.ld_res + v * 8);
+          const float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
+          acc[u][0] = f0.x; acc[u][1] = f0.y; acc[u][2] = f1.x; acc[u][3] = f1.y;
+          acc[u][4] = f2.x; acc[u][5] = f2.y; acc[u][6] = f3.x; acc[u][7] = f3.y;
+        }
+      }
+      for (int s2 = 0; s2 < p.W; ++s2) {
+        uint4 q[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          q[u] = live[u] ? ld_cg_u4(stage + ((long long)s2 * p.rows_per * p.N + off[u]) * 2) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const float2 f0 = unpack_bf16x2(q[u].x), f1 = unpack_bf16x2(q[u].y), f2 = unpack_bf16x2(q[u].z), f3 = unpack_bf16x2(q[u].w);
+          acc[u][0] += f0.x; acc[u][1] += f0.y; acc[u][2] += f1.x; acc[u][3] += f1.y;
+          acc[u][4] += f2.x; acc[u][5] += f2.y; acc[u][6] += f3.x; acc[u][7] += f3.y;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (!live[u]) continue;
+        const int idx = base + u * nthreads;
+        const int row = row0 + idx / nvec;
+        const int v = idx % nvec;
+        const uint4 o = make_uint4(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]),
+                                   pack_bf16x2(acc[u][4], acc[u][5]), pack_bf16x2(acc[u][6], acc[u][7]));
+        *reinterpret_cast<uint4*>(p.rs_out + (long long)row * p.ld_out + v * 8) = o;
+      }
+    }
+  }
+}
+
+// ------------------------------ dedicated reduce CTA (mode 3) ------------------------------
+// Streams the W staged copies of each row segment into shared memory with bulk async copies (one
+// thread keeps a 6-deep ring of 32 KB stages in flight), five consumer warps add them in fp32.
+struct RedMeta { int row, c0, cols; };
+
+B200_DEVICE void reduce_cta(const Params& p, int num_n, uint8_t* smem, uint64_t* bars) {
+  constexpr int RST = COPY_STAGES;
+  constexpr int CONSUMER_WARPS = NUM_THREADS / 32 - 1;
+  uint64_t* full = bars;
+  uint64_t* empty = bars + RST;
+  RedMeta* meta = reinterpret_cast<RedMeta*>(bars + 2 * RST);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + RST);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < RST; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], CONSUMER_WARPS); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int unit_cols = (COPY_PIECE / 2 / p.W) & ~7;
+  if (unit_cols > p.N) unit_cols = p.N;
+  const uint8_t* stage = p.stage_peer[p.rank];
+  if (warp == 0) {
+    if (lane != 0) return;
+    const int tpc = p.rows_per / BM;
+    const int items = tpc * RS_SPLIT;
+    const int want = p.W * num_n * EPI_WARPS;
+    const int* flags = p.flag_peer[p.rank];
+    int st = 0; uint32_t ph = 0;
+    bool ok = true;
+    while (ok) {
+      const int it = atomicAdd(p.work_counter, 1);
+      if (it >= items) break;
+      if (!flag_wait_geq(flags + it / RS_SPLIT, want, B200_WAIT_LIMIT_NS, p.status, 51)) break;
+      fence_proxy_async_all();
+      const int row0 = (it / RS_SPLIT) * BM + (it % RS_SPLIT) * (BM / RS_SPLIT);
+      for (int r = 0; r < BM / RS_SPLIT && ok; ++r) {
+        for (int c0 = 0; c0 < p.N; c0 += unit_cols) {
+          if (!mbar_wait(&empty[st], ph ^ 1, abort_flag, p.status, 52)) { ok = false; break; }
+          const int cols = min(unit_cols, p.N - c0);
+          meta[st].row = row0 + r; meta[st].c0 = c0; meta[st].cols = cols;
+          mbar_expect_tx(&full[st], (uint32_t)(p.W * cols * 2));
+          for (int s2 = 0; s2 < p.W; ++s2)
+            bulk_g2s(smem + st * COPY_PIECE + s2 * cols * 2,
+                     stage + (((long long)s2 * p.rows_per + row0 + r) * p.N + c0) * 2, (uint32_t)(cols * 2), &full[st]);
+          if (++st == RST) { st = 0; ph ^= 1; }
+        }
+      }
+    }
+    // sentinel: tells the consumers to leave
+    if (mbar_wait(&empty[st], ph ^ 1, abort_flag, p.status, 53)) {
+      meta[st].row = -1;
+      mbar_arrive(&full[st]);
+    }
+    return;
+  }
+  int st = 0; uint32_t ph = 0;
+  const int ctid = threadIdx.x - 32, cn = CONSUMER_WARPS * 32;
+  while (true) {
+    if (!mbar_wait(&full[st], ph, abort_flag, p.status, 54)) break;
+    const RedMeta m = meta[st];
+    if (m.row < 0) break;
+    const uint8_t* sb = smem + st * COPY_PIECE;
+    for (int v = ctid; v < m.cols / 8; v += cn) {
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
       if (p.rs_residual != nullptr) {
-        const uint4 u = *reinterpret_cast<const uint4*>(p.rs_residual + (long long)row * p.ld_res + v * 8);
-        const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+        const uint4 q = *reinterpret_cast<const uint4*>(p.rs_residual + (long long)m.row * p.ld_res + m.c0 + v * 8);
+        const float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
         acc[0] = f0.x; acc[1] = f0.y; acc[2] = f1.x; acc[3] = f1.y; acc[4] = f2.x; acc[5] = f2.y; acc[6] = f3.x; acc[7] = f3.y;
       }
-      for (int s = 0; s < p.W; ++s) {
-        const uint4 u = ld_cg_u4(stage + (((long long)s * p.rows_per + row) * p.N + v * 8) * 2);
-        const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+      for (int s2 = 0; s2 < p.W; ++s2) {
+        const uint4 q = *reinterpret_cast<const uint4*>(sb + s2 * m.cols * 2 + v * 16);
+        const float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
         acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
       }
       const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
                                  pack_bf16x2(acc[6], acc[7]));
-      *reinterpret_cast<uint4*>(p.rs_out + (long long)row * p.ld_out + v * 8) = o;
+      *reinterpret_cast<uint4*>(p.rs_out + (long long)m.row * p.ld_out + m.c0 + v * 8) = o;
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[st]);
+    if (++st == RST) { st = 0; ph ^= 1; }
   }
 }
 
@@ -249,7 +361,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   // ---------------- auxiliary CTAs: no tensor memory, no GEMM barriers ----------------
   if ((int)blockIdx.x < p.n_aux) {
-    if (p.mode == 3) reduce_loop(p, num_n, threadIdx.x, NUM_THREADS, 2, work_slot, nullptr);
+    if (p.mode == 3) reduce_cta(p, num_n, smem, bars);
     else copy_cta(p, smem, bars);
     return;
   }
@@ -446,15 +558,16 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
       }
+      // all TMEM reads of this accumulator are complete: hand it back before the (slow) publication
       tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
       if (p.mode == 3) {
         // every lane's peer stores are ordered before the counter bump that the owner acquires
         __threadfence_system();
         __syncwarp();
         if (lane == 0) red_release_sys_add(p.flag_peer[owner] + (m0 - owner * p.rows_per) / BM, 1);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
     }
     if (lane == 0) tma_store_wait_all<0>();
     // tiles done: help with the reduction of the rows this rank owns.  All four warps enter (their

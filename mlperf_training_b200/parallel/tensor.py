@@ -32,7 +32,7 @@ from ..ops.functional import _wgrad
 
 
 class TPContext:
-    def __init__(self, group=None, comm: str = "nccl", device=None, n_copy: int = 8, n_red: int = 4):
+    def __init__(self, group=None, comm: str = "nccl", device=None, n_copy: int = 8, n_red: int = 6):
         self.group = group
         on = dist.is_available() and dist.is_initialized()
         self.world = dist.get_world_size(group) if on else 1

@@ -41,9 +41,12 @@ def main(argv=None) -> int:
     exp = load_experiment(args.config, overrides=args.overrides)
     module = {"pretrain": "pre_trainer", "posttrain": "post_trainer", "hstu": "hstu_trainer", "flux": "flux_trainer"}[args.mode]
     resolved = (exp.get("modules") or {}).get(module, {}).get("resolved") or exp
-    if args.mode in ("pretrain", "posttrain"):
+    if args.mode == "pretrain":
         from .loop import run
         out = run(resolved, device=args.device)
+    elif args.mode == "posttrain":
+        from .sft import run as run_sft
+        out = run_sft(resolved, device=args.device)
     elif args.mode == "hstu":
         from .hstu import run as run_hstu
         out = run_hstu(resolved, device=args.device)

@@ -64,6 +64,12 @@ class RunConfig:
     log_interval: int = 1
     die_at_step: int = 0                                # fault injection: exit(42) after this step's save
     mllog_file: str = ""
+    tensor_parallel: int = 1                            # tensor + sequence parallel size (Megatron layout)
+    sequence_parallel: int = 1
+    pipeline_parallel: int = 1
+    context_parallel: int = 1
+    tp_comm_overlap: str = "fused"                      # "fused": in-kernel all-gather / reduce-scatter; "nccl"
+    comm: str = "nccl"                                  # optimizer-step collectives: "nccl" | "fused"
     profile_step_start: int = 0
     profile_step_end: int = 0
     profile_dir: str = ""
@@ -118,16 +124,37 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         log.log_submission(rc.benchmark, platform=f"1xB200x{world}")
 
     cfg = build_model_config(rc.model)
-    if rc.global_batch % world:
+    if int(rc.pipeline_parallel) > 1 or int(rc.context_parallel) > 1:
+        raise NotImplementedError("this run loop drives data x tensor parallel meshes; pipeline stages are "
+                                  "scheduled by parallel.pipeline")
+    tp_size = min(int(rc.tensor_parallel), world)
+    tp_ctx, dp_group, dp_rank, dp_world = None, None, rank, world
+    if tp_size > 1:
+        from ..parallel.mesh import Mesh, MeshSpec
+        from ..parallel.tensor import TPContext
+        mesh = Mesh(MeshSpec(tp=tp_size))
+        fused_tp = str(rc.tp_comm_overlap).lower() == "fused" and str(device).startswith("cuda")
+        tp_ctx = TPContext(mesh.group("tp"), comm="fused" if fused_tp else "nccl", device=device if fused_tp else None)
+        dp_group, dp_rank, dp_world = mesh.group("dp"), mesh.index("dp"), mesh.size("dp")
+        if cfg.precision != "bf16":
+            cfg.precision = "bf16"       # the tensor-parallel linears run the bf16 tcgen05 GEMMs
+    if rc.global_batch % dp_world:
         raise ValueError("global_batch must be divisible by the data-parallel size")
-    local_batch = rc.global_batch // world
+    local_batch = rc.global_batch // dp_world
     opt = OptimConfig(lr=rc.lr, beta1=rc.adam_beta1, beta2=rc.adam_beta2, eps=rc.adam_eps,
                       weight_decay=rc.weight_decay, clip_grad=rc.clip_grad)
     tc = TrainConfig(micro_batch=rc.micro_batch, local_batch=local_batch, warmup_steps=rc.lr_warmup_iters,
-                     decay_steps=rc.lr_decay_iters, min_lr_ratio=rc.min_lr_ratio, seed=rc.seed)
-    trainer = PretrainTrainer(cfg, opt, tc, device)
+                     decay_steps=rc.lr_decay_iters, min_lr_ratio=rc.min_lr_ratio, seed=rc.seed, comm=rc.comm)
+    trainer = PretrainTrainer(cfg, opt, tc, device, group=dp_group, tp=tp_ctx, freeze_base=cfg.lora_rank > 0)
     data = build_data(rc.data, cfg, rc.seed)
     eval_data = build_data(rc.data, cfg, rc.seed + 7919)
+
+    def host_batch(ds, i):
+        """One step's batch for this data-parallel rank: tokens ``[b, S+1]``, or (tokens, labels)."""
+        b = ds.batch(i, dp_rank, dp_world, local_batch)
+        if not isinstance(b, (tuple, list)) and getattr(ds, "loss_last", 0) > 0:
+            b = (b[:, :-1].contiguous(), ds.labels(b))
+        return b
 
     if rc.pretrained_checkpoint and not resuming:
         from ..checkpoint.megatron import load_torch_dist
@@ -170,10 +197,10 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             prof = StepProfiler(rc.profile_dir or ".", rank)
             prof.start()
         timer.step_start()
-        batch = data.batch(step, rank, world, local_batch)
-        if isinstance(batch, tuple):
-            raise NotImplementedError("packed SFT batches go through trainer.sft")
-        loss = trainer.train_step(batch.pin_memory() if torch.cuda.is_available() else batch)
+        batch = host_batch(data, step)
+        if torch.cuda.is_available() and str(device).startswith("cuda"):
+            batch = tuple(t.pin_memory() for t in batch) if isinstance(batch, tuple) else batch.pin_memory()
+        loss = trainer.train_step(batch)
         timer.step_stop()
         losses.append(loss)
         if prof is not None and step + 1 == rc.profile_step_end:
@@ -188,11 +215,14 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             if evals_done > rc.skip_evals:
                 log.end(ml.BLOCK_STOP, metadata={"samples_count": samples})
                 log.start(ml.EVAL_START, metadata={"samples_count": samples})
-                tot = 0.0
+                sums = torch.zeros(2, dtype=torch.float64, device=trainer.device)
                 for i in range(max(rc.eval_iters, 1)):
-                    eb = eval_data.batch(i, rank, world, local_batch).to(trainer.device)
-                    tot += float(trainer.eval_loss(eb))
-                last_eval = tot / max(rc.eval_iters, 1)
+                    eb = host_batch(eval_data, i)
+                    if isinstance(eb, tuple):
+                        sums += trainer.eval_sums(eb[0].to(trainer.device), eb[1].to(trainer.device))
+                    else:
+                        sums += trainer.eval_sums(eb.to(trainer.device))
+                last_eval = float(sums[0] / sums[1].clamp(min=1))
                 log.event(ml.EVAL_ACCURACY, last_eval, metadata={"samples_count": samples})
                 log.end(ml.EVAL_STOP, metadata={"samples_count": samples})
                 if rc.target_eval_loss > 0 and last_eval <= rc.target_eval_loss:

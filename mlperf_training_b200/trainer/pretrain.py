@@ -36,61 +36,116 @@ class TrainConfig:
 
 
 class PretrainTrainer:
-    def __init__(self, model_cfg: GPTConfig, opt: OptimConfig, train: TrainConfig, device, group=None, ep_group=None):
+    """``group`` is the data-parallel group, ``tp`` an optional ``parallel.tensor.TPContext`` (the
+    ranks of one tensor-parallel group must be fed the same batch)."""
+
+    def __init__(self, model_cfg: GPTConfig, opt: OptimConfig, train: TrainConfig, device, group=None, ep_group=None,
+                 tp=None, freeze_base: bool = False):
         self.cfg = model_cfg
         self.train_cfg = train
         self.device = torch.device(device)
-        self.model = GPT(model_cfg, device=self.device, seed=train.seed, ep_group=ep_group)
-        self.engine = ZeroEngine(self.model, opt, group=group, comm=train.comm)
+        self.tp = tp if (tp is not None and tp.world > 1) else None
+        self.model = GPT(model_cfg, device=self.device, seed=train.seed, ep_group=ep_group, tp=self.tp)
+        if freeze_base:
+            from ..models.lora import freeze_base as _freeze
+            _freeze(self.model)
+        self.engine = ZeroEngine(self.model, opt, group=group, comm=train.comm,
+                                 tp_group=self.tp.group if self.tp is not None else None)
+        self.dp_group = group
         self.step_idx = 0
         if train.local_batch % train.micro_batch != 0:
             raise ValueError("local_batch must be a multiple of micro_batch")
         self.n_micro = train.local_batch // train.micro_batch
         self._staging = None
+        self._masked = False
 
     def lr(self) -> float:
         o, t = self.engine.opt, self.train_cfg
         return cosine_lr(self.step_idx, base_lr=o.lr, min_lr=o.lr * t.min_lr_ratio, warmup=t.warmup_steps,
                          decay_steps=t.decay_steps)
 
-    def train_step_device(self, tokens: torch.Tensor) -> torch.Tensor:
-        """``tokens``: int64 ``[local_batch, seq_len + 1]`` on the device.  Returns the mean loss
-        over the step's micro-batches as a 0-d device tensor."""
+    def _split(self, tokens: torch.Tensor, labels: torch.Tensor | None):
+        """``[b, S+1]`` token rows -> (inputs, labels); explicit ``labels [b, S]`` go with ``tokens [b, S]``."""
+        if labels is None:
+            return tokens[:, :-1], tokens[:, 1:]
+        return tokens, labels
+
+    def _loss(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        # explicit labels mask part of the positions (-100): the mean runs over the labelled ones
+        masked = self._masked
+        n_valid = max(int((y != -100).sum()), 1) if masked else None
+        loss = self.model(x, y, n_valid=n_valid)
+        return loss
+
+    def train_step_device(self, tokens: torch.Tensor, labels: torch.Tensor | None = None) -> torch.Tensor:
+        """``tokens``: int64 ``[local_batch, seq_len + 1]`` on the device (or ``[local_batch, seq_len]``
+        with explicit ``labels``, -100 = no loss).  Returns the mean loss over the step's micro-batches
+        as a 0-d device tensor (summed over the tensor-parallel group when there is one)."""
         mb = self.train_cfg.micro_batch
+        self._masked = labels is not None
+        x_all, y_all = self._split(tokens, labels)
         total = None
         for i in range(self.n_micro):
-            chunk = tokens[i * mb:(i + 1) * mb]
-            loss = self.model(chunk[:, :-1], chunk[:, 1:])
+            loss = self._loss(x_all[i * mb:(i + 1) * mb], y_all[i * mb:(i + 1) * mb])
             loss.backward()
             d = loss.detach()
             total = d if total is None else total + d
         self.engine.step(self.lr(), grad_scale=1.0 / self.n_micro)
         self.step_idx += 1
-        return total / self.n_micro
+        total = total / self.n_micro
+        if self.tp is not None:
+            total = self.tp.all_reduce(total.float().clone())
+        return total
 
-    def train_step(self, batch: torch.Tensor) -> float:
+    def _to_device(self, t: torch.Tensor, slot: int) -> torch.Tensor:
+        if self._staging is None:
+            self._staging = {}
+        buf = self._staging.get(slot)
+        if buf is None or buf.shape != t.shape:
+            buf = self._staging[slot] = torch.empty(t.shape, dtype=torch.int64, device=self.device)
+        buf.copy_(t, non_blocking=True)
+        return buf
+
+    def train_step(self, batch) -> float:
         """One optimizer step from host token ids ``[local_batch, seq_len + 1]`` (int64, ideally
-        pinned).  Host -> device copy, step, and a device -> host read of the loss."""
-        if self._staging is None or self._staging.shape != batch.shape:
-            self._staging = torch.empty(batch.shape, dtype=torch.int64, device=self.device)
-        self._staging.copy_(batch, non_blocking=True)
-        loss = self.train_step_device(self._staging)
+        pinned), or a ``(tokens, labels)`` pair of ``[local_batch, seq_len]`` tensors for packed
+        fine-tuning data.  Host -> device copy, step, and a device -> host read of the loss."""
+        if isinstance(batch, (tuple, list)):
+            loss = self.train_step_device(self._to_device(batch[0], 0), self._to_device(batch[1], 1))
+        else:
+            loss = self.train_step_device(self._to_device(batch, 0))
         return float(loss.item())
 
     @torch.no_grad()
-    def eval_loss(self, tokens: torch.Tensor) -> torch.Tensor:
-        """Forward-only mean loss on device tokens ``[b, seq_len + 1]``."""
+    def eval_sums(self, tokens: torch.Tensor, labels: torch.Tensor | None = None) -> torch.Tensor:
+        """Forward-only ``[sum of token losses, number of labelled tokens]`` on device tokens, summed
+        over every rank: evaluation averages over tokens, not over micro-batches (the reference
+        accumulates the same pair, llama2_sft/primus/src/llama2_custom.py:752-915)."""
         mb = self.train_cfg.micro_batch
-        tot, n = None, 0
-        for i in range(0, tokens.shape[0], mb):
-            chunk = tokens[i:i + mb]
-            l = self.model(chunk[:, :-1], chunk[:, 1:])
-            tot = l if tot is None else tot + l
-            n += 1
-        tot = tot / n
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-            dist.all_reduce(tot, op=dist.ReduceOp.AVG)
-        return tot
+        x_all, y_all = self._split(tokens, labels)
+        acc = torch.zeros(2, dtype=torch.float64, device=self.device)
+        for i in range(0, x_all.shape[0], mb):
+            x, y = x_all[i:i + mb], y_all[i:i + mb]
+            n = (y != -100).sum()
+            l = self.model(x, y, n_valid=1)            # n_valid = 1: the plain sum of token losses
+            if self.tp is not None:
+                l = self.tp.all_reduce(l.float().clone())
+            acc[0] += l.double()
+            acc[1] += n.double()
+        if dist.is_available() and dist.is_initialized():
+            g = self.dp_group
+            if g is not None:
+                if dist.get_world_size(g) > 1:
+                    dist.all_reduce(acc, group=g)
+            elif self.tp is None and dist.get_world_size() > 1:
+                dist.all_reduce(acc)
+        return acc
+
+    @torch.no_grad()
+    def eval_loss(self, tokens: torch.Tensor, labels: torch.Tensor | None = None) -> torch.Tensor:
+        """Forward-only token-mean loss on device tokens ``[b, seq_len + 1]``."""
+        s = self.eval_sums(tokens, labels)
+        return (s[0] / s[1].clamp(min=1)).float()
 
 
 def synthetic_tokens(steps: int, local_batch: int, seq_len: int, vocab: int, seed: int, rank: int = 0,
