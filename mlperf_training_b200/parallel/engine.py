@@ -142,7 +142,8 @@ class ZeroEngine:
 
     def __init__(self, model: nn.Module, opt: OptimConfig, *, group: dist.ProcessGroup | None = None,
                  bucket_of: Callable[[str], str] = default_bucket_of, comm: str = "nccl",
-                 trainable_only: bool = True, tp_group: dist.ProcessGroup | None = None):
+                 trainable_only: bool = True, tp_group: dist.ProcessGroup | None = None,
+                 pp_group: dist.ProcessGroup | None = None):
         self.model = model
         self.opt = opt
         self.group = group
@@ -153,6 +154,8 @@ class ZeroEngine:
         # rank of ``tp_group``; all others are replicated over it and their gradients (each rank saw
         # its own block of token rows) are summed over the group before the data-parallel reduction
         self.tp_group = tp_group
+        # pipeline parallelism: every stage owns different parameters; only the clipping norm is shared
+        self.pp_group = pp_group if (pp_group is not None and dist.get_world_size(pp_group) > 1) else None
         self.tp_world = dist.get_world_size(tp_group) if tp_group is not None else 1
         named = [(n, p) for n, p in model.named_parameters() if (p.requires_grad or not trainable_only)]
         if not named:
@@ -309,6 +312,8 @@ class ZeroEngine:
                     dist.all_reduce(self.sumsq_tp, group=self.group)
                 dist.all_reduce(self.sumsq_tp, group=self.tp_group)
                 self.sumsq.add_(self.sumsq_tp)
+            if self.pp_group is not None:
+                dist.all_reduce(self.sumsq, group=self.pp_group)
             self.last_grad_norm = self.sumsq      # squared norm, before grad_scale (device scalar)
         for b in order:
             ps, gs = b.p_shard(), b.g_shard()

@@ -33,3 +33,20 @@ def test_mesh_groups_partition_the_world():
     assert coords(13, spec, 16) == {"tp": 1, "cp": 0, "dp": 2, "pp": 1}
     with pytest.raises(ValueError):
         group_ranks(MeshSpec(tp=3), 16)
+
+
+@pytest.mark.parametrize("stages", [2, 3])
+def test_pipeline_1f1b_parity_gloo(stages):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={stages}",
+                        "--master-addr", "127.0.0.1", "--master-port", "29653",
+                        os.path.join(ROOT, "tests", "multi", "pp_worker.py"), "gloo"],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT rank 0 ok=True" in r.stdout
+
+
+def test_stage_layer_split():
+    from mlperf_training_b200.parallel.pipeline import stage_layers
+    assert [list(stage_layers(10, 4, s)) for s in range(4)] == [[0, 1, 2], [3, 4, 5], [6, 7], [8, 9]]
+    assert sum(len(stage_layers(80, 8, s)) for s in range(8)) == 80
