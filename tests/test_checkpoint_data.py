@@ -1,0 +1,160 @@
+"""Checkpoint manager (atomic directories, pruning, cadence, resume position, split contract),
+Megatron name mapping and torch_dist round trip, indexed / packed datasets, warm-up restore, a
+fault-injected GPT run that resumes, and a FLUX (MMDiT) run on CPU."""
+import io
+
+import numpy as np
+import pytest
+import torch
+
+from mlperf_training_b200.checkpoint import megatron as MG
+from mlperf_training_b200.checkpoint.manager import (CheckpointManager, resume_position, select_checkpoint_reason,
+                                                      validate_split_contract)
+from mlperf_training_b200.data.indexed import (GPTSampleDataset, MMapIndexedDataset, PackedSFTDataset, SyntheticTokens,
+                                               write_indexed_dataset, write_packed_sft)
+from mlperf_training_b200.mllog import check_compliance
+from mlperf_training_b200.models.gpt import GPT, GPTConfig
+
+TINY = dict(n_layers=2, hidden=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn_hidden=128, vocab_size=256, seq_len=32,
+            dtype="fp32")
+
+
+def test_manager_atomic_save_prune_and_load(tmp_path):
+    m = CheckpointManager(str(tmp_path / "ck"), keep_last=2)
+    assert not m.present() and m.load() is None
+    (tmp_path / "ck").mkdir()
+    (tmp_path / "ck" / "7.tmp").mkdir()                       # a crashed save
+    for step in (10, 20, 30):
+        m.save(step, dense={"w": torch.full((3,), float(step))}, optim_shard={"m": torch.ones(2) * step},
+               meta={"samples": step * 4, "window": 0, "batch_idx_in_window": step})
+    assert m.steps() == [20, 30] and not (tmp_path / "ck" / "7.tmp").exists()
+    assert (tmp_path / "ck" / "latest_checkpointed_iteration.txt").read_text() == "30"
+    ck = m.load()
+    assert ck["meta"]["step"] == 30 and float(ck["dense"]["w"][0]) == 30.0 and float(ck["optim"]["m"][0]) == 30.0
+    torch.manual_seed(123)
+    m.save(40, dense=None, optim_shard=None, meta={})
+    a = torch.rand(3)
+    CheckpointManager.restore_rng(m.load(40)["rng"])
+    assert torch.equal(torch.rand(3), a)
+
+
+def test_cadence_resume_position_and_contract():
+    kw = dict(batch_in_window=0, elapsed_since_last_s=0.0)
+    assert select_checkpoint_reason(global_step=100, every_steps=50, **kw) == "global_step"
+    assert select_checkpoint_reason(global_step=101, every_steps=50, **kw) is None
+    assert select_checkpoint_reason(global_step=3, batch_in_window=8, elapsed_since_last_s=0, every_window_batches=4) == "in_window"
+    assert select_checkpoint_reason(global_step=3, batch_in_window=1, elapsed_since_last_s=99, every_seconds=60) == "wall_clock"
+    assert select_checkpoint_reason(global_step=3, window_end=True, **kw) == "window"
+    assert resume_position(None, 8)["cold_start"]
+    assert resume_position({"window": 2, "batch_idx_in_window": 5}, 8) == {"window": 2, "skip_batches": 5, "skip_samples": 40,
+                                                                           "cold_start": False}
+    assert resume_position({"window": 2, "batch_idx_in_window": -1}, 8)["window"] == 3
+    validate_split_contract({"salt": 1, "world": 8}, {"salt": 1, "world": 8})
+    with pytest.raises(RuntimeError):
+        validate_split_contract({"salt": 1, "world": 8}, {"salt": 2, "world": 8})
+    validate_split_contract({"salt": 1}, {"salt": 2}, allow_mismatch=True)
+
+
+def test_megatron_names_qkv_layout_and_torch_dist_roundtrip(tmp_path):
+    cfg = GPTConfig(**TINY)
+    a = GPT(cfg, seed=1)
+    state = MG.to_megatron_state(a)
+    assert "decoder.layers.0.self_attention.linear_qkv.weight" in state
+    assert "embedding.word_embeddings.weight" in state and "output_layer.weight" in state
+    for name in state:
+        assert MG.megatron_name(MG.local_name(name)) == name
+    w = a.blocks[0].w_qkv.detach()
+    meg = MG.qkv_to_megatron(w, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
+    assert meg.shape == w.shape and not torch.equal(meg, w)
+    assert torch.equal(MG.qkv_from_megatron(meg, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim), w)
+    # first query group of Megatron's layout: q heads of group 0, then its k head, then its v head
+    hd, g = cfg.head_dim, cfg.n_heads // cfg.n_kv_heads
+    assert torch.equal(meg[: g * hd], w[: g * hd])
+    assert torch.equal(meg[g * hd:(g + 1) * hd], w[cfg.n_heads * hd: cfg.n_heads * hd + hd])
+    root = MG.save_torch_dist(a, str(tmp_path / "base"), iteration=0)
+    assert (root / ".metadata").exists() and (tmp_path / "base" / "latest_checkpointed_iteration.txt").exists()
+    b = GPT(cfg, seed=2)
+    MG.load_torch_dist(b, str(tmp_path / "base"))
+    for (n, p), (_, q) in zip(a.named_parameters(), b.named_parameters()):
+        assert torch.equal(p, q), n
+
+
+def test_indexed_dataset_and_gpt_samples(tmp_path):
+    rng = np.random.default_rng(0)
+    docs = [rng.integers(0, 1000, size=int(n), dtype=np.int32) for n in rng.integers(5, 60, size=40)]
+    prefix = str(tmp_path / "c4")
+    write_indexed_dataset(prefix, docs)
+    ds = MMapIndexedDataset(prefix)
+    assert len(ds) == 40 and ds.num_tokens == sum(len(d) for d in docs)
+    assert np.array_equal(ds[7], docs[7])
+    flat = np.concatenate(docs)
+    assert np.array_equal(ds.tokens(33, 50), flat[33:83])
+    g = GPTSampleDataset([prefix], None, seq_len=16, seed=3)
+    b0 = g.batch(0, 0, 2, 3)
+    assert b0.shape == (3, 17) and b0.dtype == torch.int64
+    assert torch.equal(b0, GPTSampleDataset([prefix], None, seq_len=16, seed=3).batch(0, 0, 2, 3))     # deterministic
+    assert not torch.equal(b0, g.batch(0, 1, 2, 3))                                                    # rank slices differ
+
+
+def test_packed_sft_and_synthetic_labels(tmp_path):
+    samples = [{"input_ids": np.arange(10), "loss_mask": np.array([0] * 6 + [1] * 4), "seq_start_id": [0, 6]},
+               {"input_ids": np.arange(40), "loss_mask": np.ones(40, dtype=np.int64), "seq_start_id": [0]}]
+    write_packed_sft(str(tmp_path / "t.npy"), samples, str(tmp_path / "m.jsonl"))
+    ds = PackedSFTDataset(str(tmp_path / "t.npy"), seq_len=16, metadata_path=str(tmp_path / "m.jsonl"))
+    tok, lab, starts = ds[0]
+    assert tok.shape == (16,) and lab.shape == (16,)
+    assert lab[:5].eq(-100).all() and lab[5:9].tolist() == [6, 7, 8, 9] and lab[9:].eq(-100).all()   # short sample is padded
+    tok, lab, _ = ds[1]
+    assert lab.tolist() == list(range(1, 17))                                                         # long sample is cut
+    t, l = ds.batch(0, 0, 1, 2)
+    assert t.shape == (2, 16) and l.shape == (2, 16)
+    syn = SyntheticTokens(100, 16, seed=1, loss_last=4)
+    b = syn.batch(3, 0, 1, 2)
+    lab = syn.labels(b)
+    assert lab[:, :12].eq(-100).all() and torch.equal(lab[:, 12:], b[:, 13:])
+
+
+def test_warmup_restores_everything():
+    from mlperf_training_b200.parallel.engine import OptimConfig
+    from mlperf_training_b200.trainer.pretrain import PretrainTrainer, TrainConfig
+    from mlperf_training_b200.trainer.warmup import run_synthetic_warmup
+    tr = PretrainTrainer(GPTConfig(**TINY), OptimConfig(lr=1e-2), TrainConfig(micro_batch=1, local_batch=2), "cpu")
+    before = [b.param_buf.clone() for b in tr.engine.buckets]
+    run_synthetic_warmup(tr, train_steps=2, eval_steps=1)
+    assert tr.step_idx == 0 and tr.engine.step_count == 0
+    for b, p0 in zip(tr.engine.buckets, before):
+        assert torch.equal(b.param_buf, p0)
+        assert float(b.m.abs().sum()) == 0 and float(b.v.abs().sum()) == 0 and float(b.grad_buf.abs().sum()) == 0
+
+
+def test_gpt_run_die_at_step_then_resume_matches_uninterrupted(tmp_path):
+    from mlperf_training_b200.trainer.loop import run
+    base = dict(model=TINY, global_batch=2, micro_batch=1, train_iters=6, lr=3e-3, lr_warmup_iters=2, warmup_train_steps=0)
+    ref = run(dict(base), device="cpu", stream=io.StringIO())
+    exp = dict(base, checkpoint_dir=str(tmp_path / "ck"), die_at_step=3, mllog_file=str(tmp_path / "ml.log"))
+    with pytest.raises(SystemExit) as ex:
+        run(dict(exp), device="cpu", stream=io.StringIO())
+    assert ex.value.code == 42
+    exp["die_at_step"] = 0
+    out = run(dict(exp), device="cpu", stream=io.StringIO())
+    assert out["steps"] == 3
+    assert abs(out["losses"][-1] - ref["losses"][-1]) < 1e-5
+    lines = (tmp_path / "ml.log").read_text().splitlines()
+    assert sum("run_start" in l for l in lines) == 1 and sum("run_stop" in l for l in lines) == 1
+
+
+def test_flux_run_learns_on_cpu():
+    from mlperf_training_b200.trainer.flux import run
+    out = run(dict(model=dict(preset="tiny-mmdit"), global_batch=4, train_iters=12, lr=2e-3, eval_every_samples=24,
+                   prompt_dropout=0.0), device="cpu", stream=io.StringIO())
+    assert all(l == l for l in out["losses"]) and out["eval_loss"] is not None
+    assert check_compliance(out["records"]) == []
+    # flow matching on a fixed batch: the velocity target has a learnable part (-x0), the loss must fall
+    from mlperf_training_b200.models.mmdit import tiny_mmdit
+    from mlperf_training_b200.parallel.engine import OptimConfig
+    from mlperf_training_b200.trainer.flux import FluxTrainer, SyntheticFluxData
+    cfg = tiny_mmdit()
+    tr = FluxTrainer(cfg, OptimConfig(lr=3e-3, weight_decay=0.0), "cpu", 4, prompt_dropout=0.0)
+    b = SyntheticFluxData(cfg).batch(0, 0, 4)
+    ls = [tr.train_step(b) for _ in range(40)]
+    assert sum(ls[-5:]) < 0.9 * sum(ls[:5])
