@@ -1,5 +1,6 @@
 // Host-side runtime: status block, tensor-map encoding, launch counter, error text.
 #include "runtime.h"
+#include "common.cuh"
 
 #include <atomic>
 #include <cstdarg>
@@ -195,3 +196,23 @@ B200_API int b200_status_reset() {
   return 0;
 }
 B200_API int b200_sm_count() { return b200::sm_count(); }
+
+// ----------------------------------------------------------------------------------
+// Wait probe: one thread waits (bounded) for `*flag >= want`.  Used by the failure-detection tests
+// to see a wait run out and report through the status block while the context stays usable, and
+// by hosts that want to block a stream on a device flag with a deadline.
+// ----------------------------------------------------------------------------------
+namespace {
+__global__ void flag_wait_probe_kernel(const int* flag, int want, unsigned long long limit_ns, int* status, int* result) {
+  const bool ok = flag_wait_geq(flag, want, limit_ns, status, 99);
+  if (result != nullptr) *result = ok ? 1 : 0;
+}
+}  // namespace
+
+B200_API int b200_flag_wait_probe(const int* flag, int want, long long limit_ns, int* result, void* stream) {
+  if (limit_ns <= 0 || limit_ns > (long long)B200_WAIT_LIMIT_NS)
+    return b200::fail(120, "flag_wait_probe: limit %lld ns outside (0, %llu]", limit_ns, (unsigned long long)B200_WAIT_LIMIT_NS);
+  flag_wait_probe_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(flag, want, (unsigned long long)limit_ns, b200::status_ptr(), result);
+  b200::count_launch();
+  return b200::check_launch("flag_wait_probe");
+}

@@ -1,0 +1,65 @@
+"""Precision schedule (format mapping, switch step, env override, de-oscillation status) and the
+data-preparation tools (packing, metadata, checksums, time-window index)."""
+import numpy as np
+import pytest
+import torch.nn as nn
+
+from mlperf_training_b200.data import prep
+from mlperf_training_b200.data.indexed import PackedSFTDataset
+from mlperf_training_b200.ops.recipe import PrecisionSchedule, resolve_format
+
+
+def test_precision_schedule_switch_and_mapping(monkeypatch):
+    assert resolve_format("A6W4") == "mxfp8" and resolve_format("bf16") == "bf16"
+    with pytest.raises(ValueError):
+        resolve_format("int3")
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.precision = "bf16"
+            self.sub = nn.Linear(2, 2)
+            self.sub.precision = "bf16"
+    m = M()
+    s = PrecisionSchedule.from_spec({"initial": "bf16", "switch_step": 5, "final": "fp8",
+                                     "deosc": {"enabled": True, "start_step": 768}})
+    assert s.apply(m, 0) and m.precision == "bf16"
+    assert not s.apply(m, 4)
+    assert s.apply(m, 5) and m.precision == "mxfp8" and m.sub.precision == "mxfp8"
+    assert s.log == [(0, "bf16"), (5, "mxfp8")]
+    assert "inactive" in s.deosc.status("mxfp8")
+    monkeypatch.setenv("FLUX_FPROP_SWITCH_STEP", "9")
+    assert PrecisionSchedule.from_spec({"initial": "a6w4", "switch_step": 5, "final": "bf16"}).phases[1][0] == 9
+
+
+def test_pack_convert_metadata_hash_verify(tmp_path):
+    rng = np.random.default_rng(0)
+    samples = [{"input_ids": rng.integers(0, 100, size=n).tolist(), "labels": [-100] * (n // 2) + [1] * (n - n // 2)}
+               for n in (30, 9, 17, 12, 5, 33, 20)]
+    rows = prep.pack_samples(samples, seq_len=32)
+    assert sum(len(r["input_ids"]) for r in rows) == sum(len(s["input_ids"]) for s in samples)
+    assert all(len(r["input_ids"]) <= 33 for r in rows) and len(rows) <= 5
+    assert all(r["seq_start_id"][0] == 0 and r["seq_start_id"] == sorted(r["seq_start_id"]) for r in rows)
+    src = tmp_path / "s.jsonl"
+    import json
+    src.write_text("\n".join(json.dumps(s) for s in samples))
+    n = prep.convert_sft(str(src), str(tmp_path / "train.npy"), 32)
+    assert n == len(rows) and prep.write_metadata(str(tmp_path / "train.npy"), str(tmp_path / "meta.jsonl")) == n
+    ds = PackedSFTDataset(str(tmp_path / "train.npy"), 32, str(tmp_path / "meta.jsonl"))
+    assert len(ds) == n and len(ds.metadata) == n
+    manifest = tmp_path / "sums.md5"
+    manifest.write_text("\n".join(f"{d}  {name}" for d, name in prep.hash_directory(str(tmp_path)) if name != "sums.md5"))
+    assert prep.verify_directory(str(tmp_path), str(manifest)) == []
+    (tmp_path / "meta.jsonl").write_text("tampered")
+    assert prep.verify_directory(str(tmp_path), str(manifest)) == ["meta.jsonl"]
+
+
+def test_window_index_is_ordered_and_deterministic():
+    ts = np.array([50, 10, 70, 11, 130, 12, 200, 131])
+    idx = prep.build_window_index(ts, window_seconds=60, holdout=0.25, salt=7)
+    assert ts[idx["order"]].tolist() == sorted(ts.tolist())
+    assert idx["window_start"].tolist() == [0, 4, 5, 7] and idx["window_id"].tolist() == [0, 1, 2, 3]
+    again = prep.build_window_index(ts, 60, 0.25, 7)
+    assert np.array_equal(idx["holdout"], again["holdout"])
+    big = prep.build_window_index(np.arange(20000), 100, holdout=0.1, salt=1)
+    assert 0.07 < big["holdout"].mean() < 0.13
