@@ -46,6 +46,7 @@ class GPTConfig:
     top_k: int = 0
     moe_ffn_hidden: int = 0
     router_dtype: str = "fp32"
+    ep_comm: str = "nccl"          # expert-parallel token movement: "nccl" all-to-all | "fused" peer-memory kernels
     # LoRA (rank 0 = off)
     lora_rank: int = 0
     lora_alpha: float = 32.0
@@ -204,7 +205,7 @@ class Block(nn.Module):
             self.mlp = mlp
         elif cfg.n_experts:
             from .moe import MoEMLP
-            self.mlp = MoEMLP(cfg, dtype, device, ep_group=ep_group)
+            self.mlp = MoEMLP(cfg, dtype, device, ep_group=ep_group, ep_comm=cfg.ep_comm)
         else:
             self.mlp = DenseMLP(cfg, dtype, device, tp=self.tp)
         self.lora_qkv = self.lora_proj = None

@@ -13,11 +13,11 @@ import torch.nn as nn
 
 from ..ops import functional as F
 from ..ops import moe_ops as M
-from ..parallel.expert import ExpertParallelDispatcher
+from ..parallel.expert import ExpertParallelDispatcher, FusedExpertDispatcher
 
 
 class MoEMLP(nn.Module):
-    def __init__(self, cfg, dtype, device, ep_group=None):
+    def __init__(self, cfg, dtype, device, ep_group=None, ep_comm: str = "nccl"):
         super().__init__()
         self.cfg = cfg
         d, f, E = cfg.hidden, cfg.moe_ffn_hidden, cfg.n_experts
@@ -34,6 +34,8 @@ class MoEMLP(nn.Module):
         # gradients run over the ranks that hold the same experts
         self.w1.expert_parallel = self.w2.expert_parallel = self.ep > 1
         self.dispatcher = ExpertParallelDispatcher(ep_group, E) if self.ep > 1 else None
+        self.ep_comm = ep_comm
+        self._fused = None      # built on first use: its slab size depends on the number of tokens per step
 
     def forward(self, h, norm_w, eps):
         cfg = self.cfg
@@ -42,6 +44,19 @@ class MoEMLP(nn.Module):
         idx, w, counts = M.RouterFn.apply(logits, cfg.top_k)
         if self.dispatcher is None:
             y = M.moe_experts(hn, idx, w, counts, self.w1, self.w2)
+        elif self.ep_comm == "fused" and hn.is_cuda and hn.dtype == torch.bfloat16:
+            y = self._fused_dispatcher(hn.shape[0] * cfg.top_k, hn.device)(hn, idx, w, counts, self.w1, self.w2)
         else:
             y = self.dispatcher(hn, idx, w, counts, self.w1, self.w2)
         return h + y
+
+    _shared: dict = {}
+
+    def _fused_dispatcher(self, pairs: int, device):
+        """One set of slabs per (group, shape) serves every layer: each use copies its rows out of the
+        slab before the next layer touches it."""
+        key = (id(self.ep_group), self.cfg.n_experts, self.cfg.hidden, pairs, str(device))
+        d = MoEMLP._shared.get(key)
+        if d is None:
+            d = MoEMLP._shared[key] = FusedExpertDispatcher(self.ep_group, self.cfg.n_experts, self.cfg.hidden, pairs, device)
+        return d

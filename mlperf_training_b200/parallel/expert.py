@@ -74,3 +74,123 @@ class ExpertParallelDispatcher:
         # 4. return trip and weighted combine at the source
         ret = _AllToAllRows.apply(back, out_splits, in_splits, self.group)
         return M.UnpermuteFn.apply(ret, dest, w, T, k)
+
+
+# --------------------------------------------------------------------------------------
+# peer-memory path
+# --------------------------------------------------------------------------------------
+class _Route:
+    """Per-layer routing tables, all on the device (no size is read back to the host)."""
+    __slots__ = ("dst_rank", "dst_row", "seg2", "cnt2", "tile_expert", "n")
+
+
+class _PushRows(Function):
+    """rows [n, D] (this rank's pairs in sorted order) -> the owners' slabs; returns this rank's slab
+    (rows of every source, grouped by local expert, padding zero).  Backward pulls the gradient rows
+    of this rank's pairs out of the owners' gradient slabs."""
+
+    @staticmethod
+    def forward(ctx, rows, disp, route: _Route):
+        ctx.disp, ctx.route = disp, route
+        return disp._push(rows, route, disp.slab_x)
+
+    @staticmethod
+    def backward(ctx, g_slab):
+        return ctx.disp._pull(g_slab, ctx.route, ctx.disp.slab_dx), None, None
+
+
+class _PullRows(Function):
+    """slab [cap, D] (expert outputs on the owner) -> rows [n, D] of this rank's pairs, loaded from
+    the owners' slabs.  Backward pushes the gradient rows into the owners' gradient slabs."""
+
+    @staticmethod
+    def forward(ctx, slab, disp, route: _Route):
+        ctx.disp, ctx.route = disp, route
+        return disp._pull(slab, route, disp.slab_y)
+
+    @staticmethod
+    def backward(ctx, g_rows):
+        return ctx.disp._push(g_rows.contiguous(), ctx.route, ctx.disp.slab_dy), None, None
+
+
+class FusedExpertDispatcher:
+    """Token dispatch / combine by this package's kernels over NVLink peer memory.
+
+    Every rank owns four symmetric slabs ``[capacity, D]`` (inputs, outputs and their gradients).
+    Dispatch stores each (token, slot) row directly at its final, expert-grouped position in the
+    owner's slab; combine loads each pair's output row from the owner's slab.  Positions come from
+    the all-gathered per-expert counts by prefix sums on the device, so the layer runs without a
+    host synchronisation; ``capacity`` bounds the rows a rank can receive (``capacity_factor`` x the
+    balanced share) and pairs beyond it are dropped and counted in ``dropped``.
+    """
+
+    def __init__(self, group, n_experts: int, hidden: int, max_pairs: int, device, capacity_factor: float = 2.0):
+        from .symm import SymmetricBuffer
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.E, self.D = n_experts, hidden
+        self.local = n_experts // self.world
+        self.cap = (int(capacity_factor * max_pairs) + self.local * 128 + 127) // 128 * 128
+        mk = lambda: SymmetricBuffer(self.cap * hidden, torch.bfloat16, group, device)
+        self.slab_x, self.slab_y, self.slab_dy, self.slab_dx = mk(), mk(), mk(), mk()
+        self.dropped = torch.zeros(1, dtype=torch.int32, device=device)
+        self.device = device
+
+    # ------------------------------------------------------------------ routing tables
+    def _route(self, counts: torch.Tensor, seg: torch.Tensor, n: int) -> _Route:
+        W, L, E, dev = self.world, self.local, self.E, counts.device
+        allc = torch.empty((W, E), dtype=torch.int64, device=dev)
+        dist.all_gather_into_tensor(allc.view(-1), counts.to(torch.int64).contiguous(), group=self.group)
+        tot = allc.sum(0)                                            # rows every expert receives
+        padded = (tot + 127) // 128 * 128
+        seg_all = (padded.view(W, L).cumsum(1) - padded.view(W, L)).reshape(-1)      # segment start on the owner
+        before_me = allc[: self.rank].sum(0)                         # rows of lower ranks inside the segment
+        base = seg_all + before_me
+        e_of = torch.repeat_interleave(torch.arange(E, device=dev), counts.long(), output_size=n)
+        r = _Route()
+        r.n = n
+        r.dst_rank = (e_of // L).to(torch.int32)
+        row = base[e_of] + (torch.arange(n, device=dev) - seg.long()[e_of])
+        r.dst_row = torch.where(row < self.cap, row, torch.full_like(row, -1)).to(torch.int32)
+        mine = slice(self.rank * L, (self.rank + 1) * L)
+        seg2 = torch.zeros(L + 1, dtype=torch.int64, device=dev)
+        seg2[1:] = padded[mine].cumsum(0)
+        r.seg2 = seg2.clamp(max=self.cap).to(torch.int32)
+        r.cnt2 = tot[mine].to(torch.int32)
+        tile_start = torch.arange(self.cap // 128, device=dev) * 128
+        te = torch.searchsorted(seg2[1:].contiguous(), tile_start, right=True)
+        r.tile_expert = torch.where(tile_start < seg2[-1], te, torch.full_like(te, -1)).to(torch.int32)
+        return r
+
+    # ------------------------------------------------------------------ data movement
+    def _push(self, rows: torch.Tensor, route: _Route, slab) -> torch.Tensor:
+        from ..ops import _lib
+        slab.barrier()                         # every rank is done reading this slab from its previous use
+        _lib.call("b200_zero_pad_rows", _lib.ptr(slab.local), _lib.ptr(route.seg2), _lib.ptr(route.cnt2), self.local, self.D,
+                  self.cap, _lib.stream_ptr())
+        _lib.call("b200_scatter_rows_to_peers", _lib.ptr(rows), None, _lib.ptr(route.dst_rank), _lib.ptr(route.dst_row),
+                  route.n, self.D, slab.ptr_array(), self.world, self.cap, _lib.ptr(self.dropped), _lib.stream_ptr())
+        slab.barrier()                         # every rank's rows have landed
+        return slab.local.view(self.cap, self.D).clone()
+
+    def _pull(self, slab_rows: torch.Tensor, route: _Route, slab) -> torch.Tensor:
+        from ..ops import _lib
+        slab.barrier()                         # previous readers of this slab are done
+        slab.local.view(self.cap, self.D).copy_(slab_rows)
+        slab.barrier()                         # every owner's slab is complete
+        out = torch.empty((route.n, self.D), dtype=torch.bfloat16, device=slab_rows.device)
+        _lib.call("b200_gather_rows_from_peers", slab.ptr_array(), _lib.ptr(route.dst_rank), _lib.ptr(route.dst_row),
+                  route.n, self.D, _lib.ptr(out), self.world, self.cap, _lib.stream_ptr())
+        return out
+
+    def __call__(self, x, idx, w, counts, w1, w2):
+        T, k = idx.shape
+        n = T * k
+        seg, _, dest, _ = M.plan(idx, counts, self.E, pad=1)       # sorted by global expert, unpadded
+        send = M.PermuteFn.apply(x, dest, k, n)
+        route = self._route(counts, seg, n)
+        xp = _PushRows.apply(send, self, route)
+        yp = M.GroupedMLPFn.apply(xp, w1, w2, route.seg2, route.tile_expert)
+        ret = _PullRows.apply(yp, self, route)
+        return M.UnpermuteFn.apply(ret, dest, w, T, k)

@@ -70,6 +70,8 @@ class RunConfig:
     context_parallel: int = 1
     tp_comm_overlap: str = "fused"                      # "fused": in-kernel all-gather / reduce-scatter; "nccl"
     comm: str = "nccl"                                  # optimizer-step collectives: "nccl" | "fused"
+    precision_schedule: dict | str | None = None        # ops.recipe.PrecisionSchedule spec (phase switch at a step)
+    heartbeat_timeout_s: float = 0.0                    # > 0: watch the other ranks' heartbeats between steps
     profile_step_start: int = 0
     profile_step_end: int = 0
     profile_dir: str = ""
@@ -184,6 +186,14 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         log.start(ml.EPOCH_START, metadata={"epoch_num": 0})
         log.start(ml.BLOCK_START, metadata={"samples_count": 0})
 
+    sched = None
+    if rc.precision_schedule:
+        from ..ops.recipe import PrecisionSchedule
+        sched = PrecisionSchedule.from_spec(rc.precision_schedule)
+    hb = None
+    if rc.heartbeat_timeout_s > 0 and world > 1:
+        from ..parallel.health import Heartbeat
+        hb = Heartbeat(dist.distributed_c10d._get_default_store(), rank, world, interval_s=rc.heartbeat_timeout_s / 4).start()
     timer = ml.ThroughputTimer(rc.global_batch)
     t_run0 = time.perf_counter()
     last_ckpt_t = time.perf_counter()
@@ -196,6 +206,10 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             from ..utils.profiler import StepProfiler
             prof = StepProfiler(rc.profile_dir or ".", rank)
             prof.start()
+        if sched is not None and sched.apply(trainer.model, step) and rank == 0:
+            print(f"[precision] step {step}: linears run in {sched.at(step)}; {sched.deosc.status(sched.at(step))}", flush=True)
+        if hb is not None:
+            hb.check(rc.heartbeat_timeout_s)          # raises RankFailure before any kernel of the step is launched
         timer.step_start()
         batch = host_batch(data, step)
         if torch.cuda.is_available() and str(device).startswith("cuda"):
@@ -247,6 +261,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             log.close()
             sys.exit(42)
 
+    if hb is not None:
+        hb.stop()
     duration = time.perf_counter() - t_run0
     success = reached or rc.target_eval_loss <= 0
     if not reached:

@@ -39,3 +39,10 @@ def test_tensor_parallel_gpt_two_gpus(comm, lora):
     res = _run("tp_worker.py", args=("nccl", comm) + (("lora",) if lora else ()))
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "RESULT rank 0 ok=True" in res.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_expert_dispatch_matches_all_to_all():
+    res = _run("moe_fused_worker.py")
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "RESULT rank 0 ok=True" in res.stdout
