@@ -38,7 +38,12 @@ struct Cfg {
   static constexpr int EPI_BYTES = EPI_WARPS * 2 * STG_BYTES;
   static constexpr int SMEM = STAGES * STAGE + EPI_BYTES + 1024 + 256;
   static constexpr int SF_COL = 2 * BN;        // first TMEM column of the scale area
-  static constexpr int TMEM_COLS = (2 * BN + 4 + 4 * B_ATOMS) <= 256 ? 256 : 512;
+  // The scale columns are multi-buffered: tcgen05.cp of k block i+1 must not wait for the MMAs of k
+  // block i to finish reading theirs (cp and mma execute in order on the tensor pipe).
+  static constexpr int SF_SET_COLS = 4 + 4 * B_ATOMS;
+  static constexpr int SF_SETS = 4;
+  static constexpr int TMEM_COLS = (2 * BN + SF_SETS * SF_SET_COLS) <= 256 ? 256 : 512;
+  static_assert(2 * BN + SF_SETS * SF_SET_COLS <= 512, "accumulators and scale sets exceed tensor memory");
 };
 
 struct Params {
@@ -138,10 +143,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       const uint32_t idesc0 = umma_idesc_mx(0, 0, 0, 0, BM, BN);
-      const uint32_t t_sfa = tmem_base + C::SF_COL;
-      const uint32_t t_sfb = tmem_base + C::SF_COL + 4;
       int stage = 0; uint32_t phase = 0;
       int it = 0;
+      uint32_t sf_set = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
         const int acc = it & 1;
@@ -152,6 +156,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 121)) { ok = false; break; }
           tc_fence_after();
+          const uint32_t t_sfa = tmem_base + C::SF_COL + sf_set * C::SF_SET_COLS;
+          const uint32_t t_sfb = t_sfa + 4;
+          sf_set = (sf_set + 1) % C::SF_SETS;
           // scale atoms: shared memory -> TMEM (32 rows x 16 bytes each, replicated to the 4 lane quarters)
           tc_cp_32x128b_warpx4(t_sfa, umma_desc_noswz(smem_u32(sSFA + stage * C::SFA_STAGE), 0, 128));
 #pragma unroll

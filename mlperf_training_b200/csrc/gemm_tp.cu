@@ -36,7 +36,7 @@ constexpr int STG_BYTES = 4096;
 constexpr int MAXW = 16;
 constexpr int COPY_PIECE = 32768;     // bytes per bulk copy
 constexpr int COPY_STAGES = 6;
-constexpr int RS_SPLIT = 16;          // reduce work items per 128-row tile (8 rows each)
+constexpr int RS_SPLIT = 64;          // reduce work items per 128-row tile (2 rows each: a short tail)
 
 template <int BN>
 struct Cfg {
@@ -48,6 +48,8 @@ struct Cfg {
   static constexpr int TMEM_COLS = 2 * BN;
   static_assert(COPY_STAGES * COPY_PIECE + 1024 + 256 <= SMEM, "copy ring must fit the GEMM allocation");
 };
+
+struct OwnerMaps { CUtensorMap m[MAXW]; };   // mode 3: rank o's staging buffer viewed as [W * rows_per, N] bf16
 
 struct Params {
   int M, N, K;
@@ -65,7 +67,9 @@ struct Params {
   uint8_t* gdst;                   // local gather buffer
   long long chunk_bytes;           // bytes of one rank block (contiguous)
   int pieces_per_chunk;
-  int* chunk_flag;                 // [W] local counters, zero at launch
+  int* chunk_flag;                 // [W] counters of this rank, zero at launch (peer-writable memory in push mode)
+  int copy_mode;                   // 0: pull the peers' blocks; 1: push the own block to every peer
+  int* chunk_flag_peer[MAXW];      // push mode: rank d's chunk_flag array
   // reduce-scatter
   uint8_t* stage_peer[MAXW];       // rank o's staging buffer [W][rows_per][N] bf16
   int* flag_peer[MAXW];            // rank o's counters [rows_per / BM], zero at launch
@@ -172,6 +176,44 @@ B200_DEVICE void copy_cta(const Params& p, uint8_t* smem, uint64_t* bars) {
     // loads that never completed may still land: give them time before shared memory is released
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+}
+
+// Push variant: every thread of the CTA copies 16-byte vectors of this rank's block from local memory
+// straight into every peer's buffer (plain posted stores: no round trip per piece), and one thread
+// bumps the peers' counters after each PUSH_PIECE bytes, behind a system-scope fence.
+constexpr int PUSH_PIECE = 262144;
+
+B200_DEVICE void copy_cta_push(const Params& p) {
+  // Work items are (destination, piece), destination-major: the rank that consumes this block first
+  // (rank - 1: it visits its own block, then rank + 1's, ...) receives all of it first.
+  const int ppc = (int)((p.chunk_bytes + PUSH_PIECE - 1) / PUSH_PIECE);
+  const long long base = (long long)p.rank * p.chunk_bytes;
+  const uint8_t* src = p.gdst + base;
+  const int items = (p.W - 1) * ppc;
+  for (int it = blockIdx.x; it < items; it += p.n_aux) {
+    const int d = (p.rank - 1 - it / ppc + 2 * p.W) % p.W;
+    const long long off = (long long)(it % ppc) * PUSH_PIECE;
+    const long long left = p.chunk_bytes - off;
+    const int nvec = (int)((left < PUSH_PIECE ? left : PUSH_PIECE) / 16);
+    uint8_t* dst = const_cast<uint8_t*>(p.peer_src[d]) + base + off;
+    constexpr int U = 16;
+    for (int v0 = threadIdx.x; v0 < nvec; v0 += U * NUM_THREADS) {
+      uint4 q[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * NUM_THREADS;
+        if (v < nvec) q[u] = ld_cg_u4(src + off + (long long)v * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * NUM_THREADS;
+        if (v < nvec) *reinterpret_cast<uint4*>(dst + (long long)v * 16) = q[u];
+      }
+    }
+    __threadfence_system();
+    named_bar_sync(3, NUM_THREADS);
+    if (threadIdx.x == 0) red_release_sys_add(p.chunk_flag_peer[d] + p.rank, 1);
   }
 }
 
@@ -336,7 +378,8 @@ B200_DEVICE void reduce_cta(const Params& p, int num_n, uint8_t* smem, uint64_t*
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmD, const __grid_constant__ Params p) {
+               const __grid_constant__ CUtensorMap tmD, const __grid_constant__ Params p,
+               const __grid_constant__ OwnerMaps om) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -362,6 +405,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // ---------------- auxiliary CTAs: no tensor memory, no GEMM barriers ----------------
   if ((int)blockIdx.x < p.n_aux) {
     if (p.mode == 3) reduce_cta(p, num_n, smem, bars);
+    else if (p.copy_mode == 1) copy_cta_push(p);
     else copy_cta(p, smem, bars);
     return;
   }
@@ -484,13 +528,10 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, p.status, 30)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
-      // mode 3: destination row inside the owner's staging slot of this rank
+      // mode 3: the tile goes into the owner's staging slot of this rank through the owner's tensor map
       const int owner = (p.mode == 3) ? m0 / p.rows_per : 0;
-      uint8_t* rs_row = nullptr;
-      if (p.mode == 3) {
-        const int row_in = m0 - owner * p.rows_per + q * 32 + lane;
-        rs_row = p.stage_peer[owner] + ((long long)p.rank * p.rows_per + row_in) * p.N * 2;
-      }
+      const CUtensorMap* tmOut = (p.mode == 3) ? &om.m[owner] : &tmD;
+      const int out_row0 = (p.mode == 3) ? p.rank * p.rows_per + (m0 - owner * p.rows_per) + q * 32 : m0 + q * 32;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -500,16 +541,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-        if (p.mode == 3) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (col0 + j * 8 < p.N) {
-              const uint4 u = make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
-                                         pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
-              *reinterpret_cast<uint4*>(rs_row + (long long)(col0 + j * 8) * 2) = u;
-            }
-          }
-        } else if (p.out_f32) {
+        if (p.out_f32) {
           if (lane == 0) tma_store_wait_read<1>();
           __syncwarp();
           uint8_t* sb = stg + buf * STG_BYTES + lane * 128;
@@ -549,8 +581,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (lane == 0) {
               const int cs = col0 - 32;
               if (cs < p.N && m0 + q * 32 < p.M) {
-                if (p.accumulate) tma_reduce_add_2d(&tmD, stg + buf * STG_BYTES, cs, m0 + q * 32);
-                else tma_store_2d(&tmD, stg + buf * STG_BYTES, cs, m0 + q * 32);
+                if (p.accumulate) tma_reduce_add_2d(tmOut, stg + buf * STG_BYTES, cs, out_row0);
+                else tma_store_2d(tmOut, stg + buf * STG_BYTES, cs, out_row0);
               }
               tma_store_commit();
             }
@@ -562,11 +594,13 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
-      if (p.mode == 3) {
-        // every lane's peer stores are ordered before the counter bump that the owner acquires
+      if (p.mode == 3 && lane == 0) {
+        // the tile's bulk stores must be complete (not only read out of shared memory) before the
+        // owner's counter is bumped
+        tma_store_wait_all<0>();
+        fence_proxy_async_all();
         __threadfence_system();
-        __syncwarp();
-        if (lane == 0) red_release_sys_add(p.flag_peer[owner] + (m0 - owner * p.rows_per) / BM, 1);
+        red_release_sys_add(p.flag_peer[owner] + (m0 - owner * p.rows_per) / BM, 1);
       }
     }
     if (lane == 0) tma_store_wait_all<0>();
@@ -589,8 +623,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 template <int BN>
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const Params& p, int tiles,
-           cudaStream_t stream) {
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const Params& p, const OwnerMaps& om,
+           int tiles, cudaStream_t stream) {
   using C = Cfg<BN>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -608,7 +642,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   int n_gemm = sms - p.n_aux;
   if (tiles < n_gemm) n_gemm = tiles;
   if (n_gemm < 1) return b200::fail(1502, "gemm_tp: %d auxiliary CTAs leave no SM for the GEMM", p.n_aux);
-  gemm_tp_kernel<BN><<<p.n_aux + n_gemm, NUM_THREADS, C::SMEM, stream>>>(tmA, tmB, tmD, p);
+  gemm_tp_kernel<BN><<<p.n_aux + n_gemm, NUM_THREADS, C::SMEM, stream>>>(tmA, tmB, tmD, p, om);
   b200::count_launch();
   return b200::check_launch("gemm_tp");
 }
@@ -632,12 +666,15 @@ int make_ab_maps(CUtensorMap* tmA, CUtensorMap* tmB, const void* a, const void* 
 // own block (all ranks: a cross-rank barrier between that write and this launch).
 //   mode 1: the blocks are row blocks of A (rows_per rows each, M = W*rows_per, rows_per % 128 == 0)
 //   mode 2: the blocks are k blocks (rows_per k-elements each, K = W*rows_per, rows_per % 64 == 0)
-// chunk_flags: W ints of local device memory, zero at launch.  n_copy CTAs do the copies.
+// chunk_flags: W ints, zero at launch.  n_copy CTAs do the copies: copy_mode 0 pulls the peers' blocks
+// (chunk_flags may be ordinary local memory); copy_mode 1 pushes the own block to every peer, then
+// chunk_flags must be this rank's entry of flag_ptrs[0..W) (peer-writable memory, zeroed on every rank
+// before the cross-rank barrier that precedes the launch).
 B200_API int b200_gemm_tp_gather(const void* a, const void* b, void* d, int M, int N, int K, long long lda,
                                  long long ldb, long long ldd, int a_mn_major, int b_mn_major, int out_f32,
                                  int accumulate, float alpha, int mode, const unsigned long long* peer_ptrs, int W,
                                  int rank, void* gbuf_local, long long chunk_bytes, int rows_per, int* chunk_flags,
-                                 int n_copy, void* stream) {
+                                 int n_copy, int copy_mode, const unsigned long long* flag_ptrs, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return b200::fail(1510, "gemm_tp_gather: empty problem %d x %d x %d", M, N, K);
   if (W < 1 || W > MAXW || rank < 0 || rank >= W) return b200::fail(1511, "gemm_tp_gather: bad world %d / rank %d", W, rank);
   if (mode == 1 && (rows_per % BM != 0 || (long long)rows_per * W != M))
@@ -664,11 +701,18 @@ B200_API int b200_gemm_tp_gather(const void* a, const void* b, void* d, int M, i
   for (int c = 0; c < W; ++c) p.peer_src[c] = reinterpret_cast<const uint8_t*>(peer_ptrs[c]);
   p.gdst = reinterpret_cast<uint8_t*>(gbuf_local);
   p.chunk_bytes = chunk_bytes;
-  p.pieces_per_chunk = (int)((chunk_bytes + COPY_PIECE - 1) / COPY_PIECE);
   p.chunk_flag = chunk_flags;
+  p.copy_mode = (copy_mode == 1 && W > 1) ? 1 : 0;
+  const int piece = p.copy_mode == 1 ? PUSH_PIECE : COPY_PIECE;
+  p.pieces_per_chunk = (int)((chunk_bytes + piece - 1) / piece);
+  if (p.copy_mode == 1) {
+    if (flag_ptrs == nullptr) return b200::fail(1516, "gemm_tp_gather: push mode needs the peers' counter arrays");
+    for (int c = 0; c < W; ++c) p.chunk_flag_peer[c] = reinterpret_cast<int*>(flag_ptrs[c]);
+  }
+  static const OwnerMaps no_maps{};
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  if (BN == 256) return launch<256>(tmA, tmB, tmD, p, tiles, (cudaStream_t)stream);
-  return launch<128>(tmA, tmB, tmD, p, tiles, (cudaStream_t)stream);
+  if (BN == 256) return launch<256>(tmA, tmB, tmD, p, no_maps, tiles, (cudaStream_t)stream);
+  return launch<128>(tmA, tmB, tmD, p, no_maps, tiles, (cudaStream_t)stream);
 }
 
 // GEMM -> reduce-scatter.  P[M, N] = alpha * A * B^T is this rank's partial sum; rank o receives
@@ -698,7 +742,7 @@ B200_API int b200_gemm_tp_rs(const void* a, const void* b, int M, int N, int K, 
   p.a_mn_major = a_mn_major ? 1 : 0; p.b_mn_major = b_mn_major ? 1 : 0;
   p.group_m = 16; p.alpha = alpha; p.status = b200::status_ptr();
   p.mode = 3; p.W = W; p.rank = rank; p.rows_per = rows_per;
-  p.n_aux = n_red > 0 ? n_red : 4;
+  p.n_aux = n_red > 0 ? n_red : 8;
   for (int o = 0; o < W; ++o) {
     p.stage_peer[o] = reinterpret_cast<uint8_t*>(stage_ptrs[o]);
     p.flag_peer[o] = reinterpret_cast<int*>(flag_ptrs[o]);
@@ -708,7 +752,13 @@ B200_API int b200_gemm_tp_rs(const void* a, const void* b, int M, int N, int K, 
   p.ld_out = ld_out;
   p.rs_residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ld_res = ld_res;
+  OwnerMaps om{};
+  for (int o = 0; o < W; ++o) {
+    r = b200::make_tmap_2d(&om.m[o], b200::DT_BF16, p.stage_peer[o], N, (long long)W * rows_per, (long long)N * 2, 64, 32,
+                           b200::SWZ_128);
+    if (r) return r;
+  }
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
-  if (BN == 256) return launch<256>(tmA, tmB, tmD, p, tiles, (cudaStream_t)stream);
-  return launch<128>(tmA, tmB, tmD, p, tiles, (cudaStream_t)stream);
+  if (BN == 256) return launch<256>(tmA, tmB, tmD, p, om, tiles, (cudaStream_t)stream);
+  return launch<128>(tmA, tmB, tmD, p, om, tiles, (cudaStream_t)stream);
 }

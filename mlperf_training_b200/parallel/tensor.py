@@ -32,14 +32,18 @@ from ..ops.functional import _wgrad
 
 
 class TPContext:
-    def __init__(self, group=None, comm: str = "nccl", device=None, n_copy: int = 8, n_red: int = 6):
+    RS_FLAG_OFFSET = 64     # ints: [0, 16) all-gather block counters, [64, ...) reduce-scatter tile counters
+
+    def __init__(self, group=None, comm: str = "nccl", device=None, n_copy: int = 0, n_red: int = 8, copy_mode: int = 1):
         self.group = group
         on = dist.is_available() and dist.is_initialized()
         self.world = dist.get_world_size(group) if on else 1
         self.rank = dist.get_rank(group) if on else 0
         self.device = torch.device(device) if device is not None else None
         self.comm = comm
-        self.n_copy, self.n_red = n_copy, n_red
+        # copy CTAs of the all-gather kernel: enough to move (W-1)/W of the operand within the GEMM's time
+        self.n_copy = n_copy if n_copy > 0 else (16 if self.world >= 4 else 8)
+        self.n_red, self.copy_mode = n_red, copy_mode
         self._gather = [None, None]     # double-buffered symmetric gather buffers
         self._gather_turn = 0
         self._stage = None
@@ -102,8 +106,8 @@ class TPContext:
         self._gather_turn ^= 1
         full = buf.local[: rows * self.world * k].view(rows * self.world, k)
         full[self.rank * rows:(self.rank + 1) * rows].copy_(x_shard)
-        self._local_flags.zero_()
-        buf.barrier()
+        self._flags.local.zero_()
+        buf.barrier()          # every block is in place and every counter is zero before any rank launches
         return buf, full
 
     def gemm_gather(self, buf, full: torch.Tensor, other: torch.Tensor, *, mode: int, out: torch.Tensor | None = None,
@@ -121,8 +125,8 @@ class TPContext:
             out = torch.empty((M, N), dtype=out_dtype, device=full.device)
         _lib.call("b200_gemm_tp_gather", _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, Kd, a.stride(0), b.stride(0),
                   out.stride(0), a_mn, b_mn, int(out.dtype == torch.float32), int(accumulate), 1.0, mode,
-                  buf.ptr_array(), W, r, _lib.ptr(full), rows_per * Kf * 2, rows_per, _lib.ptr(self._local_flags),
-                  self.n_copy, _lib.stream_ptr())
+                  buf.ptr_array(), W, r, _lib.ptr(full), rows_per * Kf * 2, rows_per, _lib.ptr(self._flags.local),
+                  self.n_copy, self.copy_mode, self._flags.ptr_array(), _lib.stream_ptr())
         return out
 
     def gemm_reduce_scatter(self, a: torch.Tensor, b: torch.Tensor, *, b_mn_major: bool = False,
@@ -138,7 +142,8 @@ class TPContext:
         self._stage.barrier()           # counters are zero everywhere, previous readers of the staging buffer are done
         out = torch.empty((rows_per, N), dtype=torch.bfloat16, device=a.device)
         _lib.call("b200_gemm_tp_rs", _lib.ptr(a), _lib.ptr(b), M, N, Kd, a.stride(0), b.stride(0), 0, int(b_mn_major), 1.0,
-                  self._stage.ptr_array(), self._flags.ptr_array(), W, r, _lib.ptr(self._local_flags[16:]),
+                  self._stage.ptr_array(), self._flags.offset_ptr_array(4 * self.RS_FLAG_OFFSET), W, r,
+                  _lib.ptr(self._local_flags[16:]),
                   _lib.ptr(out), out.stride(0), None if residual is None else _lib.ptr(residual),
                   0 if residual is None else residual.stride(0), self.n_red, _lib.stream_ptr())
         return out
@@ -216,7 +221,8 @@ def _gather_dgrad(tp: TPContext, buf, dy_full: torch.Tensor, weight: torch.Tenso
     out = torch.empty((T, k_local), dtype=torch.bfloat16, device=dy_full.device)
     _lib.call("b200_gemm_tp_gather", _lib.ptr(dy_full), _lib.ptr(weight), _lib.ptr(out), T, k_local, N, dy_full.stride(0),
               weight.stride(0), out.stride(0), 0, 1, 0, 0, 1.0, 1, buf.ptr_array(), W, r, _lib.ptr(dy_full),
-              (T // W) * N * 2, T // W, _lib.ptr(tp._local_flags), tp.n_copy, _lib.stream_ptr())
+              (T // W) * N * 2, T // W, _lib.ptr(tp._flags.local), tp.n_copy, tp.copy_mode, tp._flags.ptr_array(),
+              _lib.stream_ptr())
     return out
 
 

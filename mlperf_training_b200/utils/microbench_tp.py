@@ -49,6 +49,9 @@ def main(argv=None) -> int:
     ap.add_argument("--ffn", type=int, default=28672)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--n-copy", type=int, default=0, help="copy CTAs of the all-gather kernel (0 = default)")
+    ap.add_argument("--n-red", type=int, default=0, help="dedicated reduce CTAs of the reduce-scatter kernel (0 = default)")
+    ap.add_argument("--copy-sweep", action="store_true", help="also time the all-gather copies alone for several n_copy")
     args = ap.parse_args(argv)
     rank = int(os.environ.get("RANK", "0"))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
@@ -76,6 +79,10 @@ def main(argv=None) -> int:
     def rs_nccl():
         return nccl.reduce_scatter_rows(K.gemm(act, w_row))
 
+    if args.n_copy:
+        fused.n_copy = args.n_copy
+    if args.n_red:
+        fused.n_red = args.n_red
     err_ag = (ag_fused().float() - ag_nccl().float()).abs().max().item()
     err_rs = (rs_fused().float() - rs_nccl().float()).abs().max().item()
     for name, f_fused, f_nccl, flops, link_bytes, err in (
@@ -85,11 +92,25 @@ def main(argv=None) -> int:
         t_n = timed(f_nccl, args.iters, args.warmup, flush)
         roof_ms = max(flops / (GEMM_PEAK_TFLOPS * 1e12), link_bytes / (NVLINK_GBS * 1e9)) * 1e3
         if rank == 0:
-            print(json.dumps({"kernel": name, "world": W, "tokens": T, "hidden": D, "ffn": args.ffn, "fused_ms": round(t_f, 4),
+            print(json.dumps({"kernel": name, "world": W, "n_copy": fused.n_copy, "n_red": fused.n_red, "tokens": T, "hidden": D, "ffn": args.ffn, "fused_ms": round(t_f, 4),
                               "nccl_plus_gemm_ms": round(t_n, 4), "speedup": round(t_n / t_f, 3),
                               "fused_tflops_per_gpu": round(flops / t_f / 1e9, 1), "nvlink_mb_per_gpu": round(link_bytes / 1e6, 1),
                               "roofline_ms": round(roof_ms, 4), "fraction_of_roofline": round(roof_ms / t_f, 3),
                               "max_abs_diff_vs_nccl": err}), flush=True)
+    if args.copy_sweep:
+        # all-gather with a negligible GEMM (N = 128): the time is the in-kernel copy of the peers' blocks
+        w_small = (torch.randn(128, D, device=dev) * 0.02).bfloat16()
+        for n_copy in (4, 8, 16, 32):
+            fused.n_copy = n_copy
+
+            def ag_small():
+                buf, full = fused.gather_begin(x_shard)
+                return fused.gemm_gather(buf, full, w_small, mode=1)
+            t = timed(ag_small, args.iters, args.warmup, flush)
+            if rank == 0:
+                mb = (W - 1) / W * T * D * 2 / 1e6
+                print(json.dumps({"kernel": "all_gather_copy_only", "world": W, "n_copy": n_copy, "ms": round(t, 4),
+                                  "pulled_mb": round(mb, 1), "gb_per_s": round(mb / t, 1)}), flush=True)
     from ..ops import _lib
     _lib.check_status("microbench_tp")
     dist.barrier()

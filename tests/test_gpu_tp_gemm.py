@@ -21,7 +21,7 @@ def _gather_call(a, b, out, M, N, K, a_mn, b_mn, mode, bufs, rank, full, rows_pe
     _lib.call("b200_gemm_tp_gather", _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0),
               out.stride(0), a_mn, b_mn, int(out.dtype == torch.float32), int(accumulate), 1.0, mode,
               _arr([t.data_ptr() for t in bufs]), W, rank, _lib.ptr(full), chunk_bytes, rows_per, _lib.ptr(flags), 4,
-              _lib.stream_ptr())
+              0, None, _lib.stream_ptr())        # pull mode: the launch depends on no other rank's kernel
     torch.cuda.synchronize()
     _lib.check_status("gemm_tp_gather")
 
@@ -91,4 +91,4 @@ def test_gemm_reduce_scatter_world1(shape, res):
         want = want + resid.float()
     err = (out.float() - want).abs().max().item()
     assert err < 2e-2 * want.abs().max().item(), err
-    assert int(work.item()) >= (M // 128) * 16
+    assert int(work.item()) >= (M // 128) * 64
