@@ -56,81 +56,87 @@ B200_DEVICE long long sf_offset(long long r, int kc, int tile_rows, int atoms_pe
   return ((tile * k_groups + (kc >> 2)) * atoms_per_tile + atom) * 512 + (ra & 31) * 16 + (ra >> 5) * 4 + (kc & 3);
 }
 
-// grid: (C / 128, R / 128); 256 threads
-__global__ void __launch_bounds__(256, 3)
+// shared-memory tile: row r starts at r * PITCH + (r >> 4) * 4 bf16 elements.  The odd word pitch
+// spreads a column over the banks and the per-16-row skew separates the eight lanes that walk one
+// column in the column pass.
+B200_DEVICE int tile_off(int r) { return r * PITCH + (r >> 4) * 4; }
+
+B200_DEVICE uint2 quant8(const float (&f)[8], float inv) {
+  return make_uint2(pack4_e4m3(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv),
+                    pack4_e4m3(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv));
+}
+
+// grid: (C / 128, R / 128); 256 threads.
+//   row pass:    a warp instruction covers 2 rows x 256 bytes of input (lane = 8 elements); a block of
+//                32 elements is 4 lanes, so amax is two shuffles; codes leave as 2 x 128 contiguous bytes.
+//   column pass: 8 lanes walk one column (16 rows each, amax of a 32-block = one shuffle) and write the
+//                column's 128 codes as one contiguous 128-byte piece of the transposed copy.
+//   scales:      staged in shared memory and written as one 32-bit word per operand row.
+__global__ void __launch_bounds__(256, 4)
 quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, int C, uint8_t* __restrict__ q_row,
                    uint8_t* __restrict__ sf_row, int row_tile, uint8_t* __restrict__ q_col,
                    uint8_t* __restrict__ sf_col, int col_tile) {
-  __shared__ __nv_bfloat16 tile[TILE * PITCH];
+  __shared__ __align__(16) __nv_bfloat16 tile[TILE * PITCH + 32];
+  __shared__ __align__(4) uint8_t sfs[2][TILE][4];     // [row pass | column pass][operand row][scale column]
   const int c0 = blockIdx.x * TILE, r0 = blockIdx.y * TILE;
-  const int tid = threadIdx.x;
-  // ---- load the 128 x 128 tile (each thread: one row half = 64 contiguous elements) ----
-  {
-    const int r = tid >> 1, h = tid & 1;
-    const __nv_bfloat16* src = x + (long long)(r0 + r) * ldx + c0 + h * 64;
-    uint4 v[8];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int sub_row = lane >> 4, chunk = lane & 15;
+  uint4 v[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = reinterpret_cast<const uint4*>(src)[i];
-    // row-wise quantisation straight from registers: two blocks of 32
-    if (q_row != nullptr) {
-      uint8_t* dst = q_row + (long long)(r0 + r) * C + c0 + h * 64;
-#pragma unroll
-      for (int blk = 0; blk < 2; ++blk) {
-        float f[32];
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint4 u = v[blk * 4 + i];
-          const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-          f[8 * i + 0] = a.x; f[8 * i + 1] = a.y; f[8 * i + 2] = b.x; f[8 * i + 3] = b.y;
-          f[8 * i + 4] = c.x; f[8 * i + 5] = c.y; f[8 * i + 6] = d.x; f[8 * i + 7] = d.y;
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(f[i]));
-        const uint32_t e = e8m0_from_amax(amax);
-        const float inv = scale_inv_from_e8m0(e);
-        uint4 o[2];
-        uint32_t* ow = reinterpret_cast<uint32_t*>(o);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ow[i] = pack4_e4m3(f[4 * i] * inv, f[4 * i + 1] * inv, f[4 * i + 2] * inv, f[4 * i + 3] * inv);
-        reinterpret_cast<uint4*>(dst + blk * 32)[0] = o[0];
-        reinterpret_cast<uint4*>(dst + blk * 32)[1] = o[1];
-        const int kc = (c0 >> 5) + h * 2 + blk;
-        sf_row[sf_offset(r0 + r, kc, row_tile, (row_tile + 127) >> 7, C >> 7)] = (uint8_t)e;
-      }
-    }
-    if (q_col != nullptr) {
-      uint32_t* trow = reinterpret_cast<uint32_t*>(tile + r * PITCH + h * 64);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { trow[4 * i] = v[i].x; trow[4 * i + 1] = v[i].y; trow[4 * i + 2] = v[i].z; trow[4 * i + 3] = v[i].w; }
-    }
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 16 + warp * 2 + sub_row;
+    v[it] = *reinterpret_cast<const uint4*>(x + (long long)(r0 + r) * ldx + c0 + chunk * 8);
   }
-  if (q_col == nullptr) return;
-  __syncthreads();
-  // ---- column-wise: thread = (column c, half h of the rows); two blocks of 32 rows ----
-  {
-    const int c = tid & 127, h = tid >> 7;
-    uint8_t* dst = q_col + (long long)(c0 + c) * R + r0 + h * 64;
 #pragma unroll
-    for (int blk = 0; blk < 2; ++blk) {
-      float f[32];
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 16 + warp * 2 + sub_row;
+    if (q_row != nullptr) {
+      const float2 a = unpack_bf16x2(v[it].x), b = unpack_bf16x2(v[it].y), c = unpack_bf16x2(v[it].z), d = unpack_bf16x2(v[it].w);
+      const float f[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
       float amax = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        f[i] = __bfloat162float(tile[(h * 64 + blk * 32 + i) * PITCH + c]);
-        amax = fmaxf(amax, fabsf(f[i]));
-      }
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
       const uint32_t e = e8m0_from_amax(amax);
-      const float inv = scale_inv_from_e8m0(e);
-      uint4 o[2];
-      uint32_t* ow = reinterpret_cast<uint32_t*>(o);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) ow[i] = pack4_e4m3(f[4 * i] * inv, f[4 * i + 1] * inv, f[4 * i + 2] * inv, f[4 * i + 3] * inv);
-      reinterpret_cast<uint4*>(dst + blk * 32)[0] = o[0];
-      reinterpret_cast<uint4*>(dst + blk * 32)[1] = o[1];
-      const int kc = (r0 >> 5) + h * 2 + blk;
-      sf_col[sf_offset(c0 + c, kc, col_tile, (col_tile + 127) >> 7, R >> 7)] = (uint8_t)e;
+      *reinterpret_cast<uint2*>(q_row + (long long)(r0 + r) * C + c0 + chunk * 8) = quant8(f, scale_inv_from_e8m0(e));
+      if ((chunk & 3) == 0) sfs[0][r][chunk >> 2] = (uint8_t)e;
     }
+    if (q_col != nullptr) {
+      uint32_t* t = reinterpret_cast<uint32_t*>(tile + tile_off(r) + chunk * 8);
+      t[0] = v[it].x; t[1] = v[it].y; t[2] = v[it].z; t[3] = v[it].w;
+    }
+  }
+  __syncthreads();
+  if (q_row != nullptr && tid < TILE) {
+    const long long o = sf_offset(r0 + tid, c0 >> 5, row_tile, (row_tile + 127) >> 7, C >> 7);
+    *reinterpret_cast<uint32_t*>(sf_row + o) = *reinterpret_cast<const uint32_t*>(&sfs[0][tid][0]);
+  }
+  if (q_col == nullptr) return;
+  const int sub = lane & 7;                      // rows sub * 16 .. + 15 of the column
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int c = pass * 32 + warp * 4 + (lane >> 3);
+    float f[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      f[i] = __bfloat162float(tile[tile_off(sub * 16 + i) + c]);
+      amax = fmaxf(amax, fabsf(f[i]));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    const uint32_t e = e8m0_from_amax(amax);
+    const float inv = scale_inv_from_e8m0(e);
+    const float lo[8] = {f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7]};
+    const float hi[8] = {f[8], f[9], f[10], f[11], f[12], f[13], f[14], f[15]};
+    const uint2 q0 = quant8(lo, inv), q1 = quant8(hi, inv);
+    *reinterpret_cast<uint4*>(q_col + (long long)(c0 + c) * R + r0 + sub * 16) = make_uint4(q0.x, q0.y, q1.x, q1.y);
+    if ((sub & 1) == 0) sfs[1][c][sub >> 1] = (uint8_t)e;
+  }
+  __syncthreads();
+  if (tid < TILE) {
+    const long long o = sf_offset(c0 + tid, r0 >> 5, col_tile, (col_tile + 127) >> 7, R >> 7);
+    *reinterpret_cast<uint32_t*>(sf_col + o) = *reinterpret_cast<const uint32_t*>(&sfs[1][tid][0]);
   }
 }
 

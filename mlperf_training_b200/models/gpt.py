@@ -52,6 +52,10 @@ class GPTConfig:
     lora_alpha: float = 32.0
     lora_dropout: float = 0.0
     lora_targets: tuple = ("qkv", "proj")
+    # activation recompute: "none" | "full" (every block's forward is run again in backward and only
+    # its input is kept); recompute_layers > 0 limits it to the first N blocks
+    recompute: str = "none"
+    recompute_layers: int = 0
     dtype: str = "bf16"
     precision: str = "bf16"         # GEMM precision of the linears: "bf16" | "mxfp8"
 
@@ -330,7 +334,12 @@ class GPT(nn.Module):
                 n_valid = ids.numel()
             ids, tgt = ids[r * rows:(r + 1) * rows], tgt[r * rows:(r + 1) * rows]
         x = F.embedding(ids, self.embed)
-        for blk in self.blocks:
-            x = blk(x, cos, sin, B, S)
+        ckpt = self.cfg.recompute == "full" and torch.is_grad_enabled()
+        for i, blk in enumerate(self.blocks):
+            if ckpt and (self.cfg.recompute_layers <= 0 or i < self.cfg.recompute_layers):
+                from torch.utils.checkpoint import checkpoint
+                x = checkpoint(blk, x, cos, sin, B, S, use_reentrant=False)
+            else:
+                x = blk(x, cos, sin, B, S)
         return F.lm_head_loss(x, self.final_norm, self.lm_head, tgt, eps=self.cfg.norm_eps,
                               n_valid=n_valid, precision=self.cfg.precision)

@@ -71,6 +71,16 @@ class StepFence:
             self.events.pop(0).synchronize()
 
 
+class _WorldView:
+    """Binds the world size into ``batch_at`` so every data source has the same call signature."""
+
+    def __init__(self, ds, world: int):
+        self.ds, self.world = ds, world
+
+    def batch_at(self, step: int, rank: int = 0, pin: bool = False) -> dict:
+        return self.ds.batch_at(step, rank, pin, self.world)
+
+
 def hstu_bucket_of(name: str) -> str:
     parts = name.split(".")
     return f"l{int(parts[1]):04d}" if parts[0] == "layers" else "a_misc"
@@ -87,7 +97,16 @@ class HSTUTrainer:
         self.engine = ZeroEngine(self.model, opt, bucket_of=hstu_bucket_of, comm=dense_comm, group=group)
         self.table = ShardedEmbedding(table_rows, cfg.emb_dim, group=group, device=self.device, dtype=cfg.torch_dtype(),
                                       lr=sparse_lr, seed=seed, comm=emb_comm, init_scale=0.05)
-        self.data = HSTUSyntheticData(table_rows, batch_per_gpu, seed=seed, **(data_kw or {}))
+        data_kw = dict(data_kw or {})
+        if data_kw.pop("kind", "synthetic") == "yambda":
+            # memory-mapped event store: time windows, per-rank slices of each window, user-hash hold-out
+            from ..data.yambda import EventStoreDataset
+            root = data_kw.pop("root")
+            self.data = _WorldView(EventStoreDataset(root, batch_per_gpu, split="train", **data_kw), self.world)
+            self.eval_data = _WorldView(EventStoreDataset(root, batch_per_gpu, split="eval", **data_kw), self.world)
+        else:
+            self.data = HSTUSyntheticData(table_rows, batch_per_gpu, seed=seed, **data_kw)
+            self.eval_data = None
         self.batch_per_gpu = batch_per_gpu
         self.step_idx = 0
         self.copy_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
@@ -135,14 +154,41 @@ class HSTUTrainer:
     def eval_batches(self, n_batches: int, start: int = 10**6):
         self.model.eval()
         ps, ls = [], []
+        src = self.eval_data if self.eval_data is not None else self.data
+        if self.eval_data is not None:
+            start = 0
         for i in range(n_batches):
-            b = HSTUSyntheticData.to_device(self.data.batch_at(start + i, self.rank), self.device)
+            b = HSTUSyntheticData.to_device(src.batch_at(start + i, self.rank), self.device)
             with torch.enable_grad():       # the lookup Function needs a graph only to skip its backward
                 emb = self.embed(b).detach()
             _, p, l = self.model(b, emb)
             ps.append(p)
             ls.append(l)
         return torch.cat(ps), torch.cat(ls)
+
+
+def _warmup(tr: "HSTUTrainer", steps: int) -> None:
+    """Untimed steps before RUN_START (first-use costs of every kernel, allocator growth, NCCL
+    channels), after which parameters, optimizer state, the embedding shard and its Adagrad sums are
+    put back (the reference's pre-RUN_START warm-ups: generative_recommenders/dlrm_v4/train/blas_warmup.py,
+    fp8_warmup.py)."""
+    if steps <= 0:
+        return
+    from .warmup import restore_engine, snapshot_engine
+    snap = snapshot_engine(tr.engine)
+    w, st = tr.table.weight.clone(), tr.table.state.clone()
+    rng_cpu = torch.get_rng_state()
+    rng_dev = torch.cuda.get_rng_state() if tr.device.type == "cuda" else None
+    for i in range(steps):
+        tr.train_step(10**7 + i)
+    torch.set_rng_state(rng_cpu)                 # RNG-neutral: dropout masks of the timed run do not move
+    if rng_dev is not None:
+        torch.cuda.set_rng_state(rng_dev)
+    restore_engine(tr.engine, snap)
+    tr.table.weight.copy_(w)
+    tr.table.state.copy_(st)
+    tr.step_idx = 0
+    tr._next = None
 
 
 def run(exp: dict, device: str | None = None, stream=None) -> dict:
@@ -166,7 +212,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                      num_positions=int(m.get("num_positions", 8192)), num_time_buckets=int(m.get("num_time_buckets", 2048)))
     emb = exp.get("embedding") or {}
     d = dict(exp.get("data") or {})
-    data_kw = {k: d[k] for k in ("length_median", "length_min", "length_max", "zipf_alpha") if k in d}
+    data_kw = {k: d[k] for k in ("length_median", "length_min", "length_max", "zipf_alpha", "kind", "root", "max_history",
+                                 "min_history", "window_seconds", "holdout", "salt") if k in d}
     bpg = int(exp.get("batch_per_gpu", 128))
     tr = HSTUTrainer(cfg, int(emb.get("rows", 1_000_000)), bpg, device, dense_lr=float(exp.get("dense_lr", 1e-3)),
                      sparse_lr=float(exp.get("sparse_lr", 1e-2)), clip_grad=float(exp.get("clip_grad", 1.0)),
@@ -184,6 +231,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     else:
         log.log_hyperparameters({"global_batch_size": bpg * world, "seed": int(exp.get("seed", 0)),
                                  "opt_base_learning_rate": float(exp.get("dense_lr", 1e-3))})
+        _warmup(tr, int(exp.get("warmup_steps", 0)))
         log.log_init_stop_run_start()
         log.start(ml.BLOCK_START, metadata={"samples_count": 0})
     steps = int(exp.get("train_steps", 10))

@@ -101,3 +101,45 @@ def normalized_entropy(scores: torch.Tensor, labels: torch.Tensor, eps: float = 
 
 def accuracy(scores: torch.Tensor, labels: torch.Tensor, threshold: float = 0.5) -> float:
     return float(((scores >= threshold).float() == labels.float()).float().mean())
+
+
+class PerfLogger:
+    """Per-interval performance line: samples/s, step time, algorithmic TFLOP/s per GPU and MFU, with
+    checkpoint / evaluation time excluded through ``pause`` (the reference's ``MetricsLogger`` perf
+    line, generative_recommenders/dlrm_v4/utils.py:842-1535), and a durable ``metrics.jsonl``."""
+
+    def __init__(self, flops_per_sample: float, world: int = 1, peak_tflops: float = 2250.0, jsonl: str | None = None):
+        import time
+        self._now = time.perf_counter
+        self.flops_per_sample, self.world, self.peak = flops_per_sample, world, peak_tflops
+        self.jsonl = jsonl
+        self.t0 = self._now()
+        self.paused = 0.0
+        self._pause_t = None
+        self.samples = 0
+        self.steps = 0
+
+    def pause(self) -> None:
+        self._pause_t = self._now()
+
+    def resume(self) -> None:
+        if self._pause_t is not None:
+            self.paused += self._now() - self._pause_t
+            self._pause_t = None
+
+    def step(self, samples: int) -> None:
+        self.samples += samples
+        self.steps += 1
+
+    def line(self, step: int, extra: dict | None = None) -> dict:
+        import json
+        dt = max(self._now() - self.t0 - self.paused, 1e-9)
+        sps = self.samples / dt
+        tflops_gpu = sps * self.flops_per_sample / self.world / 1e12
+        rec = {"step": step, "samples_per_s": sps, "step_ms": 1e3 * dt / max(self.steps, 1), "tflops_algo_per_gpu": tflops_gpu,
+               "mfu": tflops_gpu / self.peak, **(extra or {})}
+        if self.jsonl:
+            with open(self.jsonl, "a") as f:
+                f.write(json.dumps(rec) + "\n")
+        self.t0, self.paused, self.samples, self.steps = self._now(), 0.0, 0, 0
+        return rec

@@ -137,3 +137,20 @@ def test_hstu_mask_rules():
     assert m[0, :6].all() and not m[0, 6]                                     # contextual rows see all history
     assert m[3, :3].all() and m[3, 3] and not m[3, 4]
     assert m[6, :6].all() and m[6, 6]
+
+
+def test_activation_recompute_matches_plain_backward():
+    import torch
+    from mlperf_training_b200.models.gpt import GPT, GPTConfig
+    kw = dict(n_layers=3, hidden=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn_hidden=128, vocab_size=256, seq_len=32,
+              dtype="fp32")
+    tok = torch.randint(0, 256, (2, 33), generator=torch.Generator().manual_seed(0))
+    out = []
+    for rc, n in (("none", 0), ("full", 2), ("full", 0)):
+        m = GPT(GPTConfig(recompute=rc, recompute_layers=n, **kw), seed=1)
+        loss = m(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        out.append((loss.item(), [p.grad.clone() for p in m.parameters()]))
+    for l, g in out[1:]:
+        assert l == out[0][0]
+        assert all(torch.equal(a, b) for a, b in zip(g, out[0][1]))

@@ -1,0 +1,76 @@
+"""Event-store dataset (anchors, three-pool history, windows, deterministic split and rank slices),
+allocator growth monitor, performance line."""
+import json
+
+import numpy as np
+
+from mlperf_training_b200.data.yambda import EventStoreDataset, write_event_store
+from mlperf_training_b200.utils.alloc import GrowthMonitor, pregrow, recommended_env
+from mlperf_training_b200.utils.metrics import PerfLogger
+
+
+def _store(tmp_path, users=40, events=120, seed=0):
+    rng = np.random.default_rng(seed)
+    user = np.repeat(np.arange(users), events)
+    ts = 1_600_000_000 + rng.integers(0, 5 * 86_400, size=users * events)
+    item = rng.integers(0, 500, size=users * events)
+    kind = rng.choice([0, 0, 0, 1, 2], size=users * events).astype(np.uint8)
+    write_event_store(str(tmp_path / "store"), user, item, ts, kind, played=rng.integers(0, 2, size=users * events))
+    return str(tmp_path / "store")
+
+
+def test_event_store_batches(tmp_path):
+    root = _store(tmp_path)
+    ds = EventStoreDataset(root, batch=4, max_history=30, min_history=8, holdout=0.2, salt=3)
+    ev = EventStoreDataset(root, batch=4, max_history=30, min_history=8, holdout=0.2, salt=3, split="eval")
+    tr_users, ev_users = set(ds.user[ds.anchors].tolist()), set(ev.user[ev.anchors].tolist())
+    assert tr_users and ev_users and not (tr_users & ev_users)                      # the split is by user
+    assert ds.num_windows >= 4
+    a0, a1 = ds.window_anchors(1, 0, 2), ds.window_anchors(1, 1, 2)
+    assert not set(a0.tolist()) & set(a1.tolist())                                  # rank slices are disjoint
+    assert np.all(np.diff(np.asarray(ds.ts)[a0]) >= 0)                              # time order inside a window
+    b = ds.batch_at(0)
+    assert b["offsets"].tolist()[0] == 0 and b["total"] == int(b["offsets"][-1]) and b["rows"] % 128 == 0
+    lens = b["lengths"].tolist()
+    assert all(9 <= n <= 31 for n in lens)                                          # >= min_history + target, <= cap + target
+    for i in range(4):                                                              # per user: time-ordered, target last
+        seg = b["timestamps"][b["offsets"][i]:b["offsets"][i + 1]]
+        assert bool((seg[1:] >= seg[:-1]).all())
+    again = EventStoreDataset(root, batch=4, max_history=30, min_history=8, holdout=0.2, salt=3).batch_at(0)
+    assert again["item_ids"].tolist() == b["item_ids"].tolist()                     # exact-once resume contract
+    n_steps = sum(ds.batches_in_window(w) for w in range(ds.num_windows))
+    assert ds.batch_at(n_steps - 1)["total"] > 0
+
+
+def test_growth_monitor_and_perf_line(tmp_path):
+    state = {"reserved_bytes.all.current": 100, "segment.all.allocated": 2, "num_alloc_retries": 0}
+    mon = GrowthMonitor(stats=lambda: dict(state))
+    assert mon.check(1) is None and "no growth" in mon.report()
+    state["reserved_bytes.all.current"] = 100 + (3 << 20)
+    ev = mon.check(2)
+    assert ev["step"] == 2 and ev["reserved"] == 3 << 20 and "3.0 MiB" in mon.report()
+    assert pregrow(1 << 20) >= 0 and "expandable_segments" in recommended_env()["PYTORCH_CUDA_ALLOC_CONF"]
+    p = PerfLogger(flops_per_sample=1e12, world=2, peak_tflops=1000.0, jsonl=str(tmp_path / "m.jsonl"))
+    p.step(8)
+    p.pause(), p.resume()
+    rec = p.line(1, {"loss": 0.5})
+    assert rec["samples_per_s"] > 0 and abs(rec["mfu"] - rec["tflops_algo_per_gpu"] / 1000.0) < 1e-12
+    assert json.loads((tmp_path / "m.jsonl").read_text().splitlines()[0])["loss"] == 0.5
+
+
+def test_hstu_run_on_event_store_with_warmup(tmp_path):
+    import io
+    from mlperf_training_b200.mllog import check_compliance
+    from mlperf_training_b200.trainer.hstu import run
+    root = _store(tmp_path, users=60, events=100)
+    exp = dict(batch_per_gpu=4, train_steps=6, warmup_steps=2, eval_interval_steps=3, num_eval_batches=1,
+               model=dict(layers=1, dim=32, heads=2, d_qk=16, d_v=16, max_seq_len=48, dtype="fp32", mlp_hidden=16,
+                          num_positions=64, num_time_buckets=32),
+               embedding=dict(rows=500, dim=16),
+               data=dict(kind="yambda", root=root, max_history=30, min_history=8, holdout=0.3, salt=1))
+    out = run(exp, device="cpu", stream=io.StringIO())
+    assert len(out["losses"]) == 6 and all(l == l for l in out["losses"]) and len(out["aucs"]) == 2
+    assert check_compliance(out["records"]) == []
+    # warm-up left no trace: a run without it starts from the same state
+    ref = run(dict(exp, warmup_steps=0), device="cpu", stream=io.StringIO())
+    assert abs(ref["losses"][0] - out["losses"][0]) < 1e-6
