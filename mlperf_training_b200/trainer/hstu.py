@@ -109,6 +109,7 @@ class HSTUTrainer:
             self.eval_data = None
         self.batch_per_gpu = batch_per_gpu
         self.step_idx = 0
+        self.eval_lookahead = True
         self.copy_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
         self._next = None
 
@@ -150,6 +151,22 @@ class HSTUTrainer:
     def train_step(self, step: int | None = None) -> torch.Tensor:
         return self.train_step_device(self._take(self.step_idx if step is None else step))
 
+    def _eval_inputs(self, src, step: int):
+        b = HSTUSyntheticData.to_device(src.batch_at(step, self.rank), self.device)
+        with torch.enable_grad():           # the lookup Function needs a graph only to skip its backward
+            emb = self.embed(b).detach()
+        return b, emb
+
+    def lookahead_ready(self) -> bool:
+        """Evaluation lookahead (batch N+1's id exchange and row gather on a side stream while batch N
+        runs the dense model) is armed only if every rank can do it: one MIN all-reduce, so no rank
+        waits in a collective that another never issues (the reference arms its eval lookahead the
+        same way, generative_recommenders/dlrm_v4/train/eval_lookahead.py:170-1330)."""
+        ok = torch.tensor([1.0 if (self.eval_lookahead and self.device.type == "cuda") else 0.0], device=self.device)
+        if self.world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        return bool(ok.item() > 0)
+
     @torch.no_grad()
     def eval_batches(self, n_batches: int, start: int = 10**6):
         self.model.eval()
@@ -157,13 +174,28 @@ class HSTUTrainer:
         src = self.eval_data if self.eval_data is not None else self.data
         if self.eval_data is not None:
             start = 0
+        lookahead = n_batches > 1 and self.lookahead_ready()
+        side = torch.cuda.Stream() if lookahead else None
+        nxt = self._eval_inputs(src, start)
         for i in range(n_batches):
-            b = HSTUSyntheticData.to_device(src.batch_at(start + i, self.rank), self.device)
-            with torch.enable_grad():       # the lookup Function needs a graph only to skip its backward
-                emb = self.embed(b).detach()
+            b, emb = nxt
+            ev = None
+            if i + 1 < n_batches:
+                if lookahead:
+                    side.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(side):
+                        nxt = self._eval_inputs(src, start + i + 1)
+                        ev = torch.cuda.Event()
+                        ev.record()
+                else:
+                    nxt = self._eval_inputs(src, start + i + 1)
             _, p, l = self.model(b, emb)
             ps.append(p)
             ls.append(l)
+            if ev is not None:
+                torch.cuda.current_stream().wait_event(ev)
+                for t in (nxt[1], *[v for v in nxt[0].values() if torch.is_tensor(v)]):
+                    t.record_stream(torch.cuda.current_stream())
         return torch.cat(ps), torch.cat(ls)
 
 

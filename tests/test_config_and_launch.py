@@ -110,3 +110,14 @@ def test_run_and_time_end_to_end(tmp_path):
         assert chk.returncode == 0 and "SUCCESS" in chk.stdout
     finally:
         exp.unlink()
+
+
+def test_env_bootstrap_env_wins_and_partial_arm():
+    from mlperf_training_b200.config.bootstrap import apply_env_bootstrap
+    env = {"B_KEEP": "7"}
+    bindings = {"a": "B_A", "keep": "B_KEEP", "x": "B_X", "y": "B_Y", "skip": "B_SKIP"}
+    rep = apply_env_bootstrap(bindings, {"a": True, "keep": 3, "x": True, "y": False, "skip": None},
+                              arms={"fp8_forward": ["x", "y"]}, environ=env)
+    assert env["B_A"] == "1" and env["B_KEEP"] == "7" and env["B_Y"] == "0" and "B_SKIP" not in env
+    assert rep.kept == {"B_KEEP": "7"} and rep.partial_arms == {"fp8_forward": {"on": ["x"], "off": ["y"]}}
+    assert any("partial arm" in l for l in rep.lines())
