@@ -50,3 +50,13 @@ def test_stage_layer_split():
     from mlperf_training_b200.parallel.pipeline import stage_layers
     assert [list(stage_layers(10, 4, s)) for s in range(4)] == [[0, 1, 2], [3, 4, 5], [6, 7], [8, 9]]
     assert sum(len(stage_layers(80, 8, s)) for s in range(8)) == 80
+
+
+def test_context_parallel_attention_gloo():
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3",
+                        "--master-addr", "127.0.0.1", "--master-port", "29658",
+                        os.path.join(ROOT, "tests", "multi", "cp_worker.py"), "gloo"],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT rank 0 ok=True" in r.stdout

@@ -46,3 +46,17 @@ def test_fused_expert_dispatch_matches_all_to_all():
     res = _run("moe_fused_worker.py")
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "RESULT rank 0 ok=True" in res.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_context_parallel_attention_two_gpus():
+    res = _run("cp_worker.py", args=("nccl",))
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "RESULT rank 0 ok=True" in res.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_pipeline_parallel_two_gpus():
+    res = _run("pp_worker.py", args=("nccl",))
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "RESULT rank 0 ok=True" in res.stdout
