@@ -21,8 +21,9 @@ def main():
     device = torch.device("cuda", torch.cuda.current_device()) if gpu else torch.device("cpu")
     dist.init_process_group(backend)
     mesh = Mesh(MeshSpec(pp=world))
-    cfg = GPTConfig(n_layers=3, hidden=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn_hidden=128, vocab_size=256,
-                    seq_len=32, dtype="bf16" if gpu else "fp32")
+    cfg = GPTConfig(n_layers=3, hidden=256 if gpu else 64, n_heads=4, n_kv_heads=2, head_dim=64 if gpu else 16,
+                    ffn_hidden=512 if gpu else 128, vocab_size=512 if gpu else 256, seq_len=128 if gpu else 32,
+                    dtype="bf16" if gpu else "fp32")
     full = GPT(cfg, device=device, seed=5)
     stage = GPTStage(cfg, mesh.index("pp"), world, device=device)
     stage.load_from_full(full)
