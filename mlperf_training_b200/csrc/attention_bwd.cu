@@ -10,8 +10,12 @@
 // core both key-contiguous (for dQ) and as MN-major operands (P^T, dS^T) through the UMMA
 // descriptor, so no transposed copies are made.  dK / dV leave as bf16 through TMA stores.
 //
-// 320 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 softmax (one query row per
-// thread), warps 6-9 dQ drain.  TMEM (512 columns): S/dQ | dP | dK | dV.
+// 320 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2-9 workers.  Two workers share a
+// TMEM lane quarter (32 query rows): each computes P / dS for half of the 128 key columns, then
+// drains half of the dQ columns (TMEM -> registers, accumulator released, registers -> fp32 TMA
+// reduce-add while the next S / dP GEMMs run).  A quarter of the exponentials is evaluated with a
+// polynomial on the FMA pipe: 128 x 128 exp2 per tile would otherwise cost 1024 cycles of the
+// 16-per-clock special-function unit alone.  TMEM (512 columns): S/dQ | dP | dK | dV.
 //
 // The reference takes this kernel from Primus-Turbo / AITER / CK (config knobs
 // llama2_sft/primus/config_MI355X_1x8x1.sh:35-39); there is no in-tree counterpart.
@@ -113,7 +117,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 4); mbar_init(dq_full, 1); mbar_init(dq_drained, 4); mbar_init(acc_done, 1);
+    mbar_init(pds_full, 8); mbar_init(dq_full, 1); mbar_init(dq_drained, 8); mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -204,11 +208,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       if (ok) tc_commit(acc_done);
     }
-  } else if (warp < 6) {
-    // ------------------------------ softmax: P and dS ------------------------------
-    const int q = warp & 3;
+  } else {
+    // ------------------------------ workers: P / dS, then dQ drain ------------------------------
+    const int q = warp & 3;                   // TMEM lane quarter
+    const int half = (warp - 2) >> 2;         // which half of the key columns / of the dQ columns
     const int r = q * 32 + lane;
     const uint32_t lane_base = uint32_t(q * 32) << 16;
+    uint8_t* stg = sStg + (warp - 2) * STG;   // one staging buffer per worker
+    constexpr int CH = HD / 64;               // dQ chunks (32 columns) per worker
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
       const int h = hk * group + it / n_q;
@@ -229,12 +236,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int lo = p.window > 0 ? q_pos + off - p.window + 1 : 0;
       if (!mbar_wait(sdp_full, it & 1, abort_flag, p.status, 90)) { ok = false; break; }
       tc_fence_after();
-      // P / dS buffers are free once the previous iteration's MMAs have read them
-      if (it > 0 && !mbar_wait(dq_full, (it - 1) & 1, abort_flag, p.status, 91)) { ok = false; break; }
+      // the P / dS tiles are free: this warp waited for dq_full of the previous iteration in its drain step
       uint8_t* prow = sP + r * 128;
       uint8_t* drow = sdS + r * 128;
 #pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t s[32], d[32];
         tmem_ld_32x32b_x32(tm_S + lane_base + c * 32, s);
         tmem_ld_32x32b_x32(tm_dP + lane_base + c * 32, d);
@@ -245,7 +251,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const float2 a = ffma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, nl2);
-          float p0 = ex2_approx(a.x), p1 = ex2_approx(a.y);
+          float2 e;
+          if ((i & 6) == 6) e = ex2_poly2(a);
+          else e = make_float2(ex2_approx(a.x), ex2_approx(a.y));
+          float p0 = e.x, p1 = e.y;
           if (need_mask) {
             const int kp = kv0 + c * 32 + i;
             if (!row_ok || kp > hi || kp < lo) p0 = 0.f;
@@ -273,84 +282,67 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
+      // ---- dQ drain: this worker's half of the head dim ----
+      if (!mbar_wait(dq_full, it & 1, abort_flag, p.status, 95)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t v[CH][32];
+#pragma unroll
+      for (int cc = 0; cc < CH; ++cc) tmem_ld_32x32b_x32(tm_S + lane_base + (half * CH + cc) * 32, v[cc]);
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_drained);      // the accumulator may be overwritten by the next S
+#pragma unroll
+      for (int cc = 0; cc < CH; ++cc) {
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+        uint8_t* sb = stg + lane * 128;
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<uint4*>(sb + ((g ^ (lane & 7)) << 4)) =
+              make_uint4(v[cc][4 * g], v[cc][4 * g + 1], v[cc][4 * g + 2], v[cc][4 * g + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (q0 + q * 32 < p.Sq) tma_reduce_add_4d(&tmdQ, stg, (half * CH + cc) * 32, h, q0 + q * 32, b);
+          tma_store_commit();
+        }
+      }
     }
     // ------------------------------ dK / dV epilogue ------------------------------
+    // workers of half 0 write dK (staged in the P tile), those of half 1 write dV (staged in the dS tile)
     if (ok && n_iter > 0) ok = mbar_wait(acc_done, 0, abort_flag, p.status, 92);
     if (ok) {
       tc_fence_after();
-      // stage dK in the P buffer and dV in the dS buffer (both idle now), 32 rows per warp
+      uint8_t* tile = (half == 0) ? sP : sdS;
+      uint8_t* dst = tile + r * 128;
+      const uint32_t src = (half == 0 ? tm_dK : tm_dV) + lane_base;
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        uint8_t* dst = (which == 0 ? sP : sdS) + r * 128;
-        const uint32_t src = (which == 0 ? tm_dK : tm_dV) + lane_base;
-#pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t v[32];
-          if (n_iter > 0) { tmem_ld_32x32b_x32(src + c * 32, v); tc_wait_ld(); }
-          else {
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t v[32];
+        if (n_iter > 0) { tmem_ld_32x32b_x32(src + c * 32, v); tc_wait_ld(); }
+        else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0u;
-          }
-          uint8_t* blk = dst + (c / 2) * (BKV * 128);
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        uint8_t* blk = dst + (c / 2) * (BKV * 128);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int sw = (((c & 1) * 4 + g) ^ (r & 7)) << 4;
-            *reinterpret_cast<uint4*>(blk + sw) = make_uint4(
-                pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
-                pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
-                pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
-                pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
-          }
+        for (int g = 0; g < 4; ++g) {
+          const int sw = (((c & 1) * 4 + g) ^ (r & 7)) << 4;
+          *reinterpret_cast<uint4*>(blk + sw) = make_uint4(
+              pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
+              pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
+              pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
+              pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
         }
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0 && kv0 + q * 32 < p.Skv) {
 #pragma unroll
-        for (int i = 0; i < NB; ++i) {
-          tma_store_4d(&tmdK, sP + i * (BKV * 128) + q * 32 * 128, i * 64, hk, kv0 + q * 32, b);
-          tma_store_4d(&tmdV, sdS + i * (BKV * 128) + q * 32 * 128, i * 64, hk, kv0 + q * 32, b);
-        }
+        for (int i = 0; i < NB; ++i)
+          tma_store_4d(half == 0 ? &tmdK : &tmdV, tile + i * (BKV * 128) + q * 32 * 128, i * 64, hk, kv0 + q * 32, b);
         tma_store_commit();
-        tma_store_wait_all<0>();
-      }
-    }
-  } else {
-    // ------------------------------ dQ drain: TMEM -> fp32 reduce-add ------------------------------
-    const int q = warp & 3;
-    const int ew = warp - 6;
-    const uint32_t lane_base = uint32_t(q * 32) << 16;
-    uint8_t* stg = sStg + ew * 2 * STG;
-    int buf = 0;
-    bool ok = true;
-    for (int it = 0; it < n_iter && ok; ++it) {
-      const int h = hk * group + it / n_q;
-      const int q0 = (i_lo + it % n_q) * BQ;
-      if (!mbar_wait(dq_full, it & 1, abort_flag, p.status, 95)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t v[HD / 32][32];
-#pragma unroll
-      for (int c = 0; c < HD / 32; ++c) tmem_ld_32x32b_x32(tm_S + lane_base + c * 32, v[c]);
-      tc_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(dq_drained);
-#pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        if (lane == 0) tma_store_wait_read<1>();
-        __syncwarp();
-        uint8_t* sb = stg + buf * STG + lane * 128;
-#pragma unroll
-        for (int g = 0; g < 8; ++g)
-          *reinterpret_cast<uint4*>(sb + ((g ^ (lane & 7)) << 4)) =
-              make_uint4(v[c][4 * g], v[c][4 * g + 1], v[c][4 * g + 2], v[c][4 * g + 3]);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (q0 + q * 32 < p.Sq) tma_reduce_add_4d(&tmdQ, stg + buf * STG, c * 32, h, q0 + q * 32, b);
-          tma_store_commit();
-        }
-        buf ^= 1;
       }
     }
     if (lane == 0) tma_store_wait_all<0>();
