@@ -96,7 +96,7 @@ hstu_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 4); mbar_init(dq_full, 1); mbar_init(dq_drained, 4); mbar_init(acc_done, 1);
+    mbar_init(pds_full, 8); mbar_init(dq_full, 1); mbar_init(dq_drained, 8); mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -187,11 +187,16 @@ hstu_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       if (ok) tc_commit(acc_done);
     }
-  } else if (warp < 6) {
-    // ------------------------------ softmax: P and dS ------------------------------
+  } else {
+    // ------------------------------ workers (warps 2-9): P / dS, then dQ drain ------------------------------
+    // Two workers share a TMEM lane quarter: each handles half of the key columns, then half of the
+    // dQ columns (registers, accumulator released, fp32 TMA reduce-add while the next GEMMs run).
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = q * 32 + lane;
     const uint32_t lane_base = uint32_t(q * 32) << 16;
+    uint8_t* stg = sStg + (warp - 2) * STG;
+    constexpr int CH = HD / 64;
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
       const int h = hk;
@@ -203,12 +208,11 @@ hstu_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const bool need_mask = !plain || (kv0 + BKV - 1 > q0) || (kv0 + BKV > len) || (q0 + BQ > len);
       if (!mbar_wait(sdp_full, it & 1, abort_flag, p.status, 90)) { ok = false; break; }
       tc_fence_after();
-      // P / dS buffers are free once the previous iteration's MMAs have read them
-      if (it > 0 && !mbar_wait(dq_full, (it - 1) & 1, abort_flag, p.status, 91)) { ok = false; break; }
+      // the P / dS tiles are free: this warp waited for dq_full of the previous iteration in its drain step
       uint8_t* prow = sP + r * 128;
       uint8_t* drow = sdS + r * 128;
 #pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t s[32], d[32];
         tmem_ld_32x32b_x32(tm_S + lane_base + c * 32, s);
         tmem_ld_32x32b_x32(tm_dP + lane_base + c * 32, d);
@@ -253,70 +257,56 @@ hstu_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
-    }
-    // ------------------------------ dK / dV epilogue ------------------------------
-    if (ok && n_iter > 0) ok = mbar_wait(acc_done, 0, abort_flag, p.status, 92);
-    if (ok) {
-      tc_fence_after();
-      // guarded row stores: rows past the sequence end belong to the next sequence
-      const int k_pos = kv0 + r;
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        __nv_bfloat16* dst = (which == 0 ? p.dk : p.dv) + (long long)(row_base + k_pos) * (which == 0 ? p.dk_row : p.dv_row) + hk * HD;
-        const uint32_t src = (which == 0 ? tm_dK : tm_dV) + lane_base;
-#pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(src + c * 32, v);
-          tc_wait_ld();
-          if (k_pos < len) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g)
-              *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = make_uint4(
-                  pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
-                  pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
-                  pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
-                  pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
-          }
-        }
-      }
-    }
-  } else {
-    // ------------------------------ dQ drain: TMEM -> fp32 reduce-add ------------------------------
-    const int q = warp & 3;
-    const int ew = warp - 6;
-    const uint32_t lane_base = uint32_t(q * 32) << 16;
-    uint8_t* stg = sStg + ew * 2 * STG;
-    int buf = 0;
-    bool ok = true;
-    for (int it = 0; it < n_iter && ok; ++it) {
-      const int h = hk;
-      const int q0 = q_tile(it) * BQ;
+      // ---- dQ drain: this worker's half of the head dim ----
       if (!mbar_wait(dq_full, it & 1, abort_flag, p.status, 95)) { ok = false; break; }
       tc_fence_after();
-      uint32_t v[HD / 32][32];
+      uint32_t v[CH][32];
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) tmem_ld_32x32b_x32(tm_S + lane_base + c * 32, v[c]);
+      for (int cc = 0; cc < CH; ++cc) tmem_ld_32x32b_x32(tm_S + lane_base + (half * CH + cc) * 32, v[cc]);
       tc_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_drained);
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        if (lane == 0) tma_store_wait_read<1>();
+      for (int cc = 0; cc < CH; ++cc) {
+        if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
-        uint8_t* sb = stg + buf * STG + lane * 128;
+        uint8_t* sb = stg + lane * 128;
 #pragma unroll
         for (int g = 0; g < 8; ++g)
           *reinterpret_cast<uint4*>(sb + ((g ^ (lane & 7)) << 4)) =
-              make_uint4(v[c][4 * g], v[c][4 * g + 1], v[c][4 * g + 2], v[c][4 * g + 3]);
+              make_uint4(v[cc][4 * g], v[cc][4 * g + 1], v[cc][4 * g + 2], v[cc][4 * g + 3]);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (q0 + q * 32 < len) tma_reduce_add_3d(&tmdQ, stg + buf * STG, c * 32, h, row_base + q0 + q * 32);
+          if (q0 + q * 32 < len) tma_reduce_add_3d(&tmdQ, stg, (half * CH + cc) * 32, h, row_base + q0 + q * 32);
           tma_store_commit();
         }
-        buf ^= 1;
+      }
+    }
+    // ------------------------------ dK / dV epilogue ------------------------------
+    // workers of half 0 write dK, those of half 1 write dV; guarded row stores: rows past the
+    // sequence end belong to the next sequence
+    if (ok && n_iter > 0) ok = mbar_wait(acc_done, 0, abort_flag, p.status, 92);
+    if (ok) {
+      tc_fence_after();
+      const int k_pos = kv0 + r;
+      __nv_bfloat16* dst = (half == 0 ? p.dk : p.dv) + (long long)(row_base + k_pos) * (half == 0 ? p.dk_row : p.dv_row) + hk * HD;
+      const uint32_t src = (half == 0 ? tm_dK : tm_dV) + lane_base;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(src + c * 32, v);
+        tc_wait_ld();
+        if (k_pos < len) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = make_uint4(
+                pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
+                pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
+                pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
+                pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+        }
       }
     }
     if (lane == 0) tma_store_wait_all<0>();

@@ -162,20 +162,26 @@ class ZeroEngine:
             raise ValueError("ZeroEngine: the model has no trainable parameters")
         device = named[0][1].device
         groups: dict[str, list] = {}
+        main_dtype = max({p.dtype for _, p in named}, key=lambda d: sum(q.numel() for _, q in named if q.dtype == d))
         for n, p in named:
             # expert-parallel parameters exist on one rank only: their bucket is not sharded or reduced
             key = bucket_of(n) + ("_ep" if getattr(p, "expert_parallel", False) else "")
             if self.tp_world > 1 and getattr(p, "tensor_parallel", None) is not None:
                 key += "_tp"
+            if p.dtype != main_dtype:
+                # a flat buffer has one dtype: parameters kept in another one (fp32 router weights and
+                # sink logits inside a bf16 model) get a bucket of their own
+                key += "_" + str(p.dtype).split(".")[-1]
             groups.setdefault(key, []).append((n, p))
         self.buckets = []
         for k in sorted(groups):
-            local = k.endswith("_ep")
-            fused = comm == "fused" and self.world > 1 and not local and device.type == "cuda"
+            local = k.endswith("_ep") or "_ep_" in k
+            fused = (comm == "fused" and self.world > 1 and not local and device.type == "cuda"
+                     and groups[k][0][1].dtype == torch.bfloat16)      # the peer-memory step kernels move bf16 parameters
             b = Bucket(k, groups[k], 1 if local else self.world, 0 if local else self.rank, opt, device,
                        symmetric_group=(group if group is not None else dist.group.WORLD) if fused else None)
             b.local_only = local
-            b.tp_sharded = k.endswith("_tp")
+            b.tp_sharded = k.endswith("_tp") or "_tp_" in k
             self.buckets.append(b)
         self.device = device
         self.step_count = 0

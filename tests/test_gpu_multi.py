@@ -60,3 +60,10 @@ def test_pipeline_parallel_two_gpus():
     res = _run("pp_worker.py", args=("nccl",))
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "RESULT rank 0 ok=True" in res.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_moe_model_expert_parallel_fused_vs_nccl():
+    res = _run("moe_ep_worker.py")
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "RESULT rank 0 ok=True" in res.stdout
