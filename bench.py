@@ -48,6 +48,8 @@ def parse():
     ap.add_argument("--local-batch", type=int, default=4)
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="do not overlap the gradient reduce-scatter with the last micro-batch's backward")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
                     help="data-parallel step: in-kernel NVLink peer loads/stores, or NCCL collectives")
     ap.add_argument("--precision", default="mxfp8", choices=["mxfp8", "bf16"],
@@ -150,6 +152,7 @@ def main() -> int:
         trainer = BaselineTrainer(cfg, opt, tc, device)
     else:
         trainer = PretrainTrainer(cfg, opt, tc, device)
+        trainer.overlap_grad_reduce = not args.no_overlap
 
     K_, W_ = args.steps, args.warmup
     tokens_per_step = args.local_batch * cfg.seq_len * world
@@ -217,7 +220,8 @@ def main() -> int:
             "impl": args.impl,
             "config": {"model": cfg.name, "layers": cfg.n_layers, "global_batch": args.local_batch * world,
                        "seq_len": cfg.seq_len, "micro_batch": args.micro_batch,
-                       "parallelism": f"dp{world} (ZeRO-sharded optimizer, {args.comm if world > 1 else 'single GPU'} step)",
+                       "parallelism": f"dp{world} (ZeRO-sharded optimizer, {args.comm if world > 1 else 'single GPU'} step"
+                                      + (", reduce-scatter overlapped with backward)" if (world > 1 and not args.no_overlap) else ")"),
                        "l2": "no flush: per-step working set (>48 GB of weights and gradients) exceeds L2",
                        "reduced": reduced},
             "clocks": clocks, "gpu_launches": int(launches),

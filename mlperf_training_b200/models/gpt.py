@@ -277,6 +277,8 @@ class GPT(nn.Module):
         self.final_norm = nn.Parameter(torch.ones(cfg.hidden, dtype=dtype, device=device))
         self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden, dtype=dtype, device=device))
         self._rope = None
+        # optional callable(block_key): told when the backward of a block has produced all its gradients
+        self.grad_ready_hook = None
         self.reset_parameters(seed)
 
     @torch.no_grad()
@@ -335,7 +337,11 @@ class GPT(nn.Module):
             ids, tgt = ids[r * rows:(r + 1) * rows], tgt[r * rows:(r + 1) * rows]
         x = F.embedding(ids, self.embed)
         ckpt = self.cfg.recompute == "full" and torch.is_grad_enabled()
+        notify = self.grad_ready_hook if (torch.is_grad_enabled() and not ckpt) else None
         for i, blk in enumerate(self.blocks):
+            if notify is not None and x.requires_grad:
+                # the gradient w.r.t. a block's input is the last thing its backward produces
+                x.register_hook(lambda g, key=f"block{i:04d}", fn=notify: fn(key))
             if ckpt and (self.cfg.recompute_layers <= 0 or i < self.cfg.recompute_layers):
                 from torch.utils.checkpoint import checkpoint
                 x = checkpoint(blk, x, cos, sin, B, S, use_reentrant=False)

@@ -53,10 +53,14 @@ class MoEMLP(nn.Module):
     _shared: dict = {}
 
     def _fused_dispatcher(self, pairs: int, device):
-        """One set of slabs per (group, shape) serves every layer: each use copies its rows out of the
-        slab before the next layer touches it."""
-        key = (id(self.ep_group), self.cfg.n_experts, self.cfg.hidden, pairs, str(device))
-        d = MoEMLP._shared.get(key)
-        if d is None:
-            d = MoEMLP._shared[key] = FusedExpertDispatcher(self.ep_group, self.cfg.n_experts, self.cfg.hidden, pairs, device)
-        return d
+        """Every layer owns its input slab (it is read again in backward); the output and gradient
+        slabs of all layers of one (group, shape) are the same buffers."""
+        if self._fused is None or self._fused_pairs != pairs:
+            key = (id(self.ep_group), self.cfg.n_experts, self.cfg.hidden, pairs, str(device))
+            first = MoEMLP._shared.get(key)
+            self._fused = FusedExpertDispatcher(self.ep_group, self.cfg.n_experts, self.cfg.hidden, pairs, device,
+                                                share_with=first)
+            self._fused_pairs = pairs
+            if first is None:
+                MoEMLP._shared[key] = self._fused
+        return self._fused

@@ -188,6 +188,16 @@ class ZeroEngine:
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=device)
         self.sumsq_tp = torch.zeros(1, dtype=torch.float32, device=device)
         self.last_grad_norm = None
+        # gradient reduce-scatter overlapped with the last micro-batch's backward: a bucket is reduced on
+        # a side stream as soon as its block's gradients are complete (``on_block_grads_ready``)
+        self._overlap = False
+        self._comm_stream = None
+        self._by_block: dict[str, list[Bucket]] = {}
+        for b in self.buckets:
+            m = re.match(r"(block\d+|l\d+|[ds]\d+)", b.key)
+            if m and not getattr(b, "local_only", False):
+                self._by_block.setdefault(m.group(1), []).append(b)
+            b.rs_event = None
 
     # ------------------------------------------------------------------ info
     def num_params(self) -> int:
@@ -225,6 +235,55 @@ class ZeroEngine:
         else:
             dist.all_gather_into_tensor(b.param_buf, b.p_shard(), group=self.group)
 
+    # ------------------------------------------------------------------ overlap with backward
+    def begin_overlap(self) -> None:
+        """Call before the backward of the step's LAST micro-batch: from here on a block's bucket may be
+        reduced as soon as ``on_block_grads_ready`` is told that the block's backward has finished."""
+        self._overlap = self.world > 1 and self.device.type == "cuda"
+
+    def on_block_grads_ready(self, block_key: str) -> None:
+        if not self._overlap:
+            return
+        for b in self._by_block.get(block_key, []):
+            if b.rs_event is None:
+                self._launch_reduce_scatter(b)
+
+    def _fused_rs(self, b: Bucket, clip: bool) -> None:
+        from ..ops import _lib
+        if not hasattr(b, "rs_out"):
+            grid = _lib.load().b200_zero_grid()
+            b.rs_out = torch.empty(b.shard, dtype=torch.float32, device=self.device)
+            b.rs_partial = torch.empty(grid, dtype=torch.float32, device=self.device)
+        _lib.call("b200_zero_reduce_scatter", b.symm_grad.ptr_array(), self.world, self.rank, b.lo, b.shard,
+                  1.0 / self.world, _lib.ptr(b.rs_out), _lib.ptr(b.rs_partial) if clip else None, _lib.stream_ptr())
+
+    def _launch_reduce_scatter(self, b: Bucket) -> None:
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=self.device)
+        s = self._comm_stream
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            if self.tp_world > 1 and not b.tp_sharded:
+                dist.all_reduce(b.grad_buf, group=self.tp_group)
+            if b.symm_grad is not None:
+                b.symm_grad.barrier()            # every rank has finished this block's backward
+                self._fused_rs(b, self.opt.clip_grad > 0)
+            else:
+                self._reduce_scatter(b)
+            b.rs_event = torch.cuda.Event()
+            b.rs_event.record(s)
+
+    def _finish_overlap(self) -> set:
+        """Make the current stream wait for the reductions launched early; returns their buckets."""
+        done = set()
+        for b in self.buckets:
+            if b.rs_event is not None:
+                torch.cuda.current_stream().wait_event(b.rs_event)
+                b.rs_event = None
+                done.add(id(b))
+        self._overlap = False
+        return done
+
     # ------------------------------------------------------------------ step
     def zero_grad(self) -> None:
         for b in self.buckets:
@@ -236,26 +295,23 @@ class ZeroEngine:
         this package's kernels; NCCL only carries the scalar of the clipping norm."""
         from ..ops import _lib
         o = self.opt
-        lib = _lib.load()
+        early = self._finish_overlap()
         order = list(reversed(self.buckets))
         fused = [b for b in order if b.symm_grad is not None]
         if fused:
             fused[0].symm_grad.barrier()          # every rank's gradients are final
         clip = o.clip_grad > 0
-        grid = lib.b200_zero_grid()
         first = True
         for b in order:
             if b.symm_grad is None:
-                self._reduce_scatter(b)
+                if id(b) not in early:
+                    self._reduce_scatter(b)
                 if clip:
                     K.sumsq(b.g_shard(), self.sumsq, accumulate=not first)
                     first = False
                 continue
-            if not hasattr(b, "rs_out"):
-                b.rs_out = torch.empty(b.shard, dtype=torch.float32, device=self.device)
-                b.rs_partial = torch.empty(grid, dtype=torch.float32, device=self.device)
-            _lib.call("b200_zero_reduce_scatter", b.symm_grad.ptr_array(), self.world, self.rank, b.lo, b.shard,
-                      1.0 / self.world, _lib.ptr(b.rs_out), _lib.ptr(b.rs_partial) if clip else None, _lib.stream_ptr())
+            if id(b) not in early:
+                self._fused_rs(b, clip)
             if clip:
                 part = b.rs_partial.sum()
                 self.sumsq.copy_(part.view(1) if first else self.sumsq + part)
@@ -295,8 +351,11 @@ class ZeroEngine:
             if self.tp_world > 1:
                 raise NotImplementedError("comm='fused' of the optimizer step is not combined with tensor parallelism")
             return self._step_fused(lr, grad_scale)
+        early = self._finish_overlap()
         order = list(reversed(self.buckets))     # the order backward completes them
         for b in order:
+            if id(b) in early:
+                continue
             if self.tp_world > 1 and not b.tp_sharded:
                 dist.all_reduce(b.grad_buf, group=self.tp_group)
             self._reduce_scatter(b)

@@ -124,7 +124,8 @@ class FusedExpertDispatcher:
     balanced share) and pairs beyond it are dropped and counted in ``dropped``.
     """
 
-    def __init__(self, group, n_experts: int, hidden: int, max_pairs: int, device, capacity_factor: float = 2.0):
+    def __init__(self, group, n_experts: int, hidden: int, max_pairs: int, device, capacity_factor: float = 2.0,
+                 share_with: "FusedExpertDispatcher | None" = None):
         from .symm import SymmetricBuffer
         self.group = group
         self.world = dist.get_world_size(group)
@@ -133,8 +134,16 @@ class FusedExpertDispatcher:
         self.local = n_experts // self.world
         self.cap = (int(capacity_factor * max_pairs) + self.local * 128 + 127) // 128 * 128
         mk = lambda: SymmetricBuffer(self.cap * hidden, torch.bfloat16, group, device)
-        self.slab_x, self.slab_y, self.slab_dy, self.slab_dx = mk(), mk(), mk(), mk()
-        self.dropped = torch.zeros(1, dtype=torch.int32, device=device)
+        # The input slab is read again in backward (weight gradients), so every layer owns one; the
+        # output and gradient slabs are consumed right after they are filled and are shared between the
+        # layers that pass ``share_with``.
+        self.slab_x = mk()
+        if share_with is not None and share_with.cap == self.cap and share_with.D == hidden:
+            self.slab_y, self.slab_dy, self.slab_dx = share_with.slab_y, share_with.slab_dy, share_with.slab_dx
+            self.dropped = share_with.dropped
+        else:
+            self.slab_y, self.slab_dy, self.slab_dx = mk(), mk(), mk()
+            self.dropped = torch.zeros(1, dtype=torch.int32, device=device)
         self.device = device
 
     # ------------------------------------------------------------------ routing tables
@@ -172,7 +181,7 @@ class FusedExpertDispatcher:
         _lib.call("b200_scatter_rows_to_peers", _lib.ptr(rows), None, _lib.ptr(route.dst_rank), _lib.ptr(route.dst_row),
                   route.n, self.D, slab.ptr_array(), self.world, self.cap, _lib.ptr(self.dropped), _lib.stream_ptr())
         slab.barrier()                         # every rank's rows have landed
-        return slab.local.view(self.cap, self.D).clone()
+        return slab.local.view(self.cap, self.D)
 
     def _pull(self, slab_rows: torch.Tensor, route: _Route, slab) -> torch.Tensor:
         from ..ops import _lib

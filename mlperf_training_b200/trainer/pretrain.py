@@ -58,6 +58,7 @@ class PretrainTrainer:
         self.n_micro = train.local_batch // train.micro_batch
         self._staging = None
         self._masked = False
+        self.overlap_grad_reduce = True
 
     def lr(self) -> float:
         o, t = self.engine.opt, self.train_cfg
@@ -86,8 +87,14 @@ class PretrainTrainer:
         x_all, y_all = self._split(tokens, labels)
         total = None
         for i in range(self.n_micro):
+            last = i == self.n_micro - 1
+            if last and self.overlap_grad_reduce:
+                # reduce every block's gradients while the rest of this backward still runs
+                self.engine.begin_overlap()
+                self.model.grad_ready_hook = self.engine.on_block_grads_ready
             loss = self._loss(x_all[i * mb:(i + 1) * mb], y_all[i * mb:(i + 1) * mb])
             loss.backward()
+            self.model.grad_ready_hook = None
             d = loss.detach()
             total = d if total is None else total + d
         self.engine.step(self.lr(), grad_scale=1.0 / self.n_micro)
