@@ -112,10 +112,20 @@ class HSTUTrainer:
         self.eval_lookahead = True
         self.copy_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
         self._next = None
+        self._pool = None
 
     # ------------------------------------------------------------------ data prefetch
-    def _stage(self, step: int):
-        host = self.data.batch_at(step, self.rank, pin=self.device.type == "cuda")
+    def _build(self, step: int):
+        """Host side of a batch (numpy sampling, one pinned storage).  Runs on the loader thread."""
+        return self.data.batch_at(step, self.rank, pin=self.device.type == "cuda")
+
+    def _submit(self, step: int):
+        if self._pool is None:
+            from concurrent.futures import ThreadPoolExecutor
+            self._pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="hstu-loader")
+        return self._pool.submit(self._build, step)
+
+    def _to_device(self, host):
         if self.copy_stream is None:
             return host, None
         with torch.cuda.stream(self.copy_stream):
@@ -125,12 +135,17 @@ class HSTUTrainer:
         return dev, ev
 
     def _take(self, step: int):
+        """Batch ``step`` on the device.  Three stages overlap: the loader thread builds batch N+1 on the
+        host while the main thread launches step N, and N+1's H2D copy runs on the copy stream under
+        step N's kernels (the reference's data-loader workers + copy stream,
+        generative_recommenders/dlrm_v4/train/dd_own_h2d.py:65-168)."""
         if self._next is None or self._next[0] != step:
-            self._next = (step, *self._stage(step))
-        _, batch, ev = self._next
+            self._next = (step, self._submit(step))
+        host = self._next[1].result()
+        batch, ev = self._to_device(host)
         if ev is not None:
             torch.cuda.current_stream().wait_event(ev)       # only this batch's own H2D is awaited
-        self._next = (step + 1, *self._stage(step + 1))      # overlaps with the step below
+        self._next = (step + 1, self._submit(step + 1))      # built while this step runs
         return batch
 
     # ------------------------------------------------------------------ steps
