@@ -14,6 +14,8 @@
 // Replaces the reference's block-scaled GEMM providers: Primus-Turbo FlyDSL / AITER a4w4 kernels
 // (llama2_sft/primus/a4w4_tuned_gemms.csv) and the in-tree scaled-MFMA GEMMs
 // (generative_recommenders/ops/hip/k512_mx6_gemm.cu) at MXFP8 precision.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "runtime.h"
 
@@ -305,7 +307,20 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
 
 // N tile the kernel will use for an output width N (the B operand's scales must be laid out with
 // this tile height by the quantiser).
-B200_API int b200_gemm_mxfp8_bn(int N) { return N > 128 ? 224 : 128; }
+// 224 columns fill tensor memory (2 x 224 accumulator columns + scale columns <= 512) and give the
+// highest FLOP per byte staged; 128 divides power-of-two widths exactly, which wins when 224-wide tiles
+// leave a mostly empty last wave on the 148 SMs (B200_MXFP8_BN=128|224 forces one choice).
+static int pick_bn(int N) {
+  if (N <= 128) return 128;
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("B200_MXFP8_BN");
+    forced = e ? atoi(e) : 0;
+  }
+  if (forced == 128 || forced == 224) return forced;
+  return 224;
+}
+B200_API int b200_gemm_mxfp8_bn(int N) { return pick_bn(N); }
 
 // a_q [M, K] / b_q [N, K] e4m3 (row pitches lda / ldb in bytes), sfa / sfb scale atoms
 // (tile rows 128 for A, b200_gemm_mxfp8_bn(N) for B).  K must be a multiple of 128.
@@ -314,7 +329,7 @@ B200_API int b200_gemm_mxfp8(const void* a_q, const void* sfa, const void* b_q, 
                              const void* bias, const void* residual, long long ldr, float alpha, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return b200::fail(810, "gemm_mxfp8: empty problem %d x %d x %d", M, N, K);
   if (K % BK != 0) return b200::fail(811, "gemm_mxfp8: K=%d must be a multiple of %d", K, BK);
-  const int BN = N > 128 ? 224 : 128;
+  const int BN = pick_bn(N);
   CUtensorMap tmA, tmB, tmD;
   int r;
   if ((r = b200::make_tmap_2d(&tmA, b200::DT_U8, a_q, K, M, lda, BK, BM, b200::SWZ_128))) return r;
