@@ -137,7 +137,65 @@ __global__ void unpermute_sum_kernel(const __nv_bfloat16* __restrict__ yp, const
   }
 }
 
+// Backward of unpermute_sum, one warp per (token, slot) pair p:
+//   gyp[dest[p], :] = w[p] * gy[p / K, :]        (rows no pair maps to keep their previous content)
+//   gw[p]           = <gy[p / K, :], yp[dest[p], :]>
+__global__ void unpermute_bwd_kernel(const __nv_bfloat16* __restrict__ gy, const __nv_bfloat16* __restrict__ yp,
+                                     const int* __restrict__ dest, const float* __restrict__ w, long long pairs, int K,
+                                     int D, __nv_bfloat16* __restrict__ gyp, float* __restrict__ gw) {
+  const long long p = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (p >= pairs) return;
+  const long long t = p / K;
+  const long long row = dest[p];
+  const float s = w ? w[p] : 1.f;
+  const __nv_bfloat16* g = gy + t * D;
+  const __nv_bfloat16* y = yp + row * D;
+  __nv_bfloat16* o = gyp + row * D;
+  float dot = 0.f;
+  for (int v = lane; v < D / 8; v += 32) {
+    const uint4 a = *reinterpret_cast<const uint4*>(g + v * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(y + v * 8);
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+    const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
+    dot += a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y + a3.x * b3.x + a3.y * b3.y;
+    *reinterpret_cast<uint4*>(o + v * 8) =
+        make_uint4(pack_bf16x2(s * a0.x, s * a0.y), pack_bf16x2(s * a1.x, s * a1.y), pack_bf16x2(s * a2.x, s * a2.y),
+                   pack_bf16x2(s * a3.x, s * a3.y));
+  }
+  dot = warp_sum(dot);
+  if (lane == 0 && gw != nullptr) gw[p] = dot;
+}
+
+// rows of tiles that belong to no expert (tile_expert < 0) are cleared; 128 rows per tile
+__global__ void zero_dead_tiles_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ tile_expert, int D) {
+  const int tile = blockIdx.x;
+  if (tile_expert[tile] >= 0) return;
+  uint4* p = reinterpret_cast<uint4*>(buf + (long long)tile * 128 * D);
+  const int n = 128 * D / 8;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) p[i] = make_uint4(0, 0, 0, 0);
+}
+
 }  // namespace
+
+B200_API int b200_unpermute_bwd(const void* gy, const void* yp, const int* dest, const float* w, long long pairs, int K,
+                                int D, void* gyp, float* gw, void* stream) {
+  if (D % 8 != 0) return b200::fail(904, "unpermute_bwd: D=%d must be a multiple of 8", D);
+  if (pairs <= 0) return 0;
+  const long long threads = pairs * 32;
+  unpermute_bwd_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)gy, (const __nv_bfloat16*)yp, dest, w, pairs, K, D, (__nv_bfloat16*)gyp, gw);
+  b200::count_launch();
+  return b200::check_launch("unpermute_bwd");
+}
+
+B200_API int b200_zero_dead_tiles(void* buf, const int* tile_expert, int n_tiles, int D, void* stream) {
+  if (D % 8 != 0) return b200::fail(905, "zero_dead_tiles: D=%d must be a multiple of 8", D);
+  if (n_tiles <= 0) return 0;
+  zero_dead_tiles_kernel<<<n_tiles, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)buf, tile_expert, D);
+  b200::count_launch();
+  return b200::check_launch("zero_dead_tiles");
+}
 
 B200_API int b200_router_topk(const float* logits, int T, int E, int K, int* idx, float* w, int* counts, void* stream) {
   if (E > MAX_E || K > MAX_K || K > E) return b200::fail(900, "router_topk: E=%d (max %d), K=%d (max %d)", E, MAX_E, K, MAX_K);

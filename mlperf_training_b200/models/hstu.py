@@ -160,11 +160,13 @@ class STULayer(nn.Module):
         h = cfg.heads
         uvqk = F.norm_linear(x, self.in_norm_w, self.uvqk_weight, norm_b=self.in_norm_b, bias=self.uvqk_beta,
                              eps=1e-6, layer_norm=True, precision=cfg.precision)
-        s0, s1, s2, s3 = self.split
-        u = TF.silu(uvqk[:, :s0])
-        v = uvqk[:, s0:s0 + s1].unflatten(-1, (h, cfg.d_v))
-        q = uvqk[:, s0 + s1:s0 + s1 + s2].unflatten(-1, (h, cfg.d_qk))
-        k = uvqk[:, s0 + s1 + s2:].unflatten(-1, (h, cfg.d_qk))
+        # one split (its backward is a single concatenation; four slices would each build a zero-filled
+        # gradient of the whole uvqk matrix)
+        u_raw, v_raw, q_raw, k_raw = torch.split(uvqk, list(self.split), dim=1)
+        u = TF.silu(u_raw)
+        v = v_raw.unflatten(-1, (h, cfg.d_v))
+        q = q_raw.unflatten(-1, (h, cfg.d_qk))
+        k = k_raw.unflatten(-1, (h, cfg.d_qk))
         attn = hstu_attention(q, k, v, offsets, cfg.max_seq_len + cfg.contextual, cfg.d_qk ** -0.5, num_targets,
                               cfg.contextual).reshape(x.shape[0], h * cfg.d_v)
         y = u * F.layer_norm(attn, self.out_norm_w, self.out_norm_b, 1e-6)

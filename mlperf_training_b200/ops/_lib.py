@@ -70,6 +70,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_scatter_rows_to_peers": [P, P, P, P, L, I, P, I, L, P, P],
         "b200_gather_rows_from_peers": [P, P, P, L, I, P, I, L, P],
         "b200_zero_pad_rows": [P, P, P, I, I, L, P],
+        "b200_unpermute_bwd": [P, P, P, P, L, I, I, P, P, P],
+        "b200_zero_dead_tiles": [P, P, I, I, P],
         "b200_flag_wait_probe": [P, I, L, P, P],
         "b200_gemm_tp_gather": [P, P, P, I, I, I, L, L, L, I, I, I, I, F, I, P, I, I, P, L, I, P, I, I, P, P],
         "b200_gemm_tp_rs": [P, P, I, I, I, L, L, I, I, F, P, P, I, I, P, P, L, P, L, I, P],

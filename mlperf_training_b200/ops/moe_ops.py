@@ -196,6 +196,14 @@ class UnpermuteFn(Function):
         T, k = ctx.cfg
         D = yp.shape[1]
         gy = gy.contiguous()
+        if use_kernels(gy) and gy.dtype == torch.bfloat16 and yp.dtype == torch.bfloat16:
+            # one pass: scaled scatter of the gradient rows and the routing-weight gradient (a dot product per pair)
+            gyp = torch.zeros_like(yp)
+            gw32 = None if w is None else torch.empty(T * k, dtype=torch.float32, device=gy.device)
+            wf = None if w is None else w.reshape(-1).float().contiguous()
+            call("b200_unpermute_bwd", ptr(gy), ptr(yp.contiguous()), ptr(dest), ptr(wf), T * k, k, D, ptr(gyp), ptr(gw32),
+                 stream_ptr())
+            return gyp, None, (None if w is None else gw32.view(T, k).to(w.dtype)), None, None
         gyp = permute_rows(gy, dest, k, yp.shape[0])
         gw = None
         if w is not None:
@@ -242,10 +250,13 @@ def _zero_padding(t: torch.Tensor, tile_expert: torch.Tensor) -> torch.Tensor:
     """Rows of tiles past the last segment may hold stale memory: zero them so the weight-gradient
     contraction over whole tiles is exact (rows inside a segment's padding are already zero because
     they come from zero inputs)."""
+    if tile_expert.numel() * PAD != t.shape[0]:
+        return t
+    if use_kernels(t) and t.dtype == torch.bfloat16 and t.is_contiguous():
+        call("b200_zero_dead_tiles", ptr(t), ptr(tile_expert), tile_expert.numel(), t.shape[1], stream_ptr())   # in place
+        return t
     dead = (tile_expert < 0).repeat_interleave(PAD)
-    if dead.numel() == t.shape[0]:
-        t = t.masked_fill(dead[:, None], 0)
-    return t
+    return t.masked_fill(dead[:, None], 0)
 
 
 def _wgrad_into(param, dy, x, seg, E):
