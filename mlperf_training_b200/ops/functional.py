@@ -63,7 +63,7 @@ class LinearFn(Function):
         dy = dy.contiguous()
         dx, dw = L.backward(dy, saved, weight, ctx.precision, need_dx=ctx.needs_input_grad[0],
                             need_dw=weight.requires_grad and saved is not None)
-        db = _vec_grad(ctx.bias_ref, dy.float().sum(0)) if ctx.bias_ref is not None else None
+        db = _vec_grad(ctx.bias_ref, dy.sum(0, dtype=torch.float32)) if ctx.bias_ref is not None else None
         dres = dy if ctx.has_res and ctx.needs_input_grad[3] else None
         return dx, dw, db, dres, None
 
@@ -135,7 +135,7 @@ class NormLinearFn(Function):
                              need_dw=weight.requires_grad and saved is not None)
         del saved
         dx, dnw, dnb = K.norm_bwd(dxn, x, norm_w, norm_b, mean, rstd, layer_norm=layer_norm)
-        db = _vec_grad(ctx.refs[2], dy.float().sum(0)) if ctx.refs[2] is not None else None
+        db = _vec_grad(ctx.refs[2], dy.sum(0, dtype=torch.float32)) if ctx.refs[2] is not None else None
         return dx, _vec_grad(ctx.refs[0], dnw), _vec_grad(ctx.refs[1], dnb), dw, db, None, None, None
 
 
