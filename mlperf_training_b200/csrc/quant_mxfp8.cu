@@ -72,10 +72,51 @@ B200_DEVICE uint2 quant8(const float (&f)[8], float inv) {
 //   column pass: 8 lanes walk one column (16 rows each, amax of a 32-block = one shuffle) and write the
 //                column's 128 codes as one contiguous 128-byte piece of the transposed copy.
 //   scales:      staged in shared memory and written as one 32-bit word per operand row.
+//
+// MODE selects what the tile is made of (the values are rounded to bf16 first, so the codes equal
+// those of quantising the stand-alone kernel's bf16 output):
+//   0  x[r, c]
+//   1  SwiGLU forward   a[r, c]   = silu(gu[r, c]) * gu[r, F + c],          x = gu [R, 2F], C = F
+//   2  SwiGLU backward  dgu[r, c] = da * up * silu'(gate)  for c <  F
+//                                 = da * silu(gate)        for c >= F,      x = gu [R, 2F], aux = da [R, F], C = 2F
+template <int MODE>
+B200_DEVICE uint4 produce8(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ aux,
+                           long long ldaux, int F, long long row, int col) {
+  if constexpr (MODE == 0) {
+    return *reinterpret_cast<const uint4*>(x + row * ldx + col);
+  } else {
+    const int cc = (MODE == 2 && col >= F) ? col - F : col;
+    const uint4 ug = *reinterpret_cast<const uint4*>(x + row * ldx + cc);
+    const uint4 uu = *reinterpret_cast<const uint4*>(x + row * ldx + F + cc);
+    const float2 g0 = unpack_bf16x2(ug.x), g1 = unpack_bf16x2(ug.y), g2 = unpack_bf16x2(ug.z), g3 = unpack_bf16x2(ug.w);
+    const float2 u0 = unpack_bf16x2(uu.x), u1 = unpack_bf16x2(uu.y), u2 = unpack_bf16x2(uu.z), u3 = unpack_bf16x2(uu.w);
+    const float g[8] = {g0.x, g0.y, g1.x, g1.y, g2.x, g2.y, g3.x, g3.y};
+    const float u[8] = {u0.x, u0.y, u1.x, u1.y, u2.x, u2.y, u3.x, u3.y};
+    float o[8];
+    if constexpr (MODE == 1) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    } else {
+      const uint4 ud = *reinterpret_cast<const uint4*>(aux + row * ldaux + cc);
+      const float2 d0 = unpack_bf16x2(ud.x), d1 = unpack_bf16x2(ud.y), d2 = unpack_bf16x2(ud.z), d3 = unpack_bf16x2(ud.w);
+      const float d[8] = {d0.x, d0.y, d1.x, d1.y, d2.x, d2.y, d3.x, d3.y};
+      const bool up_part = col >= F;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float sg = 1.f / (1.f + __expf(-g[j]));
+        o[j] = up_part ? d[j] * (g[j] * sg) : d[j] * u[j] * sg * (1.f + g[j] * (1.f - sg));
+      }
+    }
+    return make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]), pack_bf16x2(o[4], o[5]), pack_bf16x2(o[6], o[7]));
+  }
+}
+
+template <int MODE>
 __global__ void __launch_bounds__(256, 4)
 quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, int C, uint8_t* __restrict__ q_row,
                    uint8_t* __restrict__ sf_row, int row_tile, uint8_t* __restrict__ q_col,
-                   uint8_t* __restrict__ sf_col, int col_tile) {
+                   uint8_t* __restrict__ sf_col, int col_tile, const __nv_bfloat16* __restrict__ aux, long long ldaux,
+                   int F) {
   __shared__ __align__(16) __nv_bfloat16 tile[TILE * PITCH + 32];
   __shared__ __align__(4) uint8_t sfs[2][TILE][4];     // [row pass | column pass][operand row][scale column]
   const int c0 = blockIdx.x * TILE, r0 = blockIdx.y * TILE;
@@ -85,7 +126,7 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, in
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
     const int r = it * 16 + warp * 2 + sub_row;
-    v[it] = *reinterpret_cast<const uint4*>(x + (long long)(r0 + r) * ldx + c0 + chunk * 8);
+    v[it] = produce8<MODE>(x, ldx, aux, ldaux, F, (long long)(r0 + r), c0 + chunk * 8);
   }
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
@@ -161,9 +202,38 @@ B200_API int b200_quant_mxfp8(const void* x, long long ldx, int R, int C, void* 
   if ((q_row && (row_tile % 32 != 0 || row_tile <= 0)) || (q_col && (col_tile % 32 != 0 || col_tile <= 0)))
     return b200::fail(702, "quant_mxfp8: tile rows must be positive multiples of 32");
   dim3 grid(C / 128, R / 128);
-  quant_mxfp8_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, R, C, (uint8_t*)q_row,
-                                                            (uint8_t*)sf_row, row_tile, (uint8_t*)q_col,
-                                                            (uint8_t*)sf_col, col_tile);
+  quant_mxfp8_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, R, C, (uint8_t*)q_row,
+                                                               (uint8_t*)sf_row, row_tile, (uint8_t*)q_col,
+                                                               (uint8_t*)sf_col, col_tile, nullptr, 0, 0);
   b200::count_launch();
   return b200::check_launch("quant_mxfp8");
+}
+
+// Quantised SwiGLU: the codes / scales of a = silu(gate) * up without writing a.
+//   gu: bf16 [R, 2F] (gate columns first), pitch ldgu.  Outputs as b200_quant_mxfp8 for the matrix a [R, F].
+B200_API int b200_quant_swiglu_mxfp8(const void* gu, long long ldgu, int R, int F, void* q_row, void* sf_row, int row_tile,
+                                     void* q_col, void* sf_col, int col_tile, void* stream) {
+  if (R % 128 != 0 || F % 128 != 0) return b200::fail(710, "quant_swiglu: R=%d and F=%d must be multiples of 128", R, F);
+  if (ldgu % 8 != 0 || ((uintptr_t)gu & 15) != 0) return b200::fail(711, "quant_swiglu: input must be 16-byte aligned");
+  dim3 grid(F / 128, R / 128);
+  quant_mxfp8_kernel<1><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, ldgu, R, F, (uint8_t*)q_row,
+                                                               (uint8_t*)sf_row, row_tile, (uint8_t*)q_col,
+                                                               (uint8_t*)sf_col, col_tile, nullptr, 0, F);
+  b200::count_launch();
+  return b200::check_launch("quant_swiglu_mxfp8");
+}
+
+// Quantised SwiGLU backward: the codes / scales of dgu [R, 2F] (d gate | d up) from da [R, F] and gu [R, 2F].
+B200_API int b200_quant_swiglu_bwd_mxfp8(const void* da, long long ldda, const void* gu, long long ldgu, int R, int F,
+                                         void* q_row, void* sf_row, int row_tile, void* q_col, void* sf_col, int col_tile,
+                                         void* stream) {
+  if (R % 128 != 0 || F % 128 != 0) return b200::fail(712, "quant_swiglu_bwd: R=%d and F=%d must be multiples of 128", R, F);
+  if (ldgu % 8 != 0 || ldda % 8 != 0 || (((uintptr_t)gu | (uintptr_t)da) & 15) != 0)
+    return b200::fail(713, "quant_swiglu_bwd: inputs must be 16-byte aligned");
+  dim3 grid(2 * F / 128, R / 128);
+  quant_mxfp8_kernel<2><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, ldgu, R, 2 * F, (uint8_t*)q_row,
+                                                               (uint8_t*)sf_row, row_tile, (uint8_t*)q_col,
+                                                               (uint8_t*)sf_col, col_tile, (const __nv_bfloat16*)da, ldda, F);
+  b200::count_launch();
+  return b200::check_launch("quant_swiglu_bwd_mxfp8");
 }

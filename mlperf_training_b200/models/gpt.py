@@ -167,6 +167,7 @@ class DenseMLP(nn.Module):
                 raise ValueError(f"ffn_hidden {f} is not divisible by the tensor-parallel size {self.tp.world}")
             f //= self.tp.world
         self.precision = cfg.precision
+        self.fused = True               # MXFP8: one unit with the quantisation folded into SwiGLU / dSwiGLU
         self.w_gate_up = nn.Parameter(torch.empty(2 * f, d, dtype=dtype, device=device))
         self.w_down = nn.Parameter(torch.empty(d, f, dtype=dtype, device=device))
         if self.tp is not None:
@@ -178,6 +179,8 @@ class DenseMLP(nn.Module):
             from ..parallel import tensor as T
             gu = T.column_parallel(F.rms_norm(h, norm_w, eps), self.w_gate_up, self.tp)
             return T.row_parallel(F.swiglu(gu), self.w_down, self.tp, residual=h)
+        if self.precision == "mxfp8" and self.fused and F.fused_mlp_eligible(h, self.w_gate_up, self.w_down):
+            return F.fused_mlp(h, norm_w, self.w_gate_up, self.w_down, eps)
         gu = F.norm_linear(h, norm_w, self.w_gate_up, eps=eps, precision=self.precision)
         return F.swiglu_linear(gu, self.w_down, residual=h, precision=self.precision)
 

@@ -72,6 +72,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_zero_pad_rows": [P, P, P, I, I, L, P],
         "b200_unpermute_bwd": [P, P, P, P, L, I, I, P, P, P],
         "b200_zero_dead_tiles": [P, P, I, I, P],
+        "b200_quant_swiglu_mxfp8": [P, L, I, I, P, P, I, P, P, I, P],
+        "b200_quant_swiglu_bwd_mxfp8": [P, L, P, L, I, I, P, P, I, P, P, I, P],
         "b200_flag_wait_probe": [P, I, L, P, P],
         "b200_gemm_tp_gather": [P, P, P, I, I, I, L, L, L, I, I, I, I, F, I, P, I, I, P, L, I, P, I, I, P, P],
         "b200_gemm_tp_rs": [P, P, I, I, I, L, L, I, I, F, P, P, I, I, P, P, L, P, L, I, P],

@@ -170,6 +170,84 @@ def swiglu_linear(gu, weight, residual=None, precision="bf16"):
     return SwiGLULinearFn.apply(gu, weight, residual, precision)
 
 
+def _mx_wgrad(weight, dy_col, x_col):
+    """dW = dy^T x from the transposed MXFP8 copies, into ``main_grad`` when the parameter has one."""
+    from . import mxfp8 as MX
+    if not weight.requires_grad:
+        return None
+    mg = getattr(weight, "main_grad", None)
+    if mg is not None:
+        MX.gemm(dy_col, x_col, out=mg, accumulate=True)
+        return None
+    return MX.gemm(dy_col, x_col, out_dtype=weight.dtype)
+
+
+class FusedMLPFn(Function):
+    """RMSNorm -> gate/up GEMM -> SwiGLU -> down GEMM (+ residual) as one MXFP8 unit.
+
+    The activation ``a = silu(gate) * up`` and its gradient ``dgu`` never exist in bf16: the
+    quantiser computes them on the fly (``quantize_swiglu`` / ``quantize_swiglu_bwd``) and writes only
+    the e4m3 copies the GEMMs read.  Saved for backward: the block input, the normalisation
+    statistics, ``gu`` and the transposed fp8 copy of the normalised input.  This is the reference's
+    fused dense MLP with the quantisation and dGLU folded in
+    (small_llm_pretraining/primus/config_MI355X_1x8x1.sh:42-51)."""
+
+    @staticmethod
+    def forward(ctx, h, norm_w, w_gu, w_down, eps):
+        from . import mxfp8 as MX
+        D = h.shape[1]
+        xn, _, mean, rstd = K.norm_fwd(h, norm_w, None, eps, layer_norm=False)
+        need1 = w_gu.requires_grad
+        w1_row, _ = L.weight_operands(w_gu, need_col=False)
+        xn_row, xn_col = MX.quantize(xn, row_tile=MX.A_TILE, col_tile=MX.b_tile(D) if need1 else None)
+        del xn
+        gu = MX.gemm(xn_row, w1_row, out_dtype=h.dtype)
+        a_row, _ = MX.quantize_swiglu(gu, row_tile=MX.A_TILE)
+        w2_row, _ = L.weight_operands(w_down, need_col=False)
+        out = MX.gemm(a_row, w2_row, residual=h, out_dtype=h.dtype)
+        tensors, ctx.meta = L.Saved.pack(xn_col) if xn_col is not None else ([], None)
+        ctx.save_for_backward(h, norm_w, w_gu, w_down, mean, rstd, gu, *tensors)
+        ctx.eps = eps
+        ctx.refs = (norm_w, w_gu, w_down)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import mxfp8 as MX
+        h, norm_w, w_gu, w_down, mean, rstd, gu, *tensors = ctx.saved_tensors
+        p_norm, p_gu, p_down = ctx.refs
+        dy = dy.contiguous()
+        F_ = w_down.shape[1]
+        need1, need2 = p_gu.requires_grad and ctx.meta is not None, p_down.requires_grad
+        dy_row, dy_col = MX.quantize(dy, row_tile=MX.A_TILE, col_tile=MX.A_TILE if need2 else None)
+        _, w2_col = L.weight_operands(w_down, need_col=True)
+        da = MX.gemm(dy_row, w2_col, out_dtype=dy.dtype)
+        dw2 = None
+        if need2:
+            _, a_col = MX.quantize_swiglu(gu, col_tile=MX.b_tile(F_))
+            dw2 = _mx_wgrad(p_down, dy_col, a_col)
+            del a_col
+        dgu_row, dgu_col = MX.quantize_swiglu_bwd(da, gu, row_tile=MX.A_TILE, col_tile=MX.A_TILE if need1 else None)
+        del da
+        _, w1_col = L.weight_operands(w_gu, need_col=True)
+        dxn = MX.gemm(dgu_row, w1_col, out_dtype=dy.dtype)
+        dw1 = _mx_wgrad(p_gu, dgu_col, L.Saved.unpack(tensors, ctx.meta)) if need1 else None
+        dx, dnw, _ = K.norm_bwd(dxn, h, norm_w, None, mean, rstd, layer_norm=False, dres=dy)
+        return dx, _vec_grad(p_norm, dnw), dw1, dw2, None
+
+
+def fused_mlp_eligible(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor) -> bool:
+    T, D = h.shape
+    F2 = w_gu.shape[0]
+    return (h.is_cuda and h.dtype == torch.bfloat16 and T % 128 == 0 and D % 128 == 0 and F2 % 256 == 0
+            and L.mx_eligible(T, F2, D) and L.mx_eligible(T, D, F2 // 2))
+
+
+def fused_mlp(h, norm_w, w_gate_up, w_down, eps=1e-5):
+    """``h + swiglu(rmsnorm(h) W_gu^T) W_down^T`` with MXFP8 GEMMs."""
+    return FusedMLPFn.apply(h, norm_w, w_gate_up, w_down, eps)
+
+
 class SwiGLUFn(Function):
     @staticmethod
     def forward(ctx, gu):

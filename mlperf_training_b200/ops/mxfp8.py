@@ -139,6 +139,54 @@ def quantize(x: torch.Tensor, *, row_tile: int | None = None, col_tile: int | No
     return row_op, col_op
 
 
+def _alloc_ops(R: int, C: int, row_tile, col_tile, dev):
+    q_row = sf_row = q_col = sf_col = None
+    if row_tile is not None:
+        q_row = torch.empty((R, C), dtype=torch.uint8, device=dev)
+        n = sf_bytes(R, C, row_tile)
+        sf_row = torch.zeros(n, dtype=torch.uint8, device=dev) if row_tile % 128 else torch.empty(n, dtype=torch.uint8, device=dev)
+    if col_tile is not None:
+        q_col = torch.empty((C, R), dtype=torch.uint8, device=dev)
+        n = sf_bytes(C, R, col_tile)
+        sf_col = torch.zeros(n, dtype=torch.uint8, device=dev) if col_tile % 128 else torch.empty(n, dtype=torch.uint8, device=dev)
+    return q_row, sf_row, q_col, sf_col
+
+
+def quantize_swiglu(gu: torch.Tensor, *, row_tile: int | None = None, col_tile: int | None = None):
+    """Quantised ``a = silu(gate) * up`` of ``gu [R, 2F]`` (gate columns first) without materialising
+    ``a``: same return value as ``quantize(swiglu(gu), ...)``."""
+    R, F2 = gu.shape
+    F = F2 // 2
+    if not use_kernels(gu):
+        from . import kernels as K
+        return quantize(K.swiglu_fwd(gu), row_tile=row_tile, col_tile=col_tile)
+    if gu.stride(1) != 1 or (gu.stride(0) * 2) % 16 or gu.data_ptr() % 16:
+        gu = gu.contiguous()
+    q_row, sf_row, q_col, sf_col = _alloc_ops(R, F, row_tile, col_tile, gu.device)
+    call("b200_quant_swiglu_mxfp8", ptr(gu), gu.stride(0), R, F, ptr(q_row), ptr(sf_row), row_tile or 0, ptr(q_col),
+         ptr(sf_col), col_tile or 0, stream_ptr())
+    return (MXOperand(q_row, sf_row, R, F, row_tile) if row_tile is not None else None,
+            MXOperand(q_col, sf_col, F, R, col_tile) if col_tile is not None else None)
+
+
+def quantize_swiglu_bwd(da: torch.Tensor, gu: torch.Tensor, *, row_tile: int | None = None, col_tile: int | None = None):
+    """Quantised ``dgu [R, 2F]`` (d gate | d up) from ``da [R, F]`` and ``gu [R, 2F]`` without
+    materialising it: same return value as ``quantize(swiglu_bwd(da, gu), ...)``."""
+    R, F2 = gu.shape
+    F = F2 // 2
+    if not use_kernels(gu):
+        from . import kernels as K
+        return quantize(K.swiglu_bwd(da, gu), row_tile=row_tile, col_tile=col_tile)
+    da = da if (da.stride(1) == 1 and (da.stride(0) * 2) % 16 == 0 and da.data_ptr() % 16 == 0) else da.contiguous()
+    if gu.stride(1) != 1 or (gu.stride(0) * 2) % 16 or gu.data_ptr() % 16:
+        gu = gu.contiguous()
+    q_row, sf_row, q_col, sf_col = _alloc_ops(R, F2, row_tile, col_tile, gu.device)
+    call("b200_quant_swiglu_bwd_mxfp8", ptr(da), da.stride(0), ptr(gu), gu.stride(0), R, F, ptr(q_row), ptr(sf_row),
+         row_tile or 0, ptr(q_col), ptr(sf_col), col_tile or 0, stream_ptr())
+    return (MXOperand(q_row, sf_row, R, F2, row_tile) if row_tile is not None else None,
+            MXOperand(q_col, sf_col, F2, R, col_tile) if col_tile is not None else None)
+
+
 def gemm(a: MXOperand, b: MXOperand, *, out: torch.Tensor | None = None, out_dtype=torch.bfloat16,
          accumulate: bool = False, bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
          alpha: float = 1.0) -> torch.Tensor:

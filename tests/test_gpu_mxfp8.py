@@ -68,3 +68,31 @@ def test_gemm_mxfp8_epilogues():
     assert (d.float() - (0.5 * ref + res.float() + bias.float())).abs().max().item() < 2e-2 * sc
     assert (acc - (2 * ref + 1)).abs().max().item() < 2e-3 * sc
     _lib.check_status("gemm_mxfp8 epilogues")
+
+
+def test_fused_mlp_matches_unfused_mxfp8_path():
+    """The fused unit (quantisation folded into SwiGLU / dSwiGLU) computes exactly what the separate
+    norm_linear + swiglu_linear MXFP8 path computes."""
+    import torch
+    from mlperf_training_b200.ops import functional as F
+    torch.manual_seed(0)
+    T, D, Fh = 512, 256, 512
+    h0 = torch.randn(T, D, device="cuda").bfloat16()
+    nw0 = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16()
+    w1_0 = (torch.randn(2 * Fh, D, device="cuda") * 0.05).bfloat16()
+    w2_0 = (torch.randn(D, Fh, device="cuda") * 0.05).bfloat16()
+    dy = torch.randn(T, D, device="cuda").bfloat16()
+    outs = []
+    for fused in (False, True):
+        h, nw, w1, w2 = (t.clone().requires_grad_(True) for t in (h0, nw0, w1_0, w2_0))
+        assert F.fused_mlp_eligible(h, w1, w2)
+        if fused:
+            y = F.fused_mlp(h, nw, w1, w2, 1e-5)
+        else:
+            gu = F.norm_linear(h, nw, w1, eps=1e-5, precision="mxfp8")
+            y = F.swiglu_linear(gu, w2, residual=h, precision="mxfp8")
+        y.backward(dy)
+        outs.append([t.detach().float() for t in (y, h.grad, nw.grad, w1.grad, w2.grad)])
+    torch.cuda.synchronize()
+    for name, a, b in zip(("y", "dh", "dnorm", "dw1", "dw2"), outs[0], outs[1]):
+        assert torch.equal(a, b), (name, (a - b).abs().max().item())
