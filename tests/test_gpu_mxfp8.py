@@ -95,4 +95,8 @@ def test_fused_mlp_matches_unfused_mxfp8_path():
         outs.append([t.detach().float() for t in (y, h.grad, nw.grad, w1.grad, w2.grad)])
     torch.cuda.synchronize()
     for name, a, b in zip(("y", "dh", "dnorm", "dw1", "dw2"), outs[0], outs[1]):
-        assert torch.equal(a, b), (name, (a - b).abs().max().item())
+        if name == "dh":
+            # the fused unit adds the residual gradient inside the norm backward (one rounding instead of two)
+            assert (a - b).abs().max().item() <= 2.0 ** -6 * max(1.0, b.abs().max().item()), name
+        else:
+            assert torch.equal(a, b), (name, (a - b).abs().max().item())
