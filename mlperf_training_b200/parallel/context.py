@@ -83,3 +83,63 @@ def context_parallel_attention(q, k, v, group, *, scale: float | None = None, wi
         from ..ops.functional import attention
         return attention(q, k, v, causal=True, window=window, scale=scale)
     return ContextParallelAttentionFn.apply(q, k, v, group, scale, window)
+
+
+# --------------------------------------------------------------------------------------
+# Ulysses-style sequence parallelism: exchange sequence shards for head shards around attention
+# --------------------------------------------------------------------------------------
+class _SeqToHeads(Function):
+    """``[B, S/W, H, D]`` (all heads, this rank's sequence chunk) -> ``[B, S, H/W, D]`` (whole
+    sequence, this rank's heads) with one all-to-all; backward is the inverse exchange."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _a2a_seq_heads(x, group, to_heads=True)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _a2a_seq_heads(g.contiguous(), ctx.group, to_heads=False), None
+
+
+class _HeadsToSeq(Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _a2a_seq_heads(x, group, to_heads=False)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _a2a_seq_heads(g.contiguous(), ctx.group, to_heads=True), None
+
+
+def _a2a_seq_heads(x: torch.Tensor, group, to_heads: bool) -> torch.Tensor:
+    W = dist.get_world_size(group)
+    B, s, H, D = x.shape
+    if to_heads:
+        if H % W:
+            raise ValueError(f"{H} heads do not divide over {W} ranks")
+        # piece j (heads of rank j) of my sequence chunk goes to rank j; I receive chunk i of my heads from rank i
+        send = x.view(B, s, W, H // W, D).permute(2, 0, 1, 3, 4).contiguous()          # [W, B, s, H/W, D]
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)
+        return recv.permute(1, 0, 2, 3, 4).reshape(B, W * s, H // W, D)                  # chunks in rank order = sequence order
+    S = s                                                                                 # here x is [B, S, H/W, D]
+    send = x.view(B, W, S // W, H, D).permute(1, 0, 2, 3, 4).contiguous()                # [W, B, S/W, h, D]: chunk i -> rank i
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.permute(1, 2, 0, 3, 4).reshape(B, S // W, W * H, D)                      # heads of rank j in slot j
+
+
+def ulysses_attention(q, k, v, group, *, causal: bool = False, window: int = 0, scale: float | None = None) -> torch.Tensor:
+    """Attention over a sequence sharded across ``group`` by exchanging the sharded dimension: two
+    all-to-alls turn (all heads, S/W tokens) into (H/W heads, all tokens), the local flash-attention
+    kernel runs on whole sequences, and one all-to-all brings the output back.  Needs the number of
+    query and of key/value heads to be divisible by the group size (the ``sp_size`` knob of the
+    reference's diffusion trainer, flux1/primus/conf/flux.1_schnell_t2i-pretrain.yaml:48)."""
+    from ..ops.functional import attention
+    if group is None or dist.get_world_size(group) == 1:
+        return attention(q, k, v, causal=causal, window=window, scale=scale)
+    qh, kh, vh = (_SeqToHeads.apply(t.contiguous(), group) for t in (q, k, v))
+    oh = attention(qh, kh, vh, causal=causal, window=window, scale=scale)
+    return _HeadsToSeq.apply(oh.contiguous(), group)

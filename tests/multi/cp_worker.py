@@ -8,7 +8,7 @@ import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 from mlperf_training_b200.ops.functional import attention  # noqa: E402
-from mlperf_training_b200.parallel.context import context_parallel_attention  # noqa: E402
+from mlperf_training_b200.parallel.context import context_parallel_attention, ulysses_attention  # noqa: E402
 
 
 def main():
@@ -41,6 +41,24 @@ def main():
             ok &= err <= tol * max(1.0, b.float().abs().max().item())
             if rank == 0:
                 print(f"window {window} {name}: {err:.3e}", flush=True)
+    # Ulysses exchange (sequence shards <-> head shards), non-causal and causal
+    if Hkv % world == 0:
+        for causal in (False, True):
+            qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+            ref = attention(qf, kf, vf, causal=causal)
+            ref.backward(do)
+            s = S // world
+            sl = slice(rank * s, (rank + 1) * s)
+            ql, kl, vl = (t[:, sl].clone().requires_grad_(True) for t in (q, k, v))
+            out = ulysses_attention(ql, kl, vl, dist.group.WORLD, causal=causal)
+            out.backward(do[:, sl])
+            tol = 3e-2 if gpu else 1e-5
+            for name, a, b in (("o", out, ref[:, sl]), ("dq", ql.grad, qf.grad[:, sl]), ("dk", kl.grad, kf.grad[:, sl]),
+                               ("dv", vl.grad, vf.grad[:, sl])):
+                err = (a.float() - b.float()).abs().max().item()
+                ok &= err <= tol * max(1.0, b.float().abs().max().item())
+                if rank == 0:
+                    print(f"ulysses causal={causal} {name}: {err:.3e}", flush=True)
     print(f"RESULT rank {rank} ok={ok}", flush=True)
     dist.barrier()
     dist.destroy_process_group()

@@ -52,9 +52,10 @@ def test_stage_layer_split():
     assert sum(len(stage_layers(80, 8, s)) for s in range(8)) == 80
 
 
-def test_context_parallel_attention_gloo():
+@pytest.mark.parametrize("world", [3, 2])          # world 2 divides the 2 kv heads: the Ulysses exchange runs too
+def test_context_parallel_attention_gloo(world):
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3",
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                         "--master-addr", "127.0.0.1", "--master-port", "29658",
                         os.path.join(ROOT, "tests", "multi", "cp_worker.py"), "gloo"],
                        env=env, capture_output=True, text=True, timeout=600)
