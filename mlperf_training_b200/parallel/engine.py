@@ -143,7 +143,7 @@ class ZeroEngine:
     def __init__(self, model: nn.Module, opt: OptimConfig, *, group: dist.ProcessGroup | None = None,
                  bucket_of: Callable[[str], str] = default_bucket_of, comm: str = "nccl",
                  trainable_only: bool = True, tp_group: dist.ProcessGroup | None = None,
-                 pp_group: dist.ProcessGroup | None = None):
+                 pp_group: dist.ProcessGroup | None = None, replicate_group: dist.ProcessGroup | None = None):
         self.model = model
         self.opt = opt
         self.group = group
@@ -154,6 +154,9 @@ class ZeroEngine:
         # rank of ``tp_group``; all others are replicated over it and their gradients (each rank saw
         # its own block of token rows) are summed over the group before the data-parallel reduction
         self.tp_group = tp_group
+        # hybrid sharding (HSDP): ``group`` shards the optimizer state, ``replicate_group`` holds copies of
+        # the same shard; the reduced gradient shard is averaged across the replicas as well
+        self.replicate_group = replicate_group if (replicate_group is not None and dist.get_world_size(replicate_group) > 1) else None
         # pipeline parallelism: every stage owns different parameters; only the clipping norm is shared
         self.pp_group = pp_group if (pp_group is not None and dist.get_world_size(pp_group) > 1) else None
         self.tp_world = dist.get_world_size(tp_group) if tp_group is not None else 1
@@ -224,6 +227,9 @@ class ZeroEngine:
             b.grad_buf.div_(self.world)
         else:
             dist.reduce_scatter_tensor(b.g_shard(), b.grad_buf, op=dist.ReduceOp.AVG, group=self.group)
+        if self.replicate_group is not None:
+            dist.all_reduce(b.g_shard(), group=self.replicate_group)
+            b.g_shard().div_(dist.get_world_size(self.replicate_group))
 
     def _all_gather(self, b: Bucket) -> None:
         if self.world == 1 or getattr(b, "local_only", False):
@@ -348,6 +354,8 @@ class ZeroEngine:
         lr = o.lr if lr is None else lr
         self.step_count += 1
         if any(b.symm_grad is not None for b in self.buckets):
+            if self.replicate_group is not None:
+                raise NotImplementedError("comm='fused' of the optimizer step is not combined with hybrid sharding")
             if self.tp_world > 1:
                 raise NotImplementedError("comm='fused' of the optimizer step is not combined with tensor parallelism")
             return self._step_fused(lr, grad_scale)
@@ -395,6 +403,19 @@ class ZeroEngine:
                     b.grad_buf[b.hi:].zero_()
             self._all_gather(b)
         bump_weight_epoch()   # cached low-precision weight copies are stale now
+
+    @torch.no_grad()
+    def replica_checksum_spread(self) -> float:
+        """Largest difference of a parameter checksum across data-parallel ranks (0.0 when every
+        replica holds the same weights): the cross-replica weight-hash check of the reference's SFT
+        loop (llama2_sft/primus/src/llama2_custom.py:1295-1893)."""
+        sums = torch.stack([b.param_buf.double().sum() for b in self.buckets if not getattr(b, "local_only", False)])
+        if self.world == 1:
+            return 0.0
+        lo, hi = sums.clone(), sums.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=self.group)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=self.group)
+        return float((hi - lo).abs().max())
 
     def grad_norm(self, grad_scale: float = 1.0) -> float:
         """Global gradient norm of the last step (host read)."""

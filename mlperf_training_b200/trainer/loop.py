@@ -64,6 +64,7 @@ class RunConfig:
     log_interval: int = 1
     die_at_step: int = 0                                # fault injection: exit(42) after this step's save
     mllog_file: str = ""
+    dp_replicate: int = 1                               # hybrid sharding: copies of each optimizer-state shard
     tensor_parallel: int = 1                            # tensor + sequence parallel size (Megatron layout)
     sequence_parallel: int = 1
     pipeline_parallel: int = 1
@@ -130,14 +131,19 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         raise NotImplementedError("this run loop drives data x tensor parallel meshes; pipeline stages are "
                                   "scheduled by parallel.pipeline")
     tp_size = min(int(rc.tensor_parallel), world)
-    tp_ctx, dp_group, dp_rank, dp_world = None, None, rank, world
-    if tp_size > 1:
+    tp_ctx, dp_group, dp_rank, dp_world, rep_group = None, None, rank, world, None
+    replicate = max(int(rc.dp_replicate), 1)
+    if tp_size > 1 or (replicate > 1 and world > 1):
         from ..parallel.mesh import Mesh, MeshSpec
+        mesh = Mesh(MeshSpec(tp=tp_size, dp_replicate=replicate))
+        if replicate > 1:
+            rep_group = mesh.group("dp_replicate")
+    if tp_size > 1:
         from ..parallel.tensor import TPContext
-        mesh = Mesh(MeshSpec(tp=tp_size))
         fused_tp = str(rc.tp_comm_overlap).lower() == "fused" and str(device).startswith("cuda")
         tp_ctx = TPContext(mesh.group("tp"), comm="fused" if fused_tp else "nccl", device=device if fused_tp else None)
-        dp_group, dp_rank, dp_world = mesh.group("dp"), mesh.index("dp"), mesh.size("dp")
+        dp_rank, dp_world = mesh.index("dp"), mesh.size("dp")
+        dp_group = mesh.group("dp_shard") if replicate > 1 else mesh.group("dp")
         if cfg.precision != "bf16":
             cfg.precision = "bf16"       # the tensor-parallel linears run the bf16 tcgen05 GEMMs
     if rc.global_batch % dp_world:
@@ -147,7 +153,10 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                       weight_decay=rc.weight_decay, clip_grad=rc.clip_grad)
     tc = TrainConfig(micro_batch=rc.micro_batch, local_batch=local_batch, warmup_steps=rc.lr_warmup_iters,
                      decay_steps=rc.lr_decay_iters, min_lr_ratio=rc.min_lr_ratio, seed=rc.seed, comm=rc.comm)
-    trainer = PretrainTrainer(cfg, opt, tc, device, group=dp_group, tp=tp_ctx, freeze_base=cfg.lora_rank > 0)
+    if tp_size == 1 and replicate > 1 and world > 1:
+        dp_group = mesh.group("dp_shard")
+    trainer = PretrainTrainer(cfg, opt, tc, device, group=dp_group, tp=tp_ctx, freeze_base=cfg.lora_rank > 0,
+                              replicate_group=rep_group)
     data = build_data(rc.data, cfg, rc.seed)
     eval_data = build_data(rc.data, cfg, rc.seed + 7919)
 

@@ -40,7 +40,7 @@ class PretrainTrainer:
     ranks of one tensor-parallel group must be fed the same batch)."""
 
     def __init__(self, model_cfg: GPTConfig, opt: OptimConfig, train: TrainConfig, device, group=None, ep_group=None,
-                 tp=None, freeze_base: bool = False):
+                 tp=None, freeze_base: bool = False, replicate_group=None):
         self.cfg = model_cfg
         self.train_cfg = train
         self.device = torch.device(device)
@@ -50,7 +50,7 @@ class PretrainTrainer:
             from ..models.lora import freeze_base as _freeze
             _freeze(self.model)
         self.engine = ZeroEngine(self.model, opt, group=group, comm=train.comm,
-                                 tp_group=self.tp.group if self.tp is not None else None)
+                                 tp_group=self.tp.group if self.tp is not None else None, replicate_group=replicate_group)
         self.dp_group = group
         self.step_idx = 0
         if train.local_batch % train.micro_batch != 0:

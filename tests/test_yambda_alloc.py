@@ -74,3 +74,22 @@ def test_hstu_run_on_event_store_with_warmup(tmp_path):
     # warm-up left no trace: a run without it starts from the same state
     ref = run(dict(exp, warmup_steps=0), device="cpu", stream=io.StringIO())
     assert abs(ref["losses"][0] - out["losses"][0]) < 1e-6
+
+
+def test_energy_monitor_integrates_power():
+    import time
+    from mlperf_training_b200.utils.energy import EnergyMonitor
+    m = EnergyMonitor(interval_s=0.05, reader=lambda: [100.0, 50.0]).start()
+    time.sleep(0.4)
+    rep = m.stop()
+    assert rep["samples"] >= 3 and rep["peak_w"] == 150.0
+    assert 150.0 * 0.15 < rep["energy_j"] < 150.0 * 0.6
+
+
+def test_replica_checksum_single_process():
+    import torch
+    from mlperf_training_b200.models.gpt import GPT, GPTConfig
+    from mlperf_training_b200.parallel.engine import OptimConfig, ZeroEngine
+    m = GPT(GPTConfig(n_layers=1, hidden=32, n_heads=2, n_kv_heads=1, head_dim=16, ffn_hidden=64, vocab_size=64, seq_len=8,
+                      dtype="fp32"), seed=0)
+    assert ZeroEngine(m, OptimConfig()).replica_checksum_spread() == 0.0
