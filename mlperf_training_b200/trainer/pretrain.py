@@ -52,6 +52,7 @@ class PretrainTrainer:
         self.engine = ZeroEngine(self.model, opt, group=group, comm=train.comm,
                                  tp_group=self.tp.group if self.tp is not None else None, replicate_group=replicate_group)
         self.dp_group = group
+        self.replicate_group = replicate_group
         self.step_idx = 0
         if train.local_batch % train.micro_batch != 0:
             raise ValueError("local_batch must be a multiple of micro_batch")
@@ -146,6 +147,8 @@ class PretrainTrainer:
                     dist.all_reduce(acc, group=g)
             elif self.tp is None and dist.get_world_size() > 1:
                 dist.all_reduce(acc)
+            if self.replicate_group is not None and dist.get_world_size(self.replicate_group) > 1:
+                dist.all_reduce(acc, group=self.replicate_group)      # every rank must see the same evaluation result
         return acc
 
     @torch.no_grad()
