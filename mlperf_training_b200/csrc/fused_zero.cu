@@ -3,8 +3,10 @@
 //
 //   zero_reduce_scatter : the owner of a shard reads that shard from every rank's gradient buffer
 //                         (P2P loads over NVLink, fixed rank order -> deterministic sum), scales by
-//                         1/W, keeps the fp32 result locally, clears the peers' copies for the next
-//                         accumulation and emits per-CTA partial sums of squares for clipping.
+//                         1/W, keeps the fp32 result locally and emits per-CTA partial sums of squares
+//                         for clipping.  The gradient buffers are NOT cleared here: clearing the peers'
+//                         copies would send as many bytes out over NVLink as the reduction reads in;
+//                         every rank clears its own buffer locally after the step's last barrier.
 //   zero_adamw_all_gather : AdamW on the local shard (clip coefficient from a device scalar) and
 //                         the updated bf16 parameters stored straight into EVERY rank's parameter
 //                         buffer (P2P stores): update and all-gather are one pass over the shard.
@@ -27,7 +29,7 @@ struct Ptrs {
 
 __global__ void __launch_bounds__(256)
 zero_reduce_scatter_kernel(Ptrs grads, int W, int rank, long long lo, long long n4, float scale,
-                           float* __restrict__ out, float* __restrict__ partial_sumsq) {
+                           float* __restrict__ out, float* __restrict__ partial_sumsq, int clear_peers) {
   __shared__ float red[8];
   float acc = 0.f;
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n4; i += (long long)gridDim.x * 256) {
@@ -36,7 +38,7 @@ zero_reduce_scatter_kernel(Ptrs grads, int W, int rank, long long lo, long long 
       float4* src = reinterpret_cast<float4*>(reinterpret_cast<float*>(grads.p[r]) + lo) + i;
       const float4 g = *src;
       s.x += g.x; s.y += g.y; s.z += g.z; s.w += g.w;
-      if (r != rank) *src = make_float4(0.f, 0.f, 0.f, 0.f);   // ready for the next accumulation
+      if (clear_peers && r != rank) *src = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
     reinterpret_cast<float4*>(out)[i] = s;
@@ -113,7 +115,7 @@ B200_API int b200_zero_reduce_scatter(const unsigned long long* grad_ptrs, int W
   for (int r = 0; r < W; ++r) ptrs.p[r] = reinterpret_cast<void*>(grad_ptrs[r]);
   const int grid = b200::sm_count() * 4;
   if (partial_sumsq != nullptr) cudaMemsetAsync(partial_sumsq, 0, grid * sizeof(float), (cudaStream_t)stream);
-  zero_reduce_scatter_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(ptrs, W, rank, lo, n / 4, scale, out, partial_sumsq);
+  zero_reduce_scatter_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(ptrs, W, rank, lo, n / 4, scale, out, partial_sumsq, 0);
   b200::count_launch();
   return b200::check_launch("zero_reduce_scatter");
 }

@@ -333,8 +333,14 @@ class ZeroEngine:
                              weight_decay=o.weight_decay if wd else 0.0, step=self.step_count,
                              master=None if b.master is None else b.master[s:e], grad_scale=grad_scale,
                              sumsq_buf=self.sumsq if clip else None, max_norm=o.clip_grad, zero_grad=True)
+                if self.world > 1 and not getattr(b, "local_only", False):
+                    # a bucket without peer-mapped buffers (another dtype than the kernels move): library path
+                    if b.lo > 0:
+                        b.grad_buf[:b.lo].zero_()
+                    if b.hi < b.numel:
+                        b.grad_buf[b.hi:].zero_()
+                    self._all_gather(b)
                 continue
-            b.g_shard().zero_()                   # own copy of the reduced range (peers were cleared by the kernel)
             for s, e, wd in b.segments():
                 _lib.call("b200_zero_adamw_all_gather", b.symm_param.ptr_array(), self.world, self.rank, b.lo + s, e - s,
                           _lib.ptr(b.rs_out[s:e]), _lib.ptr(b.m[s:e]), _lib.ptr(b.v[s:e]),
@@ -342,7 +348,9 @@ class ZeroEngine:
                           o.weight_decay if wd else 0.0, self.step_count, float(grad_scale),
                           _lib.ptr(self.sumsq) if clip else None, float(o.clip_grad), 0, _lib.stream_ptr())
         if fused:
-            fused[0].symm_param.barrier()         # every rank's parameters have landed
+            fused[0].symm_param.barrier()         # every rank's parameters have landed, every reduction has been read
+            for b in fused:
+                b.grad_buf.zero_()                # local clear: no peer reads this buffer any more
         bump_weight_epoch()
 
     @torch.no_grad()
