@@ -1,0 +1,78 @@
+"""Auxiliary tools: trace repair and step-wall report, the stdout filter, dataset staging with its
+sentinel, and the GPU idle check against a fake ``nvidia-smi``."""
+import json
+import os
+import stat
+import subprocess
+import sys
+
+from mlperf_training_b200.utils.profiler import clean_trace, gpu_peak_tflops, step_wall_report
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_trace_repair_and_step_report(tmp_path):
+    ev = [
+        {"ph": "X", "cat": "user_annotation", "name": "train_step#0", "ts": 100, "dur": 100, "pid": 1, "tid": 1},
+        {"ph": "X", "cat": "kernel", "name": "warmup", "ts": 10, "dur": 5, "pid": 0, "tid": 7},
+        {"ph": "X", "cat": "kernel", "name": "a", "ts": 110, "dur": 30, "pid": 0, "tid": 7},
+        {"ph": "X", "cat": "kernel", "name": "b", "ts": 130, "dur": 30, "pid": 0, "tid": 7},      # overlaps a on its lane
+        {"ph": "X", "cat": "kernel", "name": "c", "ts": 190, "dur": -3, "pid": 0, "tid": 7},      # negative duration
+        {"ph": "M", "name": "process_name", "pid": 0},
+    ]
+    p = tmp_path / "trace.json"
+    p.write_text(json.dumps({"traceEvents": ev}))
+    stats = clean_trace(p, trim_before_us=50)
+    assert stats == {"dropped": 1, "clipped": 1, "deoverlapped": 1}
+    out = json.loads(p.read_text())["traceEvents"]
+    b = next(e for e in out if e.get("name") == "b")
+    assert b["ts"] == 140 and b["dur"] == 20 and all(e.get("name") != "warmup" for e in out)
+    rep = step_wall_report(p)
+    assert rep["steps"] == [{"wall_us": 100, "gpu_busy_us": 50}]
+    assert gpu_peak_tflops("NVIDIA B200") == 2250.0
+
+
+def test_stdout_filter_passes_only_mllog(tmp_path):
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "from mlperf_training_b200.mllog import suppress\n"
+        "suppress.install(side_file=%r)\n"
+        "print('noise line'); print(':::MLLOG {\"key\": \"x\"}'); print('RESULT,bench,,1,B200,now')\n"
+        "import os; os.write(2, b'stderr noise\\n')\n"
+        "suppress.restore(); print('after restore')\n"
+    ) % (ROOT, str(tmp_path / "side.log"))
+    env = {k: v for k, v in os.environ.items() if k != "B200_VERBOSE"}
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=120)
+    assert r.returncode == 0, r.stderr
+    lines = r.stdout.splitlines()
+    assert ':::MLLOG {"key": "x"}' in lines and "RESULT,bench,,1,B200,now" in lines and "after restore" in lines
+    assert "noise line" not in lines and "stderr noise" not in r.stderr
+    assert "noise line" in (tmp_path / "side.log").read_text()
+
+
+def test_stage_dataset_sentinel(tmp_path):
+    src, dst = tmp_path / "src", tmp_path / "dst"
+    src.mkdir()
+    (src / "a.bin").write_bytes(b"x" * 1000)
+    script = os.path.join(ROOT, "workloads", "common", "stage_dataset_local.sh")
+    r1 = subprocess.run(["bash", script, str(src), str(dst)], capture_output=True, text=True, timeout=60)
+    assert r1.returncode == 0 and (dst / "a.bin").exists()
+    assert (dst / ".stage_complete").read_text().splitlines()[0] == str(src)
+    r2 = subprocess.run(["bash", script, str(src), str(dst)], capture_output=True, text=True, timeout=60)
+    assert "already staged" in r2.stdout
+
+
+def test_gpu_idle_check_with_fake_nvidia_smi(tmp_path):
+    fake = tmp_path / "nvidia-smi"
+    script = os.path.join(ROOT, "workloads", "common", "check_gpus_idle.sh")
+
+    def run(mem_lines, apps):
+        fake.write_text("#!/bin/bash\ncase \"$*\" in *compute-apps*) printf '%s' \"" + apps + "\";; *) printf '" + mem_lines + "';; esac\n")
+        fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+        env = dict(os.environ, PATH=f"{tmp_path}:{os.environ['PATH']}")
+        return subprocess.run(["bash", script], capture_output=True, text=True, env=env, timeout=60)
+
+    assert run("0, 3\\n1, 0\\n", "").returncode == 0
+    busy = run("0, 3\\n1, 40960\\n", "")
+    assert busy.returncode == 1 and "GPU 1" in busy.stdout
+    assert run("0, 0\\n", "4242\\n").returncode == 1
