@@ -15,6 +15,8 @@
 // Takes the place of the reference's library GEMM calls (hipBLASLt through torch.addmm,
 // generative_recommenders/ops/hstu_compute.py:122-126) and of its hand-written MFMA GEMMs
 // (generative_recommenders/ops/hip/k512_fp8_gemm.cu, k1536_fp8_addmm.cu) at bf16 precision.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "runtime.h"
 
@@ -311,6 +313,17 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   return b200::check_launch("gemm_bf16");
 }
 
+// Height (in tiles) of a raster group: consecutive CTAs work on `group_m` row tiles of one column tile, so the
+// column's B tile is shared in L2 while the group's A rows stay resident (B200_GEMM_GROUP_M overrides).
+static int raster_group_m() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200_GEMM_GROUP_M");
+    v = (e && atoi(e) > 0) ? atoi(e) : 16;
+  }
+  return v;
+}
+
 }  // namespace
 
 // D[M,N] (=|+=) alpha * A * B^T (+ bias) (+ residual)
@@ -337,7 +350,7 @@ B200_API int b200_gemm_bf16(const void* a, const void* b, void* d, int M, int N,
   p.M = M; p.N = N; p.K = K;
   p.a_mn_major = a_mn_major ? 1 : 0; p.b_mn_major = b_mn_major ? 1 : 0;
   p.out_f32 = out_f32 ? 1 : 0; p.accumulate = accumulate ? 1 : 0;
-  p.group_m = 16;
+  p.group_m = raster_group_m();
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ldr = ldr;

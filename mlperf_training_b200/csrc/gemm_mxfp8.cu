@@ -303,6 +303,17 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   return b200::check_launch("gemm_mxfp8");
 }
 
+// Height (in tiles) of a raster group: consecutive CTAs work on `group_m` row tiles of one column tile, so the
+// column's B tile is shared in L2 while the group's A rows stay resident (B200_GEMM_GROUP_M overrides).
+static int raster_group_m() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200_GEMM_GROUP_M");
+    v = (e && atoi(e) > 0) ? atoi(e) : 16;
+  }
+  return v;
+}
+
 }  // namespace
 
 // N tile the kernel will use for an output width N (the B operand's scales must be laid out with
@@ -341,7 +352,7 @@ B200_API int b200_gemm_mxfp8(const void* a_q, const void* sfa, const void* b_q, 
   Params p;
   p.M = M; p.N = N; p.K = K;
   p.out_f32 = out_f32 ? 1 : 0; p.accumulate = accumulate ? 1 : 0;
-  p.group_m = 16;
+  p.group_m = raster_group_m();
   p.sfa = (const uint8_t*)sfa; p.sfb = (const uint8_t*)sfb;
   p.bias = (const __nv_bfloat16*)bias;
   p.residual = (const __nv_bfloat16*)residual;
