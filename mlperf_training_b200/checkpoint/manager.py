@@ -97,6 +97,77 @@ class CheckpointManager:
         self.barrier()
         return final
 
+    # ------------------------------------------------------------------ asynchronous save
+    def save_async(self, step: int, *, dense: dict | None, optim_shard: dict | None, meta: dict, save_rng: bool = True):
+        """Snapshot the tensors to host memory now and write the checkpoint on a background thread, so
+        the training loop only pays for the device-to-host copy.  ``finalize_async()`` must be called
+        (it is called by the next ``save`` / ``save_async`` too) before the checkpoint counts as
+        complete - the async save + finalisation hook of the reference's SFT loop
+        (llama2_sft/primus/src/llama2_custom.py:1859-1863).  Single-process writers only: the barriers
+        of ``save`` cannot run on a side thread, so with ``world > 1`` this falls back to ``save``."""
+        import threading
+        self.finalize_async()
+        if self.world > 1:
+            return self.save(step, dense=dense, optim_shard=optim_shard, meta=meta, save_rng=save_rng)
+
+        def to_host(obj):
+            if torch.is_tensor(obj):
+                return obj.detach().to("cpu", copy=True)
+            if isinstance(obj, dict):
+                return {k: to_host(v) for k, v in obj.items()}
+            if isinstance(obj, (list, tuple)):
+                return type(obj)(to_host(v) for v in obj)
+            return obj
+        dense_h, optim_h = to_host(dense), to_host(optim_shard)
+        rng = None
+        if save_rng:
+            rng = {"cpu": torch.get_rng_state()}
+            if torch.cuda.is_available():
+                rng["cuda"] = torch.cuda.get_rng_state()
+        result: dict = {}
+
+        def work():
+            try:
+                result["path"] = self._write(step, dense_h, optim_h, meta, rng)
+            except Exception as e:      # surfaced by finalize_async
+                result["error"] = e
+        t = threading.Thread(target=work, name="checkpoint-writer", daemon=True)
+        t.start()
+        self._pending = (t, result)
+        return None
+
+    def finalize_async(self):
+        """Wait for the background write; returns its path (None when nothing was pending)."""
+        pending = getattr(self, "_pending", None)
+        if pending is None:
+            return None
+        t, result = pending
+        t.join()
+        self._pending = None
+        if "error" in result:
+            raise result["error"]
+        return result.get("path")
+
+    def _write(self, step: int, dense, optim_shard, meta: dict, rng) -> Path:
+        tmp, final = self.root / f"{step}.tmp", self.path(step)
+        self.root.mkdir(parents=True, exist_ok=True)
+        shutil.rmtree(tmp, ignore_errors=True)
+        (tmp / "sparse").mkdir(parents=True, exist_ok=True)
+        if dense is not None:
+            torch.save(dense, tmp / "dense.pt")
+        if optim_shard is not None:
+            torch.save(optim_shard, tmp / f"optim_rank{self.rank}.pt")
+        if rng is not None:
+            torch.save(rng, tmp / f"rng_rank{self.rank}.pt")
+        (tmp / "meta.json").write_text(json.dumps(dict(meta, step=step, world=self.world, saved_at=time.time()), indent=1))
+        if final.exists():
+            shutil.rmtree(final, ignore_errors=True)
+        os.rename(tmp, final)
+        (self.root / "latest_checkpointed_iteration.txt").write_text(str(step))
+        for old in self.steps()[:-self.keep_last] if self.keep_last > 0 else []:
+            shutil.rmtree(self.path(old), ignore_errors=True)
+        return final
+
     # ------------------------------------------------------------------ load
     def load(self, step: int | None = None, map_location="cpu") -> dict | None:
         """Returns ``{"dense", "optim", "rng", "meta", "path"}`` of ``step`` (default: latest

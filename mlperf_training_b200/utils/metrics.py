@@ -91,6 +91,22 @@ class BinnedCumulativeAUC:
         self.neg.copy_(sd["neg"])
 
 
+def grouped_auc(scores: torch.Tensor, labels: torch.Tensor, groups: torch.Tensor) -> float:
+    """GAUC: the AUC computed inside each group (user) and averaged with the group's sample count as
+    weight; groups with a single class are skipped (the per-user AUC the reference's metrics logger
+    reports next to the global one, generative_recommenders/dlrm_v4/utils.py:842-1535)."""
+    tot, wsum = 0.0, 0.0
+    for g in torch.unique(groups):
+        m = groups == g
+        y = labels[m]
+        if y.min() == y.max():
+            continue
+        n = int(m.sum())
+        tot += n * exact_auc(scores[m], y)
+        wsum += n
+    return tot / wsum if wsum > 0 else 0.5
+
+
 def normalized_entropy(scores: torch.Tensor, labels: torch.Tensor, eps: float = 1e-12) -> float:
     p = scores.double().clamp(eps, 1 - eps)
     y = labels.double()

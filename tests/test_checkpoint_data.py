@@ -158,3 +158,22 @@ def test_flux_run_learns_on_cpu():
     b = SyntheticFluxData(cfg).batch(0, 0, 4)
     ls = [tr.train_step(b) for _ in range(40)]
     assert sum(ls[-5:]) < 0.9 * sum(ls[:5])
+
+
+def test_async_checkpoint_and_gauc(tmp_path):
+    from mlperf_training_b200.utils.metrics import exact_auc, grouped_auc
+    m = CheckpointManager(str(tmp_path / "ck"), keep_last=2)
+    w = torch.arange(6.0)
+    assert m.save_async(5, dense={"w": w}, optim_shard={"m": torch.ones(2)}, meta={"samples": 20}) is None
+    w.add_(100)                                            # the snapshot was taken before this change
+    assert m.finalize_async() == m.path(5) and m.finalize_async() is None
+    ck = m.load()
+    assert ck["meta"]["step"] == 5 and torch.equal(ck["dense"]["w"], torch.arange(6.0))
+    m.save_async(6, dense={"w": w}, optim_shard=None, meta={})
+    m.save_async(7, dense={"w": w}, optim_shard=None, meta={})        # finalises 6 first
+    m.finalize_async()
+    assert m.steps() == [6, 7]
+    s = torch.tensor([0.9, 0.1, 0.8, 0.2, 0.3, 0.7])
+    y = torch.tensor([1.0, 0.0, 0.0, 1.0, 1.0, 1.0])
+    g = torch.tensor([0, 0, 1, 1, 2, 2])
+    assert grouped_auc(s, y, g) == (2 * exact_auc(s[:2], y[:2]) + 2 * exact_auc(s[2:4], y[2:4])) / 4    # group 2 has one class
