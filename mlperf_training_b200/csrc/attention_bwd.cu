@@ -166,18 +166,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int it = 0; it < n_iter && ok; ++it) {
         const uint32_t ph = it & 1;
         if (!mbar_wait(qdo_full, ph, abort_flag, p.status, 81)) { ok = false; break; }
-        if (it > 0 && !mbar_wait(dq_drained, (it - 1) & 1, abort_flag, p.status, 82)) { ok = false; break; }
         tc_fence_after();
         // S = Q K^T ; dP = dO V^T   (contraction over the head dim, both operands K-major)
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t o = (kk / 4) * (128 * 128) + (kk % 4) * 32;
-          tc_mma_f16_ss(tm_S, umma_desc_sw128(aQ + o, 16, 1024), umma_desc_sw128(aK + o, 16, 1024), id_kk, kk > 0);
-        }
+        // dP first: its accumulator was read by the workers long ago, so these MMAs run while the workers
+        // still drain dQ of the previous iteration out of the S / dQ columns
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t o = (kk / 4) * (128 * 128) + (kk % 4) * 32;
           tc_mma_f16_ss(tm_dP, umma_desc_sw128(adO + o, 16, 1024), umma_desc_sw128(aV + o, 16, 1024), id_kk, kk > 0);
+        }
+        if (it > 0 && !mbar_wait(dq_drained, (it - 1) & 1, abort_flag, p.status, 82)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t o = (kk / 4) * (128 * 128) + (kk % 4) * 32;
+          tc_mma_f16_ss(tm_S, umma_desc_sw128(aQ + o, 16, 1024), umma_desc_sw128(aK + o, 16, 1024), id_kk, kk > 0);
         }
         tc_commit(sdp_full);
         if (!mbar_wait(pds_full, ph, abort_flag, p.status, 83)) { ok = false; break; }
