@@ -73,6 +73,11 @@ class RunConfig:
     comm: str = "nccl"                                  # optimizer-step collectives: "nccl" | "fused"
     precision_schedule: dict | str | None = None        # ops.recipe.PrecisionSchedule spec (phase switch at a step)
     heartbeat_timeout_s: float = 0.0                    # > 0: watch the other ranks' heartbeats between steps
+    straggler_interval: int = 0                         # > 0: compare mean step time across ranks every N steps
+    check_replicas_every: int = 0                       # > 0: compare parameter checksums across replicas every N steps
+    async_checkpoint: bool = False                      # write checkpoints on a background thread (single process)
+    energy_monitor: bool = False                        # integrate GPU power over the run
+    perf_jsonl: str = ""                                # durable per-interval performance lines
     profile_step_start: int = 0
     profile_step_end: int = 0
     profile_dir: str = ""
@@ -203,6 +208,19 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     if rc.heartbeat_timeout_s > 0 and world > 1:
         from ..parallel.health import Heartbeat
         hb = Heartbeat(dist.distributed_c10d._get_default_store(), rank, world, interval_s=rc.heartbeat_timeout_s / 4).start()
+    straggler = None
+    if rc.straggler_interval > 0:
+        from ..parallel.health import StragglerDetector
+        straggler = StragglerDetector(interval=rc.straggler_interval)
+    energy = None
+    if rc.energy_monitor and rank == 0:
+        from ..utils.energy import EnergyMonitor
+        energy = EnergyMonitor().start()
+    perf = None
+    if rc.perf_jsonl and rank == 0:
+        from ..utils.metrics import PerfLogger
+        from ..utils.profiler import gpu_peak_tflops
+        perf = PerfLogger(cfg.flops_per_token() * cfg.seq_len, world=world, peak_tflops=gpu_peak_tflops(), jsonl=rc.perf_jsonl)
     timer = ml.ThroughputTimer(rc.global_batch)
     t_run0 = time.perf_counter()
     last_ckpt_t = time.perf_counter()
@@ -224,8 +242,21 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         if torch.cuda.is_available() and str(device).startswith("cuda"):
             batch = tuple(t.pin_memory() for t in batch) if isinstance(batch, tuple) else batch.pin_memory()
         loss = trainer.train_step(batch)
-        timer.step_stop()
+        step_s = timer.step_stop()
         losses.append(loss)
+        if perf is not None:
+            perf.step(rc.global_batch)
+            if rc.log_interval and (step + 1) % max(rc.log_interval, 1) == 0:
+                perf.line(step + 1, {"loss": loss})
+        if straggler is not None:
+            rep = straggler.record(step_s)
+            if rep and rep["stragglers"] and rank == 0:
+                print(f"[straggler] ranks {rep['stragglers']} are slower than {straggler.factor} x median "
+                      f"({rep['median'] * 1e3:.1f} ms)", flush=True)
+        if rc.check_replicas_every and (step + 1) % rc.check_replicas_every == 0:
+            spread = trainer.engine.replica_checksum_spread()
+            if spread > 0:
+                raise RuntimeError(f"step {step + 1}: data-parallel replicas hold different weights (checksum spread {spread})")
         if prof is not None and step + 1 == rc.profile_step_end:
             prof.stop()
             prof = None
@@ -258,7 +289,9 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                                               elapsed_since_last_s=time.perf_counter() - last_ckpt_t,
                                               every_steps=rc.checkpoint_every)
             if reason or (rc.die_at_step and step + 1 == rc.die_at_step):
-                resume_mgr.save(step + 1,
+                saver = resume_mgr.save_async if (rc.async_checkpoint and not (rc.die_at_step and step + 1 == rc.die_at_step)) \
+                    else resume_mgr.save
+                saver(step + 1,
                                 dense={"param_bufs": [b.param_buf.detach().cpu() for b in trainer.engine.buckets],
                                        "model_config": cfg.to_dict()},
                                 optim_shard=trainer.engine.optimizer_state(),
@@ -272,6 +305,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
 
     if hb is not None:
         hb.stop()
+    if resume_mgr is not None:
+        resume_mgr.finalize_async()
     duration = time.perf_counter() - t_run0
     success = reached or rc.target_eval_loss <= 0
     if not reached:
@@ -280,6 +315,9 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     log.log_run_stop(success, samples=timer.samples, duration_s=duration)
     log.event(ml.TRACKED_STATS, {"throughput_samples_per_s": timer.throughput(),
                                  "tokens_per_s": timer.throughput() * cfg.seq_len}, metadata={"step": step + 1})
+    if energy is not None:
+        rep = energy.stop()
+        log.event(ml.TRACKED_STATS, {"energy_kwh": rep["energy_kwh"], "peak_power_w": rep["peak_w"]}, metadata={"step": step + 1})
     log.close()
     return {"steps": step + 1 - start_step, "losses": losses, "eval_loss": last_eval, "reached": reached,
             "throughput": timer.throughput(), "records": log.lines, "trainer": trainer}

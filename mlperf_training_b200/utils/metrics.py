@@ -153,7 +153,7 @@ class PerfLogger:
         sps = self.samples / dt
         tflops_gpu = sps * self.flops_per_sample / self.world / 1e12
         rec = {"step": step, "samples_per_s": sps, "step_ms": 1e3 * dt / max(self.steps, 1), "tflops_algo_per_gpu": tflops_gpu,
-               "mfu": tflops_gpu / self.peak, **(extra or {})}
+               "mfu": (tflops_gpu / self.peak) if self.peak > 0 else 0.0, **(extra or {})}
         if self.jsonl:
             with open(self.jsonl, "a") as f:
                 f.write(json.dumps(rec) + "\n")

@@ -177,3 +177,16 @@ def test_async_checkpoint_and_gauc(tmp_path):
     y = torch.tensor([1.0, 0.0, 0.0, 1.0, 1.0, 1.0])
     g = torch.tensor([0, 0, 1, 1, 2, 2])
     assert grouped_auc(s, y, g) == (2 * exact_auc(s[:2], y[:2]) + 2 * exact_auc(s[2:4], y[2:4])) / 4    # group 2 has one class
+
+
+def test_run_loop_monitors(tmp_path):
+    """Async checkpoints, replica check, straggler detector and the performance log inside a run."""
+    import json
+    from mlperf_training_b200.trainer.loop import run
+    out = run(dict(model=TINY, global_batch=2, micro_batch=1, train_iters=4, warmup_train_steps=0, checkpoint_dir=str(tmp_path / "ck"),
+                   checkpoint_every=2, async_checkpoint=True, check_replicas_every=2, straggler_interval=2,
+                   perf_jsonl=str(tmp_path / "perf.jsonl")), device="cpu", stream=io.StringIO())
+    assert out["steps"] == 4
+    assert CheckpointManager(str(tmp_path / "ck")).steps() == [2, 4]
+    lines = [json.loads(l) for l in (tmp_path / "perf.jsonl").read_text().splitlines()]
+    assert len(lines) == 4 and lines[-1]["step"] == 4 and lines[-1]["samples_per_s"] > 0
