@@ -105,7 +105,7 @@ def bench_flux(args, rank, world, dev):
     from ..models.mmdit import flux1_schnell
     from ..parallel.engine import OptimConfig
     from ..trainer.flux import FluxTrainer, SyntheticFluxData
-    cfg = flux1_schnell()
+    cfg = flux1_schnell(precision=args.precision)
     if args.layers:
         cfg.n_double, cfg.n_single = args.layers, 2 * args.layers
     local = max((args.global_batch or 256) // world, 1)
@@ -154,6 +154,7 @@ def main(argv=None) -> int:
     ap.add_argument("--global-batch", type=int, default=0)
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8"], help="linear precision (flux1)")
     args = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
