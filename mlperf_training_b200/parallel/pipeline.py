@@ -169,3 +169,129 @@ class PipelineRunner:
             gin = bwd(grad)
             self._exchange(send_prev=gin)
         return total
+
+
+class InterleavedRunner:
+    """Interleaved (virtual-stage) 1F1B: every rank owns ``v`` model chunks; chunk ``c`` of rank ``r``
+    is virtual stage ``c * S + r`` of ``S * v``.  Micro-batches advance through the virtual stages in
+    groups of ``S``; a rank runs ``(S - r - 1) * 2 + (v - 1) * S`` warm-up forwards, then alternates
+    one forward with one backward, then drains the backwards - the schedule Megatron uses for
+    ``virtual_pipeline_model_parallel_size`` (llama2_sft/primus/conf/llama2_70b_lora_posttrain.yaml:21,
+    null in every shipped configuration).  The pipeline bubble shrinks by the factor ``v`` against the
+    plain schedule at the price of ``v`` times more messages.  The number of micro-batches must be a
+    multiple of ``S``.  Messages go to the ring neighbours (the last rank's output feeds the first
+    rank's next chunk); whenever a rank sends and receives at one point of the schedule the operations
+    are posted together in one ``batch_isend_irecv``."""
+
+    def __init__(self, chunks: list[GPTStage], rank: int, n_ranks: int, prev_rank: int, next_rank: int, group=None):
+        self.chunks, self.r, self.S, self.v = chunks, rank, n_ranks, len(chunks)
+        self.prev, self.next, self.group = prev_rank, next_rank, group
+
+    def _exchange(self, send_next=None, send_prev=None, recv_prev=None, recv_next=None):
+        ops, got_prev, got_next = [], None, None
+        if send_next is not None:
+            ops.append(dist.P2POp(dist.isend, send_next.contiguous(), self.next, self.group))
+        if send_prev is not None:
+            ops.append(dist.P2POp(dist.isend, send_prev.contiguous(), self.prev, self.group))
+        if recv_prev is not None:
+            got_prev = torch.empty_like(recv_prev)
+            ops.append(dist.P2POp(dist.irecv, got_prev, self.prev, self.group))
+        if recv_next is not None:
+            got_next = torch.empty_like(recv_next)
+            ops.append(dist.P2POp(dist.irecv, got_next, self.next, self.group))
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+        return got_prev, got_next
+
+    def run(self, micro_batches: list[tuple[torch.Tensor, torch.Tensor]]) -> torch.Tensor | None:
+        S, v, r = self.S, self.v, self.r
+        M = len(micro_batches)
+        if M % S:
+            raise ValueError(f"{M} micro-batches are not a multiple of the {S} pipeline ranks")
+        total = M * v
+        warm = min((S - r - 1) * 2 + (v - 1) * S, total)
+        remain = total - warm
+        cfg = self.chunks[0].cfg
+        tok0 = micro_batches[0][0]
+        like = torch.empty((tok0.numel(), cfg.hidden), dtype=cfg.torch_dtype(), device=tok0.device)
+        inputs = [[] for _ in range(v)]
+        outputs = [[] for _ in range(v)]
+        ograds = [[] for _ in range(v)]
+        loss_sum = None
+
+        def chunk_of(k, fwd=True):
+            c = (k % (S * v)) // S
+            return c if fwd else v - 1 - c
+
+        def mb_of(k):
+            return (k // (S * v)) * S + k % S
+
+        def is_first(c):
+            return r == 0 and c == 0
+
+        def is_last(c):
+            return r == S - 1 and c == v - 1
+
+        def fwd(k):
+            c = chunk_of(k)
+            if is_first(c) and len(inputs[c]) == len(outputs[c]):
+                inputs[c].append(None)
+            x = inputs[c][len(outputs[c])]
+            if x is not None:
+                x.requires_grad_(True)
+            out = self.chunks[c](x, *micro_batches[mb_of(k)])
+            outputs[c].append(out)
+            return None if is_last(c) else out.detach()
+
+        def bwd(k):
+            nonlocal loss_sum
+            c = chunk_of(k, False)
+            x, out = inputs[c].pop(0), outputs[c].pop(0)
+            if is_last(c):
+                out.backward()
+                loss_sum = out.detach() if loss_sum is None else loss_sum + out.detach()
+            else:
+                torch.autograd.backward(out, ograds[c].pop(0))
+            return None if (x is None or is_first(c)) else x.grad
+
+        def want_prev(k_next):                     # does forward step k_next take its input from a message?
+            return k_next < total and not is_first(chunk_of(k_next))
+
+        def want_next(k_next):                     # does backward step k_next take its gradient from a message?
+            return k_next < total and not is_last(chunk_of(k_next, False))
+
+        # the input of the very first forward
+        if want_prev(0):
+            x, _ = self._exchange(recv_prev=like)
+            inputs[chunk_of(0)].append(x)
+        for k in range(warm):
+            out = fwd(k)
+            rp = like if want_prev(k + 1) else None
+            rn = like if (k == warm - 1 and remain > 0 and want_next(0)) else None
+            x, g = self._exchange(send_next=out, recv_prev=rp, recv_next=rn)
+            if rp is not None:
+                inputs[chunk_of(k + 1)].append(x)
+            if rn is not None:
+                ograds[chunk_of(0, False)].append(g)
+        if remain == 0 and want_next(0):
+            _, g = self._exchange(recv_next=like)
+            ograds[chunk_of(0, False)].append(g)
+        for k in range(remain):
+            fk, bk = k + warm, k
+            out = fwd(fk)
+            gin = bwd(bk)
+            rp = like if want_prev(fk + 1) else None
+            rn = like if want_next(bk + 1) else None
+            x, g = self._exchange(send_next=out, send_prev=gin, recv_prev=rp, recv_next=rn)
+            if rp is not None:
+                inputs[chunk_of(fk + 1)].append(x)
+            if rn is not None:
+                ograds[chunk_of(bk + 1, False)].append(g)
+        for bk in range(remain, total):
+            gin = bwd(bk)
+            rn = like if want_next(bk + 1) else None
+            _, g = self._exchange(send_prev=gin, recv_next=rn)
+            if rn is not None:
+                ograds[chunk_of(bk + 1, False)].append(g)
+        return loss_sum

@@ -46,6 +46,17 @@ def test_pipeline_1f1b_parity_gloo(stages):
     assert "RESULT rank 0 ok=True" in r.stdout
 
 
+@pytest.mark.parametrize("ranks,chunks,micro", [(2, 2, 4), (3, 2, 6), (2, 3, 2)])
+def test_interleaved_pipeline_parity_gloo(ranks, chunks, micro):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}",
+                        "--master-addr", "127.0.0.1", "--master-port", "29663",
+                        os.path.join(ROOT, "tests", "multi", "vpp_worker.py"), str(chunks), str(micro)],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT rank 0 ok=True" in r.stdout
+
+
 def test_stage_layer_split():
     from mlperf_training_b200.parallel.pipeline import stage_layers
     assert [list(stage_layers(10, 4, s)) for s in range(4)] == [[0, 1, 2], [3, 4, 5], [6, 7], [8, 9]]
