@@ -139,17 +139,24 @@ __global__ void sumsq_final_kernel(const float* __restrict__ partial, int n, flo
 }
 
 // ---------------------------------------------------------------------------------------
-// AdamW over a flat buffer.  P: bf16 or fp32 weights; G: bf16 or fp32 grads; moments fp32.
+// AdamW over a flat buffer.  P: bf16 or fp32 weights; G: bf16 or fp32 grads; M: fp32 or bf16 moments
+// (bf16 moments halve the optimizer state; the update itself is computed in fp32).
 // If `master` is non-null it holds fp32 master weights and `p` receives the bf16 copy.
 // clip: if sumsq != null, grads are scaled by min(1, max_norm / (sqrt(*sumsq) + 1e-6)).
 // ---------------------------------------------------------------------------------------
 struct AdamArgs {
   float lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale, max_norm;
 };
-template <typename P, typename G>
+template <typename T> B200_DEVICE float to_f32(T x) {
+  if constexpr (sizeof(T) == 2) return __bfloat162float(x); else return x;
+}
+template <typename T> B200_DEVICE T from_f32(float x) {
+  if constexpr (sizeof(T) == 2) return __float2bfloat16_rn(x); else return x;
+}
+template <typename P, typename G, typename M>
 __global__ void __launch_bounds__(256)
-adamw_kernel(P* __restrict__ p, float* __restrict__ master, const G* __restrict__ g, float* __restrict__ m,
-             float* __restrict__ v, long long n, AdamArgs a, const float* __restrict__ sumsq, int zero_grad,
+adamw_kernel(P* __restrict__ p, float* __restrict__ master, const G* __restrict__ g, M* __restrict__ m,
+             M* __restrict__ v, long long n, AdamArgs a, const float* __restrict__ sumsq, int zero_grad,
              G* __restrict__ g_mut) {
   float scale = a.grad_scale;
   if (sumsq != nullptr && a.max_norm > 0.f) {
@@ -165,10 +172,10 @@ adamw_kernel(P* __restrict__ p, float* __restrict__ master, const G* __restrict_
     if (master != nullptr) w = master[i];
     else if constexpr (sizeof(P) == 2) w = __bfloat162float(p[i]);
     else w = p[i];
-    const float mi = a.beta1 * m[i] + (1.f - a.beta1) * gv;
-    const float vi = a.beta2 * v[i] + (1.f - a.beta2) * gv * gv;
-    m[i] = mi;
-    v[i] = vi;
+    const float mi = a.beta1 * to_f32<M>(m[i]) + (1.f - a.beta1) * gv;
+    const float vi = a.beta2 * to_f32<M>(v[i]) + (1.f - a.beta2) * gv * gv;
+    m[i] = from_f32<M>(mi);
+    v[i] = from_f32<M>(vi);
     const float mhat = mi / a.bc1;
     const float vhat = vi / a.bc2;
     w = w * (1.f - a.lr * a.wd) - a.lr * mhat / (sqrtf(vhat) + a.eps);
@@ -197,10 +204,10 @@ template <> struct Vec4<__nv_bfloat16> {
     *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]));
   }
 };
-template <typename P, typename G>
+template <typename P, typename G, typename M>
 __global__ void __launch_bounds__(256)
-adamw_vec4_kernel(P* __restrict__ p, float* __restrict__ master, G* __restrict__ g, float* __restrict__ m,
-                  float* __restrict__ v, long long n4, AdamArgs a, const float* __restrict__ sumsq, int zero_grad) {
+adamw_vec4_kernel(P* __restrict__ p, float* __restrict__ master, G* __restrict__ g, M* __restrict__ m,
+                  M* __restrict__ v, long long n4, AdamArgs a, const float* __restrict__ sumsq, int zero_grad) {
   float scale = a.grad_scale;
   if (sumsq != nullptr && a.max_norm > 0.f) {
     const float norm = sqrtf(*sumsq) * a.grad_scale;
@@ -213,8 +220,8 @@ adamw_vec4_kernel(P* __restrict__ p, float* __restrict__ master, G* __restrict__
     float gv[4], w[4], mi[4], vi[4];
     Vec4<G>::load(g + o, gv);
     if (master != nullptr) Vec4<float>::load(master + o, w); else Vec4<P>::load(p + o, w);
-    Vec4<float>::load(m + o, mi);
-    Vec4<float>::load(v + o, vi);
+    Vec4<M>::load(m + o, mi);
+    Vec4<M>::load(v + o, vi);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float gj = gv[j] * scale;
@@ -223,8 +230,8 @@ adamw_vec4_kernel(P* __restrict__ p, float* __restrict__ master, G* __restrict__
       w[j] = w[j] * decay - a.lr * (mi[j] * inv_bc1) / (sqrtf(vi[j] * inv_bc2) + a.eps);
       gv[j] = 0.f;
     }
-    Vec4<float>::store(m + o, mi);
-    Vec4<float>::store(v + o, vi);
+    Vec4<M>::store(m + o, mi);
+    Vec4<M>::store(v + o, vi);
     if (master != nullptr) Vec4<float>::store(master + o, w);
     Vec4<P>::store(p + o, w);
     if (zero_grad) Vec4<G>::store(g + o, gv);
@@ -260,42 +267,51 @@ B200_API int b200_sumsq(const void* g, long long n, int g_is_bf16, float* scratc
   return b200::check_launch("sumsq");
 }
 
-B200_API int b200_adamw(void* p, int p_is_bf16, float* master, void* g, int g_is_bf16, float* m, float* v,
-                        long long n, float lr, float beta1, float beta2, float eps, float wd, int step,
-                        float grad_scale, const float* sumsq, float max_norm, int zero_grad, void* stream) {
+template <typename M>
+static int launch_adamw(void* p, int p_is_bf16, float* master, void* g, int g_is_bf16, M* m, M* v, long long n, float lr,
+                        float beta1, float beta2, float eps, float wd, int step, float grad_scale, const float* sumsq,
+                        float max_norm, int zero_grad, void* stream) {
   if (n == 0) return 0;
   AdamArgs a;
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.wd = wd;
   a.bc1 = 1.f - powf(beta1, (float)step);
   a.bc2 = 1.f - powf(beta2, (float)step);
   a.grad_scale = grad_scale; a.max_norm = max_norm;
-  long long g64 = (n + 255) / 256;
-  int grid = (int)(g64 < (long long)b200::sm_count() * 16 ? g64 : (long long)b200::sm_count() * 16);
+  using bf = __nv_bfloat16;
   cudaStream_t st = (cudaStream_t)stream;
+  const long long cap = (long long)b200::sm_count() * 16;
   const uintptr_t all = (uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v | (uintptr_t)master;
   if ((all & 15) == 0 && (n & 3) == 0) {
-    const long long n4 = n / 4;
-    long long g4 = (n4 + 255) / 256;
-    int grid4 = (int)(g4 < (long long)b200::sm_count() * 16 ? g4 : (long long)b200::sm_count() * 16);
-    if (p_is_bf16 && g_is_bf16)
-      adamw_vec4_kernel<__nv_bfloat16, __nv_bfloat16><<<grid4, 256, 0, st>>>((__nv_bfloat16*)p, master, (__nv_bfloat16*)g, m, v, n4, a, sumsq, zero_grad);
-    else if (p_is_bf16)
-      adamw_vec4_kernel<__nv_bfloat16, float><<<grid4, 256, 0, st>>>((__nv_bfloat16*)p, master, (float*)g, m, v, n4, a, sumsq, zero_grad);
-    else if (g_is_bf16)
-      adamw_vec4_kernel<float, __nv_bfloat16><<<grid4, 256, 0, st>>>((float*)p, master, (__nv_bfloat16*)g, m, v, n4, a, sumsq, zero_grad);
-    else
-      adamw_vec4_kernel<float, float><<<grid4, 256, 0, st>>>((float*)p, master, (float*)g, m, v, n4, a, sumsq, zero_grad);
+    const long long n4 = n / 4, g4 = (n4 + 255) / 256;
+    const int grid4 = (int)(g4 < cap ? g4 : cap);
+    if (p_is_bf16 && g_is_bf16) adamw_vec4_kernel<bf, bf, M><<<grid4, 256, 0, st>>>((bf*)p, master, (bf*)g, m, v, n4, a, sumsq, zero_grad);
+    else if (p_is_bf16) adamw_vec4_kernel<bf, float, M><<<grid4, 256, 0, st>>>((bf*)p, master, (float*)g, m, v, n4, a, sumsq, zero_grad);
+    else if (g_is_bf16) adamw_vec4_kernel<float, bf, M><<<grid4, 256, 0, st>>>((float*)p, master, (bf*)g, m, v, n4, a, sumsq, zero_grad);
+    else adamw_vec4_kernel<float, float, M><<<grid4, 256, 0, st>>>((float*)p, master, (float*)g, m, v, n4, a, sumsq, zero_grad);
     b200::count_launch();
     return b200::check_launch("adamw");
   }
-  if (p_is_bf16 && g_is_bf16)
-    adamw_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>((__nv_bfloat16*)p, master, (const __nv_bfloat16*)g, m, v, n, a, sumsq, zero_grad, (__nv_bfloat16*)g);
-  else if (p_is_bf16)
-    adamw_kernel<__nv_bfloat16, float><<<grid, 256, 0, st>>>((__nv_bfloat16*)p, master, (const float*)g, m, v, n, a, sumsq, zero_grad, (float*)g);
-  else if (g_is_bf16)
-    adamw_kernel<float, __nv_bfloat16><<<grid, 256, 0, st>>>((float*)p, master, (const __nv_bfloat16*)g, m, v, n, a, sumsq, zero_grad, (__nv_bfloat16*)g);
-  else
-    adamw_kernel<float, float><<<grid, 256, 0, st>>>((float*)p, master, (const float*)g, m, v, n, a, sumsq, zero_grad, (float*)g);
+  const long long g64 = (n + 255) / 256;
+  const int grid = (int)(g64 < cap ? g64 : cap);
+  if (p_is_bf16 && g_is_bf16) adamw_kernel<bf, bf, M><<<grid, 256, 0, st>>>((bf*)p, master, (const bf*)g, m, v, n, a, sumsq, zero_grad, (bf*)g);
+  else if (p_is_bf16) adamw_kernel<bf, float, M><<<grid, 256, 0, st>>>((bf*)p, master, (const float*)g, m, v, n, a, sumsq, zero_grad, (float*)g);
+  else if (g_is_bf16) adamw_kernel<float, bf, M><<<grid, 256, 0, st>>>((float*)p, master, (const bf*)g, m, v, n, a, sumsq, zero_grad, (bf*)g);
+  else adamw_kernel<float, float, M><<<grid, 256, 0, st>>>((float*)p, master, (const float*)g, m, v, n, a, sumsq, zero_grad, (float*)g);
   b200::count_launch();
   return b200::check_launch("adamw");
+}
+
+B200_API int b200_adamw(void* p, int p_is_bf16, float* master, void* g, int g_is_bf16, float* m, float* v,
+                        long long n, float lr, float beta1, float beta2, float eps, float wd, int step,
+                        float grad_scale, const float* sumsq, float max_norm, int zero_grad, void* stream) {
+  return launch_adamw<float>(p, p_is_bf16, master, g, g_is_bf16, m, v, n, lr, beta1, beta2, eps, wd, step, grad_scale, sumsq,
+                             max_norm, zero_grad, stream);
+}
+
+// The same step with both moments stored in bf16.
+B200_API int b200_adamw_bf16m(void* p, int p_is_bf16, float* master, void* g, int g_is_bf16, void* m, void* v,
+                              long long n, float lr, float beta1, float beta2, float eps, float wd, int step,
+                              float grad_scale, const float* sumsq, float max_norm, int zero_grad, void* stream) {
+  return launch_adamw<__nv_bfloat16>(p, p_is_bf16, master, g, g_is_bf16, (__nv_bfloat16*)m, (__nv_bfloat16*)v, n, lr, beta1,
+                                     beta2, eps, wd, step, grad_scale, sumsq, max_norm, zero_grad, stream);
 }

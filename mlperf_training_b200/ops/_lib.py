@@ -54,6 +54,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_cross_entropy": [P, P, P, P, L, L, I, F, I, L, P],
         "b200_sumsq": [P, L, I, P, P, I, P],
         "b200_adamw": [P, I, P, P, I, P, P, L, F, F, F, F, F, I, F, P, F, I, P],
+        "b200_adamw_bf16m": [P, I, P, P, I, P, P, L, F, F, F, F, F, I, F, P, F, I, P],
         "b200_attn_fwd": [P, P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, L, L, L, L, F, I, I, P],
         "b200_quant_mxfp8": [P, L, I, I, P, P, I, P, P, I, P],
         "b200_gemm_mxfp8": [P, P, P, P, P, I, I, I, L, L, L, I, I, P, P, L, F, P],

@@ -370,7 +370,11 @@ def adamw_(p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, *
            grad_scale: float = 1.0, sumsq_buf: torch.Tensor | None = None, max_norm: float = 0.0,
            zero_grad: bool = False) -> None:
     """Fused AdamW on flat buffers.  ``sumsq_buf`` (device scalar holding the squared global
-    gradient norm, before ``grad_scale``) with ``max_norm > 0`` folds gradient clipping in."""
+    gradient norm, before ``grad_scale``) with ``max_norm > 0`` folds gradient clipping in.
+    ``m`` and ``v`` are both fp32 or both bf16; with bf16 the update is computed in fp32 from the stored
+    values and the new moments are rounded to nearest on the way back."""
+    if m.dtype != v.dtype or m.dtype not in (torch.float32, BF16):
+        raise ValueError("adamw_: moments must both be fp32 or both be bf16")
     if not use_kernels(p):
         gf = g.float() * grad_scale
         if sumsq_buf is not None and max_norm > 0:
@@ -379,10 +383,12 @@ def adamw_(p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, *
             if coef < 1:
                 gf = gf * coef
         w = master if master is not None else p.float()
-        m.mul_(beta1).add_(gf, alpha=1 - beta1)
-        v.mul_(beta2).addcmul_(gf, gf, value=1 - beta2)
-        mhat = m / (1 - beta1 ** step)
-        vhat = v / (1 - beta2 ** step)
+        mf = m.float().mul_(beta1).add_(gf, alpha=1 - beta1)
+        vf = v.float().mul_(beta2).addcmul_(gf, gf, value=1 - beta2)
+        m.copy_(mf)
+        v.copy_(vf)
+        mhat = mf / (1 - beta1 ** step)
+        vhat = vf / (1 - beta2 ** step)
         w = w * (1 - lr * weight_decay) - lr * mhat / (vhat.sqrt() + eps)
         if master is not None:
             master.copy_(w)
@@ -393,7 +399,7 @@ def adamw_(p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, *
     for t in (p, g, m, v):
         if not t.is_contiguous():
             raise ValueError("adamw_: flat contiguous buffers required")
-    call("b200_adamw", ptr(p), int(p.dtype == BF16), ptr(master), ptr(g), int(g.dtype == BF16), ptr(m), ptr(v),
+    call("b200_adamw_bf16m" if m.dtype == BF16 else "b200_adamw", ptr(p), int(p.dtype == BF16), ptr(master), ptr(g), int(g.dtype == BF16), ptr(m), ptr(v),
          p.numel(), float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), int(step),
          float(grad_scale), ptr(sumsq_buf), float(max_norm), int(zero_grad), stream_ptr())
 

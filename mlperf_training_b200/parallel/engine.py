@@ -8,7 +8,7 @@ block, one for the embeddings, one for the head), each padded to a multiple of
   forward and backward GEMMs read;
 * ``grad_buf[b]``   full fp32 ``main_grad`` - wgrad GEMM epilogues accumulate into it across
   micro-batches (``ops.functional._wgrad``);
-* ``m[b], v[b]``    fp32 Adam moments of this rank's 1/W shard only.
+* ``m[b], v[b]``    Adam moments of this rank's 1/W shard only (fp32, or bf16 with ``moment_dtype``).
 
 Step.  After the last micro-batch, bucket by bucket in the order backward finishes them:
 reduce-scatter the gradient bucket (average over data-parallel ranks), fused AdamW on the local
@@ -49,6 +49,9 @@ class OptimConfig:
     clip_grad: float = 1.0           # 0 disables clipping
     grad_dtype: torch.dtype = torch.float32
     master_weights: bool = False      # keep an fp32 master copy of the local shard
+    moment_dtype: torch.dtype = torch.float32   # torch.bfloat16 halves the Adam state (Megatron's precision-aware
+    #                                             optimizer, exp_avg_dtype / exp_avg_sq_dtype in
+    #                                             small_llm_moe_pretraining/primus/conf/gpt_oss_20B-MXFP4-deosc-mlperf-pretrain.yaml:79)
 
 
 def default_bucket_of(name: str) -> str:
@@ -102,8 +105,8 @@ class Bucket:
         else:
             self.param_buf = torch.zeros(self.numel, dtype=dtype, device=device)
             self.grad_buf = torch.zeros(self.numel, dtype=opt.grad_dtype, device=device)
-        self.m = torch.zeros(self.shard, dtype=torch.float32, device=device)
-        self.v = torch.zeros(self.shard, dtype=torch.float32, device=device)
+        self.m = torch.zeros(self.shard, dtype=opt.moment_dtype, device=device)
+        self.v = torch.zeros(self.shard, dtype=opt.moment_dtype, device=device)
         self.master = None
         self.offsets = offs
         for (name, p), o in zip(self.params, offs):
@@ -180,7 +183,8 @@ class ZeroEngine:
         for k in sorted(groups):
             local = k.endswith("_ep") or "_ep_" in k
             fused = (comm == "fused" and self.world > 1 and not local and device.type == "cuda"
-                     and groups[k][0][1].dtype == torch.bfloat16)      # the peer-memory step kernels move bf16 parameters
+                     and groups[k][0][1].dtype == torch.bfloat16       # the peer-memory step kernels move bf16 parameters
+                     and opt.moment_dtype == torch.float32)            # and keep fp32 moments
             b = Bucket(k, groups[k], 1 if local else self.world, 0 if local else self.rank, opt, device,
                        symmetric_group=(group if group is not None else dist.group.WORLD) if fused else None)
             b.local_only = local

@@ -48,6 +48,9 @@ class RunConfig:
     adam_beta1: float = 0.9
     adam_beta2: float = 0.95
     adam_eps: float = 1e-5
+    use_precision_aware_optimizer: bool = False   # with exp_avg_dtype / exp_avg_sq_dtype bf16: bf16 Adam moments
+    exp_avg_dtype: str = "fp32"
+    exp_avg_sq_dtype: str = "fp32"
     clip_grad: float = 1.0
     seed: int = 0
     eval_interval: int = 0
@@ -118,6 +121,17 @@ def _dist_info():
     return 0, 1
 
 
+def _moment_dtype(rc) -> torch.dtype:
+    if not rc.use_precision_aware_optimizer:
+        return torch.float32
+    kinds = {str(rc.exp_avg_dtype).lower(), str(rc.exp_avg_sq_dtype).lower()}
+    if kinds <= {"fp32", "float32"}:
+        return torch.float32
+    if kinds <= {"bf16", "bfloat16"}:
+        return torch.bfloat16
+    raise ValueError(f"exp_avg_dtype / exp_avg_sq_dtype {sorted(kinds)}: both moments are kept in one of fp32, bf16")
+
+
 def run(exp: dict, device: str | None = None, stream=None) -> dict:
     rc = RunConfig.from_dict(exp)
     rank, world = _dist_info()
@@ -155,7 +169,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         raise ValueError("global_batch must be divisible by the data-parallel size")
     local_batch = rc.global_batch // dp_world
     opt = OptimConfig(lr=rc.lr, beta1=rc.adam_beta1, beta2=rc.adam_beta2, eps=rc.adam_eps,
-                      weight_decay=rc.weight_decay, clip_grad=rc.clip_grad)
+                      weight_decay=rc.weight_decay, clip_grad=rc.clip_grad, moment_dtype=_moment_dtype(rc))
     tc = TrainConfig(micro_batch=rc.micro_batch, local_batch=local_batch, warmup_steps=rc.lr_warmup_iters,
                      decay_steps=rc.lr_decay_iters, min_lr_ratio=rc.min_lr_ratio, seed=rc.seed, comm=rc.comm)
     if tp_size == 1 and replicate > 1 and world > 1:

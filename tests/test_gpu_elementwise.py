@@ -105,6 +105,31 @@ def test_cross_entropy(V):
     assert lg[3].abs().max().item() == 0
 
 
+@pytest.mark.parametrize("n", [100003, 262144])
+@pytest.mark.parametrize("p_bf16,g_bf16,use_master", [(True, False, False), (True, True, True), (False, False, False)])
+def test_adamw_bf16_moments(p_bf16, g_bf16, use_master, n):
+    """bf16 moments: the kernel against the fp32 PyTorch body applied to the same bf16 state (scalar tail
+    and 4-wide paths); each stored moment may differ by one bf16 rounding."""
+    torch.manual_seed(6)
+    p = torch.randn(n)
+    g = torch.randn(n) * 0.5
+    pd = p.bfloat16() if p_bf16 else p.clone()
+    gd = g.bfloat16() if g_bf16 else g.clone()
+    state_c = dict(p=pd.clone(), g=gd.clone(), m=torch.zeros(n, dtype=torch.bfloat16), v=torch.zeros(n, dtype=torch.bfloat16),
+                   master=pd.float().clone() if use_master else None)
+    state_g = {k: (None if t is None else t.cuda()) for k, t in state_c.items()}
+    for step in (1, 2, 3):
+        for st in (state_c, state_g):
+            kernels.adamw_(st["p"], st["g"], st["m"], st["v"], lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8,
+                           weight_decay=0.1, step=step, master=st["master"])
+    torch.cuda.synchronize()
+    assert state_g["m"].dtype == torch.bfloat16
+    _close(state_g["m"].float(), state_c["m"].float(), 2 ** -7, "m")
+    _close(state_g["v"].float(), state_c["v"].float(), 2 ** -7, "v")
+    _close(state_g["p"], state_c["p"], 1e-2 if p_bf16 else 1e-3, "p")
+    _lib.check_status("elementwise")
+
+
 @pytest.mark.parametrize("p_bf16,g_bf16,use_master", [(True, False, False), (True, True, True), (False, False, False)])
 def test_adamw_and_clip(p_bf16, g_bf16, use_master):
     torch.manual_seed(4)

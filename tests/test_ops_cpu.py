@@ -2,6 +2,8 @@
 the GPU tests, so they are checked independently here)."""
 import math
 
+import pytest
+
 import torch
 import torch.nn.functional as F
 
@@ -154,3 +156,55 @@ def test_activation_recompute_matches_plain_backward():
     for l, g in out[1:]:
         assert l == out[0][0]
         assert all(torch.equal(a, b) for a, b in zip(g, out[0][1]))
+
+
+def test_adamw_bf16_moments_track_fp32_moments():
+    torch.manual_seed(5)
+    n = 4096
+    p32, p16 = torch.randn(n), None
+    p16 = p32.clone()
+    m32, v32 = torch.zeros(n), torch.zeros(n)
+    m16, v16 = torch.zeros(n, dtype=torch.bfloat16), torch.zeros(n, dtype=torch.bfloat16)
+    for step in range(1, 9):
+        g = torch.randn(n)
+        kw = dict(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+        kernels.adamw_(p32, g, m32, v32, **kw)
+        kernels.adamw_(p16, g, m16, v16, **kw)
+    assert m16.dtype == torch.bfloat16 and v16.dtype == torch.bfloat16
+    # one bf16 rounding per step on each moment: relative error of a few 2^-8, the weights stay close
+    assert (m16.float() - m32).abs().max().item() < 0.03
+    assert ((v16.float() - v32).abs() / v32).max().item() < 0.03
+    assert (p16 - p32).abs().max().item() < 5e-3
+    with pytest.raises(ValueError):
+        kernels.adamw_(p16, g, m16, v32, **kw)
+
+
+def test_engine_bf16_moments_train():
+    from mlperf_training_b200.models.gpt import GPT, GPTConfig
+    from mlperf_training_b200.parallel.engine import OptimConfig, ZeroEngine
+    cfg = GPTConfig(n_layers=2, hidden=32, n_heads=2, n_kv_heads=1, head_dim=16, ffn_hidden=64, vocab_size=64, seq_len=16, dtype="fp32")
+    tok = torch.randint(0, 64, (4, 17), generator=torch.Generator().manual_seed(0))
+    curves = []
+    for md in (torch.float32, torch.bfloat16):
+        model = GPT(cfg, seed=3)
+        eng = ZeroEngine(model, OptimConfig(lr=3e-3, weight_decay=0.0, clip_grad=1.0, moment_dtype=md))
+        assert all(b.m.dtype == md and b.v.dtype == md for b in eng.buckets)
+        losses = []
+        for _ in range(12):
+            loss = model(tok[:, :-1], tok[:, 1:])
+            loss.backward()
+            eng.step()
+            losses.append(loss.item())
+        curves.append(losses)
+        eng.load_optimizer_state(eng.optimizer_state())
+    assert curves[1][-1] < curves[1][0] - 0.3
+    assert abs(curves[1][-1] - curves[0][-1]) < 0.05
+
+
+def test_run_config_selects_moment_dtype():
+    from mlperf_training_b200.trainer.loop import RunConfig, _moment_dtype
+    assert _moment_dtype(RunConfig()) == torch.float32
+    assert _moment_dtype(RunConfig(use_precision_aware_optimizer=True, exp_avg_dtype="bf16", exp_avg_sq_dtype="bf16")) == torch.bfloat16
+    assert _moment_dtype(RunConfig(use_precision_aware_optimizer=False, exp_avg_dtype="bf16", exp_avg_sq_dtype="bf16")) == torch.float32
+    with pytest.raises(ValueError):
+        _moment_dtype(RunConfig(use_precision_aware_optimizer=True, exp_avg_dtype="fp16", exp_avg_sq_dtype="bf16"))
