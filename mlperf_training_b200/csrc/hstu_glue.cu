@@ -1,0 +1,219 @@
+// HSTU layer glue between the jagged attention and the output projection, one pass each way:
+//
+//   forward   u = silu(u_raw);  n = LayerNorm(attn) * w + b;  cat = [u | attn | u * n]        ([T, 3D] bf16)
+//   backward  from dcat = [du' | da' | dy]:
+//             du_raw = (du' + dy * n) * silu'(u_raw)
+//             dattn  = da' + LayerNorm_bwd(dy * u)
+//             dw    += sum_t (dy * u) * xhat,   db += sum_t dy * u
+//
+// u_raw is a column block of the fused uvqk projection (row pitch given), so the kernel reads it in
+// place; du_raw is written with its own pitch so it can land inside the gradient of that projection.
+// One warp owns a row (D a multiple of 256, at most 768: a lane keeps D/256 16-byte vectors of each
+// operand in registers); the weight / bias gradients are kept per lane in registers over all rows the
+// warp visits, summed over the CTA's warps in a fixed order and written as one partial row per CTA
+// that a second kernel adds up: no atomics, bit-reproducible.
+//
+// Replaces the chain the reference fuses as "layer norm * u (+ dropout)" before the output linear
+// (generative_recommenders/ops/triton/triton_hstu_linear.py: _ln_mul_dropout_fwd / _ln_mul_dropout_bwd,
+// with concat_ux) and the SiLU of u (generative_recommenders/ops/hstu_compute.py: hstu_preprocess_and_attention).
+#include "common.cuh"
+#include "runtime.h"
+
+namespace {
+
+constexpr int GV = 3;   // vectors of 8 per lane -> D <= 768
+
+B200_DEVICE void ld8(const __nv_bfloat16* p, float (&f)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+B200_DEVICE void st8(__nv_bfloat16* p, const float (&f)[8]) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
+                                            pack_bf16x2(f[6], f[7]));
+}
+B200_DEVICE float rbf(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__global__ void __launch_bounds__(256)
+gate_cat_fwd_kernel(const __nv_bfloat16* __restrict__ u_raw, long long ld_u, const __nv_bfloat16* __restrict__ attn,
+                    const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
+                    __nv_bfloat16* __restrict__ cat, float* __restrict__ mean_out, float* __restrict__ rstd_out, int T,
+                    int D, float eps) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nv = D / 256;
+  for (long long row = (long long)blockIdx.x * 8 + warp; row < T; row += (long long)gridDim.x * 8) {
+    float a[GV][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < GV; ++i)
+      if (i < nv) {
+        ld8(attn + row * D + (lane + 32 * i) * 8, a[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += a[i][j];
+      }
+    const float mean = warp_sum(s) / D;
+    float var = 0.f;
+#pragma unroll
+    for (int i = 0; i < GV; ++i)
+      if (i < nv) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float d = a[i][j] - mean; var += d * d; }
+      }
+    const float rstd = rsqrtf(warp_sum(var) / D + eps);
+    if (lane == 0) { mean_out[row] = mean; rstd_out[row] = rstd; }
+    __nv_bfloat16* out = cat + row * 3 * D;
+#pragma unroll
+    for (int i = 0; i < GV; ++i)
+      if (i < nv) {
+        const int c = (lane + 32 * i) * 8;
+        float ur[8], w8[8], b8[8], u[8], y[8];
+        ld8(u_raw + row * ld_u + c, ur);
+        ld8(w + c, w8);
+        ld8(b + c, b8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          u[j] = rbf(ur[j] / (1.f + __expf(-ur[j])));
+          const float n = rbf((a[i][j] - mean) * rstd * w8[j] + b8[j]);
+          y[j] = u[j] * n;
+        }
+        st8(out + c, u);
+        st8(out + D + c, a[i]);
+        st8(out + 2 * D + c, y);
+      }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+gate_cat_bwd_kernel(const __nv_bfloat16* __restrict__ dcat, const __nv_bfloat16* __restrict__ u_raw, long long ld_u,
+                    const __nv_bfloat16* __restrict__ attn, const __nv_bfloat16* __restrict__ w,
+                    const __nv_bfloat16* __restrict__ b, const float* __restrict__ mean_in,
+                    const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ du_raw, long long ld_du,
+                    __nv_bfloat16* __restrict__ dattn, float* __restrict__ partial, int T, int D) {
+  extern __shared__ float acc[];   // [8 warps][2][D]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nv = D / 256;
+  float gw[GV][8], gb[GV][8];
+#pragma unroll
+  for (int i = 0; i < GV; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { gw[i][j] = 0.f; gb[i][j] = 0.f; }
+  for (long long row = (long long)blockIdx.x * 8 + warp; row < T; row += (long long)gridDim.x * 8) {
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    const __nv_bfloat16* dc = dcat + row * 3 * D;
+    float xn[GV][8], g[GV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < GV; ++i)
+      if (i < nv) {
+        const int c = (lane + 32 * i) * 8;
+        float ur[8], a8[8], w8[8], b8[8], dy[8], du[8], o[8];
+        ld8(u_raw + row * ld_u + c, ur);
+        ld8(attn + row * D + c, a8);
+        ld8(w + c, w8);
+        ld8(b + c, b8);
+        ld8(dc + 2 * D + c, dy);
+        ld8(dc + c, du);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float sg = 1.f / (1.f + __expf(-ur[j]));
+          const float u = rbf(ur[j] * sg);
+          xn[i][j] = (a8[j] - mean) * rstd;
+          const float n = rbf(xn[i][j] * w8[j] + b8[j]);
+          const float dn = dy[j] * u;
+          gw[i][j] += dn * xn[i][j];
+          gb[i][j] += dn;
+          g[i][j] = dn * w8[j];
+          s1 += g[i][j] * xn[i][j];
+          s2 += g[i][j];
+          o[j] = (du[j] + dy[j] * n) * (sg * (1.f + ur[j] * (1.f - sg)));
+        }
+        st8(du_raw + row * ld_du + c, o);
+      }
+    s1 = warp_sum(s1) / D;
+    s2 = warp_sum(s2) / D;
+#pragma unroll
+    for (int i = 0; i < GV; ++i)
+      if (i < nv) {
+        const int c = (lane + 32 * i) * 8;
+        float da[8], o[8];
+        ld8(dc + D + c, da);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = da[j] + rstd * (g[i][j] - xn[i][j] * s1 - s2);
+        st8(dattn + row * D + c, o);
+      }
+  }
+  float* mine = acc + (long long)warp * 2 * D;
+#pragma unroll
+  for (int i = 0; i < GV; ++i)
+    if (i < nv) {
+      const int c = (lane + 32 * i) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { mine[c + j] = gw[i][j]; mine[D + c + j] = gb[i][j]; }
+    }
+  __syncthreads();
+  float* pw = partial + (long long)blockIdx.x * 2 * D;
+  for (int c = threadIdx.x; c < 2 * D; c += 256) {
+    float sum = 0.f;
+    for (int k = 0; k < 8; ++k) sum += acc[(long long)k * 2 * D + c];
+    pw[c] = sum;
+  }
+}
+
+__global__ void gate_cat_reduce_kernel(const float* __restrict__ partial, int nparts, int D, float* __restrict__ dw,
+                                       float* __restrict__ db, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float sw = 0.f, sb = 0.f;
+  for (int p = 0; p < nparts; ++p) {
+    sw += partial[(long long)p * 2 * D + c];
+    sb += partial[(long long)p * 2 * D + D + c];
+  }
+  dw[c] = accumulate ? dw[c] + sw : sw;
+  db[c] = accumulate ? db[c] + sb : sb;
+}
+
+int gate_grid(int T) {
+  int grid = (T + 7) / 8;
+  const int cap = b200::sm_count() * 4;
+  return grid < cap ? (grid < 1 ? 1 : grid) : cap;
+}
+
+bool gate_ok(int D, long long ld_u) { return D % 256 == 0 && D >= 256 && D <= 256 * GV && ld_u % 8 == 0; }
+
+}  // namespace
+
+// fp32 scratch elements b200_hstu_gate_cat_bwd needs for T rows of width D.
+B200_API long long b200_hstu_gate_cat_scratch_elems(int T, int D) { return (long long)gate_grid(T) * 2 * D; }
+
+// cat[T, 3D] = [silu(u_raw) | attn | silu(u_raw) * LayerNorm(attn)];  mean / rstd [T] fp32 are kept for backward.
+B200_API int b200_hstu_gate_cat_fwd(const void* u_raw, long long ld_u, const void* attn, const void* w, const void* b,
+                                    void* cat, float* mean, float* rstd, int T, int D, float eps, void* stream) {
+  if (!gate_ok(D, ld_u)) return b200::fail(900, "hstu_gate_cat_fwd: D=%d must be 256, 512 or 768 and the pitch %lld a multiple of 8", D, ld_u);
+  if (T <= 0) return 0;
+  gate_cat_fwd_kernel<<<gate_grid(T), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)u_raw, ld_u, (const __nv_bfloat16*)attn,
+                                                                      (const __nv_bfloat16*)w, (const __nv_bfloat16*)b,
+                                                                      (__nv_bfloat16*)cat, mean, rstd, T, D, eps);
+  b200::count_launch();
+  return b200::check_launch("hstu_gate_cat_fwd");
+}
+
+// du_raw (row pitch ld_du) and dattn [T, D] from dcat [T, 3D]; dw / db fp32 [D] written, or added to when
+// accumulate != 0.  scratch: b200_hstu_gate_cat_scratch_elems(T, D) floats.
+B200_API int b200_hstu_gate_cat_bwd(const void* dcat, const void* u_raw, long long ld_u, const void* attn, const void* w,
+                                    const void* b, const float* mean, const float* rstd, void* du_raw, long long ld_du,
+                                    void* dattn, float* dw, float* db, float* scratch, int T, int D, int accumulate,
+                                    void* stream) {
+  if (!gate_ok(D, ld_u) || ld_du % 8 != 0)
+    return b200::fail(901, "hstu_gate_cat_bwd: D=%d must be 256, 512 or 768 and the pitches %lld / %lld multiples of 8", D, ld_u, ld_du);
+  if (T <= 0) return 0;
+  const int grid = gate_grid(T);
+  cudaStream_t st = (cudaStream_t)stream;
+  gate_cat_bwd_kernel<<<grid, 256, 8 * 2 * D * sizeof(float), st>>>(
+      (const __nv_bfloat16*)dcat, (const __nv_bfloat16*)u_raw, ld_u, (const __nv_bfloat16*)attn, (const __nv_bfloat16*)w,
+      (const __nv_bfloat16*)b, mean, rstd, (__nv_bfloat16*)du_raw, ld_du, (__nv_bfloat16*)dattn, scratch, T, D);
+  b200::count_launch();
+  if (int r = b200::check_launch("hstu_gate_cat_bwd")) return r;
+  gate_cat_reduce_kernel<<<(D + 255) / 256, 256, 0, st>>>(scratch, grid, D, dw, db, accumulate);
+  b200::count_launch();
+  return b200::check_launch("hstu_gate_cat_reduce");
+}

@@ -29,7 +29,7 @@ import torch.nn as nn
 import torch.nn.functional as TF
 
 from ..ops import functional as F
-from ..ops.hstu_ops import hstu_attention
+from ..ops.hstu_ops import GateCatFn, gate_cat_eligible, hstu_attention
 
 
 @dataclass
@@ -143,6 +143,7 @@ class STULayer(nn.Module):
     def __init__(self, cfg: HSTUConfig, dtype, device):
         super().__init__()
         self.cfg = cfg
+        self.fuse_glue = True
         d, h = cfg.dim, cfg.heads
         self.split = [h * cfg.d_v, h * cfg.d_v, h * cfg.d_qk, h * cfg.d_qk]       # u, v, q, k
         self.uvqk_weight = nn.Parameter(torch.empty(sum(self.split), d, dtype=dtype, device=device))
@@ -163,14 +164,18 @@ class STULayer(nn.Module):
         # one split (its backward is a single concatenation; four slices would each build a zero-filled
         # gradient of the whole uvqk matrix)
         u_raw, v_raw, q_raw, k_raw = torch.split(uvqk, list(self.split), dim=1)
-        u = TF.silu(u_raw)
         v = v_raw.unflatten(-1, (h, cfg.d_v))
         q = q_raw.unflatten(-1, (h, cfg.d_qk))
         k = k_raw.unflatten(-1, (h, cfg.d_qk))
         attn = hstu_attention(q, k, v, offsets, cfg.max_seq_len + cfg.contextual, cfg.d_qk ** -0.5, num_targets,
                               cfg.contextual).reshape(x.shape[0], h * cfg.d_v)
-        y = u * F.layer_norm(attn, self.out_norm_w, self.out_norm_b, 1e-6)
-        cat = torch.cat([u, attn, y], dim=1)
+        if self.fuse_glue and gate_cat_eligible(u_raw, attn):
+            # SiLU(u), the layer norm of the attention output, their product and the concatenation in one kernel
+            cat = GateCatFn.apply(u_raw, attn, self.out_norm_w, self.out_norm_b, 1e-6)
+        else:
+            u = TF.silu(u_raw)
+            y = u * F.layer_norm(attn, self.out_norm_w, self.out_norm_b, 1e-6)
+            cat = torch.cat([u, attn, y], dim=1)
         if cfg.linear_dropout > 0 and self.training:
             cat = TF.dropout(cat, cfg.linear_dropout)
         return F.linear(cat.contiguous(), self.out_weight, None, x, cfg.precision)

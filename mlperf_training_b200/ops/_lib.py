@@ -67,6 +67,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_zero_reduce_scatter": [P, I, I, L, L, F, P, P, P],
         "b200_zero_adamw_all_gather": [P, I, I, L, L, P, P, P, P, F, F, F, F, F, I, F, P, F, I, P],
         "b200_hstu_attn_fwd": [P, P, P, P, P, P, I, L, I, I, I, I, L, L, L, L, F, P],
+        "b200_hstu_gate_cat_fwd": [P, L, P, P, P, P, P, P, I, I, F, P],
+        "b200_hstu_gate_cat_bwd": [P, P, L, P, P, P, P, P, P, L, P, P, P, P, I, I, I, P],
         "b200_hstu_attn_bwd": [P, P, P, P, P, P, P, P, P, I, L, I, I, I, I, L, L, L, L, L, L, F, P],
         "b200_scatter_rows_to_peers": [P, P, P, P, L, I, P, I, L, P, P],
         "b200_gather_rows_from_peers": [P, P, P, L, I, P, I, L, P],
@@ -91,6 +93,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn.argtypes = argtypes
         fn.restype = c_int
     lib.b200_norm_bwd_scratch_elems.argtypes = [I, I]
+    lib.b200_hstu_gate_cat_scratch_elems.argtypes = [I, I]
+    lib.b200_hstu_gate_cat_scratch_elems.restype = c_ll
     lib.b200_norm_bwd_scratch_elems.restype = c_ll
     lib.b200_sumsq_scratch_elems.restype = c_int
     if hasattr(lib, "b200_zero_grid"):

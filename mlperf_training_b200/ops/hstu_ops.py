@@ -11,6 +11,7 @@ from __future__ import annotations
 import torch
 from torch.autograd import Function
 
+from . import _lib
 from ._lib import call, ptr, stream_ptr, use_kernels
 
 
@@ -86,3 +87,60 @@ class HstuAttentionFn(Function):
 
 def hstu_attention(q, k, v, offsets, max_len: int, alpha: float, num_targets=None, contextual: int = 0):
     return HstuAttentionFn.apply(q, k, v, offsets, max_len, alpha, num_targets, contextual)
+
+
+# --------------------------------------------------------------------------------------
+# glue between the attention and the output projection
+# --------------------------------------------------------------------------------------
+def gate_cat_reference(u_raw, attn, weight, bias, eps: float = 1e-6):
+    """``[silu(u_raw) | attn | silu(u_raw) * LayerNorm(attn)]`` with plain torch operators."""
+    u = torch.nn.functional.silu(u_raw)
+    n = torch.nn.functional.layer_norm(attn.float(), (attn.shape[-1],), weight.float(), bias.float(), eps).to(attn.dtype)
+    return torch.cat([u, attn, u * n], dim=1)
+
+
+def gate_cat_eligible(u_raw: torch.Tensor, attn: torch.Tensor) -> bool:
+    D = attn.shape[-1]
+    return (use_kernels(attn) and attn.dtype == torch.bfloat16 and D in (256, 512, 768) and u_raw.stride(1) == 1
+            and u_raw.stride(0) % 8 == 0 and u_raw.data_ptr() % 16 == 0)
+
+
+class GateCatFn(Function):
+    """The concatenated input of the HSTU output projection in one pass each way (SiLU of u, layer norm
+    of the attention output, their product, the concatenation; backward recomputes all three from
+    ``u_raw`` and ``attn``).  ``u_raw`` may be a column block of the fused uvqk projection."""
+
+    @staticmethod
+    def forward(ctx, u_raw, attn, weight, bias, eps):
+        T, D = attn.shape
+        attn = attn.contiguous()
+        w, b = weight.to(torch.bfloat16).contiguous(), bias.to(torch.bfloat16).contiguous()
+        cat = torch.empty((T, 3 * D), dtype=attn.dtype, device=attn.device)
+        mean = torch.empty(T, dtype=torch.float32, device=attn.device)
+        rstd = torch.empty(T, dtype=torch.float32, device=attn.device)
+        call("b200_hstu_gate_cat_fwd", ptr(u_raw), u_raw.stride(0), ptr(attn), ptr(w), ptr(b), ptr(cat), ptr(mean), ptr(rstd),
+             T, D, float(eps), stream_ptr())
+        ctx.save_for_backward(u_raw, attn, w, b, mean, rstd)
+        ctx.refs = (weight, bias)
+        return cat
+
+    @staticmethod
+    def backward(ctx, dcat):
+        from .functional import _vec_grad
+        u_raw, attn, w, b, mean, rstd = ctx.saved_tensors
+        T, D = attn.shape
+        dcat = dcat.contiguous()
+        du = torch.empty((T, D), dtype=attn.dtype, device=attn.device)
+        da = torch.empty_like(attn)
+        dw = torch.empty(D, dtype=torch.float32, device=attn.device)
+        db = torch.empty(D, dtype=torch.float32, device=attn.device)
+        scratch = torch.empty(_lib.load().b200_hstu_gate_cat_scratch_elems(T, D), dtype=torch.float32, device=attn.device)
+        call("b200_hstu_gate_cat_bwd", ptr(dcat), ptr(u_raw), u_raw.stride(0), ptr(attn), ptr(w), ptr(b), ptr(mean), ptr(rstd),
+             ptr(du), du.stride(0), ptr(da), ptr(dw), ptr(db), ptr(scratch), T, D, 0, stream_ptr())
+        return du, da, _vec_grad(ctx.refs[0], dw), _vec_grad(ctx.refs[1], db), None
+
+
+def gate_cat(u_raw, attn, weight, bias, eps: float = 1e-6):
+    if gate_cat_eligible(u_raw, attn):
+        return GateCatFn.apply(u_raw, attn, weight, bias, eps)
+    return gate_cat_reference(u_raw, attn, weight, bias, eps)

@@ -88,3 +88,67 @@ def test_hstu_train_steps_on_gpu():
     assert all(l == l for l in out["losses"])
     assert sum(out["losses"][-5:]) < sum(out["losses"][:5])
     assert out["aucs"][-1] > 0.55
+
+
+@pytest.mark.parametrize("T,D,pitch", [(1000, 512, 2048), (37, 256, 256), (4099, 768, 1536)])
+def test_gate_cat_kernel_against_fp32_reference(T, D, pitch):
+    """silu(u) | attn | silu(u) * LN(attn): forward and all four gradients against fp32 autograd."""
+    from mlperf_training_b200.ops.hstu_ops import GateCatFn, gate_cat_eligible
+    torch.manual_seed(T)
+    wide = torch.randn(T, pitch, device="cuda").bfloat16()
+    u_raw = wide[:, :D]
+    attn = (torch.randn(T, D, device="cuda") * 2 + 0.3).bfloat16()
+    w = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16()
+    b = (0.1 * torch.randn(D, device="cuda")).bfloat16()
+    dcat = torch.randn(T, 3 * D, device="cuda").bfloat16()
+    assert gate_cat_eligible(u_raw, attn)
+    leaves = [t.clone().requires_grad_(True) for t in (u_raw.contiguous(), attn, w, b)]
+    uk = wide.clone().requires_grad_(True)
+    ak, wk, bk = (t.clone().requires_grad_(True) for t in (attn, w, b))
+    cat = GateCatFn.apply(uk[:, :D], ak, wk, bk, 1e-6)
+    cat.backward(dcat)
+    torch.cuda.synchronize()
+    _lib.check_status("gate_cat")
+    uf, af, wf, bf = (t.detach().float().requires_grad_(True) for t in leaves)
+    u = torch.nn.functional.silu(uf)
+    n = torch.nn.functional.layer_norm(af, (D,), wf, bf, 1e-6)
+    ref = torch.cat([u, af, u * n], dim=1)
+    ref.backward(dcat.float())
+
+    def close(got, want, tol, what):
+        err = (got.float() - want).abs().max().item()
+        scale = want.abs().max().item() + 1e-6
+        assert err <= tol * scale, f"{what}: err {err} scale {scale}"
+    close(cat, ref.detach(), 2e-2, "cat")
+    close(uk.grad[:, :D], uf.grad, 2e-2, "du_raw")
+    assert uk.grad[:, D:].abs().max().item() == 0 if pitch > D else True
+    close(ak.grad, af.grad, 2e-2, "dattn")
+    close(wk.grad, wf.grad, 2e-2, "dw")
+    close(bk.grad, bf.grad, 2e-2, "db")
+
+
+def test_stu_layer_fused_glue_matches_eager_glue():
+    from mlperf_training_b200.models.hstu import HSTUConfig, STULayer
+    cfg = HSTUConfig(layers=1, dim=512, heads=4, d_qk=128, d_v=128, max_seq_len=512, emb_dim=64, dtype="bf16", precision="bf16",
+                     linear_dropout=0.0)
+    torch.manual_seed(0)
+    layer = STULayer(cfg, torch.bfloat16, "cuda")
+    lengths = [100, 256, 28]
+    rows = 384
+    offs = torch.tensor([0, 100, 356, 384], dtype=torch.int32, device="cuda")
+    nt = torch.tensor([1, 2, 1], dtype=torch.int32, device="cuda")
+    x0 = torch.randn(rows, 512, device="cuda").bfloat16()
+    dy = torch.randn(rows, 512, device="cuda").bfloat16()
+    outs = []
+    for fuse in (False, True):
+        layer.fuse_glue = fuse
+        layer.zero_grad(set_to_none=True)
+        x = x0.clone().requires_grad_(True)
+        y = layer(x, offs, nt, rows)
+        y.backward(dy)
+        outs.append((y.detach().float(), x.grad.float(), layer.out_norm_w.grad.float(), layer.uvqk_weight.grad.float()))
+    torch.cuda.synchronize()
+    _lib.check_status("stu_layer")
+    for a, b, what in zip(outs[0], outs[1], ("y", "dx", "dnorm_w", "duvqk_w")):
+        err = (a - b).abs().max().item()
+        assert err <= 2e-2 * (a.abs().max().item() + 1e-6), f"{what}: {err}"
