@@ -13,9 +13,15 @@
 // warp visits, summed over the CTA's warps in a fixed order and written as one partial row per CTA
 // that a second kernel adds up: no atomics, bit-reproducible.
 //
+// Dropout of the concatenation (rate p, survivors scaled by 1 / (1 - p)) is part of both passes: the keep
+// mask comes from a Philox stream keyed by (seed, row, lane), so backward regenerates it instead of
+// reading a stored mask.
+//
 // Replaces the chain the reference fuses as "layer norm * u (+ dropout)" before the output linear
 // (generative_recommenders/ops/triton/triton_hstu_linear.py: _ln_mul_dropout_fwd / _ln_mul_dropout_bwd,
 // with concat_ux) and the SiLU of u (generative_recommenders/ops/hstu_compute.py: hstu_preprocess_and_attention).
+#include <curand_kernel.h>
+
 #include "common.cuh"
 #include "runtime.h"
 
@@ -34,11 +40,37 @@ B200_DEVICE void st8(__nv_bfloat16* p, const float (&f)[8]) {
 }
 B200_DEVICE float rbf(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
+// Keep masks of one row for this lane: bit (8 * s + j) of keep[i] covers element j of vector i in section s
+// (0 = u, 1 = attn, 2 = y).  Forward and backward call this with the same (seed, row, lane) and get the same bits.
+B200_DEVICE void draw_keep(unsigned (&keep)[GV], int nv, float p, unsigned long long seed, long long row, int lane) {
+#pragma unroll
+  for (int i = 0; i < GV; ++i) keep[i] = 0xffffffu;
+  if (p <= 0.f) return;
+  curandStatePhilox4_32_10_t st;
+  curand_init(seed, (unsigned long long)row * 32 + lane, 0, &st);
+#pragma unroll
+  for (int i = 0; i < GV; ++i)
+    if (i < nv) {
+      unsigned m = 0;
+#pragma unroll
+      for (int q = 0; q < 6; ++q) {
+        const float4 r = curand_uniform4(&st);
+        m |= (r.x >= p ? 1u : 0u) << (4 * q) | (r.y >= p ? 1u : 0u) << (4 * q + 1) | (r.z >= p ? 1u : 0u) << (4 * q + 2) |
+             (r.w >= p ? 1u : 0u) << (4 * q + 3);
+      }
+      keep[i] = m;
+    }
+}
+B200_DEVICE void apply_keep(float (&f)[8], unsigned bits, float inv_keep) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) f[j] = (bits >> j) & 1u ? f[j] * inv_keep : 0.f;
+}
+
 __global__ void __launch_bounds__(256)
 gate_cat_fwd_kernel(const __nv_bfloat16* __restrict__ u_raw, long long ld_u, const __nv_bfloat16* __restrict__ attn,
                     const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
                     __nv_bfloat16* __restrict__ cat, float* __restrict__ mean_out, float* __restrict__ rstd_out, int T,
-                    int D, float eps) {
+                    int D, float eps, float p, unsigned long long seed) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nv = D / 256;
   for (long long row = (long long)blockIdx.x * 8 + warp; row < T; row += (long long)gridDim.x * 8) {
@@ -61,6 +93,9 @@ gate_cat_fwd_kernel(const __nv_bfloat16* __restrict__ u_raw, long long ld_u, con
       }
     const float rstd = rsqrtf(warp_sum(var) / D + eps);
     if (lane == 0) { mean_out[row] = mean; rstd_out[row] = rstd; }
+    unsigned keep[GV];
+    draw_keep(keep, nv, p, seed, row, lane);
+    const float inv_keep = 1.f / (1.f - p);
     __nv_bfloat16* out = cat + row * 3 * D;
 #pragma unroll
     for (int i = 0; i < GV; ++i)
@@ -76,6 +111,11 @@ gate_cat_fwd_kernel(const __nv_bfloat16* __restrict__ u_raw, long long ld_u, con
           const float n = rbf((a[i][j] - mean) * rstd * w8[j] + b8[j]);
           y[j] = u[j] * n;
         }
+        if (p > 0.f) {
+          apply_keep(u, keep[i], inv_keep);
+          apply_keep(a[i], keep[i] >> 8, inv_keep);
+          apply_keep(y, keep[i] >> 16, inv_keep);
+        }
         st8(out + c, u);
         st8(out + D + c, a[i]);
         st8(out + 2 * D + c, y);
@@ -88,7 +128,8 @@ gate_cat_bwd_kernel(const __nv_bfloat16* __restrict__ dcat, const __nv_bfloat16*
                     const __nv_bfloat16* __restrict__ attn, const __nv_bfloat16* __restrict__ w,
                     const __nv_bfloat16* __restrict__ b, const float* __restrict__ mean_in,
                     const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ du_raw, long long ld_du,
-                    __nv_bfloat16* __restrict__ dattn, float* __restrict__ partial, int T, int D) {
+                    __nv_bfloat16* __restrict__ dattn, float* __restrict__ partial, int T, int D, float p,
+                    unsigned long long seed) {
   extern __shared__ float acc[];   // [8 warps][2][D]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nv = D / 256;
@@ -99,6 +140,9 @@ gate_cat_bwd_kernel(const __nv_bfloat16* __restrict__ dcat, const __nv_bfloat16*
     for (int j = 0; j < 8; ++j) { gw[i][j] = 0.f; gb[i][j] = 0.f; }
   for (long long row = (long long)blockIdx.x * 8 + warp; row < T; row += (long long)gridDim.x * 8) {
     const float mean = mean_in[row], rstd = rstd_in[row];
+    unsigned keep[GV];
+    draw_keep(keep, nv, p, seed, row, lane);
+    const float inv_keep = 1.f / (1.f - p);
     const __nv_bfloat16* dc = dcat + row * 3 * D;
     float xn[GV][8], g[GV][8];
     float s1 = 0.f, s2 = 0.f;
@@ -113,6 +157,10 @@ gate_cat_bwd_kernel(const __nv_bfloat16* __restrict__ dcat, const __nv_bfloat16*
         ld8(b + c, b8);
         ld8(dc + 2 * D + c, dy);
         ld8(dc + c, du);
+        if (p > 0.f) {
+          apply_keep(du, keep[i], inv_keep);
+          apply_keep(dy, keep[i] >> 16, inv_keep);
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float sg = 1.f / (1.f + __expf(-ur[j]));
@@ -137,6 +185,7 @@ gate_cat_bwd_kernel(const __nv_bfloat16* __restrict__ dcat, const __nv_bfloat16*
         const int c = (lane + 32 * i) * 8;
         float da[8], o[8];
         ld8(dc + D + c, da);
+        if (p > 0.f) apply_keep(da, keep[i] >> 8, inv_keep);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = da[j] + rstd * (g[i][j] - xn[i][j] * s1 - s2);
         st8(dattn + row * D + c, o);
@@ -185,14 +234,17 @@ bool gate_ok(int D, long long ld_u) { return D % 256 == 0 && D >= 256 && D <= 25
 // fp32 scratch elements b200_hstu_gate_cat_bwd needs for T rows of width D.
 B200_API long long b200_hstu_gate_cat_scratch_elems(int T, int D) { return (long long)gate_grid(T) * 2 * D; }
 
-// cat[T, 3D] = [silu(u_raw) | attn | silu(u_raw) * LayerNorm(attn)];  mean / rstd [T] fp32 are kept for backward.
+// cat[T, 3D] = dropout([silu(u_raw) | attn | silu(u_raw) * LayerNorm(attn)], p);  mean / rstd [T] fp32 are kept for
+// backward, which must be given the same p and seed.
 B200_API int b200_hstu_gate_cat_fwd(const void* u_raw, long long ld_u, const void* attn, const void* w, const void* b,
-                                    void* cat, float* mean, float* rstd, int T, int D, float eps, void* stream) {
+                                    void* cat, float* mean, float* rstd, int T, int D, float eps, float p,
+                                    unsigned long long seed, void* stream) {
+  if (!(p >= 0.f && p < 1.f)) return b200::fail(902, "hstu_gate_cat_fwd: dropout rate %f outside [0, 1)", (double)p);
   if (!gate_ok(D, ld_u)) return b200::fail(900, "hstu_gate_cat_fwd: D=%d must be 256, 512 or 768 and the pitch %lld a multiple of 8", D, ld_u);
   if (T <= 0) return 0;
   gate_cat_fwd_kernel<<<gate_grid(T), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)u_raw, ld_u, (const __nv_bfloat16*)attn,
                                                                       (const __nv_bfloat16*)w, (const __nv_bfloat16*)b,
-                                                                      (__nv_bfloat16*)cat, mean, rstd, T, D, eps);
+                                                                      (__nv_bfloat16*)cat, mean, rstd, T, D, eps, p, seed);
   b200::count_launch();
   return b200::check_launch("hstu_gate_cat_fwd");
 }
@@ -202,7 +254,8 @@ B200_API int b200_hstu_gate_cat_fwd(const void* u_raw, long long ld_u, const voi
 B200_API int b200_hstu_gate_cat_bwd(const void* dcat, const void* u_raw, long long ld_u, const void* attn, const void* w,
                                     const void* b, const float* mean, const float* rstd, void* du_raw, long long ld_du,
                                     void* dattn, float* dw, float* db, float* scratch, int T, int D, int accumulate,
-                                    void* stream) {
+                                    float p, unsigned long long seed, void* stream) {
+  if (!(p >= 0.f && p < 1.f)) return b200::fail(902, "hstu_gate_cat_bwd: dropout rate %f outside [0, 1)", (double)p);
   if (!gate_ok(D, ld_u) || ld_du % 8 != 0)
     return b200::fail(901, "hstu_gate_cat_bwd: D=%d must be 256, 512 or 768 and the pitches %lld / %lld multiples of 8", D, ld_u, ld_du);
   if (T <= 0) return 0;
@@ -210,7 +263,7 @@ B200_API int b200_hstu_gate_cat_bwd(const void* dcat, const void* u_raw, long lo
   cudaStream_t st = (cudaStream_t)stream;
   gate_cat_bwd_kernel<<<grid, 256, 8 * 2 * D * sizeof(float), st>>>(
       (const __nv_bfloat16*)dcat, (const __nv_bfloat16*)u_raw, ld_u, (const __nv_bfloat16*)attn, (const __nv_bfloat16*)w,
-      (const __nv_bfloat16*)b, mean, rstd, (__nv_bfloat16*)du_raw, ld_du, (__nv_bfloat16*)dattn, scratch, T, D);
+      (const __nv_bfloat16*)b, mean, rstd, (__nv_bfloat16*)du_raw, ld_du, (__nv_bfloat16*)dattn, scratch, T, D, p, seed);
   b200::count_launch();
   if (int r = b200::check_launch("hstu_gate_cat_bwd")) return r;
   gate_cat_reduce_kernel<<<(D + 255) / 256, 256, 0, st>>>(scratch, grid, D, dw, db, accumulate);

@@ -48,6 +48,7 @@ class HSTUConfig:
     contextual: int = 0                # contextual tokens prepended to every sequence
     input_dropout: float = 0.2
     linear_dropout: float = 0.1
+    fuse_glue: bool = True             # SiLU(u) * LayerNorm(attn) + concat + dropout as one kernel each way (GPU, bf16)
     num_positions: int = 8192
     num_time_buckets: int = 2048
     n_tasks: int = 1
@@ -143,7 +144,7 @@ class STULayer(nn.Module):
     def __init__(self, cfg: HSTUConfig, dtype, device):
         super().__init__()
         self.cfg = cfg
-        self.fuse_glue = True
+        self.fuse_glue = cfg.fuse_glue
         d, h = cfg.dim, cfg.heads
         self.split = [h * cfg.d_v, h * cfg.d_v, h * cfg.d_qk, h * cfg.d_qk]       # u, v, q, k
         self.uvqk_weight = nn.Parameter(torch.empty(sum(self.split), d, dtype=dtype, device=device))
@@ -171,13 +172,15 @@ class STULayer(nn.Module):
                               cfg.contextual).reshape(x.shape[0], h * cfg.d_v)
         if self.fuse_glue and gate_cat_eligible(u_raw, attn):
             # SiLU(u), the layer norm of the attention output, their product and the concatenation in one kernel
-            cat = GateCatFn.apply(u_raw, attn, self.out_norm_w, self.out_norm_b, 1e-6)
+            # (and the dropout of the concatenation, its mask regenerated in backward from a Philox seed)
+            cat = GateCatFn.apply(u_raw, attn, self.out_norm_w, self.out_norm_b, 1e-6,
+                                  cfg.linear_dropout if self.training else 0.0)
         else:
             u = TF.silu(u_raw)
             y = u * F.layer_norm(attn, self.out_norm_w, self.out_norm_b, 1e-6)
             cat = torch.cat([u, attn, y], dim=1)
-        if cfg.linear_dropout > 0 and self.training:
-            cat = TF.dropout(cat, cfg.linear_dropout)
+            if cfg.linear_dropout > 0 and self.training:
+                cat = TF.dropout(cat, cfg.linear_dropout)
         return F.linear(cat.contiguous(), self.out_weight, None, x, cfg.precision)
 
 

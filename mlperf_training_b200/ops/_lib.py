@@ -67,8 +67,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_zero_reduce_scatter": [P, I, I, L, L, F, P, P, P],
         "b200_zero_adamw_all_gather": [P, I, I, L, L, P, P, P, P, F, F, F, F, F, I, F, P, F, I, P],
         "b200_hstu_attn_fwd": [P, P, P, P, P, P, I, L, I, I, I, I, L, L, L, L, F, P],
-        "b200_hstu_gate_cat_fwd": [P, L, P, P, P, P, P, P, I, I, F, P],
-        "b200_hstu_gate_cat_bwd": [P, P, L, P, P, P, P, P, P, L, P, P, P, P, I, I, I, P],
+        "b200_hstu_gate_cat_fwd": [P, L, P, P, P, P, P, P, I, I, F, F, ctypes.c_ulonglong, P],
+        "b200_hstu_gate_cat_bwd": [P, P, L, P, P, P, P, P, P, L, P, P, P, P, I, I, I, F, ctypes.c_ulonglong, P],
         "b200_hstu_attn_bwd": [P, P, P, P, P, P, P, P, P, I, L, I, I, I, I, L, L, L, L, L, L, F, P],
         "b200_scatter_rows_to_peers": [P, P, P, P, L, I, P, I, L, P, P],
         "b200_gather_rows_from_peers": [P, P, P, L, I, P, I, L, P],

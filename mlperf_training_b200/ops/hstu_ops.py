@@ -107,21 +107,25 @@ def gate_cat_eligible(u_raw: torch.Tensor, attn: torch.Tensor) -> bool:
 
 class GateCatFn(Function):
     """The concatenated input of the HSTU output projection in one pass each way (SiLU of u, layer norm
-    of the attention output, their product, the concatenation; backward recomputes all three from
-    ``u_raw`` and ``attn``).  ``u_raw`` may be a column block of the fused uvqk projection."""
+    of the attention output, their product, the concatenation, dropout of rate ``p``; backward
+    recomputes all of it from ``u_raw`` and ``attn``, the dropout mask from its Philox seed).
+    ``u_raw`` may be a column block of the fused uvqk projection.  The seed is drawn from torch's CPU
+    generator, so ``torch.manual_seed`` fixes the masks."""
 
     @staticmethod
-    def forward(ctx, u_raw, attn, weight, bias, eps):
+    def forward(ctx, u_raw, attn, weight, bias, eps, p=0.0):
         T, D = attn.shape
         attn = attn.contiguous()
         w, b = weight.to(torch.bfloat16).contiguous(), bias.to(torch.bfloat16).contiguous()
         cat = torch.empty((T, 3 * D), dtype=attn.dtype, device=attn.device)
         mean = torch.empty(T, dtype=torch.float32, device=attn.device)
         rstd = torch.empty(T, dtype=torch.float32, device=attn.device)
+        seed = int(torch.randint(0, 2 ** 62, (1,)).item()) if p > 0 else 0
         call("b200_hstu_gate_cat_fwd", ptr(u_raw), u_raw.stride(0), ptr(attn), ptr(w), ptr(b), ptr(cat), ptr(mean), ptr(rstd),
-             T, D, float(eps), stream_ptr())
+             T, D, float(eps), float(p), seed, stream_ptr())
         ctx.save_for_backward(u_raw, attn, w, b, mean, rstd)
         ctx.refs = (weight, bias)
+        ctx.drop = (float(p), seed)
         return cat
 
     @staticmethod
@@ -136,11 +140,11 @@ class GateCatFn(Function):
         db = torch.empty(D, dtype=torch.float32, device=attn.device)
         scratch = torch.empty(_lib.load().b200_hstu_gate_cat_scratch_elems(T, D), dtype=torch.float32, device=attn.device)
         call("b200_hstu_gate_cat_bwd", ptr(dcat), ptr(u_raw), u_raw.stride(0), ptr(attn), ptr(w), ptr(b), ptr(mean), ptr(rstd),
-             ptr(du), du.stride(0), ptr(da), ptr(dw), ptr(db), ptr(scratch), T, D, 0, stream_ptr())
-        return du, da, _vec_grad(ctx.refs[0], dw), _vec_grad(ctx.refs[1], db), None
+             ptr(du), du.stride(0), ptr(da), ptr(dw), ptr(db), ptr(scratch), T, D, 0, ctx.drop[0], ctx.drop[1], stream_ptr())
+        return du, da, _vec_grad(ctx.refs[0], dw), _vec_grad(ctx.refs[1], db), None, None
 
 
-def gate_cat(u_raw, attn, weight, bias, eps: float = 1e-6):
+def gate_cat(u_raw, attn, weight, bias, eps: float = 1e-6, p: float = 0.0):
     if gate_cat_eligible(u_raw, attn):
-        return GateCatFn.apply(u_raw, attn, weight, bias, eps)
-    return gate_cat_reference(u_raw, attn, weight, bias, eps)
+        return GateCatFn.apply(u_raw, attn, weight, bias, eps, p)
+    return torch.nn.functional.dropout(gate_cat_reference(u_raw, attn, weight, bias, eps), p)

@@ -128,7 +128,7 @@ def bench_hstu(args, rank, world, dev):
     from ..models.hstu import HSTUConfig
     from ..trainer.hstu import HSTUTrainer
     cfg = HSTUConfig(layers=args.layers or 8, dim=512, heads=4, d_qk=128, d_v=128, max_seq_len=4096, emb_dim=256, dtype="bf16",
-                     precision="bf16")
+                     precision="bf16", fuse_glue=args.glue == "fused")
     rows = 400_000_000 // (args.scale or 1)
     bpg = args.global_batch // world if args.global_batch else 128
     tr = HSTUTrainer(cfg, rows, bpg, dev, emb_comm=args.comm, seed=0,
@@ -136,7 +136,7 @@ def bench_hstu(args, rank, world, dev):
     ms, loss = _timed(lambda i: tr.train_step(i), args.steps, args.warmup, world)
     return {"metric": "train samples/s", "value": bpg * world / (ms / 1e3), "unit": "samples/s", "ms_per_step": ms, "loss": loss,
             "config": {"model": "hstu", "layers": cfg.layers, "dim": cfg.dim, "heads": cfg.heads, "table_rows": rows, "emb_dim": 256,
-                       "users_per_gpu": bpg, "lengths": "lognormal median 512 in [16, 4096]", "ids": "Zipf(1.05)",
+                       "users_per_gpu": bpg, "layer_glue": args.glue, "lengths": "lognormal median 512 in [16, 4096]", "ids": "Zipf(1.05)",
                        "parallelism": f"row-wise sharded table over {world} ({args.comm} lookup) + dp{world} dense",
                        "includes": "host batch build, H2D on a side stream, sparse Adagrad in backward"}}
 
@@ -154,6 +154,7 @@ def main(argv=None) -> int:
     ap.add_argument("--global-batch", type=int, default=0)
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--glue", default="fused", choices=["fused", "eager"], help="HSTU layer glue: one kernel or torch operators")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8"], help="linear precision (flux1)")
     args = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))

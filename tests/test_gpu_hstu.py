@@ -152,3 +152,41 @@ def test_stu_layer_fused_glue_matches_eager_glue():
     for a, b, what in zip(outs[0], outs[1], ("y", "dx", "dnorm_w", "duvqk_w")):
         err = (a - b).abs().max().item()
         assert err <= 2e-2 * (a.abs().max().item() + 1e-6), f"{what}: {err}"
+
+
+def test_gate_cat_dropout_mask_is_regenerated_in_backward():
+    from mlperf_training_b200.ops.hstu_ops import GateCatFn
+    torch.manual_seed(11)
+    T, D, p = 3000, 512, 0.25
+    wide = torch.randn(T, 2048, device="cuda").bfloat16()
+    attn = (torch.randn(T, D, device="cuda") * 2 + 0.3).bfloat16()
+    w = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16()
+    b = (0.1 * torch.randn(D, device="cuda")).bfloat16()
+    dcat = torch.randn(T, 3 * D, device="cuda").bfloat16()
+    plain = GateCatFn.apply(wide[:, :D], attn, w, b, 1e-6, 0.0)
+    uk = wide.clone().requires_grad_(True)
+    ak, wk, bk = (t.clone().requires_grad_(True) for t in (attn, w, b))
+    dropped = GateCatFn.apply(uk[:, :D], ak, wk, bk, 1e-6, p)
+    dropped.backward(dcat)
+    torch.cuda.synchronize()
+    _lib.check_status("gate_cat_dropout")
+    keep = (dropped != 0) | (plain == 0)
+    frac = 1.0 - keep.float().mean().item()
+    assert abs(frac - p) < 0.01, frac
+    for sec in range(3):                                   # every section gets its own bits
+        f = 1.0 - keep[:, sec * D:(sec + 1) * D].float().mean().item()
+        assert abs(f - p) < 0.02, (sec, f)
+    want = plain.float() / (1 - p) * keep
+    assert (dropped.float() - want).abs().max().item() <= 2 ** -6 * want.abs().max().item()
+    # another call draws another mask
+    again = GateCatFn.apply(wide[:, :D], attn, w, b, 1e-6, p)
+    assert ((again != 0) != (dropped != 0)).float().mean().item() > 0.2
+    # backward against fp32 autograd through the same mask
+    uf, af, wf, bf = (t.detach().float().requires_grad_(True) for t in (wide[:, :D].contiguous(), attn, w, b))
+    u = torch.nn.functional.silu(uf)
+    n = torch.nn.functional.layer_norm(af, (D,), wf, bf, 1e-6)
+    (torch.cat([u, af, u * n], dim=1) * keep / (1 - p)).backward(dcat.float())
+    for got, ref, what in ((uk.grad[:, :D], uf.grad, "du_raw"), (ak.grad, af.grad, "dattn"), (wk.grad, wf.grad, "dw"),
+                           (bk.grad, bf.grad, "db")):
+        err = (got.float() - ref).abs().max().item()
+        assert err <= 2e-2 * (ref.abs().max().item() + 1e-6), f"{what}: {err}"
