@@ -42,43 +42,49 @@ B200_DEVICE float rbf(float x) { return __bfloat162float(__float2bfloat16_rn(x))
 
 // Keep masks of one row for this lane: bit (8 * s + j) of keep[i] covers element j of vector i in section s
 // (0 = u, 1 = attn, 2 = y).  Forward and backward call this with the same (seed, row, lane) and get the same bits.
-B200_DEVICE void draw_keep(unsigned (&keep)[GV], int nv, float p, unsigned long long seed, long long row, int lane) {
+// Every 32-bit Philox word decides two elements: a 16-bit half is compared with thr = round(p * 65536), so the
+// rate is p to within 2^-17.
+template <int NV>
+B200_DEVICE void draw_keep(unsigned (&keep)[NV], unsigned thr, unsigned long long seed, long long row, int lane) {
 #pragma unroll
-  for (int i = 0; i < GV; ++i) keep[i] = 0xffffffu;
-  if (p <= 0.f) return;
+  for (int i = 0; i < NV; ++i) keep[i] = 0xffffffu;
+  if (thr == 0) return;
   curandStatePhilox4_32_10_t st;
   curand_init(seed, (unsigned long long)row * 32 + lane, 0, &st);
 #pragma unroll
-  for (int i = 0; i < GV; ++i)
-    if (i < nv) {
-      unsigned m = 0;
+  for (int i = 0; i < NV; ++i) {
+    unsigned m = 0;
 #pragma unroll
-      for (int q = 0; q < 6; ++q) {
-        const float4 r = curand_uniform4(&st);
-        m |= (r.x >= p ? 1u : 0u) << (4 * q) | (r.y >= p ? 1u : 0u) << (4 * q + 1) | (r.z >= p ? 1u : 0u) << (4 * q + 2) |
-             (r.w >= p ? 1u : 0u) << (4 * q + 3);
+    for (int q = 0; q < 3; ++q) {
+      const uint4 r = curand4(&st);
+      const unsigned wv[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        m |= ((wv[k] & 0xffffu) >= thr ? 1u : 0u) << (8 * q + 2 * k);
+        m |= ((wv[k] >> 16) >= thr ? 1u : 0u) << (8 * q + 2 * k + 1);
       }
-      keep[i] = m;
     }
+    keep[i] = m;
+  }
 }
 B200_DEVICE void apply_keep(float (&f)[8], unsigned bits, float inv_keep) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) f[j] = (bits >> j) & 1u ? f[j] * inv_keep : 0.f;
 }
 
-__global__ void __launch_bounds__(256)
+template <int NV>
+__global__ void __launch_bounds__(256, 2)
 gate_cat_fwd_kernel(const __nv_bfloat16* __restrict__ u_raw, long long ld_u, const __nv_bfloat16* __restrict__ attn,
                     const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
                     __nv_bfloat16* __restrict__ cat, float* __restrict__ mean_out, float* __restrict__ rstd_out, int T,
-                    int D, float eps, float p, unsigned long long seed) {
+                    float eps, float p, unsigned thr, unsigned long long seed) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int nv = D / 256;
+  constexpr int D = NV * 256;
   for (long long row = (long long)blockIdx.x * 8 + warp; row < T; row += (long long)gridDim.x * 8) {
-    float a[GV][8];
+    float a[NV][8];
     float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < GV; ++i)
-      if (i < nv) {
+    for (int i = 0; i < NV; ++i) {
         ld8(attn + row * D + (lane + 32 * i) * 8, a[i]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) s += a[i][j];
@@ -86,20 +92,18 @@ gate_cat_fwd_kernel(const __nv_bfloat16* __restrict__ u_raw, long long ld_u, con
     const float mean = warp_sum(s) / D;
     float var = 0.f;
 #pragma unroll
-    for (int i = 0; i < GV; ++i)
-      if (i < nv) {
+    for (int i = 0; i < NV; ++i) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) { const float d = a[i][j] - mean; var += d * d; }
       }
     const float rstd = rsqrtf(warp_sum(var) / D + eps);
     if (lane == 0) { mean_out[row] = mean; rstd_out[row] = rstd; }
-    unsigned keep[GV];
-    draw_keep(keep, nv, p, seed, row, lane);
+    unsigned keep[NV];
+    draw_keep<NV>(keep, thr, seed, row, lane);
     const float inv_keep = 1.f / (1.f - p);
     __nv_bfloat16* out = cat + row * 3 * D;
 #pragma unroll
-    for (int i = 0; i < GV; ++i)
-      if (i < nv) {
+    for (int i = 0; i < NV; ++i) {
         const int c = (lane + 32 * i) * 8;
         float ur[8], w8[8], b8[8], u[8], y[8];
         ld8(u_raw + row * ld_u + c, ur);
@@ -111,7 +115,7 @@ gate_cat_fwd_kernel(const __nv_bfloat16* __restrict__ u_raw, long long ld_u, con
           const float n = rbf((a[i][j] - mean) * rstd * w8[j] + b8[j]);
           y[j] = u[j] * n;
         }
-        if (p > 0.f) {
+        if (thr != 0) {
           apply_keep(u, keep[i], inv_keep);
           apply_keep(a[i], keep[i] >> 8, inv_keep);
           apply_keep(y, keep[i] >> 16, inv_keep);
@@ -123,32 +127,32 @@ gate_cat_fwd_kernel(const __nv_bfloat16* __restrict__ u_raw, long long ld_u, con
   }
 }
 
-__global__ void __launch_bounds__(256)
+template <int NV>
+__global__ void __launch_bounds__(256, 2)
 gate_cat_bwd_kernel(const __nv_bfloat16* __restrict__ dcat, const __nv_bfloat16* __restrict__ u_raw, long long ld_u,
                     const __nv_bfloat16* __restrict__ attn, const __nv_bfloat16* __restrict__ w,
                     const __nv_bfloat16* __restrict__ b, const float* __restrict__ mean_in,
                     const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ du_raw, long long ld_du,
-                    __nv_bfloat16* __restrict__ dattn, float* __restrict__ partial, int T, int D, float p,
+                    __nv_bfloat16* __restrict__ dattn, float* __restrict__ partial, int T, float p, unsigned thr,
                     unsigned long long seed) {
   extern __shared__ float acc[];   // [8 warps][2][D]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int nv = D / 256;
-  float gw[GV][8], gb[GV][8];
+  constexpr int D = NV * 256;
+  float gw[NV][8], gb[NV][8];
 #pragma unroll
-  for (int i = 0; i < GV; ++i)
+  for (int i = 0; i < NV; ++i)
 #pragma unroll
     for (int j = 0; j < 8; ++j) { gw[i][j] = 0.f; gb[i][j] = 0.f; }
   for (long long row = (long long)blockIdx.x * 8 + warp; row < T; row += (long long)gridDim.x * 8) {
     const float mean = mean_in[row], rstd = rstd_in[row];
-    unsigned keep[GV];
-    draw_keep(keep, nv, p, seed, row, lane);
+    unsigned keep[NV];
+    draw_keep<NV>(keep, thr, seed, row, lane);
     const float inv_keep = 1.f / (1.f - p);
     const __nv_bfloat16* dc = dcat + row * 3 * D;
-    float xn[GV][8], g[GV][8];
+    float xn[NV][8], g[NV][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < GV; ++i)
-      if (i < nv) {
+    for (int i = 0; i < NV; ++i) {
         const int c = (lane + 32 * i) * 8;
         float ur[8], a8[8], w8[8], b8[8], dy[8], du[8], o[8];
         ld8(u_raw + row * ld_u + c, ur);
@@ -157,7 +161,7 @@ gate_cat_bwd_kernel(const __nv_bfloat16* __restrict__ dcat, const __nv_bfloat16*
         ld8(b + c, b8);
         ld8(dc + 2 * D + c, dy);
         ld8(dc + c, du);
-        if (p > 0.f) {
+        if (thr != 0) {
           apply_keep(du, keep[i], inv_keep);
           apply_keep(dy, keep[i] >> 16, inv_keep);
         }
@@ -180,12 +184,11 @@ gate_cat_bwd_kernel(const __nv_bfloat16* __restrict__ dcat, const __nv_bfloat16*
     s1 = warp_sum(s1) / D;
     s2 = warp_sum(s2) / D;
 #pragma unroll
-    for (int i = 0; i < GV; ++i)
-      if (i < nv) {
+    for (int i = 0; i < NV; ++i) {
         const int c = (lane + 32 * i) * 8;
         float da[8], o[8];
         ld8(dc + D + c, da);
-        if (p > 0.f) apply_keep(da, keep[i] >> 8, inv_keep);
+        if (thr != 0) apply_keep(da, keep[i] >> 8, inv_keep);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = da[j] + rstd * (g[i][j] - xn[i][j] * s1 - s2);
         st8(dattn + row * D + c, o);
@@ -193,8 +196,7 @@ gate_cat_bwd_kernel(const __nv_bfloat16* __restrict__ dcat, const __nv_bfloat16*
   }
   float* mine = acc + (long long)warp * 2 * D;
 #pragma unroll
-  for (int i = 0; i < GV; ++i)
-    if (i < nv) {
+  for (int i = 0; i < NV; ++i) {
       const int c = (lane + 32 * i) * 8;
 #pragma unroll
       for (int j = 0; j < 8; ++j) { mine[c + j] = gw[i][j]; mine[D + c + j] = gb[i][j]; }
@@ -223,7 +225,7 @@ __global__ void gate_cat_reduce_kernel(const float* __restrict__ partial, int np
 
 int gate_grid(int T) {
   int grid = (T + 7) / 8;
-  const int cap = b200::sm_count() * 4;
+  const int cap = b200::sm_count() * 2;   // two resident CTAs per SM
   return grid < cap ? (grid < 1 ? 1 : grid) : cap;
 }
 
@@ -242,9 +244,15 @@ B200_API int b200_hstu_gate_cat_fwd(const void* u_raw, long long ld_u, const voi
   if (!(p >= 0.f && p < 1.f)) return b200::fail(902, "hstu_gate_cat_fwd: dropout rate %f outside [0, 1)", (double)p);
   if (!gate_ok(D, ld_u)) return b200::fail(900, "hstu_gate_cat_fwd: D=%d must be 256, 512 or 768 and the pitch %lld a multiple of 8", D, ld_u);
   if (T <= 0) return 0;
-  gate_cat_fwd_kernel<<<gate_grid(T), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)u_raw, ld_u, (const __nv_bfloat16*)attn,
-                                                                      (const __nv_bfloat16*)w, (const __nv_bfloat16*)b,
-                                                                      (__nv_bfloat16*)cat, mean, rstd, T, D, eps, p, seed);
+  const unsigned thr = (unsigned)lrintf(p * 65536.f);
+  const float pe = (float)thr / 65536.f;   // the rate the 16-bit comparison realises
+  auto U = (const __nv_bfloat16*)u_raw; auto A = (const __nv_bfloat16*)attn; auto W = (const __nv_bfloat16*)w;
+  auto B = (const __nv_bfloat16*)b; auto C = (__nv_bfloat16*)cat;
+  const int grid = gate_grid(T);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (D == 256) gate_cat_fwd_kernel<1><<<grid, 256, 0, st>>>(U, ld_u, A, W, B, C, mean, rstd, T, eps, pe, thr, seed);
+  else if (D == 512) gate_cat_fwd_kernel<2><<<grid, 256, 0, st>>>(U, ld_u, A, W, B, C, mean, rstd, T, eps, pe, thr, seed);
+  else gate_cat_fwd_kernel<3><<<grid, 256, 0, st>>>(U, ld_u, A, W, B, C, mean, rstd, T, eps, pe, thr, seed);
   b200::count_launch();
   return b200::check_launch("hstu_gate_cat_fwd");
 }
@@ -261,9 +269,14 @@ B200_API int b200_hstu_gate_cat_bwd(const void* dcat, const void* u_raw, long lo
   if (T <= 0) return 0;
   const int grid = gate_grid(T);
   cudaStream_t st = (cudaStream_t)stream;
-  gate_cat_bwd_kernel<<<grid, 256, 8 * 2 * D * sizeof(float), st>>>(
-      (const __nv_bfloat16*)dcat, (const __nv_bfloat16*)u_raw, ld_u, (const __nv_bfloat16*)attn, (const __nv_bfloat16*)w,
-      (const __nv_bfloat16*)b, mean, rstd, (__nv_bfloat16*)du_raw, ld_du, (__nv_bfloat16*)dattn, scratch, T, D, p, seed);
+  const unsigned thr = (unsigned)lrintf(p * 65536.f);
+  const float pe = (float)thr / 65536.f;
+  auto DC = (const __nv_bfloat16*)dcat; auto U = (const __nv_bfloat16*)u_raw; auto A = (const __nv_bfloat16*)attn;
+  auto W = (const __nv_bfloat16*)w; auto B = (const __nv_bfloat16*)b; auto DU = (__nv_bfloat16*)du_raw; auto DA = (__nv_bfloat16*)dattn;
+  const size_t smem = 8 * 2 * D * sizeof(float);
+  if (D == 256) gate_cat_bwd_kernel<1><<<grid, 256, smem, st>>>(DC, U, ld_u, A, W, B, mean, rstd, DU, ld_du, DA, scratch, T, pe, thr, seed);
+  else if (D == 512) gate_cat_bwd_kernel<2><<<grid, 256, smem, st>>>(DC, U, ld_u, A, W, B, mean, rstd, DU, ld_du, DA, scratch, T, pe, thr, seed);
+  else gate_cat_bwd_kernel<3><<<grid, 256, smem, st>>>(DC, U, ld_u, A, W, B, mean, rstd, DU, ld_du, DA, scratch, T, pe, thr, seed);
   b200::count_launch();
   if (int r = b200::check_launch("hstu_gate_cat_bwd")) return r;
   gate_cat_reduce_kernel<<<(D + 255) / 256, 256, 0, st>>>(scratch, grid, D, dw, db, accumulate);
