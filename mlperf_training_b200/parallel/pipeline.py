@@ -12,8 +12,9 @@ both sends and receives, which is what keeps neighbouring stages from blocking e
 The reference gets this schedule from Megatron's ``get_forward_backward_func``
 (llama2_sft/primus/src/llama2_custom.py:1494) with ``pipeline_model_parallel_size`` /
 ``virtual_pipeline_model_parallel_size`` from the YAML (llama2_sft/primus/conf/llama2_70b_lora_posttrain.yaml:19-21);
-every shipped config sets the size to 1.  Interleaved (virtual) stages are accepted as a knob and
-run as the plain schedule (one model chunk per rank).
+every shipped config sets the size to 1.  ``InterleavedRunner`` is the virtual-stage variant (several
+model chunks per rank); ``trainer.pipeline_train.PipelineTrainer`` puts either schedule behind the
+trainer interface of the run loop.
 """
 from __future__ import annotations
 
@@ -68,9 +69,10 @@ class GPTStage(nn.Module):
             self._rope = K.rope_tables(self.cfg.seq_len, self.cfg.head_dim, self.cfg.rope_theta, device)
         return self._rope
 
-    def forward(self, x, tokens: torch.Tensor, labels: torch.Tensor | None):
+    def forward(self, x, tokens: torch.Tensor, labels: torch.Tensor | None, n_valid=None):
         """``x``: incoming activation ``[B*S, hidden]`` (ignored on the first stage, which embeds
-        ``tokens``).  Returns the outgoing activation, or the mean loss on the last stage."""
+        ``tokens``).  Returns the outgoing activation, or the mean loss on the last stage (the sum of
+        the token losses divided by ``n_valid`` when that is given)."""
         B, S = tokens.shape
         cos, sin = self.rope(tokens.device)
         if self.first:
@@ -79,7 +81,7 @@ class GPTStage(nn.Module):
             x = blk(x, cos, sin, B, S)
         if self.last:
             return F.lm_head_loss(x, self.final_norm, self.lm_head, labels.reshape(-1), eps=self.cfg.norm_eps,
-                                  precision=self.cfg.precision)
+                                  n_valid=n_valid, precision=self.cfg.precision)
         return x
 
 

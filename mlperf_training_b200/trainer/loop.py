@@ -71,6 +71,7 @@ class RunConfig:
     tensor_parallel: int = 1                            # tensor + sequence parallel size (Megatron layout)
     sequence_parallel: int = 1
     pipeline_parallel: int = 1
+    virtual_pipeline_parallel: int | None = None        # model chunks per pipeline rank (interleaved 1F1B)
     context_parallel: int = 1
     tp_comm_overlap: str = "fused"                      # "fused": in-kernel all-gather / reduce-scatter; "nccl"
     comm: str = "nccl"                                  # optimizer-step collectives: "nccl" | "fused"
@@ -121,6 +122,13 @@ def _dist_info():
     return 0, 1
 
 
+def _optim_shard(trainer, with_params: bool) -> dict:
+    state = trainer.engine.optimizer_state()
+    if with_params:
+        state["stage_param_bufs"] = [b.param_buf.detach().cpu() for b in trainer.engine.buckets]
+    return state
+
+
 def _moment_dtype(rc) -> torch.dtype:
     if not rc.use_precision_aware_optimizer:
         return torch.float32
@@ -146,9 +154,13 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         log.log_submission(rc.benchmark, platform=f"1xB200x{world}")
 
     cfg = build_model_config(rc.model)
-    if int(rc.pipeline_parallel) > 1 or int(rc.context_parallel) > 1:
-        raise NotImplementedError("this run loop drives data x tensor parallel meshes; pipeline stages are "
-                                  "scheduled by parallel.pipeline")
+    if int(rc.context_parallel) > 1:
+        raise NotImplementedError("this run loop drives data x tensor and data x pipeline meshes; context-parallel "
+                                  "attention is parallel.context")
+    pp_size = int(rc.pipeline_parallel)
+    if pp_size > 1 and (int(rc.tensor_parallel) > 1 or int(rc.dp_replicate) > 1 or world % pp_size):
+        raise NotImplementedError("pipeline stages combine with plain data parallelism here (tensor_parallel = 1, "
+                                  "dp_replicate = 1, world divisible by pipeline_parallel)")
     tp_size = min(int(rc.tensor_parallel), world)
     tp_ctx, dp_group, dp_rank, dp_world, rep_group = None, None, rank, world, None
     replicate = max(int(rc.dp_replicate), 1)
@@ -165,6 +177,10 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         dp_group = mesh.group("dp_shard") if replicate > 1 else mesh.group("dp")
         if cfg.precision != "bf16":
             cfg.precision = "bf16"       # the tensor-parallel linears run the bf16 tcgen05 GEMMs
+    if pp_size > 1:
+        from ..parallel.mesh import Mesh, MeshSpec
+        mesh = Mesh(MeshSpec(pp=pp_size))
+        dp_rank, dp_world = mesh.index("dp"), mesh.size("dp")
     if rc.global_batch % dp_world:
         raise ValueError("global_batch must be divisible by the data-parallel size")
     local_batch = rc.global_batch // dp_world
@@ -174,8 +190,13 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                      decay_steps=rc.lr_decay_iters, min_lr_ratio=rc.min_lr_ratio, seed=rc.seed, comm=rc.comm)
     if tp_size == 1 and replicate > 1 and world > 1:
         dp_group = mesh.group("dp_shard")
-    trainer = PretrainTrainer(cfg, opt, tc, device, group=dp_group, tp=tp_ctx, freeze_base=cfg.lora_rank > 0,
-                              replicate_group=rep_group)
+    if pp_size > 1:
+        from .pipeline_train import PipelineTrainer
+        trainer = PipelineTrainer(cfg, opt, tc, device, mesh, virtual_stages=rc.virtual_pipeline_parallel or 1,
+                                  freeze_base=cfg.lora_rank > 0)
+    else:
+        trainer = PretrainTrainer(cfg, opt, tc, device, group=dp_group, tp=tp_ctx, freeze_base=cfg.lora_rank > 0,
+                                  replicate_group=rep_group)
     data = build_data(rc.data, cfg, rc.seed)
     eval_data = build_data(rc.data, cfg, rc.seed + 7919)
 
@@ -186,13 +207,18 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             b = (b[:, :-1].contiguous(), ds.labels(b))
         return b
 
+    if rc.pretrained_checkpoint and pp_size > 1:
+        raise NotImplementedError("loading a Megatron torch_dist checkpoint into pipeline stages is not wired: load with "
+                                  "pipeline_parallel = 1, or resume from this framework's own checkpoint")
     if rc.pretrained_checkpoint and not resuming:
         from ..checkpoint.megatron import load_torch_dist
         load_torch_dist(trainer.model, rc.pretrained_checkpoint, strict=True)
     start_step = 0
     if resuming:
         ck = resume_mgr.load()
-        for b, saved in zip(trainer.engine.buckets, ck["dense"]["param_bufs"]):
+        # pipeline stages differ per rank: their parameters travel with the rank's optimizer shard
+        bufs = ck["optim"].get("stage_param_bufs") if (pp_size > 1 and ck["optim"] is not None) else ck["dense"]["param_bufs"]
+        for b, saved in zip(trainer.engine.buckets, bufs):
             b.param_buf.copy_(saved.to(b.param_buf.device))
         if ck["optim"] is not None:
             trainer.engine.load_optimizer_state(ck["optim"])
@@ -308,7 +334,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                 saver(step + 1,
                                 dense={"param_bufs": [b.param_buf.detach().cpu() for b in trainer.engine.buckets],
                                        "model_config": cfg.to_dict()},
-                                optim_shard=trainer.engine.optimizer_state(),
+                                optim_shard=_optim_shard(trainer, pp_size > 1),
                                 meta={"samples": samples, "run_started": True, "window": 0, "batch_idx_in_window": -1})
                 last_ckpt_t = time.perf_counter()
         if rc.die_at_step and step + 1 == rc.die_at_step:

@@ -82,3 +82,28 @@ def test_hybrid_sharding_matches_plain_data_parallel_gloo():
                        env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("ok=True") == 4
+
+
+@pytest.mark.parametrize("pp,virtual", [(2, 1), (2, 2)])
+def test_run_loop_over_pipeline_mesh_resumes_gloo(tmp_path, pp, virtual):
+    import json
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+
+    def launch(phase, want_rc):
+        r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+                            "--master-addr", "127.0.0.1", "--master-port", "29667",
+                            os.path.join(ROOT, "tests", "multi", "pp_loop_worker.py"), str(tmp_path), str(pp), str(virtual), phase],
+                           env=env, capture_output=True, text=True, timeout=600)
+        assert (r.returncode == 0) == (want_rc == 0), r.stdout[-2000:] + r.stderr[-3000:]
+
+    launch("straight", 0)
+    launch("die", 42)
+    launch("resume", 0)
+    straight = [json.loads((tmp_path / f"straight_rank{r}.json").read_text()) for r in range(4)]
+    resumed = [json.loads((tmp_path / f"resume_rank{r}.json").read_text()) for r in range(4)]
+    assert straight[0]["steps"] == 6 and resumed[0]["steps"] == 3
+    for r in range(2):                                      # ranks r and r + 2 are the two stages of one pipeline
+        assert straight[r]["losses"] == straight[r + 2]["losses"]
+    assert straight[0]["losses"] != straight[1]["losses"]   # the data-parallel replicas see different data
+    for r in range(4):
+        assert max(abs(a - b) for a, b in zip(resumed[r]["losses"], straight[r]["losses"][3:])) < 1e-5
