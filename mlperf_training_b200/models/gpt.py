@@ -202,6 +202,7 @@ class Block(nn.Module):
         self.w_qkv = nn.Parameter(torch.empty((self.hq + 2 * self.hkv) * hd, d, dtype=dtype, device=device))
         self.w_proj = nn.Parameter(torch.empty(d, self.hq * hd, dtype=dtype, device=device))
         self.sink = nn.Parameter(torch.zeros(self.hq, dtype=torch.float32, device=device)) if cfg.sink else None
+        self.cp = None                   # (group, mode) once GPT.set_context_parallel is called
         self.mlp_norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
         if self.tp is not None:
             self.w_qkv.tensor_parallel = ("qkv", W, self.tp.rank)
@@ -248,6 +249,25 @@ class Block(nn.Module):
             h = h + (u @ lo.b.t()) * lo.scale
         return self.mlp(h, self.mlp_norm, cfg.norm_eps)
 
+    def _attention_cp(self, qkv, cos, sin, B, S):
+        """Attention with the sequence sharded over ``self.cp = (group, mode)``: ``S`` is this rank's
+        chunk and ``cos`` / ``sin`` its rows of the tables.  ``mode`` "allgather" gathers keys and
+        values of the earlier chunks, "ulysses" trades sequence shards for head shards."""
+        from ..parallel.context import context_parallel_attention, ulysses_attention
+        cfg = self.cfg
+        group, mode = self.cp
+        Hq, Hkv, D = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        v3 = F.rope_packed(qkv, cos, sin, S=S, Hq=Hq, Hkv=Hkv, D=D).view(B, S, -1)
+        q = v3[:, :, :Hq * D].unflatten(-1, (Hq, D))
+        k = v3[:, :, Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+        v = v3[:, :, (Hq + Hkv) * D:].unflatten(-1, (Hkv, D))
+        window = cfg.layer_window(self.layer)
+        if mode == "ulysses":
+            a = ulysses_attention(q, k, v, group, causal=True, window=window)
+        else:
+            a = context_parallel_attention(q, k, v, group, window=window)
+        return a.reshape(B * S, Hq * D)
+
     def forward(self, x, cos, sin, B, S):
         cfg = self.cfg
         if self.tp is not None:
@@ -257,8 +277,11 @@ class Block(nn.Module):
         else:
             xn = F.rms_norm(x, self.attn_norm, cfg.norm_eps)
             qkv = F.linear(xn, self.w_qkv, None, None, cfg.precision) + self.lora_qkv(xn)
-        a = F.attention_packed(qkv, B=B, S=S, Hq=cfg.n_heads, Hkv=cfg.n_kv_heads, D=cfg.head_dim, cos=cos, sin=sin,
-                               sink=self.sink, causal=True, window=cfg.layer_window(self.layer))
+        if self.cp is not None:
+            a = self._attention_cp(qkv, cos, sin, B, S)
+        else:
+            a = F.attention_packed(qkv, B=B, S=S, Hq=cfg.n_heads, Hkv=cfg.n_kv_heads, D=cfg.head_dim, cos=cos, sin=sin,
+                                   sink=self.sink, causal=True, window=cfg.layer_window(self.layer))
         if self.lora_proj is None:
             h = F.linear(a, self.w_proj, None, x, cfg.precision)
         else:
@@ -280,6 +303,7 @@ class GPT(nn.Module):
         self.final_norm = nn.Parameter(torch.ones(cfg.hidden, dtype=dtype, device=device))
         self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden, dtype=dtype, device=device))
         self._rope = None
+        self.cp = None
         # optional callable(block_key): told when the backward of a block has produced all its gradients
         self.grad_ready_hook = None
         self.reset_parameters(seed)
@@ -321,9 +345,36 @@ class GPT(nn.Module):
             self._rope = K.rope_tables(self.cfg.seq_len, self.cfg.head_dim, self.cfg.rope_theta, device)
         return self._rope
 
+    def set_context_parallel(self, group, mode: str = "allgather") -> None:
+        """Shard the sequence over ``group``: ``forward`` then takes this rank's chunk ``[B, S / W]`` of
+        tokens and labels (chunk index = rank in the group) and returns the mean loss of that chunk;
+        parameters are replicated over the group, so the optimizer's gradient reduction must span it
+        (``context_parallel_size`` of the reference's Megatron model config,
+        llama2_sft/primus/src/llama2_custom.py:396-505, llama2_sft/primus/conf/llama2_70b_lora_posttrain.yaml:22)."""
+        import torch.distributed as dist
+        if group is None or dist.get_world_size(group) == 1:
+            self.cp = None
+            for blk in self.blocks:
+                blk.cp = None
+            return
+        if self.tp is not None:
+            raise NotImplementedError("context parallelism is not combined with tensor parallelism")
+        if self.cfg.sink:
+            raise NotImplementedError("context parallelism does not carry attention sink logits")
+        if mode not in ("allgather", "ulysses"):
+            raise ValueError(f"unknown context-parallel mode '{mode}'")
+        self.cp = (group, dist.get_world_size(group), dist.get_rank(group))
+        for blk in self.blocks:
+            blk.cp = (group, mode)
+
     def forward(self, tokens: torch.Tensor, labels: torch.Tensor, n_valid: int | None = None) -> torch.Tensor:
         B, S = tokens.shape
         cos, sin = self.rope(tokens.device)
+        if self.cp is not None:
+            _, W, r = self.cp
+            if S * W > cos.shape[0]:
+                raise ValueError(f"sequence {S * W} longer than the configured {cos.shape[0]}")
+            cos, sin = cos[r * S:(r + 1) * S].contiguous(), sin[r * S:(r + 1) * S].contiguous()
         if S > cos.shape[0]:
             raise ValueError(f"sequence {S} longer than the configured {cos.shape[0]}")
         ids, tgt = tokens.reshape(-1), labels.reshape(-1)

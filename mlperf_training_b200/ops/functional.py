@@ -327,6 +327,33 @@ def attention_packed(qkv, *, B, S, Hq, Hkv, D, cos=None, sin=None, sink=None, ca
     return AttentionFn.apply(qkv, sink, cos, sin, B, S, Hq, Hkv, D, causal, window, scale)
 
 
+class RopePackedFn(Function):
+    """Rotary embedding of the q and k columns of a packed ``[T, (Hq + 2 Hkv) * D]`` buffer as an
+    operator of its own (the context-parallel attention path rotates before the key/value exchange).
+    Token ``t`` sits at row ``t % S`` of the tables, so a rank holding a later chunk of the sequence
+    passes the matching slice of ``cos`` / ``sin``."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, S, n_heads, D):
+        out = qkv.contiguous().clone()
+        K.rope_(out, cos, sin, col0=0, n_heads=n_heads, head_dim=D, seq_len=S)
+        ctx.save_for_backward(cos, sin)
+        ctx.cfg = (S, n_heads, D)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        cos, sin = ctx.saved_tensors
+        S, n_heads, D = ctx.cfg
+        d = dout.contiguous().clone()
+        K.rope_(d, cos, sin, col0=0, n_heads=n_heads, head_dim=D, seq_len=S, backward=True)
+        return d, None, None, None, None, None
+
+
+def rope_packed(qkv, cos, sin, *, S, Hq, Hkv, D):
+    return RopePackedFn.apply(qkv, cos, sin, S, Hq + Hkv, D)
+
+
 class AttentionBSHDFn(Function):
     """Flash attention on separate ``[B, S, H, D]`` tensors (MMDiT joint attention, tests)."""
 

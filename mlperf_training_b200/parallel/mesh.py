@@ -54,7 +54,7 @@ def group_ranks(spec: MeshSpec, world: int) -> dict[str, list[list[int]]]:
     def rank_of(t, c, d, p):
         return ((p * dp + d) * spec.cp + c) * spec.tp + t
 
-    out = {"tp": [], "cp": [], "dp": [], "pp": [], "ep": [], "dp_shard": [], "dp_replicate": []}
+    out = {"tp": [], "cp": [], "dp": [], "pp": [], "ep": [], "dp_shard": [], "dp_replicate": [], "dp_cp": []}
     for p in range(spec.pp):
         for d in range(dp):
             for c in range(spec.cp):
@@ -75,6 +75,10 @@ def group_ranks(spec: MeshSpec, world: int) -> dict[str, list[list[int]]]:
         for c in range(spec.cp):
             for t in range(spec.tp):
                 out["pp"].append([rank_of(t, c, d, p) for p in range(spec.pp)])
+    # every rank that holds a replica of the same parameters: data x context (the gradient-reduction group)
+    for p in range(spec.pp):
+        for t in range(spec.tp):
+            out["dp_cp"].append([rank_of(t, c, d, p) for d in range(dp) for c in range(spec.cp)])
     return out
 
 

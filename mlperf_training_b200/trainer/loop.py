@@ -73,6 +73,7 @@ class RunConfig:
     pipeline_parallel: int = 1
     virtual_pipeline_parallel: int | None = None        # model chunks per pipeline rank (interleaved 1F1B)
     context_parallel: int = 1
+    context_parallel_mode: str = "allgather"            # "allgather" (keys / values of earlier chunks) | "ulysses" (head exchange)
     tp_comm_overlap: str = "fused"                      # "fused": in-kernel all-gather / reduce-scatter; "nccl"
     comm: str = "nccl"                                  # optimizer-step collectives: "nccl" | "fused"
     precision_schedule: dict | str | None = None        # ops.recipe.PrecisionSchedule spec (phase switch at a step)
@@ -154,13 +155,13 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         log.log_submission(rc.benchmark, platform=f"1xB200x{world}")
 
     cfg = build_model_config(rc.model)
-    if int(rc.context_parallel) > 1:
-        raise NotImplementedError("this run loop drives data x tensor and data x pipeline meshes; context-parallel "
-                                  "attention is parallel.context")
-    pp_size = int(rc.pipeline_parallel)
-    if pp_size > 1 and (int(rc.tensor_parallel) > 1 or int(rc.dp_replicate) > 1 or world % pp_size):
+    pp_size, cp_size = int(rc.pipeline_parallel), int(rc.context_parallel)
+    if pp_size > 1 and (int(rc.tensor_parallel) > 1 or int(rc.dp_replicate) > 1 or cp_size > 1 or world % pp_size):
         raise NotImplementedError("pipeline stages combine with plain data parallelism here (tensor_parallel = 1, "
-                                  "dp_replicate = 1, world divisible by pipeline_parallel)")
+                                  "context_parallel = 1, dp_replicate = 1, world divisible by pipeline_parallel)")
+    if cp_size > 1 and (int(rc.tensor_parallel) > 1 or int(rc.dp_replicate) > 1 or world % cp_size):
+        raise NotImplementedError("context parallelism combines with plain data parallelism here (tensor_parallel = 1, "
+                                  "dp_replicate = 1, world divisible by context_parallel)")
     tp_size = min(int(rc.tensor_parallel), world)
     tp_ctx, dp_group, dp_rank, dp_world, rep_group = None, None, rank, world, None
     replicate = max(int(rc.dp_replicate), 1)
@@ -177,10 +178,16 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         dp_group = mesh.group("dp_shard") if replicate > 1 else mesh.group("dp")
         if cfg.precision != "bf16":
             cfg.precision = "bf16"       # the tensor-parallel linears run the bf16 tcgen05 GEMMs
+    cp_group = None
     if pp_size > 1:
         from ..parallel.mesh import Mesh, MeshSpec
         mesh = Mesh(MeshSpec(pp=pp_size))
         dp_rank, dp_world = mesh.index("dp"), mesh.size("dp")
+    elif cp_size > 1:
+        from ..parallel.mesh import Mesh, MeshSpec
+        mesh = Mesh(MeshSpec(cp=cp_size))
+        dp_rank, dp_world = mesh.index("dp"), mesh.size("dp")
+        cp_group, dp_group = mesh.group("cp"), mesh.group("dp_cp")     # gradients are reduced over data x context
     if rc.global_batch % dp_world:
         raise ValueError("global_batch must be divisible by the data-parallel size")
     local_batch = rc.global_batch // dp_world
@@ -196,7 +203,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                                   freeze_base=cfg.lora_rank > 0)
     else:
         trainer = PretrainTrainer(cfg, opt, tc, device, group=dp_group, tp=tp_ctx, freeze_base=cfg.lora_rank > 0,
-                                  replicate_group=rep_group)
+                                  replicate_group=rep_group, cp_group=cp_group, cp_mode=rc.context_parallel_mode)
     data = build_data(rc.data, cfg, rc.seed)
     eval_data = build_data(rc.data, cfg, rc.seed + 7919)
 

@@ -37,10 +37,12 @@ class TrainConfig:
 
 class PretrainTrainer:
     """``group`` is the data-parallel group, ``tp`` an optional ``parallel.tensor.TPContext`` (the
-    ranks of one tensor-parallel group must be fed the same batch)."""
+    ranks of one tensor-parallel group must be fed the same batch).  With ``cp_group`` the sequence is
+    sharded over that group: its ranks are fed the same batch, each keeps its chunk of every
+    sequence, and ``group`` must then span data x context ranks (parameters are replicated over both)."""
 
     def __init__(self, model_cfg: GPTConfig, opt: OptimConfig, train: TrainConfig, device, group=None, ep_group=None,
-                 tp=None, freeze_base: bool = False, replicate_group=None):
+                 tp=None, freeze_base: bool = False, replicate_group=None, cp_group=None, cp_mode: str = "allgather"):
         self.cfg = model_cfg
         self.train_cfg = train
         self.device = torch.device(device)
@@ -51,6 +53,11 @@ class PretrainTrainer:
             _freeze(self.model)
         self.engine = ZeroEngine(self.model, opt, group=group, comm=train.comm,
                                  tp_group=self.tp.group if self.tp is not None else None, replicate_group=replicate_group)
+        self.cp_group = cp_group if (cp_group is not None and dist.get_world_size(cp_group) > 1) else None
+        self.cp_world = dist.get_world_size(self.cp_group) if self.cp_group is not None else 1
+        self.cp_rank = dist.get_rank(self.cp_group) if self.cp_group is not None else 0
+        if self.cp_group is not None:
+            self.model.set_context_parallel(self.cp_group, cp_mode)
         self.dp_group = group
         self.replicate_group = replicate_group
         self.step_idx = 0
@@ -72,11 +79,24 @@ class PretrainTrainer:
             return tokens[:, :-1], tokens[:, 1:]
         return tokens, labels
 
+    def _chunk(self, t: torch.Tensor) -> torch.Tensor:
+        """This rank's part of the sequence dimension (everything without context parallelism)."""
+        if self.cp_group is None:
+            return t
+        s = t.shape[1] // self.cp_world
+        if t.shape[1] % self.cp_world:
+            raise ValueError(f"sequence length {t.shape[1]} does not divide over {self.cp_world} context-parallel ranks")
+        return t[:, self.cp_rank * s:(self.cp_rank + 1) * s].contiguous()
+
     def _loss(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
-        # explicit labels mask part of the positions (-100): the mean runs over the labelled ones
+        # explicit labels mask part of the positions (-100): the mean runs over the labelled ones.  With the
+        # sequence sharded, every chunk divides by its share of the count, so that the average of the chunks'
+        # losses (which is what the gradient reduction forms) is the mean over the whole sequence.
         masked = self._masked
-        n_valid = max(int((y != -100).sum()), 1) if masked else None
-        loss = self.model(x, y, n_valid=n_valid)
+        n_valid = max(int((y != -100).sum()), 1) / self.cp_world if masked else None
+        if n_valid is not None and self.cp_group is None:
+            n_valid = int(n_valid)
+        loss = self.model(self._chunk(x), self._chunk(y), n_valid=n_valid)
         return loss
 
     def train_step_device(self, tokens: torch.Tensor, labels: torch.Tensor | None = None) -> torch.Tensor:
@@ -103,6 +123,10 @@ class PretrainTrainer:
         total = total / self.n_micro
         if self.tp is not None:
             total = self.tp.all_reduce(total.float().clone())
+        if self.cp_group is not None:
+            total = total.float().clone()
+            dist.all_reduce(total, group=self.cp_group)
+            total = total / self.cp_world
         return total
 
     def _to_device(self, t: torch.Tensor, slot: int) -> torch.Tensor:
@@ -133,7 +157,7 @@ class PretrainTrainer:
         x_all, y_all = self._split(tokens, labels)
         acc = torch.zeros(2, dtype=torch.float64, device=self.device)
         for i in range(0, x_all.shape[0], mb):
-            x, y = x_all[i:i + mb], y_all[i:i + mb]
+            x, y = self._chunk(x_all[i:i + mb]), self._chunk(y_all[i:i + mb])
             n = (y != -100).sum()
             l = self.model(x, y, n_valid=1)            # n_valid = 1: the plain sum of token losses
             if self.tp is not None:

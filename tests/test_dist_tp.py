@@ -107,3 +107,13 @@ def test_run_loop_over_pipeline_mesh_resumes_gloo(tmp_path, pp, virtual):
     assert straight[0]["losses"] != straight[1]["losses"]   # the data-parallel replicas see different data
     for r in range(4):
         assert max(abs(a - b) for a, b in zip(resumed[r]["losses"], straight[r]["losses"][3:])) < 1e-5
+
+
+def test_context_parallel_training_matches_plain_trainer_gloo():
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29669",
+                        os.path.join(ROOT, "tests", "multi", "cp_train_worker.py")],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "RESULT rank 0 ok=True" in r.stdout and "RESULT rank 1 ok=True" in r.stdout
