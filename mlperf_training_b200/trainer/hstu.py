@@ -98,7 +98,15 @@ class HSTUTrainer:
         self.table = ShardedEmbedding(table_rows, cfg.emb_dim, group=group, device=self.device, dtype=cfg.torch_dtype(),
                                       lr=sparse_lr, seed=seed, comm=emb_comm, init_scale=0.05)
         data_kw = dict(data_kw or {})
-        if data_kw.pop("kind", "synthetic") == "yambda":
+        kind = data_kw.pop("kind", "synthetic")
+        if kind == "sequences":
+            # per-user sequence files (MovieLens / KuaiRand layout), user-hash hold-out for evaluation
+            from ..data.sequences import SequenceFileDataset
+            path = data_kw.pop("path")
+            fmt = data_kw.pop("format", "movielens")
+            self.data = _WorldView(SequenceFileDataset(path, batch_per_gpu, kind=fmt, split="train", seed=seed, **data_kw), self.world)
+            self.eval_data = _WorldView(SequenceFileDataset(path, batch_per_gpu, kind=fmt, split="eval", seed=seed, **data_kw), self.world)
+        elif kind == "yambda":
             # memory-mapped event store: time windows, per-rank slices of each window, user-hash hold-out
             from ..data.yambda import EventStoreDataset
             root = data_kw.pop("root")
@@ -260,7 +268,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     emb = exp.get("embedding") or {}
     d = dict(exp.get("data") or {})
     data_kw = {k: d[k] for k in ("length_median", "length_min", "length_max", "zipf_alpha", "kind", "root", "max_history",
-                                 "min_history", "window_seconds", "holdout", "salt") if k in d}
+                                 "min_history", "window_seconds", "holdout", "salt", "path", "format", "num_candidates",
+                                 "action_weights", "label_bit", "eval_fraction") if k in d}
     bpg = int(exp.get("batch_per_gpu", 128))
     tr = HSTUTrainer(cfg, int(emb.get("rows", 1_000_000)), bpg, device, dense_lr=float(exp.get("dense_lr", 1e-3)),
                      sparse_lr=float(exp.get("sparse_lr", 1e-2)), clip_grad=float(exp.get("clip_grad", 1.0)),
