@@ -225,8 +225,19 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         ck = resume_mgr.load()
         # pipeline stages differ per rank: their parameters travel with the rank's optimizer shard
         bufs = ck["optim"].get("stage_param_bufs") if (pp_size > 1 and ck["optim"] is not None) else ck["dense"]["param_bufs"]
-        for b, saved in zip(trainer.engine.buckets, bufs):
-            b.param_buf.copy_(saved.to(b.param_buf.device))
+        written_by = int(ck["meta"].get("world", world))
+        if written_by != world and pp_size == 1 and tp_size == 1:
+            # another number of data-parallel ranks than the writer's: re-cut the sharded optimizer state
+            from ..checkpoint.reshard import copy_param_bufs, resharded_optimizer_state
+            copy_param_bufs(trainer.engine, bufs)
+            trainer.engine.load_optimizer_state(resharded_optimizer_state(ck["path"], trainer.engine))
+            ck["optim"] = None
+        elif written_by != world:
+            raise ValueError(f"checkpoint written by {written_by} ranks, resumed on {world}: only plain data-parallel runs "
+                             "re-cut their optimizer state")
+        else:
+            for b, saved in zip(trainer.engine.buckets, bufs):
+                b.param_buf.copy_(saved.to(b.param_buf.device))
         if ck["optim"] is not None:
             trainer.engine.load_optimizer_state(ck["optim"])
         CheckpointManager.restore_rng(ck["rng"])
@@ -274,7 +285,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     reached, evals_done, last_eval = False, 0, None
     losses = []
     prof = None
-    step = start_step
+    step = start_step - 1                               # a run resumed at its last step executes nothing
     for step in range(start_step, rc.train_iters):
         if rc.profile_step_end > rc.profile_step_start and step == rc.profile_step_start and rank == 0:
             from ..utils.profiler import StepProfiler

@@ -117,3 +117,15 @@ def test_context_parallel_training_matches_plain_trainer_gloo():
                        env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "RESULT rank 0 ok=True" in r.stdout and "RESULT rank 1 ok=True" in r.stdout
+
+
+@pytest.mark.parametrize("writers,readers", [(4, 2), (2, 4)])
+def test_resume_on_another_number_of_ranks_recuts_optimizer_state_gloo(tmp_path, writers, readers):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    for n, phase in ((writers, "write"), (readers, "read")):
+        r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                            "--master-addr", "127.0.0.1", "--master-port", "29671",
+                            os.path.join(ROOT, "tests", "multi", "reshard_worker.py"), str(tmp_path), phase],
+                           env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+        assert "RESULT rank 0 ok=True" in r.stdout
