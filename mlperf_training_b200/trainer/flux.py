@@ -3,7 +3,9 @@
 Constant-with-warm-up LR, AdamW (beta2 0.95, wd 0.1), prompt dropout 0.1, evaluation every
 ``eval_every_samples`` samples against a target validation loss, FSDP-sharded optimizer state with
 parameters kept gathered after forward (``reshard_after_forward: 0`` as in the reference's
-submission, flux1/primus/config_common.sh:134).  Event stream and hyper-parameters follow
+submission, flux1/primus/config_common.sh:134), synthetic warm-up steps whose traces are removed
+before the clock starts, checkpoints every ``checkpoint_every`` steps (keep the last ``keep_last``,
+resume from the latest: flux.1_schnell_t2i-pretrain.yaml:33-37) and ``die_at_step`` fault injection.  Event stream and hyper-parameters follow
 flux1/primus/conf/flux.1_schnell_t2i-pretrain.yaml:25-89 and config_MI355X_1x8x32.sh:7-12.
 """
 from __future__ import annotations
@@ -14,6 +16,7 @@ import time
 import torch
 import torch.distributed as dist
 
+from ..checkpoint.manager import CheckpointManager
 from ..mllog import core as ml
 from ..models.mmdit import PRESETS, MMDiT, MMDiTConfig
 from ..parallel.engine import OptimConfig, ZeroEngine
@@ -75,6 +78,30 @@ class FluxTrainer:
         dev = [t.to(self.device, non_blocking=True) for t in batch]
         return float(self.train_step_device(*dev).item())
 
+    # ------------------------------------------------------------------ state (checkpoints, warm-up restore)
+    def snapshot(self) -> dict:
+        """Everything a step changes: flat parameters, this rank's optimizer shard, step counters and
+        the noise / timestep generator."""
+        e = self.engine
+        return {"param_bufs": [b.param_buf.detach().clone() for b in e.buckets],
+                "m": [b.m.clone() for b in e.buckets], "v": [b.v.clone() for b in e.buckets],
+                "master": [None if b.master is None else b.master.clone() for b in e.buckets],
+                "step_count": e.step_count, "step_idx": self.step_idx, "gen": self.gen.get_state().clone()}
+
+    def restore(self, snap: dict) -> None:
+        e = self.engine
+        for b, p, m, v, w in zip(e.buckets, snap["param_bufs"], snap["m"], snap["v"], snap["master"]):
+            b.param_buf.copy_(p.to(b.param_buf.device))
+            b.m.copy_(m.to(b.m.device))
+            b.v.copy_(v.to(b.v.device))
+            if b.master is not None and w is not None:
+                b.master.copy_(w.to(b.master.device))
+            b.grad_buf.zero_()
+        e.step_count, self.step_idx = int(snap["step_count"]), int(snap["step_idx"])
+        self.gen.set_state(snap["gen"].cpu() if self.device.type == "cpu" else snap["gen"])
+        from ..ops.linear import bump_weight_epoch
+        bump_weight_epoch()              # cached low-precision weight copies belong to the old weights
+
     @torch.no_grad()
     def eval_loss(self, batch) -> float:
         g = torch.Generator(device=self.device).manual_seed(1234)
@@ -85,13 +112,27 @@ class FluxTrainer:
         return float(l)
 
 
+def _to_cpu(v):
+    if torch.is_tensor(v):
+        return v.detach().cpu()
+    if isinstance(v, list):
+        return [_to_cpu(x) for x in v]
+    return v
+
+
 def run(exp: dict, device: str | None = None, stream=None) -> dict:
     rank = dist.get_rank() if dist.is_initialized() else 0
     world = dist.get_world_size() if dist.is_initialized() else 1
     device = device or ("cuda" if torch.cuda.is_available() else "cpu")
-    log = ml.MLLogger(rank=rank, stream=stream or sys.stdout, sync=dist.barrier if world > 1 else None)
-    log.log_init_start()
-    log.log_submission(exp.get("benchmark", "flux1"), platform=f"1xB200x{world}")
+    sync = dist.barrier if world > 1 else None
+    ck_dir = str(exp.get("checkpoint_dir") or "")
+    mgr = CheckpointManager(ck_dir, rank, world, int(exp.get("keep_last", 3)), sync) if ck_dir else None
+    resuming = bool(mgr and mgr.present())
+    log = ml.MLLogger(rank=rank, stream=stream or sys.stdout, filename=str(exp.get("mllog_file") or "") or None, sync=sync,
+                      append=resuming)
+    if not resuming:
+        log.log_init_start()
+        log.log_submission(exp.get("benchmark", "flux1"), platform=f"1xB200x{world}")
     spec = dict(exp.get("model") or {})
     cfg = PRESETS[spec.pop("preset", "flux1-schnell")]()
     for k, v in spec.items():
@@ -105,18 +146,37 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                      comm=(exp.get("fsdp") or {}).get("comm", "nccl"), seed=int(exp.get("seed", 0)),
                      micro_batch=exp.get("micro_batch"))
     data = SyntheticFluxData(cfg, seed=int(exp.get("seed", 0)))
-    log.log_hyperparameters({"global_batch_size": gbs, "seed": int(exp.get("seed", 0)), "opt_base_learning_rate": opt.lr,
-                             "opt_learning_rate_warmup_steps": tr.warmup_iters, "opt_adamw_beta_2": opt.beta2,
-                             "opt_adamw_weight_decay": opt.weight_decay})
-    log.log_init_stop_run_start()
-    log.start(ml.BLOCK_START, metadata={"samples_count": 0})
+    start_step = 0
+    if resuming:
+        ck = mgr.load()
+        tr.restore(ck["optim"]["flux_state"])
+        start_step = int(ck["meta"]["step"])
+    else:
+        log.log_hyperparameters({"global_batch_size": gbs, "seed": int(exp.get("seed", 0)), "opt_base_learning_rate": opt.lr,
+                                 "opt_learning_rate_warmup_steps": tr.warmup_iters, "opt_adamw_beta_2": opt.beta2,
+                                 "opt_adamw_weight_decay": opt.weight_decay})
+        # MLPerf warm-up before the clock starts: synthetic train and validation steps, then every trace of
+        # them is removed (flux1/primus/conf/flux.1_schnell_t2i-pretrain.yaml:82-89: 2 train + 2 val steps)
+        n_wt, n_wv = int(exp.get("warmup_train_steps", 0)), int(exp.get("warmup_eval_steps", 0))
+        if n_wt or n_wv:
+            snap = tr.snapshot()
+            for i in range(n_wt):
+                tr.train_step(data.batch(2 * 10**6 + i, rank, local_batch))
+            for i in range(n_wv):
+                tr.eval_loss(data.batch(3 * 10**6 + i, rank, local_batch))
+            tr.restore(snap)
+        log.log_init_stop_run_start()
+    log.start(ml.BLOCK_START, metadata={"samples_count": start_step * gbs})
     iters = int(exp.get("train_iters", 10))
+    ck_every, die_at = int(exp.get("checkpoint_every", 0)), int(exp.get("die_at_step", 0))
     eval_every = int(exp.get("eval_every_samples", 0))
     target = float(exp.get("target_eval_loss", 0.0))
     timer = ml.ThroughputTimer(gbs)
     t0 = time.perf_counter()
-    losses, reached, last_eval, next_eval = [], False, None, eval_every
-    for step in range(iters):
+    losses, reached, last_eval = [], False, None
+    next_eval = (start_step * gbs // eval_every + 1) * eval_every if eval_every else 0
+    samples = start_step * gbs
+    for step in range(start_step, iters):
         timer.step_start()
         losses.append(tr.train_step(data.batch(step, rank, local_batch)))
         timer.step_stop()
@@ -133,8 +193,17 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                 reached = True
                 break
             log.start(ml.BLOCK_START, metadata={"samples_count": samples})
+        dying = die_at and step + 1 == die_at
+        if mgr is not None and ((ck_every and (step + 1) % ck_every == 0) or dying):
+            mgr.save(step + 1, dense=None, optim_shard={"flux_state": {k: _to_cpu(v) for k, v in tr.snapshot().items()}},
+                     meta={"samples": samples, "run_started": True})
+        if dying:
+            if world > 1:
+                dist.barrier()
+            log.close()
+            sys.exit(42)
     if not reached:
-        log.end(ml.BLOCK_STOP, metadata={"samples_count": timer.samples})
-    log.log_run_stop(reached or target <= 0, samples=timer.samples, duration_s=time.perf_counter() - t0)
+        log.end(ml.BLOCK_STOP, metadata={"samples_count": samples})
+    log.log_run_stop(reached or target <= 0, samples=samples, duration_s=time.perf_counter() - t0)
     return {"losses": losses, "eval_loss": last_eval, "throughput": timer.throughput(), "records": log.lines,
-            "trainer": tr}
+            "trainer": tr, "steps": len(losses)}

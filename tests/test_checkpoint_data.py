@@ -190,3 +190,21 @@ def test_run_loop_monitors(tmp_path):
     assert CheckpointManager(str(tmp_path / "ck")).steps() == [2, 4]
     lines = [json.loads(l) for l in (tmp_path / "perf.jsonl").read_text().splitlines()]
     assert len(lines) == 4 and lines[-1]["step"] == 4 and lines[-1]["samples_per_s"] > 0
+
+
+def test_flux_run_warmup_leaves_no_trace_and_resume_matches(tmp_path):
+    from mlperf_training_b200.trainer.flux import run
+    base = dict(model=dict(preset="tiny-mmdit"), global_batch=2, train_iters=5, lr=2e-3, lr_warmup_iters=2, eval_every_samples=6)
+    ref = run(dict(base), device="cpu", stream=io.StringIO())
+    warm = run(dict(base, warmup_train_steps=2, warmup_eval_steps=1), device="cpu", stream=io.StringIO())
+    assert warm["losses"] == ref["losses"] and warm["eval_loss"] == ref["eval_loss"]
+    exp = dict(base, checkpoint_dir=str(tmp_path / "ck"), checkpoint_every=2, keep_last=1, die_at_step=3,
+               mllog_file=str(tmp_path / "ml.log"))
+    with pytest.raises(SystemExit) as ex:
+        run(dict(exp), device="cpu", stream=io.StringIO())
+    assert ex.value.code == 42
+    assert CheckpointManager(str(tmp_path / "ck")).steps() == [3]                      # keep_last = 1 dropped step 2
+    out = run(dict(exp, die_at_step=0), device="cpu", stream=io.StringIO())
+    assert out["steps"] == 2 and out["losses"] == ref["losses"][3:]
+    lines = (tmp_path / "ml.log").read_text().splitlines()
+    assert sum("run_start" in l for l in lines) == 1 and sum("run_stop" in l for l in lines) == 1
