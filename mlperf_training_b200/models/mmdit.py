@@ -47,6 +47,11 @@ class MMDiTConfig:
     rope_theta: float = 10000.0
     dtype: str = "bf16"
     precision: str = "bf16"
+    # activation recompute: "full" runs the first ``recompute_ratio`` of the double and of the single blocks
+    # again in backward and keeps only their inputs (gradient checkpointing ratio 1.0 in
+    # flux1/primus/conf/flux.1_schnell_t2i-pretrain.yaml:62-70)
+    recompute: str = "none"
+    recompute_ratio: float = 1.0
 
     @property
     def img_tokens(self) -> int:
@@ -257,12 +262,23 @@ class MMDiT(nn.Module):
         vec = self.time_in2(torch.nn.functional.silu(self.time_in1(temb))) + \
             self.vec_in2(torch.nn.functional.silu(self.vec_in1(pooled.to(dt))))
         vec_act = torch.nn.functional.silu(vec)
-        for blk in self.double_blocks:
-            x_img, x_txt = blk(x_img, x_txt, vec_act, cos, sin, B)
+        ckpt = cfg.recompute == "full" and torch.is_grad_enabled()
+        if ckpt:
+            from torch.utils.checkpoint import checkpoint
+        n_d = round(cfg.recompute_ratio * len(self.double_blocks)) if ckpt else 0
+        n_s = round(cfg.recompute_ratio * len(self.single_blocks)) if ckpt else 0
+        for i, blk in enumerate(self.double_blocks):
+            if i < n_d:
+                x_img, x_txt = checkpoint(blk, x_img, x_txt, vec_act, cos, sin, B, use_reentrant=False)
+            else:
+                x_img, x_txt = blk(x_img, x_txt, vec_act, cos, sin, B)
         St, Si = cfg.txt_tokens, cfg.img_tokens
         x = torch.cat([x_txt.view(B, St, -1), x_img.view(B, Si, -1)], 1).reshape(-1, cfg.hidden)
-        for blk in self.single_blocks:
-            x = blk(x, vec_act, cos, sin, B)
+        for i, blk in enumerate(self.single_blocks):
+            if i < n_s:
+                x = checkpoint(blk, x, vec_act, cos, sin, B, use_reentrant=False)
+            else:
+                x = blk(x, vec_act, cos, sin, B)
         x = x.view(B, St + Si, -1)[:, St:].reshape(-1, cfg.hidden)
         shift, scale = self.final_mod(vec_act).chunk(2, dim=-1)
         return self.final_out(_modulate(_ln(x), shift, scale, B)).view(B, Si, cfg.in_channels)

@@ -208,3 +208,24 @@ def test_flux_run_warmup_leaves_no_trace_and_resume_matches(tmp_path):
     assert out["steps"] == 2 and out["losses"] == ref["losses"][3:]
     lines = (tmp_path / "ml.log").read_text().splitlines()
     assert sum("run_start" in l for l in lines) == 1 and sum("run_stop" in l for l in lines) == 1
+
+
+def test_mmdit_recompute_gives_the_same_gradients():
+    from mlperf_training_b200.models.mmdit import MMDiT, tiny_mmdit
+    cfg = tiny_mmdit()
+    plain = MMDiT(cfg, device="cpu", seed=4)
+    import dataclasses
+    rec = MMDiT(dataclasses.replace(cfg, recompute="full", recompute_ratio=0.5), device="cpu", seed=4)
+    rec.load_state_dict(plain.state_dict())
+    g = torch.Generator().manual_seed(0)
+    lat = torch.randn(2, cfg.img_tokens, cfg.in_channels, generator=g)
+    txt = torch.randn(2, cfg.txt_tokens, cfg.txt_dim, generator=g)
+    vec = torch.randn(2, cfg.vec_dim, generator=g)
+    for m in (plain, rec):
+        m.loss(lat, txt, vec, generator=torch.Generator().manual_seed(1)).backward()
+    for (n, p), (_, q) in zip(plain.named_parameters(), rec.named_parameters()):
+        gp = p.grad if p.grad is not None else getattr(p, "main_grad", None)
+        gq = q.grad if q.grad is not None else getattr(q, "main_grad", None)
+        assert (gp is None) == (gq is None), n
+        if gp is not None:
+            assert torch.allclose(gp, gq, atol=1e-6), n
