@@ -157,11 +157,22 @@ def _rope(x, cos, sin):
     return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
 
 
+def _attention(q, k, v, sp):
+    """Joint (non-causal) attention; with ``sp = (group, ...)`` the tokens are sharded over the group and
+    the sequence shards are traded for head shards around the kernel (Ulysses).  Non-causal attention does
+    not care in which order the exchange lines the chunks up, as long as q, k and v agree - and they do."""
+    if sp is None:
+        return F.attention(q, k, v, causal=False)
+    from ..parallel.context import ulysses_attention
+    return ulysses_attention(q.contiguous(), k.contiguous(), v.contiguous(), sp[0], causal=False)
+
+
 class DoubleBlock(nn.Module):
     def __init__(self, cfg: MMDiTConfig, dtype, device):
         super().__init__()
         d, m, hd = cfg.hidden, cfg.mlp_hidden, cfg.head_dim
         self.cfg = cfg
+        self.sp = None
         for s in ("img", "txt"):
             setattr(self, f"{s}_mod", Linear(d, 6 * d, dtype, device))
             setattr(self, f"{s}_qkv", Linear(d, 3 * d, dtype, device))
@@ -185,7 +196,7 @@ class DoubleBlock(nn.Module):
         q = _rope(torch.cat([parts["txt"][0], parts["img"][0]], 1), cos, sin)
         k = _rope(torch.cat([parts["txt"][1], parts["img"][1]], 1), cos, sin)
         v = torch.cat([parts["txt"][2], parts["img"][2]], 1)
-        attn = F.attention(q, k, v, causal=False)
+        attn = _attention(q, k, v, self.sp)
         outs = {}
         for s, x, a in (("txt", txt, attn[:, :St]), ("img", img, attn[:, St:])):
             mod = parts[s][3]
@@ -201,6 +212,7 @@ class SingleBlock(nn.Module):
         super().__init__()
         d, m = cfg.hidden, cfg.mlp_hidden
         self.cfg = cfg
+        self.sp = None
         self.mod = Linear(d, 3 * d, dtype, device)
         self.linear1 = Linear(d, 3 * d + m, dtype, device)
         self.linear2 = Linear(d + m, d, dtype, device)
@@ -215,7 +227,7 @@ class SingleBlock(nn.Module):
         qkv, mlp = y[:, :3 * d], y[:, 3 * d:]
         q, k, v = qkv.reshape(B, S, 3, H, hd).unbind(2)
         q, k = self.qknorm(q, k)
-        attn = F.attention(_rope(q, cos, sin), _rope(k, cos, sin), v.contiguous(), causal=False).reshape(-1, d)
+        attn = _attention(_rope(q, cos, sin), _rope(k, cos, sin), v.contiguous(), self.sp).reshape(-1, d)
         out = self.linear2(torch.cat([attn, F.gelu(mlp.contiguous())], dim=-1), pr)
         return _gate(x, out, gate, B)
 
@@ -239,6 +251,7 @@ class MMDiT(nn.Module):
         self.final_mod = Linear(d, 2 * d, dtype, device)
         self.final_out = Linear(d, cfg.in_channels, dtype, device)
         self._rope = None
+        self.sp = None
 
     def rope(self, device):
         if self._rope is None or self._rope[0].device != torch.device(device):
@@ -251,11 +264,41 @@ class MMDiT(nn.Module):
             self._rope = (cos.to(device), sin.to(device))
         return self._rope
 
+    def set_sequence_parallel(self, group) -> None:
+        """Shard the image and the text tokens of every sample over ``group`` (rank r keeps the r-th
+        chunk of each): ``forward`` still takes whole samples and returns this rank's chunk of the
+        prediction, ``loss`` the mean over that chunk.  Parameters are replicated over the group, so the
+        gradient reduction must span it (``sp_size`` of flux1/primus/conf/flux.1_schnell_t2i-pretrain.yaml:48)."""
+        import torch.distributed as dist
+        W = dist.get_world_size(group) if group is not None else 1
+        cfg = self.cfg
+        if W > 1 and (cfg.n_heads % W or cfg.img_tokens % W or cfg.txt_tokens % W):
+            raise ValueError(f"{cfg.n_heads} heads, {cfg.img_tokens} image and {cfg.txt_tokens} text tokens must divide over {W} ranks")
+        self.sp = (group, W, dist.get_rank(group)) if W > 1 else None
+        for blk in list(self.double_blocks) + list(self.single_blocks):
+            blk.sp = self.sp
+
+    def _chunk(self, x, n_tokens: int):
+        """This rank's tokens of ``[B, n_tokens, ...]`` (all of them without sequence parallelism)."""
+        if self.sp is None:
+            return x
+        _, W, r = self.sp
+        c = n_tokens // W
+        return x[:, r * c:(r + 1) * c]
+
     def forward(self, img, txt, pooled, t):
         cfg = self.cfg
         B = img.shape[0]
         dt = cfg.torch_dtype()
         cos, sin = self.rope(img.device)
+        St, Si = cfg.txt_tokens, cfg.img_tokens
+        if self.sp is not None:
+            _, W, r = self.sp
+            img, txt = self._chunk(img, Si).contiguous(), self._chunk(txt, St).contiguous()
+            ct, ci = St // W, Si // W
+            rows = torch.cat([torch.arange(r * ct, (r + 1) * ct), St + torch.arange(r * ci, (r + 1) * ci)]).to(cos.device)
+            cos, sin = cos[rows].contiguous(), sin[rows].contiguous()
+            St, Si = ct, ci
         x_img = self.img_in(img.reshape(-1, cfg.in_channels).to(dt))
         x_txt = self.txt_in(txt.reshape(-1, cfg.txt_dim).to(dt), cfg.precision)
         temb = timestep_embedding(t).to(dt)
@@ -272,7 +315,6 @@ class MMDiT(nn.Module):
                 x_img, x_txt = checkpoint(blk, x_img, x_txt, vec_act, cos, sin, B, use_reentrant=False)
             else:
                 x_img, x_txt = blk(x_img, x_txt, vec_act, cos, sin, B)
-        St, Si = cfg.txt_tokens, cfg.img_tokens
         x = torch.cat([x_txt.view(B, St, -1), x_img.view(B, Si, -1)], 1).reshape(-1, cfg.hidden)
         for i, blk in enumerate(self.single_blocks):
             if i < n_s:
@@ -301,7 +343,7 @@ class MMDiT(nn.Module):
             txt = torch.where(drop[:, None, None], e_txt.expand_as(txt), txt)
             pooled = torch.where(drop[:, None], e_pool.expand_as(pooled), pooled)
         pred = self.forward(xt, txt, pooled, t)
-        return ((pred.float() - (eps - x0)) ** 2).mean()
+        return ((pred.float() - self._chunk(eps - x0, self.cfg.img_tokens)) ** 2).mean()
 
 
 def patchify(latents: torch.Tensor, patch: int = 2) -> torch.Tensor:

@@ -46,19 +46,26 @@ class SyntheticFluxData:
 
 class FluxTrainer:
     def __init__(self, cfg: MMDiTConfig, opt: OptimConfig, device, local_batch: int, warmup_iters: int = 0,
-                 prompt_dropout: float = 0.1, comm: str = "nccl", seed: int = 0, micro_batch: int | None = None):
+                 prompt_dropout: float = 0.1, comm: str = "nccl", seed: int = 0, micro_batch: int | None = None,
+                 sp_group=None, group=None):
+        """``sp_group``: ranks that share every sample and split its tokens (Ulysses); ``group`` the ranks the
+        optimizer shards over and averages gradients across (all ranks when None) - it must contain the
+        sequence-parallel ranks, which all draw the same noise and timesteps from the shared seed."""
         self.cfg, self.device = cfg, torch.device(device)
         self.model = MMDiT(cfg, device=self.device, seed=seed)
-        self.engine = ZeroEngine(self.model, opt, bucket_of=flux_bucket_of, comm=comm)
+        if sp_group is not None:
+            self.model.set_sequence_parallel(sp_group)
+        self.engine = ZeroEngine(self.model, opt, bucket_of=flux_bucket_of, comm=comm, group=group)
         self.local_batch = local_batch
         self.micro_batch = micro_batch or local_batch
         self.warmup_iters = warmup_iters
         self.prompt_dropout = prompt_dropout
         self.step_idx = 0
         self.gen = torch.Generator(device=self.device).manual_seed(seed + 17)
+        self._lr_scale = 1.0
 
     def lr(self) -> float:
-        base = self.engine.opt.lr
+        base = self.engine.opt.lr * self._lr_scale
         return base * min(1.0, (self.step_idx + 1) / self.warmup_iters) if self.warmup_iters > 0 else base
 
     def train_step_device(self, latents, txt, pooled) -> torch.Tensor:
@@ -80,13 +87,39 @@ class FluxTrainer:
 
     # ------------------------------------------------------------------ state (checkpoints, warm-up restore)
     def snapshot(self) -> dict:
-        """Everything a step changes: flat parameters, this rank's optimizer shard, step counters and
-        the noise / timestep generator."""
+        """Everything a step changes, copied to host memory: flat parameters, this rank's optimizer
+        shard, step counters and the noise / timestep generator."""
         e = self.engine
-        return {"param_bufs": [b.param_buf.detach().clone() for b in e.buckets],
-                "m": [b.m.clone() for b in e.buckets], "v": [b.v.clone() for b in e.buckets],
-                "master": [None if b.master is None else b.master.clone() for b in e.buckets],
+
+        def host(t):
+            return None if t is None else t.detach().to("cpu", copy=True)
+        return {"param_bufs": [host(b.param_buf) for b in e.buckets], "m": [host(b.m) for b in e.buckets],
+                "v": [host(b.v) for b in e.buckets], "master": [host(b.master) for b in e.buckets],
                 "step_count": e.step_count, "step_idx": self.step_idx, "gen": self.gen.get_state().clone()}
+
+    def run_warmup(self, train_batches, eval_batches) -> None:
+        """Untimed steps before the clock starts, leaving no trace and needing no copy of the state: the
+        steps run with learning rate 0 (AdamW then leaves every weight bit-identical), and afterwards the
+        moments - zero before, because a warm-up only precedes a fresh start - the gradients, the step
+        counters and the generator are put back."""
+        e = self.engine
+        if e.step_count != 0 or any(float(b.m.abs().max()) != 0 for b in e.buckets):
+            raise RuntimeError("warm-up steps precede the first optimizer step of a fresh run")
+        gen, idx = self.gen.get_state().clone(), self.step_idx
+        self._lr_scale = 0.0
+        try:
+            for b in train_batches:
+                self.train_step(b)
+            for b in eval_batches:
+                self.eval_loss(b)
+        finally:
+            self._lr_scale = 1.0
+        for b in e.buckets:
+            b.m.zero_()
+            b.v.zero_()
+            b.grad_buf.zero_()
+        e.step_count, self.step_idx = 0, idx
+        self.gen.set_state(gen)
 
     def restore(self, snap: dict) -> None:
         e = self.engine
@@ -112,14 +145,6 @@ class FluxTrainer:
         return float(l)
 
 
-def _to_cpu(v):
-    if torch.is_tensor(v):
-        return v.detach().cpu()
-    if isinstance(v, list):
-        return [_to_cpu(x) for x in v]
-    return v
-
-
 def run(exp: dict, device: str | None = None, stream=None) -> dict:
     rank = dist.get_rank() if dist.is_initialized() else 0
     world = dist.get_world_size() if dist.is_initialized() else 1
@@ -137,14 +162,24 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     cfg = PRESETS[spec.pop("preset", "flux1-schnell")]()
     for k, v in spec.items():
         setattr(cfg, k, tuple(v) if isinstance(v, list) else v)
+    ratio = float(exp.get("grad_checkpoint_ratio", 0.0) or 0.0)
+    if ratio > 0:
+        cfg.recompute, cfg.recompute_ratio = "full", min(ratio, 1.0)
     gbs = int(exp.get("global_batch", 256))
-    local_batch = int(exp.get("local_batch", gbs // world))
+    sp_size = int(exp.get("sp_size", 1))
+    sp_group, dp_rank, dp_world = None, rank, world
+    if sp_size > 1:
+        # sequence-parallel ranks share their samples: the data-parallel coordinate picks the batch
+        from ..parallel.mesh import Mesh, MeshSpec
+        mesh = Mesh(MeshSpec(cp=sp_size))
+        sp_group, dp_rank, dp_world = mesh.group("cp"), mesh.index("dp"), mesh.size("dp")
+    local_batch = int(exp.get("local_batch", gbs // dp_world))
     opt = OptimConfig(lr=float(exp.get("lr", 2.5e-4)), beta1=0.9, beta2=float(exp.get("adam_beta2", 0.95)), eps=1e-8,
                       weight_decay=float(exp.get("weight_decay", 0.1)), clip_grad=float(exp.get("clip_grad", 1.0)))
     tr = FluxTrainer(cfg, opt, device, local_batch, warmup_iters=int(exp.get("lr_warmup_iters", 0)),
                      prompt_dropout=float(exp.get("prompt_dropout", 0.1)),
                      comm=(exp.get("fsdp") or {}).get("comm", "nccl"), seed=int(exp.get("seed", 0)),
-                     micro_batch=exp.get("micro_batch"))
+                     micro_batch=exp.get("micro_batch"), sp_group=sp_group)
     data = SyntheticFluxData(cfg, seed=int(exp.get("seed", 0)))
     start_step = 0
     if resuming:
@@ -159,12 +194,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         # them is removed (flux1/primus/conf/flux.1_schnell_t2i-pretrain.yaml:82-89: 2 train + 2 val steps)
         n_wt, n_wv = int(exp.get("warmup_train_steps", 0)), int(exp.get("warmup_eval_steps", 0))
         if n_wt or n_wv:
-            snap = tr.snapshot()
-            for i in range(n_wt):
-                tr.train_step(data.batch(2 * 10**6 + i, rank, local_batch))
-            for i in range(n_wv):
-                tr.eval_loss(data.batch(3 * 10**6 + i, rank, local_batch))
-            tr.restore(snap)
+            tr.run_warmup([data.batch(2 * 10**6 + i, dp_rank, local_batch) for i in range(n_wt)],
+                          [data.batch(3 * 10**6 + i, dp_rank, local_batch) for i in range(n_wv)])
         log.log_init_stop_run_start()
     log.start(ml.BLOCK_START, metadata={"samples_count": start_step * gbs})
     iters = int(exp.get("train_iters", 10))
@@ -178,7 +209,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     samples = start_step * gbs
     for step in range(start_step, iters):
         timer.step_start()
-        losses.append(tr.train_step(data.batch(step, rank, local_batch)))
+        losses.append(tr.train_step(data.batch(step, dp_rank, local_batch)))
         timer.step_stop()
         samples = (step + 1) * gbs
         log.event(ml.TRAIN_LOSS, losses[-1], metadata={"samples_count": samples})
@@ -186,7 +217,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             next_eval += eval_every
             log.end(ml.BLOCK_STOP, metadata={"samples_count": samples})
             log.start(ml.EVAL_START, metadata={"samples_count": samples})
-            last_eval = tr.eval_loss(data.batch(10**6, rank, local_batch))
+            last_eval = tr.eval_loss(data.batch(10**6, dp_rank, local_batch))
             log.event(ml.EVAL_ACCURACY, last_eval, metadata={"samples_count": samples})
             log.end(ml.EVAL_STOP, metadata={"samples_count": samples})
             if target > 0 and last_eval <= target:
@@ -195,7 +226,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             log.start(ml.BLOCK_START, metadata={"samples_count": samples})
         dying = die_at and step + 1 == die_at
         if mgr is not None and ((ck_every and (step + 1) % ck_every == 0) or dying):
-            mgr.save(step + 1, dense=None, optim_shard={"flux_state": {k: _to_cpu(v) for k, v in tr.snapshot().items()}},
+            mgr.save(step + 1, dense=None, optim_shard={"flux_state": tr.snapshot()},
                      meta={"samples": samples, "run_started": True})
         if dying:
             if world > 1:

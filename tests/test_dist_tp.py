@@ -129,3 +129,13 @@ def test_resume_on_another_number_of_ranks_recuts_optimizer_state_gloo(tmp_path,
                            env=env, capture_output=True, text=True, timeout=600)
         assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
         assert "RESULT rank 0 ok=True" in r.stdout
+
+
+def test_flux_sequence_parallel_training_matches_plain_trainer_gloo():
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29673",
+                        os.path.join(ROOT, "tests", "multi", "flux_sp_worker.py")],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "RESULT rank 0 ok=True" in r.stdout and "RESULT rank 1 ok=True" in r.stdout
