@@ -47,7 +47,7 @@ class SyntheticFluxData:
 class FluxTrainer:
     def __init__(self, cfg: MMDiTConfig, opt: OptimConfig, device, local_batch: int, warmup_iters: int = 0,
                  prompt_dropout: float = 0.1, comm: str = "nccl", seed: int = 0, micro_batch: int | None = None,
-                 sp_group=None, group=None):
+                 sp_group=None, group=None, replicate_group=None):
         """``sp_group``: ranks that share every sample and split its tokens (Ulysses); ``group`` the ranks the
         optimizer shards over and averages gradients across (all ranks when None) - it must contain the
         sequence-parallel ranks, which all draw the same noise and timesteps from the shared seed."""
@@ -55,7 +55,8 @@ class FluxTrainer:
         self.model = MMDiT(cfg, device=self.device, seed=seed)
         if sp_group is not None:
             self.model.set_sequence_parallel(sp_group)
-        self.engine = ZeroEngine(self.model, opt, bucket_of=flux_bucket_of, comm=comm, group=group)
+        self.engine = ZeroEngine(self.model, opt, bucket_of=flux_bucket_of, comm=comm, group=group,
+                                 replicate_group=replicate_group)
         self.local_batch = local_batch
         self.micro_batch = micro_batch or local_batch
         self.warmup_iters = warmup_iters
@@ -173,13 +174,22 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         from ..parallel.mesh import Mesh, MeshSpec
         mesh = Mesh(MeshSpec(cp=sp_size))
         sp_group, dp_rank, dp_world = mesh.group("cp"), mesh.index("dp"), mesh.size("dp")
+    replicate = int((exp.get("fsdp") or {}).get("dp_replicate", 1) or 1)
+    shard_group = rep_group = None
+    if replicate > 1 and world > 1:
+        # hybrid sharding: optimizer state sharded inside a group of world / replicate ranks, replicated across groups
+        if sp_size > 1:
+            raise NotImplementedError("dp_replicate is not combined with sp_size")
+        from ..parallel.mesh import Mesh, MeshSpec
+        hmesh = Mesh(MeshSpec(dp_replicate=replicate))
+        shard_group, rep_group = hmesh.group("dp_shard"), hmesh.group("dp_replicate")
     local_batch = int(exp.get("local_batch", gbs // dp_world))
     opt = OptimConfig(lr=float(exp.get("lr", 2.5e-4)), beta1=0.9, beta2=float(exp.get("adam_beta2", 0.95)), eps=1e-8,
                       weight_decay=float(exp.get("weight_decay", 0.1)), clip_grad=float(exp.get("clip_grad", 1.0)))
     tr = FluxTrainer(cfg, opt, device, local_batch, warmup_iters=int(exp.get("lr_warmup_iters", 0)),
                      prompt_dropout=float(exp.get("prompt_dropout", 0.1)),
-                     comm=(exp.get("fsdp") or {}).get("comm", "nccl"), seed=int(exp.get("seed", 0)),
-                     micro_batch=exp.get("micro_batch"), sp_group=sp_group)
+                     comm=(exp.get("fsdp") or {}).get("comm", "nccl") if replicate == 1 else "nccl", seed=int(exp.get("seed", 0)),
+                     micro_batch=exp.get("micro_batch"), sp_group=sp_group, group=shard_group, replicate_group=rep_group)
     data = SyntheticFluxData(cfg, seed=int(exp.get("seed", 0)))
     start_step = 0
     if resuming:

@@ -16,6 +16,18 @@ from mlperf_training_b200.trainer.flux import FluxTrainer, SyntheticFluxData, ru
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dist.init_process_group("gloo")
+    if world == 4:
+        # hybrid sharding (2 shards x 2 replicas) follows plain 4-way data parallelism
+        base = dict(model=dict(preset="tiny-mmdit"), global_batch=4, train_iters=3, lr=2e-3)
+        a = run(dict(base), device="cpu", stream=io.StringIO())
+        b = run(dict(base, fsdp=dict(dp_replicate=2)), device="cpu", stream=io.StringIO())
+        ok = max(abs(x - y) for x, y in zip(a["losses"], b["losses"])) < 1e-5
+        for (n, p), (_, q) in zip(a["trainer"].model.named_parameters(), b["trainer"].model.named_parameters()):
+            ok &= (p - q).abs().max().item() < 1e-5
+        print(f"RESULT rank {rank} ok={ok}", flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
+        sys.exit(0 if ok else 1)
     solo = [dist.new_group([r]) for r in range(world)][rank]
     cfg = tiny_mmdit()
     opt = OptimConfig(lr=2e-3, weight_decay=0.01, clip_grad=1.0)

@@ -131,9 +131,10 @@ def test_resume_on_another_number_of_ranks_recuts_optimizer_state_gloo(tmp_path,
         assert "RESULT rank 0 ok=True" in r.stdout
 
 
-def test_flux_sequence_parallel_training_matches_plain_trainer_gloo():
+@pytest.mark.parametrize("ranks", [2, 4])        # 2: sequence parallel vs plain; 4: hybrid sharding vs plain data parallel
+def test_flux_sequence_parallel_and_hybrid_sharding_match_plain_trainer_gloo(ranks):
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}",
                         "--master-addr", "127.0.0.1", "--master-port", "29673",
                         os.path.join(ROOT, "tests", "multi", "flux_sp_worker.py")],
                        env=env, capture_output=True, text=True, timeout=900)
