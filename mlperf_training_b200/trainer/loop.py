@@ -70,6 +70,8 @@ class RunConfig:
     dp_replicate: int = 1                               # hybrid sharding: copies of each optimizer-state shard
     tensor_parallel: int = 1                            # tensor + sequence parallel size (Megatron layout)
     sequence_parallel: int = 1
+    expert_parallel: int = 1                            # ranks an MoE layer's experts are spread over (a divisor of the world)
+    moe_dispatch: str = "fused"                         # "fused": peer-memory push / pull kernels (GPUs); "nccl": all-to-all
     pipeline_parallel: int = 1
     virtual_pipeline_parallel: int | None = None        # model chunks per pipeline rank (interleaved 1F1B)
     context_parallel: int = 1
@@ -178,7 +180,19 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         dp_group = mesh.group("dp_shard") if replicate > 1 else mesh.group("dp")
         if cfg.precision != "bf16":
             cfg.precision = "bf16"       # the tensor-parallel linears run the bf16 tcgen05 GEMMs
-    cp_group = None
+    cp_group = ep_group = None
+    ep_size = min(int(rc.expert_parallel), world) if cfg.n_experts else 1
+    if ep_size > 1:
+        if tp_size > 1 or pp_size > 1 or cp_size > 1 or replicate > 1 or world % ep_size or cfg.n_experts % ep_size:
+            raise NotImplementedError("expert parallelism combines with plain data parallelism here (tensor / pipeline / "
+                                      "context parallel = 1, dp_replicate = 1; world and experts divisible by expert_parallel)")
+        if ep_size == world:
+            ep_group = dist.group.WORLD
+        else:
+            from ..parallel.mesh import Mesh, MeshSpec
+            ep_group = Mesh(MeshSpec(ep=ep_size)).group("ep")
+        fused_ep = str(rc.moe_dispatch).lower() == "fused" and str(device).startswith("cuda")
+        cfg.ep_comm = "fused" if fused_ep else "nccl"
     if pp_size > 1:
         from ..parallel.mesh import Mesh, MeshSpec
         mesh = Mesh(MeshSpec(pp=pp_size))
@@ -202,8 +216,9 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         trainer = PipelineTrainer(cfg, opt, tc, device, mesh, virtual_stages=rc.virtual_pipeline_parallel or 1,
                                   freeze_base=cfg.lora_rank > 0)
     else:
-        trainer = PretrainTrainer(cfg, opt, tc, device, group=dp_group, tp=tp_ctx, freeze_base=cfg.lora_rank > 0,
-                                  replicate_group=rep_group, cp_group=cp_group, cp_mode=rc.context_parallel_mode)
+        trainer = PretrainTrainer(cfg, opt, tc, device, group=dp_group, ep_group=ep_group, tp=tp_ctx,
+                                  freeze_base=cfg.lora_rank > 0, replicate_group=rep_group, cp_group=cp_group,
+                                  cp_mode=rc.context_parallel_mode)
     data = build_data(rc.data, cfg, rc.seed)
     eval_data = build_data(rc.data, cfg, rc.seed + 7919)
 
@@ -214,6 +229,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             b = (b[:, :-1].contiguous(), ds.labels(b))
         return b
 
+    per_rank_params = pp_size > 1 or ep_size > 1
     if rc.pretrained_checkpoint and pp_size > 1:
         raise NotImplementedError("loading a Megatron torch_dist checkpoint into pipeline stages is not wired: load with "
                                   "pipeline_parallel = 1, or resume from this framework's own checkpoint")
@@ -223,10 +239,10 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     start_step = 0
     if resuming:
         ck = resume_mgr.load()
-        # pipeline stages differ per rank: their parameters travel with the rank's optimizer shard
-        bufs = ck["optim"].get("stage_param_bufs") if (pp_size > 1 and ck["optim"] is not None) else ck["dense"]["param_bufs"]
+        # pipeline stages and expert shards differ per rank: their parameters travel with the rank's optimizer shard
+        bufs = ck["optim"].get("stage_param_bufs") if (per_rank_params and ck["optim"] is not None) else ck["dense"]["param_bufs"]
         written_by = int(ck["meta"].get("world", world))
-        if written_by != world and pp_size == 1 and tp_size == 1:
+        if written_by != world and not per_rank_params and tp_size == 1:
             # another number of data-parallel ranks than the writer's: re-cut the sharded optimizer state
             from ..checkpoint.reshard import copy_param_bufs, resharded_optimizer_state
             copy_param_bufs(trainer.engine, bufs)
@@ -352,7 +368,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                 saver(step + 1,
                                 dense={"param_bufs": [b.param_buf.detach().cpu() for b in trainer.engine.buckets],
                                        "model_config": cfg.to_dict()},
-                                optim_shard=_optim_shard(trainer, pp_size > 1),
+                                optim_shard=_optim_shard(trainer, per_rank_params),
                                 meta={"samples": samples, "run_started": True, "window": 0, "batch_idx_in_window": -1})
                 last_ckpt_t = time.perf_counter()
         if rc.die_at_step and step + 1 == rc.die_at_step:
