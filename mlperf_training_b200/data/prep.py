@@ -146,8 +146,22 @@ def main(argv=None) -> int:
     w = sub.add_parser("window-index"); w.add_argument("timestamps"); w.add_argument("out")
     w.add_argument("--window-seconds", type=int, required=True); w.add_argument("--holdout", type=float, default=0.0)
     w.add_argument("--salt", type=int, default=0)
+    e = sub.add_parser("synthetic-events"); e.add_argument("root"); e.add_argument("--users", type=int, default=10_000)
+    e.add_argument("--events-per-user", type=int, default=200); e.add_argument("--items", type=int, default=1_000_000)
+    e.add_argument("--days", type=int, default=7); e.add_argument("--seed", type=int, default=0)
+    q = sub.add_parser("synthetic-sequences"); q.add_argument("path"); q.add_argument("--users", type=int, default=10_000)
+    q.add_argument("--items", type=int, default=100_000); q.add_argument("--kind", default="movielens", choices=["movielens", "kuairand"])
+    q.add_argument("--min-len", type=int, default=8); q.add_argument("--max-len", type=int, default=200); q.add_argument("--seed", type=int, default=0)
     a = ap.parse_args(argv)
-    if a.cmd == "convert-sft":
+    if a.cmd == "synthetic-events":
+        from .yambda import write_synthetic_event_store
+        n = write_synthetic_event_store(a.root, a.users, a.events_per_user, a.items, days=a.days, seed=a.seed)
+        print(f"{n} events of {a.users} users -> {a.root}")
+    elif a.cmd == "synthetic-sequences":
+        from .sequences import write_synthetic_sequences
+        write_synthetic_sequences(a.path, a.users, a.items, min_len=a.min_len, max_len=a.max_len, seed=a.seed, kind=a.kind)
+        print(f"{a.users} users -> {a.path}")
+    elif a.cmd == "convert-sft":
         print(f"{convert_sft(a.src, a.dst, a.seq_len)} packed rows -> {a.dst}")
     elif a.cmd == "metadata":
         print(f"{write_metadata(a.npy, a.out)} rows -> {a.out}")

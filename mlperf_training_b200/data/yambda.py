@@ -45,6 +45,26 @@ def write_event_store(root: str, user: np.ndarray, item: np.ndarray, ts: np.ndar
         np.save(d / f"{name}.npy", arr)
 
 
+def write_synthetic_event_store(root: str, users: int, events_per_user: int, items: int, *, days: int = 7,
+                                zipf_alpha: float = 1.05, seed: int = 0) -> int:
+    """A random event store for runs without the real data: item popularity follows a bounded Zipf
+    law, every user's events are spread over ``days`` days in time order, three in five events are
+    listens (four in five of them played through), the rest likes and skips.  Returns the number of
+    events.  (The reference ships a generator of synthetic streaming data for the same purpose:
+    generative_recommenders/dlrm_v4/streaming_synthetic_data.py.)"""
+    rng = np.random.default_rng(seed)
+    n = users * events_per_user
+    ranks = np.arange(1, items + 1, dtype=np.float64)
+    p = ranks ** -zipf_alpha
+    item = rng.choice(items, size=n, p=p / p.sum())
+    user = np.repeat(np.arange(users), events_per_user)
+    ts = 1_600_000_000 + rng.integers(0, days * 86_400, size=n)
+    kind = rng.choice(np.array([0, 0, 0, 1, 2], dtype=np.uint8), size=n)
+    played = (rng.random(n) < 0.8).astype(np.uint8)
+    write_event_store(root, user, item, ts, kind, played)
+    return n
+
+
 def _user_hash(user: np.ndarray, salt: int) -> np.ndarray:
     with np.errstate(over="ignore"):
         z = user.astype(np.uint64) + np.uint64(salt) * np.uint64(0x9E3779B97F4A7C15) + np.uint64(1)

@@ -154,3 +154,15 @@ def test_hstu_run_on_sequence_file(tmp_path):
                data=dict(kind="sequences", path=str(path), format="movielens", num_candidates=2, max_history=30, eval_fraction=0.3))
     out = run(exp, device="cpu", stream=io.StringIO())
     assert len(out["losses"]) == 5 and all(l == l for l in out["losses"]) and len(out["aucs"]) == 1
+
+
+def test_prep_cli_writes_synthetic_hstu_data(tmp_path):
+    from mlperf_training_b200.data.prep import main
+    from mlperf_training_b200.data.sequences import SequenceFileDataset
+    assert main(["synthetic-events", str(tmp_path / "store"), "--users", "50", "--events-per-user", "80", "--items", "300", "--days", "4"]) == 0
+    ds = EventStoreDataset(str(tmp_path / "store"), batch=4, max_history=30, min_history=8, holdout=0.2, salt=3)
+    assert ds.num_windows >= 3 and ds.batch_at(0)["total"] > 0
+    items = np.asarray(ds.item)
+    assert np.bincount(items).max() > 5 * max(np.median(np.bincount(items)), 1)       # a popular head
+    assert main(["synthetic-sequences", str(tmp_path / "kr.csv"), "--users", "30", "--items", "200", "--kind", "kuairand", "--max-len", "20"]) == 0
+    assert len(SequenceFileDataset(str(tmp_path / "kr.csv"), batch=2, kind="kuairand")) == 30
