@@ -10,6 +10,8 @@ collective:
 * ``Heartbeat``       every rank bumps ``hb/<rank>`` in a ``torch.distributed`` store from a daemon
                       thread; ``stale(timeout)`` lists ranks whose counter has not moved.  A trainer
                       calls ``check()`` before it launches a step and gets ``RankFailure``.
+                      ``arrive(step, timeout)`` is the stricter form: a store rendezvous before every
+                      step, so a rank that left is noticed before anything is launched.
 * ``pg_timeout()``    the watchdog timeout handed to ``init_process_group`` (``PG_TIMEOUT_S``;
                       generative_recommenders/dlrm_v4/train/utils.py:236-268), so a collective whose peer is gone ends with an error.
 * ``timed_barrier``   a barrier that reports how long it waited and warns above a threshold
@@ -100,6 +102,30 @@ class Heartbeat:
         bad = self.stale(timeout_s)
         if bad:
             raise RankFailure(bad, timeout_s)
+
+    def arrive(self, step: int, timeout_s: float, poll_s: float = 0.02) -> None:
+        """Host-side rendezvous before a step is launched: publish that this rank is about to run
+        ``step`` and wait until every rank has published the same (or a later) step.  A rank that
+        left between steps never publishes, so the others raise ``RankFailure`` after ``timeout_s``
+        with none of their kernels or collectives in flight."""
+        self.store.set(f"{self.prefix}/at/{self.rank}", str(step))
+        deadline = time.monotonic() + timeout_s
+        waiting = [r for r in range(self.world) if r != self.rank]
+        while waiting:
+            still = []
+            for r in waiting:
+                key = f"{self.prefix}/at/{r}"
+                try:
+                    there = self.store.check([key]) and int(self.store.get(key).decode()) >= step
+                except Exception:
+                    there = False
+                if not there:
+                    still.append(r)
+            waiting = still
+            if waiting:
+                if time.monotonic() > deadline:
+                    raise RankFailure(waiting, timeout_s)
+                time.sleep(poll_s)
 
 
 def timed_barrier(group=None, warn_after_s: float = 5.0, label: str = "barrier", out=sys.stderr) -> float:

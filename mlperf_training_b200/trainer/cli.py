@@ -41,18 +41,25 @@ def main(argv=None) -> int:
     exp = load_experiment(args.config, overrides=args.overrides)
     module = {"pretrain": "pre_trainer", "posttrain": "post_trainer", "hstu": "hstu_trainer", "flux": "flux_trainer"}[args.mode]
     resolved = (exp.get("modules") or {}).get(module, {}).get("resolved") or exp
-    if args.mode == "pretrain":
-        from .loop import run
-        out = run(resolved, device=args.device)
-    elif args.mode == "posttrain":
-        from .sft import run as run_sft
-        out = run_sft(resolved, device=args.device)
-    elif args.mode == "hstu":
-        from .hstu import run as run_hstu
-        out = run_hstu(resolved, device=args.device)
-    else:
-        from .flux import run as run_flux
-        out = run_flux(resolved, device=args.device)
+    from ..parallel import health
+    try:
+        if args.mode == "pretrain":
+            from .loop import run
+            out = run(resolved, device=args.device)
+        elif args.mode == "posttrain":
+            from .sft import run as run_sft
+            out = run_sft(resolved, device=args.device)
+        elif args.mode == "hstu":
+            from .hstu import run as run_hstu
+            out = run_hstu(resolved, device=args.device)
+        else:
+            from .flux import run as run_flux
+            out = run_flux(resolved, device=args.device)
+    except health.RankFailure as e:
+        # a peer stopped answering between steps: leave without touching the process group (a collective
+        # with a dead peer would hang) and tell the supervisor which kind of failure this was
+        print(f"rank failure detected: ranks {e.ranks} are silent; exiting {health.EXIT_RANK_FAILURE}", file=sys.stderr, flush=True)
+        health.clean_exit(health.EXIT_RANK_FAILURE)
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

@@ -79,6 +79,8 @@ class RunConfig:
     tp_comm_overlap: str = "fused"                      # "fused": in-kernel all-gather / reduce-scatter; "nccl"
     comm: str = "nccl"                                  # optimizer-step collectives: "nccl" | "fused"
     precision_schedule: dict | str | None = None        # ops.recipe.PrecisionSchedule spec (phase switch at a step)
+    vanish_at_step: int = 0                             # fault injection: rank ``vanish_rank`` leaves silently before this step
+    vanish_rank: int = 1
     heartbeat_timeout_s: float = 0.0                    # > 0: watch the other ranks' heartbeats between steps
     straggler_interval: int = 0                         # > 0: compare mean step time across ranks every N steps
     check_replicas_every: int = 0                       # > 0: compare parameter checksums across replicas every N steps
@@ -309,8 +311,19 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             prof.start()
         if sched is not None and sched.apply(trainer.model, step) and rank == 0:
             print(f"[precision] step {step}: linears run in {sched.at(step)}; {sched.deosc.status(sched.at(step))}", flush=True)
+        if rc.vanish_at_step and step == rc.vanish_at_step and rank == rc.vanish_rank:
+            # fault injection: this rank leaves between steps, silently (nothing of it is in flight); once per
+            # checkpoint directory, so that the relaunched run gets past the step
+            marker = os.path.join(rc.checkpoint_dir or ".", "vanished_once")
+            if not os.path.exists(marker):
+                open(marker, "w").close()
+                if hb is not None:
+                    hb.stop()
+                from ..parallel.health import clean_exit
+                clean_exit(0)
         if hb is not None:
             hb.check(rc.heartbeat_timeout_s)          # raises RankFailure before any kernel of the step is launched
+            hb.arrive(step, rc.heartbeat_timeout_s)   # and nobody starts a step that a peer will not join
         timer.step_start()
         batch = host_batch(data, step)
         if torch.cuda.is_available() and str(device).startswith("cuda"):

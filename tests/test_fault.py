@@ -94,3 +94,39 @@ modules:
     assert [s["action"] for s in sup] == ["restart", "done"] and sup[0]["exit_code"] == 42 and sup[1]["exit_code"] == 0
     log = (tmp_path / "ml.log").read_text()
     assert log.count("run_start") == 1 and log.count("run_stop") == 1                 # one run, resumed in place
+
+
+def test_lost_rank_is_noticed_then_run_shrinks_and_resumes_gloo(tmp_path):
+    """The whole chain on CPU ranks: a rank leaves silently between steps, the others notice at the
+    host-side rendezvous before the next step and exit 43, the supervisor relaunches on half the
+    ranks, and the run resumes from the last checkpoint with its optimizer state re-cut."""
+    import json
+    yaml = tmp_path / "exp.yaml"
+    yaml.write_text(f"""
+modules:
+  pre_trainer:
+    framework: b200
+    overrides:
+      global_batch: 4
+      micro_batch: 1
+      train_iters: 5
+      warmup_train_steps: 0
+      checkpoint_every: 2
+      checkpoint_dir: {tmp_path / 'ck'}
+      mllog_file: {tmp_path / 'ml.log'}
+      heartbeat_timeout_s: 3
+      vanish_at_step: 3
+      vanish_rank: 1
+      model: {{n_layers: 1, hidden: 32, n_heads: 2, n_kv_heads: 1, head_dim: 16, ffn_hidden: 64, vocab_size: 64, seq_len: 16, dtype: fp32}}
+      data: {{kind: synthetic}}
+""")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT, B200_QUIET="0")
+    r = subprocess.run([sys.executable, "-m", "mlperf_training_b200.trainer.supervisor", "--nproc", "4", "--max-restarts", "2", "--shrink",
+                        "--min-nproc", "2", "--", "pretrain", "--config", str(yaml), "--device", "cpu"],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    sup = [json.loads(l) for l in r.stdout.splitlines() if l.startswith('{"supervisor"')]
+    assert [(s["world"], s["exit_code"], s["action"]) for s in sup] == [(4, 43, "restart"), (2, 0, "done")], sup
+    assert "rank failure detected" in r.stdout + r.stderr
+    log = (tmp_path / "ml.log").read_text()
+    assert log.count("run_start") == 1 and log.count("run_stop") == 1
