@@ -116,6 +116,7 @@ class HSTUTrainer:
             self.data = HSTUSyntheticData(table_rows, batch_per_gpu, seed=seed, **data_kw)
             self.eval_data = None
         self.batch_per_gpu = batch_per_gpu
+        self.sparse_lr, self.lr_warmup_steps, self.lr_warmup_start_lr = float(sparse_lr), 0, 0.0
         self.step_idx = 0
         self.eval_lookahead = True
         self.copy_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
@@ -165,11 +166,23 @@ class HSTUTrainer:
 
     def train_step_device(self, batch) -> torch.Tensor:
         self.model.train()
+        dense_lr, self.table.lr = self.lrs_at(self.step_idx)     # the sparse update runs inside backward
         loss, _, _ = self.model(batch, self.embed(batch))
         loss.backward()
-        self.engine.step()
+        self.engine.step(dense_lr)
         self.step_idx += 1
         return loss.detach()
+
+    def lrs_at(self, step: int) -> tuple[float, float]:
+        """(dense, sparse) learning rates of global step ``step``: each ramps linearly from
+        ``min(lr_warmup_start_lr, base)`` to its base over ``lr_warmup_steps`` steps, then holds
+        (generative_recommenders/dlrm_v4/train/utils.py:4853-4884; the ramp scales the dense optimizer
+        and the in-backward sparse optimizer alike)."""
+        bases = (self.engine.opt.lr, self.sparse_lr)
+        if self.lr_warmup_steps <= 0:
+            return bases
+        f = min(1.0, step / self.lr_warmup_steps)
+        return tuple(min(self.lr_warmup_start_lr, b) + (b - min(self.lr_warmup_start_lr, b)) * f for b in bases)
 
     def train_step(self, step: int | None = None) -> torch.Tensor:
         return self.train_step_device(self._take(self.step_idx if step is None else step))
@@ -274,6 +287,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     tr = HSTUTrainer(cfg, int(emb.get("rows", 1_000_000)), bpg, device, dense_lr=float(exp.get("dense_lr", 1e-3)),
                      sparse_lr=float(exp.get("sparse_lr", 1e-2)), clip_grad=float(exp.get("clip_grad", 1.0)),
                      emb_comm=exp.get("emb_a2a", "nccl"), seed=int(exp.get("seed", 0)), data_kw=data_kw)
+    tr.lr_warmup_steps = int(exp.get("lr_warmup_steps", 0) or 0)
+    tr.lr_warmup_start_lr = float(exp.get("lr_warmup_start_lr", 0.0) or 0.0)
     start = 0
     if resuming:
         ck = ckpt.load()

@@ -90,3 +90,23 @@ def test_hstu_die_and_resume(tmp_path):
     assert abs(out["losses"][-1] - ref["losses"][-1]) < 1e-5
     lines = open(tmp_path / "ml.log").read().splitlines()
     assert sum("run_start" in l for l in lines) == 1 and sum("run_stop" in l for l in lines) == 1
+
+
+def test_hstu_lr_warmup_ramps_dense_and_sparse_rates():
+    from mlperf_training_b200.models.hstu import tiny_hstu
+    from mlperf_training_b200.trainer.hstu import HSTUTrainer
+    tr = HSTUTrainer(tiny_hstu(), 200, 2, "cpu", dense_lr=1e-3, sparse_lr=1e-2, data_kw=dict(length_median=12, length_min=4, length_max=24))
+    assert tr.lrs_at(0) == (1e-3, 1e-2)                                    # no warm-up configured
+    tr.lr_warmup_steps, tr.lr_warmup_start_lr = 10, 5e-3                   # a floor above the dense base: dense does not ramp
+    d0, s0 = tr.lrs_at(0)
+    assert d0 == 1e-3 and s0 == 5e-3
+    d5, s5 = tr.lrs_at(5)
+    assert d5 == 1e-3 and abs(s5 - 7.5e-3) < 1e-12
+    assert tr.lrs_at(10) == (1e-3, 1e-2) and tr.lrs_at(50) == (1e-3, 1e-2)
+    tr.lr_warmup_start_lr = 0.0
+    w0 = [p.detach().clone() for p in tr.model.parameters()]
+    t0 = tr.table.weight.detach().clone()
+    tr.train_step(0)                                                       # step 0 of a ramp from zero changes nothing
+    assert all(torch.equal(a, b) for a, b in zip(w0, tr.model.parameters())) and torch.equal(t0, tr.table.weight)
+    tr.train_step(1)
+    assert any(not torch.equal(a, b) for a, b in zip(w0, tr.model.parameters())) and not torch.equal(t0, tr.table.weight)
