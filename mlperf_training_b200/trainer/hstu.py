@@ -119,6 +119,7 @@ class HSTUTrainer:
         self.sparse_lr, self.lr_warmup_steps, self.lr_warmup_start_lr = float(sparse_lr), 0, 0.0
         self.step_idx = 0
         self.eval_lookahead = True
+        self.pipelined = True            # loader thread + copy stream ahead of the step (the reference's TRAIN_PIPELINE=1)
         self.copy_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
         self._next = None
         self._pool = None
@@ -148,6 +149,12 @@ class HSTUTrainer:
         host while the main thread launches step N, and N+1's H2D copy runs on the copy stream under
         step N's kernels (the reference's data-loader workers + copy stream,
         generative_recommenders/dlrm_v4/train/dd_own_h2d.py:65-168)."""
+        if not self.pipelined:
+            # the unpipelined loop (``train_pipeline: 0``): build, copy, run, in order
+            batch, ev = self._to_device(self._build(step))
+            if ev is not None:
+                torch.cuda.current_stream().wait_event(ev)
+            return batch
         if self._next is None or self._next[0] != step:
             self._next = (step, self._submit(step))
         host = self._next[1].result()
@@ -288,6 +295,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                      sparse_lr=float(exp.get("sparse_lr", 1e-2)), clip_grad=float(exp.get("clip_grad", 1.0)),
                      emb_comm=exp.get("emb_a2a", "nccl"), seed=int(exp.get("seed", 0)), data_kw=data_kw)
     tr.lr_warmup_steps = int(exp.get("lr_warmup_steps", 0) or 0)
+    tr.pipelined = bool(int(exp.get("train_pipeline", 1)))
     tr.lr_warmup_start_lr = float(exp.get("lr_warmup_start_lr", 0.0) or 0.0)
     start = 0
     if resuming:

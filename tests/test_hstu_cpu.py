@@ -110,3 +110,15 @@ def test_hstu_lr_warmup_ramps_dense_and_sparse_rates():
     assert all(torch.equal(a, b) for a, b in zip(w0, tr.model.parameters())) and torch.equal(t0, tr.table.weight)
     tr.train_step(1)
     assert any(not torch.equal(a, b) for a, b in zip(w0, tr.model.parameters())) and not torch.equal(t0, tr.table.weight)
+
+
+def test_hstu_unpipelined_loop_gives_the_same_losses():
+    from mlperf_training_b200.models.hstu import tiny_hstu
+    from mlperf_training_b200.trainer.hstu import HSTUTrainer
+    out = []
+    for pipelined in (True, False):
+        tr = HSTUTrainer(tiny_hstu(input_dropout=0.0, linear_dropout=0.0), 200, 2, "cpu", seed=1,
+                         data_kw=dict(length_median=12, length_min=4, length_max=24))
+        tr.pipelined = pipelined
+        out.append([float(tr.train_step(i)) for i in range(3)])
+    assert out[0] == out[1]
