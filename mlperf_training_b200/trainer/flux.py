@@ -44,6 +44,20 @@ class SyntheticFluxData:
                 torch.randn(local_batch, c.vec_dim, generator=g))
 
 
+class _EncodedView:
+    """The ``batch(step, rank, local_batch)`` call of the run loop over an on-disk training set; steps at or above
+    10**6 are the loop's evaluation and warm-up requests and read the evaluation set in file order."""
+
+    def __init__(self, train_set, eval_set, world: int):
+        self.train, self.eval, self.world = train_set, eval_set, world
+
+    def batch(self, step: int, rank: int, local_batch: int):
+        if step >= 10**6:
+            per = max(self.eval.steps_per_epoch(local_batch, self.world), 1)
+            return self.eval.batch(step % per, rank, local_batch, self.world)
+        return self.train.batch(step, rank, local_batch, self.world)
+
+
 class FluxTrainer:
     def __init__(self, cfg: MMDiTConfig, opt: OptimConfig, device, local_batch: int, warmup_iters: int = 0,
                  prompt_dropout: float = 0.1, comm: str = "nccl", seed: int = 0, micro_batch: int | None = None,
@@ -64,6 +78,7 @@ class FluxTrainer:
         self.step_idx = 0
         self.gen = torch.Generator(device=self.device).manual_seed(seed + 17)
         self._lr_scale = 1.0
+        self.empty_txt = self.empty_pooled = None       # encodings of the empty prompt (prompt dropout); zeros when absent
 
     def lr(self) -> float:
         base = self.engine.opt.lr * self._lr_scale
@@ -75,7 +90,7 @@ class FluxTrainer:
         for i in range(n_micro):
             sl = slice(i * self.micro_batch, (i + 1) * self.micro_batch)
             loss = self.model.loss(latents[sl], txt[sl], pooled[sl], generator=self.gen,
-                                   prompt_dropout=self.prompt_dropout)
+                                   prompt_dropout=self.prompt_dropout, empty_txt=self.empty_txt, empty_pooled=self.empty_pooled)
             loss.backward()
             total = loss.detach() if total is None else total + loss.detach()
         self.engine.step(self.lr(), grad_scale=1.0 / n_micro)
@@ -190,7 +205,18 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                      prompt_dropout=float(exp.get("prompt_dropout", 0.1)),
                      comm=(exp.get("fsdp") or {}).get("comm", "nccl") if replicate == 1 else "nccl", seed=int(exp.get("seed", 0)),
                      micro_batch=exp.get("micro_batch"), sp_group=sp_group, group=shard_group, replicate_group=rep_group)
-    data = SyntheticFluxData(cfg, seed=int(exp.get("seed", 0)))
+    dspec = dict(exp.get("data") or {})
+    if str(dspec.get("kind", "synthetic")) == "encoded":
+        # pre-encoded latents and text states on disk; ``eval_path`` (default: the training set) for validation
+        from ..data.flux_encoded import EncodedFluxData
+        train_set = EncodedFluxData(dspec["path"], cfg, seed=int(exp.get("seed", 0)))
+        eval_set = EncodedFluxData(dspec.get("eval_path") or dspec["path"], cfg, shuffle=False)
+        if train_set.empty_t5 is not None and train_set.empty_clip is not None:
+            dt = cfg.torch_dtype()
+            tr.empty_txt, tr.empty_pooled = train_set.empty_t5.to(tr.device, dt), train_set.empty_clip.to(tr.device, dt)
+        data = _EncodedView(train_set, eval_set, dp_world)
+    else:
+        data = SyntheticFluxData(cfg, seed=int(exp.get("seed", 0)))
     start_step = 0
     if resuming:
         ck = mgr.load()

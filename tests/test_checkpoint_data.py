@@ -229,3 +229,35 @@ def test_mmdit_recompute_gives_the_same_gradients():
         assert (gp is None) == (gq is None), n
         if gp is not None:
             assert torch.allclose(gp, gq, atol=1e-6), n
+
+
+def test_flux_run_on_pre_encoded_dataset(tmp_path):
+    import numpy as np
+    from mlperf_training_b200.data.flux_encoded import EncodedFluxData, write_encoded_dataset
+    from mlperf_training_b200.models.mmdit import patchify, tiny_mmdit, unpatchify
+    from mlperf_training_b200.trainer.flux import run
+    cfg = tiny_mmdit()
+    side = int(round((cfg.img_tokens) ** 0.5)) * 2
+    C = cfg.in_channels // 4
+    rng = np.random.default_rng(0)
+    n = 12
+    lat = rng.standard_normal((n, C, side, side)).astype(np.float16)
+    write_encoded_dataset(str(tmp_path / "enc"), lat, rng.standard_normal((n, cfg.txt_tokens, cfg.txt_dim)).astype(np.float16),
+                          rng.standard_normal((n, cfg.vec_dim)).astype(np.float16),
+                          empty_t5=np.zeros((cfg.txt_tokens, cfg.txt_dim), np.float16) + 0.5, empty_clip=np.zeros(cfg.vec_dim, np.float16) - 0.5)
+    ds = EncodedFluxData(str(tmp_path / "enc"), cfg, seed=1)
+    a, b = ds.indices(0, 0, 2, world=2), ds.indices(0, 1, 2, world=2)
+    assert not set(a) & set(b) and ds.steps_per_epoch(2, 2) == 3
+    seen = np.concatenate([ds.indices(s, r, 2, 2) for s in range(3) for r in range(2)])
+    assert sorted(seen.tolist()) == list(range(n))                                  # an epoch visits every sample once
+    assert ds.indices(3, 0, 2, 2).tolist() != a.tolist() or ds.indices(4, 0, 2, 2).tolist() != ds.indices(1, 0, 2, 2).tolist()
+    x, t5, clip = ds.batch(0, 0, 2)
+    assert x.shape == (2, cfg.img_tokens, cfg.in_channels) and t5.shape == (2, cfg.txt_tokens, cfg.txt_dim)
+    back = unpatchify(patchify(torch.from_numpy(lat[:2].astype(np.float32))), C, side // 2)
+    assert torch.equal(back, torch.from_numpy(lat[:2].astype(np.float32)))
+    with pytest.raises(ValueError):
+        EncodedFluxData(str(tmp_path / "enc"), __import__("dataclasses").replace(cfg, txt_tokens=cfg.txt_tokens * 2))
+    out = run(dict(model=dict(preset="tiny-mmdit"), global_batch=2, train_iters=4, lr=2e-3, eval_every_samples=4, prompt_dropout=0.5,
+                   data=dict(kind="encoded", path=str(tmp_path / "enc"))), device="cpu", stream=io.StringIO())
+    assert len(out["losses"]) == 4 and all(l == l for l in out["losses"]) and out["eval_loss"] is not None
+    assert out["trainer"].empty_txt is not None and float(out["trainer"].empty_txt.mean()) == 0.5
