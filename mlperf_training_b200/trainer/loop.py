@@ -175,6 +175,9 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         if replicate > 1:
             rep_group = mesh.group("dp_replicate")
     if tp_size > 1:
+        if not int(rc.sequence_parallel) and rank == 0:
+            print("[parallel] sequence_parallel: 0 ignored - the tensor-parallel blocks always shard the activations "
+                  "between them over the sequence (all-gather -> GEMM, GEMM -> reduce-scatter)", flush=True)
         from ..parallel.tensor import TPContext
         fused_tp = str(rc.tp_comm_overlap).lower() == "fused" and str(device).startswith("cuda")
         tp_ctx = TPContext(mesh.group("tp"), comm="fused" if fused_tp else "nccl", device=device if fused_tp else None)
