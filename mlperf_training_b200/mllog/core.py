@@ -98,11 +98,13 @@ class MLLogger:
 
     def log_submission(self, benchmark: str, org: str = "b200-train", platform: str = "1xB200x8",
                        division: str = "closed", status: str = "onprem") -> None:
-        self.event(SUBMISSION_BENCHMARK, benchmark)
-        self.event(SUBMISSION_ORG, org)
-        self.event(SUBMISSION_DIVISION, division)
-        self.event(SUBMISSION_STATUS, status)
-        self.event(SUBMISSION_PLATFORM, platform)
+        # MLLOG_SUBMISSION_* from the system config file win over the caller's defaults
+        env = os.environ
+        self.event(SUBMISSION_BENCHMARK, env.get("MLLOG_SUBMISSION_BENCHMARK", benchmark))
+        self.event(SUBMISSION_ORG, env.get("MLLOG_SUBMISSION_ORG", org))
+        self.event(SUBMISSION_DIVISION, env.get("MLLOG_SUBMISSION_DIVISION", division))
+        self.event(SUBMISSION_STATUS, env.get("MLLOG_SUBMISSION_STATUS", status))
+        self.event(SUBMISSION_PLATFORM, env.get("MLLOG_SUBMISSION_PLATFORM", platform))
 
     def log_hyperparameters(self, params: dict, env: dict | None = None) -> None:
         """Known MLPerf hyper-parameter keys from ``params``; ``MLLOG_<KEY>`` environment variables
