@@ -224,6 +224,11 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         trainer = PretrainTrainer(cfg, opt, tc, device, group=dp_group, ep_group=ep_group, tp=tp_ctx,
                                   freeze_base=cfg.lora_rank > 0, replicate_group=rep_group, cp_group=cp_group,
                                   cp_mode=rc.context_parallel_mode)
+    if os.environ.get("INIT_CHECKSUM", "0") == "1":
+        from ..utils.metrics import model_fingerprint
+        digest, _ = model_fingerprint(trainer.model)
+        if rank == 0:
+            print(f"[init] model fingerprint {digest}", flush=True)
     data = build_data(rc.data, cfg, rc.seed)
     eval_data = build_data(rc.data, cfg, rc.seed + 7919)
 

@@ -159,3 +159,29 @@ class PerfLogger:
                 f.write(json.dumps(rec) + "\n")
         self.t0, self.paused, self.samples, self.steps = self._now(), 0.0, 0, 0
         return rec
+
+
+def model_fingerprint(model, group=None) -> tuple[str, list[tuple[str, float, float, float]]]:
+    """Whole-model initialisation fingerprint: for every parameter in name order the element count,
+    the sum and the sum of squares in fp64, and a SHA-256 over those numbers (printed with
+    ``INIT_CHECKSUM=1``; two runs that start from the same weights print the same digest).  Parameters
+    marked as sharded over ranks (``expert_parallel`` / ``tensor_parallel`` attributes) are summed over
+    ``group`` first, so the digest does not depend on which rank prints it
+    (generative_recommenders/dlrm_v4/train/utils.py:1695-1748)."""
+    import hashlib
+
+    import torch
+    import torch.distributed as dist
+    rows = []
+    for name, p in sorted(model.named_parameters(), key=lambda kv: kv[0]):
+        d = p.detach()
+        stat = torch.tensor([float(d.numel()), float(d.sum(dtype=torch.float64)), float((d.double() ** 2).sum())],
+                            dtype=torch.float64, device=d.device)
+        sharded = getattr(p, "expert_parallel", False) or getattr(p, "tensor_parallel", None) is not None
+        if sharded and dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(stat, group=group)
+        rows.append((name, float(stat[0]), float(stat[1]), float(stat[2])))
+    h = hashlib.sha256()
+    for name, n, s, q in rows:
+        h.update(f"{name}:{n:.0f}:{s:.10e}:{q:.10e};".encode())
+    return h.hexdigest(), rows

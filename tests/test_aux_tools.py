@@ -76,3 +76,24 @@ def test_gpu_idle_check_with_fake_nvidia_smi(tmp_path):
     busy = run("0, 3\\n1, 40960\\n", "")
     assert busy.returncode == 1 and "GPU 1" in busy.stdout
     assert run("0, 0\\n", "4242\\n").returncode == 1
+
+
+def test_model_fingerprint_tracks_the_initial_weights(capsys, monkeypatch):
+    import io
+    import torch
+    from mlperf_training_b200.models.gpt import GPT, GPTConfig
+    from mlperf_training_b200.utils.metrics import model_fingerprint
+    cfg = GPTConfig(n_layers=1, hidden=32, n_heads=2, n_kv_heads=1, head_dim=16, ffn_hidden=64, vocab_size=64, seq_len=8, dtype="fp32")
+    a, rows = model_fingerprint(GPT(cfg, seed=3))
+    b, _ = model_fingerprint(GPT(cfg, seed=3))
+    c, _ = model_fingerprint(GPT(cfg, seed=4))
+    assert a == b and a != c and len(a) == 64
+    assert rows == sorted(rows) and all(n > 0 for _, n, _, _ in rows)
+    m = GPT(cfg, seed=3)
+    with torch.no_grad():
+        next(m.parameters()).view(-1)[0] += 1e-3
+    assert model_fingerprint(m)[0] != a                                     # one changed element changes the digest
+    monkeypatch.setenv("INIT_CHECKSUM", "1")
+    from mlperf_training_b200.trainer.loop import run
+    run(dict(model=cfg.to_dict(), global_batch=2, micro_batch=1, train_iters=1, warmup_train_steps=0), device="cpu", stream=io.StringIO())
+    assert "[init] model fingerprint " in capsys.readouterr().out
