@@ -97,3 +97,22 @@ def test_model_fingerprint_tracks_the_initial_weights(capsys, monkeypatch):
     from mlperf_training_b200.trainer.loop import run
     run(dict(model=cfg.to_dict(), global_batch=2, micro_batch=1, train_iters=1, warmup_train_steps=0), device="cpu", stream=io.StringIO())
     assert "[init] model fingerprint " in capsys.readouterr().out
+
+
+def test_mxfp8_site_probe_reports_snr_and_is_scale_invariant():
+    import math
+    import torch
+    from mlperf_training_b200.utils.numerics import cosine, linear_site_report, main, snr_db
+    g = torch.Generator().manual_seed(0)
+    x, w, dy = torch.randn(256, 384, generator=g), torch.randn(128, 384, generator=g) * 0.02, torch.randn(256, 128, generator=g) * 1e-3
+    assert snr_db(x, x) == math.inf and abs(cosine(x, 2 * x) - 1.0) < 1e-12
+    assert abs(snr_db(x, x * 1.1) - 20.0) < 1e-3                                     # 10 % error -> 20 dB
+    rep = linear_site_report(x, w, dy)
+    assert set(rep) == {"fwd", "dgrad", "wgrad"}
+    for site in rep.values():                                                       # e4m3 + per-32 scales: about 30 dB per GEMM
+        assert 22.0 < site["snr_db"] < 45.0 and site["cosine"] > 0.995
+    # power-of-two rescaling of an operand moves only the block exponents
+    rep2 = linear_site_report(x * 1024, w / 64, dy * 4)
+    for k in rep:
+        assert abs(rep2[k]["snr_db"] - rep[k]["snr_db"]) < 0.05
+    assert main(["--tokens", "128", "--in", "128", "--out", "128", "--outliers", "0.01"]) == 0
