@@ -315,6 +315,13 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         log.start(ml.BLOCK_START, metadata={"samples_count": 0})
     steps = int(exp.get("train_steps", 10))
     eval_every = int(exp.get("eval_interval_steps", 0))
+    # the data-fraction cadence of the benchmark: evaluate every ``eval_every_data_pct`` of the epoch and not before
+    # ``skip_eval_epoch_pct`` of it (negative: the MLPerf first-evaluation rule); both become global steps once
+    from .cadence import data_pct_to_global_steps, should_eval, skip_eval_until_step
+    epoch_samples = int(exp.get("total_train_samples", 0))
+    if float(exp.get("eval_every_data_pct", 0) or 0) > 0:
+        eval_every = data_pct_to_global_steps(float(exp["eval_every_data_pct"]), epoch_samples, bpg * world)
+    skip_until = skip_eval_until_step(float(exp.get("skip_eval_epoch_pct", 0) or 0), epoch_samples, bpg * world)
     n_eval = int(exp.get("num_eval_batches", 2))
     thr = float(exp.get("auc_threshold", 0.0))
     die_at = int(exp.get("die_at_step", 0))
@@ -334,7 +341,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             losses.append(prev)
             log.event(ml.TRAIN_LOSS, prev, metadata={"samples_count": step * bpg * world})
         samples = (step + 1) * bpg * world
-        if eval_every and (step + 1) % eval_every == 0:
+        if should_eval(step + 1, eval_every, skip_until):
             log.end(ml.BLOCK_STOP, metadata={"samples_count": samples})
             log.start(ml.EVAL_START, metadata={"samples_count": samples})
             p, l = tr.eval_batches(n_eval)

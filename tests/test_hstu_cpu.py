@@ -122,3 +122,34 @@ def test_hstu_unpipelined_loop_gives_the_same_losses():
         tr.pipelined = pipelined
         out.append([float(tr.train_step(i)) for i in range(3)])
     assert out[0] == out[1]
+
+
+def test_eval_cadence_from_data_fractions():
+    from mlperf_training_b200.trainer.cadence import data_pct_to_global_steps, first_eval_steps, should_eval, skip_eval_until_step
+    assert data_pct_to_global_steps(0.01, 1_000_000, 1024) == 10                 # ceil(10000 / 1024)
+    assert data_pct_to_global_steps(0.0, 10, 2) == 0 and data_pct_to_global_steps(0.5, 0, 2) == 0
+    assert skip_eval_until_step(0.25, 1000, 10) == 25 and skip_eval_until_step(0.0, 1000, 10) == 0
+    # the MLPerf rule at GBS 8192 over 300 M samples: interval 37 steps of 8192, first evaluation at the
+    # first multiple of it at or after floor((4480 * 8192 + 135331840) / 3) samples
+    gbs, total = 8192, 300_000_000
+    interval = -(-int(0.001 * total) // gbs) * gbs
+    first = (4480 * gbs + 135331840) // 3
+    want = -(-first // interval) * interval // gbs
+    assert skip_eval_until_step(-1.0, total, gbs) == want and want * gbs >= first
+    assert first_eval_steps(0, 10, 0) == 10 and first_eval_steps(10, 10, 0) == 10 and first_eval_steps(3, 10, 25) == 27
+    assert first_eval_steps(5, 0, 0) == 0
+    assert [g for g in range(1, 41) if should_eval(g, 10, 25)] == [30, 40]
+    assert not should_eval(0, 10) and not should_eval(10, 0)
+
+
+def test_hstu_run_skips_early_evaluations():
+    import io
+    from mlperf_training_b200.trainer.hstu import run
+    exp = dict(batch_per_gpu=2, train_steps=8, eval_interval_steps=0, num_eval_batches=1, total_train_samples=16,
+               eval_every_data_pct=0.25, skip_eval_epoch_pct=0.5,
+               model=dict(layers=1, dim=32, heads=2, d_qk=16, d_v=16, max_seq_len=32, dtype="fp32", mlp_hidden=16,
+                          num_positions=64, num_time_buckets=32),
+               embedding=dict(rows=300, dim=16), data=dict(length_median=10, length_min=4, length_max=24))
+    out = run(exp, device="cpu", stream=io.StringIO())
+    # 25 % of 16 samples at global batch 2 = every 2 steps; nothing before 50 % = step 4: evaluations after steps 4, 6, 8
+    assert len(out["aucs"]) == 3
