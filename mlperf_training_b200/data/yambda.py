@@ -141,6 +141,19 @@ class EventStoreDataset:
         ids = self.window_anchors(w, rank, world)
         return self.build_batch(ids[k * self.batch:(k + 1) * self.batch], pin)
 
+    def window_of_step(self, step: int, world: int = 1) -> int:
+        """Index of the time window that step ``step`` of the stream reads from."""
+        per_window = [self.batches_in_window(w, world) for w in range(self.num_windows)]
+        total = sum(per_window)
+        if total == 0:
+            raise IndexError("no window holds a full batch for every rank")
+        step %= total
+        for w, n in enumerate(per_window):
+            if step < n:
+                return w
+            step -= n
+        return self.num_windows - 1
+
     def batch_at(self, step: int, rank: int = 0, pin: bool = False, world: int = 1) -> dict:
         """Step ``step`` of the stream that walks the windows in order (exact-once: a resumed run that
         asks for the same step gets the same samples)."""

@@ -13,6 +13,7 @@ for a device-to-host copy; a ``StepFence`` bounds how far the host may run ahead
 """
 from __future__ import annotations
 
+import os
 import sys
 import time
 
@@ -331,7 +332,19 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     lifetime = BinnedCumulativeAUC(device=device)
     losses, aucs, reached = [], [], False
     t0 = time.perf_counter()
+    window_of = getattr(getattr(tr.data, "ds", tr.data), "window_of_step", None)
+    last_window, barrier_debug = None, os.environ.get("WINDOW_BARRIER_DEBUG", "0") == "1"
     for step in range(start, steps):
+        if window_of is not None:
+            w = window_of(step, world)
+            if w != last_window:
+                # window boundary: ranks finish a window's host work at different times; meet here, and say so
+                # when somebody had to wait long (generative_recommenders/dlrm_v4/train/utils.py:356-402)
+                from ..parallel.health import timed_barrier
+                waited = timed_barrier(label=f"window {w}") if world > 1 else 0.0
+                if barrier_debug and rank == 0:
+                    print(f"[window-barrier] step {step} window {w} waited {waited:.3f} s", flush=True)
+                last_window = w
         timer.step_start()
         loss = tr.train_step(step)
         prev = pending.push(loss)

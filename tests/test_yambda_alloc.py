@@ -166,3 +166,21 @@ def test_prep_cli_writes_synthetic_hstu_data(tmp_path):
     assert np.bincount(items).max() > 5 * max(np.median(np.bincount(items)), 1)       # a popular head
     assert main(["synthetic-sequences", str(tmp_path / "kr.csv"), "--users", "30", "--items", "200", "--kind", "kuairand", "--max-len", "20"]) == 0
     assert len(SequenceFileDataset(str(tmp_path / "kr.csv"), batch=2, kind="kuairand")) == 30
+
+
+def test_window_boundaries_are_announced(tmp_path, monkeypatch, capsys):
+    import io
+    from mlperf_training_b200.trainer.hstu import run
+    root = _store(tmp_path, users=60, events=100)
+    ds = EventStoreDataset(root, batch=4, max_history=30, min_history=8, holdout=0.3, salt=1)
+    per = [ds.batches_in_window(w) for w in range(ds.num_windows)]
+    assert [ds.window_of_step(s) for s in (0, per[0] - 1, per[0])] == [0, 0, 1] if per[0] > 1 else True
+    monkeypatch.setenv("WINDOW_BARRIER_DEBUG", "1")
+    steps = per[0] + 2
+    run(dict(batch_per_gpu=4, train_steps=steps, eval_interval_steps=0,
+             model=dict(layers=1, dim=32, heads=2, d_qk=16, d_v=16, max_seq_len=48, dtype="fp32", mlp_hidden=16,
+                        num_positions=64, num_time_buckets=32),
+             embedding=dict(rows=500, dim=16), data=dict(kind="yambda", root=root, max_history=30, min_history=8, holdout=0.3, salt=1)),
+        device="cpu", stream=io.StringIO())
+    lines = [l for l in capsys.readouterr().out.splitlines() if l.startswith("[window-barrier]")]
+    assert len(lines) == 2 and "window 0" in lines[0] and "window 1" in lines[1]
