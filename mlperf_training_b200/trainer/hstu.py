@@ -299,8 +299,15 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     tr.pipelined = bool(int(exp.get("train_pipeline", 1)))
     tr.lr_warmup_start_lr = float(exp.get("lr_warmup_start_lr", 0.0) or 0.0)
     start = 0
+    # what the train / eval split and the position inside the stream depend on: a resumed run must not change it
+    contract = {"data_kind": str(d.get("kind", "synthetic")), "holdout": float(d.get("holdout", d.get("eval_fraction", 0.0)) or 0.0),
+                "salt": int(d.get("salt", 0) or 0), "window_seconds": int(d.get("window_seconds", 86_400) or 0),
+                "batch_per_gpu": bpg, "world": world}
     if resuming:
         ck = ckpt.load()
+        from ..checkpoint.manager import validate_split_contract
+        validate_split_contract(ck["meta"].get("split_contract"), contract,
+                                allow_mismatch=os.environ.get("ALLOW_SPLIT_MISMATCH", "0") == "1")
         tr.model.load_state_dict(ck["dense"]["model"])
         tr.table.load_state_dict(torch.load(ck["path"] / "sparse" / f"shard_rank{rank}.pt", weights_only=False))
         if ck["optim"] is not None:
@@ -373,7 +380,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         if ckpt is not None and ((every and (step + 1) % every == 0) or (die_at and step + 1 == die_at)):
             sd = tr.table.state_dict()
             ckpt.save(step + 1, dense={"model": tr.model.state_dict()}, optim_shard=tr.engine.optimizer_state(),
-                      meta={"samples": samples, "window": 0, "batch_idx_in_window": step + 1},
+                      meta={"samples": samples, "window": 0, "batch_idx_in_window": step + 1, "split_contract": contract},
                       sparse_writer=lambda d_: torch.save(sd, d_ / f"shard_rank{rank}.pt"))
         if die_at and step + 1 == die_at:
             if world > 1:

@@ -90,6 +90,19 @@ def test_hstu_die_and_resume(tmp_path):
     assert abs(out["losses"][-1] - ref["losses"][-1]) < 1e-5
     lines = open(tmp_path / "ml.log").read().splitlines()
     assert sum("run_start" in l for l in lines) == 1 and sum("run_stop" in l for l in lines) == 1
+    # a resume that changes what the split or the stream position depends on is refused ...
+    changed = dict(e, batch_per_gpu=int(e.get("batch_per_gpu", 4)) * 2, train_steps=int(e.get("train_steps", 8)) + 2)
+    with pytest.raises(RuntimeError, match="split contract"):
+        run(changed, device="cpu", stream=io.StringIO())
+
+
+def test_split_contract_override(monkeypatch):
+    from mlperf_training_b200.checkpoint.manager import validate_split_contract
+    saved, live = {"salt": 1, "holdout": 0.1, "world": 8}, {"salt": 2, "holdout": 0.1, "world": 8}
+    with pytest.raises(RuntimeError):
+        validate_split_contract(saved, live)
+    validate_split_contract(saved, live, allow_mismatch=True)          # ALLOW_SPLIT_MISMATCH=1
+    validate_split_contract(None, live)                                # a checkpoint from before contracts were recorded
 
 
 def test_hstu_lr_warmup_ramps_dense_and_sparse_rates():
