@@ -77,9 +77,13 @@ class _WorldView:
 
     def __init__(self, ds, world: int):
         self.ds, self.world = ds, world
+        self.readahead = 0               # > 0: after building a batch, advise the kernel of the next N steps' bytes
 
     def batch_at(self, step: int, rank: int = 0, pin: bool = False) -> dict:
-        return self.ds.batch_at(step, rank, pin, self.world)
+        out = self.ds.batch_at(step, rank, pin, self.world)
+        if self.readahead > 0 and hasattr(self.ds, "prefetch"):
+            self.ds.prefetch(range(step + 2, step + 2 + self.readahead), rank, self.world)     # step + 1 is being built next
+        return out
 
 
 def hstu_bucket_of(name: str) -> str:
@@ -296,6 +300,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                      sparse_lr=float(exp.get("sparse_lr", 1e-2)), clip_grad=float(exp.get("clip_grad", 1.0)),
                      emb_comm=exp.get("emb_a2a", "nccl"), seed=int(exp.get("seed", 0)), data_kw=data_kw)
     tr.lr_warmup_steps = int(exp.get("lr_warmup_steps", 0) or 0)
+    if hasattr(tr.data, "readahead"):
+        tr.data.readahead = int(exp.get("cold_prefetch_steps", 0) or 0)
     tr.pipelined = bool(int(exp.get("train_pipeline", 1)))
     tr.lr_warmup_start_lr = float(exp.get("lr_warmup_start_lr", 0.0) or 0.0)
     start = 0

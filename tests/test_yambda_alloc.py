@@ -67,8 +67,9 @@ def test_hstu_run_on_event_store_with_warmup(tmp_path):
                model=dict(layers=1, dim=32, heads=2, d_qk=16, d_v=16, max_seq_len=48, dtype="fp32", mlp_hidden=16,
                           num_positions=64, num_time_buckets=32),
                embedding=dict(rows=500, dim=16),
-               data=dict(kind="yambda", root=root, max_history=30, min_history=8, holdout=0.3, salt=1))
+               data=dict(kind="yambda", root=root, max_history=30, min_history=8, holdout=0.3, salt=1), cold_prefetch_steps=2)
     out = run(exp, device="cpu", stream=io.StringIO())
+    assert out["trainer"].data.readahead == 2
     assert len(out["losses"]) == 6 and all(l == l for l in out["losses"]) and len(out["aucs"]) == 2
     assert check_compliance(out["records"]) == []
     # warm-up left no trace: a run without it starts from the same state
@@ -184,3 +185,25 @@ def test_window_boundaries_are_announced(tmp_path, monkeypatch, capsys):
         device="cpu", stream=io.StringIO())
     lines = [l for l in capsys.readouterr().out.splitlines() if l.startswith("[window-barrier]")]
     assert len(lines) == 2 and "window 0" in lines[0] and "window 1" in lines[1]
+
+
+def test_event_store_read_ahead_covers_the_batches(tmp_path):
+    root = _store(tmp_path, users=40, events=120)
+    ds = EventStoreDataset(root, batch=4, max_history=30, min_history=8, holdout=0.2, salt=3)
+    for step in (0, 1, 5):
+        anchors = ds.step_anchors(step, 1, 2)
+        b = ds.batch_at(step, 1, world=2)
+        # the batch's last event of every sample is its anchor
+        ends = (b["offsets"][1:] - 1).tolist()
+        assert b["item_ids"][ends].tolist() == np.asarray(ds.item)[anchors].tolist()
+    ranges = ds.event_ranges([0, 1], 0, 1)
+    assert all(lo < hi for lo, hi in ranges) and all(a[1] < b[0] for a, b in zip(ranges, ranges[1:]))      # merged, disjoint
+    covered = np.zeros(len(ds.user), bool)
+    for lo, hi in ranges:
+        covered[lo:hi] = True
+    for step in (0, 1):
+        for a in ds.step_anchors(step):
+            assert covered[ds._history(int(a))].all() and covered[a]
+    n = ds.prefetch([0, 1])
+    width = sum(arr.dtype.itemsize for arr in (ds.item, ds.ts, ds.kind, ds.played))
+    assert n == sum(hi - lo for lo, hi in ranges) * width
