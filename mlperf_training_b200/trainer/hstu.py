@@ -273,6 +273,8 @@ def _warmup(tr: "HSTUTrainer", steps: int) -> None:
 
 def run(exp: dict, device: str | None = None, stream=None) -> dict:
     rank = dist.get_rank() if dist.is_initialized() else 0
+    from ..utils.metrics import StartupTimeline
+    timeline = StartupTimeline()
     world = dist.get_world_size() if dist.is_initialized() else 1
     device = device or ("cuda" if torch.cuda.is_available() else "cpu")
     sync = dist.barrier if world > 1 else None
@@ -299,6 +301,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     tr = HSTUTrainer(cfg, int(emb.get("rows", 1_000_000)), bpg, device, dense_lr=float(exp.get("dense_lr", 1e-3)),
                      sparse_lr=float(exp.get("sparse_lr", 1e-2)), clip_grad=float(exp.get("clip_grad", 1.0)),
                      emb_comm=exp.get("emb_a2a", "nccl"), seed=int(exp.get("seed", 0)), data_kw=data_kw)
+    timeline.mark("model_table_data")
     tr.lr_warmup_steps = int(exp.get("lr_warmup_steps", 0) or 0)
     if hasattr(tr.data, "readahead"):
         tr.data.readahead = int(exp.get("cold_prefetch_steps", 0) or 0)
@@ -325,6 +328,10 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         log.log_hyperparameters({"global_batch_size": bpg * world, "seed": int(exp.get("seed", 0)),
                                  "opt_base_learning_rate": float(exp.get("dense_lr", 1e-3))})
         _warmup(tr, int(exp.get("warmup_steps", 0)))
+        timeline.mark("warmup")
+        if rank == 0 and os.environ.get("STARTUP_TIMELINE", "0") == "1":
+            import json
+            print("[startup] " + json.dumps(timeline.report()), flush=True)
         log.log_init_stop_run_start()
         log.start(ml.BLOCK_START, metadata={"samples_count": 0})
     steps = int(exp.get("train_steps", 10))

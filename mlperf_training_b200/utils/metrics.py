@@ -185,3 +185,25 @@ def model_fingerprint(model, group=None) -> tuple[str, list[tuple[str, float, fl
     for name, n, s, q in rows:
         h.update(f"{name}:{n:.0f}:{s:.10e}:{q:.10e};".encode())
     return h.hexdigest(), rows
+
+
+class StartupTimeline:
+    """Named phases of the time before the clock starts (model build, sharding, loaders, checkpoint
+    load, warm-ups), each stamped when it ends; ``report()`` gives seconds per phase and the total, which a
+    run prints once so that slow cold starts can be told apart from slow steps
+    (generative_recommenders/dlrm_v4/train/dl_prestart.py keeps the same kind of startup timeline)."""
+
+    def __init__(self, clock=None):
+        import time
+        self._clock = clock or time.perf_counter
+        self._t0 = self._last = self._clock()
+        self.phases: list[tuple[str, float]] = []
+
+    def mark(self, name: str) -> float:
+        now = self._clock()
+        self.phases.append((name, now - self._last))
+        self._last = now
+        return self.phases[-1][1]
+
+    def report(self) -> dict:
+        return {"phases": {n: round(t, 4) for n, t in self.phases}, "total_s": round(self._last - self._t0, 4)}

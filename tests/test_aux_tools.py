@@ -116,3 +116,11 @@ def test_mxfp8_site_probe_reports_snr_and_is_scale_invariant():
     for k in rep:
         assert abs(rep2[k]["snr_db"] - rep[k]["snr_db"]) < 0.05
     assert main(["--tokens", "128", "--in", "128", "--out", "128", "--outliers", "0.01"]) == 0
+
+
+def test_startup_timeline_phases():
+    from mlperf_training_b200.utils.metrics import StartupTimeline
+    ticks = iter([0.0, 1.5, 4.0])
+    t = StartupTimeline(clock=lambda: next(ticks))
+    assert t.mark("model") == 1.5 and t.mark("warmup") == 2.5
+    assert t.report() == {"phases": {"model": 1.5, "warmup": 2.5}, "total_s": 4.0}
