@@ -58,6 +58,11 @@ class GPTConfig:
     recompute_layers: int = 0
     dtype: str = "bf16"
     precision: str = "bf16"         # GEMM precision of the linears: "bf16" | "mxfp8"
+    # the first / last N transformer layers keep bf16 linears whatever ``precision`` says (Megatron's
+    # first_last_layers_bf16 with num_layers_at_start_in_bf16 / num_layers_at_end_in_bf16, an option of the
+    # low-precision recipes: small_llm_moe_pretraining/primus/conf/gpt_oss_20B-MXFP4-deosc-mlperf-pretrain.yaml:55-57)
+    bf16_first_layers: int = 0
+    bf16_last_layers: int = 0
 
     def torch_dtype(self) -> torch.dtype:
         return {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}[self.dtype]
@@ -167,6 +172,7 @@ class DenseMLP(nn.Module):
                 raise ValueError(f"ffn_hidden {f} is not divisible by the tensor-parallel size {self.tp.world}")
             f //= self.tp.world
         self.precision = cfg.precision
+        self.force_bf16 = False          # set for the first / last layers that stay in bf16
         self.fused = True               # MXFP8: one unit with the quantisation folded into SwiGLU / dSwiGLU
         self.w_gate_up = nn.Parameter(torch.empty(2 * f, d, dtype=dtype, device=device))
         self.w_down = nn.Parameter(torch.empty(d, f, dtype=dtype, device=device))
@@ -179,10 +185,11 @@ class DenseMLP(nn.Module):
             from ..parallel import tensor as T
             gu = T.column_parallel(F.rms_norm(h, norm_w, eps), self.w_gate_up, self.tp)
             return T.row_parallel(F.swiglu(gu), self.w_down, self.tp, residual=h)
-        if self.precision == "mxfp8" and self.fused and F.fused_mlp_eligible(h, self.w_gate_up, self.w_down):
+        pr = "bf16" if self.force_bf16 else self.precision
+        if pr == "mxfp8" and self.fused and F.fused_mlp_eligible(h, self.w_gate_up, self.w_down):
             return F.fused_mlp(h, norm_w, self.w_gate_up, self.w_down, eps)
-        gu = F.norm_linear(h, norm_w, self.w_gate_up, eps=eps, precision=self.precision)
-        return F.swiglu_linear(gu, self.w_down, residual=h, precision=self.precision)
+        gu = F.norm_linear(h, norm_w, self.w_gate_up, eps=eps, precision=pr)
+        return F.swiglu_linear(gu, self.w_down, residual=h, precision=pr)
 
 
 class Block(nn.Module):
@@ -190,6 +197,7 @@ class Block(nn.Module):
         super().__init__()
         self.cfg = cfg
         self.layer = layer
+        self.force_bf16 = layer < cfg.bf16_first_layers or layer >= cfg.n_layers - cfg.bf16_last_layers
         d, hd = cfg.hidden, cfg.head_dim
         self.tp = tp if (tp is not None and tp.world > 1) else None
         W = self.tp.world if self.tp is not None else 1
@@ -216,6 +224,7 @@ class Block(nn.Module):
             self.mlp = MoEMLP(cfg, dtype, device, ep_group=ep_group, ep_comm=cfg.ep_comm)
         else:
             self.mlp = DenseMLP(cfg, dtype, device, tp=self.tp)
+            self.mlp.force_bf16 = self.force_bf16
         self.lora_qkv = self.lora_proj = None
         if cfg.lora_rank > 0:
             from .lora import LoRAAdapter
@@ -272,20 +281,21 @@ class Block(nn.Module):
         cfg = self.cfg
         if self.tp is not None:
             return self._forward_tp(x, cos, sin, B, S)
+        pr = "bf16" if self.force_bf16 else cfg.precision
         if self.lora_qkv is None:
-            qkv = F.norm_linear(x, self.attn_norm, self.w_qkv, eps=cfg.norm_eps, precision=cfg.precision)
+            qkv = F.norm_linear(x, self.attn_norm, self.w_qkv, eps=cfg.norm_eps, precision=pr)
         else:
             xn = F.rms_norm(x, self.attn_norm, cfg.norm_eps)
-            qkv = F.linear(xn, self.w_qkv, None, None, cfg.precision) + self.lora_qkv(xn)
+            qkv = F.linear(xn, self.w_qkv, None, None, pr) + self.lora_qkv(xn)
         if self.cp is not None:
             a = self._attention_cp(qkv, cos, sin, B, S)
         else:
             a = F.attention_packed(qkv, B=B, S=S, Hq=cfg.n_heads, Hkv=cfg.n_kv_heads, D=cfg.head_dim, cos=cos, sin=sin,
                                    sink=self.sink, causal=True, window=cfg.layer_window(self.layer))
         if self.lora_proj is None:
-            h = F.linear(a, self.w_proj, None, x, cfg.precision)
+            h = F.linear(a, self.w_proj, None, x, pr)
         else:
-            h = F.linear(a, self.w_proj, None, x, cfg.precision) + self.lora_proj(a)
+            h = F.linear(a, self.w_proj, None, x, pr) + self.lora_proj(a)
         return self.mlp(h, self.mlp_norm, cfg.norm_eps)
 
 

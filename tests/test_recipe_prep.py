@@ -63,3 +63,25 @@ def test_window_index_is_ordered_and_deterministic():
     assert np.array_equal(idx["holdout"], again["holdout"])
     big = prep.build_window_index(np.arange(20000), 100, holdout=0.1, salt=1)
     assert 0.07 < big["holdout"].mean() < 0.13
+
+
+def test_first_and_last_layers_stay_in_bf16(monkeypatch):
+    import torch
+    from mlperf_training_b200.models.gpt import GPT, GPTConfig
+    from mlperf_training_b200.ops import functional as F
+    cfg = GPTConfig(n_layers=4, hidden=32, n_heads=2, n_kv_heads=1, head_dim=16, ffn_hidden=64, vocab_size=64, seq_len=8, dtype="fp32",
+                    precision="mxfp8", bf16_first_layers=1, bf16_last_layers=2)
+    m = GPT(cfg, seed=0)
+    assert [b.force_bf16 for b in m.blocks] == [True, False, True, True]
+    assert [b.mlp.force_bf16 for b in m.blocks] == [True, False, True, True]
+    seen = []
+    real = F.norm_linear
+
+    def spy(*a, **kw):
+        seen.append(kw.get("precision"))
+        return real(*a, **kw)
+    monkeypatch.setattr(F, "norm_linear", spy)
+    tok = torch.randint(0, 64, (1, 9))
+    m(tok[:, :-1], tok[:, 1:]).backward()
+    # per layer: the qkv projection and the gate/up projection
+    assert seen == ["bf16", "bf16", "mxfp8", "mxfp8", "bf16", "bf16", "bf16", "bf16"]
