@@ -96,10 +96,41 @@ def qkv_from_megatron(w: torch.Tensor, n_heads: int, n_kv: int, hd: int) -> torc
     return torch.cat([q, k, v], dim=0)
 
 
+def _stages_of(model):
+    """Pipeline stages inside ``model`` (a stage itself, or a list of them), else None."""
+    def is_stage(m):
+        return hasattr(m, "layers") and hasattr(m, "stage") and hasattr(m, "n_stages")
+    if is_stage(model):
+        return [("", model)]
+    if isinstance(model, torch.nn.ModuleList) and len(model) and all(is_stage(m) for m in model):
+        return [(f"{i}.", m) for i, m in enumerate(model)]
+    return None
+
+
+def model_config_of(model):
+    stages = _stages_of(model)
+    return model.cfg if stages is None else stages[0][1].cfg
+
+
+def global_named_parameters(model):
+    """``(name, parameter)`` with the names of the unsplit model: a pipeline stage numbers its blocks by
+    position inside the stage, a checkpoint by the layer's index in the whole network."""
+    stages = _stages_of(model)
+    if stages is None:
+        yield from model.named_parameters()
+        return
+    for _, stage in stages:
+        for name, p in stage.named_parameters():
+            parts = name.split(".")
+            if parts[0] == "blocks":
+                parts[1] = str(stage.layers[int(parts[1])])
+            yield ".".join(parts), p
+
+
 def to_megatron_state(model: GPT) -> dict[str, torch.Tensor]:
-    cfg = model.cfg
+    cfg = model_config_of(model)
     out = {}
-    for name, p in model.named_parameters():
+    for name, p in global_named_parameters(model):
         t = p.detach()
         if name.endswith("w_qkv") or name.endswith("lora_qkv.b"):
             t = qkv_to_megatron(t, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
@@ -110,10 +141,10 @@ def to_megatron_state(model: GPT) -> dict[str, torch.Tensor]:
 def load_megatron_state(model: GPT, state: dict[str, torch.Tensor], strict: bool = True) -> list[str]:
     """Copy a (Megatron-named) state dict into ``model``.  Returns the model parameters that were
     not found (e.g. freshly initialised LoRA adapters when loading a base checkpoint)."""
-    cfg = model.cfg
+    cfg = model_config_of(model)
     missing = []
     with torch.no_grad():
-        for name, p in model.named_parameters():
+        for name, p in global_named_parameters(model):
             key = megatron_name(name, moe_pre_norm=cfg.n_experts > 0)
             if key not in state:
                 missing.append(name)
@@ -165,8 +196,8 @@ def load_torch_dist(model: GPT, root: str, iteration: int | None = None, strict:
     common = torch.load(d / "common.pt", map_location="cpu", weights_only=False) if (d / "common.pt").exists() else {}
     saved_cfg = common.get("model_config") or {}
     for k in ("n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "vocab_size"):
-        if k in saved_cfg and saved_cfg[k] != getattr(model.cfg, k):
-            raise ValueError(f"checkpoint {k}={saved_cfg[k]} but model has {getattr(model.cfg, k)}")
+        if k in saved_cfg and saved_cfg[k] != getattr(model_config_of(model), k):
+            raise ValueError(f"checkpoint {k}={saved_cfg[k]} but model has {getattr(model_config_of(model), k)}")
     want = {f"model.{k}": torch.empty_like(v) for k, v in to_megatron_state(model).items()}
     reader = dcp.FileSystemReader(str(d))
     present = set(reader.read_metadata().state_dict_metadata.keys())

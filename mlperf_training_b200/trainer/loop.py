@@ -240,9 +240,6 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         return b
 
     per_rank_params = pp_size > 1 or ep_size > 1
-    if rc.pretrained_checkpoint and pp_size > 1:
-        raise NotImplementedError("loading a Megatron torch_dist checkpoint into pipeline stages is not wired: load with "
-                                  "pipeline_parallel = 1, or resume from this framework's own checkpoint")
     if rc.pretrained_checkpoint and not resuming:
         from ..checkpoint.megatron import load_torch_dist
         load_torch_dist(trainer.model, rc.pretrained_checkpoint, strict=True)

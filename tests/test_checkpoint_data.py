@@ -261,3 +261,32 @@ def test_flux_run_on_pre_encoded_dataset(tmp_path):
                    data=dict(kind="encoded", path=str(tmp_path / "enc"))), device="cpu", stream=io.StringIO())
     assert len(out["losses"]) == 4 and all(l == l for l in out["losses"]) and out["eval_loss"] is not None
     assert out["trainer"].empty_txt is not None and float(out["trainer"].empty_txt.mean()) == 0.5
+
+
+def test_torch_dist_checkpoint_loads_into_pipeline_stages(tmp_path):
+    import torch.nn as nn
+    from mlperf_training_b200.parallel.pipeline import GPTStage
+    cfg = GPTConfig(**{**TINY, "n_layers": 5})
+    full = GPT(cfg, seed=1)
+    MG.save_torch_dist(full, str(tmp_path / "base"), iteration=0)
+    # two plain stages (3 + 2 layers) ...
+    for s in range(2):
+        stage = GPTStage(cfg, s, 2)
+        info = MG.load_torch_dist(stage, str(tmp_path / "base"))
+        assert info["missing"] == []
+        for blk, i in zip(stage.blocks, stage.layers):
+            for (n, p), (_, q) in zip(blk.named_parameters(), full.blocks[i].named_parameters()):
+                assert torch.equal(p, q), (s, i, n)
+        if stage.first:
+            assert torch.equal(stage.embed, full.embed)
+        if stage.last:
+            assert torch.equal(stage.lm_head, full.lm_head) and torch.equal(stage.final_norm, full.final_norm)
+    # ... and the two chunks a rank owns under interleaved stages (virtual stages 1 and 3 of 4)
+    chunks = nn.ModuleList([GPTStage(cfg, 1, 4), GPTStage(cfg, 3, 4)])
+    MG.load_torch_dist(chunks, str(tmp_path / "base"))
+    for ch in chunks:
+        for blk, i in zip(ch.blocks, ch.layers):
+            assert torch.equal(blk.w_qkv, full.blocks[i].w_qkv)
+    assert torch.equal(chunks[1].lm_head, full.lm_head)
+    names = [n for n, _ in MG.global_named_parameters(chunks)]
+    assert len(names) == len(set(names)) and all(n in dict(full.named_parameters()) for n in names)
