@@ -1,3 +1,4 @@
+"""MLLOG logger: submission metadata."""
 
 
 def test_submission_metadata_comes_from_the_environment(monkeypatch):
