@@ -53,7 +53,9 @@ class GPTConfig:
     lora_dropout: float = 0.0
     lora_targets: tuple = ("qkv", "proj")
     # activation recompute: "none" | "full" (every block's forward is run again in backward and only
-    # its input is kept); recompute_layers > 0 limits it to the first N blocks
+    # its input is kept) | "offload" (nothing is recomputed: what a block saves for backward moves to
+    # pinned host memory, the CPU activation offload of llama2_sft/primus/src/llama2_custom.py:522-542);
+    # recompute_layers > 0 limits either to the first N blocks
     recompute: str = "none"
     recompute_layers: int = 0
     dtype: str = "bf16"
@@ -401,6 +403,7 @@ class GPT(nn.Module):
             ids, tgt = ids[r * rows:(r + 1) * rows], tgt[r * rows:(r + 1) * rows]
         x = F.embedding(ids, self.embed)
         ckpt = self.cfg.recompute == "full" and torch.is_grad_enabled()
+        offload = self.cfg.recompute == "offload" and torch.is_grad_enabled()
         notify = self.grad_ready_hook if (torch.is_grad_enabled() and not ckpt) else None
         for i, blk in enumerate(self.blocks):
             if notify is not None and x.requires_grad:
@@ -409,6 +412,10 @@ class GPT(nn.Module):
             if ckpt and (self.cfg.recompute_layers <= 0 or i < self.cfg.recompute_layers):
                 from torch.utils.checkpoint import checkpoint
                 x = checkpoint(blk, x, cos, sin, B, S, use_reentrant=False)
+            elif offload and (self.cfg.recompute_layers <= 0 or i < self.cfg.recompute_layers):
+                # keep what this block saves for backward in (pinned) host memory instead of on the device
+                with torch.autograd.graph.save_on_cpu(pin_memory=x.is_cuda):
+                    x = blk(x, cos, sin, B, S)
             else:
                 x = blk(x, cos, sin, B, S)
         return F.lm_head_loss(x, self.final_norm, self.lm_head, tgt, eps=self.cfg.norm_eps,

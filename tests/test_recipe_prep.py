@@ -85,3 +85,19 @@ def test_first_and_last_layers_stay_in_bf16(monkeypatch):
     m(tok[:, :-1], tok[:, 1:]).backward()
     # per layer: the qkv projection and the gate/up projection
     assert seen == ["bf16", "bf16", "mxfp8", "mxfp8", "bf16", "bf16", "bf16", "bf16"]
+
+
+def test_activation_offload_gives_the_same_gradients():
+    import torch
+    from mlperf_training_b200.models.gpt import GPT, GPTConfig
+    base = dict(n_layers=3, hidden=32, n_heads=2, n_kv_heads=1, head_dim=16, ffn_hidden=64, vocab_size=64, seq_len=8, dtype="fp32")
+    tok = torch.randint(0, 64, (2, 9), generator=torch.Generator().manual_seed(0))
+    grads = []
+    for mode, layers in (("none", 0), ("offload", 0), ("offload", 2), ("full", 0)):
+        m = GPT(GPTConfig(**base, recompute=mode, recompute_layers=layers), seed=2)
+        loss = m(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        grads.append((float(loss), [p.grad.clone() if p.grad is not None else p.main_grad.clone() for p in m.parameters()]))
+    for l, g in grads[1:]:
+        assert l == grads[0][0]
+        assert all(torch.allclose(a, b, atol=1e-7) for a, b in zip(g, grads[0][1]))
