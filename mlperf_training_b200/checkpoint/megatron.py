@@ -10,8 +10,10 @@ workload loads such a base checkpoint with ``finetune=True, load_optim=False, lo
   the fused-QKV layout (Megatron interleaves per KV group: ``[q_0 .. q_{g-1}, k, v]`` for each
   group; here all query heads come first, then all keys, then all values);
 * writes / reads the ``.distcp`` shards and ``.metadata`` through ``torch.distributed.checkpoint``
-  with one entry per Megatron key, so every rank (tensor/expert/pipeline shard) only touches the
-  slices it owns;
+  with one full-shape entry per Megatron key.  Under tensor parallelism a rank reads a key at its
+  full shape (a few keys at a time), converts the fused-QKV layout on the full tensor and keeps its
+  own slice; on save the slices are gathered over the tensor-parallel group first, so the file holds
+  the same unsharded tensors whatever the parallel layout of the writer;
 * writes ``common.pt``, ``metadata.json`` and ``latest_checkpointed_iteration.txt``.
 """
 from __future__ import annotations
@@ -23,7 +25,7 @@ from pathlib import Path
 import torch
 import torch.distributed.checkpoint as dcp
 
-from ..models.gpt import GPT, GPTConfig
+from ..models.gpt import GPT, GPTConfig, shard_of
 
 _LAYER = re.compile(r"blocks\.(\d+)\.(.+)")
 
@@ -127,24 +129,73 @@ def global_named_parameters(model):
             yield ".".join(parts), p
 
 
-def to_megatron_state(model: GPT) -> dict[str, torch.Tensor]:
+def full_shape_of(p: torch.Tensor) -> tuple:
+    """Shape of the unsharded tensor behind a (possibly tensor-parallel) parameter."""
+    shard = getattr(p, "tensor_parallel", None)
+    if shard is None:
+        return tuple(p.shape)
+    kind, W, _ = shard
+    if kind == "cols":
+        return (p.shape[0], p.shape[1] * W)
+    return (p.shape[0] * W, *p.shape[1:])
+
+
+def unshard(parts: list[torch.Tensor], kind: str, cfg: GPTConfig) -> torch.Tensor:
+    """Inverse of ``models.gpt.shard_of``: the full tensor from the slices of ranks 0..W-1."""
+    W = len(parts)
+    if kind == "rows":
+        return torch.cat(parts, 0)
+    if kind == "cols":
+        return torch.cat(parts, 1)
+    if kind == "rows_2":
+        halves = [t.chunk(2, 0) for t in parts]
+        return torch.cat([h[0] for h in halves] + [h[1] for h in halves], 0)
+    if kind == "qkv":
+        hd = cfg.head_dim
+        sizes = [cfg.n_heads * hd // W, cfg.n_kv_heads * hd // W, cfg.n_kv_heads * hd // W]
+        pieces = [t.split(sizes, 0) for t in parts]
+        return torch.cat([pc[i] for i in range(3) for pc in pieces], 0)
+    raise ValueError(kind)
+
+
+def _full_tensor(p: torch.Tensor, cfg: GPTConfig, tp_group) -> torch.Tensor:
+    """The unsharded value of parameter ``p`` (gathered over ``tp_group`` when it is a slice)."""
+    shard = getattr(p, "tensor_parallel", None)
+    t = p.detach()
+    if shard is None:
+        return t
+    kind, W, _ = shard
+    if tp_group is None or torch.distributed.get_world_size(tp_group) != W:
+        raise ValueError("a tensor-parallel parameter needs its tensor-parallel group to be gathered")
+    parts = [torch.empty_like(t) for _ in range(W)]
+    torch.distributed.all_gather(parts, t.contiguous(), group=tp_group)
+    return unshard(parts, kind, cfg)
+
+
+def to_megatron_state(model: GPT, tp_group=None) -> dict[str, torch.Tensor]:
+    """Megatron-named state with every tensor at its full (unsharded) shape.  Collective over
+    ``tp_group`` when the model holds tensor-parallel slices."""
     cfg = model_config_of(model)
     out = {}
     for name, p in global_named_parameters(model):
-        t = p.detach()
+        t = _full_tensor(p, cfg, tp_group)
         if name.endswith("w_qkv") or name.endswith("lora_qkv.b"):
             t = qkv_to_megatron(t, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
         out[megatron_name(name, moe_pre_norm=cfg.n_experts > 0)] = t.contiguous()
     return out
 
 
-def load_megatron_state(model: GPT, state: dict[str, torch.Tensor], strict: bool = True) -> list[str]:
-    """Copy a (Megatron-named) state dict into ``model``.  Returns the model parameters that were
-    not found (e.g. freshly initialised LoRA adapters when loading a base checkpoint)."""
-    cfg = model_config_of(model)
+def _tp_group_of(model):
+    tp = getattr(model, "tp", None)
+    return getattr(tp, "group", None) if tp is not None else None
+
+
+def _load_named(named, state: dict[str, torch.Tensor], cfg: GPTConfig) -> list[str]:
+    """Copy the entries of ``state`` (Megatron names, full shapes or this rank's slices) into the
+    parameters of ``named``; returns the names without an entry."""
     missing = []
     with torch.no_grad():
-        for name, p in global_named_parameters(model):
+        for name, p in named:
             key = megatron_name(name, moe_pre_norm=cfg.n_experts > 0)
             if key not in state:
                 missing.append(name)
@@ -152,9 +203,19 @@ def load_megatron_state(model: GPT, state: dict[str, torch.Tensor], strict: bool
             t = state[key]
             if name.endswith("w_qkv") or name.endswith("lora_qkv.b"):
                 t = qkv_from_megatron(t, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
+            shard = getattr(p, "tensor_parallel", None)
+            if shard is not None and tuple(t.shape) == full_shape_of(p):
+                t = shard_of(t, shard[0], shard[1], shard[2], cfg)     # the layout conversion ran on the full tensor
             if tuple(t.shape) != tuple(p.shape):
                 raise ValueError(f"{key}: checkpoint shape {tuple(t.shape)} vs model {tuple(p.shape)}")
             p.copy_(t.to(p.dtype))
+    return missing
+
+
+def load_megatron_state(model: GPT, state: dict[str, torch.Tensor], strict: bool = True) -> list[str]:
+    """Copy a (Megatron-named) state dict into ``model``.  Returns the model parameters that were
+    not found (e.g. freshly initialised LoRA adapters when loading a base checkpoint)."""
+    missing = _load_named(list(global_named_parameters(model)), state, model_config_of(model))
     if strict and any("lora" not in m for m in missing):
         raise KeyError(f"checkpoint lacks parameters: {[m for m in missing if 'lora' not in m]}")
     return missing
@@ -169,7 +230,7 @@ def save_torch_dist(model: GPT, root: str, iteration: int = 0, extra_common: dic
         d.mkdir(parents=True, exist_ok=True)
     if torch.distributed.is_initialized():
         torch.distributed.barrier()
-    state = {f"model.{k}": v for k, v in to_megatron_state(model).items()}
+    state = {f"model.{k}": v for k, v in to_megatron_state(model, _tp_group_of(model)).items()}
     dcp.save(state, checkpoint_id=str(d))
     if rank == 0:
         common = {"iteration": iteration, "checkpoint_version": 3.0, "args": None, "model_config": model.cfg.to_dict()}
@@ -198,10 +259,25 @@ def load_torch_dist(model: GPT, root: str, iteration: int | None = None, strict:
     for k in ("n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "vocab_size"):
         if k in saved_cfg and saved_cfg[k] != getattr(model_config_of(model), k):
             raise ValueError(f"checkpoint {k}={saved_cfg[k]} but model has {getattr(model_config_of(model), k)}")
-    want = {f"model.{k}": torch.empty_like(v) for k, v in to_megatron_state(model).items()}
+    cfg = model_config_of(model)
     reader = dcp.FileSystemReader(str(d))
     present = set(reader.read_metadata().state_dict_metadata.keys())
-    sub = {k: v for k, v in want.items() if k in present}
-    dcp.load(sub, checkpoint_id=str(d))
-    missing = load_megatron_state(model, {k[len("model."):]: v for k, v in sub.items()}, strict=strict)
+    # full-shape destinations, read and consumed a group of keys at a time (a tensor-parallel rank keeps
+    # only its slice of each, so the full tensors of the whole model never sit in memory together)
+    named = list(global_named_parameters(model))
+    sharded = any(getattr(p, "tensor_parallel", None) is not None for _, p in named)
+    per_group = 16 if sharded else len(named)
+    missing = []
+    for g0 in range(0, len(named), max(per_group, 1)):
+        group = named[g0:g0 + per_group]
+        want = {}
+        for name, p in group:
+            key = "model." + megatron_name(name, moe_pre_norm=cfg.n_experts > 0)
+            if key in present:
+                want[key] = torch.empty(full_shape_of(p), dtype=p.dtype, device="cpu")
+        if want:
+            dcp.load(want, checkpoint_id=str(d))
+        missing += _load_named(group, {k[len("model."):]: v for k, v in want.items()}, cfg)
+    if strict and any("lora" not in m for m in missing):
+        raise KeyError(f"checkpoint lacks parameters: {[m for m in missing if 'lora' not in m]}")
     return {"iteration": iteration, "missing": missing, "common": common}

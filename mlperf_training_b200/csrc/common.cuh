@@ -128,6 +128,28 @@ B200_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_f
   }
 }
 
+// Same contract, for waits on the critical path of a pipeline (a phase that completes within a few
+// hundred nanoseconds): polls with plain try_wait and no suspend hint, because a thread parked with a
+// long hint was seen to resume late after the phase completed; the clock is read every 256 polls.
+B200_DEVICE bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int where) {
+  uint64_t t0 = 0;
+  uint32_t it = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++it & 0xff) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > B200_WAIT_LIMIT_NS) {
+        b200_report(status, B200_ERR_TIMEOUT_MBAR, where);
+        *abort_flag = 1;
+        __threadfence_block();
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // Bounded acquire-wait on a 32-bit flag in global (possibly peer) memory: flag >= want.
 B200_DEVICE bool flag_wait_geq(const int* flag, int want, uint64_t limit_ns, int* status, int where) {
   uint64_t t0 = 0;
@@ -310,6 +332,11 @@ B200_DEVICE void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+B200_DEVICE void tmem_st_32x32b_x4(uint32_t taddr, const uint4& v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
 // packed two-wide fp32 arithmetic (sm_100 f32x2 instructions): one issue slot for two lanes
 B200_DEVICE float2 ffma2(float2 a, float2 b, float2 c) {
   float2 d;
@@ -430,4 +457,79 @@ B200_DEVICE float warp_max(float v) {
 }
 B200_DEVICE void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// ----------------------------------------------------------------------------------
+// CTA pairs (thread-block clusters of two; cta_group::2 tensor-core instructions)
+// ----------------------------------------------------------------------------------
+// Rank 0 of the pair issues the MMAs; both CTAs stage their halves of the operands in their own
+// shared memory with their own TMA loads (no cluster multicast loads anywhere) and signal the
+// leader's mbarrier.
+B200_DEVICE uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `smem_addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+B200_DEVICE uint32_t mapa_u32(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+B200_DEVICE void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on an mbarrier of any CTA of the cluster (address from mapa_u32)
+B200_DEVICE void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+// tiled TMA load into this CTA's shared memory whose completion bytes are counted on an mbarrier
+// of this CTA or of its pair partner (address from mapa_u32)
+B200_DEVICE void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+B200_DEVICE void tmem_alloc_pair(uint32_t* smem_holder, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_holder)),
+               "r"(ncols)
+               : "memory");
+}
+B200_DEVICE void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+B200_DEVICE void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// arrive on the mbarrier at the same shared-memory offset in every CTA of `cta_mask` once all
+// tcgen05.mma issued so far by this thread have completed (a signal, not a data transfer)
+B200_DEVICE void tc_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"(cta_mask)
+               : "memory");
+}
+// D[tmem of both CTAs, 128 rows each] (+)= A[256 x K, 128 rows per CTA] * B[N x K, N/2 rows per CTA]
+B200_DEVICE void tc_mma_f16_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
+B200_DEVICE void tc_mma_mxf8_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum,
+                                     uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// scale atoms: each CTA of the pair copies from its own shared memory to its own TMEM
+B200_DEVICE void tc_cp_32x128b_warpx4_pair(uint32_t tmem_dst, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(sdesc) : "memory");
 }

@@ -18,16 +18,19 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "gemm_core.cuh"
 #include "runtime.h"
 
 namespace {
 
+using gemmcore::tile_coords;
+
 constexpr int BM = 128;
 constexpr int BK = 64;            // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 192;
-constexpr int EPI_WARPS = 4;
-constexpr int STG_BYTES = 4096;   // one epilogue staging buffer: 32 rows x 128 bytes
+constexpr int NUM_THREADS = gemmcore::NUM_THREADS;
+constexpr int EPI_WARPS = gemmcore::EPI_WARPS;
+constexpr int STG_BYTES = gemmcore::STG_BYTES;   // one epilogue staging buffer: 32 rows x 128 bytes
 
 template <int BN>
 struct Cfg {
@@ -42,25 +45,10 @@ struct Cfg {
 struct Params {
   int M, N, K;
   int a_mn_major, b_mn_major;
-  int out_f32;        // 0: bf16 output, 1: fp32 output
-  int accumulate;     // 0: store, 1: reduce-add into D
   int group_m;        // raster group height in tiles
-  const __nv_bfloat16* bias;      // [N] or null
-  const __nv_bfloat16* residual;  // [M, ldr] or null
-  long long ldr;
-  float alpha;        // scale applied to the accumulator before bias/residual
+  gemmcore::EpiArgs epi;
   int* status;
 };
-
-B200_DEVICE void tile_coords(int t, int num_m, int num_n, int group_m, int& mb, int& nb) {
-  int in_group = group_m * num_n;
-  int g = t / in_group;
-  int first_m = g * group_m;
-  int gsz = min(num_m - first_m, group_m);
-  int r = t - g * in_group;
-  mb = first_m + (r % gsz);
-  nb = r / gsz;
-}
 
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -170,106 +158,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;                 // TMEM lane quarter owned by this warp
-    const int ew = warp - 2;                // staging slot
-    uint8_t* stg = sE + ew * 2 * STG_BYTES;
+    uint8_t* stg = sE + (warp - 2) * 2 * STG_BYTES;
     int buf = 0;
     int it = 0;
     bool ok = true;
-    const bool vec_res = p.residual != nullptr && (p.ldr % 8 == 0) && (p.N % 8 == 0) &&
-                         ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
       int mb, nb; tile_coords(t, num_m, num_n, p.group_m, mb, nb);
-      const int m0 = mb * BM, n0 = nb * BN;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, p.status, 30)) { ok = false; break; }
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;   // global row of this thread
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + c * 32, r);
-        tc_wait_ld();
-        const int col0 = n0 + c * 32;
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
-        }
-        if (p.residual != nullptr && row < p.M) {
-          const __nv_bfloat16* rp = p.residual + (long long)row * p.ldr + col0;
-          if (vec_res) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (col0 + j * 8 < p.N) {
-                uint4 u = *reinterpret_cast<const uint4*>(rp + j * 8);
-                float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
-                v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
-                v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
-              }
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) v[i] += __bfloat162float(rp[i]);
-          }
-        }
-        if (p.out_f32) {
-          // one staging buffer = 32 rows x 32 fp32 (128 bytes per row)
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
-          uint8_t* sb = stg + buf * STG_BYTES + lane * 128;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            uint4 u = make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
-                                 __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
-            *reinterpret_cast<uint4*>(sb + ((j ^ (lane & 7)) << 4)) = u;
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            if (col0 < p.N && m0 + q * 32 < p.M) {
-              if (p.accumulate) tma_reduce_add_2d(&tmD, stg + buf * STG_BYTES, col0, m0 + q * 32);
-              else tma_store_2d(&tmD, stg + buf * STG_BYTES, col0, m0 + q * 32);
-            }
-            tma_store_commit();
-          }
-          buf ^= 1;
-        } else {
-          // one staging buffer = 32 rows x 64 bf16; two 32-column chunks fill it
-          const int half = c & 1;
-          if (half == 0) {
-            if (lane == 0) tma_store_wait_read<1>();
-            __syncwarp();
-          }
-          uint8_t* sb = stg + buf * STG_BYTES + lane * 128;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 u = make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
-                                 pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
-            const int chunk = half * 4 + j;
-            *reinterpret_cast<uint4*>(sb + ((chunk ^ (lane & 7)) << 4)) = u;
-          }
-          if (half == 1) {
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              const int cs = col0 - 32;
-              if (cs < p.N && m0 + q * 32 < p.M) {
-                if (p.accumulate) tma_reduce_add_2d(&tmD, stg + buf * STG_BYTES, cs, m0 + q * 32);
-                else tma_store_2d(&tmD, stg + buf * STG_BYTES, cs, m0 + q * 32);
-              }
-              tma_store_commit();
-            }
-            buf ^= 1;
-          }
-        }
-      }
-      // all TMEM reads of this accumulator are complete (tc_wait_ld above): hand it back
+      gemmcore::epilogue_drain<BN, true>(&tmD, &tmD, p.epi, t_row, mb * BM + q * 32, nb * BN, stg, buf, lane);
+      // all TMEM reads of this accumulator are complete: hand it back
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -313,18 +214,31 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   return b200::check_launch("gemm_bf16");
 }
 
-// Height (in tiles) of a raster group: consecutive CTAs work on `group_m` row tiles of one column tile, so the
-// column's B tile is shared in L2 while the group's A rows stay resident (B200_GEMM_GROUP_M overrides).
-static int raster_group_m() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("B200_GEMM_GROUP_M");
-    v = (e && atoi(e) > 0) ? atoi(e) : 16;
-  }
-  return v;
-}
-
 }  // namespace
+
+// One CTA pair per 256 x BN tile (gemm_core.cuh).
+template <int BN>
+static int run_pair(const void* a, const void* b, void* d, int M, int N, int K, long long lda, long long ldb,
+                    long long ldd, int a_mn_major, int b_mn_major, const gemmcore::EpiArgs& epi, cudaStream_t stream) {
+  using namespace gemmcore;
+  CUtensorMap tmA, tmB, tmD;
+  int r;
+  if (!a_mn_major) r = b200::make_tmap_2d(&tmA, b200::DT_BF16, a, K, M, lda * 2, BK, 128, b200::SWZ_128);
+  else r = b200::make_tmap_2d(&tmA, b200::DT_BF16, a, M, K, lda * 2, 64, BK, b200::SWZ_128);
+  if (r) return r;
+  if (!b_mn_major) r = b200::make_tmap_2d(&tmB, b200::DT_BF16, b, K, N, ldb * 2, BK, BN / 2, b200::SWZ_128);
+  else r = b200::make_tmap_2d(&tmB, b200::DT_BF16, b, N, K, ldb * 2, 64, BK, b200::SWZ_128);
+  if (r) return r;
+  CUtensorMap tmDt;
+  if ((r = make_out_tmap<BN>(&tmD, &tmDt, d, M, N, ldd, epi.out_f32))) return r;
+  PairParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+  p.group_m = raster_group_m() > 1 ? raster_group_m() / 2 : 1;
+  p.epi = epi;
+  p.status = b200::status_ptr();
+  return launch_pair<KIND_BF16, BN, 1>(tmA, tmB, tmA, tmB, tmD, tmDt, p, stream, "gemm_bf16(pair)");
+}
 
 // D[M,N] (=|+=) alpha * A * B^T (+ bias) (+ residual)
 //   a: K-major [M, lda] (a_mn_major = 0) or MN-major [K, lda] (a_mn_major = 1); same for b with N.
@@ -335,7 +249,20 @@ B200_API int b200_gemm_bf16(const void* a, const void* b, void* d, int M, int N,
                             void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return b200::fail(210, "gemm_bf16: empty problem %d x %d x %d", M, N, K);
   const int BN = (N > 128) ? 256 : 128;
-  CUtensorMap tmA, tmB, tmD;
+  gemmcore::EpiArgs epi;
+  epi.M = M; epi.N = N;
+  epi.out_f32 = out_f32 ? 1 : 0; epi.accumulate = accumulate ? 1 : 0;
+  epi.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  epi.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  epi.ldr = ldr;
+  epi.alpha = alpha;
+  if (M > 128 && gemmcore::pair_enabled()) {
+    if (BN == 256) return run_pair<256>(a, b, d, M, N, K, lda, ldb, ldd, a_mn_major ? 1 : 0, b_mn_major ? 1 : 0, epi,
+                                        (cudaStream_t)stream);
+    return run_pair<128>(a, b, d, M, N, K, lda, ldb, ldd, a_mn_major ? 1 : 0, b_mn_major ? 1 : 0, epi,
+                         (cudaStream_t)stream);
+  }
+  CUtensorMap tmA, tmB, tmD, tmDt;
   int r;
   if (!a_mn_major) r = b200::make_tmap_2d(&tmA, b200::DT_BF16, a, K, M, lda * 2, BK, BM, b200::SWZ_128);
   else r = b200::make_tmap_2d(&tmA, b200::DT_BF16, a, M, K, lda * 2, 64, BK, b200::SWZ_128);
@@ -343,18 +270,14 @@ B200_API int b200_gemm_bf16(const void* a, const void* b, void* d, int M, int N,
   if (!b_mn_major) r = b200::make_tmap_2d(&tmB, b200::DT_BF16, b, K, N, ldb * 2, BK, BN, b200::SWZ_128);
   else r = b200::make_tmap_2d(&tmB, b200::DT_BF16, b, N, K, ldb * 2, 64, BK, b200::SWZ_128);
   if (r) return r;
-  if (out_f32) r = b200::make_tmap_2d(&tmD, b200::DT_F32, d, N, M, ldd * 4, 32, 32, b200::SWZ_128);
-  else r = b200::make_tmap_2d(&tmD, b200::DT_BF16, d, N, M, ldd * 2, 64, 32, b200::SWZ_128);
+  r = (BN == 256) ? gemmcore::make_out_tmap<256>(&tmD, &tmDt, d, M, N, ldd, out_f32)
+                  : gemmcore::make_out_tmap<128>(&tmD, &tmDt, d, M, N, ldd, out_f32);
   if (r) return r;
   Params p;
   p.M = M; p.N = N; p.K = K;
   p.a_mn_major = a_mn_major ? 1 : 0; p.b_mn_major = b_mn_major ? 1 : 0;
-  p.out_f32 = out_f32 ? 1 : 0; p.accumulate = accumulate ? 1 : 0;
-  p.group_m = raster_group_m();
-  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
-  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
-  p.ldr = ldr;
-  p.alpha = alpha;
+  p.group_m = gemmcore::raster_group_m();
+  p.epi = epi;
   p.status = b200::status_ptr();
   if (BN == 256) return launch<256>(tmA, tmB, tmD, p, (cudaStream_t)stream);
   return launch<128>(tmA, tmB, tmD, p, (cudaStream_t)stream);

@@ -3,30 +3,39 @@
 //   D[M,N] (=|+=) alpha * (A_q * 2^sfa)[M,K] * (B_q * 2^sfb)[N,K]^T (+ bias[N]) (+ residual[M,N])
 //
 // A_q / B_q are e4m3 codes, K-major; sfa / sfb hold one UE8M0 scale per 32 contraction elements in
-// the atom layout written by quant_mxfp8.cu (tile rows = 128 for A, = BN for B).  Per 128-wide
-// K stage the TMA producer brings the two code tiles (128B-swizzled) and the scale atoms (plain
-// bulk copies); the MMA warp forwards the atoms to TMEM with tcgen05.cp and issues four
-// tcgen05.mma.kind::mxf8f6f4.block_scale of K = 32, selecting the scale byte through the
-// instruction descriptor.  Accumulators are double buffered in TMEM; BN = 224 keeps
-// 2 x 224 accumulator columns + the scale columns inside the 512-column TMEM.
+// the atom layout written by quant_mxfp8.cu (tile rows = 128 for A, = BN for B; BN = 208 for N > 128).
 //
-// Roles and epilogue are those of gemm_bf16.cu (warp 0 TMA, warp 1 MMA, warps 2-5 epilogue).
+// Two kernels share that contract:
+//   * problems taller than 128 rows run gemmcore::gemm_pair_kernel (gemm_core.cuh): CTA pairs on
+//     256 x 208 tiles with tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale, two 128-byte K blocks
+//     per pipeline stage, scales written to TMEM by four forwarding warps (tcgen05.st), one
+//     tcgen05.commit per stage;
+//   * M <= 128 runs the one-CTA kernel of this file: per 128-wide K stage the TMA producer brings the
+//     two code tiles (128B-swizzled) and the scale atoms (plain bulk copies), the MMA warp forwards
+//     the atoms to TMEM with tcgen05.cp and issues four MMAs of K = 32, selecting the scale byte
+//     through the instruction descriptor.
+// Accumulators are double buffered in TMEM; BN = 208 keeps 2 x 208 accumulator columns + the scale
+// sets inside the 512 columns.
+//
 // Replaces the reference's block-scaled GEMM providers: Primus-Turbo FlyDSL / AITER a4w4 kernels
 // (llama2_sft/primus/a4w4_tuned_gemms.csv) and the in-tree scaled-MFMA GEMMs
 // (generative_recommenders/ops/hip/k512_mx6_gemm.cu) at MXFP8 precision.
 #include <cstdlib>
 
 #include "common.cuh"
+#include "gemm_core.cuh"
 #include "runtime.h"
 
 namespace {
 
+using gemmcore::tile_coords;
+
 constexpr int BM = 128;
 constexpr int BK = 128;           // 128 e4m3 = 128 bytes = one swizzle row = 4 scale columns
 constexpr int UMMA_K = 32;
-constexpr int NUM_THREADS = 192;
-constexpr int EPI_WARPS = 4;
-constexpr int STG_BYTES = 4096;
+constexpr int NUM_THREADS = gemmcore::NUM_THREADS;
+constexpr int EPI_WARPS = gemmcore::EPI_WARPS;
+constexpr int STG_BYTES = gemmcore::STG_BYTES;
 
 template <int BN>
 struct Cfg {
@@ -50,25 +59,12 @@ struct Cfg {
 
 struct Params {
   int M, N, K;
-  int out_f32, accumulate, group_m;
+  int group_m;
   const uint8_t* sfa;
   const uint8_t* sfb;
-  const __nv_bfloat16* bias;
-  const __nv_bfloat16* residual;
-  long long ldr;
-  float alpha;
+  gemmcore::EpiArgs epi;
   int* status;
 };
-
-B200_DEVICE void tile_coords(int t, int num_m, int num_n, int group_m, int& mb, int& nb) {
-  int in_group = group_m * num_n;
-  int g = t / in_group;
-  int first_m = g * group_m;
-  int gsz = min(num_m - first_m, group_m);
-  int r = t - g * in_group;
-  mb = first_m + (r % gsz);
-  nb = r / gsz;
-}
 
 B200_DEVICE void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -80,7 +76,7 @@ B200_DEVICE void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uin
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const __grid_constant__ CUtensorMap tmD, const Params p) {
+                  const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmDt, const Params p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -185,83 +181,18 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;
-    const int ew = warp - 2;
-    uint8_t* stg = sE + ew * 2 * STG_BYTES;
+    uint8_t* stg = sE + (warp - 2) * 2 * STG_BYTES;
     int buf = 0;
     int it = 0;
     bool ok = true;
-    const bool vec_res = p.residual != nullptr && (p.ldr % 8 == 0) && (p.N % 8 == 0) &&
-                         ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
       int mb, nb; tile_coords(t, num_m, num_n, p.group_m, mb, nb);
-      const int m0 = mb * BM, n0 = nb * BN;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, p.status, 130)) { ok = false; break; }
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + c * 32, r);
-        tc_wait_ld();
-        const int col0 = n0 + c * 32;
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
-        }
-        if (p.residual != nullptr && row < p.M) {
-          const __nv_bfloat16* rp = p.residual + (long long)row * p.ldr + col0;
-          if (vec_res) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (col0 + j * 8 < p.N) {
-                uint4 u = *reinterpret_cast<const uint4*>(rp + j * 8);
-                float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
-                v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
-                v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
-              }
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) v[i] += __bfloat162float(rp[i]);
-          }
-        }
-        if (lane == 0) tma_store_wait_read<1>();
-        __syncwarp();
-        if (p.out_f32) {
-          uint8_t* sb = stg + buf * STG_BYTES + lane * 128;
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(sb + ((j ^ (lane & 7)) << 4)) =
-                make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]),
-                           __float_as_uint(v[4 * j + 3]));
-        } else {
-          // bf16: 32 columns = dense 64-byte rows, 64-byte swizzle (chunk ^= (row / 2) % 4)
-          uint8_t* sb = stg + buf * STG_BYTES + lane * 64;
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<uint4*>(sb + ((j ^ ((lane >> 1) & 3)) << 4)) =
-                make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
-                           pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (col0 < p.N && m0 + q * 32 < p.M) {
-            if (p.accumulate) tma_reduce_add_2d(&tmD, stg + buf * STG_BYTES, col0, m0 + q * 32);
-            else tma_store_2d(&tmD, stg + buf * STG_BYTES, col0, m0 + q * 32);
-          }
-          tma_store_commit();
-        }
-        buf ^= 1;
-      }
+      gemmcore::epilogue_drain<BN, (BN % 64 == 0)>(&tmD, &tmDt, p.epi, t_row, mb * BM + q * 32, nb * BN, stg, buf, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -282,8 +213,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 }
 
 template <int BN>
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const Params& p,
-           cudaStream_t stream) {
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const CUtensorMap& tmDt,
+           const Params& p, cudaStream_t stream) {
   using C = Cfg<BN>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -298,29 +229,17 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
   const int tiles = num_m * num_n;
   const int grid = tiles < b200::sm_count() ? tiles : b200::sm_count();
-  gemm_mxfp8_kernel<BN><<<grid, NUM_THREADS, C::SMEM, stream>>>(tmA, tmB, tmD, p);
+  gemm_mxfp8_kernel<BN><<<grid, NUM_THREADS, C::SMEM, stream>>>(tmA, tmB, tmD, tmDt, p);
   b200::count_launch();
   return b200::check_launch("gemm_mxfp8");
-}
-
-// Height (in tiles) of a raster group: consecutive CTAs work on `group_m` row tiles of one column tile, so the
-// column's B tile is shared in L2 while the group's A rows stay resident (B200_GEMM_GROUP_M overrides).
-static int raster_group_m() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("B200_GEMM_GROUP_M");
-    v = (e && atoi(e) > 0) ? atoi(e) : 16;
-  }
-  return v;
 }
 
 }  // namespace
 
 // N tile the kernel will use for an output width N (the B operand's scales must be laid out with
 // this tile height by the quantiser).
-// 224 columns fill tensor memory (2 x 224 accumulator columns + scale columns <= 512) and give the
-// highest FLOP per byte staged; 128 divides power-of-two widths exactly, which wins when 224-wide tiles
-// leave a mostly empty last wave on the 148 SMs (B200_MXFP8_BN=128|224 forces one choice).
+// 208 columns fill tensor memory (2 x 208 accumulator columns + 6 scale sets of 16 columns = 512);
+// B200_MXFP8_BN=128|208 forces one choice.
 static int pick_bn(int N) {
   if (N <= 128) return 128;
   static int forced = -1;
@@ -328,10 +247,43 @@ static int pick_bn(int N) {
     const char* e = getenv("B200_MXFP8_BN");
     forced = e ? atoi(e) : 0;
   }
-  if (forced == 128 || forced == 224) return forced;
-  return 224;
+  if (forced == 128 || forced == 208) return forced;
+  return 208;
 }
 B200_API int b200_gemm_mxfp8_bn(int N) { return pick_bn(N); }
+
+// One CTA pair per 256 x BN tile (gemm_core.cuh); KSUB = 128-byte K blocks per pipeline stage
+// (B200_MXFP8_KSUB=1|2).
+template <int BN>
+static int run_pair(const void* a_q, const void* sfa, const void* b_q, const void* sfb, void* d, int M, int N, int K,
+                    long long lda, long long ldb, long long ldd, const gemmcore::EpiArgs& epi, cudaStream_t stream) {
+  using namespace gemmcore;
+  CUtensorMap tmA, tmB, tmSFA, tmSFB, tmD;
+  int r;
+  if ((r = b200::make_tmap_2d(&tmA, b200::DT_U8, a_q, K, M, lda, 128, 128, b200::SWZ_128))) return r;
+  if ((r = b200::make_tmap_2d(&tmB, b200::DT_U8, b_q, K, N, ldb, 128, BN / 2, b200::SWZ_128))) return r;
+  // scale atoms (512 bytes) as rows of 128 int32: [row tile][k group] for A, [column tile][k group][atom] for B
+  const int kg = K / 128, atoms = (BN + 127) / 128;
+  const long long a_rows = (long long)((M + 127) / 128) * kg;
+  const long long b_rows = (long long)((N + BN - 1) / BN) * kg * atoms;
+  if ((r = b200::make_tmap_2d(&tmSFA, b200::DT_I32, sfa, 128, a_rows, 512, 128, 1, b200::SWZ_NONE))) return r;
+  if ((r = b200::make_tmap_2d(&tmSFB, b200::DT_I32, sfb, 128, b_rows, 512, 128, atoms, b200::SWZ_NONE))) return r;
+  CUtensorMap tmDt;
+  if ((r = make_out_tmap<BN>(&tmD, &tmDt, d, M, N, ldd, epi.out_f32))) return r;
+  PairParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn_major = 0; p.b_mn_major = 0;
+  p.group_m = raster_group_m() > 1 ? raster_group_m() / 2 : 1;
+  p.epi = epi;
+  p.status = b200::status_ptr();
+  static int ksub = -1;
+  if (ksub < 0) {
+    const char* e = getenv("B200_MXFP8_KSUB");
+    ksub = (e && atoi(e) == 1) ? 1 : 2;
+  }
+  if (ksub == 2) return launch_pair<KIND_MXFP8, BN, 2>(tmA, tmB, tmSFA, tmSFB, tmD, tmDt, p, stream, "gemm_mxfp8(pair)");
+  return launch_pair<KIND_MXFP8, BN, 1>(tmA, tmB, tmSFA, tmSFB, tmD, tmDt, p, stream, "gemm_mxfp8(pair)");
+}
 
 // a_q [M, K] / b_q [N, K] e4m3 (row pitches lda / ldb in bytes), sfa / sfb scale atoms
 // (tile rows 128 for A, b200_gemm_mxfp8_bn(N) for B).  K must be a multiple of 128.
@@ -341,24 +293,30 @@ B200_API int b200_gemm_mxfp8(const void* a_q, const void* sfa, const void* b_q, 
   if (M <= 0 || N <= 0 || K <= 0) return b200::fail(810, "gemm_mxfp8: empty problem %d x %d x %d", M, N, K);
   if (K % BK != 0) return b200::fail(811, "gemm_mxfp8: K=%d must be a multiple of %d", K, BK);
   const int BN = pick_bn(N);
-  CUtensorMap tmA, tmB, tmD;
+  gemmcore::EpiArgs epi;
+  epi.M = M; epi.N = N;
+  epi.out_f32 = out_f32 ? 1 : 0; epi.accumulate = accumulate ? 1 : 0;
+  epi.bias = (const __nv_bfloat16*)bias;
+  epi.residual = (const __nv_bfloat16*)residual;
+  epi.ldr = ldr;
+  epi.alpha = alpha;
+  if (M > 128 && gemmcore::pair_enabled()) {
+    if (BN == 208) return run_pair<208>(a_q, sfa, b_q, sfb, d, M, N, K, lda, ldb, ldd, epi, (cudaStream_t)stream);
+    return run_pair<128>(a_q, sfa, b_q, sfb, d, M, N, K, lda, ldb, ldd, epi, (cudaStream_t)stream);
+  }
+  CUtensorMap tmA, tmB, tmD, tmDt;
   int r;
   if ((r = b200::make_tmap_2d(&tmA, b200::DT_U8, a_q, K, M, lda, BK, BM, b200::SWZ_128))) return r;
   if ((r = b200::make_tmap_2d(&tmB, b200::DT_U8, b_q, K, N, ldb, BK, BN, b200::SWZ_128))) return r;
-  // output leaves 32 columns at a time: fp32 boxes have 128-byte rows, bf16 boxes 64-byte rows
-  if (out_f32) r = b200::make_tmap_2d(&tmD, b200::DT_F32, d, N, M, ldd * 4, 32, 32, b200::SWZ_128);
-  else r = b200::make_tmap_2d(&tmD, b200::DT_BF16, d, N, M, ldd * 2, 32, 32, b200::SWZ_64);
+  r = (BN == 208) ? gemmcore::make_out_tmap<208>(&tmD, &tmDt, d, M, N, ldd, out_f32)
+                  : gemmcore::make_out_tmap<128>(&tmD, &tmDt, d, M, N, ldd, out_f32);
   if (r) return r;
   Params p;
   p.M = M; p.N = N; p.K = K;
-  p.out_f32 = out_f32 ? 1 : 0; p.accumulate = accumulate ? 1 : 0;
-  p.group_m = raster_group_m();
+  p.group_m = gemmcore::raster_group_m();
   p.sfa = (const uint8_t*)sfa; p.sfb = (const uint8_t*)sfb;
-  p.bias = (const __nv_bfloat16*)bias;
-  p.residual = (const __nv_bfloat16*)residual;
-  p.ldr = ldr;
-  p.alpha = alpha;
+  p.epi = epi;
   p.status = b200::status_ptr();
-  if (BN == 224) return launch<224>(tmA, tmB, tmD, p, (cudaStream_t)stream);
-  return launch<128>(tmA, tmB, tmD, p, (cudaStream_t)stream);
+  if (BN == 208) return launch<208>(tmA, tmB, tmD, tmDt, p, (cudaStream_t)stream);
+  return launch<128>(tmA, tmB, tmD, tmDt, p, (cudaStream_t)stream);
 }

@@ -199,8 +199,8 @@ B200_API int b200_quant_mxfp8(const void* x, long long ldx, int R, int C, void* 
                               void* q_col, void* sf_col, int col_tile, void* stream) {
   if (R % 128 != 0 || C % 128 != 0) return b200::fail(700, "quant_mxfp8: R=%d and C=%d must be multiples of 128", R, C);
   if (ldx % 8 != 0 || ((uintptr_t)x & 15) != 0) return b200::fail(701, "quant_mxfp8: input must be 16-byte aligned");
-  if ((q_row && (row_tile % 32 != 0 || row_tile <= 0)) || (q_col && (col_tile % 32 != 0 || col_tile <= 0)))
-    return b200::fail(702, "quant_mxfp8: tile rows must be positive multiples of 32");
+  if ((q_row && (row_tile % 16 != 0 || row_tile <= 0)) || (q_col && (col_tile % 16 != 0 || col_tile <= 0)))
+    return b200::fail(702, "quant_mxfp8: tile rows must be positive multiples of 16");
   dim3 grid(C / 128, R / 128);
   quant_mxfp8_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, R, C, (uint8_t*)q_row,
                                                                (uint8_t*)sf_row, row_tile, (uint8_t*)q_col,

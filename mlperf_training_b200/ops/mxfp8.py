@@ -28,7 +28,7 @@ def b_tile(n_rows: int) -> int:
     """N tile the GEMM uses for a B operand with ``n_rows`` rows (its scale-atom grouping)."""
     if _lib.LIB_PATH.exists():
         return int(_lib.load().b200_gemm_mxfp8_bn(int(n_rows)))     # the kernel's own rule
-    return 224 if n_rows > 128 else 128
+    return 208 if n_rows > 128 else 128
 
 
 @dataclass

@@ -99,8 +99,21 @@ def bench_mxfp8(quick: bool) -> None:
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         ms = time_ms(lambda: mxfp8.gemm(a_op, b_op, out=out))
         fl = 2.0 * M * N * K
+        lib = {}
+        try:
+            # the library's block-scaled GEMM on the same codes (cuBLASLt through torch._scaled_mm, unit scales:
+            # a timing reference only)
+            e8 = torch.float8_e8m0fnu
+            sa = torch.full((M * (K // 32),), 127, dtype=torch.uint8, device="cuda").view(e8)
+            sb = torch.full((N * (K // 32),), 127, dtype=torch.uint8, device="cuda").view(e8)
+            qa, qb = a_op.q.view(torch.float8_e4m3fn), b_op.q.view(torch.float8_e4m3fn)
+            f = lambda: torch._scaled_mm(qa, qb.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+            ms_l = time_ms(f)
+            lib = {"cublaslt_mx_ms": round(ms_l, 4), "cublaslt_mx_tflops": round(fl / ms_l / 1e9, 1)}
+        except Exception as e:  # this torch build has no MX scaled_mm for the shape
+            lib = {"cublaslt_mx_error": str(e)[:100]}
         emit(kernel="gemm_mxfp8", tag=tag, M=M, N=N, K=K, ms=round(ms, 4), tflops=round(fl / ms / 1e9, 1),
-             quant_dual_ms=round(ms_q, 4), quant_gbs=round(M * K * 4.06 / ms_q / 1e6, 1))
+             quant_dual_ms=round(ms_q, 4), quant_gbs=round(M * K * 4.06 / ms_q / 1e6, 1), **lib)
         _lib.check_status(tag)
         del a, b, out, a_op, b_op
 
