@@ -23,9 +23,14 @@
 // that overlap in time on different streams of one device race on it.  Issue all calls for a
 // device on one stream, or order the streams with events.
 //
-// Limit: n <= B200_SUMSQ_STATIC_MAX_ELEMS.  Each slot then accumulates at most 2^22 squares in
-// fp32 before the fixed-order final reduction, which bounds the rounding error; a larger n is
-// rejected with a non-zero return code and a message in b200_last_error().
+// Limit: n <= B200_SUMSQ_STATIC_MAX_ELEMS.  The first pass runs min(4 x SM count,
+// B200_SUMSQ_STATIC_SLOTS) CTAs (592 on a 148-SM part) and each slot accumulates ceil(n / CTAs)
+// squares in fp32 - at most about 2^22.9 at the largest n - before the fixed-order final reduction,
+// which bounds the rounding error; a larger n is rejected with a non-zero return code and a message
+// in b200_last_error().
+//
+// The stream must belong to the device that is current at the call: the scratch pointer is the
+// current device's, and a stream of another device is not detected here.
 #pragma once
 
 #define B200_SUMSQ_STATIC_SLOTS 1024

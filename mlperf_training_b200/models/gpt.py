@@ -323,7 +323,7 @@ class GPT(nn.Module):
     @torch.no_grad()
     def reset_parameters(self, seed: int = 0) -> None:
         """N(0, init_std) for matrices (output projections scaled by 1/sqrt(2 L) as Megatron
-        does), ones for norm weights, zeros for sinks and LoRA B."""
+        does), ones for norm weights, zeros for sinks and LoRA B, seeded Xavier-uniform LoRA A."""
         gen = torch.Generator(device="cpu").manual_seed(seed)
         std = self.cfg.init_std
         out_std = std / math.sqrt(2.0 * self.cfg.n_layers)
@@ -331,6 +331,19 @@ class GPT(nn.Module):
             if p.dim() < 2:
                 continue
             if "lora" in name:
+                # adapters: B zero, A Xavier-uniform over the unsharded shape, from a generator of its own
+                # (seeded by the parameter's name) so that every replica draws the same A whatever the
+                # process-wide RNG state is, and the base weights do not depend on the adapters' presence
+                if name.endswith(".b"):
+                    p.zero_()
+                    continue
+                shard = getattr(p, "tensor_parallel", None)
+                W_, r_ = (shard[1], shard[2]) if shard is not None else (1, 0)
+                full_in = p.shape[1] * W_
+                bound = math.sqrt(6.0 / (full_in + p.shape[0]))
+                g = torch.Generator(device="cpu").manual_seed(seed + 7919 + (zlib.crc32(name.encode()) & 0xFFFFFF))
+                full = torch.empty((p.shape[0], full_in), dtype=torch.float32).uniform_(-bound, bound, generator=g)
+                p.copy_((full.chunk(W_, 1)[r_] if W_ > 1 else full).to(p.dtype))
                 continue
             s = out_std if (name.endswith("w_proj") or name.endswith("w_down") or name.endswith("w2")) else std
             shard = getattr(p, "tensor_parallel", None)

@@ -146,7 +146,8 @@ class ZeroEngine:
     def __init__(self, model: nn.Module, opt: OptimConfig, *, group: dist.ProcessGroup | None = None,
                  bucket_of: Callable[[str], str] = default_bucket_of, comm: str = "nccl",
                  trainable_only: bool = True, tp_group: dist.ProcessGroup | None = None,
-                 pp_group: dist.ProcessGroup | None = None, replicate_group: dist.ProcessGroup | None = None):
+                 pp_group: dist.ProcessGroup | None = None, replicate_group: dist.ProcessGroup | None = None,
+                 expert_dp_group: dist.ProcessGroup | None = None):
         self.model = model
         self.opt = opt
         self.group = group
@@ -163,6 +164,11 @@ class ZeroEngine:
         # pipeline parallelism: every stage owns different parameters; only the clipping norm is shared
         self.pp_group = pp_group if (pp_group is not None and dist.get_world_size(pp_group) > 1) else None
         self.tp_world = dist.get_world_size(tp_group) if tp_group is not None else 1
+        # expert parallelism over fewer ranks than the world: the ranks of ``expert_dp_group`` hold copies of
+        # the same experts; each copy saw the tokens of its own expert-parallel block only, so the expert
+        # gradients are summed over this group before the 1 / world of the global mean is applied
+        self.edp_group = expert_dp_group if (expert_dp_group is not None and dist.get_world_size(expert_dp_group) > 1) else None
+        self.edp_world = dist.get_world_size(self.edp_group) if self.edp_group is not None else 1
         named = [(n, p) for n, p in model.named_parameters() if (p.requires_grad or not trainable_only)]
         if not named:
             raise ValueError("ZeroEngine: the model has no trainable parameters")
@@ -194,6 +200,13 @@ class ZeroEngine:
         self.step_count = 0
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=device)
         self.sumsq_tp = torch.zeros(1, dtype=torch.float32, device=device)
+        self.sumsq_ep = torch.zeros(1, dtype=torch.float32, device=device)
+        if self.edp_group is not None:
+            # the copies of an expert start from the same values
+            src = dist.get_global_rank(self.edp_group, 0)
+            for b in self.buckets:
+                if b.local_only:
+                    dist.broadcast(b.param_buf, src=src, group=self.edp_group)
         self.last_grad_norm = None
         # gradient reduce-scatter overlapped with the last micro-batch's backward: a bucket is reduced on
         # a side stream as soon as its block's gradients are complete (``on_block_grads_ready``)
@@ -222,8 +235,11 @@ class ZeroEngine:
         if self.world == 1:
             return
         if getattr(b, "local_only", False):
-            # gradients of local experts already contain every rank's contribution (they arrived
-            # through the backward all-to-all); only the 1/world of the global mean is missing
+            # gradients of local experts already contain the contribution of every rank of the expert-
+            # parallel block (they arrived through the backward all-to-all); the other blocks' copies of the
+            # same experts add theirs, then only the 1/world of the global mean is missing
+            if self.edp_group is not None:
+                dist.all_reduce(b.grad_buf, group=self.edp_group)
             b.grad_buf.mul_(1.0 / self.world)
             return
         if dist.get_backend(self.group) == "gloo":
@@ -311,12 +327,15 @@ class ZeroEngine:
         if fused:
             fused[0].symm_grad.barrier()          # every rank's gradients are final
         clip = o.clip_grad > 0
-        first = True
+        first = first_ep = True
         for b in order:
             if b.symm_grad is None:
                 if id(b) not in early:
                     self._reduce_scatter(b)
-                if clip:
+                if clip and b.local_only and self.edp_group is not None:
+                    K.sumsq(b.g_shard(), self.sumsq_ep, accumulate=not first_ep)
+                    first_ep = False
+                elif clip:
                     K.sumsq(b.g_shard(), self.sumsq, accumulate=not first)
                     first = False
                 continue
@@ -327,6 +346,8 @@ class ZeroEngine:
                 self.sumsq.copy_(part.view(1) if first else self.sumsq + part)
                 first = False
         if clip:
+            if not first_ep:
+                self.sumsq.add_(self.sumsq_ep / self.edp_world)     # every copy of an expert counts once
             dist.all_reduce(self.sumsq, group=self.group)
             self.last_grad_norm = self.sumsq
         for b in order:
@@ -381,15 +402,20 @@ class ZeroEngine:
             self._reduce_scatter(b)
         clip = o.clip_grad > 0
         if clip:
-            first = first_tp = True
+            first = first_tp = first_ep = True
             self.sumsq.zero_()
             for b in order:
                 if self.tp_world > 1 and b.tp_sharded:
                     K.sumsq(b.g_shard(), self.sumsq_tp, accumulate=not first_tp)
                     first_tp = False
+                elif b.local_only and self.edp_group is not None:
+                    K.sumsq(b.g_shard(), self.sumsq_ep, accumulate=not first_ep)
+                    first_ep = False
                 else:
                     K.sumsq(b.g_shard(), self.sumsq, accumulate=not first)
                     first = False
+            if not first_ep:
+                self.sumsq.add_(self.sumsq_ep / self.edp_world)     # every copy of an expert counts once
             if self.world > 1:
                 dist.all_reduce(self.sumsq, group=self.group)
             if self.tp_world > 1 and not first_tp:
@@ -421,13 +447,19 @@ class ZeroEngine:
         """Largest difference of a parameter checksum across data-parallel ranks (0.0 when every
         replica holds the same weights): the cross-replica weight-hash check of the reference's SFT
         loop (llama2_sft/primus/src/llama2_custom.py:1295-1893)."""
-        sums = torch.stack([b.param_buf.double().sum() for b in self.buckets if not getattr(b, "local_only", False)])
         if self.world == 1:
             return 0.0
-        lo, hi = sums.clone(), sums.clone()
-        dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=self.group)
-        dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=self.group)
-        return float((hi - lo).abs().max())
+        spread = 0.0
+        for local, group in ((False, self.group), (True, self.edp_group)):
+            sums = [b.param_buf.double().sum() for b in self.buckets if bool(getattr(b, "local_only", False)) == local]
+            if not sums or (local and group is None):
+                continue                  # expert shards without copies have nothing to be compared with
+            sums = torch.stack(sums)
+            lo, hi = sums.clone(), sums.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
+            spread = max(spread, float((hi - lo).abs().max()))
+        return spread
 
     def grad_norm(self, grad_scale: float = 1.0) -> float:
         """Global gradient norm of the last step (host read)."""

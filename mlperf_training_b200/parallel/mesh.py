@@ -54,7 +54,7 @@ def group_ranks(spec: MeshSpec, world: int) -> dict[str, list[list[int]]]:
     def rank_of(t, c, d, p):
         return ((p * dp + d) * spec.cp + c) * spec.tp + t
 
-    out = {"tp": [], "cp": [], "dp": [], "pp": [], "ep": [], "dp_shard": [], "dp_replicate": [], "dp_cp": []}
+    out = {"tp": [], "cp": [], "dp": [], "pp": [], "ep": [], "edp": [], "dp_shard": [], "dp_replicate": [], "dp_cp": []}
     for p in range(spec.pp):
         for d in range(dp):
             for c in range(spec.cp):
@@ -66,6 +66,9 @@ def group_ranks(spec: MeshSpec, world: int) -> dict[str, list[list[int]]]:
                 out["dp"].append([rank_of(t, c, d, p) for d in range(dp)])
                 for e0 in range(0, dp, spec.ep):
                     out["ep"].append([rank_of(t, c, d, p) for d in range(e0, e0 + spec.ep)])
+                # expert data parallel: the ranks that hold the same experts (same position in their ep block)
+                for e in range(spec.ep):
+                    out["edp"].append([rank_of(t, c, d, p) for d in range(e, dp, spec.ep)])
                 shard = dp // spec.dp_replicate
                 for r in range(spec.dp_replicate):
                     out["dp_shard"].append([rank_of(t, c, d, p) for d in range(r * shard, (r + 1) * shard)])

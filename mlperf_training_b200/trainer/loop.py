@@ -60,6 +60,7 @@ class RunConfig:
     warmup_train_steps: int = 2
     warmup_eval_steps: int = 0
     data: dict = field(default_factory=lambda: {"kind": "synthetic"})
+    eval_data: dict | None = None                       # validation source (same keys as ``data``); synthetic runs may omit it
     checkpoint_dir: str = ""
     checkpoint_every: int = 0
     keep_last: int = 2
@@ -119,6 +120,31 @@ def build_data(spec: dict, cfg: GPTConfig, seed: int):
     if kind == "packed_sft":
         return PackedSFTDataset(spec["path"], cfg.seq_len, spec.get("metadata"))
     raise ValueError(f"unknown data kind '{kind}'")
+
+
+def eval_spec(rc: "RunConfig") -> dict:
+    """The validation data source of a run.  The reference evaluates on a held-out set
+    (``valid_data_path`` c4-validation of the pretraining configs, ``packed_val_data_path`` of the SFT
+    recipe: small_llm_pretraining/primus/README.md:97-101, llama2_sft/primus/src/llama2_custom.py:1521);
+    a synthetic run draws another stream from another seed; a real-data run must name its validation
+    files (``eval_data``, or the shorthands ``valid_prefixes`` / ``valid_path`` inside ``data``), and a
+    run with a convergence target refuses to decide it on training samples."""
+    if rc.eval_data:
+        spec = dict(rc.data)
+        spec.update(rc.eval_data)
+        return spec
+    kind = rc.data.get("kind", "synthetic")
+    spec = dict(rc.data)
+    if kind == "indexed" and rc.data.get("valid_prefixes"):
+        spec["prefixes"], spec["weights"] = list(rc.data["valid_prefixes"]), rc.data.get("valid_weights")
+        return spec
+    if kind == "packed_sft" and rc.data.get("valid_path"):
+        spec["path"], spec["metadata"] = rc.data["valid_path"], rc.data.get("valid_metadata")
+        return spec
+    if kind != "synthetic" and rc.eval_interval and rc.target_eval_loss > 0:
+        raise ValueError(f"data kind '{kind}' with target_eval_loss needs a validation source: set eval_data "
+                         "(or data.valid_prefixes / data.valid_path)")
+    return spec
 
 
 def _dist_info():
@@ -185,7 +211,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         dp_group = mesh.group("dp_shard") if replicate > 1 else mesh.group("dp")
         if cfg.precision != "bf16":
             cfg.precision = "bf16"       # the tensor-parallel linears run the bf16 tcgen05 GEMMs
-    cp_group = ep_group = None
+    cp_group = ep_group = edp_group = None
     ep_size = min(int(rc.expert_parallel), world) if cfg.n_experts else 1
     if ep_size > 1:
         if tp_size > 1 or pp_size > 1 or cp_size > 1 or replicate > 1 or world % ep_size or cfg.n_experts % ep_size:
@@ -195,7 +221,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             ep_group = dist.group.WORLD
         else:
             from ..parallel.mesh import Mesh, MeshSpec
-            ep_group = Mesh(MeshSpec(ep=ep_size)).group("ep")
+            ep_mesh = Mesh(MeshSpec(ep=ep_size))
+            ep_group, edp_group = ep_mesh.group("ep"), ep_mesh.group("edp")
         fused_ep = str(rc.moe_dispatch).lower() == "fused" and str(device).startswith("cuda")
         cfg.ep_comm = "fused" if fused_ep else "nccl"
     if pp_size > 1:
@@ -223,14 +250,14 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     else:
         trainer = PretrainTrainer(cfg, opt, tc, device, group=dp_group, ep_group=ep_group, tp=tp_ctx,
                                   freeze_base=cfg.lora_rank > 0, replicate_group=rep_group, cp_group=cp_group,
-                                  cp_mode=rc.context_parallel_mode)
+                                  cp_mode=rc.context_parallel_mode, expert_dp_group=edp_group)
     if os.environ.get("INIT_CHECKSUM", "0") == "1":
         from ..utils.metrics import model_fingerprint
         digest, _ = model_fingerprint(trainer.model)
         if rank == 0:
             print(f"[init] model fingerprint {digest}", flush=True)
     data = build_data(rc.data, cfg, rc.seed)
-    eval_data = build_data(rc.data, cfg, rc.seed + 7919)
+    eval_data = build_data(eval_spec(rc), cfg, rc.seed + 7919)
 
     def host_batch(ds, i):
         """One step's batch for this data-parallel rank: tokens ``[b, S+1]``, or (tokens, labels)."""
@@ -239,17 +266,21 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             b = (b[:, :-1].contiguous(), ds.labels(b))
         return b
 
-    per_rank_params = pp_size > 1 or ep_size > 1
-    if rc.pretrained_checkpoint and not resuming:
+    # pipeline stages, expert shards and tensor-parallel slices differ per rank: those parameters travel
+    # with the rank's own optimizer shard instead of rank 0's dense file
+    per_rank_params = pp_size > 1 or ep_size > 1 or tp_size > 1
+    if rc.pretrained_checkpoint and (not resuming or cfg.lora_rank > 0):
+        # a LoRA run checkpoints its adapters only (the engine owns the trainable parameters), so a
+        # resumed run needs the frozen base from the pretrained checkpoint again
         from ..checkpoint.megatron import load_torch_dist
         load_torch_dist(trainer.model, rc.pretrained_checkpoint, strict=True)
-    start_step = 0
+    start_step, resumed_evals = 0, 0
     if resuming:
         ck = resume_mgr.load()
         # pipeline stages and expert shards differ per rank: their parameters travel with the rank's optimizer shard
         bufs = ck["optim"].get("stage_param_bufs") if (per_rank_params and ck["optim"] is not None) else ck["dense"]["param_bufs"]
         written_by = int(ck["meta"].get("world", world))
-        if written_by != world and not per_rank_params and tp_size == 1:
+        if written_by != world and not per_rank_params:
             # another number of data-parallel ranks than the writer's: re-cut the sharded optimizer state
             from ..checkpoint.reshard import copy_param_bufs, resharded_optimizer_state
             copy_param_bufs(trainer.engine, bufs)
@@ -265,6 +296,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             trainer.engine.load_optimizer_state(ck["optim"])
         CheckpointManager.restore_rng(ck["rng"])
         start_step = int(ck["meta"]["step"])
+        resumed_evals = int(ck["meta"].get("evals_done", 0))      # the skip-first-evaluations count survives a restart
         trainer.step_idx = start_step
 
     if not resuming:
@@ -305,7 +337,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     timer = ml.ThroughputTimer(rc.global_batch)
     t_run0 = time.perf_counter()
     last_ckpt_t = time.perf_counter()
-    reached, evals_done, last_eval = False, 0, None
+    reached, evals_done, last_eval = False, resumed_evals, None
     losses = []
     prof = None
     step = start_step - 1                               # a run resumed at its last step executes nothing
@@ -387,7 +419,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                                 dense={"param_bufs": [b.param_buf.detach().cpu() for b in trainer.engine.buckets],
                                        "model_config": cfg.to_dict()},
                                 optim_shard=_optim_shard(trainer, per_rank_params),
-                                meta={"samples": samples, "run_started": True, "window": 0, "batch_idx_in_window": -1})
+                                meta={"samples": samples, "run_started": True, "window": 0, "batch_idx_in_window": -1,
+                                      "evals_done": evals_done})
                 last_ckpt_t = time.perf_counter()
         if rc.die_at_step and step + 1 == rc.die_at_step:
             if world > 1:

@@ -42,7 +42,8 @@ class PretrainTrainer:
     sequence, and ``group`` must then span data x context ranks (parameters are replicated over both)."""
 
     def __init__(self, model_cfg: GPTConfig, opt: OptimConfig, train: TrainConfig, device, group=None, ep_group=None,
-                 tp=None, freeze_base: bool = False, replicate_group=None, cp_group=None, cp_mode: str = "allgather"):
+                 tp=None, freeze_base: bool = False, replicate_group=None, cp_group=None, cp_mode: str = "allgather",
+                 expert_dp_group=None):
         self.cfg = model_cfg
         self.train_cfg = train
         self.device = torch.device(device)
@@ -52,7 +53,8 @@ class PretrainTrainer:
             from ..models.lora import freeze_base as _freeze
             _freeze(self.model)
         self.engine = ZeroEngine(self.model, opt, group=group, comm=train.comm,
-                                 tp_group=self.tp.group if self.tp is not None else None, replicate_group=replicate_group)
+                                 tp_group=self.tp.group if self.tp is not None else None, replicate_group=replicate_group,
+                                 expert_dp_group=expert_dp_group)
         self.cp_group = cp_group if (cp_group is not None and dist.get_world_size(cp_group) > 1) else None
         self.cp_world = dist.get_world_size(self.cp_group) if self.cp_group is not None else 1
         self.cp_rank = dist.get_rank(self.cp_group) if self.cp_group is not None else 0

@@ -150,3 +150,15 @@ def test_run_loop_with_expert_parallel_resumes_gloo(tmp_path):
                        env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "RESULT rank 0 ok=True" in r.stdout and "RESULT rank 1 ok=True" in r.stdout
+
+
+def test_tensor_parallel_checkpoints_round_trip_and_runs_resume_gloo(tmp_path):
+    """Megatron torch_dist files written under tensor parallelism hold unsharded tensors; a resumed
+    tensor-parallel run restores every rank's own slices; a resumed LoRA run reloads its frozen base."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29717",
+                        os.path.join(ROOT, "tests", "multi", "tp_resume_worker.py"), str(tmp_path)],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "RESULT rank 0 ok=True" in r.stdout and "RESULT rank 1 ok=True" in r.stdout

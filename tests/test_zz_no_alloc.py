@@ -43,6 +43,24 @@ def test_static_scratch_sumsq_matches_regular_entry_twice():
     _lib.check_status("sumsq_static")
 
 
+def test_static_scratch_sumsq_call_path_allocates_nothing():
+    """After the set-up call, a call changes neither torch's allocator figures nor the driver's count
+    of free device memory: the property that callers without an allocator rely on."""
+    lib, fn = _entry()
+    x = torch.randn(3_000_001, device="cuda")
+    out = torch.zeros(1, device="cuda")
+    stream = _lib.stream_ptr()
+    assert fn(x.data_ptr(), x.numel(), 0, out.data_ptr(), 0, stream) == 0          # set-up call for this device
+    torch.cuda.synchronize()
+    before = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved(), torch.cuda.mem_get_info()[0])
+    for _ in range(3):
+        assert fn(x.data_ptr(), x.numel(), 0, out.data_ptr(), 0, stream) == 0
+    torch.cuda.synchronize()
+    after = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved(), torch.cuda.mem_get_info()[0])
+    assert after == before, (before, after)
+    assert abs(out.item() - (x.double() ** 2).sum().item()) <= 1e-5 * (x.double() ** 2).sum().item()
+
+
 def test_static_scratch_sumsq_rejects_oversize():
     lib, fn = _entry()
     x = torch.zeros(8, device="cuda")
