@@ -19,8 +19,14 @@ is far larger than L2, which is what keeps timed iterations cold.
 
 ``--impl reference`` would run the unmodified reference; it cannot be installed here (the tree has
 no setup.py / pyproject.toml and its stack is ROCm-only), so that arm prints an ``unavailable``
-line.  ``--impl baseline`` runs the same step with stock PyTorch modules (cuBLAS, SDPA, fused
-torch AdamW, DDP) for comparison on the same box.
+line.  ``--impl baseline`` runs the same step with stock PyTorch modules (cuBLAS / cuBLASLt, SDPA,
+fused torch AdamW, DDP or FSDP2) for comparison on the same box.
+
+Because the reference publishes no throughput number and cannot run here, the package's own arm also
+times the stock arms in the same invocation (same N, same shapes, a few steps each, after its own
+model has been freed) and reports ``stock``: the library stack at bf16 and at the same MXFP8
+precision (``torch._scaled_mm`` block-scaled GEMMs), with ``ratio`` = own value / stock value.
+``vs_baseline`` is the ratio against the equal-precision stock arm.  ``--stock none`` skips this.
 """
 from __future__ import annotations
 
@@ -54,7 +60,52 @@ def parse():
                     help="data-parallel step: in-kernel NVLink peer loads/stores, or NCCL collectives")
     ap.add_argument("--precision", default="mxfp8", choices=["mxfp8", "bf16"],
                     help="GEMM precision of the linears (attention, norms, residual stream stay bf16)")
+    ap.add_argument("--stock", default="mxfp8,bf16",
+                    help="stock-PyTorch arms timed after the package's own arm: comma list of mxfp8, bf16, or none")
+    ap.add_argument("--stock-steps", type=int, default=5, help="timed steps of each stock arm (3 warm-up steps)")
+    ap.add_argument("--stock-parallel", default="fsdp", choices=["fsdp", "ddp"],
+                    help="data parallelism of the stock arms at N > 1 (FSDP2 fully_shard, or DDP)")
     return ap.parse_args()
+
+
+def time_stock_arm(args, cfg, opt, tc, device, world, rank, precision: str) -> dict:
+    """Device-timed tokens/s of the stock-PyTorch trainer at ``precision`` (same shapes, max over ranks)."""
+    import copy
+
+    import torch
+    import torch.distributed as dist
+
+    from baseline.torch_gpt import BaselineTrainer
+    from mlperf_training_b200.trainer.pretrain import synthetic_tokens
+
+    scfg = copy.copy(cfg)
+    scfg.precision = precision
+    trainer = BaselineTrainer(scfg, opt, tc, device, parallel=args.stock_parallel)
+    K_, W_ = max(args.stock_steps, 1), 3
+    toks = synthetic_tokens(W_ + K_, args.local_batch, cfg.seq_len, cfg.vocab_size, seed=1, rank=rank).to(device)
+    for i in range(W_):
+        trainer.train_step_device(toks[i])
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(K_):
+        last = trainer.train_step_device(toks[W_ + i])
+    ev1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([ev0.elapsed_time(ev1)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0]) / K_
+    loss = float(last)
+    del trainer, toks
+    torch.cuda.empty_cache()
+    return {"value": round(args.local_batch * cfg.seq_len * world / (ms / 1e3), 1), "ms_per_step": round(ms, 2),
+            "steps": K_, "warmup": W_, "loss_last": round(loss, 4),
+            "stack": ("torch._scaled_mm MXFP8 (cuBLASLt block-scaled) linears" if precision == "mxfp8" else "cuBLAS bf16 linears")
+                     + ", SDPA, F.rms_norm, F.cross_entropy, torch AdamW(fused), "
+                     + (("FSDP2 fully_shard" if args.stock_parallel == "fsdp" else "DDP") if world > 1 else "single GPU")}
 
 
 class ClockSampler:
@@ -143,13 +194,14 @@ def main() -> int:
         cfg.n_layers = args.layers; reduced = True
     if args.seq_len:
         cfg.seq_len = args.seq_len; reduced = True
-    cfg.precision = args.precision if args.impl == "b200" else "bf16"
+    cfg.precision = args.precision
     opt = OptimConfig(lr=8e-4, beta1=0.9, beta2=0.95, eps=1e-5, weight_decay=0.1, clip_grad=1.0)
     tc = TrainConfig(micro_batch=args.micro_batch, local_batch=args.local_batch, warmup_steps=64, seed=0, comm=args.comm)
 
     if args.impl == "baseline":
         from baseline.torch_gpt import BaselineTrainer
-        trainer = BaselineTrainer(cfg, opt, tc, device)
+        cfg.precision = args.precision
+        trainer = BaselineTrainer(cfg, opt, tc, device, parallel=args.stock_parallel)
     else:
         trainer = PretrainTrainer(cfg, opt, tc, device)
         trainer.overlap_grad_reduce = not args.no_overlap
@@ -208,6 +260,20 @@ def main() -> int:
 
     if args.impl == "b200":
         _lib.check_status("bench")
+    stock = {}
+    if args.impl == "b200" and args.stock.lower() not in ("", "none"):
+        # free this arm's model, optimizer state and peer-mapped buffers before the stock models are built
+        del trainer
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        for prec in [s.strip() for s in args.stock.split(",") if s.strip()]:
+            try:
+                stock[prec] = time_stock_arm(args, cfg, opt, tc, device, world, rank, prec)
+            except Exception as e:                       # a stock arm that cannot run here must not lose the line
+                stock[prec] = {"error": f"{type(e).__name__}: {str(e)[:160]}"}
+                gc.collect()
+                torch.cuda.empty_cache()
     if rank == 0:
         ms_per_step = dev_ms / K_
         value = tokens_per_step / (ms_per_step / 1e3)
@@ -228,6 +294,15 @@ def main() -> int:
             "model_tflops_per_gpu": round(cfg.flops_per_token() * tokens_per_step / world / (ms_per_step / 1e3) / 1e12, 1),
             "loss_first": round(losses[0], 4) if losses else None, "loss_last": round(losses[-1], 4) if losses else None,
         }
+        for prec, rec in stock.items():
+            if "value" in rec:
+                rec["ratio"] = round(value / rec["value"], 3)
+        if stock:
+            out["stock"] = stock
+            same = stock.get(cfg.precision, {})
+            if "ratio" in same:
+                out["vs_baseline"] = same["ratio"]
+                out["vs_baseline_of"] = f"stock PyTorch arm at {cfg.precision}, same box, same invocation"
         if not args.no_e2e:
             bi = int(host[0].numel() * host[0].element_size())
             out["e2e"] = {"value": round(tokens_per_step * K_ / e2e_s, 1), "unit": "tokens/s",
