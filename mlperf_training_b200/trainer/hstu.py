@@ -327,6 +327,10 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     else:
         log.log_hyperparameters({"global_batch_size": bpg * world, "seed": int(exp.get("seed", 0)),
                                  "opt_base_learning_rate": float(exp.get("dense_lr", 1e-3))})
+        if float(exp.get("alloc_pregrow_gb", 0)) > 0:
+            # map the allocator's segments before the run starts (jagged batches change size every step)
+            from ..utils.alloc import pregrow
+            pregrow(int(float(exp["alloc_pregrow_gb"]) * 2**30), device=tr.device if tr.device.type == "cuda" else None)
         _warmup(tr, int(exp.get("warmup_steps", 0)))
         timeline.mark("warmup")
         if rank == 0 and os.environ.get("STARTUP_TIMELINE", "0") == "1":
@@ -334,6 +338,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             print("[startup] " + json.dumps(timeline.report()), flush=True)
         log.log_init_stop_run_start()
         log.start(ml.BLOCK_START, metadata={"samples_count": 0})
+    from ..utils.alloc import GrowthMonitor
+    growth = GrowthMonitor(tr.device if tr.device.type == "cuda" else None)     # allocator growth after RUN_START is reported
     steps = int(exp.get("train_steps", 10))
     eval_every = int(exp.get("eval_interval_steps", 0))
     # the data-fraction cadence of the benchmark: evaluate every ``eval_every_data_pct`` of the epoch and not before
@@ -407,6 +413,9 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         log.end(ml.BLOCK_STOP, metadata={"samples_count": timer.samples})
     lifetime.sync()
     log.log_run_stop(reached or thr <= 0, samples=timer.samples, duration_s=time.perf_counter() - t0)
+    growth.check(steps)
+    if rank == 0 and os.environ.get("ALLOC_REPORT", "0") == "1":
+        print("[alloc] " + growth.report(), flush=True)
     log.close()
     return {"losses": losses, "aucs": aucs, "lifetime_auc": lifetime.compute(), "throughput": timer.throughput(),
-            "records": log.lines, "trainer": tr}
+            "records": log.lines, "trainer": tr, "alloc_growth": growth.events}

@@ -334,6 +334,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         from ..utils.metrics import PerfLogger
         from ..utils.profiler import gpu_peak_tflops
         perf = PerfLogger(cfg.flops_per_token() * cfg.seq_len, world=world, peak_tflops=gpu_peak_tflops(), jsonl=rc.perf_jsonl)
+    from ..utils.alloc import GrowthMonitor
+    growth = GrowthMonitor(trainer.device if str(trainer.device).startswith("cuda") else None)   # growth after RUN_START
     timer = ml.ThroughputTimer(rc.global_batch)
     t_run0 = time.perf_counter()
     last_ckpt_t = time.perf_counter()
@@ -443,6 +445,9 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     if energy is not None:
         rep = energy.stop()
         log.event(ml.TRACKED_STATS, {"energy_kwh": rep["energy_kwh"], "peak_power_w": rep["peak_w"]}, metadata={"step": step + 1})
+    growth.check(step + 1)
+    if rank == 0 and os.environ.get("ALLOC_REPORT", "0") == "1":
+        print("[alloc] " + growth.report(), flush=True)
     log.close()
     return {"steps": step + 1 - start_step, "losses": losses, "eval_loss": last_eval, "reached": reached,
-            "throughput": timer.throughput(), "records": log.lines, "trainer": trainer}
+            "throughput": timer.throughput(), "records": log.lines, "trainer": trainer, "alloc_growth": growth.events}

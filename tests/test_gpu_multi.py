@@ -1,5 +1,6 @@
 """Multi-GPU tests (need >= 2 GPUs on the box): each case runs a worker script under torchrun."""
 import os
+import socket
 import subprocess
 import sys
 from pathlib import Path
@@ -11,11 +12,17 @@ pytestmark = pytest.mark.gpu
 HERE = Path(__file__).resolve().parent
 
 
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def _run(worker: str, nproc: int = 2, timeout: int = 600, extra_env: dict | None = None, args=()):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-           "--master-addr", "127.0.0.1", "--master-port", "29611", str(HERE / "multi" / worker), *args]
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(HERE / "multi" / worker), *args]
     return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
 
 

@@ -73,7 +73,8 @@ for i in $(seq 1 "${NEXP}"); do
   export SEED=$((ROOT_SEED + i - 1))
   LOG="${LOGDIR}/${DATESTAMP}_${i}.log"
   echo "Beginning trial ${i} of ${NEXP} (seed ${SEED})"
-  sync && (echo 3 > /proc/sys/vm/drop_caches) 2>/dev/null || true
+  # MLPerf asks for a cold page cache per trial; like the other host settings this is opt-in
+  if [ "${APPLY_HOST_TUNABLES:-0}" = "1" ]; then sync && (echo 3 > /proc/sys/vm/drop_caches) 2>/dev/null || true; fi
   set +e
   run_in bash "${HERE}/run_and_time.sh" 2>&1 | tee "${LOG}"
   rc=${PIPESTATUS[0]}
