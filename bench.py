@@ -60,6 +60,8 @@ def parse():
                     help="data-parallel step: in-kernel NVLink peer loads/stores, or NCCL collectives")
     ap.add_argument("--precision", default="mxfp8", choices=["mxfp8", "bf16"],
                     help="GEMM precision of the linears (attention, norms, residual stream stay bf16)")
+    ap.add_argument("--zero-stage", type=int, default=1, choices=[1, 3],
+                    help="1: optimizer state sharded, parameters replicated; 3: block matrices sharded and gathered per block")
     ap.add_argument("--stock", default="mxfp8,bf16",
                     help="stock-PyTorch arms timed after the package's own arm: comma list of mxfp8, bf16, or none")
     ap.add_argument("--stock-steps", type=int, default=5, help="timed steps of each stock arm (3 warm-up steps)")
@@ -196,7 +198,8 @@ def main() -> int:
         cfg.seq_len = args.seq_len; reduced = True
     cfg.precision = args.precision
     opt = OptimConfig(lr=8e-4, beta1=0.9, beta2=0.95, eps=1e-5, weight_decay=0.1, clip_grad=1.0)
-    tc = TrainConfig(micro_batch=args.micro_batch, local_batch=args.local_batch, warmup_steps=64, seed=0, comm=args.comm)
+    tc = TrainConfig(micro_batch=args.micro_batch, local_batch=args.local_batch, warmup_steps=64, seed=0, comm=args.comm,
+                     zero_stage=args.zero_stage)
 
     if args.impl == "baseline":
         from baseline.torch_gpt import BaselineTrainer
@@ -206,6 +209,11 @@ def main() -> int:
         trainer = PretrainTrainer(cfg, opt, tc, device)
         trainer.overlap_grad_reduce = not args.no_overlap
 
+    nvls = False
+    if args.impl == "b200":
+        eng = trainer.engine
+        nvls = bool(getattr(eng, "nvls", False)) or any(eng._nvls(getattr(b, "symm_grad", None)) for b in eng.buckets)
+        state_gb = round(eng.state_bytes() / 2**30, 2)
     K_, W_ = args.steps, args.warmup
     tokens_per_step = args.local_batch * cfg.seq_len * world
     host = synthetic_tokens(W_ + 2 * K_, args.local_batch, cfg.seq_len, cfg.vocab_size, seed=0, rank=rank)
@@ -286,11 +294,12 @@ def main() -> int:
             "impl": args.impl,
             "config": {"model": cfg.name, "layers": cfg.n_layers, "global_batch": args.local_batch * world,
                        "seq_len": cfg.seq_len, "micro_batch": args.micro_batch,
-                       "parallelism": f"dp{world} (ZeRO-sharded optimizer, {args.comm if world > 1 else 'single GPU'} step"
+                       "parallelism": f"dp{world} (ZeRO-{args.zero_stage}, {args.comm if world > 1 else 'single GPU'} step"
+                                      + (", NVLS multimem" if nvls else "")
                                       + (", reduce-scatter overlapped with backward)" if (world > 1 and not args.no_overlap) else ")"),
                        "l2": "no flush: per-step working set (>48 GB of weights and gradients) exceeds L2",
                        "reduced": reduced},
-            "clocks": clocks, "gpu_launches": int(launches),
+            "clocks": clocks, "gpu_launches": int(launches), "engine_state_gb_per_gpu": state_gb if args.impl == "b200" else None,
             "model_tflops_per_gpu": round(cfg.flops_per_token() * tokens_per_step / world / (ms_per_step / 1e3) / 1e12, 1),
             "loss_first": round(losses[0], 4) if losses else None, "loss_last": round(losses[-1], 4) if losses else None,
         }

@@ -318,6 +318,9 @@ class GPT(nn.Module):
         self.cp = None
         # optional callable(block_key): told when the backward of a block has produced all its gradients
         self.grad_ready_hook = None
+        # optional object with pre_forward(i) / pre_backward(i) / post_backward(i): a sharded-parameter engine
+        # gathers a block's matrices before the block runs and reduces its gradients right after its backward
+        self.block_hooks = None
         self.reset_parameters(seed)
 
     @torch.no_grad()
@@ -418,10 +421,22 @@ class GPT(nn.Module):
         ckpt = self.cfg.recompute == "full" and torch.is_grad_enabled()
         offload = self.cfg.recompute == "offload" and torch.is_grad_enabled()
         notify = self.grad_ready_hook if (torch.is_grad_enabled() and not ckpt) else None
+        hooks = self.block_hooks
+        n_blocks = len(self.blocks)
         for i, blk in enumerate(self.blocks):
             if notify is not None and x.requires_grad:
                 # the gradient w.r.t. a block's input is the last thing its backward produces
                 x.register_hook(lambda g, key=f"block{i:04d}", fn=notify: fn(key))
+            if hooks is not None:
+                if torch.is_grad_enabled() and x.requires_grad:
+                    # boundary between block i - 1 and block i: block i's backward has just finished (its
+                    # gradients can leave), block i - 1's is about to start (its parameters must be there)
+                    def _boundary(g, i=i, h=hooks):
+                        h.post_backward(i)
+                        if i > 0:
+                            h.pre_backward(i - 1)
+                    x.register_hook(_boundary)
+                hooks.pre_forward(i)
             if ckpt and (self.cfg.recompute_layers <= 0 or i < self.cfg.recompute_layers):
                 from torch.utils.checkpoint import checkpoint
                 x = checkpoint(blk, x, cos, sin, B, S, use_reentrant=False)
@@ -431,5 +446,7 @@ class GPT(nn.Module):
                     x = blk(x, cos, sin, B, S)
             else:
                 x = blk(x, cos, sin, B, S)
+        if hooks is not None and torch.is_grad_enabled() and x.requires_grad:
+            x.register_hook(lambda g, h=hooks, i=n_blocks - 1: h.pre_backward(i))
         return F.lm_head_loss(x, self.final_norm, self.lm_head, tgt, eps=self.cfg.norm_eps,
                               n_valid=n_valid, precision=self.cfg.precision)

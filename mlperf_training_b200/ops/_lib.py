@@ -66,6 +66,9 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_gemm_grouped_wgrad": [P, P, P, P, I, I, I, I, L, L, I, I, F, P],
         "b200_zero_reduce_scatter": [P, I, I, L, L, F, P, P, P],
         "b200_zero_adamw_all_gather": [P, I, I, L, L, P, P, P, P, F, F, F, F, F, I, F, P, F, I, P],
+        "b200_zero_reduce_scatter_mc": [P, L, L, F, P, I, P, P],
+        "b200_mc_all_gather": [P, P, L, P],
+        "b200_zero_adamw_all_gather_mc": [P, P, L, P, P, P, P, F, F, F, F, F, I, F, P, F, I, P],
         "b200_hstu_attn_fwd": [P, P, P, P, P, P, I, L, I, I, I, I, L, L, L, L, F, P],
         "b200_hstu_gate_cat_fwd": [P, L, P, P, P, P, P, P, I, I, F, F, ctypes.c_ulonglong, P],
         "b200_hstu_gate_cat_bwd": [P, P, L, P, P, P, P, P, P, L, P, P, P, P, I, I, I, F, ctypes.c_ulonglong, P],

@@ -274,12 +274,24 @@ class ZeroEngine:
             if b.rs_event is None:
                 self._launch_reduce_scatter(b)
 
+    @staticmethod
+    def _nvls(sb) -> bool:
+        """The buffer is bound to an NVLink multicast object and in-switch operations are wanted
+        (``B200_NVLS=0`` keeps the plain peer loads / stores, as the fault tests do)."""
+        import os
+        return sb is not None and sb.multicast_ptr != 0 and os.environ.get("B200_NVLS", "1") != "0"
+
     def _fused_rs(self, b: Bucket, clip: bool) -> None:
         from ..ops import _lib
         if not hasattr(b, "rs_out"):
             grid = _lib.load().b200_zero_grid()
             b.rs_out = torch.empty(b.shard, dtype=torch.float32, device=self.device)
             b.rs_partial = torch.empty(grid, dtype=torch.float32, device=self.device)
+        if self._nvls(b.symm_grad):
+            # one multimem.ld_reduce stream through the switch instead of W peer loads per element
+            _lib.call("b200_zero_reduce_scatter_mc", b.symm_grad.multicast_ptr, b.lo, b.shard, 1.0 / self.world,
+                      _lib.ptr(b.rs_out), 0, _lib.ptr(b.rs_partial) if clip else None, _lib.stream_ptr())
+            return
         _lib.call("b200_zero_reduce_scatter", b.symm_grad.ptr_array(), self.world, self.rank, b.lo, b.shard,
                   1.0 / self.world, _lib.ptr(b.rs_out), _lib.ptr(b.rs_partial) if clip else None, _lib.stream_ptr())
 
@@ -367,6 +379,14 @@ class ZeroEngine:
                     self._all_gather(b)
                 continue
             for s, e, wd in b.segments():
+                if self._nvls(b.symm_param) and (e - s) % 8 == 0 and (b.lo + s) % 8 == 0:
+                    es = b.param_buf.element_size()
+                    _lib.call("b200_zero_adamw_all_gather_mc", b.symm_param.multicast_ptr + (b.lo + s) * es,
+                              _lib.ptr(b.param_buf[b.lo + s:b.lo + e]), e - s, _lib.ptr(b.rs_out[s:e]), _lib.ptr(b.m[s:e]),
+                              _lib.ptr(b.v[s:e]), None if b.master is None else _lib.ptr(b.master[s:e]), float(lr), o.beta1,
+                              o.beta2, o.eps, o.weight_decay if wd else 0.0, self.step_count, float(grad_scale),
+                              _lib.ptr(self.sumsq) if clip else None, float(o.clip_grad), 0, _lib.stream_ptr())
+                    continue
                 _lib.call("b200_zero_adamw_all_gather", b.symm_param.ptr_array(), self.world, self.rank, b.lo + s, e - s,
                           _lib.ptr(b.rs_out[s:e]), _lib.ptr(b.m[s:e]), _lib.ptr(b.v[s:e]),
                           None if b.master is None else _lib.ptr(b.master[s:e]), float(lr), o.beta1, o.beta2, o.eps,

@@ -79,6 +79,7 @@ class RunConfig:
     context_parallel_mode: str = "allgather"            # "allgather" (keys / values of earlier chunks) | "ulysses" (head exchange)
     tp_comm_overlap: str = "fused"                      # "fused": in-kernel all-gather / reduce-scatter; "nccl"
     comm: str = "nccl"                                  # optimizer-step collectives: "nccl" | "fused"
+    zero_stage: int = 1                                 # 3: block matrices sharded too (gathered per block, parallel/zero3.py)
     precision_schedule: dict | str | None = None        # ops.recipe.PrecisionSchedule spec (phase switch at a step)
     vanish_at_step: int = 0                             # fault injection: rank ``vanish_rank`` leaves silently before this step
     vanish_rank: int = 1
@@ -240,7 +241,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     opt = OptimConfig(lr=rc.lr, beta1=rc.adam_beta1, beta2=rc.adam_beta2, eps=rc.adam_eps,
                       weight_decay=rc.weight_decay, clip_grad=rc.clip_grad, moment_dtype=_moment_dtype(rc))
     tc = TrainConfig(micro_batch=rc.micro_batch, local_batch=local_batch, warmup_steps=rc.lr_warmup_iters,
-                     decay_steps=rc.lr_decay_iters, min_lr_ratio=rc.min_lr_ratio, seed=rc.seed, comm=rc.comm)
+                     decay_steps=rc.lr_decay_iters, min_lr_ratio=rc.min_lr_ratio, seed=rc.seed, comm=rc.comm,
+                     zero_stage=int(rc.zero_stage))
     if tp_size == 1 and replicate > 1 and world > 1:
         dp_group = mesh.group("dp_shard")
     if pp_size > 1:
@@ -268,7 +270,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
 
     # pipeline stages, expert shards and tensor-parallel slices differ per rank: those parameters travel
     # with the rank's own optimizer shard instead of rank 0's dense file
-    per_rank_params = pp_size > 1 or ep_size > 1 or tp_size > 1
+    per_rank_params = pp_size > 1 or ep_size > 1 or tp_size > 1 or (int(rc.zero_stage) == 3 and world > 1)
     if rc.pretrained_checkpoint and (not resuming or cfg.lora_rank > 0):
         # a LoRA run checkpoints its adapters only (the engine owns the trainable parameters), so a
         # resumed run needs the frozen base from the pretrained checkpoint again

@@ -33,6 +33,7 @@ class TrainConfig:
     min_lr_ratio: float = 0.1
     seed: int = 0
     comm: str = "nccl"
+    zero_stage: int = 1             # 1: optimizer state sharded, parameters replicated; 3: block matrices sharded too
 
 
 class PretrainTrainer:
@@ -52,9 +53,16 @@ class PretrainTrainer:
         if freeze_base:
             from ..models.lora import freeze_base as _freeze
             _freeze(self.model)
-        self.engine = ZeroEngine(self.model, opt, group=group, comm=train.comm,
-                                 tp_group=self.tp.group if self.tp is not None else None, replicate_group=replicate_group,
-                                 expert_dp_group=expert_dp_group)
+        if int(train.zero_stage) == 3:
+            if self.tp is not None or ep_group is not None or replicate_group is not None or cp_group is not None:
+                raise NotImplementedError("zero_stage 3 shards the block matrices over plain data-parallel ranks "
+                                          "(no tensor / expert / context parallelism, no hybrid sharding)")
+            from ..parallel.zero3 import Zero3Engine
+            self.engine = Zero3Engine(self.model, opt, group=group, comm=train.comm)
+        else:
+            self.engine = ZeroEngine(self.model, opt, group=group, comm=train.comm,
+                                     tp_group=self.tp.group if self.tp is not None else None, replicate_group=replicate_group,
+                                     expert_dp_group=expert_dp_group)
         self.cp_group = cp_group if (cp_group is not None and dist.get_world_size(cp_group) > 1) else None
         self.cp_world = dist.get_world_size(self.cp_group) if self.cp_group is not None else 1
         self.cp_rank = dist.get_rank(self.cp_group) if self.cp_group is not None else 0

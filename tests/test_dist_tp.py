@@ -162,3 +162,15 @@ def test_tensor_parallel_checkpoints_round_trip_and_runs_resume_gloo(tmp_path):
                        env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "RESULT rank 0 ok=True" in r.stdout and "RESULT rank 1 ok=True" in r.stdout
+
+
+def test_sharded_parameter_engine_matches_replicated_engine_gloo():
+    """ZeRO-3: block matrices live as shards, are gathered per block into rotating windows and their
+    gradients are reduced per block; losses and parameters follow the replicated-parameter engine."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29733",
+                        os.path.join(ROOT, "tests", "multi", "zero3_worker.py"), "gloo"],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "RESULT rank 0 ok=True" in r.stdout and "RESULT rank 1 ok=True" in r.stdout

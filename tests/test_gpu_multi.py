@@ -74,3 +74,13 @@ def test_moe_model_expert_parallel_fused_vs_nccl():
     res = _run("moe_ep_worker.py")
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "RESULT rank 0 ok=True" in res.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("comm,precision", [("nccl", "bf16"), ("fused", "mxfp8")])
+def test_sharded_parameter_engine_matches_replicated_engine(comm, precision):
+    """ZeRO-3 over NCCL collectives and over the NVLS kernels (multimem.st gather, multimem.ld_reduce
+    reduce-scatter) against the replicated-parameter engine."""
+    res = _run("zero3_worker.py", args=("nccl", comm, precision), extra_env={"NCCL_NVLS_ENABLE": "1"} if comm == "fused" else None)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "RESULT rank 0 ok=True" in res.stdout
