@@ -520,6 +520,15 @@ B200_DEVICE void tc_mma_f16_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bd
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
       : "memory");
 }
+// e4m3 / e5m2 operands without block scales
+B200_DEVICE void tc_mma_f8_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
 B200_DEVICE void tc_mma_mxf8_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum,
                                      uint32_t sfa_tmem, uint32_t sfb_tmem) {
   asm volatile(

@@ -46,7 +46,7 @@ struct Params {
   int M, N, K;
   int a_mn_major, b_mn_major;
   int group_m;        // raster group height in tiles
-  gemmcore::EpiArgs epi;
+  gemmcore::EpiArgs epi = {};
   int* status;
 };
 
@@ -234,6 +234,7 @@ static int run_pair(const void* a, const void* b, void* d, int M, int N, int K, 
   PairParams p;
   p.M = M; p.N = N; p.K = K;
   p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+  p.a_fmt = 0; p.b_fmt = 0;
   p.group_m = raster_group_m() > 1 ? raster_group_m() / 2 : 1;
   p.epi = epi;
   p.status = b200::status_ptr();
@@ -249,7 +250,7 @@ B200_API int b200_gemm_bf16(const void* a, const void* b, void* d, int M, int N,
                             void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return b200::fail(210, "gemm_bf16: empty problem %d x %d x %d", M, N, K);
   const int BN = (N > 128) ? 256 : 128;
-  gemmcore::EpiArgs epi;
+  gemmcore::EpiArgs epi = {};
   epi.M = M; epi.N = N;
   epi.out_f32 = out_f32 ? 1 : 0; epi.accumulate = accumulate ? 1 : 0;
   epi.bias = reinterpret_cast<const __nv_bfloat16*>(bias);

@@ -41,7 +41,7 @@ constexpr int EPI_WARPS = 4;
 constexpr int STG_BYTES = 4096;   // one epilogue staging buffer (32 rows x 128 bytes)
 constexpr int NUM_THREADS = 192;  // warp 0 TMA, warp 1 MMA + TMEM allocation, warps 2-5 epilogue
 
-enum Kind : int { KIND_BF16 = 0, KIND_MXFP8 = 1 };
+enum Kind : int { KIND_BF16 = 0, KIND_MXFP8 = 1, KIND_FP8 = 2 };   // FP8: e4m3 / e5m2 codes, one factor per tensor
 
 struct EpiArgs {
   int M, N;
@@ -51,6 +51,8 @@ struct EpiArgs {
   const __nv_bfloat16* residual;  // [M, ldr] or null
   long long ldr;
   float alpha;                    // scale applied to the accumulator before bias / residual
+  const float* alpha_a;           // optional device scalars multiplied into alpha (per-tensor dequantisation
+  const float* alpha_b;           // factors of the FP8 operands)
 };
 
 // Grouped raster: consecutive tiles walk `group_m` row tiles of one column tile, so a column's B tile
@@ -88,6 +90,9 @@ B200_DEVICE void epilogue_drain(const CUtensorMap* tmD, const CUtensorMap* tmTai
   static_assert(BN % 16 == 0, "accumulator width must be a multiple of 16 columns");
   static_assert(!WIDE || BN % 64 == 0, "64-column stores need BN to be a multiple of 64");
   const int row = row0 + lane;
+  float alpha = e.alpha;
+  if (e.alpha_a != nullptr) alpha *= *e.alpha_a;
+  if (e.alpha_b != nullptr) alpha *= *e.alpha_b;
   const bool vec_res = e.residual != nullptr && (e.ldr % 8 == 0) && (e.N % 8 == 0) &&
                        ((reinterpret_cast<uintptr_t>(e.residual) & 15) == 0);
 #pragma unroll 1
@@ -98,7 +103,7 @@ B200_DEVICE void epilogue_drain(const CUtensorMap* tmD, const CUtensorMap* tmTai
     const int col0 = n0 + c * 32;
     float v[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * e.alpha;
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
     if (e.bias != nullptr) {
 #pragma unroll
       for (int i = 0; i < 32; ++i)
@@ -200,7 +205,7 @@ B200_DEVICE void epilogue_drain(const CUtensorMap* tmD, const CUtensorMap* tmTai
     const int col0 = n0 + c * 32;
     float v[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]) * e.alpha;
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]) * alpha;
     if (e.bias != nullptr) {
 #pragma unroll
       for (int i = 0; i < 16; ++i)
@@ -309,6 +314,7 @@ struct PairCfg {
 struct PairParams {
   int M, N, K;                    // K in elements (bf16) or bytes (e4m3)
   int a_mn_major, b_mn_major;     // bf16 only
+  int a_fmt, b_fmt;               // FP8 only: 0 = e4m3, 1 = e5m2
   int group_m;
   EpiArgs epi;
   int* status;
@@ -322,7 +328,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                  const PairParams p) {
   using C = PairCfg<KIND, BN, KSUB>;
   constexpr bool MX = C::MX;
-  constexpr int KB_ELEMS = MX ? 128 : 64;         // contraction elements per 128-byte sub-block
+  constexpr bool F8 = (KIND == KIND_FP8);
+  constexpr int KB_ELEMS = (MX || F8) ? 128 : 64; // contraction elements per 128-byte sub-block
   constexpr int UMMA_K_BYTES = 32;                // one MMA consumes 32 bytes of K per row
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -387,32 +394,32 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!mbar_wait_spin(&empty[stage], phase ^ 1, abort_flag, p.status, 310)) { ok = false; break; }
           const uint32_t bar = mapa_u32(smem_u32(&full[stage]), 0);
           if (rank == 0) mbar_expect_tx(&full[stage], 2 * C::AB_STAGE);
-          if (MX) mbar_expect_tx(&sffull[stage], C::SF_STAGE);
+          if (MX) {
+            // scale atoms first (the forwarding warps turn them into TMEM contents while the operand tiles
+            // are still in flight), as rows of 128 int32, the stage's KSUB k groups in one box each
+            // (consecutive k groups of a tile are adjacent in the atom layout): A's atoms of this CTA's 128
+            // rows, B's atoms of the whole N tile (each CTA's tensor core scales all N columns of its rows)
+            mbar_expect_tx(&sffull[stage], C::SF_STAGE);
+            const int kg = kb * KSUB;
+            tma_load_2d(sSFA + stage * KSUB * C::SFA_SUB, &tmSFA, &sffull[stage], 0, (mb * 2 + (int)rank) * num_kb128 + kg);
+            tma_load_2d(sSFB + stage * KSUB * C::SFB_SUB, &tmSFB, &sffull[stage], 0, (nb * num_kb128 + kg) * C::B_ATOMS);
+          }
 #pragma unroll
           for (int s = 0; s < KSUB; ++s) {
             uint8_t* a_dst = sA + (stage * KSUB + s) * C::A_SUB;
             uint8_t* b_dst = sB + (stage * KSUB + s) * C::B_SUB;
             const int k0 = (kb * KSUB + s) * KB_ELEMS;
-            if (MX || !p.a_mn_major) {
+            if (MX || F8 || !p.a_mn_major) {
               tma_load_2d_pair(a_dst, &tmA, bar, k0, m0);
             } else {
 #pragma unroll
               for (int j = 0; j < 2; ++j) tma_load_2d_pair(a_dst + j * 8192, &tmA, bar, m0 + 64 * j, k0);
             }
-            if (MX || !p.b_mn_major) {
+            if (MX || F8 || !p.b_mn_major) {
               tma_load_2d_pair(b_dst, &tmB, bar, k0, n0);
             } else {
 #pragma unroll
               for (int j = 0; j < C::BNH / 64; ++j) tma_load_2d_pair(b_dst + j * 8192, &tmB, bar, n0 + 64 * j, k0);
-            }
-            if (MX) {
-              // scale atoms as rows of 128 int32: A's atom of this CTA's 128 rows, B's atoms of the whole N
-              // tile (each CTA's tensor core scales all N columns of its own 128 rows)
-              const int kg = kb * KSUB + s;
-              tma_load_2d(sSFA + (stage * KSUB + s) * C::SFA_SUB, &tmSFA, &sffull[stage], 0,
-                          (mb * 2 + (int)rank) * num_kb128 + kg);
-              tma_load_2d(sSFB + (stage * KSUB + s) * C::SFB_SUB, &tmSFB, &sffull[stage], 0,
-                          (nb * num_kb128 + kg) * C::B_ATOMS);
             }
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
@@ -423,8 +430,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------ MMA issuer (leader CTA only) ------------------------------
     if (lane == 0 && rank == 0) {
       const uint32_t idesc0 = MX ? umma_idesc_mx(0, 0, 0, 0, 256, BN)
-                                 : umma_idesc(1, 1, p.a_mn_major, p.b_mn_major, 256, BN);
-      const bool a_mn = !MX && p.a_mn_major, b_mn = !MX && p.b_mn_major;
+                              : F8 ? umma_idesc(p.a_fmt, p.b_fmt, 0, 0, 256, BN)
+                                   : umma_idesc(1, 1, p.a_mn_major, p.b_mn_major, 256, BN);
+      const bool a_mn = !MX && !F8 && p.a_mn_major, b_mn = !MX && !F8 && p.b_mn_major;
       const uint32_t a_lbo = a_mn ? 8192 : 16, b_lbo = b_mn ? 8192 : 16;
       // K advance per MMA: 32 bytes along a K-major row, or 16 rows of 128 bytes in an MN-major tile
       const uint32_t a_kstep = a_mn ? 16 * 128 : UMMA_K_BYTES;
@@ -459,6 +467,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               if (MX) {
                 // scale byte kk of every 32-bit scale column: a_sf_id bits [29,31), b_sf_id bits [4,6)
                 tc_mma_mxf8_ss_pair(d_tmem, ad, bd, idesc0 | ((uint32_t)kk << 29) | ((uint32_t)kk << 4), accum, t_sfa, t_sfb);
+              } else if (F8) {
+                tc_mma_f8_ss_pair(d_tmem, ad, bd, idesc0, accum);
               } else {
                 tc_mma_f16_ss_pair(d_tmem, ad, bd, idesc0, accum);
               }

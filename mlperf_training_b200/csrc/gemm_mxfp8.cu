@@ -62,7 +62,7 @@ struct Params {
   int group_m;
   const uint8_t* sfa;
   const uint8_t* sfb;
-  gemmcore::EpiArgs epi;
+  gemmcore::EpiArgs epi = {};
   int* status;
 };
 
@@ -258,6 +258,11 @@ template <int BN>
 static int run_pair(const void* a_q, const void* sfa, const void* b_q, const void* sfb, void* d, int M, int N, int K,
                     long long lda, long long ldb, long long ldd, const gemmcore::EpiArgs& epi, cudaStream_t stream) {
   using namespace gemmcore;
+  static int ksub = -1;
+  if (ksub < 0) {
+    const char* e = getenv("B200_MXFP8_KSUB");
+    ksub = (e && atoi(e) == 1) ? 1 : 2;
+  }
   CUtensorMap tmA, tmB, tmSFA, tmSFB, tmD;
   int r;
   if ((r = b200::make_tmap_2d(&tmA, b200::DT_U8, a_q, K, M, lda, 128, 128, b200::SWZ_128))) return r;
@@ -266,21 +271,17 @@ static int run_pair(const void* a_q, const void* sfa, const void* b_q, const voi
   const int kg = K / 128, atoms = (BN + 127) / 128;
   const long long a_rows = (long long)((M + 127) / 128) * kg;
   const long long b_rows = (long long)((N + BN - 1) / BN) * kg * atoms;
-  if ((r = b200::make_tmap_2d(&tmSFA, b200::DT_I32, sfa, 128, a_rows, 512, 128, 1, b200::SWZ_NONE))) return r;
-  if ((r = b200::make_tmap_2d(&tmSFB, b200::DT_I32, sfb, 128, b_rows, 512, 128, atoms, b200::SWZ_NONE))) return r;
+  if ((r = b200::make_tmap_2d(&tmSFA, b200::DT_I32, sfa, 128, a_rows, 512, 128, ksub, b200::SWZ_NONE))) return r;
+  if ((r = b200::make_tmap_2d(&tmSFB, b200::DT_I32, sfb, 128, b_rows, 512, 128, ksub * atoms, b200::SWZ_NONE))) return r;
   CUtensorMap tmDt;
   if ((r = make_out_tmap<BN>(&tmD, &tmDt, d, M, N, ldd, epi.out_f32))) return r;
   PairParams p;
   p.M = M; p.N = N; p.K = K;
   p.a_mn_major = 0; p.b_mn_major = 0;
+  p.a_fmt = 0; p.b_fmt = 0;
   p.group_m = raster_group_m() > 1 ? raster_group_m() / 2 : 1;
   p.epi = epi;
   p.status = b200::status_ptr();
-  static int ksub = -1;
-  if (ksub < 0) {
-    const char* e = getenv("B200_MXFP8_KSUB");
-    ksub = (e && atoi(e) == 1) ? 1 : 2;
-  }
   if (ksub == 2) return launch_pair<KIND_MXFP8, BN, 2>(tmA, tmB, tmSFA, tmSFB, tmD, tmDt, p, stream, "gemm_mxfp8(pair)");
   return launch_pair<KIND_MXFP8, BN, 1>(tmA, tmB, tmSFA, tmSFB, tmD, tmDt, p, stream, "gemm_mxfp8(pair)");
 }
@@ -293,7 +294,7 @@ B200_API int b200_gemm_mxfp8(const void* a_q, const void* sfa, const void* b_q, 
   if (M <= 0 || N <= 0 || K <= 0) return b200::fail(810, "gemm_mxfp8: empty problem %d x %d x %d", M, N, K);
   if (K % BK != 0) return b200::fail(811, "gemm_mxfp8: K=%d must be a multiple of %d", K, BK);
   const int BN = pick_bn(N);
-  gemmcore::EpiArgs epi;
+  gemmcore::EpiArgs epi = {};
   epi.M = M; epi.N = N;
   epi.out_f32 = out_f32 ? 1 : 0; epi.accumulate = accumulate ? 1 : 0;
   epi.bias = (const __nv_bfloat16*)bias;

@@ -112,7 +112,7 @@ class NormLinearFn(Function):
     @staticmethod
     def forward(ctx, x, norm_w, norm_b, weight, bias, eps, layer_norm, precision):
         xn, _, mean, rstd = K.norm_fwd(x, norm_w, norm_b, eps, layer_norm=layer_norm)
-        keep = precision == "mxfp8" and L.mx_eligible(x.shape[0], weight.shape[0], weight.shape[1])
+        keep = L.low_precision(precision, x.shape[0], weight.shape[0], weight.shape[1])
         y, saved = L.forward(xn, weight, precision, bias=bias, need_wgrad=keep and weight.requires_grad)
         tensors, ctx.meta = L.Saved.pack(saved) if saved is not None else ([], None)
         ctx.save_for_backward(x, norm_w, norm_b, weight, mean, rstd, *tensors)
@@ -415,7 +415,7 @@ class LMHeadLossFn(Function):
     @staticmethod
     def forward(ctx, x, norm_w, weight, labels, eps, loss_mask_count, precision):
         xn, _, _, rstd = K.norm_fwd(x, norm_w, None, eps)
-        keep = precision == "mxfp8" and L.mx_eligible(x.shape[0], weight.shape[0], weight.shape[1])
+        keep = L.low_precision(precision, x.shape[0], weight.shape[0], weight.shape[1])
         logits, saved = L.forward(xn, weight, precision, need_wgrad=keep and weight.requires_grad)
         del xn
         n_valid = loss_mask_count if loss_mask_count is not None else max(int(labels.numel()), 1)

@@ -1,7 +1,10 @@
 """Precision-aware GEMM triple of a linear layer (forward, dgrad, wgrad).
 
 ``precision="bf16"`` runs the bf16 tcgen05 GEMM on the tensors as they are (the backward GEMMs read
-the same row-major buffers as MN-major operands).  ``precision="mxfp8"`` runs the block-scaled
+the same row-major buffers as MN-major operands).  ``precision="fp8"`` runs the per-tensor FP8 GEMM
+(e4m3 activations and weights, e5m2 gradients, delayed scaling: ``ops.fp8``); the scale state of the
+three tensor sites of a linear (input, weight, output gradient) lives on the weight parameter.
+``precision="mxfp8"`` runs the block-scaled
 GEMM: activations and gradients are quantised on the fly (one pass gives the row-wise copy for the
 next GEMM and the transposed column-wise copy that the weight-gradient GEMM needs later), weights
 are quantised once per optimizer step in both directions and cached on the parameter.
@@ -17,6 +20,7 @@ from __future__ import annotations
 
 import torch
 
+from . import fp8 as F8
 from . import kernels as K
 from . import mxfp8 as MX
 
@@ -51,6 +55,34 @@ def weight_operands(weight: torch.Tensor, need_col: bool = True):
     return row, col
 
 
+def _site(weight: torch.Tensor, name: str, fmt: str) -> "F8.DelayedScale":
+    """Delayed-scaling state of one tensor site of the linear that owns ``weight``."""
+    sites = getattr(weight, "_fp8_sites", None)
+    if sites is None:
+        sites = weight._fp8_sites = {}
+    st = sites.get(name)
+    if st is None or st.fmt != fmt:
+        st = sites[name] = F8.DelayedScale(fmt, weight.device)
+    return st
+
+
+def fp8_weight_operands(weight: torch.Tensor, need_col: bool = True):
+    """(w_row, w_col) per-tensor e4m3 copies of ``weight [N, K]`` (``w_col`` is the transposed copy for
+    dgrad), cached until the next optimizer step."""
+    cache = getattr(weight, "_fp8_cache", None)
+    epoch = _WEIGHT_EPOCH if weight.requires_grad else -1
+    if cache is not None and cache[0] == epoch and (cache[2] is not None or not need_col):
+        return cache[1], cache[2]
+    w = weight.detach()
+    if w.dtype != torch.bfloat16 and w.is_cuda:
+        w = w.to(torch.bfloat16)
+    st = _site(weight, "w", "e4m3")
+    st.prepare(w, epoch)
+    row, col = F8.quantize(w, st, want_row=True, want_col=need_col)
+    weight._fp8_cache = (epoch, row, col)
+    return row, col
+
+
 class Saved:
     """The activation copy kept for the weight-gradient GEMM."""
 
@@ -58,13 +90,24 @@ class Saved:
     def pack(obj):
         if isinstance(obj, MX.MXOperand):
             return [obj.q, obj.sf], ("mx", obj.rows, obj.k, obj.tile_rows)
+        if isinstance(obj, F8.FP8Operand):
+            return [obj.q, obj.inv_scale], ("f8", obj.rows, obj.k, obj.fmt)
         return [obj], ("t",)
 
     @staticmethod
     def unpack(tensors, meta):
         if meta[0] == "mx":
             return MX.MXOperand(tensors[0], tensors[1], meta[1], meta[2], meta[3])
+        if meta[0] == "f8":
+            return F8.FP8Operand(tensors[0], tensors[1], meta[1], meta[2], meta[3])
         return tensors[0]
+
+
+def low_precision(precision: str, rows: int, n_out: int, n_in: int) -> bool:
+    """The call runs a quantised GEMM (and saves a quantised activation copy for backward)."""
+    # (the per-tensor FP8 GEMM has CTA-pair tiles only: its M - the tokens in forward and dgrad, the output
+    # features in wgrad - must exceed one 128-row tile)
+    return precision in ("mxfp8", "fp8") and mx_eligible(rows, n_out, n_in) and (precision == "mxfp8" or (rows > 128 and n_out > 128))
 
 
 def forward(x: torch.Tensor, weight: torch.Tensor, precision: str, *, bias=None, residual=None,
@@ -77,6 +120,13 @@ def forward(x: torch.Tensor, weight: torch.Tensor, precision: str, *, bias=None,
         w_row, _ = weight_operands(weight, need_col=False)
         x_row, x_col = MX.quantize(x, row_tile=MX.A_TILE, col_tile=MX.b_tile(Kd) if need_wgrad else None)
         y = MX.gemm(x_row, w_row, bias=bias, residual=residual, out_dtype=x.dtype)
+        return y, x_col
+    if precision == "fp8" and low_precision(precision, M, N, Kd):
+        w_row, _ = fp8_weight_operands(weight, need_col=False)
+        st = _site(weight, "x", "e4m3")
+        st.prepare(x, _WEIGHT_EPOCH)
+        x_row, x_col = F8.quantize(x, st, want_row=True, want_col=need_wgrad)
+        y = F8.gemm(x_row, w_row, bias=bias, residual=residual, out_dtype=x.dtype)
         return y, x_col
     y = K.gemm(x, weight, bias=bias, residual=residual)
     return y, (x if need_wgrad else None)
@@ -106,6 +156,27 @@ def backward(dy: torch.Tensor, saved, weight: torch.Tensor, precision: str, *, n
             else:
                 dw = MX.gemm(dy_col, saved, out_dtype=weight.dtype if weight.dtype != torch.float32 else torch.float32)
         return dx, dw
+    if precision == "fp8" and low_precision(precision, M, N, Kd):
+        if need_dw and not isinstance(saved, F8.FP8Operand):
+            st = _site(weight, "x", "e4m3")
+            st.prepare(saved, _WEIGHT_EPOCH)
+            _, saved = F8.quantize(saved, st, want_row=False, want_col=True)
+        st = _site(weight, "dy", "e5m2")                 # gradients: e5m2 (range over precision)
+        st.prepare(dy, _WEIGHT_EPOCH)
+        dy_row, dy_col = F8.quantize(dy, st, want_row=need_dx, want_col=need_dw)
+        if need_dx:
+            _, w_col = fp8_weight_operands(weight, need_col=True)
+            dx = F8.gemm(dy_row, w_col, out_dtype=dy.dtype)
+        if need_dw:
+            mg = getattr(weight, "main_grad", None)
+            if mg is not None:
+                F8.gemm(dy_col, saved, out=mg, accumulate=True)
+            else:
+                dw = F8.gemm(dy_col, saved, out_dtype=weight.dtype if weight.dtype != torch.float32 else torch.float32)
+        return dx, dw
+    if isinstance(saved, F8.FP8Operand):
+        # the forward ran in fp8 but this backward cannot (a dimension of 128): dequantise the saved copy
+        saved = F8.dequantize(saved).t().contiguous().to(dy.dtype)
     if need_dx:
         dx = K.gemm(dy, weight, b_mn_major=True)
     if need_dw:

@@ -10,12 +10,20 @@ The reference trains with micro-scaled low-precision linears and changes the rec
 * GPT-OSS / FLUX: weight de-oscillation for MXFP4 (start step 768, period 100, ratio 4.0;
   small_llm_moe_pretraining/primus/conf/gpt_oss_20B-MXFP4-deosc-mlperf-pretrain.yaml:197-204).
 
-On B200 the low-precision format of this framework is MXFP8 (e4m3 with one UE8M0 scale per 32
-elements, ``tcgen05.mma.kind::mxf8f6f4.block_scale``).  ``PrecisionSchedule`` keeps the reference's
-surface - named phases with a switch step - and maps every reference format name onto the
-precision the kernels implement; switching a phase changes ``precision`` on the model's modules
-and invalidates the cached quantised weights.  De-oscillation is accepted, recorded, and reported
-as inactive with its reason: it repairs a 4-bit-weight artefact that e4m3 weights do not show.
+This framework implements two low-precision recipes with different numerics:
+
+* ``mxfp8``  e4m3 codes with one UE8M0 scale per 32 contraction elements
+  (``tcgen05.mma.kind::mxf8f6f4.block_scale``; ``ops.mxfp8``) - the micro-scaled family; the
+  reference's 4- and 6-bit micro-scaled names (mxfp4, a6w4, ...) select it, as the widest member
+  this hardware path offers and the one the benchmark definition names;
+* ``fp8``    per-tensor e4m3 forward operands and e5m2 gradients with delayed scaling
+  (``tcgen05.mma.kind::f8f6f4``; ``ops.fp8``) - what the reference calls fp8 / hybrid / delayed.
+
+``PrecisionSchedule`` keeps the reference's surface - named phases with a switch step: switching a
+phase changes ``precision`` on the model's modules and drops the cached quantised weights, and
+because the two recipes round differently the losses after the switch differ from those of a run
+that did not switch.  De-oscillation is accepted, recorded, and reported as inactive with its
+reason: it repairs a 4-bit-weight artefact that e4m3 weights do not show.
 """
 from __future__ import annotations
 
@@ -27,8 +35,8 @@ from .linear import bump_weight_epoch
 # reference recipe names -> precision implemented here
 FORMAT_MAP = {
     "bf16": "bf16", "none": "bf16",
-    "mxfp8": "mxfp8", "fp8": "mxfp8", "fp8_hybrid": "mxfp8", "hybrid": "mxfp8", "e4m3": "mxfp8", "delayed": "mxfp8",
-    "mxfp4": "mxfp8", "e2m1": "mxfp8", "nvfp4": "mxfp8", "a6w4": "mxfp8", "mxfp6": "mxfp8",
+    "mxfp8": "mxfp8", "mxfp4": "mxfp8", "e2m1": "mxfp8", "nvfp4": "mxfp8", "a6w4": "mxfp8", "mxfp6": "mxfp8",
+    "fp8": "fp8", "fp8_hybrid": "fp8", "hybrid": "fp8", "e4m3": "fp8", "delayed": "fp8", "tensorwise": "fp8",
 }
 
 

@@ -25,8 +25,8 @@ def test_precision_schedule_switch_and_mapping(monkeypatch):
                                      "deosc": {"enabled": True, "start_step": 768}})
     assert s.apply(m, 0) and m.precision == "bf16"
     assert not s.apply(m, 4)
-    assert s.apply(m, 5) and m.precision == "mxfp8" and m.sub.precision == "mxfp8"
-    assert s.log == [(0, "bf16"), (5, "mxfp8")]
+    assert s.apply(m, 5) and m.precision == "fp8" and m.sub.precision == "fp8"
+    assert s.log == [(0, "bf16"), (5, "fp8")]
     assert "inactive" in s.deosc.status("mxfp8")
     monkeypatch.setenv("FLUX_FPROP_SWITCH_STEP", "9")
     assert PrecisionSchedule.from_spec({"initial": "a6w4", "switch_step": 5, "final": "bf16"}).phases[1][0] == 9
