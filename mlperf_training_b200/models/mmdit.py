@@ -138,23 +138,19 @@ def _ln(x2d):
     return F.layer_norm(x2d, None, None, 1e-6)
 
 
-def _modulate(x2d, shift, scale, B):
-    """(1 + scale[b]) * x + shift[b] for the tokens of sample b."""
-    S = x2d.shape[0] // B
-    return (x2d.view(B, S, -1) * (1 + scale[:, None]) + shift[:, None]).reshape(x2d.shape)
+def _ln_modulate(x2d, shift, scale, B):
+    """LayerNorm(x) * (1 + scale[b]) + shift[b] for the tokens of sample b: one fused kernel each way."""
+    return F.ln_modulate(x2d, shift, scale, B, 1e-6)
 
 
 def _gate(res2d, y2d, gate, B):
-    S = y2d.shape[0] // B
-    return res2d + (y2d.view(B, S, -1) * gate[:, None]).reshape(y2d.shape)
+    """res + y * gate[b]: one fused kernel forward, the per-sample gate gradient reduced by a kernel."""
+    return F.gate_residual(res2d, y2d, gate, B)
 
 
 def _rope(x, cos, sin):
-    """x ``[B, S, H, D]`` rotate-half with tables ``[S, D/2]`` (autograd through tensor ops)."""
-    half = x.shape[-1] // 2
-    x1, x2 = x[..., :half].float(), x[..., half:].float()
-    c, s = cos[None, :, None, :], sin[None, :, None, :]
-    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
+    """x ``[B, S, H, D]`` rotate-half with the n-D position tables ``[S, D/2]`` (rotary kernel)."""
+    return F.rope_bshd(x, cos, sin)
 
 
 def _attention(q, k, v, sp):
@@ -187,7 +183,7 @@ class DoubleBlock(nn.Module):
         parts = {}
         for s, x in (("img", img), ("txt", txt)):
             mod = getattr(self, f"{s}_mod")(vec_act).chunk(6, dim=-1)
-            qkv = getattr(self, f"{s}_qkv")(_modulate(_ln(x), mod[0], mod[1], B), pr)
+            qkv = getattr(self, f"{s}_qkv")(_ln_modulate(x, mod[0], mod[1], B), pr)
             S = x.shape[0] // B
             q, k, v = qkv.view(B, S, 3, H, hd).unbind(2)
             q, k = getattr(self, f"{s}_qknorm")(q, k)
@@ -202,7 +198,7 @@ class DoubleBlock(nn.Module):
             mod = parts[s][3]
             a2 = a.reshape(-1, H * hd)
             x = _gate(x, getattr(self, f"{s}_proj")(a2, pr), mod[2], B)
-            h = F.gelu(getattr(self, f"{s}_fc1")(_modulate(_ln(x), mod[3], mod[4], B), pr))
+            h = F.gelu(getattr(self, f"{s}_fc1")(_ln_modulate(x, mod[3], mod[4], B), pr))
             outs[s] = _gate(x, getattr(self, f"{s}_fc2")(h, pr), mod[5], B)
         return outs["img"], outs["txt"]
 
@@ -222,7 +218,7 @@ class SingleBlock(nn.Module):
         cfg = self.cfg
         H, hd, d, pr = cfg.n_heads, cfg.head_dim, cfg.hidden, cfg.precision
         shift, scale, gate = self.mod(vec_act).chunk(3, dim=-1)
-        y = self.linear1(_modulate(_ln(x), shift, scale, B), pr)
+        y = self.linear1(_ln_modulate(x, shift, scale, B), pr)
         S = x.shape[0] // B
         qkv, mlp = y[:, :3 * d], y[:, 3 * d:]
         q, k, v = qkv.reshape(B, S, 3, H, hd).unbind(2)
@@ -323,7 +319,7 @@ class MMDiT(nn.Module):
                 x = blk(x, vec_act, cos, sin, B)
         x = x.view(B, St + Si, -1)[:, St:].reshape(-1, cfg.hidden)
         shift, scale = self.final_mod(vec_act).chunk(2, dim=-1)
-        return self.final_out(_modulate(_ln(x), shift, scale, B)).view(B, Si, cfg.in_channels)
+        return self.final_out(_ln_modulate(x, shift, scale, B)).view(B, Si, cfg.in_channels)
 
     def loss(self, latents, txt, pooled, generator=None, prompt_dropout: float = 0.0, empty_txt=None,
              empty_pooled=None):

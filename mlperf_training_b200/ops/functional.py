@@ -16,6 +16,7 @@ from torch.autograd import Function
 
 from . import kernels as K
 from . import linear as L
+from ._lib import call, ptr, stream_ptr, use_kernels
 
 
 def _wgrad(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor):
@@ -457,3 +458,125 @@ def _is_one(t: torch.Tensor) -> bool:
 
 def lm_head_loss(x, norm_w, weight, labels, *, eps=1e-5, n_valid=None, precision="bf16"):
     return LMHeadLossFn.apply(x, norm_w, weight, labels, eps, n_valid, precision)
+
+
+# --------------------------------------------------------------------------------------
+# MMDiT glue: AdaLN modulation, gated residual, rotary embedding on [B, S, H, D]
+# --------------------------------------------------------------------------------------
+def _mod_ok(x2d, *vecs) -> bool:
+    return (use_kernels(x2d) and x2d.dtype == torch.bfloat16 and x2d.shape[1] % 256 == 0 and x2d.shape[1] <= 4096
+            and all(v.dtype == torch.bfloat16 and v.stride(-1) == 1 and v.stride(0) % 8 == 0 and v.data_ptr() % 16 == 0 for v in vecs))
+
+
+class LNModulateFn(Function):
+    """``LayerNorm(x) * (1 + scale[b]) + shift[b]`` (no affine; sample ``b`` owns ``S`` consecutive rows):
+    one kernel forward, one row kernel + one per-sample column reduction backward."""
+
+    @staticmethod
+    def forward(ctx, x, shift, scale, B, eps):
+        T, D = x.shape
+        S = T // B
+        if _mod_ok(x, shift, scale):
+            x = x.contiguous()
+            y = torch.empty_like(x)
+            mean = torch.empty(T, dtype=torch.float32, device=x.device)
+            rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+            call("b200_ln_modulate_fwd", ptr(x), ptr(shift), ptr(scale), shift.stride(0), ptr(y), ptr(mean), ptr(rstd), T, D, S,
+                 float(eps), stream_ptr())
+        else:
+            xf = x.float()
+            mean = xf.mean(-1)
+            rstd = torch.rsqrt(xf.var(-1, unbiased=False) + eps)
+            xh = (xf - mean[:, None]) * rstd[:, None]
+            y = (xh.view(B, S, D) * (1 + scale.float()[:, None]) + shift.float()[:, None]).reshape(T, D).to(x.dtype)
+        ctx.save_for_backward(x, scale, mean, rstd)
+        ctx.cfg = (B, S, shift.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, scale, mean, rstd = ctx.saved_tensors
+        B, S, vdt = ctx.cfg
+        T, D = x.shape
+        dy = dy.contiguous()
+        if _mod_ok(x, scale) and dy.dtype == torch.bfloat16:
+            dx = torch.empty_like(x)
+            dscale = torch.empty(B, D, dtype=torch.float32, device=x.device)
+            dshift = torch.empty(B, D, dtype=torch.float32, device=x.device)
+            call("b200_ln_modulate_bwd", ptr(dy), ptr(x), ptr(scale), scale.stride(0), ptr(mean), ptr(rstd), ptr(dx), ptr(dscale),
+                 ptr(dshift), T, D, S, stream_ptr())
+        else:
+            xh = (x.float() - mean[:, None]) * rstd[:, None]
+            dyf = dy.float()
+            g = (dyf.view(B, S, D) * (1 + scale.float()[:, None])).reshape(T, D)
+            dx = (rstd[:, None] * (g - g.mean(-1, keepdim=True) - xh * (g * xh).mean(-1, keepdim=True))).to(x.dtype)
+            dscale = (dyf * xh).view(B, S, D).sum(1)
+            dshift = dyf.view(B, S, D).sum(1)
+        return dx, dshift.to(vdt), dscale.to(vdt), None, None
+
+
+def ln_modulate(x2d, shift, scale, B, eps=1e-6):
+    return LNModulateFn.apply(x2d, shift, scale, B, eps)
+
+
+class GateResidualFn(Function):
+    """``res + y * gate[b]`` with the per-sample gate gradient reduced by a kernel."""
+
+    @staticmethod
+    def forward(ctx, res, y, gate, B):
+        T, D = y.shape
+        S = T // B
+        if _mod_ok(y, gate) and res.dtype == torch.bfloat16:
+            res, y = res.contiguous(), y.contiguous()
+            out = torch.empty_like(y)
+            call("b200_gate_residual_fwd", ptr(res), ptr(y), ptr(gate), gate.stride(0), ptr(out), T, D, S, stream_ptr())
+        else:
+            out = (res.float() + (y.float().view(B, S, D) * gate.float()[:, None]).reshape(T, D)).to(y.dtype)
+        ctx.save_for_backward(y, gate)
+        ctx.cfg = (B, S)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        y, gate = ctx.saved_tensors
+        B, S = ctx.cfg
+        T, D = y.shape
+        dout = dout.contiguous()
+        if _mod_ok(y, gate) and dout.dtype == torch.bfloat16:
+            dy = torch.empty_like(y)
+            dgate = torch.empty(B, D, dtype=torch.float32, device=y.device)
+            call("b200_gate_residual_bwd", ptr(dout), ptr(y), ptr(gate), gate.stride(0), ptr(dy), ptr(dgate), T, D, S, stream_ptr())
+        else:
+            df = dout.float()
+            dy = (df.view(B, S, D) * gate.float()[:, None]).reshape(T, D).to(y.dtype)
+            dgate = (df * y.float()).view(B, S, D).sum(1)
+        return dout, dy, dgate.to(gate.dtype), None
+
+
+def gate_residual(res2d, y2d, gate, B):
+    return GateResidualFn.apply(res2d, y2d, gate, B)
+
+
+class RopeBSHDFn(Function):
+    """Rotate-half rotary embedding of ``x [B, S, H, D]`` with tables ``[S, D / 2]`` (1-D or n-D positions:
+    the tables carry them); backward is the inverse rotation of the gradient."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        B, S, H, D = x.shape
+        out = x.contiguous().clone()
+        K.rope_(out.view(B * S, H * D), cos, sin, col0=0, n_heads=H, head_dim=D, seq_len=S)
+        ctx.save_for_backward(cos, sin)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        cos, sin = ctx.saved_tensors
+        B, S, H, D = g.shape
+        g = g.contiguous().clone()
+        K.rope_(g.view(B * S, H * D), cos, sin, col0=0, n_heads=H, head_dim=D, seq_len=S, backward=True)
+        return g, None, None
+
+
+def rope_bshd(x, cos, sin):
+    return RopeBSHDFn.apply(x, cos, sin)
