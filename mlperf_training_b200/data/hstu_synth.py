@@ -55,7 +55,7 @@ class HSTUSyntheticData:
         rows_pad = (total + 127) // 128 * 128
         out = {"offsets": torch.from_numpy(offsets), "num_targets": torch.full((self.batch,), self.n_targets, dtype=torch.int32),
                "timestamps": torch.from_numpy(ts), "actions": torch.from_numpy(actions), "item_ids": torch.from_numpy(ids),
-               "total": total, "rows": rows_pad, "lengths": torch.from_numpy(lens)}
+               "total": total, "rows": rows_pad, "lengths": torch.from_numpy(lens), "max_targets": int(self.n_targets)}
         if pin and torch.cuda.is_available():
             out = {k: (v.pin_memory() if torch.is_tensor(v) else v) for k, v in out.items()}
         return out

@@ -53,6 +53,10 @@ class HSTUConfig:
     num_time_buckets: int = 2048
     n_tasks: int = 1
     task_weight_bit: int = 1           # label = (action & bit) > 0
+    # multitask head: ((name, action bit, "binary" | "regression"), ...); empty = one binary task on task_weight_bit
+    tasks: tuple = ()
+    contextual_dim: int = 0            # width of the contextual feature embeddings (0 = emb_dim)
+    extra_features: int = 0            # additional per-token embedding features (artist, album, ...) of width emb_dim
     causal_multitask_weight: float = 0.2
     time_periods: tuple = ((3600.0, 24), (86400.0, 7))   # (period seconds, units): hour of day, day of week
     targets_only_last: bool = True
@@ -184,6 +188,73 @@ class STULayer(nn.Module):
         return F.linear(cat.contiguous(), self.out_weight, None, x, cfg.precision)
 
 
+    def forward_targets_only(self, x, seq, tgt_rows, n_samples: int):
+        """Last-layer form for batches with ONE target per sample: keys and values are computed for every
+        row, queries / gates only for the target rows, and the output has one row per target
+        (generative_recommenders/modules/stu.py:677-798).  A target sees its sample's whole history and
+        itself, so its attention is a per-sample weighted sum over all rows of the sample:
+        ``out[b] = sum_l silu(alpha <q_b, k_l>) / N * v_l``.  Equals ``forward`` followed by the selection
+        of the target rows."""
+        cfg = self.cfg
+        h, hv, hq = cfg.heads, cfg.heads * cfg.d_v, cfg.heads * cfg.d_qk
+        normed = F.layer_norm(x, self.in_norm_w, self.in_norm_b, 1e-6)
+        W, beta = self.uvqk_weight, self.uvqk_beta
+        n_rows = seq.numel()
+        v = F.linear(normed, W[hv:2 * hv], beta[hv:2 * hv], None, cfg.precision)[:n_rows].unflatten(-1, (h, cfg.d_v))
+        k = F.linear(normed, W[2 * hv + hq:], beta[2 * hv + hq:], None, cfg.precision)[:n_rows].unflatten(-1, (h, cfg.d_qk))
+        nt = normed[tgt_rows]
+        # (a handful of target rows: plain matmuls, far below a tensor-core tile)
+        u = TF.silu(nt @ W[:hv].t() + beta[:hv])
+        q = (nt @ W[2 * hv:2 * hv + hq].t() + beta[2 * hv:2 * hv + hq]).unflatten(-1, (h, cfg.d_qk))
+        N = cfg.max_seq_len + cfg.contextual
+        score = (q[seq].float() * k.float()).sum(-1) * (cfg.d_qk ** -0.5)             # [rows, h]
+        p = TF.silu(score) / N
+        attn = torch.zeros((n_samples, h, cfg.d_v), dtype=torch.float32, device=x.device)
+        attn.index_add_(0, seq, p[..., None] * v.float())
+        attn = attn.reshape(n_samples, hv).to(x.dtype)
+        y = u * F.layer_norm(attn, self.out_norm_w, self.out_norm_b, 1e-6)
+        cat = torch.cat([u, attn, y], dim=1)
+        if cfg.linear_dropout > 0 and self.training:
+            cat = TF.dropout(cat, cfg.linear_dropout)
+        return x[tgt_rows] + cat @ self.out_weight.t()
+
+
+class MultitaskHead(nn.Module):
+    """``Linear(D -> D) -> SwishLN -> Linear(D -> n_tasks)`` on ``user * item`` and the per-task losses:
+    binary tasks ``BCEWithLogits * weight``, regression tasks squared error ``* weight``, each summed over
+    the candidates, divided by the clamped weight sum and scaled by ``causal_multitask_weight``
+    (generative_recommenders/modules/multitask_module.py:34-295, head built at dlrm_hstu.py:322-326)."""
+
+    def __init__(self, cfg: HSTUConfig, dtype, device):
+        super().__init__()
+        self.tasks = tuple(cfg.tasks) if cfg.tasks else (("task0", cfg.task_weight_bit, "binary"),)
+        d = cfg.dim
+        self.l1 = _Linear(d, d, dtype, device)
+        self.norm = _LN(d, dtype, device, swish=True)
+        self.l2 = _Linear(d, len(self.tasks), dtype, device)
+        self.scale = cfg.causal_multitask_weight
+
+    def forward(self, user, item, actions, values=None, weights=None):
+        """``actions [T]`` bit masks of the candidates; ``values [T]`` regression targets (watch time ...);
+        ``weights [n_tasks, T]`` supervision weights (default 1).  Returns (losses dict, preds, labels, weights)."""
+        logits = self.l2(self.norm(self.l1(user * item))).float().t()                 # [n_tasks, T]
+        T = logits.shape[1]
+        labels, preds, losses = [], [], {}
+        w = torch.ones_like(logits) if weights is None else weights.float()
+        for i, (name, bit, kind) in enumerate(self.tasks):
+            if kind == "regression":
+                lab = values.float() if values is not None else torch.zeros(T, device=logits.device)
+                per = (logits[i] - lab) ** 2
+                preds.append(logits[i])
+            else:
+                lab = ((actions & int(bit)) > 0).float()
+                per = TF.binary_cross_entropy_with_logits(logits[i], lab, reduction="none")
+                preds.append(torch.sigmoid(logits[i]))
+            labels.append(lab)
+            losses[name] = (per * w[i]).sum() / w[i].sum().clamp(min=1.0) * self.scale
+        return losses, torch.stack(preds).detach(), torch.stack(labels), w
+
+
 class HSTU(nn.Module):
     """``forward(batch, item_emb)`` -> ``(loss, preds, labels)``.
 
@@ -208,10 +279,16 @@ class HSTU(nn.Module):
         n_time = 2 * len(cfg.time_periods)
         self.post_linear = _Linear(d + n_time, d, dt, device)
         self.post_norm = _LN(d, dt, device, eps=1e-5)
-        self.item_mlp = _MLP(cfg.emb_dim, d, d, dt, device)
-        self.head1 = _Linear(d, d, dt, device)
-        self.head_norm = _LN(d, dt, device, swish=True)
-        self.head2 = _Linear(d, cfg.n_tasks, dt, device)
+        self.item_mlp = _MLP(cfg.emb_dim * (1 + cfg.extra_features), d, d, dt, device)
+        self.head = MultitaskHead(cfg, dt, device)
+        # additional-feature branch of the preprocessor: MLP(cat(extra embeddings)) added to the content branch
+        self.extra_mlp = _MLP(cfg.emb_dim * cfg.extra_features, cfg.mlp_hidden, d, dt, device) if cfg.extra_features else None
+        # contextual tokens: one [ctx_dim, D] matrix and bias per contextual feature (a batched linear)
+        if cfg.contextual > 0:
+            cd = cfg.contextual_dim or cfg.emb_dim
+            std = math.sqrt(2.0 / (cd + d))
+            self.ctx_weight = nn.Parameter(torch.empty(cfg.contextual, cd, d, dtype=dt, device=device).normal_(0, std))
+            self.ctx_bias = nn.Parameter(torch.zeros(cfg.contextual, d, dtype=dt, device=device))
 
     # ------------------------------------------------------------------ pieces
     def position_indices(self, offsets, num_targets, total: int):
@@ -242,41 +319,84 @@ class HSTU(nn.Module):
         return torch.stack(feats, dim=-1)
 
     # ------------------------------------------------------------------ forward
-    def forward(self, batch: dict, item_emb: torch.Tensor):
+    def forward(self, batch: dict, item_emb: torch.Tensor, extra_emb: torch.Tensor | None = None,
+                contextual_emb: torch.Tensor | None = None, return_all: bool = False):
+        """``extra_emb [rows, extra_features * emb_dim]``: the additional per-token features;
+        ``contextual_emb [B, contextual, ctx_dim]``: the per-sample contextual features (user id, crosses).
+        ``return_all``: also return the per-task losses, predictions ``[n_tasks, T]``, labels and weights."""
         cfg = self.cfg
         dt = cfg.torch_dtype()
-        offsets, num_targets = batch["offsets"], batch["num_targets"]
-        total = int(batch["total"]) if "total" in batch else int(offsets[-1])   # host-known token count
-        rows = item_emb.shape[0]
-        ts, actions = batch["timestamps"], batch["actions"]
-        seq, col, pos_idx = self.position_indices(offsets, num_targets, total)
-        lens = (offsets[1:] - offsets[:-1]).long()
-        is_target = col >= (lens - num_targets.long())[seq]
+        C = cfg.contextual
+        offsets0, num_targets = batch["offsets"], batch["num_targets"]
+        total0 = int(batch["total"]) if "total" in batch else int(offsets0[-1])   # host-known token count
+        rows0 = item_emb.shape[0]
+        B = offsets0.numel() - 1
+        ts0, actions0 = batch["timestamps"], batch["actions"]
+        dev = offsets0.device
+        lens0 = (offsets0[1:] - offsets0[:-1]).long()
+        seq0 = torch.repeat_interleave(torch.arange(B, device=dev), lens0, output_size=total0)
+        col0 = torch.arange(total0, device=dev) - offsets0[:-1].long()[seq0]
+        is_target0 = col0 >= (lens0 - num_targets.long())[seq0]
 
-        def pad(t):                                     # [L, ...] -> [rows, ...]
+        def pad(t, rows):                               # [L, ...] -> [rows, ...]
             if t.shape[0] == rows:
                 return t
             out = torch.zeros((rows,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
             out[:t.shape[0]] = t
             return out
 
+        # ---- preprocessor: content (+ additional features) + action branches, on the tokens as they came
         x = self.content_mlp(item_emb.to(dt), cfg.precision)
-        x = x + self.action_mlp(pad(self.action_enc(actions, is_target)).to(dt), cfg.precision)
+        if self.extra_mlp is not None:
+            if extra_emb is None:
+                raise ValueError("the model was built with extra_features: pass extra_emb")
+            x = x + self.extra_mlp(extra_emb.to(dt), cfg.precision)
+        x = x + self.action_mlp(pad(self.action_enc(actions0, is_target0), rows0).to(dt), cfg.precision)
+        # ---- contextual tokens in front of every sequence
+        if C > 0:
+            if contextual_emb is None:
+                raise ValueError("the model was built with contextual tokens: pass contextual_emb")
+            ctx = torch.baddbmm(self.ctx_bias[:, None, :].float(), contextual_emb.to(dt).float().transpose(0, 1),
+                                self.ctx_weight.float()).transpose(0, 1).to(dt)              # [B, C, D]
+            offsets = (offsets0.long() + C * torch.arange(B + 1, device=dev)).to(offsets0.dtype)
+            total = total0 + B * C
+            rows = (total + 127) // 128 * 128
+            dst_tok = offsets[:-1].long()[seq0] + C + col0
+            dst_ctx = (offsets[:-1].long()[:, None] + torch.arange(C, device=dev)[None]).reshape(-1)
+            merged = torch.zeros((rows, cfg.dim), dtype=dt, device=dev)
+            merged = merged.index_copy(0, dst_tok, x[:total0]).index_copy(0, dst_ctx, ctx.reshape(B * C, cfg.dim))
+            ts = torch.zeros(total, dtype=ts0.dtype, device=dev).index_copy(0, dst_tok, ts0[:total0])
+            x = merged
+        else:
+            offsets, total, rows, ts = offsets0, total0, rows0, ts0
+        seq, col, pos_idx = self.position_indices(offsets, num_targets, total)
+        lens = (offsets[1:] - offsets[:-1]).long()
+        is_target = col >= (lens - num_targets.long())[seq]
         bucket = self.time_buckets(ts, offsets, seq)
-        x = x * math.sqrt(cfg.dim) + pad(self.pos_emb[pos_idx] + self.ts_emb[bucket]).to(dt)
+        x = x * math.sqrt(cfg.dim) + pad(self.pos_emb[pos_idx] + self.ts_emb[bucket], rows).to(dt)
         if cfg.input_dropout > 0 and self.training:
             x = TF.dropout(x, cfg.input_dropout)
         x = x.contiguous()
-        for layer in self.layers:
+        one_target = int(batch.get("max_targets", 0)) == 1
+        if one_target:
+            # one candidate per sample, known on the host: the candidate is each sequence's last row (no device read)
+            tgt_rows, tgt_rows0 = offsets[1:].long() - 1, offsets0[1:].long() - 1
+        else:
+            tgt_rows = torch.nonzero(is_target, as_tuple=False)[:, 0]
+            tgt_rows0 = torch.nonzero(is_target0, as_tuple=False)[:, 0]
+        last = len(self.layers) - 1
+        for i, layer in enumerate(self.layers):
+            if i == last and cfg.targets_only_last and one_target:
+                user = layer.forward_targets_only(x, seq, tgt_rows, B)       # candidate rows only, no split afterwards
+                break
             x = layer(x, offsets, num_targets, rows)
-        # candidate (target) rows only
-        tgt_rows = torch.nonzero(is_target, as_tuple=False)[:, 0]
-        user = x[tgt_rows]
+        else:
+            user = x[tgt_rows]
         user = self.post_norm(self.post_linear(torch.cat([user, self.time_features(ts[tgt_rows]).to(dt)], dim=1)))
-        item = self.item_mlp(item_emb[tgt_rows].to(dt))
-        logits = self.head2(self.head_norm(self.head1(user * item)))          # [targets, n_tasks]
-        labels = ((actions[tgt_rows] & cfg.task_weight_bit) > 0).float()
-        weights = torch.ones_like(labels)
-        per = TF.binary_cross_entropy_with_logits(logits[:, 0].float(), labels, reduction="none") * weights
-        loss = per.sum() / weights.sum().clamp(min=1.0) * cfg.causal_multitask_weight
-        return loss, torch.sigmoid(logits[:, 0].float()).detach(), labels
+        cand = item_emb[tgt_rows0] if extra_emb is None else torch.cat([item_emb[tgt_rows0], extra_emb[tgt_rows0]], dim=1)
+        item = self.item_mlp(cand.to(dt))
+        losses, preds, labels, weights = self.head(user, item, actions0[tgt_rows0], batch.get("values"), batch.get("weights"))
+        loss = sum(losses.values())
+        if return_all:
+            return loss, losses, preds, labels, weights
+        return loss, preds[0], labels[0]

@@ -1,0 +1,76 @@
+"""HSTU model pieces on CPU (fp32): targets-only last layer, contextual tokens, additional features,
+multitask head."""
+import torch
+
+from mlperf_training_b200.data.hstu_synth import HSTUSyntheticData
+from mlperf_training_b200.models.hstu import HSTU, MultitaskHead, tiny_hstu
+
+
+def _batch(B=5, rows=200, seed=0):
+    d = HSTUSyntheticData(rows, B, length_median=10, length_min=3, length_max=40, seed=seed)
+    return d.batch_at(0)
+
+
+def test_targets_only_last_layer_equals_full_layer_then_split():
+    b = _batch()
+    outs = []
+    for tol in (False, True):
+        cfg = tiny_hstu(targets_only_last=tol, input_dropout=0.0, linear_dropout=0.0)
+        m = HSTU(cfg, "cpu", seed=3)
+        g = torch.Generator().manual_seed(1)
+        emb = torch.randn(b["rows"], cfg.emb_dim, generator=g)
+        emb[b["total"]:] = 0
+        emb.requires_grad_(True)
+        loss, preds, labels = m(b, emb)
+        loss.backward()
+        outs.append((loss.detach(), preds, emb.grad.clone(), m.layers[-1].uvqk_weight.grad.clone()))
+    for a, c in zip(outs[0], outs[1]):
+        assert torch.allclose(a, c, atol=2e-5, rtol=1e-4), (a - c).abs().max()
+    # with several targets per sample the layer falls back to the full form
+    b2 = dict(b, max_targets=2)
+    m = HSTU(tiny_hstu(targets_only_last=True, input_dropout=0.0, linear_dropout=0.0), "cpu", seed=3)
+    assert torch.isfinite(m(b2, emb.detach())[0])
+
+
+def test_contextual_tokens_and_additional_features():
+    b = _batch(B=4)
+    cfg = tiny_hstu(contextual=3, extra_features=2, input_dropout=0.0, linear_dropout=0.0)
+    m = HSTU(cfg, "cpu", seed=2)
+    g = torch.Generator().manual_seed(5)
+    emb = torch.randn(b["rows"], cfg.emb_dim, generator=g)
+    extra = torch.randn(b["rows"], 2 * cfg.emb_dim, generator=g)
+    ctx = torch.randn(4, 3, cfg.emb_dim, generator=g).requires_grad_(True)
+    loss, preds, labels = m(b, emb, extra_emb=extra, contextual_emb=ctx)
+    loss.backward()
+    assert torch.isfinite(loss) and preds.shape == labels.shape == (4,)
+    assert ctx.grad.abs().sum() > 0 and m.ctx_weight.grad.abs().sum() > 0 and m.extra_mlp.l1.weight.grad.abs().sum() > 0
+    # a contextual feature changes the prediction of its own sample only
+    ctx2 = ctx.detach().clone()
+    ctx2[1] += 1.0
+    p2 = m(b, emb, extra_emb=extra, contextual_emb=ctx2)[1]
+    changed = (p2 - preds).abs() > 1e-7
+    assert changed.tolist() == [False, True, False, False]
+    # the targets-only form sees the contextual rows like the full form does
+    m_full = HSTU(tiny_hstu(contextual=3, extra_features=2, input_dropout=0.0, linear_dropout=0.0, targets_only_last=False), "cpu", seed=2)
+    l_full = m_full(b, emb, extra_emb=extra, contextual_emb=ctx.detach())[0]
+    assert torch.allclose(l_full, loss.detach(), atol=2e-5)
+
+
+def test_multitask_head_losses():
+    cfg = tiny_hstu(tasks=(("listen_plus", 1, "binary"), ("like", 2, "binary"), ("watch", 0, "regression")))
+    head = MultitaskHead(cfg, torch.float32, "cpu")
+    T = 7
+    g = torch.Generator().manual_seed(0)
+    user, item = torch.randn(T, cfg.dim, generator=g), torch.randn(T, cfg.dim, generator=g)
+    actions = torch.tensor([0, 1, 2, 3, 4, 5, 6])
+    values = torch.rand(T, generator=g)
+    losses, preds, labels, w = head(user, item, actions, values)
+    assert set(losses) == {"listen_plus", "like", "watch"} and preds.shape == (3, T)
+    assert labels[0].tolist() == [0, 1, 0, 1, 0, 1, 0] and labels[1].tolist() == [0, 0, 1, 1, 0, 0, 1]
+    logits = head.l2(head.norm(head.l1(user * item))).float().t()
+    want = torch.nn.functional.binary_cross_entropy_with_logits(logits[0], labels[0]) * cfg.causal_multitask_weight
+    assert torch.allclose(losses["listen_plus"], want, atol=1e-6)
+    assert torch.allclose(losses["watch"], ((logits[2] - values) ** 2).mean() * 0.2, atol=1e-6)
+    # all-zero supervision weights: the denominator clamps to 1 and the loss is 0
+    zero = head(user, item, actions, values, weights=torch.zeros(3, T))[0]
+    assert all(float(v) == 0.0 for v in zero.values())
