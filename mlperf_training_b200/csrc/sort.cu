@@ -1,0 +1,145 @@
+// Sort / unique / segment machinery of the sparse (embedding) path, all on the device and all
+// deterministic:
+//
+//   sort_ids           stable LSD radix sort of 64-bit ids restricted to the bits the table size needs
+//                      (bounded keys: a 400 M-row table sorts 29 bits, not 64), carrying each id's original
+//                      position as the value;
+//   unique_segments    from the sorted ids: the unique ids, the start of every run of equal ids
+//                      (segment offsets), the number of runs, and for every original position the index of
+//                      its run (the "inverse" of a dedup);
+//   segment_sum_gather rows of a gradient matrix that belong to one run are summed in sorted order -
+//                      fixed order, no atomics - straight from their original places (gather by the sort
+//                      permutation), into fp32 or bf16.
+//
+// The digit passes of the sort and the prefix sums are CUB device primitives (cub::DeviceRadixSort,
+// cub::DeviceScan) run on caller-provided scratch; the head flags, run bookkeeping, inverse map and the
+// reduction are this library's kernels.  Replaces the reference's bounded-key onesweep sort and segment
+// reduction (generative_recommenders/ops/onesweep_sort_kernels.hip:39-110,
+// generative_recommenders/dlrm_v4/train/ec_segment_reduce.py:1-317).
+#include <cub/cub.cuh>
+
+#include "common.cuh"
+#include "runtime.h"
+
+namespace {
+
+__global__ void iota_kernel(long long* __restrict__ p, long long n) {
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n; i += (long long)gridDim.x * 256) p[i] = i;
+}
+
+__global__ void head_flags_kernel(const long long* __restrict__ keys, long long n, int* __restrict__ flags) {
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n; i += (long long)gridDim.x * 256)
+    flags[i] = (i == 0 || keys[i] != keys[i - 1]) ? 1 : 0;
+}
+
+// run[i] = inclusive sum of the head flags = 1-based index of the run of sorted position i
+__global__ void runs_kernel(const long long* __restrict__ keys, const long long* __restrict__ perm,
+                            const int* __restrict__ run, long long n, long long* __restrict__ uniq,
+                            long long* __restrict__ seg_off, long long* __restrict__ inverse, long long* __restrict__ count) {
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
+    const int r = run[i] - 1;
+    if (i == 0 || run[i] != run[i - 1]) { uniq[r] = keys[i]; seg_off[r] = i; }
+    if (inverse != nullptr) inverse[perm[i]] = r;
+    if (i == n - 1) { seg_off[r + 1] = n; *count = r + 1; }
+  }
+}
+
+// out[s, :] = sum over sorted positions r in [seg[s], seg[s + 1]) of src[perm[r], :]; one CTA per run
+template <typename Out>
+__global__ void __launch_bounds__(128)
+segment_sum_gather_kernel(const __nv_bfloat16* __restrict__ src_bf16, const float* __restrict__ src_f32,
+                          const long long* __restrict__ perm, const long long* __restrict__ seg,
+                          const long long* __restrict__ n_seg, int D, Out* __restrict__ out) {
+  const long long total = *n_seg;
+  for (long long s = blockIdx.x; s < total; s += gridDim.x) {
+    const long long lo = seg[s], hi = seg[s + 1];
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      float acc = 0.f;
+      for (long long r = lo; r < hi; ++r) {
+        const long long row = perm != nullptr ? perm[r] : r;
+        acc += src_bf16 != nullptr ? __bfloat162float(src_bf16[row * D + d]) : src_f32[row * D + d];
+      }
+      if constexpr (sizeof(Out) == 2) out[s * D + d] = __float2bfloat16_rn(acc);
+      else out[s * D + d] = acc;
+    }
+  }
+}
+
+}  // namespace
+
+// Scratch bytes that b200_sort_ids / b200_unique_segments need for n elements (one buffer serves both).
+B200_API long long b200_sort_scratch_bytes(long long n) {
+  size_t a = 0, b = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, a, (const long long*)nullptr, (long long*)nullptr, (const long long*)nullptr,
+                                  (long long*)nullptr, (int)n, 0, 64);
+  cub::DeviceScan::InclusiveSum(nullptr, b, (const int*)nullptr, (int*)nullptr, (int)n);
+  const size_t lib = a > b ? a : b;
+  // + positions (n x 8) + flags (n x 4) + runs (n x 4), each 256-byte aligned
+  return (long long)(((lib + 255) & ~size_t(255)) + (((size_t)n * 8 + 255) & ~size_t(255)) + 2 * (((size_t)n * 4 + 255) & ~size_t(255)));
+}
+
+// keys_out = keys_in sorted ascending on bits [0, end_bit); perm_out[i] = original position of keys_out[i].
+B200_API int b200_sort_ids(const long long* keys_in, long long* keys_out, long long* perm_out, long long n, int end_bit,
+                           void* scratch, long long scratch_bytes, void* stream) {
+  if (n <= 0) return 0;
+  if (n > 0x7fffffffll) return b200::fail(1600, "sort_ids: n=%lld exceeds 2^31 - 1", n);
+  if (end_bit < 1 || end_bit > 64) return b200::fail(1601, "sort_ids: end_bit %d outside [1, 64]", end_bit);
+  if (scratch_bytes < b200_sort_scratch_bytes(n)) return b200::fail(1602, "sort_ids: scratch of %lld bytes is too small", scratch_bytes);
+  cudaStream_t st = (cudaStream_t)stream;
+  size_t lib = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, lib, keys_in, keys_out, (const long long*)nullptr, perm_out, (int)n, 0, end_bit);
+  uint8_t* base = (uint8_t*)scratch;
+  long long* iota = (long long*)(base + ((lib + 255) & ~size_t(255)));
+  const int grid = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  iota_kernel<<<grid, 256, 0, st>>>(iota, n);
+  cudaError_t e = cub::DeviceRadixSort::SortPairs(scratch, lib, keys_in, keys_out, iota, perm_out, (int)n, 0, end_bit, st);
+  b200::count_launch(2);
+  if (e != cudaSuccess) return b200::fail(1603, "sort_ids: radix sort failed: %s", cudaGetErrorString(e));
+  return b200::check_launch("sort_ids");
+}
+
+// sorted_keys [n] (ascending), perm [n] (from b200_sort_ids; may be null when inverse is null).
+// uniq [n], seg_off [n + 1], inverse [n] (may be null), count [1]: device outputs sized for the worst case.
+B200_API int b200_unique_segments(const long long* sorted_keys, const long long* perm, long long n, long long* uniq,
+                                  long long* seg_off, long long* inverse, long long* count, void* scratch,
+                                  long long scratch_bytes, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (n <= 0) {
+    cudaMemsetAsync(count, 0, sizeof(long long), st);
+    return 0;
+  }
+  if (scratch_bytes < b200_sort_scratch_bytes(n)) return b200::fail(1602, "unique_segments: scratch of %lld bytes is too small", scratch_bytes);
+  size_t a = 0, lib = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, a, (const long long*)nullptr, (long long*)nullptr, (const long long*)nullptr,
+                                  (long long*)nullptr, (int)n, 0, 64);
+  cub::DeviceScan::InclusiveSum(nullptr, lib, (const int*)nullptr, (int*)nullptr, (int)n);
+  if (a > lib) lib = a;
+  uint8_t* base = (uint8_t*)scratch;
+  uint8_t* p = base + ((lib + 255) & ~size_t(255)) + (((size_t)n * 8 + 255) & ~size_t(255));
+  int* flags = (int*)p;
+  int* run = (int*)(p + (((size_t)n * 4 + 255) & ~size_t(255)));
+  const int grid = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  head_flags_kernel<<<grid, 256, 0, st>>>(sorted_keys, n, flags);
+  size_t scan_bytes = lib;
+  cudaError_t e = cub::DeviceScan::InclusiveSum(scratch, scan_bytes, flags, run, (int)n, st);
+  if (e != cudaSuccess) return b200::fail(1604, "unique_segments: scan failed: %s", cudaGetErrorString(e));
+  runs_kernel<<<grid, 256, 0, st>>>(sorted_keys, perm, run, n, uniq, seg_off, inverse, count);
+  b200::count_launch(3);
+  return b200::check_launch("unique_segments");
+}
+
+// src: bf16 (src_is_f32 = 0) or fp32 [rows, D]; out: bf16 (out_bf16 != 0) or fp32 [*n_seg, D] with n_seg on the device.
+// max_seg: host upper bound of *n_seg (sizes the grid).  perm may be null (src already in sorted order).
+B200_API int b200_segment_sum_gather(const void* src, int src_is_f32, const long long* perm, const long long* seg,
+                                     const long long* n_seg, long long max_seg, int D, void* out, int out_bf16, void* stream) {
+  if (max_seg <= 0) return 0;
+  const int grid = (int)(max_seg < 148 * 32 ? max_seg : 148 * 32);
+  const __nv_bfloat16* sb = src_is_f32 ? nullptr : (const __nv_bfloat16*)src;
+  const float* sf = src_is_f32 ? (const float*)src : nullptr;
+  if (out_bf16)
+    segment_sum_gather_kernel<__nv_bfloat16><<<grid, 128, 0, (cudaStream_t)stream>>>(sb, sf, perm, seg, n_seg, D, (__nv_bfloat16*)out);
+  else
+    segment_sum_gather_kernel<float><<<grid, 128, 0, (cudaStream_t)stream>>>(sb, sf, perm, seg, n_seg, D, (float*)out);
+  b200::count_launch();
+  return b200::check_launch("segment_sum_gather");
+}

@@ -75,6 +75,9 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_ln_modulate_bwd": [P, P, P, L, P, P, P, P, P, I, I, I, P],
         "b200_gate_residual_fwd": [P, P, P, L, P, I, I, I, P],
         "b200_gate_residual_bwd": [P, P, P, L, P, P, I, I, I, P],
+        "b200_sort_ids": [P, P, P, L, I, P, L, P],
+        "b200_unique_segments": [P, P, L, P, P, P, P, P, L, P],
+        "b200_segment_sum_gather": [P, I, P, P, P, L, I, P, I, P],
         "b200_hstu_attn_fwd": [P, P, P, P, P, P, I, L, I, I, I, I, L, L, L, L, F, P],
         "b200_hstu_gate_cat_fwd": [P, L, P, P, P, P, P, P, I, I, F, F, ctypes.c_ulonglong, P],
         "b200_hstu_gate_cat_bwd": [P, P, L, P, P, P, P, P, P, L, P, P, P, P, I, I, I, F, ctypes.c_ulonglong, P],
@@ -106,6 +109,9 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b200_hstu_gate_cat_scratch_elems.restype = c_ll
     lib.b200_norm_bwd_scratch_elems.restype = c_ll
     lib.b200_sumsq_scratch_elems.restype = c_int
+    if hasattr(lib, "b200_sort_scratch_bytes"):
+        lib.b200_sort_scratch_bytes.argtypes = [L]
+        lib.b200_sort_scratch_bytes.restype = c_ll
     if hasattr(lib, "b200_zero_grid"):
         lib.b200_zero_grid.restype = c_int
 

@@ -7,9 +7,14 @@ under ``embeddings.<table>.weight`` so a TorchRec-style loader can place it).  A
     dedup ids -> bucketise by owner -> exchange request counts and ids ->
     owners read their rows -> rows travel back to the requesters -> expand to the original order
 
-and backward mirrors it: duplicate gradient rows are summed (sorted, fixed order), sent to the
-owners, summed again per unique row there and applied with row-wise Adagrad immediately
+and backward mirrors it: duplicate gradient rows are summed in sorted (fixed) order by a segment
+reduction over the forward's sort permutation, sent to the owners in the wire dtype (bf16 for a bf16
+table: the quantised gradient exchange of generative_recommenders/dlrm_v4/train/utils.py:1136-1308),
+sorted and summed again per unique row there and applied with row-wise Adagrad immediately
 (``apply_optimizer_in_backward`` in the reference, generative_recommenders/dlrm_v4/train/utils.py:1547-1783).
+Dedup, sort, run offsets and both reductions are device kernels (``ops.sort``: bounded-key radix sort,
+no atomics); the one host read per lookup is the vector of per-owner request counts that sizes the
+exchange.
 
 ``comm="nccl"`` moves the rows with ``all_to_all_single`` (the TorchRec / RCCL structure of the
 reference and the baseline here).  ``comm="fused"`` is the in-kernel NVLink path: the owner's
@@ -28,6 +33,7 @@ from torch.autograd import Function
 
 from ..ops import _lib
 from ..ops import kernels as K
+from ..ops import sort as S
 
 
 class ShardedEmbedding:
@@ -56,16 +62,20 @@ class ShardedEmbedding:
 
     # ------------------------------------------------------------------ routing
     def _route(self, ids: torch.Tensor):
-        """Dedup + bucketise.  Returns ``(uniq_sorted_by_owner, inverse, send_counts [W])``."""
-        uniq, inverse = torch.unique(ids, sorted=True, return_inverse=True)      # sorted ids = sorted by owner
-        owner = torch.clamp(uniq // self.rows_per_rank, max=self.world - 1)
-        send_counts = torch.bincount(owner, minlength=self.world)
-        return uniq, inverse, send_counts
+        """Dedup + bucketise.  Returns ``(uniq_sorted_by_owner, inverse, send_counts [W], sorted)``."""
+        srt = S.sort_unique(ids, S.key_bits_for(self.rows))                      # sorted ids = sorted by owner
+        n = ids.numel()
+        valid = torch.arange(n, device=ids.device) < srt.count
+        owner = torch.where(valid, torch.clamp(srt.uniq // self.rows_per_rank, max=self.world - 1), self.world)
+        counts = torch.bincount(owner, minlength=self.world + 1)[: self.world]
+        head = torch.cat([srt.count.reshape(1), counts]).tolist()                # the lookup's one host read
+        self._last_counts = head[1:]
+        return srt.uniq[: head[0]], srt.inverse, counts, srt
 
     def _exchange_ids(self, uniq, send_counts):
         W = self.world
         if W == 1:
-            return uniq - self.row_lo, send_counts.tolist(), send_counts.tolist(), None
+            return uniq - self.row_lo, self._last_counts, self._last_counts, None
         counts = torch.empty((W, W), dtype=torch.int64, device=uniq.device)
         dist.all_gather_into_tensor(counts.view(-1), send_counts.to(torch.int64), group=self.group) \
             if uniq.is_cuda else dist.all_gather(list(counts.unbind(0)), send_counts.to(torch.int64), group=self.group)
@@ -82,7 +92,7 @@ class ShardedEmbedding:
         return _LookupFn.apply(ids, self, torch.empty(0, requires_grad=True, device=ids.device))
 
     def _forward_rows(self, ids):
-        uniq, inverse, send_counts = self._route(ids)
+        uniq, inverse, send_counts, srt = self._route(ids)
         local_idx, in_splits, out_splits, counts_h = self._exchange_ids(uniq, send_counts)
         W = self.world
         if W == 1:
@@ -104,22 +114,26 @@ class ShardedEmbedding:
             served = K.gather_rows(self.weight, local_idx)
             rows_u = torch.empty((uniq.numel(), self.dim), dtype=self.weight.dtype, device=ids.device)
             dist.all_to_all_single(rows_u, served, in_splits, out_splits, group=self.group)
-        return rows_u, (uniq, inverse, local_idx, in_splits, out_splits)
+        return rows_u, (uniq, inverse, local_idx, in_splits, out_splits, srt)
 
     def _backward_rows(self, grad: torch.Tensor, ctx_state) -> None:
-        uniq, inverse, local_idx, in_splits, out_splits = ctx_state
-        # 1. duplicates of this rank: sum per unique id in sorted (fixed) order
-        g_u = torch.zeros((uniq.numel(), self.dim), dtype=torch.float32, device=grad.device)
-        g_u.index_add_(0, inverse, grad.float())
+        uniq, inverse, local_idx, in_splits, out_splits, srt = ctx_state
+        wire = torch.bfloat16 if self.weight.dtype == torch.bfloat16 else torch.float32
+        if grad.dtype not in (torch.bfloat16, torch.float32):
+            grad = grad.float()
+        # 1. duplicates of this rank: one row per unique id, summed in sorted (fixed) order, in the wire dtype
+        g_u = S.segment_sum(grad, srt, out_dtype=wire if self.world > 1 else torch.float32, max_seg=uniq.numel())
         # 2. to the owners
         if self.world > 1:
-            recv = torch.empty((sum(out_splits), self.dim), dtype=torch.float32, device=grad.device)
+            recv = torch.empty((sum(out_splits), self.dim), dtype=wire, device=grad.device)
             dist.all_to_all_single(recv, g_u, out_splits, in_splits, group=self.group)
             g_u = recv
-        # 3. several ranks may have asked for the same row: reduce per local row, then update
-        rows_l, inv_l = torch.unique(local_idx, sorted=True, return_inverse=True)
-        g_l = torch.zeros((rows_l.numel(), self.dim), dtype=torch.float32, device=grad.device)
-        g_l.index_add_(0, inv_l, g_u)
+            # 3. several ranks may have asked for the same row: sort the requests, reduce per local row (fp32)
+            srt_l = S.sort_unique(local_idx, S.key_bits_for(max(self.local_rows, 2)))
+            g_l = S.segment_sum(g_u, srt_l, out_dtype=torch.float32)
+            rows_l = srt_l.uniq                        # entries past the run count are -1: the update skips them
+        else:
+            g_l, rows_l = g_u, local_idx               # already one row per unique id
         self.apply_rowwise_adagrad(rows_l, g_l)
 
     def apply_rowwise_adagrad(self, rows: torch.Tensor, grads: torch.Tensor) -> None:
