@@ -39,15 +39,24 @@ from ..ops import sort as S
 class ShardedEmbedding:
     def __init__(self, rows: int, dim: int, *, group=None, device="cpu", dtype=torch.bfloat16, lr: float = 1e-2,
                  eps: float = 1e-8, seed: int = 0, init_scale: float | None = None, comm: str = "nccl",
-                 max_requests: int = 1 << 20, name: str = "item"):
+                 max_requests: int = 1 << 20, name: str = "item", owner: int | None = None):
         self.group = group
         self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.rows, self.dim, self.name = rows, dim, name
-        self.rows_per_rank = (rows + self.world - 1) // self.world
-        self.row_lo = self.rank * self.rows_per_rank
-        self.local_rows = max(min(self.rows_per_rank, rows - self.row_lo), 0)
         self.device = torch.device(device)
+        # row ranges per rank: ROW_WISE cuts the table evenly; TABLE_WISE (``owner`` given) puts every row on one rank.
+        # Either way rank r owns rows [bounds[r], bounds[r + 1]) and the same routing serves both.
+        self.owner = owner
+        if owner is None:
+            self.rows_per_rank = (rows + self.world - 1) // self.world
+            bounds = [min(r * self.rows_per_rank, rows) for r in range(self.world + 1)]
+        else:
+            self.rows_per_rank = rows
+            bounds = [0 if r <= owner else rows for r in range(self.world + 1)]
+        self.bounds = torch.tensor(bounds, dtype=torch.int64, device=self.device)
+        self.row_lo = bounds[self.rank]
+        self.local_rows = bounds[self.rank + 1] - bounds[self.rank]
         g = torch.Generator(device=self.device).manual_seed(seed * 7919 + self.rank)
         scale = init_scale if init_scale is not None else (1.0 / rows) ** 0.5
         self.weight = (torch.rand(self.local_rows, dim, generator=g, device=self.device) * 2 - 1).mul_(scale).to(dtype)
@@ -66,7 +75,8 @@ class ShardedEmbedding:
         srt = S.sort_unique(ids, S.key_bits_for(self.rows))                      # sorted ids = sorted by owner
         n = ids.numel()
         valid = torch.arange(n, device=ids.device) < srt.count
-        owner = torch.where(valid, torch.clamp(srt.uniq // self.rows_per_rank, max=self.world - 1), self.world)
+        own = torch.bucketize(srt.uniq, self.bounds[1:], right=True).clamp(max=self.world - 1)
+        owner = torch.where(valid, own, self.world)
         counts = torch.bincount(owner, minlength=self.world + 1)[: self.world]
         head = torch.cat([srt.count.reshape(1), counts]).tolist()                # the lookup's one host read
         self._last_counts = head[1:]
@@ -87,13 +97,25 @@ class ShardedEmbedding:
         return recv_ids - self.row_lo, in_splits, out_splits, counts_h
 
     # ------------------------------------------------------------------ forward / backward
-    def lookup(self, ids: torch.Tensor) -> torch.Tensor:
-        """``ids`` int64 ``[n]`` (global row ids) -> rows ``[n, dim]``; differentiable."""
-        return _LookupFn.apply(ids, self, torch.empty(0, requires_grad=True, device=ids.device))
-
-    def _forward_rows(self, ids):
-        uniq, inverse, send_counts, srt = self._route(ids)
+    def input_dist(self, ids: torch.Tensor) -> dict:
+        """The id half of a lookup: sort / dedup, bucketise by owner, exchange request counts and ids.
+        It depends on the batch's ids only, so a pipelined trainer runs it for batch N + 1 on a side
+        stream while batch N computes, and hands the plan to ``lookup`` later (the sparse-data-dist stage
+        of the reference's ``_StreamingTrainPipeline``, generative_recommenders/dlrm_v4/train/utils.py:3487-3871)."""
+        uniq, inverse, send_counts, srt = self._route(ids.reshape(-1))
         local_idx, in_splits, out_splits, counts_h = self._exchange_ids(uniq, send_counts)
+        return {"uniq": uniq, "inverse": inverse, "srt": srt, "local_idx": local_idx, "in_splits": in_splits,
+                "out_splits": out_splits, "counts_h": counts_h}
+
+    def lookup(self, ids: torch.Tensor, plan: dict | None = None) -> torch.Tensor:
+        """``ids`` int64 ``[n]`` (global row ids) -> rows ``[n, dim]``; differentiable.  ``plan``: the result
+        of an earlier ``input_dist(ids)`` for the same ids."""
+        return _LookupFn.apply(ids, self, torch.empty(0, requires_grad=True, device=ids.device), plan)
+
+    def _forward_rows(self, ids, plan: dict | None = None):
+        plan = plan if plan is not None else self.input_dist(ids)
+        uniq, inverse, srt = plan["uniq"], plan["inverse"], plan["srt"]
+        local_idx, in_splits, out_splits, counts_h = plan["local_idx"], plan["in_splits"], plan["out_splits"], plan["counts_h"]
         W = self.world
         if W == 1:
             rows_u = K.gather_rows(self.weight, local_idx)
@@ -167,12 +189,12 @@ class ShardedEmbedding:
 
 class _LookupFn(Function):
     @staticmethod
-    def forward(ctx, ids, table: ShardedEmbedding, _anchor):
-        rows_u, st = table._forward_rows(ids.reshape(-1))
+    def forward(ctx, ids, table: ShardedEmbedding, _anchor, plan=None):
+        rows_u, st = table._forward_rows(ids.reshape(-1), plan)
         ctx.table, ctx.state = table, st
         return rows_u[st[1]]
 
     @staticmethod
     def backward(ctx, grad):
         ctx.table._backward_rows(grad.contiguous(), ctx.state)
-        return None, None, None
+        return None, None, None, None

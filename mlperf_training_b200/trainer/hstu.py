@@ -2,10 +2,14 @@
 engine, sparse row-wise Adagrad in backward, MLLOG events, window-AUC evaluation with a target,
 checkpoint cadence and host-side fault injection.
 
-Step structure (the reference's pipelined step, generative_recommenders/dlrm_v4/train/utils.py:4989-5255):
+Step structure (the reference's pipelined step, generative_recommenders/dlrm_v4/train/utils.py:3487-3871,
+4989-5255) - three stages in flight at once:
 
-    batch N+1 built on the host and copied H2D on a side stream  ||  step N on the main stream
-    lookup(ids) -> HSTU forward -> loss -> backward (sparse update applied inside) -> dense AdamW
+    batch N+2  built on the host by the loader thread
+    batch N+1  copied H2D on the copy stream, then its sparse input-dist (id sort / dedup, request counts
+               and id exchange) on the dist stream
+    batch N    row exchange + HSTU forward -> loss -> backward (sparse update inside) -> dense AdamW on the
+               main stream
 
 The train loss is read one step late from a pinned buffer (``PendingScalar``), so no step waits
 for a device-to-host copy; a ``StepFence`` bounds how far the host may run ahead
@@ -86,6 +90,22 @@ class _WorldView:
         return out
 
 
+def _tensors_of(obj) -> list:
+    """Every tensor inside a (nested) dict / list / dataclass-like plan."""
+    out = []
+    if torch.is_tensor(obj):
+        out.append(obj)
+    elif isinstance(obj, dict):
+        for v in obj.values():
+            out += _tensors_of(v)
+    elif isinstance(obj, (list, tuple)):
+        for v in obj:
+            out += _tensors_of(v)
+    elif hasattr(obj, "__dict__"):
+        out += _tensors_of(vars(obj))
+    return [t for t in out if t.is_cuda]
+
+
 def hstu_bucket_of(name: str) -> str:
     parts = name.split(".")
     return f"l{int(parts[1]):04d}" if parts[0] == "layers" else "a_misc"
@@ -126,7 +146,10 @@ class HSTUTrainer:
         self.eval_lookahead = True
         self.pipelined = True            # loader thread + copy stream ahead of the step (the reference's TRAIN_PIPELINE=1)
         self.copy_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
+        self.dist_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
+        self.pipeline_input_dist = True  # the id half of batch N+1's lookup runs under step N (3-stage sparse pipeline)
         self._next = None
+        self._ready = None               # (step, device batch, plan, event) prepared ahead
         self._pool = None
 
     # ------------------------------------------------------------------ data prefetch
@@ -160,20 +183,51 @@ class HSTUTrainer:
             if ev is not None:
                 torch.cuda.current_stream().wait_event(ev)
             return batch
-        if self._next is None or self._next[0] != step:
-            self._next = (step, self._submit(step))
-        host = self._next[1].result()
-        batch, ev = self._to_device(host)
+        if not self.pipeline_input_dist:
+            if self._next is None or self._next[0] != step:
+                self._next = (step, self._submit(step))
+            host = self._next[1].result()
+            batch, ev = self._to_device(host)
+            if ev is not None:
+                torch.cuda.current_stream().wait_event(ev)       # only this batch's own H2D is awaited
+            self._next = (step + 1, self._submit(step + 1))      # built while this step runs
+            return batch
+        # three stages: (N+2) host build | (N+1) H2D + input-dist on side streams | (N) compute
+        if self._ready is None or self._ready[0] != step:
+            if self._next is None or self._next[0] != step:
+                self._next = (step, self._submit(step))
+            self._ready = self._prepare(step, self._next[1].result())
+            self._next = (step + 1, self._submit(step + 1))
+        _, batch, plan, ev = self._ready
         if ev is not None:
-            torch.cuda.current_stream().wait_event(ev)       # only this batch's own H2D is awaited
-        self._next = (step + 1, self._submit(step + 1))      # built while this step runs
+            main = torch.cuda.current_stream()
+            main.wait_event(ev)
+            for t in _tensors_of(batch) + _tensors_of(plan):     # allocated on side streams, consumed on this one
+                t.record_stream(main)
+        batch = dict(batch, _plan=plan)
+        nxt = self._next[1].result() if self._next[0] == step + 1 else self._build(step + 1)
+        self._ready = self._prepare(step + 1, nxt)               # launched now, runs under step N's kernels
+        self._next = (step + 2, self._submit(step + 2))
         return batch
+
+    def _prepare(self, step: int, host):
+        """H2D of a host batch on the copy stream, then the id half of its embedding lookup on the dist
+        stream; returns ``(step, device batch, plan, event)``."""
+        batch, ev = self._to_device(host)
+        if self.dist_stream is None:
+            return step, batch, self.table.input_dist(batch["item_ids"]), None
+        with torch.cuda.stream(self.dist_stream):
+            self.dist_stream.wait_event(ev)
+            plan = self.table.input_dist(batch["item_ids"])
+            done = torch.cuda.Event()
+            done.record()
+        return step, batch, plan, done
 
     # ------------------------------------------------------------------ steps
     def embed(self, batch):
         rows = batch["rows"]
         emb = torch.zeros((rows, self.cfg.emb_dim), dtype=self.cfg.torch_dtype(), device=self.device)
-        emb[: batch["total"]] = self.table.lookup(batch["item_ids"]).to(emb.dtype)
+        emb[: batch["total"]] = self.table.lookup(batch["item_ids"], batch.get("_plan")).to(emb.dtype)
         return emb
 
     def train_step_device(self, batch) -> torch.Tensor:
@@ -269,6 +323,7 @@ def _warmup(tr: "HSTUTrainer", steps: int) -> None:
     tr.table.state.copy_(st)
     tr.step_idx = 0
     tr._next = None
+    tr._ready = None
 
 
 def run(exp: dict, device: str | None = None, stream=None) -> dict:

@@ -74,3 +74,18 @@ def test_multitask_head_losses():
     # all-zero supervision weights: the denominator clamps to 1 and the loss is 0
     zero = head(user, item, actions, values, weights=torch.zeros(3, T))[0]
     assert all(float(v) == 0.0 for v in zero.values())
+
+
+def test_three_stage_pipeline_gives_the_same_losses():
+    """Batch N+1's sparse input-dist prepared ahead of step N changes the schedule, not the numbers."""
+    from mlperf_training_b200.trainer.hstu import HSTUTrainer
+    losses = {}
+    for mode in ("plain", "loader", "three_stage"):
+        torch.manual_seed(0)
+        cfg = tiny_hstu(input_dropout=0.0, linear_dropout=0.0)
+        tr = HSTUTrainer(cfg, 300, 6, "cpu", seed=4, data_kw=dict(length_median=10, length_min=3, length_max=30))
+        tr.pipelined = mode != "plain"
+        tr.pipeline_input_dist = mode == "three_stage"
+        losses[mode] = [float(tr.train_step()) for _ in range(5)]
+    assert losses["plain"] == losses["loader"] == losses["three_stage"]
+    assert losses["plain"][-1] == losses["plain"][-1] and len(set(losses["plain"])) > 1
