@@ -28,6 +28,10 @@ constexpr int BQ = 128;
 constexpr int BKV = 128;
 constexpr int NTHREADS = 320;
 constexpr int STG = 4096;  // dQ staging chunk: 32 rows x 32 fp32
+#ifndef B200_ATTN_BWD_POLY
+#define B200_ATTN_BWD_POLY 6
+#endif
+constexpr int POLY = B200_ATTN_BWD_POLY;   // pairs with (i & POLY) == POLY take the FMA-pipe polynomial: 6 = a quarter, 2 = half
 
 struct BwdParams {
   int B, Hq, Hkv, Sq, Skv;
@@ -255,7 +259,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int i = 0; i < 32; i += 2) {
           const float2 a = ffma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, nl2);
           float2 e;
-          if ((i & 6) == 6) e = ex2_poly2(a);
+          if ((i & POLY) == POLY) e = ex2_poly2(a);
           else e = make_float2(ex2_approx(a.x), ex2_approx(a.y));
           float p0 = e.x, p1 = e.y;
           if (need_mask) {

@@ -27,6 +27,10 @@
 
 namespace {
 
+#ifndef B200_ATTN_FWD_POLY
+#define B200_ATTN_FWD_POLY 3
+#endif
+constexpr int POLY = B200_ATTN_FWD_POLY;  // pairs with (i & POLY) == POLY take the FMA-pipe polynomial: 3 = a quarter, 1 = half
 constexpr int BQ = 128;   // query rows per tile (two tiles per CTA)
 constexpr int BKV = 128;  // keys per tile
 constexpr int NTHREADS = 320;  // warps 0-3 / 4-7: softmax of tile 0 / 1; warp 8: TMA; warp 9: MMA
@@ -289,7 +293,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const int e = c * 32 + 2 * i;
           const float2 a = ffma2(make_float2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])), sc2, nm2);
           float2 x;
-          if ((i & 3) == 3) x = ex2_poly2(a);
+          if ((i & POLY) == POLY) x = ex2_poly2(a);
           else x = make_float2(ex2_approx(a.x), ex2_approx(a.y));
           rs2[i & 1] = fadd2(rs2[i & 1], x);
           pk[i] = pack_bf16x2(x.x, x.y);

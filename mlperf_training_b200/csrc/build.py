@@ -54,12 +54,20 @@ def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
-def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile all ``*.cu`` files and link the shared library.  Returns its path."""
+DEBUG_LIB_NAME = "_b200_kernels_dbg.so"
+
+
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False, debug_bounds: bool = False) -> Path:
+    """Compile all ``*.cu`` files and link the shared library.  Returns its path.  ``debug_bounds`` builds
+    the bounds-reporting variant (``-DB200_DEBUG_BOUNDS``) into ``_b200_kernels_dbg.so``; point
+    ``B200_KERNELS_LIB`` at it to run a program over it."""
     nvcc = _nvcc()
-    obj_dir = CSRC / "build"
+    obj_dir = CSRC / ("build_dbg" if debug_bounds else "build")
     obj_dir.mkdir(exist_ok=True)
-    flags = list(NVCC_FLAGS)
+    lib_path = PKG / DEBUG_LIB_NAME if debug_bounds else LIB_PATH
+    flags = list(NVCC_FLAGS) + os.environ.get("B200_NVCC_EXTRA", "").split()      # tuning macros
+    if debug_bounds:
+        flags.append("-DB200_DEBUG_BOUNDS")
     if ptxas_info:
         flags += ["-Xptxas", "-v"]
     flag_key = " ".join(flags)
@@ -84,15 +92,16 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
         for r in results:
             if r[2]:
                 print(r[2], file=sys.stderr)
-    if rebuilt or not LIB_PATH.exists() or force:
+    if rebuilt or not lib_path.exists() or force:
         cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
-               "-o", str(LIB_PATH), *[str(o) for o in objs]]
+               "-o", str(lib_path), *[str(o) for o in objs]]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    path = build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    path = build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv,
+                 debug_bounds="--debug-bounds" in sys.argv)
     print(path)

@@ -38,6 +38,16 @@ B200_DEVICE void b200_report(int* status, int code, int where) {
   atomicAdd(&status[3], 1);
 }
 
+// Debug bounds build (-DB200_DEBUG_BOUNDS): kernels that index memory with data-dependent ids already skip
+// an id outside its table; in this build they also record B200_ERR_BOUNDS with a kernel tag in the status
+// block, so a bad index shows up as a host-side error instead of silently missing rows.  The access is
+// skipped either way - nothing traps.  Stands in for a memory sanitizer on boxes where none may run.
+#ifdef B200_DEBUG_BOUNDS
+#define B200_BOUNDS_REPORT(status, where) b200_report((status), B200_ERR_BOUNDS, (where))
+#else
+#define B200_BOUNDS_REPORT(status, where) ((void)0)
+#endif
+
 // wall-clock limit of a single wait, in nanoseconds of %globaltimer
 #ifndef B200_WAIT_LIMIT_NS
 #define B200_WAIT_LIMIT_NS 2000000000ull

@@ -139,7 +139,7 @@ __global__ void gelu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv
 // Embedding gather: out[t, :] = table[ids[t], :] (bf16, D % 8 == 0); ids < 0 give zero rows.
 // ---------------------------------------------------------------------------------------
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ table, const long long* __restrict__ ids,
-                                   __nv_bfloat16* __restrict__ out, long long T, int D, long long rows) {
+                                   __nv_bfloat16* __restrict__ out, long long T, int D, long long rows, int* status) {
   const int vpr = D / 8;
   const long long total = T * vpr;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -149,12 +149,13 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ table, cons
     const long long id = ids[t];
     uint4 u = make_uint4(0, 0, 0, 0);
     if (id >= 0 && id < rows) u = *reinterpret_cast<const uint4*>(table + id * D + v * 8);
+    else if (v == 0) B200_BOUNDS_REPORT(status, 401);
     *reinterpret_cast<uint4*>(out + t * D + v * 8) = u;
   }
 }
 // grad_table[ids[t], :] += dy[t, :]  (fp32 atomics; used for the vocabulary embedding)
 __global__ void scatter_add_rows_kernel(const __nv_bfloat16* __restrict__ dy, const long long* __restrict__ ids,
-                                        float* __restrict__ grad, long long T, int D, long long rows) {
+                                        float* __restrict__ grad, long long T, int D, long long rows, int* status) {
   const int vpr = D / 8;
   const long long total = T * vpr;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -162,7 +163,10 @@ __global__ void scatter_add_rows_kernel(const __nv_bfloat16* __restrict__ dy, co
     const long long t = i / vpr;
     const int v = (int)(i % vpr);
     const long long id = ids[t];
-    if (id < 0 || id >= rows) continue;
+    if (id < 0 || id >= rows) {
+      if (v == 0) B200_BOUNDS_REPORT(status, 402);
+      continue;
+    }
     float d[8];
     ld8(dy + t * D + v * 8, d);
     float* g = grad + id * D + v * 8;
@@ -254,7 +258,7 @@ B200_API int b200_gather_rows(const void* table, const long long* ids, void* out
   if (D % 8 != 0) return b200::fail(403, "gather_rows: D=%d must be a multiple of 8", D);
   if (T == 0) return 0;
   gather_rows_kernel<<<grid_for(T * (D / 8), 256), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)table, ids,
-                                                                                  (__nv_bfloat16*)out, T, D, rows);
+                                                                                  (__nv_bfloat16*)out, T, D, rows, b200::status_ptr());
   b200::count_launch();
   return b200::check_launch("gather_rows");
 }
@@ -263,7 +267,7 @@ B200_API int b200_scatter_add_rows(const void* dy, const long long* ids, float* 
   if (D % 8 != 0) return b200::fail(403, "scatter_add_rows: D=%d must be a multiple of 8", D);
   if (T == 0) return 0;
   scatter_add_rows_kernel<<<grid_for(T * (D / 8), 256), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, ids,
-                                                                                       grad, T, D, rows);
+                                                                                       grad, T, D, rows, b200::status_ptr());
   b200::count_launch();
   return b200::check_launch("scatter_add_rows");
 }

@@ -27,7 +27,7 @@ struct PeerBufs {
 // requests are grouped by requesting rank: recv_off[r] .. recv_off[r+1]
 __global__ void gather_rows_to_peers_kernel(const __nv_bfloat16* __restrict__ table, long long rows,
                                             const long long* __restrict__ local_idx,
-                                            const long long* __restrict__ recv_off, int W, int D, PeerBufs out) {
+                                            const long long* __restrict__ recv_off, int W, int D, PeerBufs out, int* status) {
   const int vpr = D / 8;
   const long long n = recv_off[W];
   const long long total = n * vpr;
@@ -39,6 +39,7 @@ __global__ void gather_rows_to_peers_kernel(const __nv_bfloat16* __restrict__ ta
     const long long id = local_idx[req];
     uint4 u = make_uint4(0, 0, 0, 0);
     if (id >= 0 && id < rows) u = *reinterpret_cast<const uint4*>(table + id * D + v * 8);
+    else if (v == 0) B200_BOUNDS_REPORT(status, 1301);
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out.p[r]) + (out.base_row[r] + (req - recv_off[r])) * D + v * 8;
     *reinterpret_cast<uint4*>(dst) = u;
   }
@@ -47,12 +48,15 @@ __global__ void gather_rows_to_peers_kernel(const __nv_bfloat16* __restrict__ ta
 // one warp per unique row
 __global__ void rowwise_adagrad_kernel(__nv_bfloat16* __restrict__ table, float* __restrict__ state,
                                        const long long* __restrict__ ids, const float* __restrict__ grads, long long n,
-                                       int D, float lr, float eps, long long rows) {
+                                       int D, float lr, float eps, long long rows, int* status) {
   const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (w >= n) return;
   const long long id = ids[w];
-  if (id < 0 || id >= rows) return;
+  if (id < 0 || id >= rows) {
+    if (lane == 0 && id != -1) B200_BOUNDS_REPORT(status, 1302);   // -1 pads the unique list past the run count
+    return;
+  }
   const float* g = grads + w * D;
   float ss = 0.f;
   for (int d = lane; d < D; d += 32) ss += g[d] * g[d];
@@ -93,7 +97,7 @@ B200_API int b200_gather_rows_to_peers(const void* table, long long rows, const 
   long long g = (work + 255) / 256;
   long long cap = (long long)b200::sm_count() * 16;
   gather_rows_to_peers_kernel<<<(unsigned)(g < cap ? g : cap), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)table, rows, local_idx, recv_off, W, D, pb);
+      (const __nv_bfloat16*)table, rows, local_idx, recv_off, W, D, pb, b200::status_ptr());
   b200::count_launch();
   return b200::check_launch("gather_rows_to_peers");
 }
@@ -103,7 +107,7 @@ B200_API int b200_rowwise_adagrad(void* table, float* state, const long long* id
   if (n <= 0) return 0;
   const long long threads = n * 32;
   rowwise_adagrad_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-      (__nv_bfloat16*)table, state, ids, grads, n, D, lr, eps, rows);
+      (__nv_bfloat16*)table, state, ids, grads, n, D, lr, eps, rows, b200::status_ptr());
   b200::count_launch();
   return b200::check_launch("rowwise_adagrad");
 }

@@ -49,7 +49,7 @@ template <typename Out>
 __global__ void __launch_bounds__(128)
 segment_sum_gather_kernel(const __nv_bfloat16* __restrict__ src_bf16, const float* __restrict__ src_f32,
                           const long long* __restrict__ perm, const long long* __restrict__ seg,
-                          const long long* __restrict__ n_seg, int D, Out* __restrict__ out) {
+                          const long long* __restrict__ n_seg, int D, Out* __restrict__ out, long long src_rows, int* status) {
   const long long total = *n_seg;
   for (long long s = blockIdx.x; s < total; s += gridDim.x) {
     const long long lo = seg[s], hi = seg[s + 1];
@@ -57,6 +57,10 @@ segment_sum_gather_kernel(const __nv_bfloat16* __restrict__ src_bf16, const floa
       float acc = 0.f;
       for (long long r = lo; r < hi; ++r) {
         const long long row = perm != nullptr ? perm[r] : r;
+        if (row < 0 || row >= src_rows) {               // a permutation entry outside the gradient matrix
+          if (d == 0) B200_BOUNDS_REPORT(status, 1601);
+          continue;
+        }
         acc += src_bf16 != nullptr ? __bfloat162float(src_bf16[row * D + d]) : src_f32[row * D + d];
       }
       if constexpr (sizeof(Out) == 2) out[s * D + d] = __float2bfloat16_rn(acc);
@@ -129,17 +133,19 @@ B200_API int b200_unique_segments(const long long* sorted_keys, const long long*
 }
 
 // src: bf16 (src_is_f32 = 0) or fp32 [rows, D]; out: bf16 (out_bf16 != 0) or fp32 [*n_seg, D] with n_seg on the device.
-// max_seg: host upper bound of *n_seg (sizes the grid).  perm may be null (src already in sorted order).
-B200_API int b200_segment_sum_gather(const void* src, int src_is_f32, const long long* perm, const long long* seg,
-                                     const long long* n_seg, long long max_seg, int D, void* out, int out_bf16, void* stream) {
+// max_seg: host upper bound of *n_seg (sizes the grid).  perm may be null (src already in sorted order);
+// its entries must lie in [0, src_rows).
+B200_API int b200_segment_sum_gather(const void* src, int src_is_f32, long long src_rows, const long long* perm,
+                                     const long long* seg, const long long* n_seg, long long max_seg, int D, void* out,
+                                     int out_bf16, void* stream) {
   if (max_seg <= 0) return 0;
   const int grid = (int)(max_seg < 148 * 32 ? max_seg : 148 * 32);
   const __nv_bfloat16* sb = src_is_f32 ? nullptr : (const __nv_bfloat16*)src;
   const float* sf = src_is_f32 ? (const float*)src : nullptr;
   if (out_bf16)
-    segment_sum_gather_kernel<__nv_bfloat16><<<grid, 128, 0, (cudaStream_t)stream>>>(sb, sf, perm, seg, n_seg, D, (__nv_bfloat16*)out);
+    segment_sum_gather_kernel<__nv_bfloat16><<<grid, 128, 0, (cudaStream_t)stream>>>(sb, sf, perm, seg, n_seg, D, (__nv_bfloat16*)out, src_rows, b200::status_ptr());
   else
-    segment_sum_gather_kernel<float><<<grid, 128, 0, (cudaStream_t)stream>>>(sb, sf, perm, seg, n_seg, D, (float*)out);
+    segment_sum_gather_kernel<float><<<grid, 128, 0, (cudaStream_t)stream>>>(sb, sf, perm, seg, n_seg, D, (float*)out, src_rows, b200::status_ptr());
   b200::count_launch();
   return b200::check_launch("segment_sum_gather");
 }

@@ -136,6 +136,93 @@ def build_window_index(timestamps: np.ndarray, window_seconds: int, holdout: flo
             "contract": np.array([window_seconds, salt, int(holdout * 1e6)], dtype=np.int64)}
 
 
+# --------------------------------------------------------------------------- downloads
+def download_manifest(manifest: str, dest: str, retries: int = 3) -> list[str]:
+    """Fetch the files of a manifest (one ``<md5>  <relative path>  <url>`` per line) into ``dest``, skipping
+    files whose md5 already matches, verifying each download.  Returns the paths fetched.  The dataset
+    scripts of the reference do the same with rclone / wget and md5 lists
+    (small_llm_pretraining/primus/README.md:30-60, llama2_sft/primus/README.md:10-64)."""
+    import hashlib
+    import urllib.request
+    got = []
+    for line in Path(manifest).read_text().splitlines():
+        parts = line.split()
+        if len(parts) < 3 or line.lstrip().startswith("#"):
+            continue
+        digest, rel, url = parts[0], parts[1], parts[2]
+        out = Path(dest) / rel
+        if out.exists() and hashlib.md5(out.read_bytes()).hexdigest() == digest:
+            continue
+        out.parent.mkdir(parents=True, exist_ok=True)
+        for attempt in range(retries):
+            tmp = out.with_suffix(out.suffix + ".part")
+            urllib.request.urlretrieve(url, tmp)
+            if hashlib.md5(tmp.read_bytes()).hexdigest() == digest:
+                tmp.replace(out)
+                got.append(str(out))
+                break
+            tmp.unlink(missing_ok=True)
+        else:
+            raise OSError(f"{rel}: md5 mismatch after {retries} attempts")
+    return got
+
+
+# --------------------------------------------------------------------------- Hugging Face -> torch_dist
+def hf_llama_to_gpt_state(hf: dict, n_layers: int) -> dict:
+    """Hugging Face Llama parameter names -> this package's ``GPT`` names (fused q|k|v and gate|up rows;
+    both sides use the rotate-half rotary convention, so no permutation of the projection rows)."""
+    import torch
+    out = {"embed": hf["model.embed_tokens.weight"], "final_norm": hf["model.norm.weight"],
+           "lm_head": hf.get("lm_head.weight", hf["model.embed_tokens.weight"])}
+    for i in range(n_layers):
+        p = f"model.layers.{i}."
+        out[f"blocks.{i}.attn_norm"] = hf[p + "input_layernorm.weight"]
+        out[f"blocks.{i}.w_qkv"] = torch.cat([hf[p + f"self_attn.{n}_proj.weight"] for n in ("q", "k", "v")], 0)
+        out[f"blocks.{i}.w_proj"] = hf[p + "self_attn.o_proj.weight"]
+        out[f"blocks.{i}.mlp_norm"] = hf[p + "post_attention_layernorm.weight"]
+        out[f"blocks.{i}.mlp.w_gate_up"] = torch.cat([hf[p + "mlp.gate_proj.weight"], hf[p + "mlp.up_proj.weight"]], 0)
+        out[f"blocks.{i}.mlp.w_down"] = hf[p + "mlp.down_proj.weight"]
+    return out
+
+
+def convert_hf_llama(hf_dir: str, out_root: str, preset: str = "llama2-70b", dtype: str = "bf16") -> str:
+    """A Hugging Face Llama directory (``*.safetensors`` or ``pytorch_model*.bin`` shards + ``config.json``) ->
+    a Megatron ``torch_dist`` checkpoint that ``pretrained_checkpoint`` loads (the reference converts with
+    Megatron-Bridge: llama2_sft/primus/README.md:53-76)."""
+    import json
+
+    import torch
+
+    from ..checkpoint.megatron import save_torch_dist
+    from ..models.gpt import GPT, PRESETS
+    cfg = PRESETS[preset]()
+    hf_cfg = json.loads((Path(hf_dir) / "config.json").read_text()) if (Path(hf_dir) / "config.json").exists() else {}
+    for ours, theirs in (("n_layers", "num_hidden_layers"), ("hidden", "hidden_size"), ("n_heads", "num_attention_heads"),
+                         ("n_kv_heads", "num_key_value_heads"), ("ffn_hidden", "intermediate_size"), ("vocab_size", "vocab_size")):
+        if theirs in hf_cfg:
+            setattr(cfg, ours, int(hf_cfg[theirs]))
+    cfg.dtype = dtype
+    state = {}
+    shards = sorted(Path(hf_dir).glob("*.safetensors"))
+    if shards:
+        from safetensors.torch import load_file
+        for f in shards:
+            state.update(load_file(str(f)))
+    else:
+        for f in sorted(Path(hf_dir).glob("pytorch_model*.bin")):
+            state.update(torch.load(f, map_location="cpu", weights_only=True))
+    if not state:
+        raise FileNotFoundError(f"no *.safetensors or pytorch_model*.bin under {hf_dir}")
+    model = GPT(cfg, device="cpu", seed=0)
+    mine = dict(model.named_parameters())
+    with torch.no_grad():
+        for name, t in hf_llama_to_gpt_state(state, cfg.n_layers).items():
+            if tuple(mine[name].shape) != tuple(t.shape):
+                raise ValueError(f"{name}: checkpoint shape {tuple(t.shape)} vs model {tuple(mine[name].shape)}")
+            mine[name].copy_(t.to(mine[name].dtype))
+    return str(save_torch_dist(model, out_root, iteration=0))
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="b200-data-prep")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -152,8 +239,16 @@ def main(argv=None) -> int:
     q = sub.add_parser("synthetic-sequences"); q.add_argument("path"); q.add_argument("--users", type=int, default=10_000)
     q.add_argument("--items", type=int, default=100_000); q.add_argument("--kind", default="movielens", choices=["movielens", "kuairand"])
     q.add_argument("--min-len", type=int, default=8); q.add_argument("--max-len", type=int, default=200); q.add_argument("--seed", type=int, default=0)
+    d = sub.add_parser("download"); d.add_argument("manifest"); d.add_argument("dest")
+    f = sub.add_parser("hf-to-torch-dist"); f.add_argument("hf_dir"); f.add_argument("out_root")
+    f.add_argument("--preset", default="llama2-70b"); f.add_argument("--dtype", default="bf16")
     a = ap.parse_args(argv)
-    if a.cmd == "synthetic-events":
+    if a.cmd == "download":
+        for path in download_manifest(a.manifest, a.dest):
+            print(f"fetched {path}")
+    elif a.cmd == "hf-to-torch-dist":
+        print(f"torch_dist checkpoint -> {convert_hf_llama(a.hf_dir, a.out_root, a.preset, a.dtype)}")
+    elif a.cmd == "synthetic-events":
         from .yambda import write_synthetic_event_store
         n = write_synthetic_event_store(a.root, a.users, a.events_per_user, a.items, days=a.days, seed=a.seed)
         print(f"{n} events of {a.users} users -> {a.root}")

@@ -249,15 +249,13 @@ class Block(nn.Module):
         qkv = T.column_parallel(xn, self.w_qkv, tp)
         if self.lora_qkv is not None:
             lo = self.lora_qkv
-            u = T.GatherRows.apply(lo.drop(xn) @ lo.a.t(), tp)
-            qkv = qkv + (u @ lo.b.t()) * lo.scale
+            qkv = qkv + lo.up(T.GatherRows.apply(lo.down(xn), tp))
         a = F.attention_packed(qkv, B=B, S=S, Hq=self.hq, Hkv=self.hkv, D=cfg.head_dim, cos=cos, sin=sin,
                                sink=self.sink, causal=True, window=cfg.layer_window(self.layer))
         h = T.row_parallel(a, self.w_proj, tp, residual=x)
         if self.lora_proj is not None:
             lo = self.lora_proj
-            u = T.ScatterRows.apply(lo.drop(a) @ lo.a.t(), tp)
-            h = h + (u @ lo.b.t()) * lo.scale
+            h = h + lo.up(T.ScatterRows.apply(lo.down(a), tp))
         return self.mlp(h, self.mlp_norm, cfg.norm_eps)
 
     def _attention_cp(self, qkv, cos, sin, B, S):
@@ -288,7 +286,7 @@ class Block(nn.Module):
             qkv = F.norm_linear(x, self.attn_norm, self.w_qkv, eps=cfg.norm_eps, precision=pr)
         else:
             xn = F.rms_norm(x, self.attn_norm, cfg.norm_eps)
-            qkv = F.linear(xn, self.w_qkv, None, None, pr) + self.lora_qkv(xn)
+            qkv = F.linear(xn, self.w_qkv, None, self.lora_qkv(xn), pr)      # adapter output joins in the GEMM epilogue
         if self.cp is not None:
             a = self._attention_cp(qkv, cos, sin, B, S)
         else:
@@ -297,7 +295,7 @@ class Block(nn.Module):
         if self.lora_proj is None:
             h = F.linear(a, self.w_proj, None, x, pr)
         else:
-            h = F.linear(a, self.w_proj, None, x, pr) + self.lora_proj(a)
+            h = F.linear(a, self.w_proj, None, x + self.lora_proj(a), pr)
         return self.mlp(h, self.mlp_norm, cfg.norm_eps)
 
 

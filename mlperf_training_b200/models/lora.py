@@ -33,10 +33,24 @@ class LoRAAdapter(nn.Module):
     def drop(self, x):
         return TF.dropout(x, self.dropout) if (self.dropout > 0 and self.training) else x
 
+    def down(self, x):
+        """``dropout(x) A^T`` ``[T, rank]``: on the tcgen05 GEMM (a skinny-N tile) for CUDA bf16 rows."""
+        return _mm(self.drop(x), self.a)
+
+    def up(self, u):
+        """``scale * u B^T`` ``[T, n_out]``."""
+        return _mm(u * self.scale, self.b)
+
     def forward(self, x):
-        x = self.drop(x)
-        # rank-16 GEMMs are far below the tensor-core tile: plain matmuls, bf16
-        return (x @ self.a.t()) @ self.b.t() * self.scale
+        return self.up(self.down(x))
+
+
+def _mm(x, w):
+    """``x W^T`` through the package's GEMM (forward, dgrad and wgrad) when the operands allow it
+    (2-D, inner dimensions multiples of 8 elements = 16 bytes), else a plain matmul."""
+    if x.dim() == 2 and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and x.dtype == w.dtype:
+        return F.linear(x, w)
+    return x @ w.t()
 
 
 def freeze_base(model: nn.Module) -> list[str]:

@@ -40,7 +40,7 @@ class MoEMLP(nn.Module):
     def forward(self, h, norm_w, eps):
         cfg = self.cfg
         hn = F.rms_norm(h, norm_w, eps)
-        logits = hn.float() @ self.router.t()
+        logits = F.router_logits(hn, self.router)          # fp32 logits on the tcgen05 GEMM (split-precision weight)
         idx, w, counts = M.RouterFn.apply(logits, cfg.top_k)
         if self.dispatcher is None:
             y = M.moe_experts(hn, idx, w, counts, self.w1, self.w2)

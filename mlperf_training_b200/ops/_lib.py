@@ -19,7 +19,8 @@ from pathlib import Path
 import torch
 
 _PKG = Path(__file__).resolve().parent.parent
-LIB_PATH = _PKG / "_b200_kernels.so"
+# B200_KERNELS_LIB selects another build of the library (the bounds-reporting debug build)
+LIB_PATH = Path(os.environ["B200_KERNELS_LIB"]) if os.environ.get("B200_KERNELS_LIB") else _PKG / "_b200_kernels.so"
 
 _lib = None
 _lock = threading.Lock()
@@ -77,7 +78,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_gate_residual_bwd": [P, P, P, L, P, P, I, I, I, P],
         "b200_sort_ids": [P, P, P, L, I, P, L, P],
         "b200_unique_segments": [P, P, L, P, P, P, P, P, L, P],
-        "b200_segment_sum_gather": [P, I, P, P, P, L, I, P, I, P],
+        "b200_segment_sum_gather": [P, I, L, P, P, P, L, I, P, I, P],
         "b200_hstu_attn_fwd": [P, P, P, P, P, P, I, L, I, I, I, I, L, L, L, L, F, P],
         "b200_hstu_gate_cat_fwd": [P, L, P, P, P, P, P, P, I, I, F, F, ctypes.c_ulonglong, P],
         "b200_hstu_gate_cat_bwd": [P, P, L, P, P, P, P, P, P, L, P, P, P, P, I, I, I, F, ctypes.c_ulonglong, P],

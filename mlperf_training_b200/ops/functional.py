@@ -580,3 +580,40 @@ class RopeBSHDFn(Function):
 
 def rope_bshd(x, cos, sin):
     return RopeBSHDFn.apply(x, cos, sin)
+
+
+# --------------------------------------------------------------------------------------
+# MoE router projection
+# --------------------------------------------------------------------------------------
+class RouterLogitsFn(Function):
+    """fp32 router logits ``hn W^T`` with ``W [E, d]`` kept in fp32, on the bf16 tensor-core GEMM: the
+    weight is split into a bf16 head and a bf16 remainder (``W = hi + lo`` to ~16 mantissa bits) and the
+    two products accumulate in fp32, so the logits match an fp32-weight GEMM of the bf16 activations to
+    rounding; the backward GEMMs take the logit gradient in bf16 (the reference's Megatron patch runs the
+    router backward in bf16 as well: small_llm_moe_pretraining/primus/patches)."""
+
+    @staticmethod
+    def forward(ctx, hn, router):
+        ctx.save_for_backward(hn, router)
+        if not use_kernels(hn) or hn.dtype != torch.bfloat16 or hn.shape[1] % 8 or router.shape[0] % 8:
+            return hn.float() @ router.float().t()
+        hi = router.detach().to(torch.bfloat16)
+        lo = (router.detach().float() - hi.float()).to(torch.bfloat16)
+        out = K.gemm(hn.contiguous(), hi, out_dtype=torch.float32)
+        K.gemm(hn.contiguous(), lo, out=out, accumulate=True)
+        return out
+
+    @staticmethod
+    def backward(ctx, dl):
+        hn, router = ctx.saved_tensors
+        if not use_kernels(hn) or hn.dtype != torch.bfloat16 or hn.shape[1] % 8 or router.shape[0] % 8:
+            return (dl.float() @ router.float()).to(hn.dtype), (dl.float().t() @ hn.float()).to(router.dtype)
+        g = dl.to(torch.bfloat16).contiguous()
+        dhn = K.gemm(g, router.detach().to(torch.bfloat16).contiguous(), b_mn_major=True) if ctx.needs_input_grad[0] else None
+        dw = K.gemm(g, hn.contiguous(), a_mn_major=True, b_mn_major=True, out_dtype=torch.float32).to(router.dtype) \
+            if ctx.needs_input_grad[1] else None
+        return dhn, dw
+
+
+def router_logits(hn, router):
+    return RouterLogitsFn.apply(hn, router)

@@ -290,3 +290,51 @@ def test_torch_dist_checkpoint_loads_into_pipeline_stages(tmp_path):
     assert torch.equal(chunks[1].lm_head, full.lm_head)
     names = [n for n, _ in MG.global_named_parameters(chunks)]
     assert len(names) == len(set(names)) and all(n in dict(full.named_parameters()) for n in names)
+
+
+def test_hf_llama_directory_converts_to_a_loadable_torch_dist_checkpoint(tmp_path):
+    """Hugging Face names / split projections -> fused GPT parameters -> torch_dist files that load back."""
+    import json
+
+    import torch
+
+    from mlperf_training_b200.checkpoint.megatron import load_torch_dist
+    from mlperf_training_b200.data.prep import convert_hf_llama
+    from mlperf_training_b200.models.gpt import GPT, PRESETS
+    cfg = PRESETS["llama2-70b"]()
+    small = dict(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, intermediate_size=128, vocab_size=96)
+    hd = cfg.head_dim = 16
+    g = torch.Generator().manual_seed(0)
+    hf = {"model.embed_tokens.weight": torch.randn(96, 64, generator=g), "model.norm.weight": torch.ones(64),
+          "lm_head.weight": torch.randn(96, 64, generator=g)}
+    for i in range(2):
+        p = f"model.layers.{i}."
+        hf[p + "input_layernorm.weight"] = torch.ones(64)
+        hf[p + "post_attention_layernorm.weight"] = torch.ones(64)
+        hf[p + "self_attn.q_proj.weight"] = torch.randn(4 * hd, 64, generator=g)
+        hf[p + "self_attn.k_proj.weight"] = torch.randn(2 * hd, 64, generator=g)
+        hf[p + "self_attn.v_proj.weight"] = torch.randn(2 * hd, 64, generator=g)
+        hf[p + "self_attn.o_proj.weight"] = torch.randn(64, 4 * hd, generator=g)
+        hf[p + "mlp.gate_proj.weight"] = torch.randn(128, 64, generator=g)
+        hf[p + "mlp.up_proj.weight"] = torch.randn(128, 64, generator=g)
+        hf[p + "mlp.down_proj.weight"] = torch.randn(64, 128, generator=g)
+    src = tmp_path / "hf"
+    src.mkdir()
+    (src / "config.json").write_text(json.dumps(small))
+    torch.save(hf, src / "pytorch_model.bin")
+    import mlperf_training_b200.models.gpt as G
+    orig = G.PRESETS["llama2-70b"]
+    G.PRESETS["llama2-70b"] = lambda: G.GPTConfig(head_dim=16, dtype="fp32", seq_len=32)
+    try:
+        out = convert_hf_llama(str(src), str(tmp_path / "ckpt"), dtype="fp32")
+        c = G.PRESETS["llama2-70b"]()
+        for k, v in dict(n_layers=2, hidden=64, n_heads=4, n_kv_heads=2, ffn_hidden=128, vocab_size=96).items():
+            setattr(c, k, v)
+        m = GPT(c, device="cpu", seed=5)
+        load_torch_dist(m, str(tmp_path / "ckpt"))
+    finally:
+        G.PRESETS["llama2-70b"] = orig
+    assert "iter_0000000" in out
+    assert torch.equal(m.blocks[1].w_qkv[:4 * hd], hf["model.layers.1.self_attn.q_proj.weight"])
+    assert torch.equal(m.blocks[0].mlp.w_gate_up[128:], hf["model.layers.0.mlp.up_proj.weight"])
+    assert torch.equal(m.lm_head, hf["lm_head.weight"])
