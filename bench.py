@@ -62,6 +62,9 @@ def parse():
                     help="GEMM precision of the linears (attention, norms, residual stream stay bf16)")
     ap.add_argument("--zero-stage", type=int, default=1, choices=[1, 3],
                     help="1: optimizer state sharded, parameters replicated; 3: block matrices sharded and gathered per block")
+    ap.add_argument("--check", action="store_true",
+                    help="instead of timing: 3 steps with the in-kernel (fused / NVLS) data-parallel step and 3 with the "
+                         "NCCL step on the same data, compare losses and gradient norms, print RESULT ok=...")
     ap.add_argument("--stock", default="mxfp8,bf16",
                     help="stock-PyTorch arms timed after the package's own arm: comma list of mxfp8, bf16, or none")
     ap.add_argument("--stock-steps", type=int, default=5, help="timed steps of each stock arm (3 warm-up steps)")
@@ -108,6 +111,49 @@ def time_stock_arm(args, cfg, opt, tc, device, world, rank, precision: str) -> d
             "stack": ("torch._scaled_mm MXFP8 (cuBLASLt block-scaled) linears" if precision == "mxfp8" else "cuBLAS bf16 linears")
                      + ", SDPA, F.rms_norm, F.cross_entropy, torch AdamW(fused), "
                      + (("FSDP2 fully_shard" if args.stock_parallel == "fsdp" else "DDP") if world > 1 else "single GPU")}
+
+
+def check_comm_paths(args, cfg, opt, device, world, rank) -> int:
+    """Correctness of the in-kernel data-parallel step at this N: the same model, seed and batches through
+    ``comm=fused`` (peer loads / stores or NVLS multimem) and through ``comm=nccl``; losses and global gradient
+    norms of 3 steps must agree."""
+    import gc
+
+    import torch
+    import torch.distributed as dist
+
+    from mlperf_training_b200.ops import _lib
+    from mlperf_training_b200.trainer.pretrain import PretrainTrainer, TrainConfig, synthetic_tokens
+
+    host = synthetic_tokens(3, args.local_batch, cfg.seq_len, cfg.vocab_size, seed=0, rank=rank)
+    seen = {}
+    for comm in ("fused", "nccl"):
+        tc = TrainConfig(micro_batch=args.micro_batch, local_batch=args.local_batch, warmup_steps=64, seed=0, comm=comm,
+                         zero_stage=args.zero_stage)
+        tr = PretrainTrainer(cfg, opt, tc, device)
+        losses, norms = [], []
+        for i in range(3):
+            losses.append(tr.train_step(host[i]))
+            norms.append(tr.engine.grad_norm())
+        torch.cuda.synchronize()
+        _lib.check_status(f"check {comm}")
+        seen[comm] = (losses, norms)
+        del tr
+        gc.collect()
+        torch.cuda.empty_cache()
+    ok = all(abs(a - b) <= 2e-2 * max(abs(b), 1.0) for a, b in zip(seen["fused"][0], seen["nccl"][0]))
+    ok &= all(abs(a - b) <= 3e-2 * max(abs(b), 1e-3) for a, b in zip(seen["fused"][1], seen["nccl"][1]))
+    flag = torch.tensor([1.0 if ok else 0.0], device=device)
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(json.dumps({"check": "comm fused vs nccl", "n_gpus": world, "zero_stage": args.zero_stage, "ok": bool(flag.item()),
+                          "loss_fused": seen["fused"][0], "loss_nccl": seen["nccl"][0],
+                          "grad_norm_fused": seen["fused"][1], "grad_norm_nccl": seen["nccl"][1]}))
+        print(f"RESULT ok={bool(flag.item())}", flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0 if flag.item() == 1.0 else 1
 
 
 class ClockSampler:
@@ -201,6 +247,8 @@ def main() -> int:
     tc = TrainConfig(micro_batch=args.micro_batch, local_batch=args.local_batch, warmup_steps=64, seed=0, comm=args.comm,
                      zero_stage=args.zero_stage)
 
+    if args.check:
+        return check_comm_paths(args, cfg, opt, device, world, rank)
     if args.impl == "baseline":
         from baseline.torch_gpt import BaselineTrainer
         cfg.precision = args.precision
