@@ -44,27 +44,45 @@ __global__ void runs_kernel(const long long* __restrict__ keys, const long long*
   }
 }
 
-// out[s, :] = sum over sorted positions r in [seg[s], seg[s + 1]) of src[perm[r], :]; one CTA per run
+// out[s, :] = sum over sorted positions r in [seg[s], seg[s + 1]) of src[perm[r], :]; one warp per run, a lane
+// owns 8-element vectors (16-byte loads of bf16 rows), runs are taken grid-stride
 template <typename Out>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 segment_sum_gather_kernel(const __nv_bfloat16* __restrict__ src_bf16, const float* __restrict__ src_f32,
                           const long long* __restrict__ perm, const long long* __restrict__ seg,
                           const long long* __restrict__ n_seg, int D, Out* __restrict__ out, long long src_rows, int* status) {
   const long long total = *n_seg;
-  for (long long s = blockIdx.x; s < total; s += gridDim.x) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (blockIdx.x * 256ll + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * 256) >> 5;
+  const int nvec = D / 8;
+  for (long long s = warp0; s < total; s += nwarps) {
     const long long lo = seg[s], hi = seg[s + 1];
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-      float acc = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (long long r = lo; r < hi; ++r) {
         const long long row = perm != nullptr ? perm[r] : r;
         if (row < 0 || row >= src_rows) {               // a permutation entry outside the gradient matrix
-          if (d == 0) B200_BOUNDS_REPORT(status, 1601);
+          if (v == 0) B200_BOUNDS_REPORT(status, 1601);
           continue;
         }
-        acc += src_bf16 != nullptr ? __bfloat162float(src_bf16[row * D + d]) : src_f32[row * D + d];
+        if (src_bf16 != nullptr) {
+          const uint4 u = *reinterpret_cast<const uint4*>(src_bf16 + row * D + v * 8);
+          const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+          acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+        } else {
+          const float4 a = *reinterpret_cast<const float4*>(src_f32 + row * D + v * 8);
+          const float4 b = *reinterpret_cast<const float4*>(src_f32 + row * D + v * 8 + 4);
+          acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+        }
       }
-      if constexpr (sizeof(Out) == 2) out[s * D + d] = __float2bfloat16_rn(acc);
-      else out[s * D + d] = acc;
+      if constexpr (sizeof(Out) == 2) {
+        *reinterpret_cast<uint4*>(out + s * D + v * 8) =
+            make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+      } else {
+        *reinterpret_cast<float4*>(out + s * D + v * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        *reinterpret_cast<float4*>(out + s * D + v * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      }
     }
   }
 }
@@ -139,13 +157,16 @@ B200_API int b200_segment_sum_gather(const void* src, int src_is_f32, long long 
                                      const long long* seg, const long long* n_seg, long long max_seg, int D, void* out,
                                      int out_bf16, void* stream) {
   if (max_seg <= 0) return 0;
-  const int grid = (int)(max_seg < 148 * 32 ? max_seg : 148 * 32);
+  if (D % 8 != 0 || ((uintptr_t)src & 15) || ((uintptr_t)out & 15))
+    return b200::fail(1605, "segment_sum_gather: D=%d must be a multiple of 8 and the matrices 16-byte aligned", D);
+  const long long want = (max_seg + 7) / 8;            // 8 warps (runs) per CTA
+  const int grid = (int)(want < 148 * 16 ? want : 148 * 16);
   const __nv_bfloat16* sb = src_is_f32 ? nullptr : (const __nv_bfloat16*)src;
   const float* sf = src_is_f32 ? (const float*)src : nullptr;
   if (out_bf16)
-    segment_sum_gather_kernel<__nv_bfloat16><<<grid, 128, 0, (cudaStream_t)stream>>>(sb, sf, perm, seg, n_seg, D, (__nv_bfloat16*)out, src_rows, b200::status_ptr());
+    segment_sum_gather_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(sb, sf, perm, seg, n_seg, D, (__nv_bfloat16*)out, src_rows, b200::status_ptr());
   else
-    segment_sum_gather_kernel<float><<<grid, 128, 0, (cudaStream_t)stream>>>(sb, sf, perm, seg, n_seg, D, (float*)out, src_rows, b200::status_ptr());
+    segment_sum_gather_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(sb, sf, perm, seg, n_seg, D, (float*)out, src_rows, b200::status_ptr());
   b200::count_launch();
   return b200::check_launch("segment_sum_gather");
 }

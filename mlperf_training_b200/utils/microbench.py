@@ -2,7 +2,7 @@
 each next to the stock library call for the same problem (cuBLAS through ``torch.matmul``,
 ``scaled_dot_product_attention``), with an L2 flush between timed launches.
 
-    python -m mlperf_training_b200.utils.microbench gemm attention elementwise [--quick]
+    python -m mlperf_training_b200.utils.microbench gemm mxfp8 fp8 attention elementwise grouped hstu glue sparse [--quick]
 
 Prints one JSON object per measurement.
 """
@@ -187,6 +187,101 @@ def bench_elementwise(quick: bool) -> None:
     _lib.check_status("elementwise")
 
 
+def bench_fp8(quick: bool) -> None:
+    """Per-tensor FP8 GEMM (e4m3 x e4m3, e5m2 x e4m3) and its quantiser."""
+    from ..ops import fp8
+    shapes = [(M, N, K, tag) for (M, N, K, a_mn, b_mn, tag) in GEMM_SHAPES if not a_mn and not b_mn]
+    for M, N, K, tag in (shapes[:3] if quick else shapes):
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = torch.randn(N, K, device="cuda").bfloat16()
+        for fa in ("e4m3", "e5m2"):
+            sa, sb = fp8.DelayedScale(fa, "cuda"), fp8.DelayedScale("e4m3", "cuda")
+            sa.prepare(a, 0)
+            sb.prepare(b, 0)
+            ms_q = time_ms(lambda: fp8.quantize(a, sa, want_row=True, want_col=True))
+            a_op, _ = fp8.quantize(a, sa)
+            b_op, _ = fp8.quantize(b, sb)
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            ms = time_ms(lambda: fp8.gemm(a_op, b_op, out=out))
+            emit(kernel="gemm_fp8", tag=tag, a_fmt=fa, M=M, N=N, K=K, ms=round(ms, 4), tflops=round(2.0 * M * N * K / ms / 1e9, 1),
+                 quant_dual_ms=round(ms_q, 4), quant_gbs=round(M * K * 4.0 / ms_q / 1e6, 1))
+        _lib.check_status(tag)
+        del a, b
+
+
+def bench_grouped(quick: bool) -> None:
+    """Grouped (per-expert) GEMMs of the GPT-OSS MoE layer: 32 experts, hidden 2880, top-4."""
+    from ..ops import moe_ops as M
+    T, E, k, D, Fh = (4096 if quick else 32768), 32, 4, 2880, 2880
+    logits = torch.randn(T, E, device="cuda")
+    idx, w, cnt = M.router_topk(logits, k)
+    seg, te, dest, rows = M.plan(idx, cnt, E)
+    x = torch.randn(T, D, device="cuda").bfloat16()
+    w1 = (torch.randn(E, 2 * Fh, D, device="cuda") * 0.02).bfloat16()
+    xp = M.permute_rows(x, dest, k, rows)
+    ms = time_ms(lambda: M.grouped_rows(xp, w1, te, seg))
+    emit(kernel="gemm_grouped fc1", T=T, pairs=T * k, E=E, D=D, N=2 * Fh, ms=round(ms, 4),
+         tflops=round(2.0 * T * k * D * 2 * Fh / ms / 1e9, 1))
+    ms_p = time_ms(lambda: M.permute_rows(x, dest, k, rows))
+    emit(kernel="permute_rows", T=T, k=k, D=D, ms=round(ms_p, 4), gbs=round(T * D * 2 * (1 + k) / ms_p / 1e6, 1))
+    _lib.check_status("grouped")
+
+
+def bench_hstu(quick: bool) -> None:
+    """Jagged pointwise-SiLU attention at the HSTU benchmark shape: log-normal lengths, 4 heads of 128."""
+    from ..ops.hstu_ops import hstu_attention
+    g = torch.Generator().manual_seed(0)
+    B = 32 if quick else 128
+    lens = torch.exp(torch.randn(B, generator=g) + math.log(512)).clamp(16, 4095).long() + 1
+    offs = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)]).to(torch.int32).cuda()
+    L, H, D, N = int(lens.sum()), 4, 128, 4096
+    q, k, v = (torch.randn(L, H, D, device="cuda").bfloat16().requires_grad_(True) for _ in range(3))
+    nt = torch.ones(B, dtype=torch.int32, device="cuda")
+    pairs = float((lens.double() ** 2).sum()) / 2
+    ms_f = time_ms(lambda: hstu_attention(q, k, v, offs, N, D ** -0.5, nt, 0))
+    out = hstu_attention(q, k, v, offs, N, D ** -0.5, nt, 0)
+    do = torch.randn_like(out)
+
+    def bwd():
+        q.grad = k.grad = v.grad = None
+        out.backward(do, retain_graph=True)
+    ms_b = time_ms(bwd)
+    emit(kernel="hstu_attention", B=B, tokens=L, H=H, D=D, fwd_ms=round(ms_f, 4), fwd_tflops=round(4.0 * H * pairs * D / ms_f / 1e9, 1),
+         bwd_ms=round(ms_b, 4), bwd_tflops=round(10.0 * H * pairs * D / ms_b / 1e9, 1))
+    _lib.check_status("hstu")
+
+
+def bench_glue(quick: bool) -> None:
+    """MMDiT glue kernels at the FLUX shape: 32 samples x 512 tokens x 3072."""
+    from ..ops import functional as F
+    B, S, D = (8 if quick else 32), 512, 3072
+    x = torch.randn(B * S, D, device="cuda").bfloat16().requires_grad_(True)
+    mod = torch.randn(B, 3 * D, device="cuda").bfloat16()
+    shift, scale, gate = mod.chunk(3, dim=-1)
+    ms = time_ms(lambda: F.ln_modulate(x, shift, scale, B, 1e-6))
+    emit(kernel="ln_modulate_fwd", T=B * S, D=D, ms=round(ms, 4), gbs=round(2 * B * S * D * 2 / ms / 1e6, 1))
+    y = torch.randn(B * S, D, device="cuda").bfloat16()
+    ms = time_ms(lambda: F.gate_residual(x, y, gate, B))
+    emit(kernel="gate_residual_fwd", T=B * S, D=D, ms=round(ms, 4), gbs=round(3 * B * S * D * 2 / ms / 1e6, 1))
+    _lib.check_status("glue")
+
+
+def bench_sparse(quick: bool) -> None:
+    """Sort / unique / segment reduction of the embedding path at the HSTU step size."""
+    from ..ops import sort
+    n, rows, D = (200_000 if quick else 2_000_000), 400_000_000, 256
+    u = torch.rand(n, device="cuda")
+    ids = (torch.exp(u * math.log(rows)).long() - 1).clamp(0, rows - 1)        # Zipf-like skew
+    ms = time_ms(lambda: sort.sort_unique(ids, sort.key_bits_for(rows)))
+    s = sort.sort_unique(ids, sort.key_bits_for(rows))
+    g = torch.randn(n, D, device="cuda").bfloat16()
+    ms_s = time_ms(lambda: sort.segment_sum(g, s, torch.bfloat16))
+    emit(kernel="sort_unique", n=n, key_bits=sort.key_bits_for(rows), ms=round(ms, 4), mkeys_per_s=round(n / ms / 1e3, 1),
+         unique=s.n_unique())
+    emit(kernel="segment_sum_gather", n=n, D=D, ms=round(ms_s, 4), gbs=round(n * D * 2 * 1.5 / ms_s / 1e6, 1))
+    _lib.check_status("sparse")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("what", nargs="*", default=["gemm", "attention", "elementwise"])
@@ -200,7 +295,8 @@ def main(argv=None) -> int:
         print("microbench needs a CUDA device", file=sys.stderr)
         return 1
     for w in args.what:
-        {"gemm": bench_gemm, "mxfp8": bench_mxfp8, "attention": bench_attention, "elementwise": bench_elementwise}[w](args.quick)
+        {"gemm": bench_gemm, "mxfp8": bench_mxfp8, "fp8": bench_fp8, "attention": bench_attention, "elementwise": bench_elementwise,
+         "grouped": bench_grouped, "hstu": bench_hstu, "glue": bench_glue, "sparse": bench_sparse}[w](args.quick)
     return 0
 
 

@@ -19,6 +19,8 @@ def _free_port() -> int:
 
 
 def _run(worker: str, nproc: int = 2, timeout: int = 600, extra_env: dict | None = None, args=()):
+    # B200_TEST_NPROC=8 runs the same workers on every GPU of the box (the W = 8 result checks)
+    nproc = min(int(os.environ.get("B200_TEST_NPROC", nproc)), torch.cuda.device_count())
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
