@@ -231,7 +231,7 @@ static int run_pair(const void* a, const void* b, void* d, int M, int N, int K, 
   if (r) return r;
   CUtensorMap tmDt;
   if ((r = make_out_tmap<BN>(&tmD, &tmDt, d, M, N, ldd, epi.out_f32))) return r;
-  PairParams p;
+  PairParams p = {};
   p.M = M; p.N = N; p.K = K;
   p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
   p.a_fmt = 0; p.b_fmt = 0;

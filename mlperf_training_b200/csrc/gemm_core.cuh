@@ -78,15 +78,16 @@ inline int raster_group_m() {
 }
 
 // Drains one accumulator (TMEM address t_row: this warp's lane quarter, first accumulator column)
-// to D rows [row0, row0 + 32) x columns [n0, n0 + BN).  `stg` is this warp's pair of staging buffers,
-// `buf` its running buffer index.  fp32 output and narrow bf16 output leave 32 columns per TMA
+// to D rows [row0, row0 + 32) x columns [n0, n0 + BN) (row0 is checked against e.M; `row_off` is added to
+// the row coordinate of the stores: the first row of the tile's matrix inside a stacked output).  `stg` is
+// this warp's pair of staging buffers, `buf` its running buffer index.  fp32 output and narrow bf16 output leave 32 columns per TMA
 // store (tmD boxes: fp32 32 x 32 with 128-byte swizzle, bf16 32 x 32 with 64-byte swizzle); WIDE
 // bf16 output (BN a multiple of 64) leaves 64 columns per store (box 64 x 32, 128-byte swizzle).
 // A BN of 32 k + 16 ends with one 16-column store through tmTail (fp32: box 16 x 32 with 64-byte
 // swizzle; bf16: box 16 x 32, dense 32-byte rows).
 template <int BN, bool WIDE>
 B200_DEVICE void epilogue_drain(const CUtensorMap* tmD, const CUtensorMap* tmTail, const EpiArgs& e, uint32_t t_row,
-                                int row0, int n0, uint8_t* stg, int& buf, int lane) {
+                                int row0, int n0, uint8_t* stg, int& buf, int lane, int row_off = 0) {
   static_assert(BN % 16 == 0, "accumulator width must be a multiple of 16 columns");
   static_assert(!WIDE || BN % 64 == 0, "64-column stores need BN to be a multiple of 64");
   const int row = row0 + lane;
@@ -141,8 +142,8 @@ B200_DEVICE void epilogue_drain(const CUtensorMap* tmD, const CUtensorMap* tmTai
       __syncwarp();
       if (lane == 0) {
         if (col0 < e.N && row0 < e.M) {
-          if (e.accumulate) tma_reduce_add_2d(tmD, stg + buf * STG_BYTES, col0, row0);
-          else tma_store_2d(tmD, stg + buf * STG_BYTES, col0, row0);
+          if (e.accumulate) tma_reduce_add_2d(tmD, stg + buf * STG_BYTES, col0, row0 + row_off);
+          else tma_store_2d(tmD, stg + buf * STG_BYTES, col0, row0 + row_off);
         }
         tma_store_commit();
       }
@@ -161,8 +162,8 @@ B200_DEVICE void epilogue_drain(const CUtensorMap* tmD, const CUtensorMap* tmTai
       __syncwarp();
       if (lane == 0) {
         if (col0 < e.N && row0 < e.M) {
-          if (e.accumulate) tma_reduce_add_2d(tmD, stg + buf * STG_BYTES, col0, row0);
-          else tma_store_2d(tmD, stg + buf * STG_BYTES, col0, row0);
+          if (e.accumulate) tma_reduce_add_2d(tmD, stg + buf * STG_BYTES, col0, row0 + row_off);
+          else tma_store_2d(tmD, stg + buf * STG_BYTES, col0, row0 + row_off);
         }
         tma_store_commit();
       }
@@ -188,8 +189,8 @@ B200_DEVICE void epilogue_drain(const CUtensorMap* tmD, const CUtensorMap* tmTai
         if (lane == 0) {
           const int cs = col0 - 32;
           if (cs < e.N && row0 < e.M) {
-            if (e.accumulate) tma_reduce_add_2d(tmD, stg + buf * STG_BYTES, cs, row0);
-            else tma_store_2d(tmD, stg + buf * STG_BYTES, cs, row0);
+            if (e.accumulate) tma_reduce_add_2d(tmD, stg + buf * STG_BYTES, cs, row0 + row_off);
+            else tma_store_2d(tmD, stg + buf * STG_BYTES, cs, row0 + row_off);
           }
           tma_store_commit();
         }
@@ -252,8 +253,8 @@ B200_DEVICE void epilogue_drain(const CUtensorMap* tmD, const CUtensorMap* tmTai
     __syncwarp();
     if (lane == 0) {
       if (col0 < e.N && row0 < e.M) {
-        if (e.accumulate) tma_reduce_add_2d(tmTail, stg + buf * STG_BYTES, col0, row0);
-        else tma_store_2d(tmTail, stg + buf * STG_BYTES, col0, row0);
+        if (e.accumulate) tma_reduce_add_2d(tmTail, stg + buf * STG_BYTES, col0, row0 + row_off);
+        else tma_store_2d(tmTail, stg + buf * STG_BYTES, col0, row0 + row_off);
       }
       tma_store_commit();
     }
@@ -311,14 +312,60 @@ struct PairCfg {
   static_assert(BN % 16 == 0 && BN <= 256, "N of a 256-row MMA must be a multiple of 16 up to 256");
 };
 
+// Grouped (per-expert) problems on the pair kernel, MXFP8 operands:
+//   mode 1  D[r, :] = A[r, :] * B[e(r)]^T over a row buffer whose expert segments start at multiples of
+//           256 rows; B is the experts' matrices stacked as [(E * N), K], its scale atoms were laid out
+//           with N a multiple of the N tile (a tile never straddles two experts); tiles of 256 rows whose
+//           tile_expert is negative (past the last segment) are skipped by every role
+//   mode 2  D[e] (+)= A[:, seg[e]:seg[e+1]] * B[:, seg[e]:seg[e+1]]^T - the contraction runs over the
+//           expert's rows of the (transposed, K-major) operands; D is the experts' [M, N] outputs stacked
+//           as [(E * M), N]; an expert without rows is skipped (accumulate into a zeroed D)
+struct GroupArgs {
+  int mode;                       // 0: plain GEMM
+  int E;
+  const int* tile_expert;         // mode 1: [ceil(M / 256)]
+  const int* seg;                 // mode 2: [E + 1], multiples of 256
+};
+
+struct TileInfo {
+  int mb, nb, e, kb0, nkb;
+  bool valid;
+};
+
 struct PairParams {
-  int M, N, K;                    // K in elements (bf16) or bytes (e4m3)
+  GroupArgs grp;
+  int M, N, K;                    // K in elements (bf16) or bytes (e4m3); mode 2: M, N per expert, K = all rows
   int a_mn_major, b_mn_major;     // bf16 only
   int a_fmt, b_fmt;               // FP8 only: 0 = e4m3, 1 = e5m2
   int group_m;
   EpiArgs epi;
   int* status;
 };
+
+// Tile t of the launch: its row / column tile, expert and range of k stages (kb_elems = contraction
+// elements per stage).
+B200_DEVICE TileInfo tile_info(int t, int num_m, int num_n, int num_kb, int kb_elems, const PairParams& p) {
+  TileInfo ti;
+  ti.e = 0; ti.kb0 = 0; ti.nkb = num_kb; ti.valid = true;
+  if (p.grp.mode == 2) {
+    const int per = num_m * num_n;
+    ti.e = t / per;
+    const int r = t - ti.e * per;
+    ti.nb = r / num_m;
+    ti.mb = r - ti.nb * num_m;
+    const int lo = p.grp.seg[ti.e], hi = p.grp.seg[ti.e + 1];
+    ti.kb0 = lo / kb_elems;
+    ti.nkb = (hi - lo) / kb_elems;
+    ti.valid = ti.nkb > 0;
+  } else {
+    tile_coords(t, num_m, num_n, p.group_m, ti.mb, ti.nb);
+    if (p.grp.mode == 1) {
+      ti.e = p.grp.tile_expert[ti.mb];
+      ti.valid = ti.e >= 0;
+    }
+  }
+  return ti;
+}
 
 template <int KIND, int BN, int KSUB>
 __global__ void __launch_bounds__(PairCfg<KIND, BN, KSUB>::THREADS, 1)
@@ -356,7 +403,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_pairs = gridDim.x >> 1;
   const int num_m = (p.M + 255) / 256;
   const int num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
+  const int num_tiles = (p.grp.mode == 2 ? p.grp.E : 1) * num_m * num_n;
   const int num_kb = (p.K + KB_ELEMS * KSUB - 1) / (KB_ELEMS * KSUB);
   const int num_kb128 = (p.K + KB_ELEMS - 1) / KB_ELEMS;   // 128-byte K blocks (scale groups of the MX layout)
 
@@ -387,10 +434,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-        int mb, nb; tile_coords(t, num_m, num_n, p.group_m, mb, nb);
+        const TileInfo ti = tile_info(t, num_m, num_n, num_kb, KB_ELEMS * KSUB, p);
+        if (!ti.valid) continue;
+        const int mb = ti.mb;
+        const int nb = ti.nb + (p.grp.mode == 1 ? ti.e * num_n : 0);   // column tile inside the stacked B
         const int m0 = mb * 256 + (int)rank * 128;          // this CTA's rows of A
-        const int n0 = nb * BN + (int)rank * C::BNH;        // this CTA's rows of B
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int n0 = ti.nb * BN + (int)rank * C::BNH + (p.grp.mode == 1 ? ti.e * p.N : 0);   // this CTA's rows of B
+        for (int kb = ti.kb0; kb < ti.kb0 + ti.nkb; ++kb) {
           if (!mbar_wait_spin(&empty[stage], phase ^ 1, abort_flag, p.status, 310)) { ok = false; break; }
           const uint32_t bar = mapa_u32(smem_u32(&full[stage]), 0);
           if (rank == 0) mbar_expect_tx(&full[stage], 2 * C::AB_STAGE);
@@ -440,13 +490,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0; uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
+      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+        const TileInfo ti = tile_info(t, num_m, num_n, num_kb, KB_ELEMS * KSUB, p);
+        if (!ti.valid) continue;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+        ++it;
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag, p.status, 320)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
+        for (int kb = 0; kb < ti.nkb && ok; ++kb) {
           if (!mbar_wait_spin(&full[stage], phase, abort_flag, p.status, 321)) { ok = false; break; }
           if (MX && !mbar_wait_spin(&sfrdy[stage], phase, abort_flag, p.status, 322)) { ok = false; break; }
           tc_fence_after();
@@ -489,14 +542,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int buf = 0;
     int it = 0;
     bool ok = true;
-    for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
-      int mb, nb; tile_coords(t, num_m, num_n, p.group_m, mb, nb);
+    for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+      const TileInfo ti = tile_info(t, num_m, num_n, num_kb, KB_ELEMS * KSUB, p);
+      if (!ti.valid) continue;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      ++it;
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, p.status, 330)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
-      epilogue_drain<BN, (BN % 64 == 0)>(&tmD, &tmDt, p.epi, t_row, mb * 256 + (int)rank * 128 + q * 32, nb * BN, stg, buf, lane);
+      epilogue_drain<BN, (BN % 64 == 0)>(&tmD, &tmDt, p.epi, t_row, ti.mb * 256 + (int)rank * 128 + q * 32, ti.nb * BN, stg, buf,
+                                         lane, p.grp.mode == 2 ? ti.e * p.M : 0);
       // all TMEM reads of this accumulator are complete (tcgen05.wait::ld inside): hand it back to the leader
       tc_fence_before();
       __syncwarp();
@@ -514,7 +570,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int stage = 0; uint32_t phase = 0;
     bool ok = true;
     for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-      for (int kb = 0; kb < num_kb; ++kb) {
+      const TileInfo ti = tile_info(t, num_m, num_n, num_kb, KB_ELEMS * KSUB, p);
+      if (!ti.valid) continue;
+      for (int kb = 0; kb < ti.nkb; ++kb) {
         // the atoms of this stage have landed; its scale sets are free, because the producer loaded the
         // stage only after the MMAs of its previous use had completed
         if (!mbar_wait_spin(&sffull[stage], phase, abort_flag, p.status, 340)) { ok = false; break; }
@@ -596,7 +654,7 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
     max_pairs[dev] = n;
   }
   const int num_m = (p.M + 255) / 256, num_n = (p.N + BN - 1) / BN;
-  const int tiles = num_m * num_n;
+  const int tiles = (p.grp.mode == 2 ? p.grp.E : 1) * num_m * num_n;
   const int pairs = tiles < max_pairs[dev] ? tiles : max_pairs[dev];
   cfg.gridDim = dim3(2 * pairs, 1, 1);
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmSFA, tmSFB, tmD, tmDt, p);

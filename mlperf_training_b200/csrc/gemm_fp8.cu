@@ -30,7 +30,7 @@ B200_API int b200_gemm_fp8(const void* a_q, const void* b_q, void* d, int M, int
   epi.ldr = ldr;
   epi.alpha = alpha;
   epi.alpha_a = inv_scale_a; epi.alpha_b = inv_scale_b;
-  PairParams p;
+  PairParams p = {};
   p.M = M; p.N = N; p.K = K;
   p.a_mn_major = 0; p.b_mn_major = 0;
   p.a_fmt = a_e5m2 ? 1 : 0; p.b_fmt = b_e5m2 ? 1 : 0;

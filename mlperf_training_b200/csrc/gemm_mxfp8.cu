@@ -275,7 +275,7 @@ static int run_pair(const void* a_q, const void* sfa, const void* b_q, const voi
   if ((r = b200::make_tmap_2d(&tmSFB, b200::DT_I32, sfb, 128, b_rows, 512, 128, ksub * atoms, b200::SWZ_NONE))) return r;
   CUtensorMap tmDt;
   if ((r = make_out_tmap<BN>(&tmD, &tmDt, d, M, N, ldd, epi.out_f32))) return r;
-  PairParams p;
+  PairParams p = {};
   p.M = M; p.N = N; p.K = K;
   p.a_mn_major = 0; p.b_mn_major = 0;
   p.a_fmt = 0; p.b_fmt = 0;

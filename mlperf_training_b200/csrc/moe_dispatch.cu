@@ -74,6 +74,70 @@ __global__ void zero_pad_rows_kernel(__nv_bfloat16* __restrict__ buf, const int*
     *reinterpret_cast<uint4*>(buf + (lo + i / vpr) * D + (i % vpr) * 8) = make_uint4(0, 0, 0, 0);
 }
 
+// Routing tables of the peer-memory dispatch from the all-gathered per-expert counts, in one launch.
+//   allc [W, E]   pairs every rank routes to every (global) expert
+//   seg  [E + 1]  offsets of this rank's pairs sorted by global expert (unpadded)
+// Every expert's segment on its owner starts at a multiple of `pad` rows; inside it the sources' rows follow in
+// rank order.  Outputs: dst_rank / dst_row [n] for this rank's sorted pairs (row -1 = beyond the slab capacity),
+// seg2 [L + 1] / cnt2 [L] / tile_expert [cap / pad] for the experts this rank owns.
+constexpr int ROUTE_MAX_E = 1024;
+__global__ void __launch_bounds__(256)
+ep_route_kernel(const int* __restrict__ allc, const int* __restrict__ seg, int W, int E, int L, int rank, int pad,
+                long long cap, long long n, int* __restrict__ dst_rank, int* __restrict__ dst_row, int* __restrict__ seg2,
+                int* __restrict__ cnt2, int* __restrict__ tile_expert, int n_tiles) {
+  __shared__ long long base[ROUTE_MAX_E];         // first row of this rank's pairs of expert e on the owner
+  __shared__ int padded[ROUTE_MAX_E];
+  __shared__ int my_seg[ROUTE_MAX_E + 1];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int tot = 0, before = 0;
+    for (int w = 0; w < W; ++w) {
+      const int c = allc[w * E + e];
+      tot += c;
+      if (w < rank) before += c;
+    }
+    padded[e] = (tot + pad - 1) / pad * pad;
+    base[e] = before;
+    if (blockIdx.x == 0 && e / L == rank) cnt2[e - rank * L] = tot;
+  }
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) my_seg[e] = seg[e];
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    long long start = 0;
+    for (int j = (e / L) * L; j < e; ++j) start += padded[j];
+    base[e] += start;                              // each thread updates only its own entries: no race with the reads of padded[]
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    // this rank's own segments and the expert of every `pad`-row tile of its slab
+    __shared__ long long own[ROUTE_MAX_E + 1];
+    if (threadIdx.x == 0) {
+      long long acc = 0;
+      own[0] = 0;
+      for (int l = 0; l < L; ++l) { acc += padded[rank * L + l]; own[l + 1] = acc; }
+      for (int l = 0; l <= L; ++l) seg2[l] = (int)(own[l] < cap ? own[l] : cap);
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < n_tiles; t += blockDim.x) {
+      const long long row = (long long)t * pad;
+      int e = -1;
+      if (row < own[L]) {
+        int lo = 0, hi = L - 1;
+        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (own[mid] <= row) lo = mid; else hi = mid - 1; }
+        e = lo;
+      }
+      tile_expert[t] = e;
+    }
+  }
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
+    int lo = 0, hi = E - 1;                        // last expert whose segment starts at or before pair i and is not empty before i
+    while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (my_seg[mid] <= i) lo = mid; else hi = mid - 1; }
+    const int e = lo;
+    const long long row = base[e] + (i - my_seg[e]);
+    dst_rank[i] = e / L;
+    dst_row[i] = row < cap ? (int)row : -1;
+  }
+}
+
 int grid_for(long long work) {
   long long g = (work + 255) / 256;
   const long long cap = (long long)b200::sm_count() * 16;
@@ -116,4 +180,16 @@ B200_API int b200_zero_pad_rows(void* buf, const int* seg, const int* count, int
   zero_pad_rows_kernel<<<n_seg, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)buf, seg, count, D, cap);
   b200::count_launch();
   return b200::check_launch("zero_pad_rows");
+}
+
+// See ep_route_kernel.  allc [W, E] int32 (all-gathered counts), seg [E + 1] int32; all pointers on the device.
+B200_API int b200_ep_route(const int* allc, const int* seg, int W, int E, int rank, int pad, long long cap, long long n,
+                           int* dst_rank, int* dst_row, int* seg2, int* cnt2, int* tile_expert, void* stream) {
+  if (W < 1 || E < W || E % W != 0 || E > ROUTE_MAX_E || pad < 1 || cap % pad != 0)
+    return b200::fail(1630, "ep_route: W=%d E=%d pad=%d cap=%lld", W, E, pad, cap);
+  const int n_tiles = (int)(cap / pad);
+  ep_route_kernel<<<grid_for(n > 0 ? n : 1), 256, 0, (cudaStream_t)stream>>>(allc, seg, W, E, E / W, rank, pad, cap, n, dst_rank,
+                                                                           dst_row, seg2, cnt2, tile_expert, n_tiles);
+  b200::count_launch();
+  return b200::check_launch("ep_route");
 }

@@ -66,7 +66,8 @@ B200_DEVICE uint2 quant8(const float (&f)[8], float inv) {
                     pack4_e4m3(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv));
 }
 
-// grid: (C / 128, R / 128); 256 threads.
+// grid: (ceil(C / 128), R / 128); 256 threads.  R is a multiple of 128, C a multiple of 32: in the last column tile
+// the columns past C read as zero and nothing is stored for them (their scale bytes are written as 0).
 //   row pass:    a warp instruction covers 2 rows x 256 bytes of input (lane = 8 elements); a block of
 //                32 elements is 4 lanes, so amax is two shuffles; codes leave as 2 x 128 contiguous bytes.
 //   column pass: 8 lanes walk one column (16 rows each, amax of a 32-block = one shuffle) and write the
@@ -122,11 +123,12 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, in
   const int c0 = blockIdx.x * TILE, r0 = blockIdx.y * TILE;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int sub_row = lane >> 4, chunk = lane & 15;
+  const bool col_live = c0 + chunk * 8 < C;
   uint4 v[8];
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
     const int r = it * 16 + warp * 2 + sub_row;
-    v[it] = produce8<MODE>(x, ldx, aux, ldaux, F, (long long)(r0 + r), c0 + chunk * 8);
+    v[it] = col_live ? produce8<MODE>(x, ldx, aux, ldaux, F, (long long)(r0 + r), c0 + chunk * 8) : make_uint4(0u, 0u, 0u, 0u);
   }
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
@@ -140,7 +142,8 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, in
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
       const uint32_t e = e8m0_from_amax(amax);
-      *reinterpret_cast<uint2*>(q_row + (long long)(r0 + r) * C + c0 + chunk * 8) = quant8(f, scale_inv_from_e8m0(e));
+      if (col_live)
+        *reinterpret_cast<uint2*>(q_row + (long long)(r0 + r) * C + c0 + chunk * 8) = quant8(f, scale_inv_from_e8m0(e));
       if ((chunk & 3) == 0) sfs[0][r][chunk >> 2] = (uint8_t)e;
     }
     if (q_col != nullptr) {
@@ -150,7 +153,7 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, in
   }
   __syncthreads();
   if (q_row != nullptr && tid < TILE) {
-    const long long o = sf_offset(r0 + tid, c0 >> 5, row_tile, (row_tile + 127) >> 7, C >> 7);
+    const long long o = sf_offset(r0 + tid, c0 >> 5, row_tile, (row_tile + 127) >> 7, (C + 127) >> 7);
     *reinterpret_cast<uint32_t*>(sf_row + o) = *reinterpret_cast<const uint32_t*>(&sfs[0][tid][0]);
   }
   if (q_col == nullptr) return;
@@ -171,14 +174,27 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, in
     const float lo[8] = {f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7]};
     const float hi[8] = {f[8], f[9], f[10], f[11], f[12], f[13], f[14], f[15]};
     const uint2 q0 = quant8(lo, inv), q1 = quant8(hi, inv);
-    *reinterpret_cast<uint4*>(q_col + (long long)(c0 + c) * R + r0 + sub * 16) = make_uint4(q0.x, q0.y, q1.x, q1.y);
+    if (c0 + c < C)
+      *reinterpret_cast<uint4*>(q_col + (long long)(c0 + c) * R + r0 + sub * 16) = make_uint4(q0.x, q0.y, q1.x, q1.y);
     if ((sub & 1) == 0) sfs[1][c][sub >> 1] = (uint8_t)e;
   }
   __syncthreads();
-  if (tid < TILE) {
+  if (tid < TILE && c0 + tid < C) {
     const long long o = sf_offset(c0 + tid, r0 >> 5, col_tile, (col_tile + 127) >> 7, R >> 7);
     *reinterpret_cast<uint32_t*>(sf_col + o) = *reinterpret_cast<const uint32_t*>(&sfs[1][tid][0]);
   }
+}
+
+
+template <int MODE>
+int launch_quant(const void* x, long long ldx, const void* aux, long long ldaux, int R, int C, void* q_row, void* sf_row,
+                 int row_tile, void* q_col, void* sf_col, int col_tile, int F, cudaStream_t stream, const char* what) {
+  dim3 grid((C + TILE - 1) / TILE, R / TILE);
+  quant_mxfp8_kernel<MODE><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, R, C, (uint8_t*)q_row, (uint8_t*)sf_row,
+                                                     row_tile, (uint8_t*)q_col, (uint8_t*)sf_col, col_tile,
+                                                     (const __nv_bfloat16*)aux, ldaux, F);
+  b200::count_launch();
+  return b200::check_launch(what);
 }
 
 }  // namespace
@@ -188,52 +204,44 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, in
 B200_API long long b200_mxfp8_sf_bytes(long long rows, long long k, int tile_rows) {
   const long long tiles = (rows + tile_rows - 1) / tile_rows;
   const long long atoms = (tile_rows + 127) / 128;
-  return tiles * (k / 128) * atoms * 512;
+  return tiles * ((k + 127) / 128) * atoms * 512;
 }
 
-// x: bf16 [R, C] with row pitch ldx (elements); R and C multiples of 128.
+// x: bf16 [R, C] with row pitch ldx (elements); R a multiple of 128, C a multiple of 32.
 // q_row / sf_row (row-wise copy, rows tiled by row_tile) and q_col / sf_col (column-wise copy stored
 // transposed as [C, R], rows tiled by col_tile) may each be null.  Scale buffers must be zero-filled
-// by the caller when tile_rows is not a multiple of 128 (padding rows of the last atom are not written).
+// by the caller when tile_rows or the operand's row count is not a multiple of 128 (padding rows of
+// the last atom are not written).
 B200_API int b200_quant_mxfp8(const void* x, long long ldx, int R, int C, void* q_row, void* sf_row, int row_tile,
                               void* q_col, void* sf_col, int col_tile, void* stream) {
-  if (R % 128 != 0 || C % 128 != 0) return b200::fail(700, "quant_mxfp8: R=%d and C=%d must be multiples of 128", R, C);
+  if (R % 128 != 0 || C % 32 != 0 || R <= 0 || C <= 0)
+    return b200::fail(700, "quant_mxfp8: R=%d must be a multiple of 128 and C=%d of 32", R, C);
   if (ldx % 8 != 0 || ((uintptr_t)x & 15) != 0) return b200::fail(701, "quant_mxfp8: input must be 16-byte aligned");
   if ((q_row && (row_tile % 16 != 0 || row_tile <= 0)) || (q_col && (col_tile % 16 != 0 || col_tile <= 0)))
     return b200::fail(702, "quant_mxfp8: tile rows must be positive multiples of 16");
-  dim3 grid(C / 128, R / 128);
-  quant_mxfp8_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, R, C, (uint8_t*)q_row,
-                                                               (uint8_t*)sf_row, row_tile, (uint8_t*)q_col,
-                                                               (uint8_t*)sf_col, col_tile, nullptr, 0, 0);
-  b200::count_launch();
-  return b200::check_launch("quant_mxfp8");
+  return launch_quant<0>(x, ldx, nullptr, 0, R, C, q_row, sf_row, row_tile, q_col, sf_col, col_tile, 0, (cudaStream_t)stream,
+                         "quant_mxfp8");
 }
 
 // Quantised SwiGLU: the codes / scales of a = silu(gate) * up without writing a.
 //   gu: bf16 [R, 2F] (gate columns first), pitch ldgu.  Outputs as b200_quant_mxfp8 for the matrix a [R, F].
 B200_API int b200_quant_swiglu_mxfp8(const void* gu, long long ldgu, int R, int F, void* q_row, void* sf_row, int row_tile,
                                      void* q_col, void* sf_col, int col_tile, void* stream) {
-  if (R % 128 != 0 || F % 128 != 0) return b200::fail(710, "quant_swiglu: R=%d and F=%d must be multiples of 128", R, F);
+  if (R % 128 != 0 || F % 32 != 0 || R <= 0 || F <= 0)
+    return b200::fail(710, "quant_swiglu: R=%d must be a multiple of 128 and F=%d of 32", R, F);
   if (ldgu % 8 != 0 || ((uintptr_t)gu & 15) != 0) return b200::fail(711, "quant_swiglu: input must be 16-byte aligned");
-  dim3 grid(F / 128, R / 128);
-  quant_mxfp8_kernel<1><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, ldgu, R, F, (uint8_t*)q_row,
-                                                               (uint8_t*)sf_row, row_tile, (uint8_t*)q_col,
-                                                               (uint8_t*)sf_col, col_tile, nullptr, 0, F);
-  b200::count_launch();
-  return b200::check_launch("quant_swiglu_mxfp8");
+  return launch_quant<1>(gu, ldgu, nullptr, 0, R, F, q_row, sf_row, row_tile, q_col, sf_col, col_tile, F, (cudaStream_t)stream,
+                         "quant_swiglu_mxfp8");
 }
 
 // Quantised SwiGLU backward: the codes / scales of dgu [R, 2F] (d gate | d up) from da [R, F] and gu [R, 2F].
 B200_API int b200_quant_swiglu_bwd_mxfp8(const void* da, long long ldda, const void* gu, long long ldgu, int R, int F,
                                          void* q_row, void* sf_row, int row_tile, void* q_col, void* sf_col, int col_tile,
                                          void* stream) {
-  if (R % 128 != 0 || F % 128 != 0) return b200::fail(712, "quant_swiglu_bwd: R=%d and F=%d must be multiples of 128", R, F);
+  if (R % 128 != 0 || F % 128 != 0 || R <= 0 || F <= 0)
+    return b200::fail(712, "quant_swiglu_bwd: R=%d and F=%d must be multiples of 128", R, F);
   if (ldgu % 8 != 0 || ldda % 8 != 0 || (((uintptr_t)gu | (uintptr_t)da) & 15) != 0)
     return b200::fail(713, "quant_swiglu_bwd: inputs must be 16-byte aligned");
-  dim3 grid(2 * F / 128, R / 128);
-  quant_mxfp8_kernel<2><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, ldgu, R, 2 * F, (uint8_t*)q_row,
-                                                               (uint8_t*)sf_row, row_tile, (uint8_t*)q_col,
-                                                               (uint8_t*)sf_col, col_tile, (const __nv_bfloat16*)da, ldda, F);
-  b200::count_launch();
-  return b200::check_launch("quant_swiglu_bwd_mxfp8");
+  return launch_quant<2>(gu, ldgu, da, ldda, R, 2 * F, q_row, sf_row, row_tile, q_col, sf_col, col_tile, F, (cudaStream_t)stream,
+                         "quant_swiglu_bwd_mxfp8");
 }

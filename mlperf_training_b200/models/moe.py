@@ -42,25 +42,27 @@ class MoEMLP(nn.Module):
         hn = F.rms_norm(h, norm_w, eps)
         logits = F.router_logits(hn, self.router)          # fp32 logits on the tcgen05 GEMM (split-precision weight)
         idx, w, counts = M.RouterFn.apply(logits, cfg.top_k)
+        prec = M.expert_precision(getattr(cfg, "precision", "bf16"), self.w1, self.w2)
         if self.dispatcher is None:
-            y = M.moe_experts(hn, idx, w, counts, self.w1, self.w2)
+            y = M.moe_experts(hn, idx, w, counts, self.w1, self.w2, prec)
         elif self.ep_comm == "fused" and hn.is_cuda and hn.dtype == torch.bfloat16:
-            y = self._fused_dispatcher(hn.shape[0] * cfg.top_k, hn.device)(hn, idx, w, counts, self.w1, self.w2)
+            y = self._fused_dispatcher(hn.shape[0] * cfg.top_k, hn.device, M.pad_rows(prec))(hn, idx, w, counts, self.w1,
+                                                                                             self.w2, prec)
         else:
-            y = self.dispatcher(hn, idx, w, counts, self.w1, self.w2)
+            y = self.dispatcher(hn, idx, w, counts, self.w1, self.w2, prec)
         return h + y
 
     _shared: dict = {}
 
-    def _fused_dispatcher(self, pairs: int, device):
+    def _fused_dispatcher(self, pairs: int, device, pad: int = M.PAD):
         """Every layer owns its input slab (it is read again in backward); the output and gradient
         slabs of all layers of one (group, shape) are the same buffers."""
-        if self._fused is None or self._fused_pairs != pairs:
-            key = (id(self.ep_group), self.cfg.n_experts, self.cfg.hidden, pairs, str(device))
+        if self._fused is None or self._fused_pairs != (pairs, pad):
+            key = (id(self.ep_group), self.cfg.n_experts, self.cfg.hidden, pairs, pad, str(device))
             first = MoEMLP._shared.get(key)
             self._fused = FusedExpertDispatcher(self.ep_group, self.cfg.n_experts, self.cfg.hidden, pairs, device,
-                                                share_with=first)
-            self._fused_pairs = pairs
+                                                share_with=first, pad=pad)
+            self._fused_pairs = (pairs, pad)
             if first is None:
                 MoEMLP._shared[key] = self._fused
         return self._fused

@@ -65,6 +65,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_unpermute_sum": [P, P, P, I, I, I, P, P],
         "b200_gemm_grouped_rows": [P, P, P, P, I, I, I, I, L, L, I, I, F, P],
         "b200_gemm_grouped_wgrad": [P, P, P, P, I, I, I, I, L, L, I, I, F, P],
+        "b200_gemm_grouped_mx_rows": [P, P, P, P, P, P, I, I, I, I, L, L, L, I, F, P],
+        "b200_gemm_grouped_mx_wgrad": [P, P, P, P, P, P, I, I, I, I, L, L, I, I, F, P],
         "b200_zero_reduce_scatter": [P, I, I, L, L, F, P, P, P],
         "b200_zero_adamw_all_gather": [P, I, I, L, L, P, P, P, P, F, F, F, F, F, I, F, P, F, I, P],
         "b200_zero_reduce_scatter_mc": [P, L, L, F, P, I, P, P],
@@ -78,7 +80,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_gate_residual_bwd": [P, P, P, L, P, P, I, I, I, P],
         "b200_sort_ids": [P, P, P, L, I, P, L, P],
         "b200_unique_segments": [P, P, L, P, P, P, P, P, L, P],
-        "b200_segment_sum_gather": [P, I, L, P, P, P, L, I, P, I, P],
+        "b200_segment_sum_gather": [P, I, L, P, P, P, L, L, I, P, I, P, P],
         "b200_hstu_attn_fwd": [P, P, P, P, P, P, I, L, I, I, I, I, L, L, L, L, F, P],
         "b200_hstu_gate_cat_fwd": [P, L, P, P, P, P, P, P, I, I, F, F, ctypes.c_ulonglong, P],
         "b200_hstu_gate_cat_bwd": [P, P, L, P, P, P, P, P, P, L, P, P, P, P, I, I, I, F, ctypes.c_ulonglong, P],
@@ -86,6 +88,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_scatter_rows_to_peers": [P, P, P, P, L, I, P, I, L, P, P],
         "b200_gather_rows_from_peers": [P, P, P, L, I, P, I, L, P],
         "b200_zero_pad_rows": [P, P, P, I, I, L, P],
+        "b200_ep_route": [P, P, I, I, I, I, L, L, P, P, P, P, P, P],
         "b200_unpermute_bwd": [P, P, P, P, L, I, I, P, P, P],
         "b200_zero_dead_tiles": [P, P, I, I, P],
         "b200_quant_swiglu_mxfp8": [P, L, I, I, P, P, I, P, P, I, P],
@@ -113,6 +116,12 @@ def _declare(lib: ctypes.CDLL) -> None:
     if hasattr(lib, "b200_sort_scratch_bytes"):
         lib.b200_sort_scratch_bytes.argtypes = [L]
         lib.b200_sort_scratch_bytes.restype = c_ll
+    if hasattr(lib, "b200_segment_sum_scratch_elems"):
+        lib.b200_segment_sum_scratch_elems.argtypes = [L, I]
+        lib.b200_segment_sum_scratch_elems.restype = c_ll
+    if hasattr(lib, "b200_gemm_grouped_mx_bn"):
+        lib.b200_gemm_grouped_mx_bn.argtypes = [I]
+        lib.b200_gemm_grouped_mx_bn.restype = c_int
     if hasattr(lib, "b200_zero_grid"):
         lib.b200_zero_grid.restype = c_int
 

@@ -28,6 +28,11 @@ from . import mxfp8 as MX
 _WEIGHT_EPOCH = 0
 
 
+def weight_epoch() -> int:
+    """Counter that advances whenever parameters may have changed outside autograd's version tracking."""
+    return _WEIGHT_EPOCH
+
+
 def bump_weight_epoch() -> None:
     global _WEIGHT_EPOCH
     _WEIGHT_EPOCH += 1

@@ -17,9 +17,31 @@ import torch
 from torch.autograd import Function
 
 from . import kernels as K
+from . import mxfp8
 from ._lib import call, ptr, stream_ptr, use_kernels
 
-PAD = 128
+PAD = 128        # row padding of an expert segment for the bf16 grouped kernels (one 128-row tile)
+PAD_MX = 256     # ... for the block-scaled grouped kernels (one CTA pair works on 256 rows)
+
+
+def pad_rows(precision: str) -> int:
+    """Segment padding the grouped kernels of ``precision`` need."""
+    return PAD_MX if precision == "mxfp8" else PAD
+
+
+def grouped_bn(n: int) -> int:
+    """N tile of the block-scaled grouped GEMM for a per-expert output width ``n`` (0 = unsupported width)."""
+    from . import _lib
+    if _lib.LIB_PATH.exists():
+        return int(_lib.load().b200_gemm_grouped_mx_bn(int(n)))
+    return 192 if n % 192 == 0 else (128 if n % 128 == 0 else 0)
+
+
+def mx_supported(w1: torch.Tensor, w2: torch.Tensor) -> bool:
+    """Whether the expert weights ``w1 [E, 2F, D]`` / ``w2 [E, D, F]`` fit the block-scaled grouped kernels."""
+    _, f2, d = w1.shape
+    f = w2.shape[2]
+    return all(grouped_bn(n) > 0 for n in (f2, d, f)) and d % 32 == 0 and f % 32 == 0
 
 
 def max_rows(pairs: int, n_experts: int, pad: int = PAD) -> int:
@@ -104,21 +126,22 @@ def unpermute_sum(yp: torch.Tensor, dest: torch.Tensor, w: torch.Tensor | None, 
 
 
 def grouped_rows(a: torch.Tensor, b: torch.Tensor, tile_expert: torch.Tensor, seg: torch.Tensor, *,
-                 b_mn_major: bool = False) -> torch.Tensor:
+                 b_mn_major: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
     """``d[r] = a[r] @ op(b[e(r)])^T`` over the padded row buffer.  ``b`` is ``[E, N, K]`` or, with
-    ``b_mn_major``, ``[E, K, N]``."""
+    ``b_mn_major``, ``[E, K, N]``.  ``out``: write the result there (a peer-visible slab) instead of a new tensor."""
     rows, Kd = a.shape
     E = b.shape[0]
     N = b.shape[2] if b_mn_major else b.shape[1]
     if not use_kernels(a) or a.dtype != torch.bfloat16:
-        out = torch.zeros((rows, N), dtype=a.dtype, device=a.device)
+        out = torch.zeros((rows, N), dtype=a.dtype, device=a.device) if out is None else out.zero_()
         s = seg.tolist()
         for e in range(E):
             if s[e + 1] > s[e]:
                 w = b[e].float() if b_mn_major else b[e].float().t()
                 out[s[e]:s[e + 1]] = (a[s[e]:s[e + 1]].float() @ w).to(a.dtype)
         return out
-    out = torch.empty((rows, N), dtype=a.dtype, device=a.device)
+    if out is None:
+        out = torch.empty((rows, N), dtype=a.dtype, device=a.device)
     call("b200_gemm_grouped_rows", ptr(a.contiguous()), ptr(b.contiguous()), ptr(out), ptr(tile_expert), rows, N, Kd, E,
          a.stride(0), out.stride(0), int(b_mn_major), 0, 1.0, stream_ptr())
     # tiles past the last segment are not written: their rows are padding and are never read back
@@ -221,12 +244,13 @@ class GroupedMLPFn(Function):
     gradients accumulate into ``main_grad`` when the parameters carry one."""
 
     @staticmethod
-    def forward(ctx, x, w1, w2, seg, tile_expert):
+    def forward(ctx, x, w1, w2, seg, tile_expert, y_out=None, dx_out=None):
         gu = grouped_rows(x, w1, tile_expert, seg)
         a = K.swiglu_fwd(gu)
-        y = grouped_rows(a, w2, tile_expert, seg)
+        y = grouped_rows(a, w2, tile_expert, seg, out=y_out)
         ctx.save_for_backward(x, gu, w1, w2, seg, tile_expert)
         ctx.refs = (w1, w2)
+        ctx.dx_out = dx_out
         return y
 
     @staticmethod
@@ -242,8 +266,121 @@ class GroupedMLPFn(Function):
         dgu = K.swiglu_bwd(da, gu)
         dgu = _zero_padding(dgu, tile_expert)
         g1 = _wgrad_into(p1, dgu, x, seg, E)
-        dx = grouped_rows(dgu, w1, tile_expert, seg, b_mn_major=True)
-        return dx, g1, g2, None, None
+        dx = grouped_rows(dgu, w1, tile_expert, seg, b_mn_major=True, out=ctx.dx_out)
+        return dx, g1, g2, None, None, None, None
+
+
+# --------------------------------------------------------------------------------------
+# block-scaled (MXFP8) expert MLP
+# --------------------------------------------------------------------------------------
+def _stacked_weight_op(w: torch.Tensor, transposed: bool) -> mxfp8.MXOperand:
+    """Quantised copy of the stacked expert weight ``w [E, N, K]`` (or of every expert's transpose) as one
+    K-major operand of ``E * N`` rows, scale tiles of ``grouped_bn(N)`` rows; cached until the weight changes."""
+    from .linear import weight_epoch
+    key = "_mx_stack_t" if transposed else "_mx_stack"
+    hit = getattr(w, key, None)
+    stamp = (w._version, weight_epoch())
+    if hit is not None and hit[0] == stamp:
+        return hit[1]
+    src = w.detach().transpose(1, 2).contiguous() if transposed else w.detach()
+    E, N, Kd = src.shape
+    op, _ = mxfp8.quantize(src.reshape(E * N, Kd), row_tile=grouped_bn(N))
+    setattr(w, key, (stamp, op))
+    return op
+
+
+def grouped_rows_mx(a: mxfp8.MXOperand, b: mxfp8.MXOperand, tile_expert: torch.Tensor, n_experts: int,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """``d[r] = deq(a)[r] @ deq(b)[e(r) * N : (e(r) + 1) * N]^T`` -> bf16 ``[rows, N]``; ``tile_expert`` names the
+    expert of every 256-row tile (-1: not computed, rows left unwritten)."""
+    rows, Kd = a.rows, a.k
+    N = b.rows // n_experts
+    if not a.is_cuda:
+        A, B = mxfp8.dequantize(a), mxfp8.dequantize(b).view(n_experts, N, Kd)
+        out = torch.zeros((rows, N), dtype=torch.bfloat16) if out is None else out.zero_()
+        for t, e in enumerate(tile_expert.tolist()):
+            if e >= 0:
+                out[t * PAD_MX:(t + 1) * PAD_MX] = (A[t * PAD_MX:(t + 1) * PAD_MX] @ B[e].t()).to(torch.bfloat16)
+        return out
+    if out is None:
+        out = torch.empty((rows, N), dtype=torch.bfloat16, device=a.q.device)
+    call("b200_gemm_grouped_mx_rows", ptr(a.q), ptr(a.sf), ptr(b.q), ptr(b.sf), ptr(out), ptr(tile_expert), rows, N, Kd,
+         n_experts, a.q.stride(0), b.q.stride(0), out.stride(0), 0, 1.0, stream_ptr())
+    return out
+
+
+def grouped_wgrad_mx(dy_t: mxfp8.MXOperand, x_t: mxfp8.MXOperand, seg: torch.Tensor, n_experts: int, out: torch.Tensor):
+    """``out[e] += deq(dy_t)[:, seg[e]:seg[e+1]] @ deq(x_t)[:, seg[e]:seg[e+1]]^T``; both operands are column-wise
+    copies (rows = features, contraction = the padded buffer's rows); ``out`` ``[E, M, N]`` fp32 or bf16."""
+    M, N, T = dy_t.rows, x_t.rows, dy_t.k
+    if not dy_t.is_cuda:
+        A, B = mxfp8.dequantize(dy_t), mxfp8.dequantize(x_t)
+        s = seg.tolist()
+        for e in range(n_experts):
+            out[e] += (A[:, s[e]:s[e + 1]] @ B[:, s[e]:s[e + 1]].t()).to(out.dtype)
+        return out
+    call("b200_gemm_grouped_mx_wgrad", ptr(dy_t.q), ptr(dy_t.sf), ptr(x_t.q), ptr(x_t.sf), ptr(out), ptr(seg), T, M, N,
+         n_experts, dy_t.q.stride(0), x_t.q.stride(0), int(out.dtype == torch.float32), 1, 1.0, stream_ptr())
+    return out
+
+
+class GroupedMLPMXFn(Function):
+    """``GroupedMLPFn`` with every GEMM on block-scaled e4m3 operands: the row buffer is quantised once per
+    use (row-wise copy for the forward / dgrad GEMM, column-wise copy for the weight gradient), SwiGLU and
+    its backward are folded into the quantiser where the width allows, the stacked weights are quantised once
+    per optimizer step.  Expert segments start at multiples of 256 rows."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w2, seg, tile_expert, y_out=None, dx_out=None):
+        E, F2, D = w1.shape
+        F = F2 // 2
+        x_row, x_col = mxfp8.quantize(x, row_tile=mxfp8.A_TILE, col_tile=grouped_bn(D))
+        # rows of tiles past the last segment are never written and never contribute: the row GEMMs skip those
+        # tiles and the weight-gradient contraction stops at the last segment's end
+        gu = grouped_rows_mx(x_row, _stacked_weight_op(w1, False), tile_expert, E)
+        a_row, a_col = mxfp8.quantize_swiglu(gu, row_tile=mxfp8.A_TILE, col_tile=grouped_bn(F))
+        y = grouped_rows_mx(a_row, _stacked_weight_op(w2, False), tile_expert, E, out=y_out)
+        ctx.save_for_backward(gu, w1, w2, seg, tile_expert, x_col.q, x_col.sf, a_col.q, a_col.sf)
+        ctx.refs = (w1, w2)
+        ctx.dx_out = dx_out
+        ctx.dims = (x.shape[0], D, F)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        gu, w1, w2, seg, tile_expert, xq, xsf, aq, asf = ctx.saved_tensors
+        p1, p2 = ctx.refs
+        rows, D, F = ctx.dims
+        E = w1.shape[0]
+        x_col = mxfp8.MXOperand(xq, xsf, D, rows, grouped_bn(D))
+        a_col = mxfp8.MXOperand(aq, asf, F, rows, grouped_bn(F))
+        gy_row, gy_col = mxfp8.quantize(gy.contiguous(), row_tile=mxfp8.A_TILE, col_tile=mxfp8.A_TILE)
+        g2 = _wgrad_into_mx(p2, gy_col, a_col, seg, E)
+        da = grouped_rows_mx(gy_row, _stacked_weight_op(w2, True), tile_expert, E)
+        dgu_row, dgu_col = mxfp8.quantize_swiglu_bwd(da, gu, row_tile=mxfp8.A_TILE, col_tile=mxfp8.A_TILE)
+        g1 = _wgrad_into_mx(p1, dgu_col, x_col, seg, E)
+        dx = grouped_rows_mx(dgu_row, _stacked_weight_op(w1, True), tile_expert, E, out=ctx.dx_out)
+        return dx, g1, g2, None, None, None, None
+
+
+def _wgrad_into_mx(param, dy_t, x_t, seg, E):
+    if not param.requires_grad:
+        return None
+    mg = getattr(param, "main_grad", None)
+    if mg is not None:
+        grouped_wgrad_mx(dy_t, x_t, seg, E, mg)
+        return None
+    out = torch.zeros((E, dy_t.rows, x_t.rows), dtype=torch.float32, device=dy_t.q.device)
+    return grouped_wgrad_mx(dy_t, x_t, seg, E, out).to(param.dtype)
+
+
+def grouped_mlp(x, w1, w2, seg, tile_expert, precision: str = "bf16", y_out=None, dx_out=None):
+    """Expert MLP over a padded row buffer whose segments are padded to ``pad_rows(precision)``.  ``y_out`` /
+    ``dx_out``: buffers of the row buffer's shape that receive the output / the input gradient (peer-visible slabs
+    of the expert-parallel dispatch, filled by the last GEMM of each direction instead of by a copy)."""
+    if precision == "mxfp8":
+        return GroupedMLPMXFn.apply(x, w1, w2, seg, tile_expert, y_out, dx_out)
+    return GroupedMLPFn.apply(x, w1, w2, seg, tile_expert, y_out, dx_out)
 
 
 def _zero_padding(t: torch.Tensor, tile_expert: torch.Tensor) -> torch.Tensor:
@@ -269,12 +406,20 @@ def _wgrad_into(param, dy, x, seg, E):
     return grouped_wgrad(dy, x, seg, E, out_dtype=param.dtype)
 
 
-def moe_experts(x, idx, w, counts, w1, w2):
+def expert_precision(precision: str, w1, w2) -> str:
+    """Precision the expert GEMMs run at: ``mxfp8`` when asked for and the widths fit its tiles, else bf16."""
+    if precision == "mxfp8" and w1.dtype == torch.bfloat16 and mx_supported(w1, w2):
+        return "mxfp8"
+    return "bf16"
+
+
+def moe_experts(x, idx, w, counts, w1, w2, precision: str = "bf16"):
     """Local (all experts on this rank) MoE expert stage: dispatch by permutation, grouped MLP,
     weighted combine.  ``x`` ``[T, D]``; returns ``[T, D]``."""
     T, k = idx.shape
     E = w1.shape[0]
-    seg, tile_expert, dest, rows = plan(idx, counts, E)
+    precision = expert_precision(precision, w1, w2)
+    seg, tile_expert, dest, rows = plan(idx, counts, E, pad=pad_rows(precision))
     xp = PermuteFn.apply(x, dest, k, rows)
-    yp = GroupedMLPFn.apply(xp, w1, w2, seg, tile_expert)
+    yp = grouped_mlp(xp, w1, w2, seg, tile_expert, precision)
     return UnpermuteFn.apply(yp, dest, w, T, k)

@@ -77,12 +77,12 @@ def sf_index(rows: int, k: int, tile_rows: int, device) -> torch.Tensor:
     tile = r // tile_rows
     rr = r - tile * tile_rows
     atom, ra = rr // 128, rr % 128
-    return ((tile * (k // 128) + kc // 4) * atoms + atom) * 512 + (ra % 32) * 16 + (ra // 32) * 4 + (kc % 4)
+    return ((tile * ((k + 127) // 128) + kc // 4) * atoms + atom) * 512 + (ra % 32) * 16 + (ra // 32) * 4 + (kc % 4)
 
 
 def sf_bytes(rows: int, k: int, tile_rows: int) -> int:
     tiles = (rows + tile_rows - 1) // tile_rows
-    return tiles * (k // 128) * ((tile_rows + 127) // 128) * 512
+    return tiles * ((k + 127) // 128) * ((tile_rows + 127) // 128) * 512
 
 
 def sf_plain(op: MXOperand) -> torch.Tensor:
@@ -105,10 +105,10 @@ def quantize(x: torch.Tensor, *, row_tile: int | None = None, col_tile: int | No
     ``row_op`` (when ``row_tile`` is given) has rows = R, contraction = C; ``col_op`` (when
     ``col_tile`` is given) is the transposed copy with rows = C, contraction = R.  The tile
     arguments say how the consuming GEMM tiles the operand's rows: ``A_TILE`` for an A operand,
-    ``b_tile(rows)`` for a B operand.  R and C must be multiples of 128."""
+    ``b_tile(rows)`` for a B operand.  R must be a multiple of 128 and C of 32."""
     R, C = x.shape
-    if R % 128 or C % 128:
-        raise ValueError(f"mxfp8.quantize: shape {R}x{C} must be a multiple of 128 in both dims")
+    if R % 128 or C % 32:
+        raise ValueError(f"mxfp8.quantize: shape {R}x{C}: rows must be a multiple of 128, columns of 32")
     if not use_kernels(x):
         row_op = col_op = None
         if row_tile is not None:
@@ -122,16 +122,7 @@ def quantize(x: torch.Tensor, *, row_tile: int | None = None, col_tile: int | No
         raise TypeError("mxfp8.quantize: bf16 input required")
     if x.stride(1) != 1 or (x.stride(0) * 2) % 16 or x.data_ptr() % 16:
         x = x.contiguous()
-    dev = x.device
-    q_row = sf_row = q_col = sf_col = None
-    if row_tile is not None:
-        q_row = torch.empty((R, C), dtype=torch.uint8, device=dev)
-        n = sf_bytes(R, C, row_tile)
-        sf_row = torch.zeros(n, dtype=torch.uint8, device=dev) if row_tile % 128 else torch.empty(n, dtype=torch.uint8, device=dev)
-    if col_tile is not None:
-        q_col = torch.empty((C, R), dtype=torch.uint8, device=dev)
-        n = sf_bytes(C, R, col_tile)
-        sf_col = torch.zeros(n, dtype=torch.uint8, device=dev) if col_tile % 128 else torch.empty(n, dtype=torch.uint8, device=dev)
+    q_row, sf_row, q_col, sf_col = _alloc_ops(R, C, row_tile, col_tile, x.device)
     call("b200_quant_mxfp8", ptr(x), x.stride(0), R, C, ptr(q_row), ptr(sf_row), row_tile or 0, ptr(q_col),
          ptr(sf_col), col_tile or 0, stream_ptr())
     row_op = MXOperand(q_row, sf_row, R, C, row_tile) if row_tile is not None else None
@@ -139,16 +130,22 @@ def quantize(x: torch.Tensor, *, row_tile: int | None = None, col_tile: int | No
     return row_op, col_op
 
 
+def _sf_buffer(rows: int, k: int, tile: int, dev) -> torch.Tensor:
+    """Scale buffer of an operand; zero-filled when the quantiser leaves padding rows of an atom unwritten."""
+    n = sf_bytes(rows, k, tile)
+    if tile % 128 or rows % 128:
+        return torch.zeros(n, dtype=torch.uint8, device=dev)
+    return torch.empty(n, dtype=torch.uint8, device=dev)
+
+
 def _alloc_ops(R: int, C: int, row_tile, col_tile, dev):
     q_row = sf_row = q_col = sf_col = None
     if row_tile is not None:
         q_row = torch.empty((R, C), dtype=torch.uint8, device=dev)
-        n = sf_bytes(R, C, row_tile)
-        sf_row = torch.zeros(n, dtype=torch.uint8, device=dev) if row_tile % 128 else torch.empty(n, dtype=torch.uint8, device=dev)
+        sf_row = _sf_buffer(R, C, row_tile, dev)
     if col_tile is not None:
         q_col = torch.empty((C, R), dtype=torch.uint8, device=dev)
-        n = sf_bytes(C, R, col_tile)
-        sf_col = torch.zeros(n, dtype=torch.uint8, device=dev) if col_tile % 128 else torch.empty(n, dtype=torch.uint8, device=dev)
+        sf_col = _sf_buffer(C, R, col_tile, dev)
     return q_row, sf_row, q_col, sf_col
 
 
@@ -174,7 +171,7 @@ def quantize_swiglu_bwd(da: torch.Tensor, gu: torch.Tensor, *, row_tile: int | N
     materialising it: same return value as ``quantize(swiglu_bwd(da, gu), ...)``."""
     R, F2 = gu.shape
     F = F2 // 2
-    if not use_kernels(gu):
+    if not use_kernels(gu) or F % 128:      # the fused kernel's tiles must not straddle the gate | up boundary
         from . import kernels as K
         return quantize(K.swiglu_bwd(da, gu), row_tile=row_tile, col_tile=col_tile)
     da = da if (da.stride(1) == 1 and (da.stride(0) * 2) % 16 == 0 and da.data_ptr() % 16 == 0) else da.contiguous()

@@ -97,6 +97,9 @@ def segment_sum(src: torch.Tensor, s: SortedIds, out_dtype=torch.float32, max_se
         return out
     if src.dtype not in (torch.bfloat16, torch.float32) or out_dtype not in (torch.bfloat16, torch.float32):
         raise TypeError("segment_sum: bf16 or fp32 rows")
+    from . import _lib
+    # partial sums of the runs that are too long for one warp (skewed ids): one fp32 row pair per 64 sorted positions
+    partial = torch.empty(int(_lib.load().b200_segment_sum_scratch_elems(n, D)), dtype=torch.float32, device=src.device)
     call("b200_segment_sum_gather", ptr(src.contiguous()), int(src.dtype == torch.float32), src.shape[0], ptr(s.perm), ptr(s.seg), ptr(s.count),
-         out.shape[0], D, ptr(out), int(out_dtype == torch.bfloat16), stream_ptr())
+         n, out.shape[0], D, ptr(out), int(out_dtype == torch.bfloat16), ptr(partial), stream_ptr())
     return out

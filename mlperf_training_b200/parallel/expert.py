@@ -48,7 +48,7 @@ class ExpertParallelDispatcher:
         self.E = n_experts
         self.local = n_experts // self.world
 
-    def __call__(self, x, idx, w, counts, w1, w2):
+    def __call__(self, x, idx, w, counts, w1, w2, precision: str = "bf16"):
         T, k = idx.shape
         W, L = self.world, self.local
         # 1. rows sorted by global expert, unpadded (pad = 1): destination ranks are contiguous
@@ -67,9 +67,9 @@ class ExpertParallelDispatcher:
         local_idx = torch.repeat_interleave(torch.arange(L, device=x.device).repeat(W), recv_counts.reshape(-1),
                                             output_size=n_recv).to(torch.int32).view(-1, 1)
         local_counts = recv_counts.sum(0).to(torch.int32)
-        seg2, tile_expert, dest2, rows2 = M.plan(local_idx, local_counts, L)
+        seg2, tile_expert, dest2, rows2 = M.plan(local_idx, local_counts, L, pad=M.pad_rows(precision))
         xp = M.PermuteFn.apply(recv, dest2, 1, rows2)
-        yp = M.GroupedMLPFn.apply(xp, w1, w2, seg2, tile_expert)
+        yp = M.grouped_mlp(xp, w1, w2, seg2, tile_expert, precision)
         back = M.UnpermuteFn.apply(yp, dest2, None, n_recv, 1)
         # 4. return trip and weighted combine at the source
         ret = _AllToAllRows.apply(back, out_splits, in_splits, self.group)
@@ -125,14 +125,15 @@ class FusedExpertDispatcher:
     """
 
     def __init__(self, group, n_experts: int, hidden: int, max_pairs: int, device, capacity_factor: float = 2.0,
-                 share_with: "FusedExpertDispatcher | None" = None):
+                 share_with: "FusedExpertDispatcher | None" = None, pad: int = M.PAD):
         from .symm import SymmetricBuffer
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.E, self.D = n_experts, hidden
         self.local = n_experts // self.world
-        self.cap = (int(capacity_factor * max_pairs) + self.local * 128 + 127) // 128 * 128
+        self.pad = pad                     # row padding of an expert segment (the grouped kernels' row tile)
+        self.cap = (int(capacity_factor * max_pairs) + self.local * pad + pad - 1) // pad * pad
         mk = lambda: SymmetricBuffer(self.cap * hidden, torch.bfloat16, group, device)
         # The input slab is read again in backward (weight gradients), so every layer owns one; the
         # output and gradient slabs are consumed right after they are filled and are shared between the
@@ -149,10 +150,27 @@ class FusedExpertDispatcher:
     # ------------------------------------------------------------------ routing tables
     def _route(self, counts: torch.Tensor, seg: torch.Tensor, n: int) -> _Route:
         W, L, E, dev = self.world, self.local, self.E, counts.device
+        from ..ops import _lib
+        if _lib.use_kernels(counts):
+            # one exchange of the per-expert counts, then every table in one kernel
+            allc32 = torch.empty((W, E), dtype=torch.int32, device=dev)
+            dist.all_gather_into_tensor(allc32.view(-1), counts.to(torch.int32).contiguous(), group=self.group)
+            r = _Route()
+            r.n = n
+            r.dst_rank = torch.empty(n, dtype=torch.int32, device=dev)
+            r.dst_row = torch.empty(n, dtype=torch.int32, device=dev)
+            r.seg2 = torch.empty(L + 1, dtype=torch.int32, device=dev)
+            r.cnt2 = torch.empty(L, dtype=torch.int32, device=dev)
+            r.tile_expert = torch.empty(self.cap // self.pad, dtype=torch.int32, device=dev)
+            _lib.call("b200_ep_route", _lib.ptr(allc32), _lib.ptr(seg.to(torch.int32).contiguous()), W, E, self.rank, self.pad,
+                      self.cap, n, _lib.ptr(r.dst_rank), _lib.ptr(r.dst_row), _lib.ptr(r.seg2), _lib.ptr(r.cnt2),
+                      _lib.ptr(r.tile_expert), _lib.stream_ptr())
+            return r
         allc = torch.empty((W, E), dtype=torch.int64, device=dev)
         dist.all_gather_into_tensor(allc.view(-1), counts.to(torch.int64).contiguous(), group=self.group)
         tot = allc.sum(0)                                            # rows every expert receives
-        padded = (tot + 127) // 128 * 128
+        pad = self.pad
+        padded = (tot + pad - 1) // pad * pad
         seg_all = (padded.view(W, L).cumsum(1) - padded.view(W, L)).reshape(-1)      # segment start on the owner
         before_me = allc[: self.rank].sum(0)                         # rows of lower ranks inside the segment
         base = seg_all + before_me
@@ -167,7 +185,7 @@ class FusedExpertDispatcher:
         seg2[1:] = padded[mine].cumsum(0)
         r.seg2 = seg2.clamp(max=self.cap).to(torch.int32)
         r.cnt2 = tot[mine].to(torch.int32)
-        tile_start = torch.arange(self.cap // 128, device=dev) * 128
+        tile_start = torch.arange(self.cap // pad, device=dev) * pad
         te = torch.searchsorted(seg2[1:].contiguous(), tile_start, right=True)
         r.tile_expert = torch.where(tile_start < seg2[-1], te, torch.full_like(te, -1)).to(torch.int32)
         return r
@@ -185,21 +203,26 @@ class FusedExpertDispatcher:
 
     def _pull(self, slab_rows: torch.Tensor, route: _Route, slab) -> torch.Tensor:
         from ..ops import _lib
-        slab.barrier()                         # previous readers of this slab are done
-        slab.local.view(self.cap, self.D).copy_(slab_rows)
+        if slab_rows.data_ptr() != slab.local.data_ptr():
+            slab.barrier()                     # previous readers of this slab are done
+            slab.local.view(self.cap, self.D).copy_(slab_rows)
+        # else: the expert GEMM wrote the slab in place.  Its previous readers (the peers' gathers of the layer
+        # before) are ordered before that GEMM by the collective this layer ran since: the exchange of the counts in
+        # forward, the barriers of the gradient push in backward.
         slab.barrier()                         # every owner's slab is complete
         out = torch.empty((route.n, self.D), dtype=torch.bfloat16, device=slab_rows.device)
         _lib.call("b200_gather_rows_from_peers", slab.ptr_array(), _lib.ptr(route.dst_rank), _lib.ptr(route.dst_row),
                   route.n, self.D, _lib.ptr(out), self.world, self.cap, _lib.stream_ptr())
         return out
 
-    def __call__(self, x, idx, w, counts, w1, w2):
+    def __call__(self, x, idx, w, counts, w1, w2, precision: str = "bf16"):
         T, k = idx.shape
         n = T * k
         seg, _, dest, _ = M.plan(idx, counts, self.E, pad=1)       # sorted by global expert, unpadded
         send = M.PermuteFn.apply(x, dest, k, n)
         route = self._route(counts, seg, n)
         xp = _PushRows.apply(send, self, route)
-        yp = M.GroupedMLPFn.apply(xp, w1, w2, route.seg2, route.tile_expert)
+        yp = M.grouped_mlp(xp, w1, w2, route.seg2, route.tile_expert, precision,
+                           y_out=self.slab_y.local.view(self.cap, self.D), dx_out=self.slab_dx.local.view(self.cap, self.D))
         ret = _PullRows.apply(yp, self, route)
         return M.UnpermuteFn.apply(ret, dest, w, T, k)

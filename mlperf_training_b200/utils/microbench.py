@@ -116,6 +116,16 @@ def bench_mxfp8(quick: bool) -> None:
              quant_dual_ms=round(ms_q, 4), quant_gbs=round(M * K * 4.06 / ms_q / 1e6, 1), **lib)
         _lib.check_status(tag)
         del a, b, out, a_op, b_op
+    # the quantisers that carry SwiGLU and its backward (Llama-3.1-8B MLP width)
+    R, F = 8192, (4096 if quick else 14336)
+    gu = torch.randn(R, 2 * F, device="cuda").bfloat16()
+    da = torch.randn(R, F, device="cuda").bfloat16()
+    ms1 = time_ms(lambda: mxfp8.quantize_swiglu(gu, row_tile=mxfp8.A_TILE, col_tile=mxfp8.b_tile(F)))
+    emit(kernel="quant_swiglu_mxfp8", R=R, F=F, ms=round(ms1, 4), gbs=round(R * F * (4 + 2.06) / ms1 / 1e6, 1))
+    ms2 = time_ms(lambda: mxfp8.quantize_swiglu_bwd(da, gu, row_tile=mxfp8.A_TILE, col_tile=mxfp8.A_TILE))
+    emit(kernel="quant_swiglu_bwd_mxfp8", R=R, F=F, ms=round(ms2, 4), gbs=round(R * F * (6 + 4.12) / ms2 / 1e6, 1))
+    _lib.check_status("quant swiglu")
+    del gu, da
 
 
 ATTN_SHAPES = [
@@ -212,7 +222,7 @@ def bench_fp8(quick: bool) -> None:
 def bench_grouped(quick: bool) -> None:
     """Grouped (per-expert) GEMMs of the GPT-OSS MoE layer: 32 experts, hidden 2880, top-4."""
     from ..ops import moe_ops as M
-    T, E, k, D, Fh = (4096 if quick else 32768), 32, 4, 2880, 2880
+    T, E, k, D, Fh = (8192 if quick else 32768), 32, 4, 2880, 2880
     logits = torch.randn(T, E, device="cuda")
     idx, w, cnt = M.router_topk(logits, k)
     seg, te, dest, rows = M.plan(idx, cnt, E)
@@ -225,6 +235,36 @@ def bench_grouped(quick: bool) -> None:
     ms_p = time_ms(lambda: M.permute_rows(x, dest, k, rows))
     emit(kernel="permute_rows", T=T, k=k, D=D, ms=round(ms_p, 4), gbs=round(T * D * 2 * (1 + k) / ms_p / 1e6, 1))
     _lib.check_status("grouped")
+    # the same layer on block-scaled operands (segments padded to 256 rows)
+    from ..ops import mxfp8
+    w2 = (torch.randn(E, D, Fh, device="cuda") * 0.02).bfloat16()
+    seg2, te2, dest2, rows2 = M.plan(idx, cnt, E, pad=M.PAD_MX)
+    xp2 = M.permute_rows(x, dest2, k, rows2)
+    fl = 2.0 * T * k * D * 2 * Fh
+    ms_q = time_ms(lambda: mxfp8.quantize(xp2, row_tile=128, col_tile=M.grouped_bn(D)))
+    a_op, at_op = mxfp8.quantize(xp2, row_tile=128, col_tile=M.grouped_bn(D))
+    b_op = M._stacked_weight_op(w1, False)
+    ms = time_ms(lambda: M.grouped_rows_mx(a_op, b_op, te2, E))
+    emit(kernel="gemm_grouped_mx fc1", T=T, pairs=T * k, rows=rows2, E=E, D=D, N=2 * Fh, ms=round(ms, 4),
+         tflops=round(fl / ms / 1e9, 1), quant_rows_ms=round(ms_q, 4))
+    gu = M.grouped_rows_mx(a_op, b_op, te2, E)
+    _, gt_op = mxfp8.quantize(gu, col_tile=128)
+    acc = torch.zeros(E, 2 * Fh, D, device="cuda")
+    ms = time_ms(lambda: M.grouped_wgrad_mx(gt_op, at_op, seg2, E, acc))
+    emit(kernel="gemm_grouped_mx wgrad fc1 (fp32 accumulate)", T=T, E=E, M=2 * Fh, N=D, ms=round(ms, 4),
+         tflops=round(fl / ms / 1e9, 1), out_gbs=round(E * 2 * Fh * D * 8 / ms / 1e6, 1))
+    xg = x.clone().requires_grad_()
+    p1, p2 = w1.clone().requires_grad_(), w2.clone().requires_grad_()
+    p1.main_grad, p2.main_grad = torch.zeros_like(p1, dtype=torch.float32), torch.zeros_like(p2, dtype=torch.float32)
+    for prec in ("bf16", "mxfp8"):
+        def step():
+            y = M.moe_experts(xg, idx, w, cnt, p1, p2, prec)
+            y.backward(y.detach())
+            p1.grad = p2.grad = xg.grad = None
+        ms = time_ms(step)
+        emit(kernel=f"moe_experts fwd+bwd ({prec})", T=T, E=E, k=k, D=D, F=Fh, ms=round(ms, 4),
+             tflops=round(3 * 3 * fl / 2 / ms / 1e9, 1))
+    _lib.check_status("grouped mx")
 
 
 def bench_hstu(quick: bool) -> None:

@@ -5,6 +5,7 @@ import torch
 
 from mlperf_training_b200.models.gpt import GPT, GPTConfig
 from mlperf_training_b200.ops import _lib, moe_ops as M
+from tests._tol import assert_tiles_close
 
 pytestmark = pytest.mark.gpu
 
@@ -57,6 +58,59 @@ def test_grouped_gemms(T, E, k, D, Fh):
     wg_ref = M.grouped_wgrad(dy.cpu(), xp.cpu(), seg.cpu(), E, out_dtype=torch.float32)
     assert (acc.cpu() - 2 * wg_ref).abs().max() < 2e-2 * max(wg_ref.abs().max().item(), 1)
     _lib.check_status("grouped gemm")
+
+
+@pytest.mark.parametrize("T,E,k,D,Fh", [(1024, 8, 2, 256, 256), (4096, 32, 4, 960, 576)])
+def test_grouped_mxfp8_mlp_matches_emulation(T, E, k, D, Fh):
+    """Block-scaled grouped GEMMs against the eager emulation that rounds the same way; the second case has
+    widths that are not multiples of 128 (partial K blocks, unfused dSwiGLU)."""
+    torch.manual_seed(3)
+    logits = torch.randn(T, E)
+    logits[:, 1] -= 100.0                                   # an expert without tokens
+    idx, w, cnt = M.router_topk(logits.cuda(), k)
+    seg, te, dest, rows = M.plan(idx, cnt, E, pad=M.PAD_MX)
+    x = (torch.randn(T, D) * 0.5).bfloat16().cuda()
+    w1 = (torch.randn(E, 2 * Fh, D) * 0.05).bfloat16().cuda()
+    w2 = (torch.randn(E, D, Fh) * 0.05).bfloat16().cuda()
+    assert M.mx_supported(w1, w2)
+    xp = M.permute_rows(x, dest, k, rows)
+    live = (te.cpu() >= 0).repeat_interleave(M.PAD_MX)
+    # forward / dgrad GEMM
+    from mlperf_training_b200.ops import mxfp8
+    a_g, at_g = mxfp8.quantize(xp, row_tile=128, col_tile=M.grouped_bn(D))
+    b_g = M._stacked_weight_op(w1, False)
+    out = M.grouped_rows_mx(a_g, b_g, te, E)
+    torch.cuda.synchronize()
+    _lib.check_status("grouped mx rows")
+    a_c, at_c = mxfp8.quantize(xp.cpu(), row_tile=128, col_tile=M.grouped_bn(D))
+    b_c, _ = mxfp8.quantize(w1.cpu().reshape(E * 2 * Fh, D), row_tile=M.grouped_bn(2 * Fh))
+    ref = M.grouped_rows_mx(a_c, b_c, te.cpu(), E)
+    assert_tiles_close(out.float().cpu()[live], ref.float()[live], rel=2e-2, what="grouped mx rows")
+    # weight gradient: contraction over every expert's rows, accumulated twice into fp32
+    dy = out.masked_fill(~live.cuda()[:, None], 0)
+    _, dyt_g = mxfp8.quantize(dy, col_tile=128)
+    acc = torch.zeros(E, 2 * Fh, D, device="cuda")
+    M.grouped_wgrad_mx(dyt_g, at_g, seg, E, acc)
+    M.grouped_wgrad_mx(dyt_g, at_g, seg, E, acc)
+    torch.cuda.synchronize()
+    _lib.check_status("grouped mx wgrad")
+    _, dyt_c = mxfp8.quantize(dy.cpu(), col_tile=128)
+    wg_ref = M.grouped_wgrad_mx(dyt_c, at_c, seg.cpu(), E, torch.zeros(E, 2 * Fh, D))
+    assert acc[1].abs().max() == 0                            # the empty expert's gradient stays zero
+    assert_tiles_close(acc.cpu().view(-1, D), 2 * wg_ref.view(-1, D), rel=1e-3, what="grouped mx wgrad")
+    # the whole MLP with autograd against the bf16 grouped path
+    def run(prec):
+        xx = x.clone().requires_grad_()
+        p1, p2 = w1.clone().requires_grad_(), w2.clone().requires_grad_()
+        y = M.moe_experts(xx, idx, w, cnt, p1, p2, prec)
+        (y.float() ** 2).sum().backward()
+        return y.detach().float(), xx.grad.float(), p1.grad.float(), p2.grad.float()
+    base, mx = run("bf16"), run("mxfp8")
+    torch.cuda.synchronize()
+    _lib.check_status("grouped mx mlp")
+    for name, u, v in zip(("y", "dx", "dw1", "dw2"), base, mx):
+        rel = ((u - v).norm() / u.norm()).item()
+        assert rel < 0.12, (name, rel)
 
 
 def test_moe_model_step_matches_cpu():

@@ -26,6 +26,26 @@ def test_quantize_matches_emulation(R, C):
         assert (err <= x.float().abs().view(R, C // 32, 32).amax(-1, keepdim=True).expand(-1, -1, 32).reshape(R, C) * 0.07 + 1e-30).all()
 
 
+@pytest.mark.parametrize("R,C", [(256, 160), (384, 960), (2048, 2880)])
+def test_quantize_partial_column_tile(R, C):
+    """Widths that are multiples of 32 but not of 128 (the last 128-column tile is partial)."""
+    torch.manual_seed(R + C)
+    x = (torch.randn(R, C) * torch.exp(torch.randn(R, 1))).bfloat16()
+    r_c, c_c = mxfp8.quantize(x, row_tile=128, col_tile=192)
+    r_g, c_g = mxfp8.quantize(x.cuda(), row_tile=128, col_tile=192)
+    torch.cuda.synchronize()
+    _lib.check_status("quant partial")
+    for cpu, gpu, what in ((r_c, r_g, "row"), (c_c, c_g, "col")):
+        assert torch.equal(mxfp8.sf_plain(gpu).cpu(), cpu.sf), f"{what} scales"
+        assert torch.equal(gpu.q.cpu(), cpu.q), f"{what} codes"
+    gu = (torch.randn(R, 2 * C) * 2).bfloat16()
+    a_c, at_c = mxfp8.quantize_swiglu(gu, row_tile=128, col_tile=192)
+    a_g, at_g = mxfp8.quantize_swiglu(gu.cuda(), row_tile=128, col_tile=192)
+    ref = mxfp8.dequantize(a_c)
+    assert (mxfp8.dequantize(a_g).cpu() - ref).abs().max() <= 0.13 * ref.abs().max()      # SwiGLU rounding may flip a code
+    assert (mxfp8.dequantize(at_g).cpu() - mxfp8.dequantize(at_c)).abs().max() <= 0.13 * ref.abs().max()
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 224, 256), (384, 448, 512), (512, 1000, 384),
                                    (1024, 4096, 1024), (136, 72, 128)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])

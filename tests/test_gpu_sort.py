@@ -30,6 +30,26 @@ def test_sort_unique_and_segment_sum(n, rows):
     assert torch.equal(b2, sort.segment_sum(src.cuda(), d, torch.float32))                  # run twice: bit-identical
 
 
+def test_segment_sum_long_runs():
+    """Skewed ids: runs longer than one warp's share (summed through per-block partial sums), runs that start in the
+    middle of a block, a run of exactly the block size, next to ordinary short runs."""
+    g = torch.Generator().manual_seed(5)
+    ids = torch.cat([torch.full((1000,), 7), torch.full((65,), 3), torch.full((64,), 11), torch.full((129,), 2),
+                     torch.randint(100, 5000, (3000,), generator=g), torch.full((300,), 99)])
+    ids = ids[torch.randperm(ids.numel(), generator=g)]
+    for D, dt in ((256, torch.bfloat16), (72, torch.float32)):
+        src = torch.randn(ids.numel(), D, generator=g).to(dt)
+        c = sort.sort_unique(ids, 13)
+        d = sort.sort_unique(ids.cuda(), 13)
+        cnt = int(c.count)
+        a = sort.segment_sum(src, c, torch.float32)[:cnt]
+        b = sort.segment_sum(src.cuda(), d, torch.float32)
+        torch.cuda.synchronize()
+        _lib.check_status("segment sum long runs")
+        assert (a - b[:cnt].cpu()).abs().max() <= 2e-4 * max(a.abs().max().item(), 1.0)
+        assert torch.equal(b, sort.segment_sum(src.cuda(), d, torch.float32))               # bit-identical when repeated
+
+
 def test_embedding_backward_is_deterministic_and_matches_cpu():
     torch.manual_seed(0)
     ids = torch.randint(0, 500, (4000,))

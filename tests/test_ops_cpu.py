@@ -208,3 +208,29 @@ def test_run_config_selects_moment_dtype():
     assert _moment_dtype(RunConfig(use_precision_aware_optimizer=False, exp_avg_dtype="bf16", exp_avg_sq_dtype="bf16")) == torch.float32
     with pytest.raises(ValueError):
         _moment_dtype(RunConfig(use_precision_aware_optimizer=True, exp_avg_dtype="fp16", exp_avg_sq_dtype="bf16"))
+
+
+def test_grouped_mlp_block_scaled_emulation_close_to_bf16():
+    """The block-scaled expert MLP (eager emulation: e4m3 codes, one power-of-two scale per 32) stays within
+    quantisation error of the bf16 grouped path, forward and all three gradients, with an empty expert."""
+    from mlperf_training_b200.ops import moe_ops as M
+    torch.manual_seed(0)
+    T, k, E, D, F = 96, 2, 4, 192, 192
+    x = torch.randn(T, D).bfloat16()
+    logits = torch.randn(T, E)
+    logits[:, 2] -= 100.0
+    w1 = (torch.randn(E, 2 * F, D) * 0.05).bfloat16().requires_grad_()
+    w2 = (torch.randn(E, D, F) * 0.05).bfloat16().requires_grad_()
+    idx, w, counts = M.router_topk(logits, k)
+    assert M.expert_precision("mxfp8", w1, w2) == "mxfp8"
+
+    def run(prec):
+        xx = x.clone().requires_grad_()
+        w1.grad = w2.grad = None
+        y = M.moe_experts(xx, idx, w, counts, w1, w2, prec)
+        y.float().square().sum().backward()
+        return y.detach().float(), xx.grad.float(), w1.grad.float().clone(), w2.grad.float().clone()
+
+    for u, v in zip(run("bf16"), run("mxfp8")):
+        assert ((u - v).norm() / u.norm()).item() < 0.12
+    assert w1.grad[2].abs().max() == 0
