@@ -1,4 +1,7 @@
-// Tensor-parallel GEMMs fused with their collective over NVLink peer memory (bf16, tcgen05).
+// Tensor-parallel GEMMs fused with their collective over NVLink peer memory (tcgen05; bf16 operands, or
+// e4m3 / e5m2 operands with one dequantisation factor per tensor - the frozen-base linears of the LoRA
+// fine-tuning recipe, llama2_sft/primus/src/llama2_custom.py:1904-1910 - whose gathered blocks then cross
+// NVLink at one byte per element).
 //
 //   mode 1  all-gather -> GEMM (rows):  D[T, N] = gather_rows(A)[T, K] * B^T.  Every rank holds the
 //           rows [r*T/W, (r+1)*T/W) of A in its copy of a symmetric buffer.  A few CTAs of the SAME
@@ -58,6 +61,10 @@ struct Params {
   int group_m;
   float alpha;
   int* status;
+  // ---- 8-bit operands (K-major only): format codes 0 = e4m3, 1 = e5m2; factors are device scalars
+  int fp8, a_fmt, b_fmt;
+  const float* inv_a;
+  const float* inv_b;
   // ---- tensor-parallel part
   int mode, W, rank;
   int rows_per;                    // rows (mode 1, 3) or k elements (mode 2) per rank block
@@ -400,7 +407,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int bk = p.fp8 ? 2 * BK : BK;           // contraction elements per 128-byte k block
+  const int num_kb = (p.K + bk - 1) / bk;
 
   // ---------------- auxiliary CTAs: no tensor memory, no GEMM barriers ----------------
   if ((int)blockIdx.x < p.n_aux) {
@@ -434,7 +442,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       uint32_t ready = 1u << p.rank;          // rank blocks known to be in the local buffer
-      const int kb_per = (p.mode == 2) ? p.rows_per / BK : 0;
+      const int kb_per = (p.mode == 2) ? p.rows_per / bk : 0;
       const int kb_start = (p.mode == 2) ? p.rank * kb_per : 0;
       auto need = [&](int c) -> bool {
         if (ready & (1u << c)) return true;
@@ -461,7 +469,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           mbar_expect_tx(&full[stage], C::A_STAGE + C::B_STAGE);
           uint8_t* a_dst = sA + stage * C::A_STAGE;
           uint8_t* b_dst = sB + stage * C::B_STAGE;
-          const int k0 = kb * BK;
+          const int k0 = kb * bk;
           if (!p.a_mn_major) {
             tma_load_2d(a_dst, &tmA, &full[stage], k0, m0);
           } else {
@@ -481,7 +489,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc(1, 1, p.a_mn_major, p.b_mn_major, BM, BN);
+      const uint32_t idesc = p.fp8 ? umma_idesc(p.a_fmt, p.b_fmt, 0, 0, BM, BN) : umma_idesc(1, 1, p.a_mn_major, p.b_mn_major, BM, BN);
       const uint32_t a_lbo = p.a_mn_major ? BK * 128 : 16;
       const uint32_t b_lbo = p.b_mn_major ? BK * 128 : 16;
       const uint32_t a_kstep = p.a_mn_major ? UMMA_K * 128 : UMMA_K * 2;
@@ -504,7 +512,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t ad = umma_desc_sw128(a_addr + kk * a_kstep, a_lbo, 1024);
             const uint64_t bd = umma_desc_sw128(b_addr + kk * b_kstep, b_lbo, 1024);
-            tc_mma_f16_ss(d_tmem, ad, bd, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            if (p.fp8) tc_mma_f8_ss(d_tmem, ad, bd, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            else tc_mma_f16_ss(d_tmem, ad, bd, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
           }
           tc_commit(&empty[stage]);
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
@@ -517,6 +526,9 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int q = warp & 3;
     const int ew = warp - 2;
     uint8_t* stg = sE + ew * 2 * STG_BYTES;
+    float alpha = p.alpha;
+    if (p.inv_a != nullptr) alpha *= *p.inv_a;       // dequantisation factors of 8-bit operands
+    if (p.inv_b != nullptr) alpha *= *p.inv_b;
     int buf = 0;
     int it = 0;
     bool ok = true;
@@ -540,7 +552,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int col0 = n0 + c * 32;
         float v[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
         if (p.out_f32) {
           if (lane == 0) tma_store_wait_read<1>();
           __syncwarp();
@@ -647,9 +659,19 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   return b200::check_launch("gemm_tp");
 }
 
+struct Fp8Args {                 // 8-bit operands: element = byte, pitches in bytes, K-major only
+  int on, a_fmt, b_fmt;
+  const float* inv_a;
+  const float* inv_b;
+};
+
 int make_ab_maps(CUtensorMap* tmA, CUtensorMap* tmB, const void* a, const void* b, int M, int N, int K, long long lda,
-                 long long ldb, int a_mn, int b_mn, int BN) {
+                 long long ldb, int a_mn, int b_mn, int BN, bool fp8) {
   int r;
+  if (fp8) {
+    if ((r = b200::make_tmap_2d(tmA, b200::DT_U8, a, K, M, lda, 2 * BK, BM, b200::SWZ_128))) return r;
+    return b200::make_tmap_2d(tmB, b200::DT_U8, b, K, N, ldb, 2 * BK, BN, b200::SWZ_128);
+  }
   if (!a_mn) r = b200::make_tmap_2d(tmA, b200::DT_BF16, a, K, M, lda * 2, BK, BM, b200::SWZ_128);
   else r = b200::make_tmap_2d(tmA, b200::DT_BF16, a, M, K, lda * 2, 64, BK, b200::SWZ_128);
   if (r) return r;
@@ -670,23 +692,24 @@ int make_ab_maps(CUtensorMap* tmA, CUtensorMap* tmB, const void* a, const void* 
 // (chunk_flags may be ordinary local memory); copy_mode 1 pushes the own block to every peer, then
 // chunk_flags must be this rank's entry of flag_ptrs[0..W) (peer-writable memory, zeroed on every rank
 // before the cross-rank barrier that precedes the launch).
-B200_API int b200_gemm_tp_gather(const void* a, const void* b, void* d, int M, int N, int K, long long lda,
-                                 long long ldb, long long ldd, int a_mn_major, int b_mn_major, int out_f32,
-                                 int accumulate, float alpha, int mode, const unsigned long long* peer_ptrs, int W,
-                                 int rank, void* gbuf_local, long long chunk_bytes, int rows_per, int* chunk_flags,
-                                 int n_copy, int copy_mode, const unsigned long long* flag_ptrs, void* stream) {
+static int tp_gather_impl(const void* a, const void* b, void* d, int M, int N, int K, long long lda,
+                          long long ldb, long long ldd, int a_mn_major, int b_mn_major, int out_f32,
+                          int accumulate, float alpha, int mode, const unsigned long long* peer_ptrs, int W,
+                          int rank, void* gbuf_local, long long chunk_bytes, int rows_per, int* chunk_flags,
+                          int n_copy, int copy_mode, const unsigned long long* flag_ptrs, void* stream, const Fp8Args& f8) {
+  if (f8.on && (a_mn_major || b_mn_major)) return b200::fail(1517, "gemm_tp_gather: 8-bit operands must be K-major");
   if (M <= 0 || N <= 0 || K <= 0) return b200::fail(1510, "gemm_tp_gather: empty problem %d x %d x %d", M, N, K);
   if (W < 1 || W > MAXW || rank < 0 || rank >= W) return b200::fail(1511, "gemm_tp_gather: bad world %d / rank %d", W, rank);
   if (mode == 1 && (rows_per % BM != 0 || (long long)rows_per * W != M))
     return b200::fail(1512, "gemm_tp_gather: mode 1 needs M = W * rows_per with rows_per %% 128 == 0 (M=%d rows_per=%d)", M, rows_per);
-  if (mode == 2 && (rows_per % BK != 0 || (long long)rows_per * W != K))
+  if (mode == 2 && (rows_per % (f8.on ? 2 * BK : BK) != 0 || (long long)rows_per * W != K))
     return b200::fail(1513, "gemm_tp_gather: mode 2 needs K = W * rows_per with rows_per %% 64 == 0 (K=%d rows_per=%d)", K, rows_per);
   if (mode != 1 && mode != 2) return b200::fail(1514, "gemm_tp_gather: mode %d", mode);
   if (chunk_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(gbuf_local) & 15))
     return b200::fail(1515, "gemm_tp_gather: blocks must be 16-byte aligned and sized");
   const int BN = (N > 128) ? 256 : 128;
   CUtensorMap tmA, tmB, tmD;
-  int r = make_ab_maps(&tmA, &tmB, a, b, M, N, K, lda, ldb, a_mn_major, b_mn_major, BN);
+  int r = make_ab_maps(&tmA, &tmB, a, b, M, N, K, lda, ldb, a_mn_major, b_mn_major, BN, f8.on != 0);
   if (r) return r;
   if (out_f32) r = b200::make_tmap_2d(&tmD, b200::DT_F32, d, N, M, ldd * 4, 32, 32, b200::SWZ_128);
   else r = b200::make_tmap_2d(&tmD, b200::DT_BF16, d, N, M, ldd * 2, 64, 32, b200::SWZ_128);
@@ -696,6 +719,7 @@ B200_API int b200_gemm_tp_gather(const void* a, const void* b, void* d, int M, i
   p.a_mn_major = a_mn_major ? 1 : 0; p.b_mn_major = b_mn_major ? 1 : 0;
   p.out_f32 = out_f32 ? 1 : 0; p.accumulate = accumulate ? 1 : 0;
   p.group_m = 16; p.alpha = alpha; p.status = b200::status_ptr();
+  p.fp8 = f8.on; p.a_fmt = f8.a_fmt; p.b_fmt = f8.b_fmt; p.inv_a = f8.inv_a; p.inv_b = f8.inv_b;
   p.mode = mode; p.W = W; p.rank = rank; p.rows_per = rows_per;
   p.n_aux = (W > 1) ? (n_copy > 0 ? n_copy : 8) : 0;
   for (int c = 0; c < W; ++c) p.peer_src[c] = reinterpret_cast<const uint8_t*>(peer_ptrs[c]);
@@ -715,16 +739,41 @@ B200_API int b200_gemm_tp_gather(const void* a, const void* b, void* d, int M, i
   return launch<128>(tmA, tmB, tmD, p, no_maps, tiles, (cudaStream_t)stream);
 }
 
+B200_API int b200_gemm_tp_gather(const void* a, const void* b, void* d, int M, int N, int K, long long lda,
+                                 long long ldb, long long ldd, int a_mn_major, int b_mn_major, int out_f32,
+                                 int accumulate, float alpha, int mode, const unsigned long long* peer_ptrs, int W,
+                                 int rank, void* gbuf_local, long long chunk_bytes, int rows_per, int* chunk_flags,
+                                 int n_copy, int copy_mode, const unsigned long long* flag_ptrs, void* stream) {
+  return tp_gather_impl(a, b, d, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, out_f32, accumulate, alpha, mode, peer_ptrs,
+                        W, rank, gbuf_local, chunk_bytes, rows_per, chunk_flags, n_copy, copy_mode, flag_ptrs, stream,
+                        Fp8Args{0, 0, 0, nullptr, nullptr});
+}
+
+// The same with 8-bit operands: a [M, K] / b [N, K] hold e4m3 (fmt 0) or e5m2 (fmt 1) codes, pitches in bytes,
+// value = code * (*inv_scale) with the factors read on the device; the gathered blocks are codes as well, and
+// every rank must have quantised its block with the same factor.
+B200_API int b200_gemm_tp_gather_fp8(const void* a, const void* b, void* d, int M, int N, int K, long long lda,
+                                     long long ldb, long long ldd, int a_e5m2, int b_e5m2, const float* inv_a,
+                                     const float* inv_b, int out_f32, int accumulate, float alpha, int mode,
+                                     const unsigned long long* peer_ptrs, int W, int rank, void* gbuf_local,
+                                     long long chunk_bytes, int rows_per, int* chunk_flags, int n_copy, int copy_mode,
+                                     const unsigned long long* flag_ptrs, void* stream) {
+  return tp_gather_impl(a, b, d, M, N, K, lda, ldb, ldd, 0, 0, out_f32, accumulate, alpha, mode, peer_ptrs, W, rank,
+                        gbuf_local, chunk_bytes, rows_per, chunk_flags, n_copy, copy_mode, flag_ptrs, stream,
+                        Fp8Args{1, a_e5m2 ? 1 : 0, b_e5m2 ? 1 : 0, inv_a, inv_b});
+}
+
 // GEMM -> reduce-scatter.  P[M, N] = alpha * A * B^T is this rank's partial sum; rank o receives
 // out[rows_per, N] = sum over ranks of P[o*rows_per .. , :] (+ residual), bf16.
 //   stage_ptrs[o]: rank o's staging buffer, W * rows_per * N bf16 (symmetric memory)
 //   flag_ptrs[o] : rank o's counters, rows_per / 128 ints (symmetric memory), zero at launch on every
 //                  rank (zero them, then a cross-rank barrier, then launch)
 //   work_counter : one local int, zero at launch.  n_red CTAs only reduce.
-B200_API int b200_gemm_tp_rs(const void* a, const void* b, int M, int N, int K, long long lda, long long ldb,
-                             int a_mn_major, int b_mn_major, float alpha, const unsigned long long* stage_ptrs,
-                             const unsigned long long* flag_ptrs, int W, int rank, int* work_counter, void* out,
-                             long long ld_out, const void* residual, long long ld_res, int n_red, void* stream) {
+static int tp_rs_impl(const void* a, const void* b, int M, int N, int K, long long lda, long long ldb,
+                      int a_mn_major, int b_mn_major, float alpha, const unsigned long long* stage_ptrs,
+                      const unsigned long long* flag_ptrs, int W, int rank, int* work_counter, void* out,
+                      long long ld_out, const void* residual, long long ld_res, int n_red, void* stream, const Fp8Args& f8) {
+  if (f8.on && (a_mn_major || b_mn_major)) return b200::fail(1524, "gemm_tp_rs: 8-bit operands must be K-major");
   if (M <= 0 || N <= 0 || K <= 0) return b200::fail(1520, "gemm_tp_rs: empty problem %d x %d x %d", M, N, K);
   if (W < 1 || W > MAXW || rank < 0 || rank >= W) return b200::fail(1521, "gemm_tp_rs: bad world %d / rank %d", W, rank);
   if (M % (W * BM) != 0) return b200::fail(1522, "gemm_tp_rs: M=%d must be a multiple of W * 128 = %d", M, W * BM);
@@ -733,7 +782,7 @@ B200_API int b200_gemm_tp_rs(const void* a, const void* b, int M, int N, int K, 
   const int BN = (N > 128) ? 256 : 128;
   const int rows_per = M / W;
   CUtensorMap tmA, tmB, tmD;
-  int r = make_ab_maps(&tmA, &tmB, a, b, M, N, K, lda, ldb, a_mn_major, b_mn_major, BN);
+  int r = make_ab_maps(&tmA, &tmB, a, b, M, N, K, lda, ldb, a_mn_major, b_mn_major, BN, f8.on != 0);
   if (r) return r;
   r = b200::make_tmap_2d(&tmD, b200::DT_BF16, out, N, rows_per, ld_out * 2, 64, 32, b200::SWZ_128);   // not used by mode 3
   if (r) return r;
@@ -741,6 +790,7 @@ B200_API int b200_gemm_tp_rs(const void* a, const void* b, int M, int N, int K, 
   p.M = M; p.N = N; p.K = K;
   p.a_mn_major = a_mn_major ? 1 : 0; p.b_mn_major = b_mn_major ? 1 : 0;
   p.group_m = 16; p.alpha = alpha; p.status = b200::status_ptr();
+  p.fp8 = f8.on; p.a_fmt = f8.a_fmt; p.b_fmt = f8.b_fmt; p.inv_a = f8.inv_a; p.inv_b = f8.inv_b;
   p.mode = 3; p.W = W; p.rank = rank; p.rows_per = rows_per;
   p.n_aux = n_red > 0 ? n_red : 8;
   for (int o = 0; o < W; ++o) {
@@ -761,4 +811,23 @@ B200_API int b200_gemm_tp_rs(const void* a, const void* b, int M, int N, int K, 
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   if (BN == 256) return launch<256>(tmA, tmB, tmD, p, om, tiles, (cudaStream_t)stream);
   return launch<128>(tmA, tmB, tmD, p, om, tiles, (cudaStream_t)stream);
+}
+
+B200_API int b200_gemm_tp_rs(const void* a, const void* b, int M, int N, int K, long long lda, long long ldb,
+                             int a_mn_major, int b_mn_major, float alpha, const unsigned long long* stage_ptrs,
+                             const unsigned long long* flag_ptrs, int W, int rank, int* work_counter, void* out,
+                             long long ld_out, const void* residual, long long ld_res, int n_red, void* stream) {
+  return tp_rs_impl(a, b, M, N, K, lda, ldb, a_mn_major, b_mn_major, alpha, stage_ptrs, flag_ptrs, W, rank, work_counter, out,
+                    ld_out, residual, ld_res, n_red, stream, Fp8Args{0, 0, 0, nullptr, nullptr});
+}
+
+// The same with 8-bit operands (see b200_gemm_tp_gather_fp8); every rank may use its own factors, the partial sums
+// travel as bf16.
+B200_API int b200_gemm_tp_rs_fp8(const void* a, const void* b, int M, int N, int K, long long lda, long long ldb,
+                                 int a_e5m2, int b_e5m2, const float* inv_a, const float* inv_b, float alpha,
+                                 const unsigned long long* stage_ptrs, const unsigned long long* flag_ptrs, int W, int rank,
+                                 int* work_counter, void* out, long long ld_out, const void* residual, long long ld_res,
+                                 int n_red, void* stream) {
+  return tp_rs_impl(a, b, M, N, K, lda, ldb, 0, 0, alpha, stage_ptrs, flag_ptrs, W, rank, work_counter, out, ld_out, residual,
+                    ld_res, n_red, stream, Fp8Args{1, a_e5m2 ? 1 : 0, b_e5m2 ? 1 : 0, inv_a, inv_b});
 }

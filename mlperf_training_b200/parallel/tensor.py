@@ -17,6 +17,13 @@ llama2_sft/primus/config_MI355X_1x8x1.sh:115-118; llama2_sft/primus/conf/llama2_
 the transfer happens inside the GEMM kernel over peer memory, tile by tile.
 
 Weight gradients are accumulated into ``weight.main_grad`` when the parameter has one.
+
+``precision="fp8"`` (fused path, frozen weights - the base of a LoRA run): the weight is quantised once to
+per-tensor e4m3 (both orientations), activations go to e4m3 and gradients to e5m2 with delayed scaling, and
+the fused kernels run the 8-bit tensor-core path; gathered blocks cross NVLink as codes, one byte per
+element.  A gathered tensor is decoded with ONE factor, so its sites share their scale across the group:
+their amax words live in one pool that is max-reduced over the group once per optimizer step
+(llama2_sft/primus/src/llama2_custom.py:1904-1910 pre-quantises the frozen base in the reference).
 """
 from __future__ import annotations
 
@@ -27,15 +34,22 @@ import torch.distributed as dist
 from torch.autograd import Function
 
 from ..ops import _lib
+from ..ops import fp8 as F8
 from ..ops import kernels as K
 from ..ops.functional import _wgrad
+from ..ops.linear import _site, fp8_weight_operands, weight_epoch
 
 
 class TPContext:
     RS_FLAG_OFFSET = 64     # ints: [0, 16) all-gather block counters, [64, ...) reduce-scatter tile counters
 
-    def __init__(self, group=None, comm: str = "nccl", device=None, n_copy: int = 0, n_red: int = 8, copy_mode: int = 1):
+    def __init__(self, group=None, comm: str = "nccl", device=None, n_copy: int = 0, n_red: int = 8, copy_mode: int = 1,
+                 precision: str = "bf16"):
         self.group = group
+        self.precision = precision      # "fp8": frozen-weight linears of the fused path run on 8-bit operands
+        self._amax_pool = None          # int32 words of the sites whose scale is shared by the group
+        self._amax_used = 0
+        self._amax_epoch = None
         on = dist.is_available() and dist.is_initialized()
         self.world = dist.get_world_size(group) if on else 1
         self.rank = dist.get_rank(group) if on else 0
@@ -83,6 +97,42 @@ class TPContext:
     def fused_ok(self, t: torch.Tensor) -> bool:
         return self.comm == "fused" and t.is_cuda and t.dtype == torch.bfloat16
 
+    def fp8_ok(self, t: torch.Tensor, weight: torch.Tensor) -> bool:
+        """8-bit path: fused kernels, a frozen bf16 weight, every dimension a multiple of 128."""
+        return (self.precision == "fp8" and self.fused_ok(t) and not weight.requires_grad and weight.dtype == torch.bfloat16
+                and t.shape[0] % 128 == 0 and t.shape[1] % 128 == 0 and weight.shape[0] % 128 == 0 and weight.shape[1] % 128 == 0)
+
+    def shared_site(self, weight: torch.Tensor, name: str, fmt: str) -> "F8.DelayedScale":
+        """Scale state of a tensor that is gathered over the group: its amax word is a slot of the pool."""
+        st = _site(weight, name, fmt)
+        if getattr(st, "_pooled", None) is not self:
+            if self._amax_pool is None:
+                self._amax_pool = torch.zeros(8192, dtype=torch.int32, device=weight.device)
+            if self._amax_used >= self._amax_pool.numel():
+                raise RuntimeError("tensor-parallel FP8: more shared scale sites than pool slots")
+            st.amax = self._amax_pool[self._amax_used:self._amax_used + 1]
+            self._amax_used += 1
+            st._pooled = self
+        return st
+
+    def prepare_shared(self, st: "F8.DelayedScale", x: torch.Tensor) -> None:
+        """``st.scale`` valid for ``x`` in the current epoch and equal on every rank of the group."""
+        epoch = weight_epoch()
+        if not st.primed:
+            a = x.detach().abs().amax().float().reshape(1)
+            if self.world > 1:
+                dist.all_reduce(a, op=dist.ReduceOp.MAX, group=self.group)
+            st._set_from(a)
+            st.primed, st.epoch = True, epoch
+            return
+        if epoch != self._amax_epoch:
+            # one max-reduction of every shared site's amax per optimizer step (bit patterns of non-negative
+            # floats order like the floats); sites primed in this epoch hold zeros and are not rolled yet
+            self._amax_epoch = epoch
+            if self.world > 1 and self._amax_used:
+                dist.all_reduce(self._amax_pool[: self._amax_used], op=dist.ReduceOp.MAX, group=self.group)
+        st.prepare(x, epoch)
+
     def _symm(self, numel: int, dtype):
         from .symm import SymmetricBuffer
         return SymmetricBuffer(numel, dtype, self.group, self.device)
@@ -109,6 +159,50 @@ class TPContext:
         self._flags.local.zero_()
         buf.barrier()          # every block is in place and every counter is zero before any rank launches
         return buf, full
+
+    def gather_begin_codes(self, q_shard: torch.Tensor):
+        """``gather_begin`` for a block of 8-bit codes ``[rows, k]`` (uint8): the gather buffer is viewed as bytes."""
+        rows, k = q_shard.shape
+        self._ensure(gather_numel=(rows * self.world * k + 1) // 2)
+        buf = self._gather[self._gather_turn]
+        self._gather_turn ^= 1
+        full = buf.local.view(torch.uint8)[: rows * self.world * k].view(rows * self.world, k)
+        full[self.rank * rows:(self.rank + 1) * rows].copy_(q_shard)
+        self._flags.local.zero_()
+        buf.barrier()
+        return buf, full
+
+    def gemm_gather_fp8(self, buf, full: torch.Tensor, a_inv: torch.Tensor, a_fmt: str, b: "F8.FP8Operand") -> torch.Tensor:
+        """``dequant(full [T, K] codes) @ dequant(b [N, K])^T -> [T, N]`` bf16, the peers' row blocks of ``full``
+        pulled or pushed inside the kernel."""
+        W, r = self.world, self.rank
+        T, Kd = full.shape
+        N = b.rows
+        rows_per = T // W
+        out = torch.empty((T, N), dtype=torch.bfloat16, device=full.device)
+        _lib.call("b200_gemm_tp_gather_fp8", _lib.ptr(full), _lib.ptr(b.q), _lib.ptr(out), T, N, Kd, full.stride(0),
+                  b.q.stride(0), out.stride(0), int(a_fmt == "e5m2"), int(b.fmt == "e5m2"), _lib.ptr(a_inv), _lib.ptr(b.inv_scale),
+                  0, 0, 1.0, 1, buf.ptr_array(), W, r, _lib.ptr(full), rows_per * Kd, rows_per, _lib.ptr(self._flags.local),
+                  self.n_copy, self.copy_mode, self._flags.ptr_array(), _lib.stream_ptr())
+        return out
+
+    def gemm_reduce_scatter_fp8(self, a: "F8.FP8Operand", b: "F8.FP8Operand", residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``reduce_scatter_rows(dequant(a) @ dequant(b)^T) (+ residual)`` -> ``[T/W, N]`` bf16 in one kernel."""
+        W, r = self.world, self.rank
+        M, Kd, N = a.rows, a.k, b.rows
+        rows_per = M // W
+        self._ensure(stage_numel=M * N)
+        self._flags.local.zero_()
+        self._local_flags.zero_()
+        self._stage.barrier()
+        out = torch.empty((rows_per, N), dtype=torch.bfloat16, device=a.q.device)
+        _lib.call("b200_gemm_tp_rs_fp8", _lib.ptr(a.q), _lib.ptr(b.q), M, N, Kd, a.q.stride(0), b.q.stride(0),
+                  int(a.fmt == "e5m2"), int(b.fmt == "e5m2"), _lib.ptr(a.inv_scale), _lib.ptr(b.inv_scale), 1.0,
+                  self._stage.ptr_array(), self._flags.offset_ptr_array(4 * self.RS_FLAG_OFFSET), W, r,
+                  _lib.ptr(self._local_flags[16:]), _lib.ptr(out), out.stride(0),
+                  None if residual is None else _lib.ptr(residual), 0 if residual is None else residual.stride(0), self.n_red,
+                  _lib.stream_ptr())
+        return out
 
     def gemm_gather(self, buf, full: torch.Tensor, other: torch.Tensor, *, mode: int, out: torch.Tensor | None = None,
                     accumulate: bool = False, out_dtype=torch.bfloat16) -> torch.Tensor:
@@ -153,6 +247,16 @@ class ColumnParallelFn(Function):
     @staticmethod
     def forward(ctx, x_shard, weight, tp: TPContext):
         ctx.tp = tp
+        ctx.fp8 = tp.fp8_ok(x_shard, weight)
+        if ctx.fp8:
+            # frozen weight: no weight gradient, so the activation is not kept
+            ctx.save_for_backward(weight)
+            st = tp.shared_site(weight, "x", "e4m3")
+            tp.prepare_shared(st, x_shard)
+            xq, _ = F8.quantize(x_shard, st)
+            buf, full = tp.gather_begin_codes(xq.q)
+            w_row, _ = fp8_weight_operands(weight)
+            return tp.gemm_gather_fp8(buf, full, st.inv_scale, "e4m3", w_row)
         ctx.save_for_backward(x_shard, weight)
         if tp.fused_ok(x_shard):
             buf, full = tp.gather_begin(x_shard)
@@ -162,6 +266,16 @@ class ColumnParallelFn(Function):
     @staticmethod
     def backward(ctx, dy):
         tp: TPContext = ctx.tp
+        if ctx.fp8:
+            (weight,) = ctx.saved_tensors
+            if not ctx.needs_input_grad[0]:
+                return None, None, None
+            dy = dy.contiguous()
+            st = _site(weight, "dy", "e5m2")            # partial sums are decoded per rank: a local scale is enough
+            st.prepare(dy, weight_epoch())
+            dyq, _ = F8.quantize(dy, st)
+            _, w_col = fp8_weight_operands(weight)      # [K, N_local]: contraction over the local output features
+            return tp.gemm_reduce_scatter_fp8(dyq, w_col), None, None
         x_shard, weight = ctx.saved_tensors
         dy = dy.contiguous()
         need_w = weight.requires_grad
@@ -190,8 +304,16 @@ class RowParallelFn(Function):
     @staticmethod
     def forward(ctx, x, weight, residual_shard, tp: TPContext):
         ctx.tp = tp
-        ctx.save_for_backward(x, weight)
         ctx.has_res = residual_shard is not None
+        ctx.fp8 = tp.fp8_ok(x, weight)
+        if ctx.fp8:
+            ctx.save_for_backward(weight)
+            st = _site(weight, "x", "e4m3")
+            st.prepare(x, weight_epoch())
+            xq, _ = F8.quantize(x.contiguous(), st)
+            w_row, _ = fp8_weight_operands(weight)
+            return tp.gemm_reduce_scatter_fp8(xq, w_row, residual=residual_shard)
+        ctx.save_for_backward(x, weight)
         if tp.fused_ok(x):
             return tp.gemm_reduce_scatter(x.contiguous(), weight, residual=residual_shard)
         y = tp.reduce_scatter_rows(K.gemm(x, weight))
@@ -200,6 +322,18 @@ class RowParallelFn(Function):
     @staticmethod
     def backward(ctx, dy_shard):
         tp: TPContext = ctx.tp
+        if ctx.fp8:
+            (weight,) = ctx.saved_tensors
+            dy_shard = dy_shard.contiguous()
+            dx = None
+            if ctx.needs_input_grad[0]:
+                st = tp.shared_site(weight, "dy", "e5m2")
+                tp.prepare_shared(st, dy_shard)
+                dyq, _ = F8.quantize(dy_shard, st)
+                buf, full = tp.gather_begin_codes(dyq.q)
+                _, w_col = fp8_weight_operands(weight)  # [K_local, N]: contraction over the output features
+                dx = tp.gemm_gather_fp8(buf, full, st.inv_scale, "e5m2", w_col)
+            return dx, None, (dy_shard if ctx.has_res else None), None
         x, weight = ctx.saved_tensors
         dy_shard = dy_shard.contiguous()
         if tp.fused_ok(dy_shard):

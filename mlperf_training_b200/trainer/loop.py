@@ -207,11 +207,15 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                   "between them over the sequence (all-gather -> GEMM, GEMM -> reduce-scatter)", flush=True)
         from ..parallel.tensor import TPContext
         fused_tp = str(rc.tp_comm_overlap).lower() == "fused" and str(device).startswith("cuda")
-        tp_ctx = TPContext(mesh.group("tp"), comm="fused" if fused_tp else "nccl", device=device if fused_tp else None)
+        # low-precision recipes run the frozen linears of the fused tensor-parallel path (the base of a LoRA run) on
+        # per-tensor FP8 operands; trainable tensor-parallel linears run the bf16 tcgen05 GEMMs
+        tp_prec = "fp8" if (fused_tp and cfg.precision != "bf16") else "bf16"
+        tp_ctx = TPContext(mesh.group("tp"), comm="fused" if fused_tp else "nccl", device=device if fused_tp else None,
+                           precision=tp_prec)
         dp_rank, dp_world = mesh.index("dp"), mesh.size("dp")
         dp_group = mesh.group("dp_shard") if replicate > 1 else mesh.group("dp")
         if cfg.precision != "bf16":
-            cfg.precision = "bf16"       # the tensor-parallel linears run the bf16 tcgen05 GEMMs
+            cfg.precision = "bf16"       # everything outside the tensor-parallel linears stays bf16
     cp_group = ep_group = edp_group = None
     ep_size = min(int(rc.expert_parallel), world) if cfg.n_experts else 1
     if ep_size > 1:

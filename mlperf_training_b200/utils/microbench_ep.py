@@ -64,22 +64,26 @@ def main(argv=None) -> int:
     w1 = (torch.randn(L, 2 * Fh, D, device=dev) * 0.02).bfloat16().requires_grad_(True)
     w2 = (torch.randn(L, D, Fh, device=dev) * 0.02).bfloat16().requires_grad_(True)
     gy = torch.randn(T, D, device=dev).bfloat16()
-    disp = {"nccl": ExpertParallelDispatcher(dist.group.WORLD, E), "fused": FusedExpertDispatcher(dist.group.WORLD, E, D, T * k, dev)}
-    res = {}
-    for name, d in disp.items():
-        def layer():
-            idx, w, counts = M.RouterFn.apply(logits, k)
-            y = d(x, idx, w, counts, w1, w2)
-            y.backward(gy)
-            x.grad = w1.grad = w2.grad = None
-        res[name] = timed(layer, args.iters, args.warmup)
+    w1.main_grad, w2.main_grad = torch.zeros_like(w1, dtype=torch.float32), torch.zeros_like(w2, dtype=torch.float32)
     flops = 3 * 2.0 * T * k * (3 * D * Fh)              # fwd + dgrad + wgrad of fc1 (2F) and fc2 (F), all ranks' tokens land somewhere
-    if rank == 0:
-        print(json.dumps({"kernel": "moe_layer_fwd_bwd", "world": W, "tokens_per_rank": T, "hidden": D, "experts": E, "top_k": k,
-                          "nccl_all_to_all_ms": round(res["nccl"], 3), "fused_peer_ms": round(res["fused"], 3),
-                          "speedup": round(res["nccl"] / res["fused"], 3),
-                          "expert_gemm_tflops_per_gpu_fused": round(flops / res["fused"] / 1e9, 1),
-                          "dropped_pairs": int(disp["fused"].dropped.item())}), flush=True)
+    for precision in ("bf16", "mxfp8"):
+        disp = {"nccl": ExpertParallelDispatcher(dist.group.WORLD, E),
+                "fused": FusedExpertDispatcher(dist.group.WORLD, E, D, T * k, dev, pad=M.pad_rows(precision))}
+        res = {}
+        for name, d in disp.items():
+            def layer():
+                idx, w, counts = M.RouterFn.apply(logits, k)
+                y = d(x, idx, w, counts, w1, w2, precision)
+                y.backward(gy)
+                x.grad = None
+            res[name] = timed(layer, args.iters, args.warmup)
+        if rank == 0:
+            print(json.dumps({"kernel": "moe_layer_fwd_bwd", "precision": precision, "world": W, "tokens_per_rank": T, "hidden": D,
+                              "experts": E, "top_k": k, "nccl_all_to_all_ms": round(res["nccl"], 3),
+                              "fused_peer_ms": round(res["fused"], 3), "speedup": round(res["nccl"] / res["fused"], 3),
+                              "expert_gemm_tflops_per_gpu_fused": round(flops / res["fused"] / 1e9, 1),
+                              "dropped_pairs": int(disp["fused"].dropped.item())}), flush=True)
+        del disp
 
     # ---------------- sharded embedding ----------------
     from ..data.hstu_synth import HSTUSyntheticData

@@ -97,6 +97,39 @@ def main(argv=None) -> int:
                               "fused_tflops_per_gpu": round(flops / t_f / 1e9, 1), "nvlink_mb_per_gpu": round(link_bytes / 1e6, 1),
                               "roofline_ms": round(roof_ms, 4), "fraction_of_roofline": round(roof_ms / t_f, 3),
                               "max_abs_diff_vs_nccl": err}), flush=True)
+    # the same two linears with a frozen weight on per-tensor FP8 operands (quantisation of the activation included)
+    from ..ops import fp8 as F8
+    from ..ops.linear import _site, fp8_weight_operands, weight_epoch
+    f8 = TPContext(None, "fused", dev, precision="fp8")
+    if args.n_copy:
+        f8.n_copy = args.n_copy
+    if args.n_red:
+        f8.n_red = args.n_red
+    w_col.requires_grad_(False), w_row.requires_grad_(False)
+
+    def ag_fp8():
+        st = f8.shared_site(w_col, "x", "e4m3")
+        f8.prepare_shared(st, x_shard)
+        xq, _ = F8.quantize(x_shard, st)
+        buf, full = f8.gather_begin_codes(xq.q)
+        return f8.gemm_gather_fp8(buf, full, st.inv_scale, "e4m3", fp8_weight_operands(w_col)[0])
+
+    def rs_fp8():
+        st = _site(w_row, "x", "e4m3")
+        st.prepare(act, weight_epoch())
+        aq, _ = F8.quantize(act, st)
+        return f8.gemm_reduce_scatter_fp8(aq, fp8_weight_operands(w_row)[0])
+
+    for name, fn, ref, flops, link_bytes in (
+            ("all_gather_gemm_fp8", ag_fp8, ag_nccl, 2.0 * T * Fl * D, (W - 1) / W * T * D),
+            ("gemm_reduce_scatter_fp8", rs_fp8, rs_nccl, 2.0 * T * D * (args.ffn // W), (W - 1) / W * T * D * 2)):
+        a, b = fn().float(), ref().float()
+        rel = ((a - b).norm() / b.norm()).item()
+        t_f = timed(fn, args.iters, args.warmup, flush)
+        if rank == 0:
+            print(json.dumps({"kernel": name, "world": W, "tokens": T, "hidden": D, "ffn": args.ffn, "fused_ms": round(t_f, 4),
+                              "fused_tflops_per_gpu": round(flops / t_f / 1e9, 1), "nvlink_mb_per_gpu": round(link_bytes / 1e6, 1),
+                              "rel_diff_vs_bf16": round(rel, 4)}), flush=True)
     if args.copy_sweep:
         # all-gather with a negligible GEMM (N = 128): the time is the in-kernel copy of the peers' blocks
         w_small = (torch.randn(128, D, device=dev) * 0.02).bfloat16()

@@ -51,8 +51,16 @@ def test_tensor_parallel_gpt_two_gpus(comm, lora):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fused_expert_dispatch_matches_all_to_all():
-    res = _run("moe_fused_worker.py")
+def test_tensor_parallel_lora_frozen_base_fp8():
+    """LoRA over a frozen base whose tensor-parallel linears run the fused kernels on per-tensor FP8 operands."""
+    res = _run("tp_worker.py", args=("nccl", "fused", "lora", "fp8"))
+    assert res.returncode == 0 and res.stdout.count("ok=True") >= 2, res.stdout[-3000:] + res.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("precision", ["bf16", "mxfp8"])
+def test_fused_expert_dispatch_matches_all_to_all(precision):
+    res = _run("moe_fused_worker.py", args=(precision,))
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "RESULT rank 0 ok=True" in res.stdout
 

@@ -92,3 +92,62 @@ def test_gemm_reduce_scatter_world1(shape, res):
     err = (out.float() - want).abs().max().item()
     assert err < 2e-2 * want.abs().max().item(), err
     assert int(work.item()) >= (M // 128) * 64
+
+
+@pytest.mark.parametrize("W", [1, 2])
+@pytest.mark.parametrize("a_fmt", ["e4m3", "e5m2"])
+def test_all_gather_gemm_rows_fp8(W, a_fmt):
+    """8-bit operands: the gathered blocks are codes, the result is decoded with the two per-tensor factors."""
+    from mlperf_training_b200.ops import fp8
+    torch.manual_seed(W)
+    rows_per, K, N = 256, 384, 384
+    T = W * rows_per
+    x = (torch.randn(T, K, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    sx, sw = fp8.DelayedScale(a_fmt, "cuda"), fp8.DelayedScale("e4m3", "cuda")
+    sx.prepare(x, 0); sw.prepare(w, 0)
+    xq, _ = fp8.quantize(x, sx)
+    wq, _ = fp8.quantize(w, sw)
+    want = fp8.dequantize(xq) @ fp8.dequantize(wq).t()
+    bufs = []
+    for r in range(W):
+        buf = torch.full((T, K), 0x7f, device="cuda", dtype=torch.uint8)
+        buf[r * rows_per:(r + 1) * rows_per] = xq.q[r * rows_per:(r + 1) * rows_per]
+        bufs.append(buf)
+    for r in range(W):
+        out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+        flags = torch.zeros(32, dtype=torch.int32, device="cuda")
+        _lib.call("b200_gemm_tp_gather_fp8", _lib.ptr(bufs[r]), _lib.ptr(wq.q), _lib.ptr(out), T, N, K, K, K, N,
+                  int(a_fmt == "e5m2"), 0, _lib.ptr(sx.inv_scale), _lib.ptr(sw.inv_scale), 0, 0, 1.0, 1,
+                  _arr([t.data_ptr() for t in bufs]), W, r, _lib.ptr(bufs[r]), rows_per * K, rows_per, _lib.ptr(flags), 4, 0,
+                  None, _lib.stream_ptr())
+        torch.cuda.synchronize()
+        _lib.check_status("gemm_tp_gather_fp8")
+        assert torch.equal(bufs[r], xq.q), f"rank {r}: gathered codes differ"
+        err = (out.float() - want).abs().max().item()
+        assert err < 1e-2 * want.abs().max().item(), (r, err)
+
+
+def test_gemm_reduce_scatter_fp8_world1():
+    from mlperf_training_b200.ops import fp8
+    torch.manual_seed(9)
+    M, N, K = 512, 384, 640
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    sa, sb = fp8.DelayedScale("e5m2", "cuda"), fp8.DelayedScale("e4m3", "cuda")
+    sa.prepare(a, 0); sb.prepare(b, 0)
+    aq, _ = fp8.quantize(a, sa)
+    bq, _ = fp8.quantize(b, sb)
+    resid = torch.randn(M, N, device="cuda").bfloat16()
+    stage = torch.full((M, N), float("nan"), device="cuda").bfloat16()
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    work = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    _lib.call("b200_gemm_tp_rs_fp8", _lib.ptr(aq.q), _lib.ptr(bq.q), M, N, K, K, K, 1, 0, _lib.ptr(sa.inv_scale),
+              _lib.ptr(sb.inv_scale), 1.0, _arr([stage.data_ptr()]), _arr([flags.data_ptr()]), 1, 0, _lib.ptr(work),
+              _lib.ptr(out), out.stride(0), _lib.ptr(resid), resid.stride(0), 4, _lib.stream_ptr())
+    torch.cuda.synchronize()
+    _lib.check_status("gemm_tp_rs_fp8")
+    want = (fp8.dequantize(aq) @ fp8.dequantize(bq).t()).bfloat16().float() + resid.float()
+    err = (out.float() - want).abs().max().item()
+    assert err < 2e-2 * want.abs().max().item(), err
