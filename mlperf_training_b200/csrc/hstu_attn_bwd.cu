@@ -208,7 +208,12 @@ hstu_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const bool row_ok = q_pos < len;
       const int q_id = min(max(q_pos - ctx + (ctx > 0 ? 1 : 0), 0), max_id);
       const bool plain = (n_tgt == 0 && ctx == 0);
-      const bool need_mask = !plain || (kv0 + BKV - 1 > q0) || (kv0 + BKV > len) || (q0 + BQ > len);
+      // a tile whose every (query, key) pair is visible needs no element mask: ids grow with the position, so it
+      // is enough that the tile's first query is later than its last key, and that both tiles lie inside the sequence
+      const int first_q_id = min(max(q0 - ctx + (ctx > 0 ? 1 : 0), 0), max_id);
+      const int last_k_id = min(max(kv0 + BKV - 1 - ctx + (ctx > 0 ? 1 : 0), 0), max_id);
+      const bool inside = (kv0 + BKV <= len) && (q0 + BQ <= len);
+      const bool need_mask = plain ? ((kv0 + BKV - 1 > q0) || !inside) : !(inside && first_q_id > last_k_id);
       if (!mbar_wait(sdp_full, it & 1, abort_flag, p.status, 90)) { ok = false; break; }
       tc_fence_after();
       // the P / dS tiles are free: this warp waited for dq_full of the previous iteration in its drain step

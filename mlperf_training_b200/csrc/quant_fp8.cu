@@ -83,7 +83,59 @@ quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, int 
   }
 }
 
+// Row-wise copy only, any number of rows (jagged token buffers): a thread converts 8 elements.
+template <int E5M2>
+__global__ void __launch_bounds__(256)
+quant_fp8_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, long long R, int C, const float* __restrict__ scale,
+                      uint8_t* __restrict__ q, long long ldq, unsigned int* __restrict__ amax_bits) {
+  __shared__ float red[8];
+  const float s = scale != nullptr ? *scale : 1.f;
+  const int vpr = C / 8;
+  const long long total = R * vpr;
+  float amax = 0.f;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+    const long long r = i / vpr;
+    const int v = (int)(i - r * vpr);
+    const uint4 u = *reinterpret_cast<const uint4*>(x + r * ldx + v * 8);
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+    const float f[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+    *reinterpret_cast<uint2*>(q + r * ldq + v * 8) =
+        make_uint2(pack4<E5M2>(f[0] * s, f[1] * s, f[2] * s, f[3] * s), pack4<E5M2>(f[4] * s, f[5] * s, f[6] * s, f[7] * s));
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0 && amax_bits != nullptr) {
+    float m = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+    atomicMax(amax_bits, __float_as_uint(m));
+  }
+}
+
 }  // namespace
+
+// x: bf16 [R, C] with row pitch ldx (elements), any R, C a multiple of 8; q: [R, C] codes with row pitch ldq (bytes,
+// a multiple of 8).  scale / amax_bits as in b200_quant_fp8.
+B200_API int b200_quant_fp8_rows(const void* x, long long ldx, long long R, int C, const float* scale, int e5m2, void* q,
+                                 long long ldq, void* amax_bits, void* stream) {
+  if (R <= 0) return 0;
+  if (C % 8 != 0 || ldx % 8 != 0 || ldq % 8 != 0 || ((uintptr_t)x & 15) != 0 || ((uintptr_t)q & 7) != 0)
+    return b200::fail(722, "quant_fp8_rows: C=%d and the pitches must be multiples of 8, the buffers aligned", C);
+  long long g = (R * (C / 8) + 255) / 256;
+  const long long cap = (long long)b200::sm_count() * 8;
+  const int grid = (int)(g < cap ? g : cap);
+  if (e5m2)
+    quant_fp8_rows_kernel<1><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, R, C, scale, (uint8_t*)q, ldq,
+                                                                    (unsigned int*)amax_bits);
+  else
+    quant_fp8_rows_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, R, C, scale, (uint8_t*)q, ldq,
+                                                                    (unsigned int*)amax_bits);
+  b200::count_launch();
+  return b200::check_launch("quant_fp8_rows");
+}
 
 // x: bf16 [R, C] (row pitch ldx elements; R, C multiples of 128).  scale: one device float multiplied
 // into every element before the cast (null = 1).  q_row [R, C] / q_col [C, R]: outputs, either may be

@@ -62,6 +62,7 @@ class HSTUConfig:
     targets_only_last: bool = True
     dtype: str = "bf16"
     precision: str = "bf16"
+    attn_precision: str = "bf16"       # "fp8": attention forward on per-tensor e4m3 Q, K, V (head dim 128, GPU)
 
     def torch_dtype(self):
         return {"bf16": torch.bfloat16, "fp32": torch.float32}[self.dtype]
@@ -173,7 +174,7 @@ class STULayer(nn.Module):
         q = q_raw.unflatten(-1, (h, cfg.d_qk))
         k = k_raw.unflatten(-1, (h, cfg.d_qk))
         attn = hstu_attention(q, k, v, offsets, cfg.max_seq_len + cfg.contextual, cfg.d_qk ** -0.5, num_targets,
-                              cfg.contextual).reshape(x.shape[0], h * cfg.d_v)
+                              cfg.contextual, precision=cfg.attn_precision, owner=self).reshape(x.shape[0], h * cfg.d_v)
         if self.fuse_glue and gate_cat_eligible(u_raw, attn):
             # SiLU(u), the layer norm of the attention output, their product and the concatenation in one kernel
             # (and the dropout of the concatenation, its mask regenerated in backward from a Philox seed)

@@ -73,6 +73,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_mc_all_gather": [P, P, L, P],
         "b200_zero_adamw_all_gather_mc": [P, P, L, P, P, P, P, F, F, F, F, F, I, F, P, F, I, P],
         "b200_quant_fp8": [P, L, I, I, P, I, P, P, P, P],
+        "b200_quant_fp8_rows": [P, L, L, I, P, I, P, L, P, P],
+        "b200_hstu_attn_fwd_fp8": [P, P, P, P, P, P, I, L, I, I, I, I, L, L, L, L, F, P, P, P, P],
         "b200_gemm_fp8": [P, P, P, I, I, I, L, L, L, I, I, P, P, I, I, P, P, L, F, P],
         "b200_ln_modulate_fwd": [P, P, P, L, P, P, P, I, I, I, F, P],
         "b200_ln_modulate_bwd": [P, P, P, L, P, P, P, P, P, I, I, I, P],

@@ -107,6 +107,23 @@ def quantize(x: torch.Tensor, state: DelayedScale, *, want_row: bool = True, wan
             FP8Operand(q_col, state.inv_scale, C, R, fmt) if want_col else None)
 
 
+def quantize_rows(x: torch.Tensor, state: DelayedScale) -> FP8Operand:
+    """Row-wise copy of a 2-D bf16 ``x [R, C]`` with any number of rows (jagged token buffers; ``x`` may be a
+    column block of a wider matrix): codes ``[R, C]``, ``state.scale`` applied, amax accumulated."""
+    R, C = x.shape
+    fmt = state.fmt
+    if not use_kernels(x):
+        return quantize(x, state)[0]
+    if x.dtype != torch.bfloat16:
+        raise TypeError("fp8.quantize_rows: bf16 input required")
+    if x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()
+    q = torch.empty((R, C), dtype=torch.uint8, device=x.device)
+    call("b200_quant_fp8_rows", ptr(x), x.stride(0), R, C, ptr(state.scale), int(fmt == "e5m2"), ptr(q), q.stride(0),
+         ptr(state.amax), stream_ptr())
+    return FP8Operand(q, state.inv_scale, R, C, fmt)
+
+
 def dequantize(op: FP8Operand) -> torch.Tensor:
     return op.q.view(_TORCH[op.fmt]).float() * op.inv_scale.to(op.q.device)
 

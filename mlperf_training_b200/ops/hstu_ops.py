@@ -44,12 +44,55 @@ def hstu_attention_reference(q, k, v, offsets, max_len: int, alpha: float, num_t
     return out
 
 
+def hstu_attention_fp8_reference(q, k, v, offsets, max_len: int, alpha: float, num_targets=None, contextual: int = 0,
+                                 scales=None):
+    """Eager emulation of the 8-bit forward: Q, K, V rounded to per-tensor e4m3, the activation ``silu(alpha s)``
+    rounded to e4m3 before it meets V, ``1 / N`` applied to the output.  ``scales``: the three ``DelayedScale`` states
+    (None: every tensor's own maximum)."""
+    from . import fp8 as F8
+    deq = []
+    for i, t in enumerate((q, k, v)):
+        if scales is not None:
+            sc = scales[i].scale.to(t.device).float()
+        else:
+            sc = F8.FMAX["e4m3"] / t.detach().abs().amax().float().clamp_min(1e-30)
+        deq.append((t.float() * sc).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float() / sc)
+    qd, kd, vd = deq
+    out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+    offs = offsets.tolist()
+    for b in range(len(offs) - 1):
+        lo, hi = offs[b], offs[b + 1]
+        if hi <= lo:
+            continue
+        nt = int(num_targets[b]) if num_targets is not None else 0
+        qb, kb, vb = (t[lo:hi].transpose(0, 1) for t in (qd, kd, vd))
+        s = torch.matmul(qb, kb.transpose(-1, -2)) * alpha
+        p = torch.nn.functional.silu(s) * valid_mask(hi - lo, nt, contextual, q.device)[None]
+        p = p.clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float()
+        out[lo:hi] = (torch.matmul(p, vb) / max_len).transpose(0, 1)
+    return out
+
+
+def _fp8_sites(owner, device):
+    """Delayed-scaling states of Q, K, V for the module (or any object) that owns this attention call."""
+    from . import fp8 as F8
+    sites = getattr(owner, "_attn_fp8_sites", None) if owner is not None else None
+    if sites is None:
+        sites = tuple(F8.DelayedScale("e4m3", device) for _ in range(3))
+        if owner is not None:
+            owner._attn_fp8_sites = sites
+    return sites
+
+
 class HstuAttentionFn(Function):
     @staticmethod
-    def forward(ctx, q, k, v, offsets, max_len, alpha, num_targets, contextual):
+    def forward(ctx, q, k, v, offsets, max_len, alpha, num_targets, contextual, fp8_owner=False):
         ctx.cfg = (max_len, alpha, contextual)
+        use_fp8 = fp8_owner is not False and q.shape[2] == 128
         if not use_kernels(q):
             ctx.save_for_backward(q, k, v, offsets, num_targets)
+            if use_fp8:
+                return hstu_attention_fp8_reference(q, k, v, offsets, max_len, alpha, num_targets, contextual).to(q.dtype)
             return hstu_attention_reference(q, k, v, offsets, max_len, alpha, num_targets, contextual).to(q.dtype)
         L, H, D = q.shape
         for t in (q, k, v):
@@ -58,9 +101,22 @@ class HstuAttentionFn(Function):
         offs = offsets.to(torch.int32).contiguous()
         nt = None if num_targets is None else num_targets.to(torch.int32).contiguous()
         out = torch.zeros((L, H, D), dtype=q.dtype, device=q.device)
-        call("b200_hstu_attn_fwd", ptr(q), ptr(k), ptr(v), ptr(out), ptr(offs), ptr(nt), offs.numel() - 1, L, H, D,
-             int(max_len), int(contextual), q.stride(0), k.stride(0), v.stride(0), out.stride(0), float(alpha),
-             stream_ptr())
+        if use_fp8 and q.dtype == torch.bfloat16:
+            # e4m3 forward (delayed per-tensor factors); the backward below runs on the bf16 tensors
+            from . import fp8 as F8
+            from .linear import weight_epoch
+            ops = []
+            for t, st in zip((q, k, v), _fp8_sites(fp8_owner, q.device)):
+                t2 = t.as_strided((L, H * D), (t.stride(0), 1))      # heads are contiguous inside a row
+                st.prepare(t2, weight_epoch())
+                ops.append(F8.quantize_rows(t2, st))
+            call("b200_hstu_attn_fwd_fp8", ptr(ops[0].q), ptr(ops[1].q), ptr(ops[2].q), ptr(out), ptr(offs), ptr(nt),
+                 offs.numel() - 1, L, H, D, int(max_len), int(contextual), H * D, H * D, H * D, out.stride(0), float(alpha),
+                 ptr(ops[0].inv_scale), ptr(ops[1].inv_scale), ptr(ops[2].inv_scale), stream_ptr())
+        else:
+            call("b200_hstu_attn_fwd", ptr(q), ptr(k), ptr(v), ptr(out), ptr(offs), ptr(nt), offs.numel() - 1, L, H, D,
+                 int(max_len), int(contextual), q.stride(0), k.stride(0), v.stride(0), out.stride(0), float(alpha),
+                 stream_ptr())
         ctx.save_for_backward(q, k, v, offs, nt)
         return out
 
@@ -73,7 +129,7 @@ class HstuAttentionFn(Function):
             with torch.enable_grad():
                 o = hstu_attention_reference(qf, kf, vf, offs, max_len, alpha, nt, contextual)
             dq, dk, dv = torch.autograd.grad(o, (qf, kf, vf), dout.float())
-            return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None, None, None
+            return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None, None, None, None
         L, H, D = q.shape
         dout = dout if (dout.stride(2) == 1 and dout.stride(1) == D) else dout.contiguous()
         dq = torch.zeros((L, H, D), dtype=torch.float32, device=q.device)
@@ -82,11 +138,16 @@ class HstuAttentionFn(Function):
         call("b200_hstu_attn_bwd", ptr(q), ptr(k), ptr(v), ptr(dout), ptr(dq), ptr(dk), ptr(dv), ptr(offs), ptr(nt),
              offs.numel() - 1, L, H, D, int(max_len), int(contextual), q.stride(0), k.stride(0), v.stride(0),
              dout.stride(0), dk.stride(0), dv.stride(0), float(alpha), stream_ptr())
-        return dq.to(q.dtype), dk, dv, None, None, None, None, None
+        return dq.to(q.dtype), dk, dv, None, None, None, None, None, None
 
 
-def hstu_attention(q, k, v, offsets, max_len: int, alpha: float, num_targets=None, contextual: int = 0):
-    return HstuAttentionFn.apply(q, k, v, offsets, max_len, alpha, num_targets, contextual)
+def hstu_attention(q, k, v, offsets, max_len: int, alpha: float, num_targets=None, contextual: int = 0,
+                   precision: str = "bf16", owner=None):
+    """``precision="fp8"`` (head dim 128): the forward runs on per-tensor e4m3 copies of Q, K, V whose delayed-scaling
+    states live on ``owner`` (the calling module; None = fresh states, i.e. every call uses its own maxima); the
+    backward uses the bf16 tensors."""
+    fp8_owner = (owner if owner is not None else None) if precision == "fp8" else False
+    return HstuAttentionFn.apply(q, k, v, offsets, max_len, alpha, num_targets, contextual, fp8_owner)
 
 
 # --------------------------------------------------------------------------------------

@@ -288,6 +288,14 @@ def bench_hstu(quick: bool) -> None:
     ms_b = time_ms(bwd)
     emit(kernel="hstu_attention", B=B, tokens=L, H=H, D=D, fwd_ms=round(ms_f, 4), fwd_tflops=round(4.0 * H * pairs * D / ms_f / 1e9, 1),
          bwd_ms=round(ms_b, 4), bwd_tflops=round(10.0 * H * pairs * D / ms_b / 1e9, 1))
+
+    class _Owner:                     # keeps the delayed-scaling states of Q, K, V between calls, like a layer does
+        pass
+    own = _Owner()
+    with torch.no_grad():
+        ms_8 = time_ms(lambda: hstu_attention(q, k, v, offs, N, D ** -0.5, nt, 0, precision="fp8", owner=own))
+    emit(kernel="hstu_attention fp8 forward (3 quantise launches included)", B=B, tokens=L, H=H, D=D, fwd_ms=round(ms_8, 4),
+         fwd_tflops=round(4.0 * H * pairs * D / ms_8 / 1e9, 1))
     _lib.check_status("hstu")
 
 

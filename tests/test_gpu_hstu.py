@@ -47,6 +47,43 @@ def test_hstu_attention_fwd_bwd(lengths, targets, ctx, via_uvqk):
         assert (g - want).abs().max().item() < 4e-2 * s + 1e-5, name
 
 
+@pytest.mark.parametrize("lengths,targets,ctx", [
+    ([128], None, 0),
+    ([17, 300, 1, 513], None, 0),
+    ([200, 40, 384], [1, 3, 2], 8),
+])
+@pytest.mark.parametrize("via_uvqk", [False, True])
+def test_hstu_attention_fp8_forward(lengths, targets, ctx, via_uvqk):
+    """e4m3 forward against the eager emulation that rounds Q, K, V and the activation the same way, and against
+    the fp32 oracle within quantisation error; the backward still runs (bf16 kernels)."""
+    from mlperf_training_b200.ops.hstu_ops import hstu_attention_fp8_reference
+    torch.manual_seed(sum(lengths) + 1)
+    H, D, N = 4, 128, 1024
+    L = sum(lengths)
+    offs = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32)
+    nt = None if targets is None else torch.tensor(targets, dtype=torch.int32)
+    if via_uvqk:
+        uvqk = torch.randn(L, 4 * H * D, device="cuda").bfloat16()
+        v = uvqk[:, H * D:2 * H * D].unflatten(-1, (H, D))
+        q = uvqk[:, 2 * H * D:3 * H * D].unflatten(-1, (H, D))
+        k = uvqk[:, 3 * H * D:].unflatten(-1, (H, D))
+    else:
+        q, k, v = (torch.randn(L, H, D, device="cuda").bfloat16() for _ in range(3))
+    alpha = D ** -0.5
+    qg, kg, vg = (t.detach().requires_grad_(True) for t in (q, k, v))
+    out = hstu_attention(qg, kg, vg, offs.cuda(), N, alpha, None if nt is None else nt.cuda(), ctx, precision="fp8")
+    out.backward(torch.randn_like(out))
+    torch.cuda.synchronize()
+    _lib.check_status("hstu attention fp8")
+    assert qg.grad is not None and torch.isfinite(qg.grad.float()).all()
+    emu = hstu_attention_fp8_reference(q.float().cpu(), k.float().cpu(), v.float().cpu(), offs, N, alpha, nt, ctx)
+    ref = hstu_attention_reference(q.float().cpu(), k.float().cpu(), v.float().cpu(), offs, N, alpha, nt, ctx)
+    got = out.float().cpu()
+    sc = ref.abs().max().item() + 1e-9
+    assert (got - emu).abs().max().item() < 2e-2 * sc + 1e-5          # a score on a rounding boundary may flip one code
+    assert ((got - ref).norm() / ref.norm()).item() < 0.08
+
+
 def test_rowwise_adagrad_and_segment_sum_kernels():
     from mlperf_training_b200.parallel.embedding import ShardedEmbedding
     torch.manual_seed(0)
