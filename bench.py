@@ -262,6 +262,7 @@ def main() -> int:
         eng = trainer.engine
         nvls = bool(getattr(eng, "nvls", False)) or any(eng._nvls(getattr(b, "symm_grad", None)) for b in eng.buckets)
         state_gb = round(eng.state_bytes() / 2**30, 2)
+        del eng                          # the stock arms below need this arm's memory back: hold no second reference
     K_, W_ = args.steps, args.warmup
     tokens_per_step = args.local_batch * cfg.seq_len * world
     host = synthetic_tokens(W_ + 2 * K_, args.local_batch, cfg.seq_len, cfg.vocab_size, seed=0, rank=rank)
@@ -319,10 +320,13 @@ def main() -> int:
     stock = {}
     if args.impl == "b200" and args.stock.lower() not in ("", "none"):
         # free this arm's model, optimizer state and peer-mapped buffers before the stock models are built
-        del trainer
+        del trainer, dev_tokens
         import gc
         gc.collect()
+        torch.cuda.synchronize()
         torch.cuda.empty_cache()
+        if rank == 0:
+            print(f"[bench] own arm freed: {torch.cuda.memory_allocated(device) / 2**30:.1f} GiB still allocated", file=sys.stderr, flush=True)
         for prec in [s.strip() for s in args.stock.split(",") if s.strip()]:
             try:
                 stock[prec] = time_stock_arm(args, cfg, opt, tc, device, world, rank, prec)

@@ -2,7 +2,7 @@
 each next to the stock library call for the same problem (cuBLAS through ``torch.matmul``,
 ``scaled_dot_product_attention``), with an L2 flush between timed launches.
 
-    python -m mlperf_training_b200.utils.microbench gemm mxfp8 fp8 attention elementwise grouped hstu glue sparse [--quick]
+    python -m mlperf_training_b200.utils.microbench gemm mxfp8 fp8 attention elementwise grouped hstu glue sparse comm [--quick]
 
 Prints one JSON object per measurement.
 """
@@ -330,6 +330,93 @@ def bench_sparse(quick: bool) -> None:
     _lib.check_status("sparse")
 
 
+def bench_comm(quick: bool) -> None:
+    """The peer-memory kernels with every "peer" a buffer of THIS GPU (world 8 emulated): the same instruction
+    streams as on NVLink, so launch geometry, register use and memory-side behaviour can be profiled on one GPU;
+    the bytes that would cross NVLink are reported next to the time.  None of these kernels waits for another rank."""
+    import ctypes
+    from ..ops import moe_ops as M
+    W = 8
+    arr = lambda ts: (ctypes.c_ulonglong * len(ts))(*[t.data_ptr() for t in ts])
+    # ZeRO step: reduce-scatter of fp32 gradients by peer loads, AdamW + all-gather by peer stores
+    n_total = (16 if quick else 64) * 1024 * 1024
+    n = n_total // W
+    grads = [torch.randn(n_total, device="cuda") for _ in range(W)]
+    out = torch.empty(n, device="cuda")
+    part = torch.zeros(_lib.load().b200_zero_grid(), device="cuda")
+    ms = time_ms(lambda: _lib.call("b200_zero_reduce_scatter", arr(grads), W, 1, n, n, 1.0 / W, _lib.ptr(out), _lib.ptr(part),
+                                   _lib.stream_ptr()))
+    emit(kernel="zero_reduce_scatter (8 emulated ranks)", shard_elems=n, ms=round(ms, 4), read_gbs=round(W * n * 4 / ms / 1e6, 1),
+         nvlink_mb=round((W - 1) * n * 4 / 1e6, 1))
+    del grads
+    params = [torch.zeros(n_total, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    m, v, master = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda"), torch.randn(n, device="cuda")
+    sumsq = torch.ones(1, device="cuda")
+    ms = time_ms(lambda: _lib.call("b200_zero_adamw_all_gather", arr(params), W, 1, n, n, _lib.ptr(out), _lib.ptr(m), _lib.ptr(v),
+                                   _lib.ptr(master), 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, _lib.ptr(sumsq), 1.0, 0, _lib.stream_ptr()))
+    emit(kernel="zero_adamw_all_gather (8 emulated ranks)", shard_elems=n, ms=round(ms, 4),
+         local_gbs=round(n * (4 * 4 + 3 * 4) / ms / 1e6, 1), nvlink_mb=round((W - 1) * n * 2 / 1e6, 1))
+    del params, m, v, master
+    # expert dispatch: scatter rows into the owners' slabs, gather rows back
+    T, k, D = (4096 if quick else 8192), 4, 2880
+    rows = T * k
+    cap = 2 * rows
+    slabs = [torch.zeros(cap, D, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    src = torch.randn(rows, D, device="cuda").bfloat16()
+    dst_rank = torch.randint(0, W, (rows,), device="cuda", dtype=torch.int32)
+    dst_row = torch.randperm(cap, device="cuda")[:rows].to(torch.int32)
+    dropped = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ms = time_ms(lambda: _lib.call("b200_scatter_rows_to_peers", _lib.ptr(src), None, _lib.ptr(dst_rank), _lib.ptr(dst_row), rows, D,
+                                   arr(slabs), W, cap, _lib.ptr(dropped), _lib.stream_ptr()))
+    emit(kernel="scatter_rows_to_peers (8 emulated ranks)", rows=rows, D=D, ms=round(ms, 4), gbs=round(2 * rows * D * 2 / ms / 1e6, 1),
+         nvlink_mb=round((W - 1) / W * rows * D * 2 / 1e6, 1))
+    back = torch.empty(rows, D, device="cuda", dtype=torch.bfloat16)
+    ms = time_ms(lambda: _lib.call("b200_gather_rows_from_peers", arr(slabs), _lib.ptr(dst_rank), _lib.ptr(dst_row), rows, D,
+                                   _lib.ptr(back), W, cap, _lib.stream_ptr()))
+    emit(kernel="gather_rows_from_peers (8 emulated ranks)", rows=rows, D=D, ms=round(ms, 4), gbs=round(2 * rows * D * 2 / ms / 1e6, 1))
+    del slabs
+    # routing tables of the dispatch in one kernel
+    E, L = 32, 4
+    allc = torch.randint(900, 1200, (W, E), device="cuda", dtype=torch.int32)
+    seg = torch.cat([torch.zeros(1, dtype=torch.int32, device="cuda"), allc[1].cumsum(0).to(torch.int32)])
+    npairs = int(seg[-1])
+    outs = [torch.empty(npairs, dtype=torch.int32, device="cuda") for _ in range(2)]
+    seg2, cnt2 = torch.empty(L + 1, dtype=torch.int32, device="cuda"), torch.empty(L, dtype=torch.int32, device="cuda")
+    capr = 2 * npairs // 256 * 256
+    te = torch.empty(capr // 256, dtype=torch.int32, device="cuda")
+    ms = time_ms(lambda: _lib.call("b200_ep_route", _lib.ptr(allc), _lib.ptr(seg), W, E, 1, 256, capr, npairs, _lib.ptr(outs[0]),
+                                   _lib.ptr(outs[1]), _lib.ptr(seg2), _lib.ptr(cnt2), _lib.ptr(te), _lib.stream_ptr()))
+    emit(kernel="ep_route", pairs=npairs, experts=E, ms=round(ms, 4))
+    # all-gather -> GEMM with two emulated ranks (pull mode: the copy CTAs of the launch fetch the other block)
+    rows_per, K, N = 2048, (4096 if quick else 8192), 3584
+    x = (torch.randn(2 * rows_per, K, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+    bufs = [x.clone(), x.clone()]
+    o = torch.empty(2 * rows_per, N, device="cuda", dtype=torch.bfloat16)
+    flags = torch.zeros(32, dtype=torch.int32, device="cuda")
+
+    def ag():
+        flags.zero_()
+        _lib.call("b200_gemm_tp_gather", _lib.ptr(bufs[0]), _lib.ptr(w), _lib.ptr(o), 2 * rows_per, N, K, K, K, N, 0, 0, 0, 0, 1.0, 1,
+                  arr(bufs), 2, 0, _lib.ptr(bufs[0]), rows_per * K * 2, rows_per, _lib.ptr(flags), 8, 0, None, _lib.stream_ptr())
+    ms = time_ms(ag)
+    emit(kernel="gemm_tp all-gather -> GEMM (2 emulated ranks, pull)", M=2 * rows_per, N=N, K=K, ms=round(ms, 4),
+         tflops=round(2.0 * 2 * rows_per * N * K / ms / 1e9, 1), pulled_mb=round(rows_per * K * 2 / 1e6, 1))
+    stage = torch.empty(2 * rows_per, N, device="cuda", dtype=torch.bfloat16)
+    rs_flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    work = torch.zeros(1, dtype=torch.int32, device="cuda")
+    o2 = torch.empty(2 * rows_per, N, device="cuda", dtype=torch.bfloat16)
+
+    def rs():
+        rs_flags.zero_(); work.zero_()
+        _lib.call("b200_gemm_tp_rs", _lib.ptr(x), _lib.ptr(w), 2 * rows_per, N, K, K, K, 0, 0, 1.0, arr([stage]), arr([rs_flags]), 1, 0,
+                  _lib.ptr(work), _lib.ptr(o2), N, None, 0, 8, _lib.stream_ptr())
+    ms = time_ms(rs)
+    emit(kernel="gemm_tp GEMM -> reduce-scatter (world 1: staging + reduce queue)", M=2 * rows_per, N=N, K=K, ms=round(ms, 4),
+         tflops=round(2.0 * 2 * rows_per * N * K / ms / 1e9, 1))
+    _lib.check_status("comm")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("what", nargs="*", default=["gemm", "attention", "elementwise"])
@@ -344,7 +431,7 @@ def main(argv=None) -> int:
         return 1
     for w in args.what:
         {"gemm": bench_gemm, "mxfp8": bench_mxfp8, "fp8": bench_fp8, "attention": bench_attention, "elementwise": bench_elementwise,
-         "grouped": bench_grouped, "hstu": bench_hstu, "glue": bench_glue, "sparse": bench_sparse}[w](args.quick)
+         "grouped": bench_grouped, "hstu": bench_hstu, "glue": bench_glue, "sparse": bench_sparse, "comm": bench_comm}[w](args.quick)
     return 0
 
 
