@@ -34,6 +34,8 @@
 
 #include "common.cuh"
 #include "runtime.h"
+#include "tp_copy.cuh"
+#include "tp_reduce.cuh"
 
 namespace gemmcore {
 
@@ -308,7 +310,7 @@ struct PairCfg {
   static_assert(USED_COLS <= 512, "accumulators and scale sets exceed tensor memory");
   static_assert(B_SUB % 1024 == 0, "B half tile must be whole swizzle atoms");
   static_assert(STAGES >= 2, "not enough shared memory for two stages");
-  static_assert(NUM_BARS * 8 + 8 <= 512, "barrier block overflows its 512 bytes");
+  static_assert(NUM_BARS * 8 + 16 <= 512, "barrier block overflows its 512 bytes");
   static_assert(BN % 16 == 0 && BN <= 256, "N of a 256-row MMA must be a multiple of 16 up to 256");
 };
 
@@ -332,6 +334,56 @@ struct TileInfo {
   bool valid;
 };
 
+// All-gather -> GEMM inside one launch (tensor parallelism, sequence-parallel activations): the rows of A are
+// gathered over W ranks.  Rank c's block is the byte range [c * chunk_bytes, (c + 1) * chunk_bytes) of a buffer
+// that exists on every rank at peer_src[c] (this rank's copy: gdst); this rank has written its own block.  The
+// first n_aux CTA pairs of the launch do nothing but move blocks over NVLink (tp_copy.cuh: pull the peers' blocks
+// with bulk async copies, or push the own block to every peer with posted stores) and publish per-block counters;
+// the TMA producers of the GEMM pairs visit the row tiles own-block first, then rank + 1, rank + 2, ... - the order
+// in which the blocks land - and wait (bounded) on the counter of the block a tile needs.
+constexpr int TP_MAXW = 16;
+struct TpGather {
+  int on;
+  int W, rank;
+  int rows_per;                    // rows of A per rank block (a multiple of 256)
+  int n_aux;                       // CTA pairs that only copy
+  int copy_mode;                   // 0: pull the peers' blocks; 1: push the own block to every peer
+  const uint8_t* peer_src[TP_MAXW];
+  uint8_t* gdst;
+  long long chunk_bytes;
+  int pieces_per_chunk;
+  int* chunk_flag;                 // [W] counters of this rank, zero at launch (peer-writable memory in push mode)
+  int* chunk_flag_peer[TP_MAXW];   // push mode: rank d's chunk_flag array
+  int* status;
+};
+
+// GEMM -> reduce-scatter inside one launch (tensor parallelism, row-parallel linear): P = A * B^T is this rank's
+// partial sum [M, N]; rank o owns rows [o * rows_per, (o + 1) * rows_per).  The epilogue warps store each bf16 tile
+// into the owner's staging buffer (slot of the sending rank) through the owner's tensor map and bump the owner's
+// per-128-row counter; the first n_aux CTA pairs and, once their tiles are done, the epilogue warps of the GEMM
+// pairs reduce the rows this rank owns (tp_reduce.cuh).  Tiles are visited row-tile-major across owners, so that row
+// tile j of every owner completes while tile j + 1 is being computed.
+struct TpReduce {
+  int on;
+  int W, rank;
+  int rows_per;                    // rows per owner (a multiple of 256)
+  int n_aux;                       // CTA pairs that only reduce
+  int N;
+  uint8_t* stage_peer[TP_MAXW];    // rank o's staging buffer [W][rows_per][N] bf16
+  int* flag_peer[TP_MAXW];         // rank o's counters [rows_per / 128], zero at launch
+  int* work_counter;               // local, zero at launch
+  __nv_bfloat16* rs_out;
+  long long ld_out;
+  const __nv_bfloat16* rs_residual;
+  long long ld_res;
+  int* status;
+};
+
+// Tensor maps of the owners' staging buffers ([W * rows_per, N] bf16, 64 x 32 boxes); one unused entry for the
+// launches that do not reduce-scatter.
+template <int NOWN>
+struct OwnerMaps { CUtensorMap m[NOWN]; };
+
 struct PairParams {
   GroupArgs grp;
   int M, N, K;                    // K in elements (bf16) or bytes (e4m3); mode 2: M, N per expert, K = all rows
@@ -340,6 +392,8 @@ struct PairParams {
   int group_m;
   EpiArgs epi;
   int* status;
+  TpGather tp;
+  TpReduce rs;
 };
 
 // Tile t of the launch: its row / column tile, expert and range of k stages (kb_elems = contraction
@@ -359,6 +413,17 @@ B200_DEVICE TileInfo tile_info(int t, int num_m, int num_n, int num_kb, int kb_e
     ti.valid = ti.nkb > 0;
   } else {
     tile_coords(t, num_m, num_n, p.group_m, ti.mb, ti.nb);
+    if (p.tp.on) {
+      // own block first, then the blocks of rank + 1, rank + 2, ...: the order in which the gathered blocks arrive
+      const int tpc = p.tp.rows_per / 256;
+      ti.mb = ((p.tp.rank + ti.mb / tpc) % p.tp.W) * tpc + (ti.mb % tpc);
+    }
+    if (p.rs.on) {
+      // row-tile-major across owners, starting with the next rank's rows
+      const int tpc = p.rs.rows_per / 256;
+      const int ml = ti.mb;
+      ti.mb = ((p.rs.rank + 1 + ml % p.rs.W) % p.rs.W) * tpc + ml / p.rs.W;
+    }
     if (p.grp.mode == 1) {
       ti.e = p.grp.tile_expert[ti.mb];
       ti.valid = ti.e >= 0;
@@ -367,12 +432,12 @@ B200_DEVICE TileInfo tile_info(int t, int num_m, int num_n, int num_kb, int kb_e
   return ti;
 }
 
-template <int KIND, int BN, int KSUB>
+template <int KIND, int BN, int KSUB, int NOWN = 1>
 __global__ void __launch_bounds__(PairCfg<KIND, BN, KSUB>::THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                  const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmDt,
-                 const PairParams p) {
+                 const __grid_constant__ PairParams p, const __grid_constant__ OwnerMaps<NOWN> om) {
   using C = PairCfg<KIND, BN, KSUB>;
   constexpr bool MX = C::MX;
   constexpr bool F8 = (KIND == KIND_FP8);
@@ -395,12 +460,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* sfrdy = sffull + C::STAGES;           // MX only: [STAGES]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + C::NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  volatile int* work_slot = abort_flag + 1;       // reduce-scatter: the work item the epilogue warps share
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();        // 0 = leader of the pair
-  const int pair_id = blockIdx.x >> 1;
-  const int num_pairs = gridDim.x >> 1;
+  // leading CTA pairs that only move gathered blocks / only reduce
+  const int n_aux = p.tp.on ? p.tp.n_aux : (p.rs.on ? p.rs.n_aux : 0);
+  const bool is_aux = (int)(blockIdx.x >> 1) < n_aux;
+  const int pair_id = (int)(blockIdx.x >> 1) - n_aux;
+  const int num_pairs = (int)(gridDim.x >> 1) - n_aux;
   const int num_m = (p.M + 255) / 256;
   const int num_n = (p.N + BN - 1) / BN;
   const int num_tiles = (p.grp.mode == 2 ? p.grp.E : 1) * num_m * num_n;
@@ -408,15 +477,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_kb128 = (p.K + KB_ELEMS - 1) / KB_ELEMS;   // 128-byte K blocks (scale groups of the MX layout)
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < C::STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 2 * EPI_WARPS); }
-    if (MX) {
-      for (int i = 0; i < C::STAGES; ++i) { mbar_init(&sffull[i], 1); mbar_init(&sfrdy[i], 8); }
+    if (!is_aux) {                                // a copy CTA sets up its own barriers in the same words
+      for (int i = 0; i < C::STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+      for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 2 * EPI_WARPS); }
+      if (MX) {
+        for (int i = 0; i < C::STAGES; ++i) { mbar_init(&sffull[i], 1); mbar_init(&sfrdy[i], 8); }
+      }
     }
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 1) {
+  if (warp == 1 && !is_aux) {
     tmem_alloc_pair(tmem_holder, C::TMEM_COLS);   // one warp of each CTA of the pair takes part
     tmem_relinquish_pair();
   }
@@ -424,15 +495,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   cluster_sync_all();                             // the partner's barriers are initialised before any remote signal
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_base = is_aux ? 0u : *tmem_holder;
 
-  if (warp == 0) {
+  if (is_aux) {
+    // ------------------------------ copy CTAs of the all-gather ------------------------------
+    if constexpr (!MX) {                          // (the gathering launchers use the bf16 and per-tensor FP8 kinds)
+      static_assert(tpcopy::COPY_STAGES * tpcopy::COPY_PIECE <= C::STAGES * C::STAGE, "copy ring must fit the operand stages");
+      if (p.rs.on) tpreduce::reduce_cta(p.rs, num_n, smem, bars, C::THREADS);
+      else if (p.tp.copy_mode == 1) tpcopy::copy_cta_push(p.tp, (int)blockIdx.x, 2 * n_aux, C::THREADS);
+      else tpcopy::copy_cta(p.tp, (int)blockIdx.x, 2 * n_aux, smem, bars);
+    }
+  } else if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
     if (lane == 0) {
       tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB);
       if (MX) { tma_prefetch_desc(&tmSFA); tma_prefetch_desc(&tmSFB); }
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
+      uint32_t ready = p.tp.on ? (1u << p.tp.rank) : 0xffffffffu;   // gathered blocks known to be in the local buffer
       for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
         const TileInfo ti = tile_info(t, num_m, num_n, num_kb, KB_ELEMS * KSUB, p);
         if (!ti.valid) continue;
@@ -440,6 +520,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int nb = ti.nb + (p.grp.mode == 1 ? ti.e * num_n : 0);   // column tile inside the stacked B
         const int m0 = mb * 256 + (int)rank * 128;          // this CTA's rows of A
         const int n0 = ti.nb * BN + (int)rank * C::BNH + (p.grp.mode == 1 ? ti.e * p.N : 0);   // this CTA's rows of B
+        if (p.tp.on) {
+          const int c = (mb * 256) / p.tp.rows_per;             // rank block that holds this tile's rows of A
+          if (!(ready & (1u << c))) {
+            if (!flag_wait_geq(p.tp.chunk_flag + c, p.tp.pieces_per_chunk, B200_WAIT_LIMIT_NS, p.status, 311)) {
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            tpcopy::fence_proxy_async_all();                    // the block was written through another CTA's (or GPU's) proxy
+            ready |= 1u << c;
+          }
+        }
         for (int kb = ti.kb0; kb < ti.kb0 + ti.nkb; ++kb) {
           if (!mbar_wait_spin(&empty[stage], phase ^ 1, abort_flag, p.status, 310)) { ok = false; break; }
           const uint32_t bar = mapa_u32(smem_u32(&full[stage]), 0);
@@ -551,14 +643,33 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, p.status, 330)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
-      epilogue_drain<BN, (BN % 64 == 0)>(&tmD, &tmDt, p.epi, t_row, ti.mb * 256 + (int)rank * 128 + q * 32, ti.nb * BN, stg, buf,
-                                         lane, p.grp.mode == 2 ? ti.e * p.M : 0);
+      if (p.rs.on) {
+        // the tile goes into the owner's staging slot of this rank, through the owner's tensor map; then the owner's
+        // counter of these 128 rows learns that this warp's part has landed
+        const int m0 = ti.mb * 256 + (int)rank * 128;
+        const int owner = m0 / p.rs.rows_per;
+        const CUtensorMap* tmo = &om.m[owner < NOWN ? owner : 0];
+        epilogue_drain<BN, (BN % 64 == 0)>(tmo, tmo, p.epi, t_row, m0 + q * 32, ti.nb * BN, stg, buf, lane,
+                                           (p.rs.rank - owner) * p.rs.rows_per);
+        if (lane == 0) {
+          tma_store_wait_all<0>();
+          tpcopy::fence_proxy_async_all();
+          __threadfence_system();
+          tpcopy::red_release_sys_add(p.rs.flag_peer[owner] + (m0 - owner * p.rs.rows_per) / 128, 1);
+        }
+      } else {
+        epilogue_drain<BN, (BN % 64 == 0)>(&tmD, &tmDt, p.epi, t_row, ti.mb * 256 + (int)rank * 128 + q * 32, ti.nb * BN, stg, buf,
+                                           lane, p.grp.mode == 2 ? ti.e * p.M : 0);
+      }
       // all TMEM reads of this accumulator are complete (tcgen05.wait::ld inside): hand it back to the leader
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc ? tempty_leader1 : tempty_leader0);
     }
     if (lane == 0) tma_store_wait_all<0>();
+    // tiles done: help with the reduction of the rows this rank owns.  All four warps enter (their named barrier
+    // needs every one of them); after an abort the leader hands out no work.
+    if (p.rs.on) tpreduce::reduce_loop(p.rs, num_n, (int)threadIdx.x - 64, EPI_WARPS * 32, 1, work_slot, abort_flag);
   } else if (MX) {
     // ------------------------------ scale forwarders (both CTAs, MXFP8) ------------------------------
     // Warp of TMEM lane quarter q: per k block, lane l reads the 16 bytes of each staged atom that hold
@@ -602,7 +713,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 
   // ------------------------------ teardown ------------------------------
-  if (*abort_flag) {
+  if (!is_aux && *abort_flag) {                   // (a copy / reduce CTA reuses these words and waits for its own copies)
     // let copies that are still in flight land before shared memory is released
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -610,7 +721,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();                             // no signal to the partner is in flight past this point
-  if (warp == 1) {
+  if (warp == 1 && !is_aux) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
   }
@@ -619,16 +730,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // Launches gemm_pair_kernel on as many CTA pairs as can be resident at once (a persistent grid must
 // not exceed that: a pair that waits for SMs would start only after a resident pair finished all its
 // tiles).  Returns 0, or a failure code with message.
-template <int KIND, int BN, int KSUB>
+template <int KIND, int BN, int KSUB, int NOWN = 1>
 int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmSFA, const CUtensorMap& tmSFB,
                 const CUtensorMap& tmD, const CUtensorMap& tmDt, const PairParams& p, cudaStream_t stream,
-                const char* what) {
+                const char* what, const OwnerMaps<NOWN>* owners = nullptr) {
   using C = PairCfg<KIND, BN, KSUB>;
   static int max_pairs[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
   dev &= 63;
-  auto kern = gemm_pair_kernel<KIND, BN, KSUB>;
+  auto kern = gemm_pair_kernel<KIND, BN, KSUB, NOWN>;
+  static const OwnerMaps<NOWN> no_owners = {};
+  const OwnerMaps<NOWN>& om = owners != nullptr ? *owners : no_owners;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -655,9 +768,13 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
   }
   const int num_m = (p.M + 255) / 256, num_n = (p.N + BN - 1) / BN;
   const int tiles = (p.grp.mode == 2 ? p.grp.E : 1) * num_m * num_n;
-  const int pairs = tiles < max_pairs[dev] ? tiles : max_pairs[dev];
+  // every CTA of a gathering launch must be resident at once: its GEMM pairs wait for its copy pairs
+  const int n_aux = p.tp.on ? p.tp.n_aux : (p.rs.on ? p.rs.n_aux : 0);
+  if (n_aux >= max_pairs[dev]) return b200::fail(823, "%s: %d copy pairs leave no SM for the GEMM", what, n_aux);
+  const int room = max_pairs[dev] - n_aux;
+  const int pairs = (tiles < room ? tiles : room) + n_aux;
   cfg.gridDim = dim3(2 * pairs, 1, 1);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmSFA, tmSFB, tmD, tmDt, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmSFA, tmSFB, tmD, tmDt, p, om);
   b200::count_launch();
   if (e != cudaSuccess) {
     cudaGetLastError();

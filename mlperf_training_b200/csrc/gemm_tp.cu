@@ -27,6 +27,8 @@
 // Loads never use cluster multicast.  Every wait is bounded (2 s) and reports into the status block.
 #include "common.cuh"
 #include "runtime.h"
+#include "tp_copy.cuh"
+#include "tp_reduce.cuh"
 
 namespace {
 
@@ -37,9 +39,16 @@ constexpr int NUM_THREADS = 192;
 constexpr int EPI_WARPS = 4;
 constexpr int STG_BYTES = 4096;
 constexpr int MAXW = 16;
-constexpr int COPY_PIECE = 32768;     // bytes per bulk copy
-constexpr int COPY_STAGES = 6;
-constexpr int RS_SPLIT = 64;          // reduce work items per 128-row tile (2 rows each: a short tail)
+using tpcopy::COPY_PIECE;
+using tpcopy::COPY_STAGES;
+using tpcopy::PUSH_PIECE;
+using tpcopy::bulk_g2s;
+using tpcopy::bulk_s2g;
+using tpcopy::fence_proxy_async_all;
+using tpcopy::red_release_gpu_add;
+using tpcopy::red_release_sys_add;
+using tpcopy::ld_cg_u4;
+using tpreduce::RS_SPLIT;
 
 template <int BN>
 struct Cfg {
@@ -87,29 +96,6 @@ struct Params {
   long long ld_res;
 };
 
-B200_DEVICE void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-B200_DEVICE void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
-               "r"(bytes)
-               : "memory");
-}
-B200_DEVICE void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
-B200_DEVICE void red_release_gpu_add(int* p, int v) {
-  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-B200_DEVICE void red_release_sys_add(int* p, int v) {
-  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-B200_DEVICE uint4 ld_cg_u4(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
-
 // logical tile index -> (row tile, column tile) with the visiting order of the mode
 B200_DEVICE void tile_coords(int t, int num_m, int num_n, const Params& p, int& mb, int& nb) {
   const int in_group = p.group_m * num_n;
@@ -127,258 +113,6 @@ B200_DEVICE void tile_coords(int t, int num_m, int num_n, const Params& p, int& 
     mb = ((p.rank + 1 + ml % p.W) % p.W) * tpc + ml / p.W;
   } else {
     mb = ml;
-  }
-}
-
-// ------------------------------ copy CTA (modes 1, 2) ------------------------------
-// One thread drives a ring of bulk copies peer -> shared -> local and publishes a piece two
-// stores after it was issued (its bulk group is then complete).
-B200_DEVICE void copy_cta(const Params& p, uint8_t* smem, uint64_t* bars) {
-  if (threadIdx.x != 0) return;
-  for (int i = 0; i < COPY_STAGES; ++i) mbar_init(&bars[i], 1);
-  mbar_fence_init();
-  const int ppc = p.pieces_per_chunk;
-  const int total = (p.W - 1) * ppc;
-  const int mine = (total - (int)blockIdx.x + p.n_aux - 1) / p.n_aux;   // pieces blockIdx, blockIdx + n_aux, ...
-  volatile int dummy_abort = 0;
-  auto piece_of = [&](int i, int& chunk, long long& off, uint32_t& bytes) {
-    const int g = blockIdx.x + i * p.n_aux;
-    chunk = (p.rank + 1 + g / ppc) % p.W;
-    off = (long long)(g % ppc) * COPY_PIECE;
-    const long long left = p.chunk_bytes - off;
-    bytes = (uint32_t)(left < COPY_PIECE ? left : COPY_PIECE);
-  };
-  auto issue_load = [&](int i) {
-    int c; long long off; uint32_t bytes;
-    piece_of(i, c, off, bytes);
-    const int s = i % COPY_STAGES;
-    mbar_expect_tx(&bars[s], bytes);
-    bulk_g2s(smem + s * COPY_PIECE, p.peer_src[c] + (long long)c * p.chunk_bytes + off, bytes, &bars[s]);
-  };
-  auto publish = [&](int i) {
-    int c; long long off; uint32_t bytes;
-    piece_of(i, c, off, bytes);
-    fence_proxy_async_all();
-    red_release_gpu_add(p.chunk_flag + c, 1);
-  };
-  const int ahead = COPY_STAGES - 2;
-  for (int i = 0; i < mine && i < ahead; ++i) issue_load(i);
-  bool ok = true;
-  for (int i = 0; i < mine; ++i) {
-    const int s = i % COPY_STAGES;
-    if (!mbar_wait(&bars[s], (i / COPY_STAGES) & 1, &dummy_abort, p.status, 40)) { ok = false; break; }
-    int c; long long off; uint32_t bytes;
-    piece_of(i, c, off, bytes);
-    bulk_s2g(p.gdst + (long long)c * p.chunk_bytes + off, smem + s * COPY_PIECE, bytes);
-    tma_store_commit();
-    tma_store_wait_all<2>();                 // stores up to i-2 are complete
-    if (i >= 2) publish(i - 2);
-    if (i + ahead < mine) issue_load(i + ahead);   // stage (i-2) % STAGES: its store has completed
-  }
-  tma_store_wait_all<0>();
-  if (ok) {
-    if (mine >= 2) publish(mine - 2);
-    if (mine >= 1) publish(mine - 1);
-  } else {
-    // loads that never completed may still land: give them time before shared memory is released
-    const uint64_t t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
-  }
-}
-
-// Push variant: every thread of the CTA copies 16-byte vectors of this rank's block from local memory
-// straight into every peer's buffer (plain posted stores: no round trip per piece), and one thread
-// bumps the peers' counters after each PUSH_PIECE bytes, behind a system-scope fence.
-constexpr int PUSH_PIECE = 262144;
-
-B200_DEVICE void copy_cta_push(const Params& p) {
-  // Work items are (destination, piece), destination-major: the rank that consumes this block first
-  // (rank - 1: it visits its own block, then rank + 1's, ...) receives all of it first.
-  const int ppc = (int)((p.chunk_bytes + PUSH_PIECE - 1) / PUSH_PIECE);
-  const long long base = (long long)p.rank * p.chunk_bytes;
-  const uint8_t* src = p.gdst + base;
-  const int items = (p.W - 1) * ppc;
-  for (int it = blockIdx.x; it < items; it += p.n_aux) {
-    const int d = (p.rank - 1 - it / ppc + 2 * p.W) % p.W;
-    const long long off = (long long)(it % ppc) * PUSH_PIECE;
-    const long long left = p.chunk_bytes - off;
-    const int nvec = (int)((left < PUSH_PIECE ? left : PUSH_PIECE) / 16);
-    uint8_t* dst = const_cast<uint8_t*>(p.peer_src[d]) + base + off;
-    constexpr int U = 16;
-    for (int v0 = threadIdx.x; v0 < nvec; v0 += U * NUM_THREADS) {
-      uint4 q[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int v = v0 + u * NUM_THREADS;
-        if (v < nvec) q[u] = ld_cg_u4(src + off + (long long)v * 16);
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int v = v0 + u * NUM_THREADS;
-        if (v < nvec) *reinterpret_cast<uint4*>(dst + (long long)v * 16) = q[u];
-      }
-    }
-    __threadfence_system();
-    named_bar_sync(3, NUM_THREADS);
-    if (threadIdx.x == 0) red_release_sys_add(p.chunk_flag_peer[d] + p.rank, 1);
-  }
-}
-
-// ------------------------------ reduce work (mode 3) ------------------------------
-// `nthreads` threads (a named barrier `bar_id` among them) claim items until the queue is empty.
-B200_DEVICE void reduce_loop(const Params& p, int num_n, int tid, int nthreads, int bar_id, volatile int* slot,
-                             volatile int* abort_flag) {
-  const int tpc = p.rows_per / BM;
-  const int items = tpc * RS_SPLIT;
-  const int nvec = p.N / 8;
-  const uint8_t* stage = p.stage_peer[p.rank];
-  const int* flags = p.flag_peer[p.rank];
-  while (true) {
-    if (tid == 0) {
-      int it = (abort_flag != nullptr && *abort_flag) ? items : atomicAdd(p.work_counter, 1);
-      if (it < items) {
-        const int want = p.W * num_n * EPI_WARPS;
-        if (!flag_wait_geq(flags + it / RS_SPLIT, want, B200_WAIT_LIMIT_NS, p.status, 50)) it = items;  // give up
-      }
-      *slot = it;
-    }
-    named_bar_sync(bar_id, nthreads);
-    const int it = *slot;
-    named_bar_sync(bar_id, nthreads);      // everyone has read the slot before it is rewritten
-    if (it >= items) break;
-    const int row0 = (it / RS_SPLIT) * BM + (it % RS_SPLIT) * (BM / RS_SPLIT);
-    constexpr int U = 4;                   // vectors per thread in flight per source
-    const int total = (BM / RS_SPLIT) * nvec;
-    for (int base = tid; base < total; base += U * nthreads) {
-      float acc[U][8];
-      long long off[U];
-      bool live[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int idx = base + u * nthreads;
-        live[u] = idx < total;
-        const int row = row0 + (live[u] ? idx / nvec : 0);
-        const int v = live[u] ? idx % nvec : 0;
-        off[u] = (long long)row * p.N + v * 8;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
-        if (p.rs_residual != nullptr && live[u]) {
-          const uint4 q = *reinterpret_cast<const uint4*>(p.rs_residual + (long long)row * p.ld_res + v * 8);
-          const float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
-          acc[u][0] = f0.x; acc[u][1] = f0.y; acc[u][2] = f1.x; acc[u][3] = f1.y;
-          acc[u][4] = f2.x; acc[u][5] = f2.y; acc[u][6] = f3.x; acc[u][7] = f3.y;
-        }
-      }
-      for (int s2 = 0; s2 < p.W; ++s2) {
-        uint4 q[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          q[u] = live[u] ? ld_cg_u4(stage + ((long long)s2 * p.rows_per * p.N + off[u]) * 2) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const float2 f0 = unpack_bf16x2(q[u].x), f1 = unpack_bf16x2(q[u].y), f2 = unpack_bf16x2(q[u].z), f3 = unpack_bf16x2(q[u].w);
-          acc[u][0] += f0.x; acc[u][1] += f0.y; acc[u][2] += f1.x; acc[u][3] += f1.y;
-          acc[u][4] += f2.x; acc[u][5] += f2.y; acc[u][6] += f3.x; acc[u][7] += f3.y;
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (!live[u]) continue;
-        const int idx = base + u * nthreads;
-        const int row = row0 + idx / nvec;
-        const int v = idx % nvec;
-        const uint4 o = make_uint4(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]),
-                                   pack_bf16x2(acc[u][4], acc[u][5]), pack_bf16x2(acc[u][6], acc[u][7]));
-        *reinterpret_cast<uint4*>(p.rs_out + (long long)row * p.ld_out + v * 8) = o;
-      }
-    }
-  }
-}
-
-// ------------------------------ dedicated reduce CTA (mode 3) ------------------------------
-// Streams the W staged copies of each row segment into shared memory with bulk async copies (one
-// thread keeps a 6-deep ring of 32 KB stages in flight), five consumer warps add them in fp32.
-struct RedMeta { int row, c0, cols; };
-
-B200_DEVICE void reduce_cta(const Params& p, int num_n, uint8_t* smem, uint64_t* bars) {
-  constexpr int RST = COPY_STAGES;
-  constexpr int CONSUMER_WARPS = NUM_THREADS / 32 - 1;
-  uint64_t* full = bars;
-  uint64_t* empty = bars + RST;
-  RedMeta* meta = reinterpret_cast<RedMeta*>(bars + 2 * RST);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + RST);
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < RST; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], CONSUMER_WARPS); }
-    *abort_flag = 0;
-    mbar_fence_init();
-  }
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int unit_cols = (COPY_PIECE / 2 / p.W) & ~7;
-  if (unit_cols > p.N) unit_cols = p.N;
-  const uint8_t* stage = p.stage_peer[p.rank];
-  if (warp == 0) {
-    if (lane != 0) return;
-    const int tpc = p.rows_per / BM;
-    const int items = tpc * RS_SPLIT;
-    const int want = p.W * num_n * EPI_WARPS;
-    const int* flags = p.flag_peer[p.rank];
-    int st = 0; uint32_t ph = 0;
-    bool ok = true;
-    while (ok) {
-      const int it = atomicAdd(p.work_counter, 1);
-      if (it >= items) break;
-      if (!flag_wait_geq(flags + it / RS_SPLIT, want, B200_WAIT_LIMIT_NS, p.status, 51)) break;
-      fence_proxy_async_all();
-      const int row0 = (it / RS_SPLIT) * BM + (it % RS_SPLIT) * (BM / RS_SPLIT);
-      for (int r = 0; r < BM / RS_SPLIT && ok; ++r) {
-        for (int c0 = 0; c0 < p.N; c0 += unit_cols) {
-          if (!mbar_wait(&empty[st], ph ^ 1, abort_flag, p.status, 52)) { ok = false; break; }
-          const int cols = min(unit_cols, p.N - c0);
-          meta[st].row = row0 + r; meta[st].c0 = c0; meta[st].cols = cols;
-          mbar_expect_tx(&full[st], (uint32_t)(p.W * cols * 2));
-          for (int s2 = 0; s2 < p.W; ++s2)
-            bulk_g2s(smem + st * COPY_PIECE + s2 * cols * 2,
-                     stage + (((long long)s2 * p.rows_per + row0 + r) * p.N + c0) * 2, (uint32_t)(cols * 2), &full[st]);
-          if (++st == RST) { st = 0; ph ^= 1; }
-        }
-      }
-    }
-    // sentinel: tells the consumers to leave
-    if (mbar_wait(&empty[st], ph ^ 1, abort_flag, p.status, 53)) {
-      meta[st].row = -1;
-      mbar_arrive(&full[st]);
-    }
-    return;
-  }
-  int st = 0; uint32_t ph = 0;
-  const int ctid = threadIdx.x - 32, cn = CONSUMER_WARPS * 32;
-  while (true) {
-    if (!mbar_wait(&full[st], ph, abort_flag, p.status, 54)) break;
-    const RedMeta m = meta[st];
-    if (m.row < 0) break;
-    const uint8_t* sb = smem + st * COPY_PIECE;
-    for (int v = ctid; v < m.cols / 8; v += cn) {
-      float acc[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      if (p.rs_residual != nullptr) {
-        const uint4 q = *reinterpret_cast<const uint4*>(p.rs_residual + (long long)m.row * p.ld_res + m.c0 + v * 8);
-        const float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
-        acc[0] = f0.x; acc[1] = f0.y; acc[2] = f1.x; acc[3] = f1.y; acc[4] = f2.x; acc[5] = f2.y; acc[6] = f3.x; acc[7] = f3.y;
-      }
-      for (int s2 = 0; s2 < p.W; ++s2) {
-        const uint4 q = *reinterpret_cast<const uint4*>(sb + s2 * m.cols * 2 + v * 16);
-        const float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
-        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-      }
-      const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
-                                 pack_bf16x2(acc[6], acc[7]));
-      *reinterpret_cast<uint4*>(p.rs_out + (long long)m.row * p.ld_out + m.c0 + v * 8) = o;
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[st]);
-    if (++st == RST) { st = 0; ph ^= 1; }
   }
 }
 
@@ -412,9 +146,9 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   // ---------------- auxiliary CTAs: no tensor memory, no GEMM barriers ----------------
   if ((int)blockIdx.x < p.n_aux) {
-    if (p.mode == 3) reduce_cta(p, num_n, smem, bars);
-    else if (p.copy_mode == 1) copy_cta_push(p);
-    else copy_cta(p, smem, bars);
+    if (p.mode == 3) tpreduce::reduce_cta(p, num_n, smem, bars, NUM_THREADS);
+    else if (p.copy_mode == 1) tpcopy::copy_cta_push(p, (int)blockIdx.x, p.n_aux, NUM_THREADS);
+    else tpcopy::copy_cta(p, (int)blockIdx.x, p.n_aux, smem, bars);
     return;
   }
   const int cta = blockIdx.x - p.n_aux;
@@ -618,7 +352,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) tma_store_wait_all<0>();
     // tiles done: help with the reduction of the rows this rank owns.  All four warps enter (their
     // named barrier needs every one of them); after an abort the leader hands out no work.
-    if (p.mode == 3) reduce_loop(p, num_n, threadIdx.x - 64, EPI_WARPS * 32, 1, work_slot, abort_flag);
+    if (p.mode == 3) tpreduce::reduce_loop(p, num_n, threadIdx.x - 64, EPI_WARPS * 32, 1, work_slot, abort_flag);
   }
 
   // ------------------------------ teardown ------------------------------

@@ -98,6 +98,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200_flag_wait_probe": [P, I, L, P, P],
         "b200_gemm_tp_gather": [P, P, P, I, I, I, L, L, L, I, I, I, I, F, I, P, I, I, P, L, I, P, I, I, P, P],
         "b200_gemm_tp_rs": [P, P, I, I, I, L, L, I, I, F, P, P, I, I, P, P, L, P, L, I, P],
+        "b200_gemm_tp_gather_pair": [P, P, P, I, I, I, L, L, L, I, I, I, P, P, F, P, I, I, P, L, I, P, I, I, P, P],
+        "b200_gemm_tp_rs_pair": [P, P, I, I, I, L, L, I, I, I, P, P, F, P, P, I, I, P, P, L, P, L, I, P],
         "b200_gemm_tp_gather_fp8": [P, P, P, I, I, I, L, L, L, I, I, P, P, I, I, F, I, P, I, I, P, L, I, P, I, I, P, P],
         "b200_gemm_tp_rs_fp8": [P, P, I, I, I, L, L, I, I, P, P, F, P, P, I, I, P, P, L, P, L, I, P],
         "b200_gather_rows_to_peers": [P, L, P, P, L, I, I, P, P, P],

@@ -180,6 +180,13 @@ class TPContext:
         N = b.rows
         rows_per = T // W
         out = torch.empty((T, N), dtype=torch.bfloat16, device=full.device)
+        if rows_per % 256 == 0:
+            # the CTA-pair core with copy pairs inside the launch
+            _lib.call("b200_gemm_tp_gather_pair", _lib.ptr(full), _lib.ptr(b.q), _lib.ptr(out), T, N, Kd, full.stride(0),
+                      b.q.stride(0), out.stride(0), 1, int(a_fmt == "e5m2"), int(b.fmt == "e5m2"), _lib.ptr(a_inv),
+                      _lib.ptr(b.inv_scale), 1.0, buf.ptr_array(), W, r, _lib.ptr(full), rows_per * Kd, rows_per,
+                      _lib.ptr(self._flags.local), self.n_copy, self.copy_mode, self._flags.ptr_array(), _lib.stream_ptr())
+            return out
         _lib.call("b200_gemm_tp_gather_fp8", _lib.ptr(full), _lib.ptr(b.q), _lib.ptr(out), T, N, Kd, full.stride(0),
                   b.q.stride(0), out.stride(0), int(a_fmt == "e5m2"), int(b.fmt == "e5m2"), _lib.ptr(a_inv), _lib.ptr(b.inv_scale),
                   0, 0, 1.0, 1, buf.ptr_array(), W, r, _lib.ptr(full), rows_per * Kd, rows_per, _lib.ptr(self._flags.local),
@@ -196,6 +203,14 @@ class TPContext:
         self._local_flags.zero_()
         self._stage.barrier()
         out = torch.empty((rows_per, N), dtype=torch.bfloat16, device=a.q.device)
+        if rows_per % 256 == 0:
+            _lib.call("b200_gemm_tp_rs_pair", _lib.ptr(a.q), _lib.ptr(b.q), M, N, Kd, a.q.stride(0), b.q.stride(0), 1,
+                      int(a.fmt == "e5m2"), int(b.fmt == "e5m2"), _lib.ptr(a.inv_scale), _lib.ptr(b.inv_scale), 1.0,
+                      self._stage.ptr_array(), self._flags.offset_ptr_array(4 * self.RS_FLAG_OFFSET), W, r,
+                      _lib.ptr(self._local_flags[16:]), _lib.ptr(out), out.stride(0),
+                      None if residual is None else _lib.ptr(residual), 0 if residual is None else residual.stride(0), self.n_red,
+                      _lib.stream_ptr())
+            return out
         _lib.call("b200_gemm_tp_rs_fp8", _lib.ptr(a.q), _lib.ptr(b.q), M, N, Kd, a.q.stride(0), b.q.stride(0),
                   int(a.fmt == "e5m2"), int(b.fmt == "e5m2"), _lib.ptr(a.inv_scale), _lib.ptr(b.inv_scale), 1.0,
                   self._stage.ptr_array(), self._flags.offset_ptr_array(4 * self.RS_FLAG_OFFSET), W, r,
@@ -217,6 +232,12 @@ class TPContext:
             a, b, M, N, Kd, a_mn, b_mn = other, full, other.shape[1], Kf, T, 1, 1
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=full.device)
+        if mode == 1 and rows_per % 256 == 0 and out.dtype == torch.bfloat16 and not accumulate:
+            # the CTA-pair core with copy pairs inside the launch
+            _lib.call("b200_gemm_tp_gather_pair", _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, Kd, a.stride(0), b.stride(0),
+                      out.stride(0), 0, 0, 0, None, None, 1.0, buf.ptr_array(), W, r, _lib.ptr(full), rows_per * Kf * 2, rows_per,
+                      _lib.ptr(self._flags.local), self.n_copy, self.copy_mode, self._flags.ptr_array(), _lib.stream_ptr())
+            return out
         _lib.call("b200_gemm_tp_gather", _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, Kd, a.stride(0), b.stride(0),
                   out.stride(0), a_mn, b_mn, int(out.dtype == torch.float32), int(accumulate), 1.0, mode,
                   buf.ptr_array(), W, r, _lib.ptr(full), rows_per * Kf * 2, rows_per, _lib.ptr(self._flags.local),
@@ -235,6 +256,14 @@ class TPContext:
         self._local_flags.zero_()
         self._stage.barrier()           # counters are zero everywhere, previous readers of the staging buffer are done
         out = torch.empty((rows_per, N), dtype=torch.bfloat16, device=a.device)
+        if rows_per % 256 == 0 and not b_mn_major:
+            # the CTA-pair core with reduce pairs inside the launch
+            _lib.call("b200_gemm_tp_rs_pair", _lib.ptr(a), _lib.ptr(b), M, N, Kd, a.stride(0), b.stride(0), 0, 0, 0, None, None, 1.0,
+                      self._stage.ptr_array(), self._flags.offset_ptr_array(4 * self.RS_FLAG_OFFSET), W, r,
+                      _lib.ptr(self._local_flags[16:]), _lib.ptr(out), out.stride(0),
+                      None if residual is None else _lib.ptr(residual), 0 if residual is None else residual.stride(0), self.n_red,
+                      _lib.stream_ptr())
+            return out
         _lib.call("b200_gemm_tp_rs", _lib.ptr(a), _lib.ptr(b), M, N, Kd, a.stride(0), b.stride(0), 0, int(b_mn_major), 1.0,
                   self._stage.ptr_array(), self._flags.offset_ptr_array(4 * self.RS_FLAG_OFFSET), W, r,
                   _lib.ptr(self._local_flags[16:]),

@@ -151,3 +151,84 @@ def test_gemm_reduce_scatter_fp8_world1():
     want = (fp8.dequantize(aq) @ fp8.dequantize(bq).t()).bfloat16().float() + resid.float()
     err = (out.float() - want).abs().max().item()
     assert err < 2e-2 * want.abs().max().item(), err
+
+
+@pytest.mark.parametrize("W", [1, 2])
+@pytest.mark.parametrize("fp8_fmt", [None, "e4m3"])
+@pytest.mark.parametrize("N", [384, 128])
+def test_all_gather_gemm_rows_pair_core(W, fp8_fmt, N):
+    """The CTA-pair kernel with copy pairs inside the launch (emulated ranks, pull mode), bf16 and 8-bit operands."""
+    from mlperf_training_b200.ops import fp8
+    torch.manual_seed(W + N)
+    rows_per, K = 512, 640
+    T = W * rows_per
+    x = (torch.randn(T, K, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    if fp8_fmt:
+        sx, sw = fp8.DelayedScale(fp8_fmt, "cuda"), fp8.DelayedScale("e4m3", "cuda")
+        sx.prepare(x, 0); sw.prepare(w, 0)
+        xq, _ = fp8.quantize(x, sx)
+        wq, _ = fp8.quantize(w, sw)
+        src, wt, esz = xq.q, wq.q, 1
+        want = fp8.dequantize(xq) @ fp8.dequantize(wq).t()
+    else:
+        src, wt, esz = x, w, 2
+        want = x.float() @ w.float().t()
+    bufs = []
+    for r in range(W):
+        buf = torch.zeros_like(src)
+        buf[r * rows_per:(r + 1) * rows_per] = src[r * rows_per:(r + 1) * rows_per]
+        bufs.append(buf)
+    for r in range(W):
+        out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+        flags = torch.zeros(32, dtype=torch.int32, device="cuda")
+        _lib.call("b200_gemm_tp_gather_pair", _lib.ptr(bufs[r]), _lib.ptr(wt), _lib.ptr(out), T, N, K, K, K, N,
+                  int(bool(fp8_fmt)), 0, 0, _lib.ptr(sx.inv_scale) if fp8_fmt else None, _lib.ptr(sw.inv_scale) if fp8_fmt else None,
+                  1.0, _arr([t.data_ptr() for t in bufs]), W, r, _lib.ptr(bufs[r]), rows_per * K * esz, rows_per,
+                  _lib.ptr(flags), 4, 0, None, _lib.stream_ptr())
+        torch.cuda.synchronize()
+        _lib.check_status("gemm_tp_gather_pair")
+        assert torch.equal(bufs[r], src), f"rank {r}: gathered operand differs"
+        err = (out.float() - want).abs().max().item()
+        assert err < 2e-2 * want.abs().max().item(), (r, err)
+
+
+@pytest.mark.parametrize("shape", [(512, 384, 320), (1024, 128, 512)])
+@pytest.mark.parametrize("fp8_on", [False, True])
+@pytest.mark.parametrize("res", [False, True])
+def test_gemm_reduce_scatter_pair_core_world1(shape, fp8_on, res):
+    """GEMM -> reduce-scatter on the CTA-pair core, world 1: tiles through the staging buffer, counters, reduce queue."""
+    from mlperf_training_b200.ops import fp8
+    M, N, K = shape
+    torch.manual_seed(M + N)
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    inv_a = inv_b = None
+    if fp8_on:
+        K = (K + 127) // 128 * 128
+        a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+        b = (torch.randn((N + 127) // 128 * 128, K, device="cuda") * 0.5).bfloat16()
+        sa, sb = fp8.DelayedScale("e5m2", "cuda"), fp8.DelayedScale("e4m3", "cuda")
+        sa.prepare(a, 0); sb.prepare(b, 0)
+        aq, _ = fp8.quantize(a, sa)
+        bq, _ = fp8.quantize(b, sb)
+        N = b.shape[0]
+        want = (fp8.dequantize(aq) @ fp8.dequantize(bq).t()).bfloat16().float()
+        A, B, inv_a, inv_b = aq.q, bq.q, sa.inv_scale, sb.inv_scale
+    else:
+        want = (a.float() @ b.float().t()).bfloat16().float()
+        A, B = a, b
+    resid = torch.randn(M, N, device="cuda").bfloat16() if res else None
+    stage = torch.full((M, N), float("nan"), device="cuda").bfloat16()
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    work = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    _lib.call("b200_gemm_tp_rs_pair", _lib.ptr(A), _lib.ptr(B), M, N, K, K, K, int(fp8_on), int(fp8_on), 0, _lib.ptr(inv_a),
+              _lib.ptr(inv_b), 1.0, _arr([stage.data_ptr()]), _arr([flags.data_ptr()]), 1, 0, _lib.ptr(work), _lib.ptr(out),
+              out.stride(0), _lib.ptr(resid), 0 if resid is None else resid.stride(0), 4, _lib.stream_ptr())
+    torch.cuda.synchronize()
+    _lib.check_status("gemm_tp_rs_pair")
+    if res:
+        want = want + resid.float()
+    err = (out.float() - want).abs().max().item()
+    assert err < 2e-2 * want.abs().max().item(), err
