@@ -48,7 +48,7 @@ def _timed(step_fn, steps: int, warmup: int, world: int):
 def bench_gpt_oss(args, rank, world, dev):
     from ..models.gpt import GPT, gpt_oss_20b
     from ..parallel.engine import OptimConfig, ZeroEngine
-    cfg = gpt_oss_20b(precision="bf16", ep_comm=args.comm)
+    cfg = gpt_oss_20b(precision=args.precision if args.precision in ("bf16", "mxfp8") else "bf16", ep_comm=args.comm)
     if args.layers:
         cfg.n_layers = args.layers
     ep = dist.group.WORLD if world > 1 else None
@@ -71,7 +71,8 @@ def bench_gpt_oss(args, rank, world, dev):
     return {"metric": "train tokens/s", "value": tokens / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms, "loss": loss,
             "config": {"model": cfg.name, "layers": cfg.n_layers, "experts": cfg.n_experts, "top_k": cfg.top_k,
                        "global_batch": local * world, "seq_len": cfg.seq_len, "parallelism": f"ep{world} ({args.comm} dispatch) + dp{world} dense",
-                       "linears": "bf16 tcgen05 (grouped experts), bf16 dense"}}
+                       "linears": ("MXFP8 grouped experts on the CTA-pair core (bf16 where a width is not a multiple of 128)"
+                                   if cfg.precision == "mxfp8" else "bf16 tcgen05 (grouped experts), bf16 dense")}}
 
 
 def bench_llama70b_lora(args, rank, world, dev):
@@ -82,7 +83,8 @@ def bench_llama70b_lora(args, rank, world, dev):
     cfg = llama2_70b(precision="bf16", lora_rank=16, lora_alpha=32.0, lora_dropout=0.1)
     if args.layers:
         cfg.n_layers = args.layers
-    tp = TPContext(dist.group.WORLD, comm="fused" if args.comm == "fused" else "nccl", device=dev) if world > 1 else None
+    tp_prec = "fp8" if (args.precision != "bf16" and args.comm == "fused") else "bf16"
+    tp = TPContext(dist.group.WORLD, comm="fused" if args.comm == "fused" else "nccl", device=dev, precision=tp_prec) if world > 1 else None
     solo = [dist.new_group([r]) for r in range(world)][rank] if world > 1 else None
     local = args.global_batch or 8                       # data-parallel size 1: every rank sees the whole batch
     tr = PretrainTrainer(cfg, OptimConfig(lr=4e-4, beta2=0.999, eps=1e-8, weight_decay=1e-4, clip_grad=0.3),
@@ -98,7 +100,7 @@ def bench_llama70b_lora(args, rank, world, dev):
             "config": {"model": cfg.name, "layers": cfg.n_layers, "global_batch": local, "seq_len": cfg.seq_len,
                        "lora": "rank 16 alpha 32 on qkv + proj, base frozen", "loss_positions": 1024,
                        "parallelism": f"tp{world} + sequence parallel ({args.comm} all-gather->GEMM / GEMM->reduce-scatter)",
-                       "linears": "bf16 tcgen05"}}
+                       "linears": "frozen base on per-tensor FP8 (e4m3 forward, e5m2 gradients), LoRA bf16" if tp_prec == "fp8" else "bf16 tcgen05"}}
 
 
 def bench_flux(args, rank, world, dev):
@@ -128,7 +130,7 @@ def bench_hstu(args, rank, world, dev):
     from ..models.hstu import HSTUConfig
     from ..trainer.hstu import HSTUTrainer
     cfg = HSTUConfig(layers=args.layers or 8, dim=512, heads=4, d_qk=128, d_v=128, max_seq_len=4096, emb_dim=256, dtype="bf16",
-                     precision="bf16", fuse_glue=args.glue == "fused")
+                     precision="bf16", fuse_glue=args.glue == "fused", attn_precision="fp8" if args.precision == "fp8" else "bf16")
     rows = 400_000_000 // (args.scale or 1)
     bpg = args.global_batch // world if args.global_batch else 128
     tr = HSTUTrainer(cfg, rows, bpg, dev, emb_comm=args.comm, seed=0,
@@ -155,7 +157,9 @@ def main(argv=None) -> int:
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--glue", default="fused", choices=["fused", "eager"], help="HSTU layer glue: one kernel or torch operators")
-    ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8"], help="linear precision (flux1)")
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8", "fp8"],
+                    help="flux1 / gpt-oss-20b: linear precision; llama2-70b-lora: mxfp8 or fp8 = frozen base on per-tensor FP8; "
+                         "hstu: fp8 = e4m3 attention forward")
     args = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))

@@ -30,7 +30,7 @@ def main():
     heads, kv = max(4, world), max(2, world)              # every rank needs at least one query and one kv head
     hd = 64 if gpu else 16
     cfg = GPTConfig(n_layers=2, hidden=heads * hd, n_heads=heads, n_kv_heads=kv, head_dim=hd,
-                    ffn_hidden=(512 if gpu else 128) * max(world // 2, 1), vocab_size=512, seq_len=128 * world if gpu else 32,
+                    ffn_hidden=(512 if gpu else 128) * max(world // 2, 1), vocab_size=512, seq_len=256 * world if gpu else 32,     # 256 rows per rank: the CTA-pair fused kernels
                     dtype="bf16" if gpu else "fp32", lora_rank=8 if lora else 0, lora_dropout=0.0)
     torch.manual_seed(1)
     full = GPT(cfg, device=device, seed=3)
