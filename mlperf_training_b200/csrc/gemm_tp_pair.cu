@@ -10,6 +10,12 @@
 
 using namespace gemmcore;
 
+// Raster group height in 256-row tiles (B200_TP_RS_GROUP_M / B200_TP_AG_GROUP_M override the defaults).
+static int env_int(const char* name, int dflt) {
+  const char* e = getenv(name);
+  return (e && atoi(e) > 0) ? atoi(e) : dflt;
+}
+
 // a: this rank's gather buffer [M = W * rows_per, K] (own block written; row pitch lda: elements for bf16, bytes for
 // 8-bit codes), b [N, K], d [M, N] bf16.  fp8 = 0: bf16 operands; fp8 = 1: codes with formats a_e5m2 / b_e5m2 and
 // device factors inv_a / inv_b.  peer_ptrs[c]: rank c's gather buffer; chunk_bytes: bytes of one rank block;
@@ -29,7 +35,7 @@ B200_API int b200_gemm_tp_gather_pair(const void* a, const void* b, void* d, int
   PairParams p = {};
   p.M = M; p.N = N; p.K = K;
   p.a_fmt = a_e5m2 ? 1 : 0; p.b_fmt = b_e5m2 ? 1 : 0;
-  p.group_m = 8;
+  p.group_m = env_int("B200_TP_AG_GROUP_M", 8);
   p.epi.M = M; p.epi.N = N;
   p.epi.alpha = alpha;
   p.epi.alpha_a = fp8 ? inv_a : nullptr;
@@ -91,7 +97,7 @@ B200_API int b200_gemm_tp_rs_pair(const void* a, const void* b, int M, int N, in
   PairParams p = {};
   p.M = M; p.N = N; p.K = K;
   p.a_fmt = a_e5m2 ? 1 : 0; p.b_fmt = b_e5m2 ? 1 : 0;
-  p.group_m = 2 * W;              // one row tile of every owner per raster group
+  p.group_m = env_int("B200_TP_RS_GROUP_M", W);   // one row tile of every owner per raster group: a row block completes early
   p.epi.M = M; p.epi.N = N;
   p.epi.alpha = alpha;
   p.epi.alpha_a = fp8 ? inv_a : nullptr;

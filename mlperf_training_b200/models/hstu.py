@@ -320,11 +320,41 @@ class HSTU(nn.Module):
         return torch.stack(feats, dim=-1)
 
     # ------------------------------------------------------------------ forward
+    def _token_layout(self, batch: dict):
+        """Per-token sample index, position inside the sample and target flag, from the batch alone."""
+        offsets0, num_targets = batch["offsets"], batch["num_targets"]
+        total0 = int(batch["total"]) if "total" in batch else int(offsets0[-1])
+        B = offsets0.numel() - 1
+        dev = offsets0.device
+        lens0 = (offsets0[1:] - offsets0[:-1]).long()
+        seq0 = torch.repeat_interleave(torch.arange(B, device=dev), lens0, output_size=total0)
+        col0 = torch.arange(total0, device=dev) - offsets0[:-1].long()[seq0]
+        is_target0 = col0 >= (lens0 - num_targets.long())[seq0]
+        return total0, lens0, seq0, col0, is_target0
+
+    def action_branch(self, batch: dict, rows: int) -> torch.Tensor:
+        """The action branch of the preprocessor (action encoder + its MLP), ``[rows, dim]``.  It reads the batch
+        only - no embedding - so a trainer may issue it before the embedding rows have arrived and pass the
+        result to ``forward(action_out=...)``: it then runs under the lookup's all-to-all instead of behind it
+        (generative_recommenders/modules/action_prefill.py:1-80; the sum it enters is formed in the same order,
+        so the result is bit-identical)."""
+        cfg = self.cfg
+        dt = cfg.torch_dtype()
+        _, _, _, _, is_target0 = self._token_layout(batch)
+        enc = self.action_enc(batch["actions"], is_target0)
+        if enc.shape[0] != rows:
+            padded = torch.zeros((rows,) + tuple(enc.shape[1:]), dtype=enc.dtype, device=enc.device)
+            padded[:enc.shape[0]] = enc
+            enc = padded
+        return self.action_mlp(enc.to(dt), cfg.precision)
+
     def forward(self, batch: dict, item_emb: torch.Tensor, extra_emb: torch.Tensor | None = None,
-                contextual_emb: torch.Tensor | None = None, return_all: bool = False):
+                contextual_emb: torch.Tensor | None = None, return_all: bool = False,
+                action_out: torch.Tensor | None = None):
         """``extra_emb [rows, extra_features * emb_dim]``: the additional per-token features;
         ``contextual_emb [B, contextual, ctx_dim]``: the per-sample contextual features (user id, crosses).
-        ``return_all``: also return the per-task losses, predictions ``[n_tasks, T]``, labels and weights."""
+        ``return_all``: also return the per-task losses, predictions ``[n_tasks, T]``, labels and weights.
+        ``action_out``: the result of ``action_branch`` issued earlier."""
         cfg = self.cfg
         dt = cfg.torch_dtype()
         C = cfg.contextual
@@ -352,7 +382,8 @@ class HSTU(nn.Module):
             if extra_emb is None:
                 raise ValueError("the model was built with extra_features: pass extra_emb")
             x = x + self.extra_mlp(extra_emb.to(dt), cfg.precision)
-        x = x + self.action_mlp(pad(self.action_enc(actions0, is_target0), rows0).to(dt), cfg.precision)
+        x = x + (action_out if action_out is not None
+                 else self.action_mlp(pad(self.action_enc(actions0, is_target0), rows0).to(dt), cfg.precision))
         # ---- contextual tokens in front of every sequence
         if C > 0:
             if contextual_emb is None:

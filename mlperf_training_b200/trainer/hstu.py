@@ -147,6 +147,8 @@ class HSTUTrainer:
         self.pipelined = True            # loader thread + copy stream ahead of the step (the reference's TRAIN_PIPELINE=1)
         self.copy_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
         self.dist_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
+        self.lookup_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
+        self.action_prefill = True       # issue the preprocessor's action branch under the embedding all-to-all
         self.pipeline_input_dist = True  # the id half of batch N+1's lookup runs under step N (3-stage sparse pipeline)
         self._next = None
         self._ready = None               # (step, device batch, plan, event) prepared ahead
@@ -230,10 +232,28 @@ class HSTUTrainer:
         emb[: batch["total"]] = self.table.lookup(batch["item_ids"], batch.get("_plan")).to(emb.dtype)
         return emb
 
+    def _embed_and_prefill(self, batch):
+        """Embedding rows of the batch and, issued under their all-to-all, the embedding-independent action branch
+        of the preprocessor: the row exchange runs on its own stream while the main stream computes the branch
+        (generative_recommenders/modules/action_prefill.py)."""
+        if self.lookup_stream is None or not self.action_prefill:
+            return self.embed(batch), None
+        main = torch.cuda.current_stream()
+        self.lookup_stream.wait_stream(main)
+        with torch.cuda.stream(self.lookup_stream):
+            emb = self.embed(batch)
+            done = torch.cuda.Event()
+            done.record()
+        pre = self.model.action_branch(batch, batch["rows"])
+        main.wait_event(done)
+        emb.record_stream(main)
+        return emb, pre
+
     def train_step_device(self, batch) -> torch.Tensor:
         self.model.train()
         dense_lr, self.table.lr = self.lrs_at(self.step_idx)     # the sparse update runs inside backward
-        loss, _, _ = self.model(batch, self.embed(batch))
+        emb, pre = self._embed_and_prefill(batch)
+        loss, _, _ = self.model(batch, emb, action_out=pre)
         loss.backward()
         self.engine.step(dense_lr)
         self.step_idx += 1

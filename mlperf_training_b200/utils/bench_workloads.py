@@ -88,7 +88,7 @@ def bench_llama70b_lora(args, rank, world, dev):
     solo = [dist.new_group([r]) for r in range(world)][rank] if world > 1 else None
     local = args.global_batch or 8                       # data-parallel size 1: every rank sees the whole batch
     tr = PretrainTrainer(cfg, OptimConfig(lr=4e-4, beta2=0.999, eps=1e-8, weight_decay=1e-4, clip_grad=0.3),
-                         TrainConfig(micro_batch=args.micro_batch or 1, local_batch=local, warmup_steps=0, seed=0), dev, group=solo, tp=tp,
+                         TrainConfig(micro_batch=args.micro_batch or 4, local_batch=local, warmup_steps=0, seed=0), dev, group=solo, tp=tp,
                          freeze_base=True)
     g = torch.Generator().manual_seed(0)
     toks = torch.randint(0, cfg.vocab_size, (local, cfg.seq_len + 1), generator=g).to(dev)
@@ -98,7 +98,7 @@ def bench_llama70b_lora(args, rank, world, dev):
     tokens = local * cfg.seq_len
     return {"metric": "train tokens/s", "value": tokens / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms, "loss": loss,
             "config": {"model": cfg.name, "layers": cfg.n_layers, "global_batch": local, "seq_len": cfg.seq_len,
-                       "lora": "rank 16 alpha 32 on qkv + proj, base frozen", "loss_positions": 1024,
+                       "micro_batch": args.micro_batch or 4, "lora": "rank 16 alpha 32 on qkv + proj, base frozen", "loss_positions": 1024,
                        "parallelism": f"tp{world} + sequence parallel ({args.comm} all-gather->GEMM / GEMM->reduce-scatter)",
                        "linears": "frozen base on per-tensor FP8 (e4m3 forward, e5m2 gradients), LoRA bf16" if tp_prec == "fp8" else "bf16 tcgen05"}}
 

@@ -89,3 +89,26 @@ def test_three_stage_pipeline_gives_the_same_losses():
         losses[mode] = [float(tr.train_step()) for _ in range(5)]
     assert losses["plain"] == losses["loader"] == losses["three_stage"]
     assert losses["plain"][-1] == losses["plain"][-1] and len(set(losses["plain"])) > 1
+
+
+def test_action_branch_issued_early_is_bit_identical():
+    """The action branch computed ahead of the embeddings and handed to forward gives the same loss and gradients."""
+    import torch
+    from mlperf_training_b200.data.hstu_synth import HSTUSyntheticData
+    from mlperf_training_b200.models.hstu import HSTU, HSTUConfig
+    cfg = HSTUConfig(layers=2, dim=64, heads=2, d_qk=16, d_v=16, max_seq_len=64, emb_dim=32, mlp_hidden=32, dtype="fp32",
+                     input_dropout=0.0, linear_dropout=0.0)
+    torch.manual_seed(0)
+    model = HSTU(cfg, "cpu", seed=1)
+    data = HSTUSyntheticData(1000, 4, seed=0, length_median=20, length_min=4, length_max=60)
+    batch = data.batch_at(0, 0)
+    emb = torch.randn(batch["rows"], cfg.emb_dim)
+    res = []
+    for early in (False, True):
+        model.zero_grad()
+        pre = model.action_branch(batch, batch["rows"]) if early else None
+        loss, _, _ = model(batch, emb, action_out=pre)
+        loss.backward()
+        res.append((loss.detach().clone(), [p.grad.clone() for p in model.parameters() if p.grad is not None]))
+    assert torch.equal(res[0][0], res[1][0])
+    assert all(torch.equal(a, b) for a, b in zip(res[0][1], res[1][1]))
