@@ -63,6 +63,15 @@ class HSTUConfig:
     dtype: str = "bf16"
     precision: str = "bf16"
     attn_precision: str = "bf16"       # "fp8": attention forward on per-tensor e4m3 Q, K, V (head dim 128, GPU)
+    # stochastic depth: in training every layer is skipped (identity) with this probability, decided per forward from a
+    # counter-seeded generator that leaves the global RNG untouched (generative_recommenders/modules/dynamic_stu.py:118-196)
+    sd_ratio: float = 0.0
+    sd_seed: int = 0
+    # recent-window layers: the last `recent_window_layers` layers see, per sample, only the contextual tokens, the most
+    # recent `recent_window` history tokens and the targets; older tokens bypass them unchanged (dynamic_stu.py:207-303)
+    recent_window: int = 0
+    recent_window_layers: int = 0
+    postprocessor: str = "timestamp_ln"   # "timestamp_ln" | "ln" | "l2" (modules/postprocessors.py)
 
     def torch_dtype(self):
         return {"bf16": torch.bfloat16, "fp32": torch.float32}[self.dtype]
@@ -162,7 +171,8 @@ class STULayer(nn.Module):
         self.out_norm_w = nn.Parameter(torch.ones(h * cfg.d_v, dtype=dtype, device=device))
         self.out_norm_b = nn.Parameter(torch.zeros(h * cfg.d_v, dtype=dtype, device=device))
 
-    def forward(self, x, offsets, num_targets, rows: int):
+    def forward(self, x, offsets, num_targets, rows: int, max_len: int | None = None):
+        """``max_len``: the static length bound N of the attention (its 1 / N factor and grid); default the model's."""
         cfg = self.cfg
         h = cfg.heads
         uvqk = F.norm_linear(x, self.in_norm_w, self.uvqk_weight, norm_b=self.in_norm_b, bias=self.uvqk_beta,
@@ -173,7 +183,7 @@ class STULayer(nn.Module):
         v = v_raw.unflatten(-1, (h, cfg.d_v))
         q = q_raw.unflatten(-1, (h, cfg.d_qk))
         k = k_raw.unflatten(-1, (h, cfg.d_qk))
-        attn = hstu_attention(q, k, v, offsets, cfg.max_seq_len + cfg.contextual, cfg.d_qk ** -0.5, num_targets,
+        attn = hstu_attention(q, k, v, offsets, max_len or (cfg.max_seq_len + cfg.contextual), cfg.d_qk ** -0.5, num_targets,
                               cfg.contextual, precision=cfg.attn_precision, owner=self).reshape(x.shape[0], h * cfg.d_v)
         if self.fuse_glue and gate_cat_eligible(u_raw, attn):
             # SiLU(u), the layer norm of the attention output, their product and the concatenation in one kernel
@@ -282,6 +292,7 @@ class HSTU(nn.Module):
         self.post_norm = _LN(d, dt, device, eps=1e-5)
         self.item_mlp = _MLP(cfg.emb_dim * (1 + cfg.extra_features), d, d, dt, device)
         self.head = MultitaskHead(cfg, dt, device)
+        self._sd_iter = 0                # training forwards seen: seeds the stochastic-depth draws (kept in the state dict)
         # additional-feature branch of the preprocessor: MLP(cat(extra embeddings)) added to the content branch
         self.extra_mlp = _MLP(cfg.emb_dim * cfg.extra_features, cfg.mlp_hidden, d, dt, device) if cfg.extra_features else None
         # contextual tokens: one [ctx_dim, D] matrix and bias per contextual feature (a batched linear)
@@ -290,6 +301,49 @@ class HSTU(nn.Module):
             std = math.sqrt(2.0 / (cd + d))
             self.ctx_weight = nn.Parameter(torch.empty(cfg.contextual, cd, d, dtype=dt, device=device).normal_(0, std))
             self.ctx_bias = nn.Parameter(torch.zeros(cfg.contextual, d, dtype=dt, device=device))
+
+    # ------------------------------------------------------------------ dynamic layers
+    def get_extra_state(self):
+        return {"sd_iter": self._sd_iter}
+
+    def set_extra_state(self, state):
+        self._sd_iter = int((state or {}).get("sd_iter", 0))
+
+    def skipped_layers(self, it: int) -> list:
+        """Layers that stochastic depth turns into the identity in training forward number ``it``."""
+        cfg = self.cfg
+        if cfg.sd_ratio <= 0:
+            return []
+        out = []
+        for i in range(cfg.layers):
+            g = torch.Generator().manual_seed(cfg.sd_seed + 1000003 * i + it)
+            if float(torch.rand(1, generator=g)) <= cfg.sd_ratio:
+                out.append(i)
+        return out
+
+    def _recent_window_layer(self, layer, x, offsets, num_targets, seq, col, total: int, max_targets: int):
+        """Run ``layer`` on the contextual tokens, the last ``recent_window`` history tokens and the targets of every
+        sample; the older tokens keep their value.  Sizes are static bounds, so nothing is read back to the host."""
+        cfg = self.cfg
+        C, W = cfg.contextual, cfg.recent_window
+        B = offsets.numel() - 1
+        lens = (offsets[1:] - offsets[:-1]).long()
+        prefix = (lens - W - num_targets.long() - C).clamp(min=0)         # oldest history tokens: bypass
+        keep = (col < C) | (col >= (C + prefix)[seq])
+        rows2 = min(x.shape[0], (B * (W + C + max_targets) + 127) // 128 * 128)
+        pos2 = torch.cumsum(keep.long(), 0) - 1
+        idx = torch.where(keep, pos2, torch.full_like(pos2, rows2))        # dropped tokens land in a spare row
+        x2 = torch.zeros((rows2 + 1, x.shape[1]), dtype=x.dtype, device=x.device).index_copy(0, idx, x[:total])[:rows2]
+        lens2 = lens - prefix
+        offsets2 = torch.zeros_like(offsets)
+        offsets2[1:] = torch.cumsum(lens2, 0).to(offsets.dtype)
+        n2 = min(cfg.max_seq_len + C, W + C + max_targets)
+        y2 = layer(x2.contiguous(), offsets2, num_targets, rows2, max_len=n2)
+        y2 = torch.cat([y2, y2.new_zeros((1, y2.shape[1]))], dim=0)
+        out = torch.where(keep[:, None], y2[idx], x[:total])
+        if x.shape[0] > total:
+            out = torch.cat([out, x[total:]], dim=0)
+        return out
 
     # ------------------------------------------------------------------ pieces
     def position_indices(self, offsets, num_targets, total: int):
@@ -417,14 +471,33 @@ class HSTU(nn.Module):
             tgt_rows = torch.nonzero(is_target, as_tuple=False)[:, 0]
             tgt_rows0 = torch.nonzero(is_target0, as_tuple=False)[:, 0]
         last = len(self.layers) - 1
+        skipped = []
+        if self.training and cfg.sd_ratio > 0:
+            skipped = self.skipped_layers(self._sd_iter)
+            self._sd_iter += 1
+        first_windowed = len(self.layers) - cfg.recent_window_layers if cfg.recent_window > 0 else len(self.layers)
+        max_t = int(batch.get("max_targets", 0)) or int(num_targets.max())
+        user = None
         for i, layer in enumerate(self.layers):
+            if i in skipped:
+                continue                                                     # stochastic depth: identity this time
+            if i >= first_windowed:
+                x = self._recent_window_layer(layer, x, offsets, num_targets, seq, col, total, max_t)
+                continue
             if i == last and cfg.targets_only_last and one_target:
                 user = layer.forward_targets_only(x, seq, tgt_rows, B)       # candidate rows only, no split afterwards
                 break
             x = layer(x, offsets, num_targets, rows)
-        else:
+        if user is None:
             user = x[tgt_rows]
-        user = self.post_norm(self.post_linear(torch.cat([user, self.time_features(ts[tgt_rows]).to(dt)], dim=1)))
+        if cfg.postprocessor == "timestamp_ln":
+            user = self.post_norm(self.post_linear(torch.cat([user, self.time_features(ts[tgt_rows]).to(dt)], dim=1)))
+        elif cfg.postprocessor == "ln":
+            user = self.post_norm(user)
+        elif cfg.postprocessor == "l2":
+            user = (user.float() / user.float().norm(dim=-1, keepdim=True).clamp(min=1e-6)).to(dt)
+        else:
+            raise ValueError(f"unknown postprocessor '{cfg.postprocessor}'")
         cand = item_emb[tgt_rows0] if extra_emb is None else torch.cat([item_emb[tgt_rows0], extra_emb[tgt_rows0]], dim=1)
         item = self.item_mlp(cand.to(dt))
         losses, preds, labels, weights = self.head(user, item, actions0[tgt_rows0], batch.get("values"), batch.get("weights"))

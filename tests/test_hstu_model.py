@@ -112,3 +112,89 @@ def test_action_branch_issued_early_is_bit_identical():
         res.append((loss.detach().clone(), [p.grad.clone() for p in model.parameters() if p.grad is not None]))
     assert torch.equal(res[0][0], res[1][0])
     assert all(torch.equal(a, b) for a, b in zip(res[0][1], res[1][1]))
+
+
+def _tiny(**kw):
+    import torch
+    from mlperf_training_b200.data.hstu_synth import HSTUSyntheticData
+    from mlperf_training_b200.models.hstu import HSTU, HSTUConfig
+    base = dict(layers=3, dim=64, heads=2, d_qk=16, d_v=16, max_seq_len=64, emb_dim=32, mlp_hidden=32, dtype="fp32",
+                input_dropout=0.0, linear_dropout=0.0, targets_only_last=False)
+    base.update(kw)
+    cfg = HSTUConfig(**base)
+    torch.manual_seed(0)
+    model = HSTU(cfg, "cpu", seed=1)
+    data = HSTUSyntheticData(1000, 4, seed=0, length_median=20, length_min=4, length_max=60)
+    batch = data.batch_at(0, 0)
+    emb = torch.randn(batch["rows"], cfg.emb_dim)
+    return cfg, model, batch, emb
+
+
+def test_stochastic_depth_skips_layers_deterministically():
+    import torch
+    cfg, model, batch, emb = _tiny(sd_ratio=0.5, sd_seed=7)
+    plain_cfg, plain, _, _ = _tiny()
+    plain.load_state_dict(model.state_dict())
+    rng = torch.get_rng_state()
+    draws = [model.skipped_layers(it) for it in range(20)]
+    assert torch.equal(rng, torch.get_rng_state())                    # the global generator is untouched
+    assert draws == [model.skipped_layers(it) for it in range(20)]    # a function of (seed, layer, forward number)
+    assert any(d for d in draws) and any(len(d) < cfg.layers for d in draws)
+    model.eval(); plain.eval()
+    assert torch.equal(model(batch, emb)[0], plain(batch, emb)[0])    # evaluation never skips
+    model.train()
+    it = next(i for i, d in enumerate(draws) if d)                    # a forward in which something is skipped
+    model.set_extra_state({"sd_iter": it})
+    loss = model(batch, emb)[0]
+    assert model.get_extra_state()["sd_iter"] == it + 1
+    # the same forward with those layers removed by hand
+    plain.train()
+    kept = [l for i, l in enumerate(plain.layers) if i not in draws[it]]
+    plain.layers = torch.nn.ModuleList(kept)
+    assert torch.allclose(loss, plain(batch, emb)[0], atol=1e-6)
+    full_ratio = _tiny(sd_ratio=1.0)[1]
+    assert full_ratio.skipped_layers(3) == [0, 1, 2]
+
+
+def test_recent_window_layers_leave_old_tokens_untouched():
+    import torch
+    cfg, model, batch, emb = _tiny(recent_window=8, recent_window_layers=1)
+    wide_cfg, wide, _, _ = _tiny(recent_window=4096, recent_window_layers=1)
+    plain_cfg, plain, _, _ = _tiny()
+    wide.load_state_dict(model.state_dict()); plain.load_state_dict(model.state_dict())
+    # a window that covers every sequence changes only the attention's length bound: run the plain model with that bound
+    offsets, nt = batch["offsets"], batch["num_targets"]
+    total = int(batch["total"])
+    lens = (offsets[1:] - offsets[:-1]).long()
+    seq = torch.repeat_interleave(torch.arange(lens.numel()), lens)
+    col = torch.arange(total) - offsets[:-1].long()[seq]
+    x = torch.randn(batch["rows"], cfg.dim)
+    layer = model.layers[-1]
+    max_t = int(batch.get("max_targets", 0)) or int(nt.max())
+    y = model._recent_window_layer(layer, x, offsets, nt, seq, col, total, max_t)
+    prefix = (lens - 8 - nt.long()).clamp(min=0)
+    old = col < prefix[seq]
+    assert old.any() and torch.equal(y[:total][old], x[:total][old])                    # bypassed rows keep their value
+    assert not torch.allclose(y[:total][~old], x[:total][~old])
+    # the recent rows equal the layer run on a batch made of the windows alone
+    keep = ~old
+    lens2 = lens - prefix
+    off2 = torch.zeros_like(offsets); off2[1:] = torch.cumsum(lens2, 0).to(offsets.dtype)
+    n_keep = int(keep.sum())
+    rows2 = (n_keep + 127) // 128 * 128
+    x2 = torch.zeros(rows2, cfg.dim); x2[:n_keep] = x[:total][keep]
+    ref = layer(x2, off2, nt, rows2, max_len=min(cfg.max_seq_len, 8 + max_t))
+    assert torch.allclose(y[:total][keep], ref[:n_keep], atol=1e-5)
+    # end to end: gradients flow to every layer and the loss is finite
+    loss = model(batch, emb)[0]
+    loss.backward()
+    assert torch.isfinite(loss) and all(p.grad is not None for p in model.layers[-1].parameters())
+
+
+def test_postprocessor_variants():
+    import torch
+    for kind in ("timestamp_ln", "ln", "l2"):
+        cfg, model, batch, emb = _tiny(postprocessor=kind)
+        loss = model(batch, emb)[0]
+        loss.backward()
+        assert torch.isfinite(loss)
