@@ -7,6 +7,11 @@ model can learn it (AUC above chance) - used by the convergence tests.  Stands i
 reference's synthetic / Yambda loaders (generative_recommenders/dlrm_v4/datasets/dataset.py:1033-1209
 ``DLRMv4RandomDataset``, yambda.py) with the same batch structure: jagged values + lengths, one
 storage per batch, pinned for the H2D copy.
+
+``balance_world = W > 1``: the lengths of a step's W x batch users are drawn once, identically on every rank, and
+dealt to the ranks longest first, each to the least loaded rank with a free slot, so every rank gets the same number of
+users and nearly the same attention work (which goes with the sum of squared lengths).  The global batch is the same set of i.i.d.
+users either way; only their placement changes, and with it the time the slowest rank takes.
 """
 from __future__ import annotations
 
@@ -16,8 +21,9 @@ import torch
 
 class HSTUSyntheticData:
     def __init__(self, rows: int, batch: int, length_median: int = 512, length_min: int = 16, length_max: int = 4096,
-                 zipf_alpha: float = 1.05, sigma: float = 1.0, seed: int = 0, n_targets: int = 1):
+                 zipf_alpha: float = 1.05, sigma: float = 1.0, seed: int = 0, n_targets: int = 1, balance_world: int = 0):
         self.rows, self.batch = rows, batch
+        self.balance_world = int(balance_world)
         self.median, self.lmin, self.lmax = length_median, length_min, length_max
         self.alpha, self.sigma, self.seed, self.n_targets = zipf_alpha, sigma, seed, n_targets
 
@@ -34,8 +40,25 @@ class HSTUSyntheticData:
 
     def batch_at(self, step: int, rank: int = 0, pin: bool = False) -> dict:
         rng = np.random.default_rng((self.seed * 1000003 + step) * 4099 + rank)
-        hist = np.clip(np.exp(rng.normal(np.log(self.median), self.sigma, self.batch)), self.lmin,
-                       self.lmax - self.n_targets).astype(np.int64)
+        if self.balance_world > 1:
+            W = self.balance_world
+            grng = np.random.default_rng((self.seed * 1000003 + step) * 4099 + 4098)      # the same draw on every rank
+            allh = np.clip(np.exp(grng.normal(np.log(self.median), self.sigma, self.batch * W)), self.lmin,
+                           self.lmax - self.n_targets).astype(np.int64)
+            # longest first, each user to the least loaded rank that still has a free slot (cost = squared length)
+            load = np.zeros(W)
+            slots = np.full(W, self.batch)
+            mine = []
+            for h in allh[np.argsort(-allh, kind="stable")]:
+                r = int(np.argmin(np.where(slots > 0, load, np.inf)))
+                load[r] += float(h + self.n_targets) ** 2
+                slots[r] -= 1
+                if r == rank % W:
+                    mine.append(h)
+            hist = np.asarray(mine, dtype=np.int64)[rng.permutation(self.batch)]   # no length trend inside the rank's batch
+        else:
+            hist = np.clip(np.exp(rng.normal(np.log(self.median), self.sigma, self.batch)), self.lmin,
+                           self.lmax - self.n_targets).astype(np.int64)
         lens = hist + self.n_targets
         offsets = np.zeros(self.batch + 1, dtype=np.int32)
         offsets[1:] = np.cumsum(lens)

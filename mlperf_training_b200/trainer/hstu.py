@@ -365,13 +365,17 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     cfg = HSTUConfig(layers=int(m.get("layers", 8)), dim=int(m.get("dim", 512)), heads=int(m.get("heads", 4)),
                      d_qk=int(m.get("d_qk", 128)), d_v=int(m.get("d_v", 128)), max_seq_len=int(m.get("max_seq_len", 4096)),
                      emb_dim=int((exp.get("embedding") or {}).get("dim", 256)), dtype=m.get("dtype", "bf16"),
-                     precision=m.get("precision", "bf16"), mlp_hidden=int(m.get("mlp_hidden", 256)),
+                     precision=m.get("precision", "bf16"), attn_precision=str(m.get("attn_precision", "bf16")),
+                     mlp_hidden=int(m.get("mlp_hidden", 256)),
                      num_positions=int(m.get("num_positions", 8192)), num_time_buckets=int(m.get("num_time_buckets", 2048)))
     emb = exp.get("embedding") or {}
     d = dict(exp.get("data") or {})
     data_kw = {k: d[k] for k in ("length_median", "length_min", "length_max", "zipf_alpha", "kind", "root", "max_history",
                                  "min_history", "window_seconds", "holdout", "salt", "path", "format", "num_candidates",
                                  "action_weights", "label_bit", "eval_fraction") if k in d}
+    if int(d.get("balance_lengths", 0) or 0) and d.get("kind", "synthetic") == "synthetic":
+        import torch.distributed as _dist
+        data_kw["balance_world"] = _dist.get_world_size() if _dist.is_available() and _dist.is_initialized() else 1
     bpg = int(exp.get("batch_per_gpu", 128))
     tr = HSTUTrainer(cfg, int(emb.get("rows", 1_000_000)), bpg, device, dense_lr=float(exp.get("dense_lr", 1e-3)),
                      sparse_lr=float(exp.get("sparse_lr", 1e-2)), clip_grad=float(exp.get("clip_grad", 1.0)),

@@ -134,11 +134,13 @@ def bench_hstu(args, rank, world, dev):
     rows = 400_000_000 // (args.scale or 1)
     bpg = args.global_batch // world if args.global_batch else 128
     tr = HSTUTrainer(cfg, rows, bpg, dev, emb_comm=args.comm, seed=0,
-                     data_kw=dict(length_median=512, length_min=16, length_max=4096, zipf_alpha=1.05))
+                     data_kw=dict(length_median=512, length_min=16, length_max=4096, zipf_alpha=1.05,
+                                  balance_world=world if args.balance else 0))
     ms, loss = _timed(lambda i: tr.train_step(i), args.steps, args.warmup, world)
     return {"metric": "train samples/s", "value": bpg * world / (ms / 1e3), "unit": "samples/s", "ms_per_step": ms, "loss": loss,
             "config": {"model": "hstu", "layers": cfg.layers, "dim": cfg.dim, "heads": cfg.heads, "table_rows": rows, "emb_dim": 256,
-                       "users_per_gpu": bpg, "layer_glue": args.glue, "lengths": "lognormal median 512 in [16, 4096]", "ids": "Zipf(1.05)",
+                       "users_per_gpu": bpg, "layer_glue": args.glue, "lengths": "lognormal median 512 in [16, 4096]" + (", users dealt to ranks by length (longest first to the least loaded rank)" if args.balance else ""),
+                       "ids": "Zipf(1.05)",
                        "parallelism": f"row-wise sharded table over {world} ({args.comm} lookup) + dp{world} dense",
                        "includes": "host batch build, H2D on a side stream, sparse Adagrad in backward"}}
 
@@ -156,6 +158,7 @@ def main(argv=None) -> int:
     ap.add_argument("--global-batch", type=int, default=0)
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--balance", type=int, default=1, help="hstu: deal each step's users to the ranks by length (0 = every rank draws its own)")
     ap.add_argument("--glue", default="fused", choices=["fused", "eager"], help="HSTU layer glue: one kernel or torch operators")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8", "fp8"],
                     help="flux1 / gpt-oss-20b: linear precision; llama2-70b-lora: mxfp8 or fp8 = frozen base on per-tensor FP8; "

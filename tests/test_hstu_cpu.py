@@ -166,3 +166,23 @@ def test_hstu_run_skips_early_evaluations():
     out = run(exp, device="cpu", stream=io.StringIO())
     # 25 % of 16 samples at global batch 2 = every 2 steps; nothing before 50 % = step 4: evaluations after steps 4, 6, 8
     assert len(out["aucs"]) == 3
+
+
+def test_length_balanced_placement_keeps_the_global_batch():
+    """Dealing a step's users to the ranks by length changes placement only: the union over ranks is one draw of
+    W x batch lengths, every rank gets `batch` users, and the squared-length cost per rank is nearly equal."""
+    import numpy as np
+    from mlperf_training_b200.data.hstu_synth import HSTUSyntheticData
+    W, B = 4, 64
+    d = HSTUSyntheticData(10 ** 5, B, seed=3, balance_world=W, length_median=200, length_max=2048)
+    per_rank = [d.batch_at(5, r)["lengths"].numpy() for r in range(W)]
+    assert all(len(x) == B for x in per_rank)
+    again = [d.batch_at(5, r)["lengths"].numpy() for r in range(W)]
+    assert all((a == b).all() for a, b in zip(per_rank, again))                       # deterministic per (step, rank)
+    grng = np.random.default_rng((3 * 1000003 + 5) * 4099 + 4098)
+    want = np.clip(np.exp(grng.normal(np.log(200), 1.0, B * W)), 16, 2048 - 1).astype(np.int64) + 1
+    assert sorted(np.concatenate(per_rank).tolist()) == sorted(want.tolist())          # the same multiset of users
+    cost = np.array([(x.astype(np.float64) ** 2).sum() for x in per_rank])
+    plain = HSTUSyntheticData(10 ** 5, B, seed=3, length_median=200, length_max=2048)
+    cost0 = np.array([(plain.batch_at(5, r)["lengths"].numpy().astype(np.float64) ** 2).sum() for r in range(W)])
+    assert cost.max() / cost.mean() < 1.05 <= cost0.max() / cost0.mean() + 0.05
