@@ -133,6 +133,9 @@ def full_shape_of(p: torch.Tensor) -> tuple:
     """Shape of the unsharded tensor behind a (possibly tensor-parallel) parameter."""
     shard = getattr(p, "tensor_parallel", None)
     if shard is None:
+        ep = getattr(p, "expert_shard", None)
+        if ep is not None:                       # stacked experts [E / EP, ...]: a block of the expert dimension
+            return (p.shape[0] * ep[0], *p.shape[1:])
         return tuple(p.shape)
     kind, W, _ = shard
     if kind == "cols":
@@ -158,12 +161,27 @@ def unshard(parts: list[torch.Tensor], kind: str, cfg: GPTConfig) -> torch.Tenso
     raise ValueError(kind)
 
 
-def _full_tensor(p: torch.Tensor, cfg: GPTConfig, tp_group) -> torch.Tensor:
-    """The unsharded value of parameter ``p`` (gathered over ``tp_group`` when it is a slice)."""
+def _ep_group_of(model):
+    """Process group over which the model's experts are split (None: every rank holds all experts)."""
+    for m in model.modules():
+        if getattr(m, "ep_group", None) is not None and getattr(m, "ep", 1) > 1:
+            return m.ep_group
+    return None
+
+
+def _full_tensor(p: torch.Tensor, cfg: GPTConfig, tp_group, ep_group=None) -> torch.Tensor:
+    """The unsharded value of parameter ``p`` (gathered over ``tp_group`` / ``ep_group`` when it is a slice)."""
     shard = getattr(p, "tensor_parallel", None)
     t = p.detach()
     if shard is None:
-        return t
+        ep = getattr(p, "expert_shard", None)
+        if ep is None:
+            return t
+        if ep_group is None or torch.distributed.get_world_size(ep_group) != ep[0]:
+            raise ValueError("an expert-parallel parameter needs its expert-parallel group to be gathered")
+        parts = [torch.empty_like(t) for _ in range(ep[0])]
+        torch.distributed.all_gather(parts, t.contiguous(), group=ep_group)
+        return torch.cat(parts, 0)
     kind, W, _ = shard
     if tp_group is None or torch.distributed.get_world_size(tp_group) != W:
         raise ValueError("a tensor-parallel parameter needs its tensor-parallel group to be gathered")
@@ -176,12 +194,63 @@ def to_megatron_state(model: GPT, tp_group=None) -> dict[str, torch.Tensor]:
     """Megatron-named state with every tensor at its full (unsharded) shape.  Collective over
     ``tp_group`` when the model holds tensor-parallel slices."""
     cfg = model_config_of(model)
+    ep_group = _ep_group_of(model) if isinstance(model, torch.nn.Module) else None
     out = {}
     for name, p in global_named_parameters(model):
-        t = _full_tensor(p, cfg, tp_group)
+        t = _full_tensor(p, cfg, tp_group, ep_group)
         if name.endswith("w_qkv") or name.endswith("lora_qkv.b"):
             t = qkv_to_megatron(t, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
         out[megatron_name(name, moe_pre_norm=cfg.n_experts > 0)] = t.contiguous()
+    return out
+
+
+def sharded_megatron_state(model: GPT, tp_group) -> dict:
+    """Megatron-named state in which every tensor-parallel parameter is a ``ShardedTensor`` over ``tp_group``: each
+    rank contributes only its slice, described by its offsets inside the full tensor, so the checkpoint records
+    the sharding (one or two chunks per rank and tensor) instead of a gathered copy, and a run with another
+    tensor-parallel degree reads the chunks it needs.  The fused q | k | v weight is stored in Megatron's per-group
+    layout, in which a rank's heads are one contiguous row block; the stacked gate | up weight contributes two
+    chunks, one inside each half.  Replicated parameters stay plain tensors.  Collective over ``tp_group``."""
+    from torch.distributed._shard.sharded_tensor import Shard, ShardMetadata, init_from_local_shards
+    cfg = model_config_of(model)
+    ep_group = _ep_group_of(model) if isinstance(model, torch.nn.Module) else None
+    out = {}
+    for name, p in global_named_parameters(model):
+        key = megatron_name(name, moe_pre_norm=cfg.n_experts > 0)
+        shard = getattr(p, "tensor_parallel", None)
+        t = p.detach()
+        ep = getattr(p, "expert_shard", None)
+        if shard is None and ep is not None and ep_group is not None:
+            # stacked experts: this rank's block of the expert dimension, over the expert-parallel group
+            n, r = ep
+            dev = f"rank:{r}/{'cpu' if t.device.type == 'cpu' else str(t.device)}"
+            meta = ShardMetadata(shard_offsets=[r * t.shape[0]] + [0] * (t.dim() - 1), shard_sizes=list(t.shape), placement=dev)
+            out[key] = init_from_local_shards([Shard(tensor=t.contiguous(), metadata=meta)], *full_shape_of(p),
+                                              process_group=ep_group)
+            continue
+        if shard is None:
+            if name.endswith("w_qkv") or name.endswith("lora_qkv.b"):
+                t = qkv_to_megatron(t, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
+            out[key] = t.contiguous()
+            continue
+        kind, W, r = shard
+        full = full_shape_of(p)
+        if kind == "qkv":
+            t = qkv_to_megatron(t, cfg.n_heads // W, cfg.n_kv_heads // W, cfg.head_dim)
+        tail = [0] * (t.dim() - 1)
+        if kind in ("rows", "qkv"):
+            pieces = [(t, [r * t.shape[0]] + tail)]
+        elif kind == "cols":
+            pieces = [(t, [0, r * t.shape[1]] + tail[1:])]
+        elif kind == "rows_2":
+            h = t.shape[0] // 2
+            pieces = [(t[:h], [r * h] + tail), (t[h:], [full[0] // 2 + r * h] + tail)]
+        else:
+            raise ValueError(kind)
+        dev = f"rank:{r}/{'cpu' if t.device.type == 'cpu' else str(t.device)}"
+        shards = [Shard(tensor=x.contiguous(), metadata=ShardMetadata(shard_offsets=list(off), shard_sizes=list(x.shape),
+                                                                      placement=dev)) for x, off in pieces]
+        out[key] = init_from_local_shards(shards, *full, process_group=tp_group)
     return out
 
 
@@ -206,6 +275,9 @@ def _load_named(named, state: dict[str, torch.Tensor], cfg: GPTConfig) -> list[s
             shard = getattr(p, "tensor_parallel", None)
             if shard is not None and tuple(t.shape) == full_shape_of(p):
                 t = shard_of(t, shard[0], shard[1], shard[2], cfg)     # the layout conversion ran on the full tensor
+            ep = getattr(p, "expert_shard", None)
+            if shard is None and ep is not None and tuple(t.shape) == full_shape_of(p):
+                t = t.chunk(ep[0], 0)[ep[1]]                           # this rank's experts
             if tuple(t.shape) != tuple(p.shape):
                 raise ValueError(f"{key}: checkpoint shape {tuple(t.shape)} vs model {tuple(p.shape)}")
             p.copy_(t.to(p.dtype))
@@ -221,19 +293,27 @@ def load_megatron_state(model: GPT, state: dict[str, torch.Tensor], strict: bool
     return missing
 
 
-def save_torch_dist(model: GPT, root: str, iteration: int = 0, extra_common: dict | None = None) -> Path:
+def save_torch_dist(model: GPT, root: str, iteration: int = 0, extra_common: dict | None = None,
+                    sharded: bool = True) -> Path:
     """Write ``<root>/iter_<iteration:07d>/`` in the ``torch_dist`` layout.  Collective when a
-    process group is initialised (every rank calls it)."""
+    process group is initialised (every rank calls it).  Under tensor parallelism every rank writes its own
+    slices with their offsets (``sharded``; ``False`` gathers full tensors first)."""
     d = Path(root) / f"iter_{iteration:07d}"
     rank = torch.distributed.get_rank() if torch.distributed.is_initialized() else 0
     if rank == 0:
         d.mkdir(parents=True, exist_ok=True)
     if torch.distributed.is_initialized():
         torch.distributed.barrier()
-    state = {f"model.{k}": v for k, v in to_megatron_state(model, _tp_group_of(model)).items()}
+    tp_group = _tp_group_of(model)
+    ep_group = _ep_group_of(model) if isinstance(model, torch.nn.Module) else None
+    tp_sharded = sharded and ((tp_group is not None and torch.distributed.get_world_size(tp_group) > 1) or ep_group is not None)
+    megatron_state = sharded_megatron_state(model, tp_group) if tp_sharded else to_megatron_state(model, tp_group)
+    state = {f"model.{k}": v for k, v in megatron_state.items()}
     dcp.save(state, checkpoint_id=str(d))
     if rank == 0:
-        common = {"iteration": iteration, "checkpoint_version": 3.0, "args": None, "model_config": model.cfg.to_dict()}
+        common = {"iteration": iteration, "checkpoint_version": 3.0, "args": None, "model_config": model.cfg.to_dict(),
+                  "tensor_parallel_shards": torch.distributed.get_world_size(tp_group) if (tp_sharded and tp_group is not None) else 1,
+                  "expert_parallel_shards": torch.distributed.get_world_size(ep_group) if (tp_sharded and ep_group is not None) else 1}
         common.update(extra_common or {})
         torch.save(common, d / "common.pt")
         (d / "metadata.json").write_text(json.dumps({"sharded_backend": "torch_dist", "sharded_backend_version": 1,
@@ -265,7 +345,7 @@ def load_torch_dist(model: GPT, root: str, iteration: int | None = None, strict:
     # full-shape destinations, read and consumed a group of keys at a time (a tensor-parallel rank keeps
     # only its slice of each, so the full tensors of the whole model never sit in memory together)
     named = list(global_named_parameters(model))
-    sharded = any(getattr(p, "tensor_parallel", None) is not None for _, p in named)
+    sharded = any(getattr(p, "tensor_parallel", None) is not None or getattr(p, "expert_shard", None) is not None for _, p in named)
     per_group = 16 if sharded else len(named)
     missing = []
     for g0 in range(0, len(named), max(per_group, 1)):

@@ -33,6 +33,9 @@ class MoEMLP(nn.Module):
         # expert weights belong to this expert-parallel rank only: data-parallel reductions of their
         # gradients run over the ranks that hold the same experts
         self.w1.expert_parallel = self.w2.expert_parallel = self.ep > 1
+        if self.ep > 1:
+            # (expert-parallel size, this rank's index): which block of the stacked expert dimension this rank holds
+            self.w1.expert_shard = self.w2.expert_shard = (self.ep, self.ep_rank)
         self.dispatcher = ExpertParallelDispatcher(ep_group, E) if self.ep > 1 else None
         self.ep_comm = ep_comm
         self._fused = None      # built on first use: its slab size depends on the number of tokens per step

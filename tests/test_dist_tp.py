@@ -153,7 +153,7 @@ def test_run_loop_with_expert_parallel_resumes_gloo(tmp_path):
 
 
 def test_tensor_parallel_checkpoints_round_trip_and_runs_resume_gloo(tmp_path):
-    """Megatron torch_dist files written under tensor parallelism hold unsharded tensors; a resumed
+    """Megatron torch_dist files written under tensor parallelism describe full tensors (every rank its slices); a resumed
     tensor-parallel run restores every rank's own slices; a resumed LoRA run reloads its frozen base."""
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
@@ -174,3 +174,27 @@ def test_sharded_parameter_engine_matches_replicated_engine_gloo():
                        env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "RESULT rank 0 ok=True" in r.stdout and "RESULT rank 1 ok=True" in r.stdout
+
+
+def test_tensor_parallel_torch_dist_checkpoint_records_shards_gloo(tmp_path):
+    """Every tensor-parallel rank writes its own slices with their offsets; the checkpoint loads into the same
+    sharding and into an unsharded model."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29649",
+                        os.path.join(ROOT, "tests", "multi", "tp_ckpt_worker.py"), str(tmp_path / "ckpt")],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("ok=True") == 2
+
+
+def test_expert_parallel_torch_dist_checkpoint_records_shards_gloo(tmp_path):
+    """Every expert-parallel rank writes its own experts as a block of the stacked expert dimension; the checkpoint
+    loads into the same sharding and into a model that holds every expert."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29651",
+                        os.path.join(ROOT, "tests", "multi", "ep_ckpt_worker.py"), str(tmp_path / "ckpt")],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("ok=True") == 2
