@@ -187,6 +187,40 @@ class ShardedEmbedding:
         self.state.copy_(sd[f"embeddings.{self.name}.rowwise_adagrad.sum"])
 
 
+    # ------------------------------------------------------------------ sharded (TorchRec-layout) state
+    def sharded_state_dict(self, prefix: str = "") -> dict:
+        """The table and its row-wise Adagrad sums as ``ShardedTensor``s over the table's group, under the key names a
+        TorchRec ``EmbeddingCollection`` uses (``<prefix>embeddings.<table>.weight``; the fused optimizer state beside it):
+        this rank's rows are one chunk at their row offset inside the ``[rows, dim]`` table, so a checkpoint written
+        from it can be read back under another number of ranks or another placement (row-wise <-> table-wise).
+        Collective over the group."""
+        from torch.distributed._shard.sharded_tensor import Shard, ShardMetadata, init_from_local_shards
+        if self.world == 1:
+            return {f"{prefix}embeddings.{self.name}.weight": self.weight,
+                    f"{prefix}embeddings.{self.name}.rowwise_adagrad.sum": self.state}
+        dev = f"rank:{self.rank}/{'cpu' if self.device.type == 'cpu' else str(self.device)}"
+        out = {}
+        for key, t, size in ((f"{prefix}embeddings.{self.name}.weight", self.weight, (self.rows, self.dim)),
+                             (f"{prefix}embeddings.{self.name}.rowwise_adagrad.sum", self.state, (self.rows,))):
+            shards = []
+            if self.local_rows > 0:
+                meta = ShardMetadata(shard_offsets=[int(self.row_lo)] + [0] * (t.dim() - 1), shard_sizes=list(t.shape), placement=dev)
+                shards = [Shard(tensor=t, metadata=meta)]
+            out[key] = init_from_local_shards(shards, *size, process_group=self.group)
+        return out
+
+    def save_sharded(self, path: str, prefix: str = "") -> None:
+        """Write the sharded state with torch's distributed checkpoint writer (every rank its own rows)."""
+        import torch.distributed.checkpoint as dcp
+        dcp.save(self.sharded_state_dict(prefix), checkpoint_id=str(path))
+
+    def load_sharded(self, path: str, prefix: str = "") -> None:
+        """Read this rank's rows of a sharded checkpoint, whatever layout wrote it (the reader fetches the chunks that
+        overlap this rank's row range)."""
+        import torch.distributed.checkpoint as dcp
+        dcp.load(self.sharded_state_dict(prefix), checkpoint_id=str(path))      # the local shards are views of the live tensors
+
+
 class _LookupFn(Function):
     @staticmethod
     def forward(ctx, ids, table: ShardedEmbedding, _anchor, plan=None):

@@ -120,5 +120,21 @@ class EmbeddingCollection:
         for t in self.tables.values():
             t.load_state_dict(sd)
 
+    def sharded_state_dict(self, prefix: str = "") -> dict:
+        """Every table as ``ShardedTensor``s under TorchRec's key names (see ``ShardedEmbedding.sharded_state_dict``)."""
+        sd = {}
+        for t in self.tables.values():
+            sd.update(t.sharded_state_dict(prefix))
+        return sd
+
+    def save_sharded(self, path: str, prefix: str = "") -> None:
+        import torch.distributed.checkpoint as dcp
+        dcp.save(self.sharded_state_dict(prefix), checkpoint_id=str(path))
+
+    def load_sharded(self, path: str, prefix: str = "") -> None:
+        """Load a sharded checkpoint written under any number of ranks and any placement plan."""
+        import torch.distributed.checkpoint as dcp
+        dcp.load(self.sharded_state_dict(prefix), checkpoint_id=str(path))
+
     def local_bytes(self) -> int:
         return sum(t.weight.numel() * t.weight.element_size() for t in self.tables.values())

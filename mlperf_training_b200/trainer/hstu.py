@@ -397,7 +397,11 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         validate_split_contract(ck["meta"].get("split_contract"), contract,
                                 allow_mismatch=os.environ.get("ALLOW_SPLIT_MISMATCH", "0") == "1")
         tr.model.load_state_dict(ck["dense"]["model"])
-        tr.table.load_state_dict(torch.load(ck["path"] / "sparse" / f"shard_rank{rank}.pt", weights_only=False))
+        if (ck["path"] / "sparse" / "dcp").exists():
+            # TorchRec-layout sharded state: readable under any number of ranks / placement
+            tr.table.load_sharded(str(ck["path"] / "sparse" / "dcp"), prefix="model._embedding_collection.")
+        else:
+            tr.table.load_state_dict(torch.load(ck["path"] / "sparse" / f"shard_rank{rank}.pt", weights_only=False))
         if ck["optim"] is not None:
             tr.engine.load_optimizer_state(ck["optim"])
         CheckpointManager.restore_rng(ck["rng"])
@@ -476,10 +480,15 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                 break
             log.start(ml.BLOCK_START, metadata={"samples_count": samples})
         if ckpt is not None and ((every and (step + 1) % every == 0) or (die_at and step + 1 == die_at)):
-            sd = tr.table.state_dict()
+            if str(exp.get("sparse_checkpoint", "per_rank")) == "sharded":
+                # every rank writes its rows as ShardedTensor chunks under TorchRec's key names (collective)
+                writer = lambda d_: tr.table.save_sharded(str(d_ / "dcp"), prefix="model._embedding_collection.")
+            else:
+                sd = tr.table.state_dict()
+                writer = lambda d_: torch.save(sd, d_ / f"shard_rank{rank}.pt")
             ckpt.save(step + 1, dense={"model": tr.model.state_dict()}, optim_shard=tr.engine.optimizer_state(),
                       meta={"samples": samples, "window": 0, "batch_idx_in_window": step + 1, "split_contract": contract},
-                      sparse_writer=lambda d_: torch.save(sd, d_ / f"shard_rank{rank}.pt"))
+                      sparse_writer=writer)
         if die_at and step + 1 == die_at:
             if world > 1:
                 dist.barrier()

@@ -117,3 +117,19 @@ def test_collection_table_wise_and_row_wise_gloo():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert res == {0: True, 1: True}
+
+
+def test_sharded_state_round_trips_across_placement_plans_gloo(tmp_path):
+    """TorchRec-layout sharded state: written row-wise / table-wise by 2 ranks, read back under the same and under the
+    swapped placement plan."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29655",
+                        os.path.join(root, "tests", "multi", "emb_ckpt_worker.py"), str(tmp_path)],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("ok=True") == 2

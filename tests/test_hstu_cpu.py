@@ -78,10 +78,12 @@ def test_hstu_run_learns_and_logs():
     assert check_compliance(out["records"]) == []
 
 
-def test_hstu_die_and_resume(tmp_path):
+@pytest.mark.parametrize("sparse_format", ["per_rank", "sharded"])
+def test_hstu_die_and_resume(tmp_path, sparse_format):
     from mlperf_training_b200.trainer.hstu import run
     ref = run(_exp(), device="cpu", stream=io.StringIO())
-    e = _exp(checkpoint_dir=str(tmp_path / "ck"), die_at_step=6, mllog_file=str(tmp_path / "ml.log"))
+    e = _exp(checkpoint_dir=str(tmp_path / "ck"), die_at_step=6, mllog_file=str(tmp_path / "ml.log"),
+             sparse_checkpoint=sparse_format)
     with pytest.raises(SystemExit) as ex:
         run(e, device="cpu", stream=io.StringIO())
     assert ex.value.code == 42
