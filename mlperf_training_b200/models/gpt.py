@@ -58,6 +58,7 @@ class GPTConfig:
     # recompute_layers > 0 limits either to the first N blocks
     recompute: str = "none"
     recompute_layers: int = 0
+    swiglu_store: str = "bf16"          # "fp8": the fused MXFP8 MLP keeps its gate | up activation for backward as e4m3 codes
     dtype: str = "bf16"
     precision: str = "bf16"         # GEMM precision of the linears: "bf16" | "mxfp8"
     # the first / last N transformer layers keep bf16 linears whatever ``precision`` says (Megatron's
@@ -176,6 +177,7 @@ class DenseMLP(nn.Module):
         self.precision = cfg.precision
         self.force_bf16 = False          # set for the first / last layers that stay in bf16
         self.fused = True               # MXFP8: one unit with the quantisation folded into SwiGLU / dSwiGLU
+        self.store_fp8 = getattr(cfg, "swiglu_store", "bf16") == "fp8"
         self.w_gate_up = nn.Parameter(torch.empty(2 * f, d, dtype=dtype, device=device))
         self.w_down = nn.Parameter(torch.empty(d, f, dtype=dtype, device=device))
         if self.tp is not None:
@@ -189,7 +191,7 @@ class DenseMLP(nn.Module):
             return T.row_parallel(F.swiglu(gu), self.w_down, self.tp, residual=h)
         pr = "bf16" if self.force_bf16 else self.precision
         if pr == "mxfp8" and self.fused and F.fused_mlp_eligible(h, self.w_gate_up, self.w_down):
-            return F.fused_mlp(h, norm_w, self.w_gate_up, self.w_down, eps)
+            return F.fused_mlp(h, norm_w, self.w_gate_up, self.w_down, eps, self.store_fp8)
         gu = F.norm_linear(h, norm_w, self.w_gate_up, eps=eps, precision=pr)
         return F.swiglu_linear(gu, self.w_down, residual=h, precision=pr)
 

@@ -191,10 +191,14 @@ class FusedMLPFn(Function):
     the e4m3 copies the GEMMs read.  Saved for backward: the block input, the normalisation
     statistics, ``gu`` and the transposed fp8 copy of the normalised input.  This is the reference's
     fused dense MLP with the quantisation and dGLU folded in
-    (small_llm_pretraining/primus/config_MI355X_1x8x1.sh:42-51)."""
+    (small_llm_pretraining/primus/config_MI355X_1x8x1.sh:42-51).
+
+    ``store_fp8``: ``gu`` - the largest saved activation, ``[T, 2F]`` - is kept for backward as per-tensor e4m3
+    codes (delayed scale) instead of bf16, half the bytes; backward decodes it before dSwiGLU (the reference's
+    SwiGLU op with FP8 input store, llama2_sft/primus/patches/megatron_lm_mxfp4_recipe.patch)."""
 
     @staticmethod
-    def forward(ctx, h, norm_w, w_gu, w_down, eps):
+    def forward(ctx, h, norm_w, w_gu, w_down, eps, store_fp8=False):
         from . import mxfp8 as MX
         D = h.shape[1]
         xn, _, mean, rstd = K.norm_fwd(h, norm_w, None, eps, layer_norm=False)
@@ -207,7 +211,15 @@ class FusedMLPFn(Function):
         w2_row, _ = L.weight_operands(w_down, need_col=False)
         out = MX.gemm(a_row, w2_row, residual=h, out_dtype=h.dtype)
         tensors, ctx.meta = L.Saved.pack(xn_col) if xn_col is not None else ([], None)
-        ctx.save_for_backward(h, norm_w, w_gu, w_down, mean, rstd, gu, *tensors)
+        ctx.gu_fp8 = bool(store_fp8)
+        if store_fp8:
+            from . import fp8 as F8
+            st = L._site(w_gu, "gu_store", "e4m3")
+            st.prepare(gu, L.weight_epoch())
+            op = F8.quantize_rows(gu, st)
+            ctx.save_for_backward(h, norm_w, w_gu, w_down, mean, rstd, op.q, op.inv_scale.clone(), *tensors)
+        else:
+            ctx.save_for_backward(h, norm_w, w_gu, w_down, mean, rstd, gu, *tensors)
         ctx.eps = eps
         ctx.refs = (norm_w, w_gu, w_down)
         return out
@@ -215,7 +227,12 @@ class FusedMLPFn(Function):
     @staticmethod
     def backward(ctx, dy):
         from . import mxfp8 as MX
-        h, norm_w, w_gu, w_down, mean, rstd, gu, *tensors = ctx.saved_tensors
+        if ctx.gu_fp8:
+            h, norm_w, w_gu, w_down, mean, rstd, gu_q, gu_inv, *tensors = ctx.saved_tensors
+            gu = (gu_q.view(torch.float8_e4m3fn).to(torch.float32) * gu_inv).to(h.dtype)
+            del gu_q
+        else:
+            h, norm_w, w_gu, w_down, mean, rstd, gu, *tensors = ctx.saved_tensors
         p_norm, p_gu, p_down = ctx.refs
         dy = dy.contiguous()
         F_ = w_down.shape[1]
@@ -234,7 +251,7 @@ class FusedMLPFn(Function):
         dxn = MX.gemm(dgu_row, w1_col, out_dtype=dy.dtype)
         dw1 = _mx_wgrad(p_gu, dgu_col, L.Saved.unpack(tensors, ctx.meta)) if need1 else None
         dx, dnw, _ = K.norm_bwd(dxn, h, norm_w, None, mean, rstd, layer_norm=False, dres=dy)
-        return dx, _vec_grad(p_norm, dnw), dw1, dw2, None
+        return dx, _vec_grad(p_norm, dnw), dw1, dw2, None, None
 
 
 def fused_mlp_eligible(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor) -> bool:
@@ -244,9 +261,9 @@ def fused_mlp_eligible(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor
             and L.mx_eligible(T, F2, D) and L.mx_eligible(T, D, F2 // 2))
 
 
-def fused_mlp(h, norm_w, w_gate_up, w_down, eps=1e-5):
+def fused_mlp(h, norm_w, w_gate_up, w_down, eps=1e-5, store_fp8: bool = False):
     """``h + swiglu(rmsnorm(h) W_gu^T) W_down^T`` with MXFP8 GEMMs."""
-    return FusedMLPFn.apply(h, norm_w, w_gate_up, w_down, eps)
+    return FusedMLPFn.apply(h, norm_w, w_gate_up, w_down, eps, store_fp8)
 
 
 class SwiGLUFn(Function):

@@ -18,7 +18,8 @@ def _cfg(**kw):
 
 
 @pytest.mark.parametrize("kw", [dict(), dict(head_dim=128, hidden=512), dict(window=128, window_layers="even", sink=True),
-                                dict(head_dim=128, hidden=512, precision="mxfp8")])
+                                dict(head_dim=128, hidden=512, precision="mxfp8"),
+                                dict(head_dim=128, hidden=512, precision="mxfp8", swiglu_store="fp8")])
 def test_loss_and_grads_match_cpu(kw):
     cfg = _cfg(**kw)
     ref = GPT(GPTConfig(**{**cfg.to_dict(), "dtype": "fp32"}), "cpu", seed=1)
