@@ -187,6 +187,14 @@ class ShardedEmbedding:
         self.state.copy_(sd[f"embeddings.{self.name}.rowwise_adagrad.sum"])
 
 
+    def snapshot(self):
+        """Copies of the shard and its optimizer sums (warm-up steps are undone from them)."""
+        return self.weight.clone(), self.state.clone()
+
+    def restore(self, snap) -> None:
+        self.weight.copy_(snap[0])
+        self.state.copy_(snap[1])
+
     # ------------------------------------------------------------------ sharded (TorchRec-layout) state
     def sharded_state_dict(self, prefix: str = "") -> dict:
         """The table and its row-wise Adagrad sums as ``ShardedTensor``s over the table's group, under the key names a

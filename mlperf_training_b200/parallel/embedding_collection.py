@@ -92,6 +92,21 @@ class EmbeddingCollection:
         for t in self.tables.values():
             t.lr = lr
 
+    @property
+    def lr(self) -> float:
+        return next(iter(self.tables.values())).lr
+
+    @lr.setter
+    def lr(self, value: float) -> None:
+        self.set_lr(value)
+
+    def snapshot(self):
+        return {n: t.snapshot() for n, t in self.tables.items()}
+
+    def restore(self, snap) -> None:
+        for n, t in self.tables.items():
+            t.restore(snap[n])
+
     def lookup(self, kjt: KeyedJagged) -> dict[str, torch.Tensor]:
         """``{feature: rows [n_values(feature), dim]}`` for every key of ``kjt`` that maps to a table."""
         ranges = kjt.key_ranges()

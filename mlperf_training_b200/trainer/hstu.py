@@ -113,16 +113,36 @@ def hstu_bucket_of(name: str) -> str:
 
 class HSTUTrainer:
     def __init__(self, cfg: HSTUConfig, table_rows: int, batch_per_gpu: int, device, *, dense_lr=1e-3, sparse_lr=1e-2,
-                 clip_grad=1.0, emb_comm="nccl", dense_comm="nccl", seed=0, data_kw: dict | None = None, group=None):
+                 clip_grad=1.0, emb_comm="nccl", dense_comm="nccl", seed=0, data_kw: dict | None = None, group=None,
+                 table_set: str | None = None, table_scale: int = 1):
+        """``table_set="yambda"``: the multi-table form - an ``EmbeddingCollection`` over the benchmark's eleven tables
+        (item / artist / album ids, user id, seven hashed crosses; rows divided by ``table_scale``), batches that carry
+        keyed jagged features, a model with the additional-feature branch and the contextual tokens
+        (generative_recommenders/modules/dlrm_hstu.py:989-1116).  Default: one item table."""
         self.cfg, self.device = cfg, torch.device(device)
+        self.table_set = table_set
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         self.world = dist.get_world_size() if dist.is_initialized() else 1
         self.model = HSTU(cfg, device=self.device, seed=seed)
         opt = OptimConfig(lr=dense_lr, beta1=0.95, beta2=0.999, eps=1e-8, weight_decay=0.0, clip_grad=clip_grad)
         self.engine = ZeroEngine(self.model, opt, bucket_of=hstu_bucket_of, comm=dense_comm, group=group)
-        self.table = ShardedEmbedding(table_rows, cfg.emb_dim, group=group, device=self.device, dtype=cfg.torch_dtype(),
-                                      lr=sparse_lr, seed=seed, comm=emb_comm, init_scale=0.05)
         data_kw = dict(data_kw or {})
+        if table_set == "yambda":
+            from ..parallel.embedding_collection import EmbeddingCollection, YAMBDA_TABLES, TableConfig
+            from ..data.hstu_synth import YambdaSyntheticSamples
+            tables = [TableConfig(t.name, max(t.rows // table_scale, 2), cfg.emb_dim, t.features, cfg.dtype) for t in YAMBDA_TABLES]
+            n_ctx = sum(1 for t in tables if t.name == "uid" or t.name.startswith("cross_"))
+            if cfg.extra_features != 2 or cfg.contextual != n_ctx:
+                raise ValueError(f"the yambda table set needs a model with extra_features=2 and contextual={n_ctx}")
+            self.table = EmbeddingCollection(tables, group=group, device=self.device, lr=sparse_lr, seed=seed, comm=emb_comm)
+            self.ctx_keys = [t.name for t in tables if t.name == "uid" or t.name.startswith("cross_")]
+            data_kw.pop("kind", None)
+            self.data = YambdaSyntheticSamples(tables, batch_per_gpu, seed=seed, **data_kw)
+            self.eval_data = None
+            data_kw = {"kind": "_done"}
+        else:
+            self.table = ShardedEmbedding(table_rows, cfg.emb_dim, group=group, device=self.device, dtype=cfg.torch_dtype(),
+                                          lr=sparse_lr, seed=seed, comm=emb_comm, init_scale=0.05)
         kind = data_kw.pop("kind", "synthetic")
         if kind == "sequences":
             # per-user sequence files (MovieLens / KuaiRand layout), user-hash hold-out for evaluation
@@ -137,7 +157,7 @@ class HSTUTrainer:
             root = data_kw.pop("root")
             self.data = _WorldView(EventStoreDataset(root, batch_per_gpu, split="train", **data_kw), self.world)
             self.eval_data = _WorldView(EventStoreDataset(root, batch_per_gpu, split="eval", **data_kw), self.world)
-        else:
+        elif kind != "_done":
             self.data = HSTUSyntheticData(table_rows, batch_per_gpu, seed=seed, **data_kw)
             self.eval_data = None
         self.batch_per_gpu = batch_per_gpu
@@ -149,7 +169,7 @@ class HSTUTrainer:
         self.dist_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
         self.lookup_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
         self.action_prefill = True       # issue the preprocessor's action branch under the embedding all-to-all
-        self.pipeline_input_dist = True  # the id half of batch N+1's lookup runs under step N (3-stage sparse pipeline)
+        self.pipeline_input_dist = table_set is None   # the id half of batch N+1's lookup runs under step N (3-stage sparse pipeline)
         self._next = None
         self._ready = None               # (step, device batch, plan, event) prepared ahead
         self._pool = None
@@ -228,9 +248,27 @@ class HSTUTrainer:
     # ------------------------------------------------------------------ steps
     def embed(self, batch):
         rows = batch["rows"]
+        if self.table_set is not None:
+            return self._embed_features(batch)
         emb = torch.zeros((rows, self.cfg.emb_dim), dtype=self.cfg.torch_dtype(), device=self.device)
         emb[: batch["total"]] = self.table.lookup(batch["item_ids"], batch.get("_plan")).to(emb.dtype)
         return emb
+
+    def _embed_features(self, batch):
+        """Multi-table lookup of a keyed jagged batch: ``(item rows, additional-feature rows, contextual rows)`` in the
+        token order of the dense model.  Every table is looked up once over the merged history + candidate ids."""
+        rows, total, dt = batch["rows"], batch["total"], self.cfg.torch_dtype()
+        feats = self.table.lookup(batch["samples"].merged())
+        tok = batch["token_row"]
+
+        def per_token(name):
+            out = torch.zeros((rows, self.cfg.emb_dim), dtype=dt, device=self.device)
+            out[:total] = torch.cat([feats["uih_" + name], feats[name]], dim=0)[tok].to(dt)
+            return out
+        item = per_token("item_id")
+        extra = torch.cat([per_token("artist_id"), per_token("album_id")], dim=1)
+        ctx = torch.stack([feats[k].to(dt) for k in self.ctx_keys], dim=1)           # [B, contextual, dim]
+        return item, extra, ctx
 
     def _embed_and_prefill(self, batch):
         """Embedding rows of the batch and, issued under their all-to-all, the embedding-independent action branch
@@ -246,14 +284,18 @@ class HSTUTrainer:
             done.record()
         pre = self.model.action_branch(batch, batch["rows"])
         main.wait_event(done)
-        emb.record_stream(main)
+        for t in (emb if isinstance(emb, tuple) else (emb,)):
+            t.record_stream(main)
         return emb, pre
 
     def train_step_device(self, batch) -> torch.Tensor:
         self.model.train()
         dense_lr, self.table.lr = self.lrs_at(self.step_idx)     # the sparse update runs inside backward
         emb, pre = self._embed_and_prefill(batch)
-        loss, _, _ = self.model(batch, emb, action_out=pre)
+        if self.table_set is not None:
+            loss, _, _ = self.model(batch, emb[0], emb[1], emb[2], action_out=pre)
+        else:
+            loss, _, _ = self.model(batch, emb, action_out=pre)
         loss.backward()
         self.engine.step(dense_lr)
         self.step_idx += 1
@@ -276,7 +318,8 @@ class HSTUTrainer:
     def _eval_inputs(self, src, step: int):
         b = HSTUSyntheticData.to_device(src.batch_at(step, self.rank), self.device)
         with torch.enable_grad():           # the lookup Function needs a graph only to skip its backward
-            emb = self.embed(b).detach()
+            emb = self.embed(b)
+            emb = tuple(t.detach() for t in emb) if isinstance(emb, tuple) else emb.detach()
         return b, emb
 
     def lookahead_ready(self) -> bool:
@@ -311,12 +354,12 @@ class HSTUTrainer:
                         ev.record()
                 else:
                     nxt = self._eval_inputs(src, start + i + 1)
-            _, p, l = self.model(b, emb)
+            _, p, l = self.model(b, *emb) if isinstance(emb, tuple) else self.model(b, emb)
             ps.append(p)
             ls.append(l)
             if ev is not None:
                 torch.cuda.current_stream().wait_event(ev)
-                for t in (nxt[1], *[v for v in nxt[0].values() if torch.is_tensor(v)]):
+                for t in (*(nxt[1] if isinstance(nxt[1], tuple) else (nxt[1],)), *[v for v in nxt[0].values() if torch.is_tensor(v)]):
                     t.record_stream(torch.cuda.current_stream())
         return torch.cat(ps), torch.cat(ls)
 
@@ -330,7 +373,7 @@ def _warmup(tr: "HSTUTrainer", steps: int) -> None:
         return
     from .warmup import restore_engine, snapshot_engine
     snap = snapshot_engine(tr.engine)
-    w, st = tr.table.weight.clone(), tr.table.state.clone()
+    table_snap = tr.table.snapshot()
     rng_cpu = torch.get_rng_state()
     rng_dev = torch.cuda.get_rng_state() if tr.device.type == "cuda" else None
     for i in range(steps):
@@ -339,8 +382,7 @@ def _warmup(tr: "HSTUTrainer", steps: int) -> None:
     if rng_dev is not None:
         torch.cuda.set_rng_state(rng_dev)
     restore_engine(tr.engine, snap)
-    tr.table.weight.copy_(w)
-    tr.table.state.copy_(st)
+    tr.table.restore(table_snap)
     tr.step_idx = 0
     tr._next = None
     tr._ready = None
@@ -369,6 +411,9 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                      mlp_hidden=int(m.get("mlp_hidden", 256)),
                      num_positions=int(m.get("num_positions", 8192)), num_time_buckets=int(m.get("num_time_buckets", 2048)))
     emb = exp.get("embedding") or {}
+    table_set = emb.get("tables") or None            # "yambda": the benchmark's eleven tables instead of one item table
+    if table_set == "yambda":
+        cfg.extra_features, cfg.contextual = 2, 8     # artist + album per token; user id + seven crosses per sample
     d = dict(exp.get("data") or {})
     data_kw = {k: d[k] for k in ("length_median", "length_min", "length_max", "zipf_alpha", "kind", "root", "max_history",
                                  "min_history", "window_seconds", "holdout", "salt", "path", "format", "num_candidates",
@@ -379,7 +424,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     bpg = int(exp.get("batch_per_gpu", 128))
     tr = HSTUTrainer(cfg, int(emb.get("rows", 1_000_000)), bpg, device, dense_lr=float(exp.get("dense_lr", 1e-3)),
                      sparse_lr=float(exp.get("sparse_lr", 1e-2)), clip_grad=float(exp.get("clip_grad", 1.0)),
-                     emb_comm=exp.get("emb_a2a", "nccl"), seed=int(exp.get("seed", 0)), data_kw=data_kw)
+                     emb_comm=exp.get("emb_a2a", "nccl"), seed=int(exp.get("seed", 0)), data_kw=data_kw,
+                     table_set=table_set, table_scale=int(emb.get("table_scale", 1) or 1))
     timeline.mark("model_table_data")
     tr.lr_warmup_steps = int(exp.get("lr_warmup_steps", 0) or 0)
     if hasattr(tr.data, "readahead"):
