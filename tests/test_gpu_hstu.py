@@ -127,6 +127,22 @@ def test_hstu_train_steps_on_gpu():
     assert out["aucs"][-1] > 0.55
 
 
+def test_hstu_multi_table_train_steps_on_gpu():
+    """The eleven-table feature set through the run loop on the GPU kernels: one sorted / deduplicated lookup per table,
+    additional-feature branch, contextual tokens, row-wise Adagrad in backward."""
+    import io
+    from mlperf_training_b200.trainer.hstu import run
+    exp = dict(batch_per_gpu=16, train_steps=24, dense_lr=2e-3, sparse_lr=0.05, eval_interval_steps=12, num_eval_batches=2,
+               model=dict(layers=2, dim=256, heads=2, d_qk=128, d_v=128, max_seq_len=512, dtype="bf16", mlp_hidden=64,
+                          num_positions=1024, num_time_buckets=128),
+               embedding=dict(rows=5000, dim=128, tables="yambda", table_scale=2000),
+               data=dict(length_median=100, length_min=8, length_max=400))
+    out = run(exp, device="cuda", stream=io.StringIO())
+    _lib.check_status("hstu multi-table run")
+    assert all(l == l for l in out["losses"])
+    assert sum(out["losses"][-5:]) < sum(out["losses"][:5])
+
+
 @pytest.mark.parametrize("T,D,pitch", [(1000, 512, 2048), (37, 256, 256), (4099, 768, 1536)])
 def test_gate_cat_kernel_against_fp32_reference(T, D, pitch):
     """silu(u) | attn | silu(u) * LN(attn): forward and all four gradients against fp32 autograd."""
