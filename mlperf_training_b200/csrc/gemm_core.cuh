@@ -29,6 +29,15 @@
 // The N tile of the MXFP8 kernels is 208 so that 2 accumulators + 6 scale sets fill the 512 columns.
 // Every wait is bounded (common.cuh); the cluster barrier before exit keeps both CTAs' shared
 // memory and barriers alive until the partner's last signal has landed.
+//
+// Tile schedulers on the same mainloop (tile_info):
+//   * dense            grouped raster over (row tile, column tile)
+//   * GroupArgs        MoE: rows grouped by expert with the stacked expert weights as B (forward, dgrad), or one
+//                      contraction range per expert (weight gradients)
+//   * TpGather         all-gather -> GEMM: the first CTA pairs of the launch copy the ranks' row blocks over NVLink
+//                      (tp_copy.cuh), the producers wait per block and visit the blocks in arrival order
+//   * TpReduce         GEMM -> reduce-scatter: tiles leave through the owners' tensor maps into their staging
+//                      buffers, the first CTA pairs and - after their tiles - all epilogue warps reduce (tp_reduce.cuh)
 #pragma once
 #include <cstdlib>
 

@@ -24,6 +24,10 @@
 // parallel linears; the TransformerEngine userbuffer overlap is switched off in every shipped
 // config: llama2_sft/primus/config_MI355X_1x8x1.sh:115-118).
 //
+// This file holds the one-CTA-per-tile kernels.  Row blocks that are multiples of 256 run modes 1 and 3 on the CTA-pair
+// core instead (gemm_tp_pair.cu, gemm_core.cuh), with the same copy and reduce roles (tp_copy.cuh, tp_reduce.cuh); these
+// kernels serve the remaining shapes and mode 2.
+//
 // Loads never use cluster multicast.  Every wait is bounded (2 s) and reports into the status block.
 #include "common.cuh"
 #include "runtime.h"
