@@ -199,7 +199,7 @@ class STULayer(nn.Module):
         return F.linear(cat.contiguous(), self.out_weight, None, x, cfg.precision)
 
 
-    def forward_targets_only(self, x, seq, tgt_rows, n_samples: int):
+    def forward_targets_only(self, x, seq, tgt_rows, n_samples: int, offsets=None):
         """Last-layer form for batches with ONE target per sample: keys and values are computed for every
         row, queries / gates only for the target rows, and the output has one row per target
         (generative_recommenders/modules/stu.py:677-798).  A target sees its sample's whole history and
@@ -218,7 +218,9 @@ class STULayer(nn.Module):
         u = TF.silu(nt @ W[:hv].t() + beta[:hv])
         q = (nt @ W[2 * hv:2 * hv + hq].t() + beta[2 * hv:2 * hv + hq]).unflatten(-1, (h, cfg.d_qk))
         N = cfg.max_seq_len + cfg.contextual
-        score = (q[seq].float() * k.float()).sum(-1) * (cfg.d_qk ** -0.5)             # [rows, h]
+        # every sample's query over its own rows (segment-sum backward when the group bounds are given)
+        q_rows = q[seq] if offsets is None else F.expand_rows(q.reshape(n_samples, hq), seq, offsets).unflatten(-1, (h, cfg.d_qk))
+        score = (q_rows.float() * k.float()).sum(-1) * (cfg.d_qk ** -0.5)             # [rows, h]
         p = TF.silu(score) / N
         attn = torch.zeros((n_samples, h, cfg.d_v), dtype=torch.float32, device=x.device)
         attn.index_add_(0, seq, p[..., None] * v.float())
@@ -459,7 +461,9 @@ class HSTU(nn.Module):
         lens = (offsets[1:] - offsets[:-1]).long()
         is_target = col >= (lens - num_targets.long())[seq]
         bucket = self.time_buckets(ts, offsets, seq)
-        x = x * math.sqrt(cfg.dim) + pad(self.pos_emb[pos_idx] + self.ts_emb[bucket], rows).to(dt)
+        # position and time-bucket rows through the gather / scatter-add kernels (advanced indexing would sort the
+        # hundred thousand indices again in backward: two launches of ~2.5 ms each at the benchmark size)
+        x = x * math.sqrt(cfg.dim) + pad(F.embedding(pos_idx, self.pos_emb) + F.embedding(bucket, self.ts_emb), rows).to(dt)
         if cfg.input_dropout > 0 and self.training:
             x = TF.dropout(x, cfg.input_dropout)
         x = x.contiguous()
@@ -485,7 +489,7 @@ class HSTU(nn.Module):
                 x = self._recent_window_layer(layer, x, offsets, num_targets, seq, col, total, max_t)
                 continue
             if i == last and cfg.targets_only_last and one_target:
-                user = layer.forward_targets_only(x, seq, tgt_rows, B)       # candidate rows only, no split afterwards
+                user = layer.forward_targets_only(x, seq, tgt_rows, B, offsets)   # candidate rows only, no split afterwards
                 break
             x = layer(x, offsets, num_targets, rows)
         if user is None:

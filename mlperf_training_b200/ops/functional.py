@@ -425,6 +425,42 @@ def embedding(ids, table):
     return EmbeddingFn.apply(ids, table)
 
 
+class ExpandRowsFn(Function):
+    """``out[r] = src[seq[r]]`` for rows grouped by ``seq`` (ascending; group ``b`` = rows ``offsets[b] : offsets[b + 1]``):
+    every sample's vector repeated over the sample's tokens.  Backward is the per-group sum of the incoming rows - one
+    deterministic segment reduction instead of a sort of ``seq`` and an accumulating index put."""
+
+    @staticmethod
+    def forward(ctx, src, seq, offsets):
+        ctx.save_for_backward(seq, offsets)
+        ctx.shape, ctx.dtype = src.shape, src.dtype
+        return K.gather_rows(src, seq.view(-1))
+
+    @staticmethod
+    def backward(ctx, g):
+        seq, offsets = ctx.saved_tensors
+        B, D = ctx.shape
+        g = g.contiguous()
+        if use_kernels(g) and g.dtype in (torch.bfloat16, torch.float32) and D % 8 == 0:
+            from . import _lib
+            out = torch.zeros((B, D), dtype=torch.float32, device=g.device)
+            seg = offsets.to(torch.int64).contiguous()
+            n_seg = torch.full((1,), B, dtype=torch.int64, device=g.device)
+            n = g.shape[0]
+            partial = torch.empty(int(_lib.load().b200_segment_sum_scratch_elems(n, D)), dtype=torch.float32, device=g.device)
+            call("b200_segment_sum_gather", ptr(g), int(g.dtype == torch.float32), n, None, ptr(seg), ptr(n_seg), n, B, D, ptr(out), 0,
+                 ptr(partial), stream_ptr())
+            return out.to(ctx.dtype), None, None
+        out = torch.zeros((B, D), dtype=torch.float32, device=g.device)
+        out.index_add_(0, seq.view(-1), g.float())
+        return out.to(ctx.dtype), None, None
+
+
+def expand_rows(src, seq, offsets):
+    """``src[seq]`` with a segment-sum backward; ``offsets [B + 1]`` bound the groups of the ascending ``seq``."""
+    return ExpandRowsFn.apply(src, seq, offsets)
+
+
 class LMHeadLossFn(Function):
     """loss = mean CE(norm(x) W^T, labels): final norm, vocabulary GEMM and fused cross-entropy.
     The logits buffer is overwritten with its own gradient during forward, so backward starts

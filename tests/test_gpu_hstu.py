@@ -243,3 +243,22 @@ def test_gate_cat_dropout_mask_is_regenerated_in_backward():
                            (bk.grad, bf.grad, "db")):
         err = (got.float() - ref).abs().max().item()
         assert err <= 2e-2 * (ref.abs().max().item() + 1e-6), f"{what}: {err}"
+
+
+def test_expand_rows_backward_is_a_segment_sum():
+    """``src[seq]`` over ascending groups: gather forward, per-group sum backward, against index arithmetic."""
+    from mlperf_training_b200.ops import functional as F
+    torch.manual_seed(3)
+    lens = torch.tensor([5, 0, 300, 1, 77, 2000])
+    offs = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)]).to(torch.int32).cuda()
+    seq = torch.repeat_interleave(torch.arange(lens.numel()), lens).cuda()
+    src = torch.randn(lens.numel(), 512, device="cuda").bfloat16().requires_grad_(True)
+    out = F.expand_rows(src, seq, offs)
+    assert torch.equal(out, src.detach()[seq])
+    g = torch.randn_like(out)
+    out.backward(g)
+    torch.cuda.synchronize()
+    _lib.check_status("expand rows")
+    want = torch.zeros(lens.numel(), 512, device="cuda").index_add_(0, seq, g.float())
+    assert (src.grad.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+    assert src.grad[1].abs().max() == 0
