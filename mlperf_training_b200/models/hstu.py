@@ -154,6 +154,37 @@ class ActionEncoder(nn.Module):
         return torch.where(is_target[:, None], self.target_row.expand_as(emb), emb)
 
 
+class ContentEncoder(nn.Module):
+    """Content embedding of every token as one concatenation: the item embedding, additional per-token content
+    features, and "target enrichment" features that exist for candidates only - a history token carries a learned
+    dummy row in their place (generative_recommenders/modules/content_encoder.py:24-109).  An alternative to the
+    additional-feature branch of the preprocessor for feature sets whose extras are concatenated, not summed."""
+
+    def __init__(self, emb_dim: int, additional: dict | None = None, target_enrich: dict | None = None, dtype=torch.float32,
+                 device="cpu"):
+        super().__init__()
+        self.emb_dim = emb_dim
+        self.additional = dict(additional or {})              # feature name -> width
+        self.target_enrich = dict(target_enrich or {})
+        self.dummy = nn.ParameterDict({n: nn.Parameter(torch.empty(1, w, dtype=dtype, device=device).normal_(0, 0.1))
+                                       for n, w in self.target_enrich.items()})
+
+    @property
+    def output_dim(self) -> int:
+        return self.emb_dim + sum(self.additional.values()) + sum(self.target_enrich.values())
+
+    def forward(self, item_emb: torch.Tensor, payloads: dict, is_target: torch.Tensor) -> torch.Tensor:
+        """``item_emb [L, emb_dim]``; ``payloads[name]``: ``[L, w]`` for additional features, ``[n_targets, w]`` (rows of
+        the candidates, in token order) for enrichment features; ``is_target [L]`` marks the candidate tokens."""
+        parts = [item_emb] + [payloads[n].to(item_emb.dtype) for n in self.additional]
+        if self.target_enrich:
+            tgt = torch.nonzero(is_target, as_tuple=False)[:, 0]
+            for n in self.target_enrich:
+                full = self.dummy[n].to(item_emb.dtype).expand(item_emb.shape[0], -1).clone()
+                parts.append(full.index_copy(0, tgt, payloads[n].to(item_emb.dtype)))
+        return parts[0] if len(parts) == 1 else torch.cat(parts, dim=1)
+
+
 class STULayer(nn.Module):
     def __init__(self, cfg: HSTUConfig, dtype, device):
         super().__init__()

@@ -198,3 +198,24 @@ def test_postprocessor_variants():
         loss = model(batch, emb)[0]
         loss.backward()
         assert torch.isfinite(loss)
+
+
+def test_content_encoder_concatenates_and_fills_history_with_dummy_rows():
+    import torch
+    from mlperf_training_b200.models.hstu import ContentEncoder
+    torch.manual_seed(0)
+    enc = ContentEncoder(8, additional={"genre": 4}, target_enrich={"rank": 3})
+    assert enc.output_dim == 15
+    L = 10
+    is_target = torch.zeros(L, dtype=torch.bool); is_target[[4, 9]] = True
+    item = torch.randn(L, 8)
+    pay = {"genre": torch.randn(L, 4), "rank": torch.randn(2, 3)}
+    out = enc(item, pay, is_target)
+    assert out.shape == (L, 15)
+    assert torch.equal(out[:, :8], item) and torch.equal(out[:, 8:12], pay["genre"])
+    assert torch.equal(out[4, 12:], pay["rank"][0]) and torch.equal(out[9, 12:], pay["rank"][1])
+    assert torch.equal(out[0, 12:], enc.dummy["rank"][0]) and torch.equal(out[8, 12:], enc.dummy["rank"][0])
+    out.sum().backward()
+    assert enc.dummy["rank"].grad is not None and float(enc.dummy["rank"].grad.sum()) == 8 * 3
+    plain = ContentEncoder(8)
+    assert plain(item, {}, is_target) is item
