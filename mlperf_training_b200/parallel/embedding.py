@@ -225,8 +225,19 @@ class ShardedEmbedding:
     def load_sharded(self, path: str, prefix: str = "") -> None:
         """Read this rank's rows of a sharded checkpoint, whatever layout wrote it (the reader fetches the chunks that
         overlap this rank's row range)."""
-        import torch.distributed.checkpoint as dcp
-        dcp.load(self.sharded_state_dict(prefix), checkpoint_id=str(path))      # the local shards are views of the live tensors
+        load_matching(self.sharded_state_dict(prefix), path)                    # the local shards are views of the live tensors
+
+
+def load_matching(state: dict, path) -> list:
+    """``dcp.load`` of the entries of ``state`` whose global shape equals the checkpoint's; returns the keys left
+    out (the Adagrad sums of a column-wise table are ``[rows, shards]``: they do not carry over to or from a
+    row-wise layout, and such a table then keeps the sums it has)."""
+    import torch.distributed.checkpoint as dcp
+    meta = dcp.FileSystemReader(str(path)).read_metadata().state_dict_metadata
+    skipped = [k for k, v in state.items() if k in meta and hasattr(meta[k], "size")
+               and tuple(meta[k].size) != tuple(v.size() if callable(getattr(v, "size", None)) else v.shape)]
+    dcp.load({k: v for k, v in state.items() if k not in skipped}, checkpoint_id=str(path))
+    return skipped
 
 
 class _LookupFn(Function):
@@ -240,3 +251,118 @@ class _LookupFn(Function):
     def backward(ctx, grad):
         ctx.table._backward_rows(grad.contiguous(), ctx.state)
         return None, None, None, None
+
+
+class ColumnShardedEmbedding(ShardedEmbedding):
+    """COLUMN_WISE sharding: rank ``r`` of ``W`` holds columns ``[r * dim / W, (r + 1) * dim / W)`` of EVERY row
+    (TorchRec's placement for wide tables whose rows are hit unevenly: each rank serves the same number of
+    rows per lookup whatever the id distribution, where ROW_WISE loads the owner of a hot row range).
+
+    A lookup sends this rank's unique ids to every rank, each rank reads its column slice of all requested
+    rows, and one all-to-all brings the ``W`` slices of a row back to its requester, which lays them side by
+    side.  Backward cuts a gradient row into its ``W`` column slices, sends slice ``r`` to rank ``r``, reduces
+    the requests of all ranks per row there (sorted order, fp32) and applies row-wise Adagrad to the slice.
+    The Adagrad sum of a row is kept per column shard (the mean of squares runs over the shard's columns),
+    which is how TorchRec's fused optimizer treats a column-wise shard: every shard is a table of its own.
+    """
+
+    def __init__(self, rows: int, dim: int, *, group=None, device="cpu", dtype=torch.bfloat16, lr: float = 1e-2,
+                 eps: float = 1e-8, seed: int = 0, init_scale: float | None = None, name: str = "item", **_unused):
+        self.group = group
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        if dim % self.world:
+            raise ValueError(f"column-wise sharding needs the width ({dim}) to divide by the ranks ({self.world})")
+        self.rows, self.dim, self.name = rows, dim, name
+        self.device = torch.device(device)
+        self.owner = None
+        self.cols = dim // self.world
+        self.col_lo = self.rank * self.cols
+        self.rows_per_rank = self.local_rows = rows
+        self.row_lo = 0
+        self.bounds = torch.tensor([0] + [rows] * self.world, dtype=torch.int64, device=self.device)
+        g = torch.Generator(device=self.device).manual_seed(seed * 7919 + self.rank)
+        scale = init_scale if init_scale is not None else (1.0 / rows) ** 0.5
+        self.weight = (torch.rand(rows, self.cols, generator=g, device=self.device) * 2 - 1).mul_(scale).to(dtype)
+        self.state = torch.zeros(rows, dtype=torch.float32, device=self.device)
+        self.lr, self.eps = lr, eps
+        self.comm, self.recv = "nccl", None
+
+    # ------------------------------------------------------------------ the id half
+    def input_dist(self, ids: torch.Tensor) -> dict:
+        srt = S.sort_unique(ids.reshape(-1), S.key_bits_for(self.rows))
+        n_u = srt.n_unique()                                            # the lookup's one host read
+        uniq = srt.uniq[:n_u]
+        W = self.world
+        if W == 1:
+            return {"uniq": uniq, "inverse": srt.inverse, "srt": srt, "req_ids": uniq, "counts": [n_u]}
+        mine = torch.tensor([n_u], dtype=torch.int64, device=uniq.device)
+        allc = [torch.empty_like(mine) for _ in range(W)]
+        dist.all_gather(allc, mine, group=self.group)
+        counts = torch.cat(allc).tolist()
+        req_ids = torch.empty(sum(counts), dtype=torch.int64, device=uniq.device)
+        dist.all_to_all_single(req_ids, uniq.repeat(W), counts, [n_u] * W, group=self.group)
+        return {"uniq": uniq, "inverse": srt.inverse, "srt": srt, "req_ids": req_ids, "counts": counts}
+
+    def _forward_rows(self, ids, plan: dict | None = None):
+        plan = plan if plan is not None else self.input_dist(ids)
+        uniq, req_ids, counts = plan["uniq"], plan["req_ids"], plan["counts"]
+        W, n_u = self.world, plan["uniq"].numel()
+        served = K.gather_rows(self.weight, req_ids)                    # my columns of every rank's rows
+        if W == 1:
+            rows_u = served
+        else:
+            got = torch.empty((W * n_u, self.cols), dtype=self.weight.dtype, device=served.device)
+            dist.all_to_all_single(got, served, [n_u] * W, counts, group=self.group)
+            rows_u = got.view(W, n_u, self.cols).transpose(0, 1).reshape(n_u, self.dim)
+        return rows_u, (uniq, plan["inverse"], req_ids, counts, None, plan["srt"])
+
+    def _backward_rows(self, grad: torch.Tensor, ctx_state) -> None:
+        uniq, _inverse, req_ids, counts, _, srt = ctx_state
+        W, n_u = self.world, uniq.numel()
+        wire = torch.bfloat16 if self.weight.dtype == torch.bfloat16 else torch.float32
+        if grad.dtype not in (torch.bfloat16, torch.float32):
+            grad = grad.float()
+        g_u = S.segment_sum(grad, srt, out_dtype=wire if W > 1 else torch.float32, max_seg=n_u)
+        if W == 1:
+            self.apply_rowwise_adagrad(req_ids, g_u)
+            return
+        send = g_u.view(n_u, W, self.cols).transpose(0, 1).contiguous().view(W * n_u, self.cols)
+        recv = torch.empty((sum(counts), self.cols), dtype=wire, device=grad.device)
+        dist.all_to_all_single(recv, send, counts, [n_u] * W, group=self.group)
+        srt_l = S.sort_unique(req_ids, S.key_bits_for(max(self.rows, 2)))
+        g_l = S.segment_sum(recv, srt_l, out_dtype=torch.float32)
+        self.apply_rowwise_adagrad(srt_l.uniq, g_l)
+
+    def apply_rowwise_adagrad(self, rows: torch.Tensor, grads: torch.Tensor) -> None:
+        dim, self.dim = self.dim, self.cols                              # the update runs on this rank's slice
+        try:
+            super().apply_rowwise_adagrad(rows, grads)
+        finally:
+            self.dim = dim
+
+    # ------------------------------------------------------------------ state
+    def state_dict(self) -> dict:
+        key = f"embeddings.{self.name}.weight"
+        return {key: self.weight, f"{key}.col_offset": self.col_lo, f"{key}.global_cols": self.dim,
+                f"embeddings.{self.name}.rowwise_adagrad.sum": self.state}
+
+    def load_state_dict(self, sd: dict) -> None:
+        key = f"embeddings.{self.name}.weight"
+        if int(sd[f"{key}.col_offset"]) != self.col_lo or int(sd[f"{key}.global_cols"]) != self.dim:
+            raise ValueError("embedding shard layout differs from the checkpoint (resharding is not supported here)")
+        self.weight.copy_(sd[key])
+        self.state.copy_(sd[f"embeddings.{self.name}.rowwise_adagrad.sum"])
+
+    def sharded_state_dict(self, prefix: str = "") -> dict:
+        """The table as a ``ShardedTensor`` cut along columns (readable under any other placement); the Adagrad
+        sums as ``[rows, W]``, one column per shard - they only reload under the same number of ranks."""
+        from torch.distributed._shard.sharded_tensor import Shard, ShardMetadata, init_from_local_shards
+        wkey, skey = f"{prefix}embeddings.{self.name}.weight", f"{prefix}embeddings.{self.name}.rowwise_adagrad.sum"
+        if self.world == 1:
+            return {wkey: self.weight, skey: self.state}
+        dev = f"rank:{self.rank}/{'cpu' if self.device.type == 'cpu' else str(self.device)}"
+        w = Shard(tensor=self.weight, metadata=ShardMetadata(shard_offsets=[0, self.col_lo], shard_sizes=list(self.weight.shape), placement=dev))
+        s = Shard(tensor=self.state.view(self.rows, 1), metadata=ShardMetadata(shard_offsets=[0, self.rank], shard_sizes=[self.rows, 1], placement=dev))
+        return {wkey: init_from_local_shards([w], self.rows, self.dim, process_group=self.group),
+                skey: init_from_local_shards([s], self.rows, self.world, process_group=self.group)}

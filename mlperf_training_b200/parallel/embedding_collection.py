@@ -1,7 +1,8 @@
 """Embedding collection: many named tables, each sharded by a planner, looked up from one keyed jagged batch.
 
-``plan_tables`` decides per table between ROW_WISE (rows cut evenly over the ranks: the big tables)
-and TABLE_WISE (the whole table on one rank, ranks filled greedily by bytes: the small ones) under a
+``plan_tables`` decides per table between ROW_WISE (rows cut evenly over the ranks: the big tables),
+TABLE_WISE (the whole table on one rank, ranks filled greedily by bytes: the small ones) and, for the
+tables a caller names, COLUMN_WISE (every rank holds a slice of the width of every row) under a
 per-rank memory budget - the decision TorchRec's planner makes for the reference
 (generative_recommenders/dlrm_v4/train/utils.py:1311-1545; tables at
 generative_recommenders/dlrm_v4/configs.py:761-803).  ``EmbeddingCollection.lookup`` takes a
@@ -17,7 +18,7 @@ import torch
 import torch.distributed as dist
 
 from ..data.samples import KeyedJagged
-from .embedding import ShardedEmbedding
+from .embedding import ColumnShardedEmbedding, ShardedEmbedding
 
 
 @dataclass
@@ -48,14 +49,22 @@ YAMBDA_TABLES = (
 )
 
 
-def plan_tables(tables, world: int, row_wise_min_bytes: int = 1 << 30, budget_bytes: int | None = None) -> dict:
-    """``{table: ("row_wise", None) | ("table_wise", owner)}``.  Tables of at least ``row_wise_min_bytes``
-    are cut over all ranks; the others go whole to the rank that holds the fewest bytes so far (largest
-    first).  With ``budget_bytes`` the plan is checked against a per-rank limit."""
+def plan_tables(tables, world: int, row_wise_min_bytes: int = 1 << 30, budget_bytes: int | None = None,
+                column_wise: tuple = ()) -> dict:
+    """``{table: ("row_wise", None) | ("table_wise", owner) | ("column_wise", None)}``.  Tables named in
+    ``column_wise`` (their width must divide by the ranks) are cut along columns; tables of at least
+    ``row_wise_min_bytes`` are cut over all ranks by rows; the others go whole to the rank that holds the
+    fewest bytes so far (largest first).  With ``budget_bytes`` the plan is checked against a per-rank limit."""
     out, load = {}, [0] * max(world, 1)
     small = []
     for t in tables:
-        if world > 1 and t.bytes() >= row_wise_min_bytes:
+        if world > 1 and t.name in column_wise:
+            if t.dim % world:
+                raise ValueError(f"table {t.name}: width {t.dim} does not divide by {world} ranks")
+            out[t.name] = ("column_wise", None)
+            for r in range(world):
+                load[r] += t.bytes() // world
+        elif world > 1 and t.bytes() >= row_wise_min_bytes:
             out[t.name] = ("row_wise", None)
             for r in range(world):
                 load[r] += t.bytes() // world
@@ -82,9 +91,10 @@ class EmbeddingCollection:
         for i, t in enumerate(self.configs):
             kind, owner = self.plan[t.name]
             dt = torch.bfloat16 if t.dtype == "bf16" else torch.float32
-            self.tables[t.name] = ShardedEmbedding(t.rows, t.dim, group=group, device=device, dtype=dt, lr=lr, eps=eps,
-                                                   seed=seed + 101 * i, comm=comm if kind == "row_wise" else "nccl", name=t.name,
-                                                   owner=owner if kind == "table_wise" else None)
+            cls = ColumnShardedEmbedding if kind == "column_wise" else ShardedEmbedding
+            self.tables[t.name] = cls(t.rows, t.dim, group=group, device=device, dtype=dt, lr=lr, eps=eps,
+                                      seed=seed + 101 * i, comm=comm if kind == "row_wise" else "nccl", name=t.name,
+                                      owner=owner if kind == "table_wise" else None)
             for f in t.features:
                 self.feature_table[f] = t.name
 
@@ -148,8 +158,8 @@ class EmbeddingCollection:
 
     def load_sharded(self, path: str, prefix: str = "") -> None:
         """Load a sharded checkpoint written under any number of ranks and any placement plan."""
-        import torch.distributed.checkpoint as dcp
-        dcp.load(self.sharded_state_dict(prefix), checkpoint_id=str(path))
+        from .embedding import load_matching
+        load_matching(self.sharded_state_dict(prefix), path)
 
     def local_bytes(self) -> int:
         return sum(t.weight.numel() * t.weight.element_size() for t in self.tables.values())

@@ -133,3 +133,69 @@ def test_sharded_state_round_trips_across_placement_plans_gloo(tmp_path):
                        env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("ok=True") == 2
+
+
+def _cw_worker(rank, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=2)
+    try:
+        tabs = [TableConfig("wide", 40, 8, ("wide",), "fp32")]
+        ec = EmbeddingCollection(tabs, lr=0.5, seed=3, plan=plan_tables(tabs, 2, column_wise=("wide",)))
+        t = ec.tables["wide"]
+        ok = t.weight.shape == (40, 4) and t.col_lo == 4 * rank
+        parts = [torch.zeros(40, 4) for _ in range(2)]
+        dist.all_gather(parts, t.weight.clone())
+        full = torch.cat(parts, 1)
+        g = torch.Generator().manual_seed(10 + rank)
+        ids = torch.randint(0, 40, (11,), generator=g)
+        ids[3] = ids[0]                                                     # a duplicate on this rank
+        out = ec.lookup(KeyedJagged.from_dict({"wide": (ids, torch.tensor([5, 6]))}))["wide"]
+        ok &= torch.equal(out, full[ids])
+        coef = torch.randn(11, 8, generator=g)
+        (out * coef).sum().backward()
+        # the unsharded truth: both ranks' gradient rows summed per id; Adagrad sum per column shard
+        both_ids, both_g = [torch.zeros(11, dtype=torch.int64) for _ in range(2)], [torch.zeros(11, 8) for _ in range(2)]
+        dist.all_gather(both_ids, ids)
+        dist.all_gather(both_g, coef)
+        dense = torch.zeros(40, 8).index_add_(0, torch.cat(both_ids), torch.cat(both_g))
+        hit = torch.zeros(40, dtype=torch.bool)
+        hit[torch.cat(both_ids)] = True
+        mine = dense[:, 4 * rank:4 * rank + 4]
+        st = (mine * mine).mean(-1)
+        want = full[:, 4 * rank:4 * rank + 4] - 0.5 * mine / (st.sqrt()[:, None] + 1e-8)
+        want = torch.where(hit[:, None], want, full[:, 4 * rank:4 * rank + 4])
+        ok &= torch.allclose(t.weight, want, atol=1e-6) and torch.allclose(t.state, torch.where(hit, st, torch.zeros(())), atol=1e-6)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_column_wise_table_lookup_and_update_gloo():
+    """COLUMN_WISE: every rank holds half the width of every row; rows come back whole, the sparse update
+    reaches both column shards with the gradient rows of both ranks."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_cw_worker, args=(r, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert res == {0: True, 1: True}
+
+
+def test_column_wise_single_rank_is_a_plain_table():
+    from mlperf_training_b200.parallel.embedding import ColumnShardedEmbedding
+    t = ColumnShardedEmbedding(20, 6, dtype=torch.float32, lr=0.1, seed=2)
+    ids = torch.tensor([3, 3, 7])
+    w0 = t.weight.clone()
+    rows = t.lookup(ids)
+    assert torch.equal(rows, w0[ids])
+    rows.sum().backward()
+    assert not torch.equal(t.weight[3], w0[3]) and torch.equal(t.weight[4], w0[4])
+    with pytest.raises(ValueError):
+        plan_tables([TableConfig("odd", 10, 7, ("odd",))], 2, column_wise=("odd",))
