@@ -72,6 +72,17 @@ class HSTUConfig:
     recent_window: int = 0
     recent_window_layers: int = 0
     postprocessor: str = "timestamp_ln"   # "timestamp_ln" | "ln" | "l2" (modules/postprocessors.py)
+    # "sum": one token per event, content + action branches added.  "interleave": every history event becomes a content
+    # token followed by an action token, a target stays one content token (modules/contextual_interleave_preprocessor.py)
+    preprocessor: str = "sum"
+    # "simple": the content / action MLPs are plain MLPs.  "parameterized": their weight matrix and bias are generated per
+    # sample from the contextual features (modules/contextualize_mlps.py: ParameterizedContextualizedMLP)
+    contextualized_mlp: str = "simple"
+    pmlp_contextual_dropout: float = 0.0
+
+    def attn_len(self) -> int:
+        """The sequence length the attention normalises by (and sizes its tiles for)."""
+        return (2 if self.preprocessor == "interleave" else 1) * self.max_seq_len + self.contextual
 
     def torch_dtype(self):
         return {"bf16": torch.bfloat16, "fp32": torch.float32}[self.dtype]
@@ -135,6 +146,40 @@ class _MLP(nn.Module):
 
     def forward(self, x, precision="bf16"):
         return self.n2(self.l2(self.n1(self.l1(x, precision)), precision))
+
+
+class _ParameterizedMLP(nn.Module):
+    """A linear map whose ``[n_in, n_out]`` matrix and bias are functions of the sample's contextual features:
+    ``shared = Linear(ctx)``; ``W_b = LayerNorm_{in,out}(Linear(shared))``; ``bias_b = Linear(SwishLN(Linear(shared)))``;
+    every token of sample ``b`` gets ``x W_b + bias_b``
+    (generative_recommenders/modules/contextualize_mlps.py:79-141).  The per-sample products run as one batched
+    matmul over the padded ``[B, N, n_in]`` view of the jagged tokens."""
+
+    def __init__(self, ctx_flat, n_in, hidden, n_out, dtype, device):
+        super().__init__()
+        self.n_in, self.n_out = n_in, n_out
+        self.compress = _Linear(ctx_flat, hidden, dtype, device)
+        self.raw = _Linear(hidden, n_in * n_out, dtype, device)
+        self.norm_w = nn.Parameter(torch.ones(n_in, n_out, dtype=dtype, device=device))
+        self.norm_b = nn.Parameter(torch.zeros(n_in, n_out, dtype=dtype, device=device))
+        self.res1 = _Linear(hidden, hidden, dtype, device)
+        self.res_n = _LN(hidden, dtype, device, swish=True)
+        self.res2 = _Linear(hidden, n_out, dtype, device)
+
+    def forward(self, x, seq, col, n_samples: int, max_len: int, ctx_flat):
+        """``x [rows, n_in]`` (the first ``seq.numel()`` rows are tokens), ``seq`` / ``col``: sample and position of every
+        token, ``ctx_flat [B, ctx_flat]``.  Returns ``[rows, n_out]`` (padding rows zero)."""
+        shared = self.compress(ctx_flat.to(x.dtype))
+        w = TF.layer_norm(self.raw(shared).float().view(n_samples, self.n_in, self.n_out), (self.n_in, self.n_out),
+                          self.norm_w.float(), self.norm_b.float(), 1e-5)
+        bias = self.res2(self.res_n(self.res1(shared))).float()
+        n = seq.numel()
+        dense = torch.zeros((n_samples, max_len, self.n_in), dtype=torch.float32, device=x.device)
+        dense = dense.index_put((seq, col), x[:n].float())
+        y = torch.baddbmm(bias[:, None, :], dense, w)[seq, col]
+        out = torch.zeros((x.shape[0], self.n_out), dtype=x.dtype, device=x.device)
+        out[:n] = y.to(x.dtype)
+        return out
 
 
 class ActionEncoder(nn.Module):
@@ -214,7 +259,7 @@ class STULayer(nn.Module):
         v = v_raw.unflatten(-1, (h, cfg.d_v))
         q = q_raw.unflatten(-1, (h, cfg.d_qk))
         k = k_raw.unflatten(-1, (h, cfg.d_qk))
-        attn = hstu_attention(q, k, v, offsets, max_len or (cfg.max_seq_len + cfg.contextual), cfg.d_qk ** -0.5, num_targets,
+        attn = hstu_attention(q, k, v, offsets, max_len or cfg.attn_len(), cfg.d_qk ** -0.5, num_targets,
                               cfg.contextual, precision=cfg.attn_precision, owner=self).reshape(x.shape[0], h * cfg.d_v)
         if self.fuse_glue and gate_cat_eligible(u_raw, attn):
             # SiLU(u), the layer norm of the attention output, their product and the concatenation in one kernel
@@ -248,7 +293,7 @@ class STULayer(nn.Module):
         # (a handful of target rows: plain matmuls, far below a tensor-core tile)
         u = TF.silu(nt @ W[:hv].t() + beta[:hv])
         q = (nt @ W[2 * hv:2 * hv + hq].t() + beta[2 * hv:2 * hv + hq]).unflatten(-1, (h, cfg.d_qk))
-        N = cfg.max_seq_len + cfg.contextual
+        N = cfg.attn_len()
         # every sample's query over its own rows (segment-sum backward when the group bounds are given)
         q_rows = q[seq] if offsets is None else F.expand_rows(q.reshape(n_samples, hq), seq, offsets).unflatten(-1, (h, cfg.d_qk))
         score = (q_rows.float() * k.float()).sum(-1) * (cfg.d_qk ** -0.5)             # [rows, h]
@@ -326,6 +371,14 @@ class HSTU(nn.Module):
         self.item_mlp = _MLP(cfg.emb_dim * (1 + cfg.extra_features), d, d, dt, device)
         self.head = MultitaskHead(cfg, dt, device)
         self._sd_iter = 0                # training forwards seen: seeds the stochastic-depth draws (kept in the state dict)
+        if cfg.preprocessor not in ("sum", "interleave") or cfg.contextualized_mlp not in ("simple", "parameterized"):
+            raise ValueError("preprocessor: 'sum' | 'interleave'; contextualized_mlp: 'simple' | 'parameterized'")
+        if cfg.contextualized_mlp == "parameterized":
+            if cfg.contextual <= 0:
+                raise ValueError("parameterized content / action MLPs are generated from the contextual features: contextual > 0")
+            flat = cfg.contextual * (cfg.contextual_dim or cfg.emb_dim)
+            self.content_mlp = _ParameterizedMLP(flat, cfg.emb_dim, cfg.mlp_hidden, d, dt, device)
+            self.action_mlp = _ParameterizedMLP(flat, len(cfg.action_bits) * cfg.action_dim, cfg.mlp_hidden, d, dt, device)
         # additional-feature branch of the preprocessor: MLP(cat(extra embeddings)) added to the content branch
         self.extra_mlp = _MLP(cfg.emb_dim * cfg.extra_features, cfg.mlp_hidden, d, dt, device) if cfg.extra_features else None
         # contextual tokens: one [ctx_dim, D] matrix and bias per contextual feature (a batched linear)
@@ -370,7 +423,7 @@ class HSTU(nn.Module):
         lens2 = lens - prefix
         offsets2 = torch.zeros_like(offsets)
         offsets2[1:] = torch.cumsum(lens2, 0).to(offsets.dtype)
-        n2 = min(cfg.max_seq_len + C, W + C + max_targets)
+        n2 = min(cfg.attn_len(), W + C + max_targets)
         y2 = layer(x2.contiguous(), offsets2, num_targets, rows2, max_len=n2)
         y2 = torch.cat([y2, y2.new_zeros((1, y2.shape[1]))], dim=0)
         out = torch.where(keep[:, None], y2[idx], x[:total])
@@ -419,6 +472,20 @@ class HSTU(nn.Module):
         is_target0 = col0 >= (lens0 - num_targets.long())[seq0]
         return total0, lens0, seq0, col0, is_target0
 
+    @staticmethod
+    def interleave_layout(lens0, num_targets, seq0, col0, is_target0):
+        """Where the tokens of the interleaved sequence go: history event ``i`` of a sample becomes rows ``2 i``
+        (content) and ``2 i + 1`` (action) of the sample, target ``j`` row ``2 * history + j``.  Returns
+        ``(offsets [B + 1], lengths [B], content row of every token, indices of the history tokens, their action rows)``."""
+        hist = lens0 - num_targets.long()
+        lens_i = 2 * hist + num_targets.long()
+        offsets_i = torch.zeros(lens0.numel() + 1, dtype=torch.long, device=lens0.device)
+        offsets_i[1:] = torch.cumsum(lens_i, 0)
+        base = offsets_i[:-1][seq0]
+        dst_c = torch.where(is_target0, base + hist[seq0] + col0, base + 2 * col0)
+        h_rows = torch.nonzero(~is_target0, as_tuple=False)[:, 0]
+        return offsets_i, lens_i, dst_c, h_rows, dst_c[h_rows] + 1
+
     def action_branch(self, batch: dict, rows: int) -> torch.Tensor:
         """The action branch of the preprocessor (action encoder + its MLP), ``[rows, dim]``.  It reads the batch
         only - no embedding - so a trainer may issue it before the embedding rows have arrived and pass the
@@ -427,6 +494,8 @@ class HSTU(nn.Module):
         so the result is bit-identical)."""
         cfg = self.cfg
         dt = cfg.torch_dtype()
+        if cfg.contextualized_mlp != "simple":
+            raise ValueError("the action branch reads the contextual embeddings with a parameterized MLP: it cannot run ahead of the lookup")
         _, _, _, _, is_target0 = self._token_layout(batch)
         enc = self.action_enc(batch["actions"], is_target0)
         if enc.shape[0] != rows:
@@ -463,31 +532,58 @@ class HSTU(nn.Module):
             out[:t.shape[0]] = t
             return out
 
-        # ---- preprocessor: content (+ additional features) + action branches, on the tokens as they came
-        x = self.content_mlp(item_emb.to(dt), cfg.precision)
+        # ---- preprocessor: content (+ additional features) and action branches, on the tokens as they came
+        if cfg.contextualized_mlp == "parameterized":
+            if contextual_emb is None:
+                raise ValueError("parameterized MLPs need contextual_emb")
+            flat = contextual_emb.reshape(B, -1).to(dt)
+            if cfg.pmlp_contextual_dropout > 0 and self.training:
+                flat = TF.dropout(flat, cfg.pmlp_contextual_dropout)
+            x = self.content_mlp(item_emb.to(dt), seq0, col0, B, cfg.max_seq_len, flat)
+            act = self.action_mlp(pad(self.action_enc(actions0, is_target0), rows0).to(dt), seq0, col0, B, cfg.max_seq_len, flat)
+        else:
+            x = self.content_mlp(item_emb.to(dt), cfg.precision)
+            act = (action_out if action_out is not None
+                   else self.action_mlp(pad(self.action_enc(actions0, is_target0), rows0).to(dt), cfg.precision))
         if self.extra_mlp is not None:
             if extra_emb is None:
                 raise ValueError("the model was built with extra_features: pass extra_emb")
             x = x + self.extra_mlp(extra_emb.to(dt), cfg.precision)
-        x = x + (action_out if action_out is not None
-                 else self.action_mlp(pad(self.action_enc(actions0, is_target0), rows0).to(dt), cfg.precision))
+        if cfg.preprocessor == "interleave":
+            # history event i of a sample -> rows 2 i (content) and 2 i + 1 (action); target j -> row 2 * history + j
+            n_tgt = int(batch["total_targets"]) if "total_targets" in batch else \
+                (B if int(batch.get("max_targets", 0)) == 1 else int(num_targets.sum()))
+            offsets_i, lens_i, dst_c, h_rows, dst_a = self.interleave_layout(lens0, num_targets, seq0, col0, is_target0)
+            total_i = 2 * total0 - n_tgt
+            rows_i = (total_i + 127) // 128 * 128
+            merged = torch.zeros((rows_i, cfg.dim), dtype=dt, device=dev).index_copy(0, dst_c, x[:total0])
+            ts_i = torch.zeros(total_i, dtype=ts0.dtype, device=dev).index_copy(0, dst_c, ts0[:total0])
+            x = merged.index_copy(0, dst_a, act[h_rows])
+            ts0_l = ts_i.index_copy(0, dst_a, ts0[h_rows])
+            # from here on the interleaved tokens are "the tokens as they came"
+            offsets_l, total_l, rows_l = offsets_i.to(offsets0.dtype), total_i, rows_i
+            seq_l = torch.repeat_interleave(torch.arange(B, device=dev), lens_i, output_size=total_i)
+            col_l = torch.arange(total_i, device=dev) - offsets_i[:-1][seq_l]
+        else:
+            x = x + act
+            offsets_l, total_l, rows_l, ts0_l, seq_l, col_l = offsets0, total0, rows0, ts0, seq0, col0
         # ---- contextual tokens in front of every sequence
         if C > 0:
             if contextual_emb is None:
                 raise ValueError("the model was built with contextual tokens: pass contextual_emb")
             ctx = torch.baddbmm(self.ctx_bias[:, None, :].float(), contextual_emb.to(dt).float().transpose(0, 1),
                                 self.ctx_weight.float()).transpose(0, 1).to(dt)              # [B, C, D]
-            offsets = (offsets0.long() + C * torch.arange(B + 1, device=dev)).to(offsets0.dtype)
-            total = total0 + B * C
+            offsets = (offsets_l.long() + C * torch.arange(B + 1, device=dev)).to(offsets0.dtype)
+            total = total_l + B * C
             rows = (total + 127) // 128 * 128
-            dst_tok = offsets[:-1].long()[seq0] + C + col0
+            dst_tok = offsets[:-1].long()[seq_l] + C + col_l
             dst_ctx = (offsets[:-1].long()[:, None] + torch.arange(C, device=dev)[None]).reshape(-1)
             merged = torch.zeros((rows, cfg.dim), dtype=dt, device=dev)
-            merged = merged.index_copy(0, dst_tok, x[:total0]).index_copy(0, dst_ctx, ctx.reshape(B * C, cfg.dim))
-            ts = torch.zeros(total, dtype=ts0.dtype, device=dev).index_copy(0, dst_tok, ts0[:total0])
+            merged = merged.index_copy(0, dst_tok, x[:total_l]).index_copy(0, dst_ctx, ctx.reshape(B * C, cfg.dim))
+            ts = torch.zeros(total, dtype=ts0.dtype, device=dev).index_copy(0, dst_tok, ts0_l[:total_l])
             x = merged
         else:
-            offsets, total, rows, ts = offsets0, total0, rows0, ts0
+            offsets, total, rows, ts = offsets_l, total_l, rows_l, ts0_l
         seq, col, pos_idx = self.position_indices(offsets, num_targets, total)
         lens = (offsets[1:] - offsets[:-1]).long()
         is_target = col >= (lens - num_targets.long())[seq]

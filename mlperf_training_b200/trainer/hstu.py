@@ -277,7 +277,7 @@ class HSTUTrainer:
         """Embedding rows of the batch and, issued under their all-to-all, the embedding-independent action branch
         of the preprocessor: the row exchange runs on its own stream while the main stream computes the branch
         (generative_recommenders/modules/action_prefill.py)."""
-        if self.lookup_stream is None or not self.action_prefill:
+        if self.lookup_stream is None or not self.action_prefill or self.cfg.contextualized_mlp != "simple":
             return self.embed(batch), None
         main = torch.cuda.current_stream()
         self.lookup_stream.wait_stream(main)
@@ -411,7 +411,9 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                      d_qk=int(m.get("d_qk", 128)), d_v=int(m.get("d_v", 128)), max_seq_len=int(m.get("max_seq_len", 4096)),
                      emb_dim=int((exp.get("embedding") or {}).get("dim", 256)), dtype=m.get("dtype", "bf16"),
                      precision=m.get("precision", "bf16"), attn_precision=str(m.get("attn_precision", "bf16")),
-                     mlp_hidden=int(m.get("mlp_hidden", 256)),
+                     mlp_hidden=int(m.get("mlp_hidden", 256)), preprocessor=str(m.get("preprocessor", "sum")),
+                     contextualized_mlp=str(m.get("contextualized_mlp", "simple")),
+                     pmlp_contextual_dropout=float(m.get("pmlp_contextual_dropout", 0.0)),
                      num_positions=int(m.get("num_positions", 8192)), num_time_buckets=int(m.get("num_time_buckets", 2048)))
     emb = exp.get("embedding") or {}
     table_set = emb.get("tables") or None            # "yambda": the benchmark's eleven tables instead of one item table

@@ -227,3 +227,12 @@ def test_yambda_synthetic_samples_are_consistent():
     for t in tables:
         for f in t.features:
             assert int(kjt.values[slice(*ranges[f])].max()) < t.rows
+
+
+def test_hstu_trainer_steps_with_the_interleaved_preprocessor():
+    from mlperf_training_b200.models.hstu import tiny_hstu
+    from mlperf_training_b200.trainer.hstu import HSTUTrainer
+    tr = HSTUTrainer(tiny_hstu(preprocessor="interleave", input_dropout=0.0, linear_dropout=0.0), 200, 3, "cpu", seed=2,
+                     data_kw=dict(length_median=12, length_min=4, length_max=24))
+    losses = [float(tr.train_step(i)) for i in range(4)]
+    assert all(l == l and l < 10 for l in losses)

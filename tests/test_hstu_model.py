@@ -219,3 +219,82 @@ def test_content_encoder_concatenates_and_fills_history_with_dummy_rows():
     assert enc.dummy["rank"].grad is not None and float(enc.dummy["rank"].grad.sum()) == 8 * 3
     plain = ContentEncoder(8)
     assert plain(item, {}, is_target) is item
+
+
+def test_interleave_preprocessor_layout_and_forward():
+    """Interleaved form: every history event is a content token followed by an action token, a target one content
+    token.  The layout helper against a per-sample loop; then a forward whose loss reaches both branches and whose
+    targets-only last layer equals the full form."""
+    lens = torch.tensor([4, 2, 5])
+    nt = torch.tensor([1, 1, 2])
+    off = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)])
+    seq = torch.repeat_interleave(torch.arange(3), lens)
+    col = torch.arange(int(lens.sum())) - off[:-1][seq]
+    is_t = col >= (lens - nt)[seq]
+    off_i, lens_i, dst_c, h_rows, dst_a = HSTU.interleave_layout(lens, nt, seq, col, is_t)
+    want_c, want_a, base = [], [], 0
+    for L, T in zip(lens.tolist(), nt.tolist()):
+        h = L - T
+        want_c += [base + 2 * i for i in range(h)] + [base + 2 * h + j for j in range(T)]
+        want_a += [base + 2 * i + 1 for i in range(h)]
+        base += 2 * h + T
+    assert dst_c.tolist() == want_c and dst_a.tolist() == want_a and off_i.tolist() == [0, 7, 10, 18]
+    assert sorted(dst_c.tolist() + dst_a.tolist()) == list(range(18)) and lens_i.tolist() == [7, 3, 8]
+
+    b = _batch(B=4)
+    outs = []
+    for tol in (False, True):
+        cfg = tiny_hstu(preprocessor="interleave", contextual=2, input_dropout=0.0, linear_dropout=0.0, targets_only_last=tol)
+        m = HSTU(cfg, "cpu", seed=4)
+        g = torch.Generator().manual_seed(2)
+        emb = torch.randn(b["rows"], cfg.emb_dim, generator=g)
+        emb[b["total"]:] = 0
+        ctx = torch.randn(4, 2, cfg.emb_dim, generator=g)
+        loss, preds, labels = m(b, emb, contextual_emb=ctx)
+        loss.backward()
+        assert torch.isfinite(loss) and preds.shape == (4,)
+        assert m.content_mlp.l1.weight.grad.abs().sum() > 0 and m.action_mlp.l1.weight.grad.abs().sum() > 0
+        outs.append(loss.detach())
+    assert torch.allclose(outs[0], outs[1], atol=2e-5)
+    # the action of a history event is its own token now: changing one action changes the loss, the sum form's
+    # action branch is not part of the content token
+    b2 = dict(b, actions=b["actions"].clone())
+    b2["actions"][0] ^= 1
+    assert not torch.allclose(m(b2, emb, contextual_emb=ctx)[0], outs[1])
+
+
+def test_parameterized_contextual_mlp_matches_per_sample_matmul():
+    from mlperf_training_b200.models.hstu import _ParameterizedMLP
+    torch.manual_seed(0)
+    mlp = _ParameterizedMLP(12, 6, 8, 5, torch.float32, "cpu")
+    with torch.no_grad():
+        mlp.norm_w.uniform_(0.5, 1.5)
+        mlp.norm_b.uniform_(-0.1, 0.1)
+    lens = torch.tensor([3, 1, 4])
+    seq = torch.repeat_interleave(torch.arange(3), lens)
+    col = torch.cat([torch.arange(int(n)) for n in lens])
+    x = torch.randn(16, 6)
+    x[8:] = 0
+    ctx = torch.randn(3, 12)
+    y = mlp(x, seq, col, 3, 4, ctx)
+    assert y.shape == (16, 5) and torch.equal(y[8:], torch.zeros(8, 5))
+    shared = mlp.compress(ctx)
+    for t in range(8):
+        s = int(seq[t])
+        w = torch.nn.functional.layer_norm(mlp.raw(shared[s:s + 1]).view(6, 5), (6, 5), mlp.norm_w, mlp.norm_b, 1e-5)
+        bias = mlp.res2(mlp.res_n(mlp.res1(shared[s:s + 1])))[0]
+        assert torch.allclose(y[t], x[t] @ w + bias, atol=1e-5)
+    # through the model: the contextual features of a sample steer its own content / action maps only
+    b = _batch(B=4)
+    cfg = tiny_hstu(contextualized_mlp="parameterized", contextual=2, input_dropout=0.0, linear_dropout=0.0)
+    m = HSTU(cfg, "cpu", seed=6)
+    g = torch.Generator().manual_seed(3)
+    emb = torch.randn(b["rows"], cfg.emb_dim, generator=g)
+    ctx = torch.randn(4, 2, cfg.emb_dim, generator=g)
+    loss, preds, _ = m(b, emb, contextual_emb=ctx)
+    loss.backward()
+    assert torch.isfinite(loss) and m.content_mlp.raw.weight.grad.abs().sum() > 0 and m.action_mlp.res2.weight.grad.abs().sum() > 0
+    ctx2 = ctx.clone()
+    ctx2[2] += 0.5
+    changed = (m(b, emb, contextual_emb=ctx2)[1] - preds).abs() > 1e-7
+    assert changed.tolist() == [False, False, True, False]
