@@ -12,7 +12,9 @@ both sends and receives, which is what keeps neighbouring stages from blocking e
 The reference gets this schedule from Megatron's ``get_forward_backward_func``
 (llama2_sft/primus/src/llama2_custom.py:1494) with ``pipeline_model_parallel_size`` /
 ``virtual_pipeline_model_parallel_size`` from the YAML (llama2_sft/primus/conf/llama2_70b_lora_posttrain.yaml:19-21);
-every shipped config sets the size to 1.  ``InterleavedRunner`` is the virtual-stage variant (several
+every shipped config sets the size to 1.  A stage may itself be tensor + sequence parallel (``tp``): its ranks
+then hold slices of the stage's matrices, each passes its own block of token rows to the same-index rank of
+the next stage, and the messages shrink by the group size.  ``InterleavedRunner`` is the virtual-stage variant (several
 model chunks per rank); ``trainer.pipeline_train.PipelineTrainer`` puts either schedule behind the
 trainer interface of the run loop.
 """
@@ -22,7 +24,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-from ..models.gpt import Block, GPTConfig
+from ..models.gpt import Block, GPTConfig, shard_of
 from ..ops import functional as F
 from ..ops import kernels as K
 
@@ -48,10 +50,20 @@ class GPTStage(nn.Module):
             self.final_norm = nn.Parameter(torch.ones(cfg.hidden, dtype=dtype, device=device))
             self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden, dtype=dtype, device=device))
         self._rope = None
+        self.tp = tp if (tp is not None and tp.world > 1) else None
         with torch.no_grad():
             for n, p in self.named_parameters():
                 if p.dim() >= 2 and "lora" not in n:
-                    p.normal_(0.0, cfg.init_std)
+                    shard = getattr(p, "tensor_parallel", None)
+                    if shard is None:
+                        p.normal_(0.0, cfg.init_std)
+                        continue
+                    # tensor-parallel slice: draw the full matrix (the ranks of a stage share the seed, so they draw
+                    # the same one) and keep this rank's part - equal slices would never grow apart
+                    kind, W, r = shard
+                    full_shape = (p.shape[0] * W, p.shape[1]) if kind in ("rows", "rows_2", "qkv") else (p.shape[0], p.shape[1] * W)
+                    full = torch.empty(full_shape, dtype=p.dtype, device=p.device).normal_(0.0, cfg.init_std)
+                    p.copy_(shard_of(full, kind, W, r, cfg))
 
     @torch.no_grad()
     def load_from_full(self, full: nn.Module) -> None:
@@ -59,7 +71,13 @@ class GPTStage(nn.Module):
         if self.first:
             self.embed.copy_(full.embed)
         for blk, i in zip(self.blocks, self.layers):
-            blk.load_state_dict(full.blocks[i].state_dict())
+            src = dict(full.blocks[i].named_parameters())
+            for n, p in blk.named_parameters():
+                shard = getattr(p, "tensor_parallel", None)
+                if shard is not None and src[n].shape != p.shape:        # the unsplit model holds the whole matrix
+                    p.copy_(shard_of(src[n], shard[0], shard[1], shard[2], self.cfg))
+                else:
+                    p.copy_(src[n])
         if self.last:
             self.final_norm.copy_(full.final_norm)
             self.lm_head.copy_(full.lm_head)
@@ -75,8 +93,21 @@ class GPTStage(nn.Module):
         the token losses divided by ``n_valid`` when that is given)."""
         B, S = tokens.shape
         cos, sin = self.rope(tokens.device)
+        ids = tokens.reshape(-1)
+        if self.tp is not None:
+            # tensor + sequence parallel inside the stage: every rank of the group embeds, passes on and scores its
+            # own block of token rows; the returned loss is this rank's share of the mean
+            W, r = self.tp.world, self.tp.rank
+            if ids.numel() % W:
+                raise ValueError("the number of tokens must be divisible by the tensor-parallel size")
+            rows = ids.numel() // W
+            if n_valid is None:
+                n_valid = ids.numel()
+            ids = ids[r * rows:(r + 1) * rows]
+            if labels is not None:
+                labels = labels.reshape(-1)[r * rows:(r + 1) * rows]
         if self.first:
-            x = F.embedding(tokens.reshape(-1), self.embed)
+            x = F.embedding(ids, self.embed)
         for blk in self.blocks:
             x = blk(x, cos, sin, B, S)
         if self.last:
@@ -125,7 +156,8 @@ class PipelineRunner:
         M = len(micro_batches)
         S, s = st.n_stages, st.stage
         tok0 = micro_batches[0][0]
-        act_like = torch.empty((tok0.numel(), st.cfg.hidden), dtype=st.cfg.torch_dtype(), device=tok0.device)
+        act_like = torch.empty((tok0.numel() // (st.tp.world if st.tp is not None else 1), st.cfg.hidden),
+                               dtype=st.cfg.torch_dtype(), device=tok0.device)
         warm = min(S - s - 1, M)
         steady = M - warm
         live: list[tuple[torch.Tensor | None, torch.Tensor]] = []
@@ -216,7 +248,9 @@ class InterleavedRunner:
         remain = total - warm
         cfg = self.chunks[0].cfg
         tok0 = micro_batches[0][0]
-        like = torch.empty((tok0.numel(), cfg.hidden), dtype=cfg.torch_dtype(), device=tok0.device)
+        tp = self.chunks[0].tp
+        like = torch.empty((tok0.numel() // (tp.world if tp is not None else 1), cfg.hidden), dtype=cfg.torch_dtype(),
+                           device=tok0.device)
         inputs = [[] for _ in range(v)]
         outputs = [[] for _ in range(v)]
         ograds = [[] for _ in range(v)]

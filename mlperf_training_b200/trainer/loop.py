@@ -187,9 +187,9 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
 
     cfg = build_model_config(rc.model)
     pp_size, cp_size = int(rc.pipeline_parallel), int(rc.context_parallel)
-    if pp_size > 1 and (int(rc.tensor_parallel) > 1 or int(rc.dp_replicate) > 1 or cp_size > 1 or world % pp_size):
-        raise NotImplementedError("pipeline stages combine with plain data parallelism here (tensor_parallel = 1, "
-                                  "context_parallel = 1, dp_replicate = 1, world divisible by pipeline_parallel)")
+    if pp_size > 1 and (int(rc.dp_replicate) > 1 or cp_size > 1 or world % (pp_size * max(int(rc.tensor_parallel), 1))):
+        raise NotImplementedError("pipeline stages combine with data and tensor parallelism here (context_parallel = 1, "
+                                  "dp_replicate = 1, world divisible by pipeline_parallel x tensor_parallel)")
     if cp_size > 1 and (int(rc.tensor_parallel) > 1 or int(rc.dp_replicate) > 1 or world % cp_size):
         raise NotImplementedError("context parallelism combines with plain data parallelism here (tensor_parallel = 1, "
                                   "dp_replicate = 1, world divisible by context_parallel)")
@@ -198,7 +198,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     replicate = max(int(rc.dp_replicate), 1)
     if tp_size > 1 or (replicate > 1 and world > 1):
         from ..parallel.mesh import Mesh, MeshSpec
-        mesh = Mesh(MeshSpec(tp=tp_size, dp_replicate=replicate))
+        mesh = Mesh(MeshSpec(tp=tp_size, pp=pp_size, dp_replicate=replicate))
         if replicate > 1:
             rep_group = mesh.group("dp_replicate")
     if tp_size > 1:
@@ -206,7 +206,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             print("[parallel] sequence_parallel: 0 ignored - the tensor-parallel blocks always shard the activations "
                   "between them over the sequence (all-gather -> GEMM, GEMM -> reduce-scatter)", flush=True)
         from ..parallel.tensor import TPContext
-        fused_tp = str(rc.tp_comm_overlap).lower() == "fused" and str(device).startswith("cuda")
+        # (stages of a pipeline keep the library collectives: the fused kernels' symmetric buffers are per process group)
+        fused_tp = str(rc.tp_comm_overlap).lower() == "fused" and str(device).startswith("cuda") and pp_size == 1
         # low-precision recipes run the frozen linears of the fused tensor-parallel path (the base of a LoRA run) on
         # per-tensor FP8 operands; trainable tensor-parallel linears run the bf16 tcgen05 GEMMs
         tp_prec = "fp8" if (fused_tp and cfg.precision != "bf16") else "bf16"
@@ -230,7 +231,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             ep_group, edp_group = ep_mesh.group("ep"), ep_mesh.group("edp")
         fused_ep = str(rc.moe_dispatch).lower() == "fused" and str(device).startswith("cuda")
         cfg.ep_comm = "fused" if fused_ep else "nccl"
-    if pp_size > 1:
+    if pp_size > 1 and tp_size == 1:
         from ..parallel.mesh import Mesh, MeshSpec
         mesh = Mesh(MeshSpec(pp=pp_size))
         dp_rank, dp_world = mesh.index("dp"), mesh.size("dp")
@@ -252,7 +253,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     if pp_size > 1:
         from .pipeline_train import PipelineTrainer
         trainer = PipelineTrainer(cfg, opt, tc, device, mesh, virtual_stages=rc.virtual_pipeline_parallel or 1,
-                                  freeze_base=cfg.lora_rank > 0)
+                                  freeze_base=cfg.lora_rank > 0, tp=tp_ctx)
     else:
         trainer = PretrainTrainer(cfg, opt, tc, device, group=dp_group, ep_group=ep_group, tp=tp_ctx,
                                   freeze_base=cfg.lora_rank > 0, replicate_group=rep_group, cp_group=cp_group,

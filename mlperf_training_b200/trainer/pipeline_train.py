@@ -5,7 +5,9 @@
 run loop drives either.  A rank owns one ``parallel.pipeline.GPTStage`` (plain 1F1B) or
 ``virtual_stages`` of them (interleaved 1F1B); the ranks of one pipeline get the same batch, the
 data-parallel replicas of a stage share its ZeRO-sharded optimizer, and the gradient-norm of the
-clip is summed over the pipeline group.  The loss lives on the last stage and is broadcast to the
+clip is summed over the pipeline group.  With ``tp`` a stage is itself tensor + sequence parallel: the mesh
+is tensor x data x pipeline, the ranks of a tensor-parallel group see the same batch and each scores its own
+block of token rows.  The loss lives on the last stage and is broadcast to the
 pipeline group by an all-reduce, so every rank reports the same number.
 
 The reference reaches this through Megatron's ``get_forward_backward_func`` with
@@ -32,17 +34,19 @@ def _chunk_bucket_of(name: str) -> str:
 
 class PipelineTrainer:
     def __init__(self, model_cfg: GPTConfig, opt: OptimConfig, train: TrainConfig, device, mesh, virtual_stages: int = 1,
-                 freeze_base: bool = False):
+                 freeze_base: bool = False, tp=None):
         self.cfg, self.train_cfg = model_cfg, train
         self.device = torch.device(device)
         self.mesh = mesh
         self.S, self.r = mesh.size("pp"), mesh.index("pp")
         self.v = max(int(virtual_stages or 1), 1)
         self.pp_group, self.dp_group = mesh.group("pp"), mesh.group("dp")
+        # tensor + sequence parallel stages: the ranks of ``tp.group`` hold slices of one stage and a block of its token rows
+        self.tp = tp if (tp is not None and tp.world > 1) else None
         torch.manual_seed(train.seed + 1000 * self.r)       # replicas of a stage start from the same weights
         pp_ranks = mesh.ranks["pp"]
         if self.v == 1:
-            self.model = GPTStage(model_cfg, self.r, self.S, device=self.device)
+            self.model = GPTStage(model_cfg, self.r, self.S, device=self.device, tp=self.tp)
             prev, nxt = mesh.prev_next_stage()
             self.runner = PipelineRunner(self.model, prev, nxt)
             bucket_of = pp_bucket_of
@@ -50,7 +54,7 @@ class PipelineTrainer:
         else:
             if model_cfg.n_layers < self.S * self.v:
                 raise ValueError(f"{model_cfg.n_layers} layers cannot fill {self.S} x {self.v} virtual stages")
-            self.chunks = [GPTStage(model_cfg, c * self.S + self.r, self.S * self.v, device=self.device) for c in range(self.v)]
+            self.chunks = [GPTStage(model_cfg, c * self.S + self.r, self.S * self.v, device=self.device, tp=self.tp) for c in range(self.v)]
             self.model = nn.ModuleList(self.chunks)
             self.runner = InterleavedRunner(self.chunks, self.r, self.S, pp_ranks[(self.r - 1) % self.S],
                                             pp_ranks[(self.r + 1) % self.S])
@@ -58,7 +62,8 @@ class PipelineTrainer:
         if freeze_base:
             from ..models.lora import freeze_base as _freeze
             _freeze(self.model)
-        self.engine = ZeroEngine(self.model, opt, group=self.dp_group, comm="nccl", bucket_of=bucket_of, pp_group=self.pp_group)
+        self.engine = ZeroEngine(self.model, opt, group=self.dp_group, comm="nccl", bucket_of=bucket_of, pp_group=self.pp_group,
+                                 tp_group=self.tp.group if self.tp is not None else None)
         if train.local_batch % train.micro_batch:
             raise ValueError("local_batch must be a multiple of micro_batch")
         self.n_micro = train.local_batch // train.micro_batch
@@ -96,6 +101,8 @@ class PipelineTrainer:
         if total is not None:
             out += total.float() / self.n_micro
         dist.all_reduce(out, group=self.pp_group)
+        if self.tp is not None:
+            dist.all_reduce(out, group=self.tp.group)          # every rank of a stage scored its own token rows
         return out
 
     def _to_device(self, t: torch.Tensor, slot: int) -> torch.Tensor:
@@ -123,7 +130,8 @@ class PipelineTrainer:
         prev, nxt = pp_ranks[(self.r - 1) % self.S], pp_ranks[(self.r + 1) % self.S]
         for i in range(0, x_all.shape[0], mb):
             x, y = x_all[i:i + mb].contiguous(), y_all[i:i + mb].contiguous()
-            like = torch.empty((x.numel(), self.cfg.hidden), dtype=self.cfg.torch_dtype(), device=self.device)
+            tpw = self.tp.world if self.tp is not None else 1
+            like = torch.empty((x.numel() // tpw, self.cfg.hidden), dtype=self.cfg.torch_dtype(), device=self.device)
             for chunk in self.chunks:
                 act = None
                 if not chunk.first:
@@ -132,10 +140,14 @@ class PipelineTrainer:
                 out = chunk(act, x, y, n_valid=1)
                 if chunk.last:
                     acc[0] += out.double()
-                    acc[1] += (y != -100).sum().double()
+                    rows = y.numel() // tpw                      # this rank scored its own block of token rows
+                    mine = y.reshape(-1)[self.tp.rank * rows:(self.tp.rank + 1) * rows] if self.tp is not None else y
+                    acc[1] += (mine != -100).sum().double()
                 else:
                     dist.send(out.contiguous(), dst=nxt)
         dist.all_reduce(acc, group=self.pp_group)        # only the last stage contributed
+        if self.tp is not None:
+            dist.all_reduce(acc, group=self.tp.group)
         if dist.get_world_size(self.dp_group) > 1:
             dist.all_reduce(acc, group=self.dp_group)
         return acc

@@ -84,6 +84,36 @@ def test_hybrid_sharding_matches_plain_data_parallel_gloo():
     assert r.stdout.count("ok=True") == 4
 
 
+@pytest.mark.parametrize("virtual", [1, 2])
+def test_tensor_parallel_pipeline_stages_follow_the_unsplit_model_gloo(virtual):
+    """Tensor 2 x pipeline 2 on four ranks: loss, gradient norm and weights against the unsplit model, then the run loop."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+                        "--master-addr", "127.0.0.1", "--master-port", "29673",
+                        os.path.join(ROOT, "tests", "multi", "tp_pp_worker.py"), str(virtual)],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("ok=True") == 4
+
+
+def test_run_loop_over_tensor_x_pipeline_mesh_resumes_gloo(tmp_path):
+    """A run that stops after a checkpoint and resumes ends on the losses of the straight run (every rank owns its own
+    slices of its own stage: they travel with the rank's optimizer shard)."""
+    import json
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    for phase, want_rc in (("straight", 0), ("die", 42), ("resume", 0)):
+        r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+                            "--master-addr", "127.0.0.1", "--master-port", "29674",
+                            os.path.join(ROOT, "tests", "multi", "pp_loop_worker.py"), str(tmp_path), "2", "1", phase, "2"],
+                           env=env, capture_output=True, text=True, timeout=600)
+        assert (r.returncode == 0) == (want_rc == 0), r.stdout[-2000:] + r.stderr[-3000:]
+    straight = [json.loads((tmp_path / f"straight_rank{r}.json").read_text()) for r in range(4)]
+    resumed = [json.loads((tmp_path / f"resume_rank{r}.json").read_text()) for r in range(4)]
+    assert all(s["losses"] == straight[0]["losses"] for s in straight)        # one pipeline, one batch: one loss
+    for r in range(4):
+        assert max(abs(a - b) for a, b in zip(resumed[r]["losses"], straight[r]["losses"][3:])) < 1e-5
+
+
 @pytest.mark.parametrize("pp,virtual", [(2, 1), (2, 2)])
 def test_run_loop_over_pipeline_mesh_resumes_gloo(tmp_path, pp, virtual):
     import json
