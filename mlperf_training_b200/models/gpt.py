@@ -263,8 +263,9 @@ class Block(nn.Module):
     def _attention_cp(self, qkv, cos, sin, B, S):
         """Attention with the sequence sharded over ``self.cp = (group, mode)``: ``S`` is this rank's
         chunk and ``cos`` / ``sin`` its rows of the tables.  ``mode`` "allgather" gathers keys and
-        values of the earlier chunks, "ulysses" trades sequence shards for head shards."""
-        from ..parallel.context import context_parallel_attention, ulysses_attention
+        values of the earlier chunks, "ulysses" trades sequence shards for head shards, "ring" passes key / value
+        blocks round the ring over zig-zag chunks."""
+        from ..parallel.context import context_parallel_attention, ring_attention, ulysses_attention
         cfg = self.cfg
         group, mode = self.cp
         Hq, Hkv, D = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
@@ -275,6 +276,10 @@ class Block(nn.Module):
         window = cfg.layer_window(self.layer)
         if mode == "ulysses":
             a = ulysses_attention(q, k, v, group, causal=True, window=window)
+        elif mode == "ring":
+            if window:
+                raise NotImplementedError("ring attention does not carry a sliding window")
+            a = ring_attention(q, k, v, group)
         else:
             a = context_parallel_attention(q, k, v, group, window=window)
         return a.reshape(B * S, Hq * D)
@@ -375,7 +380,8 @@ class GPT(nn.Module):
 
     def set_context_parallel(self, group, mode: str = "allgather") -> None:
         """Shard the sequence over ``group``: ``forward`` then takes this rank's chunk ``[B, S / W]`` of
-        tokens and labels (chunk index = rank in the group) and returns the mean loss of that chunk;
+        tokens and labels (chunk index = rank in the group; with ``mode="ring"`` the two zig-zag chunks ``r`` and
+        ``2 W - 1 - r`` side by side) and returns the mean loss of that chunk;
         parameters are replicated over the group, so the optimizer's gradient reduction must span it
         (``context_parallel_size`` of the reference's Megatron model config,
         llama2_sft/primus/src/llama2_custom.py:396-505, llama2_sft/primus/conf/llama2_70b_lora_posttrain.yaml:22)."""
@@ -389,9 +395,10 @@ class GPT(nn.Module):
             raise NotImplementedError("context parallelism is not combined with tensor parallelism")
         if self.cfg.sink:
             raise NotImplementedError("context parallelism does not carry attention sink logits")
-        if mode not in ("allgather", "ulysses"):
+        if mode not in ("allgather", "ulysses", "ring"):
             raise ValueError(f"unknown context-parallel mode '{mode}'")
         self.cp = (group, dist.get_world_size(group), dist.get_rank(group))
+        self.cp_mode = mode
         for blk in self.blocks:
             blk.cp = (group, mode)
 
@@ -402,7 +409,12 @@ class GPT(nn.Module):
             _, W, r = self.cp
             if S * W > cos.shape[0]:
                 raise ValueError(f"sequence {S * W} longer than the configured {cos.shape[0]}")
-            cos, sin = cos[r * S:(r + 1) * S].contiguous(), sin[r * S:(r + 1) * S].contiguous()
+            if getattr(self, "cp_mode", "allgather") == "ring":
+                # zig-zag: this rank's tokens are chunks r and 2 W - 1 - r of the 2 W chunks of the sequence
+                from ..parallel.context import zigzag_chunk
+                cos, sin = zigzag_chunk(cos[:S * W], W, r, dim=0), zigzag_chunk(sin[:S * W], W, r, dim=0)
+            else:
+                cos, sin = cos[r * S:(r + 1) * S].contiguous(), sin[r * S:(r + 1) * S].contiguous()
         if S > cos.shape[0]:
             raise ValueError(f"sequence {S} longer than the configured {cos.shape[0]}")
         ids, tgt = tokens.reshape(-1), labels.reshape(-1)

@@ -12,8 +12,13 @@ reduce-scatter along the sequence.
 The reference exposes ``context_parallel_size`` (Megatron) and ``sp_size`` (FLUX, Ulysses-style) as
 knobs that are 1 in every shipped configuration
 (llama2_sft/primus/conf/llama2_70b_lora_posttrain.yaml:22; flux1/primus/conf/flux.1_schnell_t2i-pretrain.yaml:48;
-llama2_sft/primus/src/llama2_custom.py:393-397).  The work per rank grows with ``r`` (a zig-zag
-chunk assignment would balance it); correctness does not depend on the assignment.
+llama2_sft/primus/src/llama2_custom.py:393-397).  In this all-gather form the work per rank grows with ``r``.
+
+``ring_attention`` is the balanced form (Megatron's default ``cp_comm_type`` p2p): the sequence is cut into
+``2 W`` chunks and rank ``r`` holds chunks ``r`` and ``2 W - 1 - r`` (zig-zag), key / value blocks travel round
+the ring with point-to-point messages posted before the attention of the block in hand, the partial outputs
+are merged by their log-sum-exp, and every ring step costs every rank the same half block of work.  Memory
+stays at one visiting key / value block instead of the whole prefix.
 """
 from __future__ import annotations
 
@@ -83,6 +88,155 @@ def context_parallel_attention(q, k, v, group, *, scale: float | None = None, wi
         from ..ops.functional import attention
         return attention(q, k, v, causal=True, window=window, scale=scale)
     return ContextParallelAttentionFn.apply(q, k, v, group, scale, window)
+
+
+# --------------------------------------------------------------------------------------
+# Ring attention over zig-zag chunks
+# --------------------------------------------------------------------------------------
+def zigzag_chunk(t: torch.Tensor, world: int, rank: int, dim: int = 1) -> torch.Tensor:
+    """Chunks ``rank`` and ``2 * world - 1 - rank`` of the ``2 * world`` equal chunks of ``t`` along ``dim``."""
+    if t.shape[dim] % (2 * world):
+        raise ValueError(f"length {t.shape[dim]} does not divide into {2 * world} zig-zag chunks")
+    parts = t.chunk(2 * world, dim=dim)
+    return torch.cat([parts[rank], parts[2 * world - 1 - rank]], dim=dim).contiguous()
+
+
+def zigzag_unchunk(parts: list, dim: int = 1) -> torch.Tensor:
+    """Inverse of ``zigzag_chunk`` over the list of every rank's piece."""
+    W = len(parts)
+    halves = [p.chunk(2, dim=dim) for p in parts]
+    return torch.cat([halves[r][0] for r in range(W)] + [halves[W - 1 - r][1] for r in range(W)], dim=dim)
+
+
+def _block_bwd(dout, q, k, v, out, lse, scale, causal):
+    """Gradients of one (query block, key / value block) pair of an attention whose softmax is normalised by the
+    GLOBAL ``lse`` (and whose ``out`` is the merged output): ``P = exp(S - lse)``, ``dS = P (dP - rowsum(dO O))``.
+    Returns fp32 ``(dq, dk, dv)``."""
+    if q.is_cuda:
+        dq, dk, dv, _ = K.attention_bwd(dout.contiguous(), q.contiguous(), k.contiguous(), v.contiguous(), out.contiguous(),
+                                        lse.contiguous(), scale=scale, causal=causal)
+        return dq.float(), dk.float(), dv.float()
+    B, Sq, Hq, D = q.shape
+    Skv, Hkv = k.shape[1], k.shape[2]
+    g = Hq // Hkv
+    qf, do, of = q.float(), dout.float(), out.float()
+    kf, vf = k.float().repeat_interleave(g, dim=2), v.float().repeat_interleave(g, dim=2)
+    sc = torch.einsum("bqhd,bkhd->bhqk", qf, kf) * scale
+    if causal:
+        vis = torch.arange(Skv)[None, :] <= torch.arange(Sq)[:, None] + (Skv - Sq)
+        sc = sc.masked_fill(~vis, float("-inf"))
+    p = torch.exp(sc - lse[..., None])
+    delta = (do * of).sum(-1).transpose(1, 2)                                   # [B, Hq, Sq]
+    dv = torch.einsum("bhqk,bqhd->bkhd", p, do)
+    dp = torch.einsum("bqhd,bkhd->bhqk", do, vf)
+    ds = p * (dp - delta[..., None])
+    dq = torch.einsum("bhqk,bkhd->bqhd", ds, kf) * scale
+    dk = torch.einsum("bhqk,bqhd->bkhd", ds, qf) * scale
+    return dq, dk.view(B, Skv, Hkv, g, D).sum(3), dv.view(B, Skv, Hkv, g, D).sum(3)
+
+
+def _ring_exchange(send: list, recv_like: list, nxt: int, prv: int, group):
+    """Post the sends to the next rank and the receives from the previous one together; returns (requests, buffers)."""
+    ops, bufs = [], []
+    for t in send:
+        ops.append(dist.P2POp(dist.isend, t, nxt, group))
+    for t in recv_like:
+        b = torch.empty_like(t)
+        bufs.append(b)
+        ops.append(dist.P2POp(dist.irecv, b, prv, group))
+    return (dist.batch_isend_irecv(ops) if ops else []), bufs
+
+
+class RingAttentionFn(Function):
+    """Causal attention with ``q``, ``k``, ``v`` ``[B, 2 c, H, D]`` holding this rank's two zig-zag chunks.  At ring
+    step ``t`` the rank holds the keys / values of rank ``j = (r - t) mod W``: its own (``t = 0``: causal attention
+    over the local rows - the first chunk precedes the second), an earlier rank's (``j < r``: every query sees the
+    visitor's first chunk, nothing of its second) or a later rank's (``j > r``: only the queries of the second chunk
+    see the visitor, all of it)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, group, scale):
+        W, r = dist.get_world_size(group), dist.get_rank(group)
+        ranks = dist.get_process_group_ranks(group)
+        nxt, prv = ranks[(r + 1) % W], ranks[(r - 1) % W]
+        c = q.shape[1] // 2
+        q = q.contiguous()
+        kv = torch.stack([k, v]).contiguous()
+        out = lse = None
+        for t in range(W):
+            reqs, bufs = _ring_exchange([kv], [kv], nxt, prv, group) if t + 1 < W else ([], [])
+            j = (r - t) % W
+            if t == 0:
+                o, l = K.attention_fwd(q, kv[0], kv[1], scale=scale, causal=True)
+                out, lse = o.float(), l.clone()
+            else:
+                lo = 0 if j < r else c                                          # the query rows that see the visitor
+                kk, vv = (kv[0][:, :c], kv[1][:, :c]) if j < r else (kv[0], kv[1])
+                o, l = K.attention_fwd(q[:, lo:].contiguous(), kk.contiguous(), vv.contiguous(), scale=scale, causal=False)
+                new = torch.logaddexp(lse[:, :, lo:], l)
+                w_old = torch.exp(lse[:, :, lo:] - new).transpose(1, 2)[..., None]
+                w_new = torch.exp(l - new).transpose(1, 2)[..., None]
+                out[:, lo:] = out[:, lo:] * w_old + o.float() * w_new
+                lse[:, :, lo:] = new
+            for w in reqs:
+                w.wait()
+            if bufs:
+                kv = bufs[0]
+        out = out.to(q.dtype)
+        ctx.save_for_backward(q, k.contiguous(), v.contiguous(), out, lse)
+        ctx.cfg = (group, W, r, nxt, prv, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        group, W, r, nxt, prv, scale = ctx.cfg
+        c = q.shape[1] // 2
+        dout = dout.contiguous()
+        dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        kv = torch.stack([k, v]).contiguous()
+        dkv = torch.zeros(kv.shape, dtype=torch.float32, device=q.device)     # travels with the block it belongs to
+        for t in range(W):
+            reqs, bufs = _ring_exchange([kv], [kv], nxt, prv, group) if t + 1 < W else ([], [])
+            j = (r - t) % W
+            if t == 0:
+                a, b, d = _block_bwd(dout, q, kv[0], kv[1], out, lse, scale, True)
+                dq += a
+                dkv[0] += b
+                dkv[1] += d
+            elif j < r:
+                a, b, d = _block_bwd(dout, q, kv[0][:, :c], kv[1][:, :c], out, lse, scale, False)
+                dq += a
+                dkv[0][:, :c] += b
+                dkv[1][:, :c] += d
+            else:
+                a, b, d = _block_bwd(dout[:, c:], q[:, c:], kv[0], kv[1], out[:, c:], lse[:, :, c:], scale, False)
+                dq[:, c:] += a
+                dkv[0] += b
+                dkv[1] += d
+            for w in reqs:
+                w.wait()
+            # the gradient block follows its keys / values; after the last step it arrives at its owner
+            greqs, gbufs = _ring_exchange([dkv], [dkv], nxt, prv, group)
+            for w in greqs:
+                w.wait()
+            dkv = gbufs[0]
+            if bufs:
+                kv = bufs[0]
+        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None
+
+
+def ring_attention(q, k, v, group, *, scale: float | None = None) -> torch.Tensor:
+    """Causal attention over a sequence sharded across ``group`` in zig-zag order: ``q [B, S / W, Hq, D]`` and
+    ``k`` / ``v`` hold chunks ``r`` and ``2 W - 1 - r`` of the ``2 W`` chunks of the sequence (``zigzag_chunk``)."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    if group is None or dist.get_world_size(group) == 1:
+        from ..ops.functional import attention
+        return attention(q, k, v, causal=True, scale=scale)
+    if q.shape[1] % 2:
+        raise ValueError("ring attention needs an even number of rows per rank (two zig-zag chunks)")
+    return RingAttentionFn.apply(q, k, v, group, scale)
 
 
 # --------------------------------------------------------------------------------------

@@ -76,7 +76,7 @@ class RunConfig:
     pipeline_parallel: int = 1
     virtual_pipeline_parallel: int | None = None        # model chunks per pipeline rank (interleaved 1F1B)
     context_parallel: int = 1
-    context_parallel_mode: str = "allgather"            # "allgather" (keys / values of earlier chunks) | "ulysses" (head exchange)
+    context_parallel_mode: str = "allgather"            # "allgather" (keys / values of earlier chunks) | "ulysses" (head exchange) | "ring" (zig-zag chunks, p2p ring)
     tp_comm_overlap: str = "fused"                      # "fused": in-kernel all-gather / reduce-scatter; "nccl"
     comm: str = "nccl"                                  # optimizer-step collectives: "nccl" | "fused"
     zero_stage: int = 1                                 # 3: block matrices sharded too (gathered per block, parallel/zero3.py)

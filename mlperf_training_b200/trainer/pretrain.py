@@ -66,6 +66,7 @@ class PretrainTrainer:
         self.cp_group = cp_group if (cp_group is not None and dist.get_world_size(cp_group) > 1) else None
         self.cp_world = dist.get_world_size(self.cp_group) if self.cp_group is not None else 1
         self.cp_rank = dist.get_rank(self.cp_group) if self.cp_group is not None else 0
+        self.cp_mode = cp_mode
         if self.cp_group is not None:
             self.model.set_context_parallel(self.cp_group, cp_mode)
         self.dp_group = group
@@ -96,6 +97,9 @@ class PretrainTrainer:
         s = t.shape[1] // self.cp_world
         if t.shape[1] % self.cp_world:
             raise ValueError(f"sequence length {t.shape[1]} does not divide over {self.cp_world} context-parallel ranks")
+        if self.cp_mode == "ring":
+            from ..parallel.context import zigzag_chunk
+            return zigzag_chunk(t, self.cp_world, self.cp_rank, dim=1)
         return t[:, self.cp_rank * s:(self.cp_rank + 1) * s].contiguous()
 
     def _loss(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:

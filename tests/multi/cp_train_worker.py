@@ -20,7 +20,7 @@ def main():
     cfg = dict(n_layers=2, hidden=32, n_heads=4, n_kv_heads=2, head_dim=8, ffn_hidden=64, vocab_size=64, seq_len=32, dtype="fp32")
     opt = OptimConfig(lr=3e-3, weight_decay=0.01, clip_grad=1.0)
     ok = True
-    for mode, masked in (("allgather", False), ("ulysses", False), ("allgather", True)):
+    for mode, masked in (("allgather", False), ("ulysses", False), ("allgather", True), ("ring", False), ("ring", True)):
         tc = TrainConfig(micro_batch=1, local_batch=2, warmup_steps=0, seed=3)
         plain = PretrainTrainer(GPTConfig(**cfg), opt, tc, "cpu", group=solo)
         cp = PretrainTrainer(GPTConfig(**cfg), opt, tc, "cpu", group=dist.group.WORLD, cp_group=dist.group.WORLD, cp_mode=mode)
@@ -45,13 +45,17 @@ def main():
         ok &= abs(float(ea) - float(eb)) < 1e-5
     # the run loop over a context x data mesh
     from mlperf_training_b200.trainer.loop import run
-    out = run(dict(model=cfg, global_batch=2, micro_batch=1, train_iters=3, warmup_train_steps=1, context_parallel=world,
-                   eval_interval=3, eval_iters=1), device="cpu", stream=io.StringIO())
-    t = torch.tensor(out["losses"], dtype=torch.float64)
-    lo, hi = t.clone(), t.clone()
-    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
-    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
-    ok &= bool((hi - lo).abs().max() < 1e-9) and out["steps"] == 3 and out["eval_loss"] is not None
+    per_mode = []
+    for mode in ("allgather", "ring"):
+        out = run(dict(model=cfg, global_batch=2, micro_batch=1, train_iters=3, warmup_train_steps=1, context_parallel=world,
+                       context_parallel_mode=mode, eval_interval=3, eval_iters=1), device="cpu", stream=io.StringIO())
+        t = torch.tensor(out["losses"], dtype=torch.float64)
+        lo, hi = t.clone(), t.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        ok &= bool((hi - lo).abs().max() < 1e-9) and out["steps"] == 3 and out["eval_loss"] is not None
+        per_mode.append(t)
+    ok &= bool((per_mode[0] - per_mode[1]).abs().max() < 1e-5)          # the two forms train the same model
     print(f"RESULT rank {rank} ok={ok}", flush=True)
     dist.barrier()
     dist.destroy_process_group()

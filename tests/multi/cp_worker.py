@@ -1,5 +1,5 @@
 """Worker: context-parallel causal attention (sequence sharded over the ranks) equals attention
-over the whole sequence, forward and backward."""
+over the whole sequence, forward and backward.  argv: backend [ring]: with ``ring`` also the zig-zag ring form."""
 import os
 import sys
 
@@ -8,7 +8,8 @@ import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 from mlperf_training_b200.ops.functional import attention  # noqa: E402
-from mlperf_training_b200.parallel.context import context_parallel_attention, ulysses_attention  # noqa: E402
+from mlperf_training_b200.parallel.context import (context_parallel_attention, ring_attention, ulysses_attention,  # noqa: E402
+                                                   zigzag_chunk, zigzag_unchunk)
 
 
 def main():
@@ -59,6 +60,23 @@ def main():
                 ok &= err <= tol * max(1.0, b.float().abs().max().item())
                 if rank == 0:
                     print(f"ulysses causal={causal} {name}: {err:.3e}", flush=True)
+    if len(sys.argv) > 2 and sys.argv[2] == "ring":
+        qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+        ref = attention(qf, kf, vf, causal=True)
+        ref.backward(do)
+        ql, kl, vl = (zigzag_chunk(t, world, rank).requires_grad_(True) for t in (q, k, v))
+        out = ring_attention(ql, kl, vl, dist.group.WORLD)
+        out.backward(zigzag_chunk(do, world, rank))
+        tol = 3e-2 if gpu else 1e-5
+        for name, a, b in (("o", out, ref), ("dq", ql.grad, qf.grad), ("dk", kl.grad, kf.grad), ("dv", vl.grad, vf.grad)):
+            b = zigzag_chunk(b.detach(), world, rank)
+            err = (a.float() - b.float()).abs().max().item()
+            ok &= err <= tol * max(1.0, b.float().abs().max().item())
+            if rank == 0:
+                print(f"ring {name}: {err:.3e}", flush=True)
+        pieces = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(pieces, out.detach().contiguous())
+        ok &= bool((zigzag_unchunk(pieces) - ref.detach()).abs().max() <= tol)
     print(f"RESULT rank {rank} ok={ok}", flush=True)
     dist.barrier()
     dist.destroy_process_group()

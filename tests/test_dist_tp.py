@@ -68,7 +68,7 @@ def test_context_parallel_attention_gloo(world):
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                         "--master-addr", "127.0.0.1", "--master-port", "29658",
-                        os.path.join(ROOT, "tests", "multi", "cp_worker.py"), "gloo"],
+                        os.path.join(ROOT, "tests", "multi", "cp_worker.py"), "gloo", "ring"],
                        env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "RESULT rank 0 ok=True" in r.stdout
