@@ -14,7 +14,9 @@ The reference gets this schedule from Megatron's ``get_forward_backward_func``
 ``virtual_pipeline_model_parallel_size`` from the YAML (llama2_sft/primus/conf/llama2_70b_lora_posttrain.yaml:19-21);
 every shipped config sets the size to 1.  A stage may itself be tensor + sequence parallel (``tp``): its ranks
 then hold slices of the stage's matrices, each passes its own block of token rows to the same-index rank of
-the next stage, and the messages shrink by the group size.  ``InterleavedRunner`` is the virtual-stage variant (several
+the next stage, and the messages shrink by the group size.  With ``ep_group`` the experts of a stage's
+mixture-of-experts blocks are spread over the data-parallel replicas of the stage, which follow the same
+schedule and so meet in the same token exchanges.  ``InterleavedRunner`` is the virtual-stage variant (several
 model chunks per rank); ``trainer.pipeline_train.PipelineTrainer`` puts either schedule behind the
 trainer interface of the run loop.
 """
@@ -37,7 +39,7 @@ def stage_layers(n_layers: int, n_stages: int, stage: int) -> range:
 
 
 class GPTStage(nn.Module):
-    def __init__(self, cfg: GPTConfig, stage: int, n_stages: int, device="cpu", tp=None):
+    def __init__(self, cfg: GPTConfig, stage: int, n_stages: int, device="cpu", tp=None, ep_group=None):
         super().__init__()
         self.cfg, self.stage, self.n_stages = cfg, stage, n_stages
         self.first, self.last = stage == 0, stage == n_stages - 1
@@ -45,7 +47,7 @@ class GPTStage(nn.Module):
         dtype = cfg.torch_dtype()
         if self.first:
             self.embed = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden, dtype=dtype, device=device))
-        self.blocks = nn.ModuleList([Block(cfg, i, dtype, device, tp=tp) for i in self.layers])
+        self.blocks = nn.ModuleList([Block(cfg, i, dtype, device, tp=tp, ep_group=ep_group) for i in self.layers])
         if self.last:
             self.final_norm = nn.Parameter(torch.ones(cfg.hidden, dtype=dtype, device=device))
             self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden, dtype=dtype, device=device))
@@ -76,6 +78,10 @@ class GPTStage(nn.Module):
                 shard = getattr(p, "tensor_parallel", None)
                 if shard is not None and src[n].shape != p.shape:        # the unsplit model holds the whole matrix
                     p.copy_(shard_of(src[n], shard[0], shard[1], shard[2], self.cfg))
+                elif getattr(p, "expert_parallel", False) and src[n].shape != p.shape:
+                    ep, ep_rank = p.expert_shard                         # this rank's block of the stacked experts
+                    per = src[n].shape[0] // ep
+                    p.copy_(src[n][ep_rank * per:(ep_rank + 1) * per])
                 else:
                     p.copy_(src[n])
         if self.last:

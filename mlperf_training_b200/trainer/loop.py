@@ -220,20 +220,27 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     cp_group = ep_group = edp_group = None
     ep_size = min(int(rc.expert_parallel), world) if cfg.n_experts else 1
     if ep_size > 1:
-        if tp_size > 1 or pp_size > 1 or cp_size > 1 or replicate > 1 or world % ep_size or cfg.n_experts % ep_size:
-            raise NotImplementedError("expert parallelism combines with plain data parallelism here (tensor / pipeline / "
-                                      "context parallel = 1, dp_replicate = 1; world and experts divisible by expert_parallel)")
-        if ep_size == world:
+        if tp_size > 1 or cp_size > 1 or replicate > 1 or (world // pp_size) % ep_size or cfg.n_experts % ep_size:
+            raise NotImplementedError("expert parallelism combines with data and pipeline parallelism here (tensor / context "
+                                      "parallel = 1, dp_replicate = 1; data-parallel size and experts divisible by expert_parallel)")
+        if pp_size > 1:
+            # experts spread over (a block of) the data-parallel replicas of every pipeline stage
+            from ..parallel.mesh import Mesh, MeshSpec
+            mesh = Mesh(MeshSpec(pp=pp_size, ep=ep_size))
+            ep_group = mesh.group("ep")
+            edp_group = mesh.group("edp") if mesh.size("edp") > 1 else None
+        elif ep_size == world:
             ep_group = dist.group.WORLD
         else:
             from ..parallel.mesh import Mesh, MeshSpec
             ep_mesh = Mesh(MeshSpec(ep=ep_size))
             ep_group, edp_group = ep_mesh.group("ep"), ep_mesh.group("edp")
-        fused_ep = str(rc.moe_dispatch).lower() == "fused" and str(device).startswith("cuda")
+        fused_ep = str(rc.moe_dispatch).lower() == "fused" and str(device).startswith("cuda") and pp_size == 1
         cfg.ep_comm = "fused" if fused_ep else "nccl"
     if pp_size > 1 and tp_size == 1:
-        from ..parallel.mesh import Mesh, MeshSpec
-        mesh = Mesh(MeshSpec(pp=pp_size))
+        if ep_size == 1:
+            from ..parallel.mesh import Mesh, MeshSpec
+            mesh = Mesh(MeshSpec(pp=pp_size))
         dp_rank, dp_world = mesh.index("dp"), mesh.size("dp")
     elif cp_size > 1:
         from ..parallel.mesh import Mesh, MeshSpec
@@ -253,7 +260,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     if pp_size > 1:
         from .pipeline_train import PipelineTrainer
         trainer = PipelineTrainer(cfg, opt, tc, device, mesh, virtual_stages=rc.virtual_pipeline_parallel or 1,
-                                  freeze_base=cfg.lora_rank > 0, tp=tp_ctx)
+                                  freeze_base=cfg.lora_rank > 0, tp=tp_ctx, ep_group=ep_group, expert_dp_group=edp_group)
     else:
         trainer = PretrainTrainer(cfg, opt, tc, device, group=dp_group, ep_group=ep_group, tp=tp_ctx,
                                   freeze_base=cfg.lora_rank > 0, replicate_group=rep_group, cp_group=cp_group,

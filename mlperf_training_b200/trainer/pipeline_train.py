@@ -34,7 +34,7 @@ def _chunk_bucket_of(name: str) -> str:
 
 class PipelineTrainer:
     def __init__(self, model_cfg: GPTConfig, opt: OptimConfig, train: TrainConfig, device, mesh, virtual_stages: int = 1,
-                 freeze_base: bool = False, tp=None):
+                 freeze_base: bool = False, tp=None, ep_group=None, expert_dp_group=None):
         self.cfg, self.train_cfg = model_cfg, train
         self.device = torch.device(device)
         self.mesh = mesh
@@ -46,7 +46,7 @@ class PipelineTrainer:
         torch.manual_seed(train.seed + 1000 * self.r)       # replicas of a stage start from the same weights
         pp_ranks = mesh.ranks["pp"]
         if self.v == 1:
-            self.model = GPTStage(model_cfg, self.r, self.S, device=self.device, tp=self.tp)
+            self.model = GPTStage(model_cfg, self.r, self.S, device=self.device, tp=self.tp, ep_group=ep_group)
             prev, nxt = mesh.prev_next_stage()
             self.runner = PipelineRunner(self.model, prev, nxt)
             bucket_of = pp_bucket_of
@@ -54,7 +54,8 @@ class PipelineTrainer:
         else:
             if model_cfg.n_layers < self.S * self.v:
                 raise ValueError(f"{model_cfg.n_layers} layers cannot fill {self.S} x {self.v} virtual stages")
-            self.chunks = [GPTStage(model_cfg, c * self.S + self.r, self.S * self.v, device=self.device, tp=self.tp) for c in range(self.v)]
+            self.chunks = [GPTStage(model_cfg, c * self.S + self.r, self.S * self.v, device=self.device, tp=self.tp, ep_group=ep_group)
+                           for c in range(self.v)]
             self.model = nn.ModuleList(self.chunks)
             self.runner = InterleavedRunner(self.chunks, self.r, self.S, pp_ranks[(self.r - 1) % self.S],
                                             pp_ranks[(self.r + 1) % self.S])
@@ -63,7 +64,7 @@ class PipelineTrainer:
             from ..models.lora import freeze_base as _freeze
             _freeze(self.model)
         self.engine = ZeroEngine(self.model, opt, group=self.dp_group, comm="nccl", bucket_of=bucket_of, pp_group=self.pp_group,
-                                 tp_group=self.tp.group if self.tp is not None else None)
+                                 tp_group=self.tp.group if self.tp is not None else None, expert_dp_group=expert_dp_group)
         if train.local_batch % train.micro_batch:
             raise ValueError("local_batch must be a multiple of micro_batch")
         self.n_micro = train.local_batch // train.micro_batch

@@ -96,6 +96,18 @@ def test_tensor_parallel_pipeline_stages_follow_the_unsplit_model_gloo(virtual):
     assert r.stdout.count("ok=True") == 4
 
 
+def test_expert_parallel_pipeline_stages_follow_the_unsplit_model_gloo(tmp_path):
+    """Pipeline 2 x data 2 with the experts of every stage spread over its replicas: parity with the unsplit
+    mixture-of-experts model, then the run loop (straight, exit after a checkpoint, resume)."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+                        "--master-addr", "127.0.0.1", "--master-port", "29675",
+                        os.path.join(ROOT, "tests", "multi", "pp_ep_worker.py"), str(tmp_path)],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("ok=True") == 4
+
+
 def test_run_loop_over_tensor_x_pipeline_mesh_resumes_gloo(tmp_path):
     """A run that stops after a checkpoint and resumes ends on the losses of the straight run (every rank owns its own
     slices of its own stage: they travel with the rank's optimizer shard)."""
