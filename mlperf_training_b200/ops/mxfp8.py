@@ -48,9 +48,9 @@ class MXOperand:
         return self.q.is_cuda
 
 
-def _e8m0(amax: torch.Tensor) -> torch.Tensor:
-    """Biased exponent of the smallest power of two s with amax / s <= 448 (0 for amax == 0)."""
-    t = (amax.float() / 448.0)
+def _e8m0(amax: torch.Tensor, v_max: float = 448.0) -> torch.Tensor:
+    """Biased exponent of the smallest power of two s with amax / s <= v_max (448 for e4m3; 0 for amax == 0)."""
+    t = (amax.float() / v_max)
     bits = t.view(torch.int32)
     e = ((bits >> 23) & 0xff) - 127
     e = e + ((bits & 0x7fffff) != 0).to(torch.int32)
@@ -67,6 +67,44 @@ def _quant_rows_cpu(x: torch.Tensor):
     y = (xb * inv[..., None]).clamp(-448.0, 448.0)
     q = y.to(torch.float8_e4m3fn).view(torch.uint8).view(R, C)
     return q, sf
+
+
+# element formats of the micro-scaled family: (mantissa bits, smallest normal exponent, largest magnitude).  Every value
+# of the 4- and 6-bit formats is also an e4m3 value, so an operand rounded to one of them travels as e4m3 codes with the
+# same per-32 power-of-two scales and the block-scaled GEMM multiplies it exactly: the numerics of the narrow format at
+# the 8-bit operand rate.
+ELEMENT_FORMATS = {"e4m3": (3, -6, 448.0), "e3m2": (2, -2, 28.0), "e2m3": (3, 0, 7.5), "e2m1": (1, 0, 6.0)}
+
+
+def round_to_format(y: torch.Tensor, fmt: str, stochastic: bool = False) -> torch.Tensor:
+    """``y`` (fp32) rounded to the nearest value of ``fmt`` (ties to even; saturating), or rounded stochastically:
+    up with the probability of the distance to the lower neighbour, so that the expectation is ``y``."""
+    m_bits, e_min, v_max = ELEMENT_FORMATS[fmt]
+    a = y.abs().clamp(max=v_max)
+    _, ex = torch.frexp(a)                                   # a = m * 2^ex with m in [0.5, 1)
+    quantum = torch.exp2((ex - 1).clamp(min=e_min).float() - m_bits)
+    t = a / quantum
+    r = torch.floor(t + torch.rand_like(t)) if stochastic else torch.round(t)
+    return torch.copysign((r * quantum).clamp(max=v_max), y)
+
+
+def quantize_rows_narrow(x: torch.Tensor, fmt: str, tile_rows: int, stochastic: bool = False) -> MXOperand:
+    """Row-wise micro-scaled operand of ``x [R, C]`` with elements rounded to ``fmt`` (one power-of-two scale per 32
+    contraction elements, chosen so that the block's largest magnitude fits the format), stored as e4m3 codes.  Runs as
+    tensor operations on either device; on CUDA the scales go into the atom layout the GEMM reads."""
+    R, C = x.shape
+    if C % 32:
+        raise ValueError(f"quantize_rows_narrow: {C} columns are not a multiple of 32")
+    v_max = ELEMENT_FORMATS[fmt][2]
+    xb = x.float().view(R, C // 32, 32)
+    sf = _e8m0(xb.abs().amax(-1), v_max)
+    y = round_to_format(xb * torch.exp2(127.0 - sf.float())[..., None], fmt, stochastic)
+    q = y.to(torch.float8_e4m3fn).view(torch.uint8).view(R, C)
+    if x.is_cuda:
+        buf = torch.zeros(sf_bytes(R, C, tile_rows), dtype=torch.uint8, device=x.device)
+        buf[sf_index(R, C, tile_rows, x.device)] = sf
+        sf = buf
+    return MXOperand(q, sf, R, C, tile_rows)
 
 
 def sf_index(rows: int, k: int, tile_rows: int, device) -> torch.Tensor:
@@ -99,8 +137,10 @@ def dequantize(op: MXOperand) -> torch.Tensor:
     return (q * s[..., None]).view(op.rows, op.k)
 
 
-def quantize(x: torch.Tensor, *, row_tile: int | None = None, col_tile: int | None = None):
-    """bf16 ``x`` ``[R, C]`` -> ``(row_op, col_op)``.
+def quantize(x: torch.Tensor, *, row_tile: int | None = None, col_tile: int | None = None, fmt: str = "e4m3",
+             col_fmt: str | None = None, stochastic: bool = False):
+    """bf16 ``x`` ``[R, C]`` -> ``(row_op, col_op)``.  ``fmt`` / ``col_fmt`` (default: ``fmt``): element format of the
+    row-wise / column-wise copy; anything but round-to-nearest e4m3 goes through ``quantize_rows_narrow``.
 
     ``row_op`` (when ``row_tile`` is given) has rows = R, contraction = C; ``col_op`` (when
     ``col_tile`` is given) is the transposed copy with rows = C, contraction = R.  The tile
@@ -109,6 +149,11 @@ def quantize(x: torch.Tensor, *, row_tile: int | None = None, col_tile: int | No
     R, C = x.shape
     if R % 128 or C % 32:
         raise ValueError(f"mxfp8.quantize: shape {R}x{C}: rows must be a multiple of 128, columns of 32")
+    col_fmt = col_fmt or fmt
+    if stochastic or fmt != "e4m3" or col_fmt != "e4m3":
+        row_op = quantize_rows_narrow(x, fmt, row_tile, stochastic) if row_tile is not None else None
+        col_op = quantize_rows_narrow(x.t().contiguous(), col_fmt, col_tile, stochastic) if col_tile is not None else None
+        return row_op, col_op
     if not use_kernels(x):
         row_op = col_op = None
         if row_tile is not None:

@@ -10,32 +10,46 @@ The reference trains with micro-scaled low-precision linears and changes the rec
 * GPT-OSS / FLUX: weight de-oscillation for MXFP4 (start step 768, period 100, ratio 4.0;
   small_llm_moe_pretraining/primus/conf/gpt_oss_20B-MXFP4-deosc-mlperf-pretrain.yaml:197-204).
 
-This framework implements two low-precision recipes with different numerics:
+This framework implements two low-precision recipe families with different numerics:
 
-* ``mxfp8``  e4m3 codes with one UE8M0 scale per 32 contraction elements
-  (``tcgen05.mma.kind::mxf8f6f4.block_scale``; ``ops.mxfp8``) - the micro-scaled family; the
-  reference's 4- and 6-bit micro-scaled names (mxfp4, a6w4, ...) select it, as the widest member
-  this hardware path offers and the one the benchmark definition names;
+* the micro-scaled family - one UE8M0 scale per 32 contraction elements
+  (``tcgen05.mma.kind::mxf8f6f4.block_scale``; ``ops.mxfp8``, ``ops.linear.MX_RECIPES``): ``mxfp8`` (e4m3
+  elements, the width the benchmark definition names), ``mxfp6`` (e2m3 / e3m2), ``mxfp4`` (e2m1, stochastic
+  gradient rounding, Hadamard transform on the weight-gradient operands) and ``a6w4`` (MXFP6 activations x MXFP4
+  weights forward, MXFP4 backward).  The narrow members round their operands to the 6- / 4-bit element format
+  and carry them as e4m3 codes - every such value is an e4m3 value - so the GEMM result is the narrow
+  format's bit for bit, at the 8-bit operand rate (not the 4-bit rate);
 * ``fp8``    per-tensor e4m3 forward operands and e5m2 gradients with delayed scaling
   (``tcgen05.mma.kind::f8f6f4``; ``ops.fp8``) - what the reference calls fp8 / hybrid / delayed.
 
 ``PrecisionSchedule`` keeps the reference's surface - named phases with a switch step: switching a
 phase changes ``precision`` on the model's modules and drops the cached quantised weights, and
-because the two recipes round differently the losses after the switch differ from those of a run
-that did not switch.  De-oscillation is accepted, recorded, and reported as inactive with its
-reason: it repairs a 4-bit-weight artefact that e4m3 weights do not show.
+because the recipes round differently the losses after the switch differ from those of a run
+that did not switch.
+
+``Deoscillator`` is the weight de-oscillation of the 4-bit recipes: a weight whose master value sits near a
+rounding boundary of the coarse grid flips between two codes from step to step, which acts as noise on
+the forward pass.  Every step it compares each weight's quantised code with the previous step's; at the end of
+every ``period`` steps (from ``start_step`` on) a weight that flipped at least ``ratio`` times per grid
+step of net movement is declared oscillating and its master value is set to the grid value it currently
+rounds to (a direct quantise-dequantise of the master weight), which moves it to the centre of its
+rounding interval.  State (previous code, code at the period start, flip count) is kept per element of
+the rank's optimizer shard.
 """
 from __future__ import annotations
 
 import os
 from dataclasses import dataclass, field
 
+import torch
+
 from .linear import bump_weight_epoch
 
 # reference recipe names -> precision implemented here
 FORMAT_MAP = {
     "bf16": "bf16", "none": "bf16",
-    "mxfp8": "mxfp8", "mxfp4": "mxfp8", "e2m1": "mxfp8", "nvfp4": "mxfp8", "a6w4": "mxfp8", "mxfp6": "mxfp8",
+    "mxfp8": "mxfp8", "mxfp6": "mxfp6", "mxfp4": "mxfp4", "e2m1": "mxfp4", "nvfp4": "mxfp4", "a4w4": "mxfp4", "a6w4": "a6w4",
+    "mxfp8_fwd_mxfp4_bwd": "mxfp8_fwd_mxfp4_bwd", "fp8_fwd_mxfp4_bwd": "mxfp8_fwd_mxfp4_bwd",
     "fp8": "fp8", "fp8_hybrid": "fp8", "hybrid": "fp8", "e4m3": "fp8", "delayed": "fp8", "tensorwise": "fp8",
 }
 
@@ -57,8 +71,109 @@ class DeoscConfig:
     def status(self, precision: str) -> str:
         if not self.enabled:
             return "deosc: off"
-        return (f"deosc: requested (start {self.start_step}, period {self.period}, ratio {self.ratio}) - inactive: "
-                f"weights are {precision} (8-bit mantissa/exponent codes), the oscillation it damps is a 4-bit effect")
+        from .linear import MX_RECIPES
+        fmt = MX_RECIPES.get(precision, ("", "e4m3"))[1]
+        if fmt != "e2m1":
+            return (f"deosc: requested (start {self.start_step}, period {self.period}, ratio {self.ratio}) - idle: "
+                    f"weights are {precision} ({fmt} elements), the oscillation it damps is a 4-bit-weight effect")
+        return f"deosc: on (start {self.start_step}, period {self.period}, ratio {self.ratio})"
+
+
+class Deoscillator:
+    """Tracks code flips of the 4-bit-quantised weights of ``engine``'s parameters and snaps oscillating master
+    weights to their grid value (see the module docstring).  ``after_step(step, precision)`` is called once per
+    optimizer step; it does nothing unless the active recipe quantises weights to e2m1."""
+
+    def __init__(self, engine, cfg: DeoscConfig, fmt: str = "e2m1"):
+        self.engine, self.cfg, self.fmt = engine, cfg, fmt
+        self.state: dict = {}
+        self.snapped = 0                     # weights snapped so far (this rank's shards)
+        self.history: list = []              # (step, snapped at that period end)
+        self._grid = None
+
+    def _keys(self, b):
+        """Per element of this rank's shard of bucket ``b``: (tracked?, scale-and-code key, code, grid value)."""
+        from . import mxfp8 as MX
+        dev = b.param_buf.device
+        n = b.hi - b.lo
+        tracked = torch.zeros(n, dtype=torch.bool, device=dev)
+        key = torch.zeros(n, dtype=torch.int32, device=dev)
+        code = torch.zeros(n, dtype=torch.int32, device=dev)
+        value = torch.zeros(n, dtype=torch.float32, device=dev)
+        if self._grid is None or self._grid.device != dev:
+            pos = MX.round_to_format(torch.linspace(0.0, MX.ELEMENT_FORMATS[self.fmt][2], 4097), self.fmt).unique()
+            self._grid = torch.cat([-pos.flip(0)[:-1], pos]).to(dev)
+        v_max = MX.ELEMENT_FORMATS[self.fmt][2]
+        for (name, p), o in zip(b.params, b.offsets):
+            if p.dim() != 2 or p.shape[1] % 32 or getattr(p, "_mx_cache", None) is None:
+                continue                      # only matrices that a micro-scaled linear has quantised
+            lo, hi = max(o, b.lo), min(o + p.numel(), b.hi)
+            if lo >= hi:
+                continue
+            w = p.detach().float().view(p.shape[0], p.shape[1] // 32, 32)
+            sf = MX._e8m0(w.abs().amax(-1), v_max)
+            scale = torch.exp2(sf.float() - 127.0)[..., None]
+            r = MX.round_to_format(w / scale, self.fmt)
+            c = torch.bucketize(r, self._grid).to(torch.int32)
+            k = sf.to(torch.int32)[..., None] * 64 + c
+            sl = slice(lo - b.lo, hi - b.lo)
+            src = slice(lo - o, hi - o)
+            tracked[sl] = True
+            key[sl] = k.reshape(-1)[src]
+            code[sl] = c.reshape(-1)[src]
+            value[sl] = (r * scale).reshape(-1)[src]
+        return tracked, key, code, value
+
+    def after_step(self, step: int, precision: str) -> int:
+        """Returns the number of weights snapped at this step (non-zero only at a period end)."""
+        from .linear import MX_RECIPES
+        cfg = self.cfg
+        if not cfg.enabled or step < cfg.start_step or MX_RECIPES.get(precision, ("", ""))[1] != self.fmt:
+            return 0
+        period_end = (step - cfg.start_step + 1) % max(cfg.period, 1) == 0
+        n_snapped = 0
+        with torch.no_grad():
+            for b in self.engine.buckets:
+                tracked, key, code, value = self._keys(b)
+                if not bool(tracked.any()):
+                    continue
+                st = self.state.get(id(b))
+                if st is None:
+                    st = self.state[id(b)] = {"prev": key.clone(), "start_key": key.clone(), "start_code": code.clone(),
+                                              "flips": torch.zeros_like(key, dtype=torch.int16)}
+                else:
+                    st["flips"] += (key != st["prev"]).to(torch.int16)
+                    st["prev"] = key
+                if not period_end:
+                    continue
+                same_scale = (key // 64) == (st["start_key"] // 64)
+                moved = torch.where(same_scale, (code - st["start_code"]).abs(), torch.full_like(code, 64))
+                osc = tracked & (st["flips"].to(torch.float32) >= cfg.ratio * (1 + moved).to(torch.float32))
+                k = int(osc.sum())
+                if k:
+                    shard = b.p_shard()
+                    shard[osc] = value[osc].to(shard.dtype)
+                    if b.master is not None:
+                        b.master[osc] = value[osc]
+                n_snapped += k
+                st["start_key"], st["start_code"] = key.clone(), code.clone()
+                st["flips"].zero_()
+        if period_end:
+            # every rank's shard of every touched bucket goes back to all replicas (the call is collective: ranks
+            # agree on "touched" through the reduced count)
+            total = torch.tensor([n_snapped], dtype=torch.int64, device=self.engine.device)
+            if self.engine.world > 1:
+                import torch.distributed as dist
+                dist.all_reduce(total, group=self.engine.group)
+                if int(total) > 0:
+                    for b in self.engine.buckets:
+                        if id(b) in self.state and not getattr(b, "local_only", False):
+                            self.engine._all_gather(b)
+            if int(total) > 0:
+                bump_weight_epoch()
+            self.snapped += n_snapped
+            self.history.append((step, n_snapped))
+        return n_snapped
 
 
 @dataclass

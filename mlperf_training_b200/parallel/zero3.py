@@ -183,7 +183,7 @@ class Zero3Engine(ZeroEngine):
         for _, p in b.params:
             c = getattr(p, "_mx_cache", None)
             epoch = L._WEIGHT_EPOCH if p.requires_grad else -1
-            if c is None or c[0] != epoch or (need_col and c[2] is None):
+            if c is None or c[0][0] != epoch or (need_col and c[2] is None):      # key: (epoch, row format, column format)
                 return False
         return True
 

@@ -243,10 +243,22 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     losses, reached, last_eval = [], False, None
     next_eval = (start_step * gbs // eval_every + 1) * eval_every if eval_every else 0
     samples = start_step * gbs
+    # forward-precision switch (flux1/primus/patches/flux_fprop_switch.py:36-308): e.g. {"initial": "a6w4", "switch_step": N,
+    # "final": "mxfp8_fwd_mxfp4_bwd", "deosc": {...}}; FLUX_FPROP_SWITCH_STEP overrides the step
+    sched = deosc = None
+    if exp.get("precision_schedule"):
+        from ..ops.recipe import Deoscillator, PrecisionSchedule
+        sched = PrecisionSchedule.from_spec(exp["precision_schedule"])
+        if sched.deosc.enabled:
+            deosc = Deoscillator(tr.engine, sched.deosc)
     for step in range(start_step, iters):
+        if sched is not None and sched.apply(tr.model, step) and rank == 0:
+            print(f"[precision] step {step}: linears run in {sched.at(step)}; {sched.deosc.status(sched.at(step))}", flush=True)
         timer.step_start()
         losses.append(tr.train_step(data.batch(step, dp_rank, local_batch)))
         timer.step_stop()
+        if deosc is not None:
+            deosc.after_step(step, sched.at(step))
         samples = (step + 1) * gbs
         log.event(ml.TRAIN_LOSS, losses[-1], metadata={"samples_count": samples})
         if eval_every and samples >= next_eval:

@@ -331,6 +331,10 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     if rc.precision_schedule:
         from ..ops.recipe import PrecisionSchedule
         sched = PrecisionSchedule.from_spec(rc.precision_schedule)
+    deosc = None
+    if sched is not None and sched.deosc.enabled:
+        from ..ops.recipe import Deoscillator
+        deosc = Deoscillator(trainer.engine, sched.deosc)
     hb = None
     if rc.heartbeat_timeout_s > 0 and world > 1:
         from ..parallel.health import Heartbeat
@@ -382,6 +386,10 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         if torch.cuda.is_available() and str(device).startswith("cuda"):
             batch = tuple(t.pin_memory() for t in batch) if isinstance(batch, tuple) else batch.pin_memory()
         loss = trainer.train_step(batch)
+        if deosc is not None:
+            n_snap = deosc.after_step(step, sched.at(step))
+            if n_snap and rank == 0:
+                print(f"[deosc] step {step}: {n_snap} oscillating weights of this rank's shards set to their grid value", flush=True)
         step_s = timer.step_stop()
         losses.append(loss)
         if perf is not None:
@@ -464,4 +472,6 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         print("[alloc] " + growth.report(), flush=True)
     log.close()
     return {"steps": step + 1 - start_step, "losses": losses, "eval_loss": last_eval, "reached": reached,
-            "throughput": timer.throughput(), "records": log.lines, "trainer": trainer, "alloc_growth": growth.events}
+            "throughput": timer.throughput(), "records": log.lines, "trainer": trainer, "alloc_growth": growth.events,
+            "precision_log": list(sched.log) if sched is not None else [],
+            "deosc_history": list(deosc.history) if deosc is not None else []}

@@ -38,7 +38,7 @@ def test_fp8_linear_triple_is_close_to_bf16_and_differs_from_mxfp8():
     for a, b in zip(outs["fp8"], outs["bf16"]):
         assert (a - b).norm() / b.norm() < 0.08
     assert not torch.equal(outs["fp8"][0], outs["mxfp8"][0])      # two recipes, two roundings
-    assert resolve_format("fp8_hybrid") == "fp8" and resolve_format("a6w4") == "mxfp8"
+    assert resolve_format("fp8_hybrid") == "fp8" and resolve_format("a6w4") == "a6w4"
 
 
 def test_schedule_switch_changes_the_numbers():
@@ -61,4 +61,4 @@ def test_schedule_switch_changes_the_numbers():
         ys.append(m(x).float())
     assert torch.equal(ys[0], ys[1]) and torch.equal(ys[2], ys[3])
     assert not torch.equal(ys[1], ys[2])
-    assert sched.log == [(0, "mxfp8"), (2, "fp8")]
+    assert sched.log == [(0, "a6w4"), (2, "fp8")]

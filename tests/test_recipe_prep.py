@@ -10,7 +10,7 @@ from mlperf_training_b200.ops.recipe import PrecisionSchedule, resolve_format
 
 
 def test_precision_schedule_switch_and_mapping(monkeypatch):
-    assert resolve_format("A6W4") == "mxfp8" and resolve_format("bf16") == "bf16"
+    assert resolve_format("A6W4") == "a6w4" and resolve_format("nvfp4") == "mxfp4" and resolve_format("bf16") == "bf16"
     with pytest.raises(ValueError):
         resolve_format("int3")
 
@@ -27,7 +27,7 @@ def test_precision_schedule_switch_and_mapping(monkeypatch):
     assert not s.apply(m, 4)
     assert s.apply(m, 5) and m.precision == "fp8" and m.sub.precision == "fp8"
     assert s.log == [(0, "bf16"), (5, "fp8")]
-    assert "inactive" in s.deosc.status("mxfp8")
+    assert "idle" in s.deosc.status("mxfp8") and s.deosc.status("mxfp4").startswith("deosc: on")
     monkeypatch.setenv("FLUX_FPROP_SWITCH_STEP", "9")
     assert PrecisionSchedule.from_spec({"initial": "a6w4", "switch_step": 5, "final": "bf16"}).phases[1][0] == 9
 
