@@ -26,7 +26,8 @@ PAD_MX = 256     # ... for the block-scaled grouped kernels (one CTA pair works 
 
 def pad_rows(precision: str) -> int:
     """Segment padding the grouped kernels of ``precision`` need."""
-    return PAD_MX if precision == "mxfp8" else PAD
+    from .linear import is_mx
+    return PAD_MX if is_mx(precision) else PAD
 
 
 def grouped_bn(n: int) -> int:
@@ -273,18 +274,19 @@ class GroupedMLPFn(Function):
 # --------------------------------------------------------------------------------------
 # block-scaled (MXFP8) expert MLP
 # --------------------------------------------------------------------------------------
-def _stacked_weight_op(w: torch.Tensor, transposed: bool) -> mxfp8.MXOperand:
+def _stacked_weight_op(w: torch.Tensor, transposed: bool, fmt: str = "e4m3") -> mxfp8.MXOperand:
     """Quantised copy of the stacked expert weight ``w [E, N, K]`` (or of every expert's transpose) as one
-    K-major operand of ``E * N`` rows, scale tiles of ``grouped_bn(N)`` rows; cached until the weight changes."""
+    K-major operand of ``E * N`` rows, scale tiles of ``grouped_bn(N)`` rows, elements of format ``fmt``; cached until
+    the weight changes."""
     from .linear import weight_epoch
     key = "_mx_stack_t" if transposed else "_mx_stack"
     hit = getattr(w, key, None)
-    stamp = (w._version, weight_epoch())
+    stamp = (w._version, weight_epoch(), fmt)
     if hit is not None and hit[0] == stamp:
         return hit[1]
     src = w.detach().transpose(1, 2).contiguous() if transposed else w.detach()
     E, N, Kd = src.shape
-    op, _ = mxfp8.quantize(src.reshape(E * N, Kd), row_tile=grouped_bn(N))
+    op, _ = mxfp8.quantize(src.reshape(E * N, Kd), row_tile=grouped_bn(N), fmt=fmt)
     setattr(w, key, (stamp, op))
     return op
 
@@ -331,36 +333,65 @@ class GroupedMLPMXFn(Function):
     per optimizer step.  Expert segments start at multiples of 256 rows."""
 
     @staticmethod
-    def forward(ctx, x, w1, w2, seg, tile_expert, y_out=None, dx_out=None):
+    def forward(ctx, x, w1, w2, seg, tile_expert, y_out=None, dx_out=None, recipe="mxfp8"):
+        from .linear import MX_RECIPES
         E, F2, D = w1.shape
         F = F2 // 2
-        x_row, x_col = mxfp8.quantize(x, row_tile=mxfp8.A_TILE, col_tile=grouped_bn(D))
+        f_act, f_w, _, _, b_act, _, _ = MX_RECIPES[recipe]
+        narrow = recipe != "mxfp8"
+        if narrow:
+            x = _zero_padding_mx(x, tile_expert)
+        x_row, x_col = mxfp8.quantize(x, row_tile=mxfp8.A_TILE, col_tile=grouped_bn(D), fmt=f_act, col_fmt=b_act)
         # rows of tiles past the last segment are never written and never contribute: the row GEMMs skip those
         # tiles and the weight-gradient contraction stops at the last segment's end
-        gu = grouped_rows_mx(x_row, _stacked_weight_op(w1, False), tile_expert, E)
-        a_row, a_col = mxfp8.quantize_swiglu(gu, row_tile=mxfp8.A_TILE, col_tile=grouped_bn(F))
-        y = grouped_rows_mx(a_row, _stacked_weight_op(w2, False), tile_expert, E, out=y_out)
+        gu = grouped_rows_mx(x_row, _stacked_weight_op(w1, False, f_w), tile_expert, E)
+        if narrow:            # the fused SwiGLU quantiser writes e4m3 elements: the narrow formats round a materialised activation
+            a_row, a_col = mxfp8.quantize(_zero_padding_mx(K.swiglu_fwd(gu), tile_expert), row_tile=mxfp8.A_TILE,
+                                          col_tile=grouped_bn(F), fmt=f_act, col_fmt=b_act)
+        else:
+            a_row, a_col = mxfp8.quantize_swiglu(gu, row_tile=mxfp8.A_TILE, col_tile=grouped_bn(F))
+        y = grouped_rows_mx(a_row, _stacked_weight_op(w2, False, f_w), tile_expert, E, out=y_out)
         ctx.save_for_backward(gu, w1, w2, seg, tile_expert, x_col.q, x_col.sf, a_col.q, a_col.sf)
         ctx.refs = (w1, w2)
         ctx.dx_out = dx_out
         ctx.dims = (x.shape[0], D, F)
+        ctx.recipe = recipe
         return y
 
     @staticmethod
     def backward(ctx, gy):
+        from .linear import MX_RECIPES
         gu, w1, w2, seg, tile_expert, xq, xsf, aq, asf = ctx.saved_tensors
         p1, p2 = ctx.refs
         rows, D, F = ctx.dims
         E = w1.shape[0]
+        _, _, g_fmt, b_w, _, g_sr, _ = MX_RECIPES[ctx.recipe]
+        narrow = ctx.recipe != "mxfp8"
         x_col = mxfp8.MXOperand(xq, xsf, D, rows, grouped_bn(D))
         a_col = mxfp8.MXOperand(aq, asf, F, rows, grouped_bn(F))
-        gy_row, gy_col = mxfp8.quantize(gy.contiguous(), row_tile=mxfp8.A_TILE, col_tile=mxfp8.A_TILE)
+        gy = gy.contiguous()
+        if narrow:
+            gy = _zero_padding_mx(gy, tile_expert)
+        gy_row, gy_col = mxfp8.quantize(gy, row_tile=mxfp8.A_TILE, col_tile=mxfp8.A_TILE, fmt=g_fmt, stochastic=g_sr)
         g2 = _wgrad_into_mx(p2, gy_col, a_col, seg, E)
-        da = grouped_rows_mx(gy_row, _stacked_weight_op(w2, True), tile_expert, E)
-        dgu_row, dgu_col = mxfp8.quantize_swiglu_bwd(da, gu, row_tile=mxfp8.A_TILE, col_tile=mxfp8.A_TILE)
+        da = grouped_rows_mx(gy_row, _stacked_weight_op(w2, True, b_w), tile_expert, E)
+        if narrow:
+            dgu_row, dgu_col = mxfp8.quantize(_zero_padding_mx(K.swiglu_bwd(da, gu), tile_expert), row_tile=mxfp8.A_TILE,
+                                              col_tile=mxfp8.A_TILE, fmt=g_fmt, stochastic=g_sr)
+        else:
+            dgu_row, dgu_col = mxfp8.quantize_swiglu_bwd(da, gu, row_tile=mxfp8.A_TILE, col_tile=mxfp8.A_TILE)
         g1 = _wgrad_into_mx(p1, dgu_col, x_col, seg, E)
-        dx = grouped_rows_mx(dgu_row, _stacked_weight_op(w1, True), tile_expert, E, out=ctx.dx_out)
-        return dx, g1, g2, None, None, None, None
+        dx = grouped_rows_mx(dgu_row, _stacked_weight_op(w1, True, b_w), tile_expert, E, out=ctx.dx_out)
+        return dx, g1, g2, None, None, None, None, None
+
+
+def _zero_padding_mx(t: torch.Tensor, tile_expert: torch.Tensor) -> torch.Tensor:
+    """Rows of 256-row tiles without an expert are never written by the grouped GEMM and may hold anything (NaN
+    included); the tensor-operation quantiser of the narrow formats reads whole 32-row blocks, so clear them first."""
+    dead = (tile_expert < 0).repeat_interleave(PAD_MX)
+    if dead.numel() != t.shape[0]:
+        return t
+    return t.masked_fill(dead[:, None], 0)
 
 
 def _wgrad_into_mx(param, dy_t, x_t, seg, E):
@@ -378,8 +409,9 @@ def grouped_mlp(x, w1, w2, seg, tile_expert, precision: str = "bf16", y_out=None
     """Expert MLP over a padded row buffer whose segments are padded to ``pad_rows(precision)``.  ``y_out`` /
     ``dx_out``: buffers of the row buffer's shape that receive the output / the input gradient (peer-visible slabs
     of the expert-parallel dispatch, filled by the last GEMM of each direction instead of by a copy)."""
-    if precision == "mxfp8":
-        return GroupedMLPMXFn.apply(x, w1, w2, seg, tile_expert, y_out, dx_out)
+    from .linear import is_mx
+    if is_mx(precision):
+        return GroupedMLPMXFn.apply(x, w1, w2, seg, tile_expert, y_out, dx_out, precision)
     return GroupedMLPFn.apply(x, w1, w2, seg, tile_expert, y_out, dx_out)
 
 
@@ -407,9 +439,11 @@ def _wgrad_into(param, dy, x, seg, E):
 
 
 def expert_precision(precision: str, w1, w2) -> str:
-    """Precision the expert GEMMs run at: ``mxfp8`` when asked for and the widths fit its tiles, else bf16."""
-    if precision == "mxfp8" and w1.dtype == torch.bfloat16 and mx_supported(w1, w2):
-        return "mxfp8"
+    """Precision the expert GEMMs run at: the micro-scaled recipe asked for when the widths fit the block-scaled
+    grouped tiles, else bf16."""
+    from .linear import is_mx
+    if is_mx(precision) and w1.dtype == torch.bfloat16 and mx_supported(w1, w2):
+        return precision
     return "bf16"
 
 

@@ -105,12 +105,14 @@ class Deoscillator:
             self._grid = torch.cat([-pos.flip(0)[:-1], pos]).to(dev)
         v_max = MX.ELEMENT_FORMATS[self.fmt][2]
         for (name, p), o in zip(b.params, b.offsets):
-            if p.dim() != 2 or p.shape[1] % 32 or getattr(p, "_mx_cache", None) is None:
-                continue                      # only matrices that a micro-scaled linear has quantised
+            # only matrices that a micro-scaled linear, or stacks of them that the grouped expert MLP, has quantised
+            seen = getattr(p, "_mx_cache", None) is not None if p.dim() == 2 else getattr(p, "_mx_stack", None) is not None
+            if p.dim() not in (2, 3) or p.shape[-1] % 32 or not seen:
+                continue
             lo, hi = max(o, b.lo), min(o + p.numel(), b.hi)
             if lo >= hi:
                 continue
-            w = p.detach().float().view(p.shape[0], p.shape[1] // 32, 32)
+            w = p.detach().float().reshape(-1, p.shape[-1] // 32, 32)
             sf = MX._e8m0(w.abs().amax(-1), v_max)
             scale = torch.exp2(sf.float() - 127.0)[..., None]
             r = MX.round_to_format(w / scale, self.fmt)

@@ -133,3 +133,29 @@ def test_run_loop_switches_recipes_and_deoscillates():
     assert [s for s, _ in sw["deosc_history"]] == [1]                  # one full period (steps 0-1) under 4-bit weights, then idle
     assert all(l == l for l in sw["losses"]) and abs(sw["losses"][0] - plain["losses"][0]) > 1e-4
     assert abs(sw["losses"][0] - plain["losses"][0]) < 0.2             # 4-bit forward: close, not equal
+
+
+def test_deoscillator_tracks_stacked_expert_weights():
+    from mlperf_training_b200.ops import moe_ops as M
+
+    class Experts(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w1 = torch.nn.Parameter((torch.randn(2, 384, 192) * 0.05).bfloat16())
+            self.w2 = torch.nn.Parameter((torch.randn(2, 192, 192) * 0.05).bfloat16())
+    torch.manual_seed(0)
+    m = Experts()
+    eng = ZeroEngine(m, OptimConfig(lr=1e-3, weight_decay=0.0, clip_grad=0.0))
+    x = torch.randn(64, 192).bfloat16()
+    idx, w, counts = M.router_topk(torch.randn(64, 2), 1)
+    M.moe_experts(x, idx, w, counts, m.w1, m.w2, "mxfp4")              # the grouped MLP has quantised the stacks
+    de = Deoscillator(eng, DeoscConfig(enabled=True, start_step=0, period=6, ratio=2.0))
+    with torch.no_grad():
+        m.w1[1, 5, :32] = 0.1
+        m.w1[1, 5, 0] = 6.0
+    for step in range(6):
+        with torch.no_grad():
+            m.w1[1, 5, 3] = 1.27 if step % 2 == 0 else 1.23
+        n = de.after_step(step, "mxfp4")
+    assert n == 1 and float(m.w1[1, 5, 3]) in (1.0, 1.5)
+    assert eng.buckets[0].master is None or float(eng.buckets[0].master.max()) <= 6.0

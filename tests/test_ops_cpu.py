@@ -231,6 +231,14 @@ def test_grouped_mlp_block_scaled_emulation_close_to_bf16():
         y.float().square().sum().backward()
         return y.detach().float(), xx.grad.float(), w1.grad.float().clone(), w2.grad.float().clone()
 
-    for u, v in zip(run("bf16"), run("mxfp8")):
+    ref = run("bf16")
+    for u, v in zip(ref, run("mxfp8")):
         assert ((u - v).norm() / u.norm()).item() < 0.12
     assert w1.grad[2].abs().max() == 0
+    # the narrower micro-scaled recipes run the same grouped path on operands rounded to their element grids
+    assert M.expert_precision("mxfp4", w1, w2) == "mxfp4" and M.pad_rows("a6w4") == M.PAD_MX
+    e8 = [((u - v).norm() / u.norm()).item() for u, v in zip(ref, run("mxfp8"))]
+    e6 = [((u - v).norm() / u.norm()).item() for u, v in zip(ref, run("mxfp6"))]
+    e4 = [((u - v).norm() / u.norm()).item() for u, v in zip(ref, run("mxfp4"))]
+    assert all(a < b * 1.3 for a, b in zip(e8, e6)) and all(a < b for a, b in zip(e6, e4)) and max(e4) < 0.6
+    assert w1.grad[2].abs().max() == 0 and w1._mx_stack[0][2] == "e2m1"
