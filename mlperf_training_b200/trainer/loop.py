@@ -80,6 +80,10 @@ class RunConfig:
     tp_comm_overlap: str = "fused"                      # "fused": in-kernel all-gather / reduce-scatter; "nccl"
     comm: str = "nccl"                                  # optimizer-step collectives: "nccl" | "fused"
     zero_stage: int = 1                                 # 3: block matrices sharded too (gathered per block, parallel/zero3.py)
+    # no loss at the positions whose input token is the end-of-document token (Megatron's ``eod_mask_loss``,
+    # small_llm_moe_pretraining/primus/conf/gpt_oss_20B-MXFP4-deosc-mlperf-pretrain.yaml:86; off for Llama-3.1-8B)
+    eod_mask_loss: bool = False
+    eod_token: int = 128001                              # <|end_of_text|> of the Llama-3 tokenizer
     precision_schedule: dict | str | None = None        # ops.recipe.PrecisionSchedule spec (phase switch at a step)
     vanish_at_step: int = 0                             # fault injection: rank ``vanish_rank`` leaves silently before this step
     vanish_rank: int = 1
@@ -121,6 +125,18 @@ def build_data(spec: dict, cfg: GPTConfig, seed: int):
     if kind == "packed_sft":
         return PackedSFTDataset(spec["path"], cfg.seq_len, spec.get("metadata"))
     raise ValueError(f"unknown data kind '{kind}'")
+
+
+def eod_masked(batch, eod_token: int):
+    """``(inputs, labels)`` with label -100 wherever the input token is ``eod_token``: the prediction that follows an
+    end-of-document token belongs to the next document and carries no loss.  ``batch``: token rows ``[b, S + 1]`` or an
+    ``(inputs, labels)`` pair."""
+    if isinstance(batch, (tuple, list)):
+        x, y = batch[0], batch[1].clone()
+    else:
+        x, y = batch[:, :-1].contiguous(), batch[:, 1:].clone()
+    y[x == eod_token] = -100
+    return x, y
 
 
 def eval_spec(rc: "RunConfig") -> dict:
@@ -278,6 +294,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         b = ds.batch(i, dp_rank, dp_world, local_batch)
         if not isinstance(b, (tuple, list)) and getattr(ds, "loss_last", 0) > 0:
             b = (b[:, :-1].contiguous(), ds.labels(b))
+        if rc.eod_mask_loss:
+            b = eod_masked(b, int(rc.eod_token))
         return b
 
     # pipeline stages, expert shards and tensor-parallel slices differ per rank: those parameters travel

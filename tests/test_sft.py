@@ -65,3 +65,23 @@ modules:
                        timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert "run_stop" in r.stdout and "train_loss" in r.stdout
+
+
+def test_eod_mask_loss_drops_positions_after_document_ends():
+    """``eod_mask_loss``: the label is -100 wherever the input token is the end-of-document token; the run loop's loss
+    is then the mean over the remaining positions."""
+    import io
+
+    import torch
+
+    from mlperf_training_b200.trainer.loop import eod_masked, run
+    tok = torch.tensor([[5, 9, 2, 7, 9, 9, 1]])
+    x, y = eod_masked(tok, 9)
+    assert x.tolist() == [[5, 9, 2, 7, 9, 9]] and y.tolist() == [[9, -100, 7, 9, -100, -100]]
+    x2, y2 = eod_masked((tok[:, :-1], torch.tensor([[-100, -100, 7, 9, 9, 1]])), 9)      # explicit labels keep their own mask
+    assert y2.tolist() == [[-100, -100, 7, 9, -100, -100]]
+    tiny = dict(n_layers=2, hidden=32, n_heads=2, n_kv_heads=1, head_dim=16, ffn_hidden=64, vocab_size=8, seq_len=32, dtype="fp32")
+    base = dict(model=tiny, global_batch=2, micro_batch=1, train_iters=2, lr=1e-3, lr_warmup_iters=1)
+    a = run(dict(base), device="cpu", stream=io.StringIO())
+    b = run(dict(base, eod_mask_loss=1, eod_token=3), device="cpu", stream=io.StringIO())
+    assert a["losses"][0] != b["losses"][0] and abs(a["losses"][0] - b["losses"][0]) < 0.2   # an eighth of the positions left out
