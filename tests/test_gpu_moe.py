@@ -135,3 +135,36 @@ def test_moe_model_step_matches_cpu():
         if rel > (0.4 if n.endswith('router') else 0.15):   # top-k ties flip between fp32 and bf16 activations
             bad.append((n, rel))
     assert not bad, bad
+
+
+@pytest.mark.parametrize("recipe", ["mxfp6", "mxfp4"])
+def test_grouped_mlp_narrow_recipes(recipe):
+    """The grouped expert MLP on operands rounded to 6- / 4-bit element grids (carried as e4m3 codes), forward and all
+    three gradients against the bf16 grouped path, with an empty expert."""
+    from mlperf_training_b200.ops import _lib
+    from mlperf_training_b200.ops import moe_ops as M
+    torch.manual_seed(0)
+    T, k, E, D, F = 300, 2, 4, 384, 384
+    x = torch.randn(T, D, device="cuda").bfloat16()
+    logits = torch.randn(T, E, device="cuda")
+    logits[:, 2] -= 100.0
+    w1 = (torch.randn(E, 2 * F, D, device="cuda") * 0.05).bfloat16().requires_grad_()
+    w2 = (torch.randn(E, D, F, device="cuda") * 0.05).bfloat16().requires_grad_()
+    idx, w, counts = M.router_topk(logits, k)
+    assert M.expert_precision(recipe, w1, w2) == recipe
+
+    def run(prec):
+        xx = x.clone().requires_grad_()
+        w1.grad = w2.grad = None
+        y = M.moe_experts(xx, idx, w, counts, w1, w2, prec)
+        y.float().square().sum().backward()
+        return y.detach().float(), xx.grad.float(), w1.grad.float().clone(), w2.grad.float().clone()
+
+    ref = run("bf16")
+    got = run(recipe)
+    torch.cuda.synchronize()
+    _lib.check_status("narrow grouped mlp")
+    limit = 0.2 if recipe == "mxfp6" else 0.6
+    for u, v in zip(ref, got):
+        assert torch.isfinite(v).all() and ((u - v).norm() / u.norm()).item() < limit
+    assert got[2][2].abs().max() == 0

@@ -120,3 +120,42 @@ def test_fused_mlp_matches_unfused_mxfp8_path():
             assert (a - b).abs().max().item() <= 2.0 ** -6 * max(1.0, b.abs().max().item()), name
         else:
             assert torch.equal(a, b), (name, (a - b).abs().max().item())
+
+
+@pytest.mark.parametrize("fmt", ["e2m1", "e2m3", "e3m2"])
+def test_narrow_element_formats_match_the_cpu_oracle(fmt):
+    """Operands rounded to a 4- / 6-bit element grid and carried as e4m3 codes: the same codes and scales as the CPU
+    routine, and the block-scaled GEMM multiplies them like the dequantised matrices."""
+    torch.manual_seed(0)
+    x = (torch.randn(256, 384) * torch.logspace(-2, 1, 384)[None, :]).bfloat16()
+    w = (torch.randn(256, 384) * 0.05).bfloat16()
+    a_c = mxfp8.quantize(x, row_tile=mxfp8.A_TILE, fmt=fmt)[0]
+    a_g = mxfp8.quantize(x.cuda(), row_tile=mxfp8.A_TILE, fmt=fmt)[0]
+    assert torch.equal(a_g.q.cpu(), a_c.q) and torch.equal(mxfp8.sf_plain(a_g).cpu(), a_c.sf)
+    bt = mxfp8.b_tile(256)
+    b_c = mxfp8.quantize(w, row_tile=bt, fmt=fmt)[0]
+    b_g = mxfp8.quantize(w.cuda(), row_tile=bt, fmt=fmt)[0]
+    y_g = mxfp8.gemm(a_g, b_g, out_dtype=torch.float32)
+    y_c = mxfp8.gemm(a_c, b_c, out_dtype=torch.float32)
+    assert (y_g.cpu() - y_c).abs().max() <= 1e-3 * y_c.abs().max()
+    _, col_g = mxfp8.quantize(x.cuda(), col_tile=bt, fmt="e4m3", col_fmt=fmt)
+    _, col_c = mxfp8.quantize(x, col_tile=bt, fmt="e4m3", col_fmt=fmt)
+    assert torch.equal(col_g.q.cpu(), col_c.q) and torch.equal(mxfp8.sf_plain(col_g).cpu(), col_c.sf)
+
+
+@pytest.mark.parametrize("recipe", ["mxfp4", "a6w4"])
+def test_narrow_recipes_through_the_linear_triple(recipe):
+    from mlperf_training_b200.ops import functional as F
+    torch.manual_seed(1)
+    x = torch.randn(256, 256).bfloat16()
+    w = (torch.randn(384, 256) * 0.05).bfloat16()
+    g = torch.randn(256, 384).bfloat16()
+    y_c = F.linear(x, w, None, None, recipe)
+    xg, wg = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+    y_g = F.linear(xg, wg, None, None, recipe)
+    assert (y_g.float().cpu() - y_c.float()).abs().max() <= 2e-2 * y_c.float().abs().max()      # same operands, bf16 output
+    y_g.backward(g.cuda())
+    ref_dx, ref_dw = g.float() @ w.float(), g.float().t() @ x.float()
+    rel = lambda a, b: float((a.float().cpu() - b).norm() / b.norm())
+    assert rel(xg.grad, ref_dx) < 0.3 and rel(wg.grad, ref_dw) < 0.3        # stochastic 4-bit gradients: close, not equal
+    _lib.check_status("narrow recipes")
