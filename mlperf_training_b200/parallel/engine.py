@@ -49,6 +49,10 @@ class OptimConfig:
     clip_grad: float = 1.0           # 0 disables clipping
     grad_dtype: torch.dtype = torch.float32
     master_weights: bool = False      # keep an fp32 master copy of the local shard
+    # dtype the gradients cross the wire in (library-collective path): None = as accumulated (fp32); torch.bfloat16 is
+    # Megatron's ``grad_reduce_in_bf16`` (small_llm_pretraining/primus/conf/llama3.1_8B-pretrain-fp4.yaml:110-111):
+    # accumulate in fp32 locally, round once, reduce-scatter half the bytes, keep the result in the fp32 shard
+    reduce_dtype: torch.dtype | None = None
     moment_dtype: torch.dtype = torch.float32   # torch.bfloat16 halves the Adam state (Megatron's precision-aware
     #                                             optimizer, exp_avg_dtype / exp_avg_sq_dtype in
     #                                             small_llm_moe_pretraining/primus/conf/gpt_oss_20B-MXFP4-deosc-mlperf-pretrain.yaml:79)
@@ -242,7 +246,17 @@ class ZeroEngine:
                 dist.all_reduce(b.grad_buf, group=self.edp_group)
             b.grad_buf.mul_(1.0 / self.world)
             return
-        if dist.get_backend(self.group) == "gloo":
+        wire = self.opt.reduce_dtype
+        if wire is not None and wire != b.grad_buf.dtype:
+            low = b.grad_buf.to(wire)
+            if dist.get_backend(self.group) == "gloo":
+                dist.all_reduce(low, group=self.group)
+                b.g_shard().copy_(low[b.lo:b.hi].float().div_(self.world))
+            else:
+                out = torch.empty(b.hi - b.lo, dtype=wire, device=low.device)
+                dist.reduce_scatter_tensor(out, low, op=dist.ReduceOp.AVG, group=self.group)
+                b.g_shard().copy_(out)
+        elif dist.get_backend(self.group) == "gloo":
             dist.all_reduce(b.grad_buf, group=self.group)
             b.grad_buf.div_(self.world)
         else:

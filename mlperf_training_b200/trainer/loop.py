@@ -82,6 +82,7 @@ class RunConfig:
     zero_stage: int = 1                                 # 3: block matrices sharded too (gathered per block, parallel/zero3.py)
     # no loss at the positions whose input token is the end-of-document token (Megatron's ``eod_mask_loss``,
     # small_llm_moe_pretraining/primus/conf/gpt_oss_20B-MXFP4-deosc-mlperf-pretrain.yaml:86; off for Llama-3.1-8B)
+    grad_reduce_in_bf16: bool = False                   # gradients cross the wire in bf16 (library-collective engine)
     eod_mask_loss: bool = False
     eod_token: int = 128001                              # <|end_of_text|> of the Llama-3 tokenizer
     precision_schedule: dict | str | None = None        # ops.recipe.PrecisionSchedule spec (phase switch at a step)
@@ -267,7 +268,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         raise ValueError("global_batch must be divisible by the data-parallel size")
     local_batch = rc.global_batch // dp_world
     opt = OptimConfig(lr=rc.lr, beta1=rc.adam_beta1, beta2=rc.adam_beta2, eps=rc.adam_eps,
-                      weight_decay=rc.weight_decay, clip_grad=rc.clip_grad, moment_dtype=_moment_dtype(rc))
+                      weight_decay=rc.weight_decay, clip_grad=rc.clip_grad, moment_dtype=_moment_dtype(rc),
+                      reduce_dtype=torch.bfloat16 if rc.grad_reduce_in_bf16 else None)
     tc = TrainConfig(micro_batch=rc.micro_batch, local_batch=local_batch, warmup_steps=rc.lr_warmup_iters,
                      decay_steps=rc.lr_decay_iters, min_lr_ratio=rc.min_lr_ratio, seed=rc.seed, comm=rc.comm,
                      zero_stage=int(rc.zero_stage))

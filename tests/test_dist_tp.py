@@ -74,6 +74,16 @@ def test_context_parallel_attention_gloo(world):
     assert "RESULT rank 0 ok=True" in r.stdout
 
 
+def test_bf16_gradient_wire_follows_the_fp32_wire_gloo():
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29676",
+                        os.path.join(ROOT, "tests", "multi", "bf16_reduce_worker.py")],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("ok=True") == 2
+
+
 def test_hybrid_sharding_matches_plain_data_parallel_gloo():
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
