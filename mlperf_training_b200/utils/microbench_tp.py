@@ -19,7 +19,7 @@ import torch.distributed as dist
 from ..ops import kernels as K
 from ..parallel.tensor import TPContext
 
-GEMM_PEAK_TFLOPS = 1421.6      # measured sustained cuBLAS bf16 on this pool
+GEMM_PEAK_TFLOPS = 1421.6      # measured sustained cuBLAS bf16 on the B200s these numbers were taken on
 NVLINK_GBS = 770.0             # measured peer copy, per direction
 
 
