@@ -159,3 +159,23 @@ def test_deoscillator_tracks_stacked_expert_weights():
         n = de.after_step(step, "mxfp4")
     assert n == 1 and float(m.w1[1, 5, 3]) in (1.0, 1.5)
     assert eng.buckets[0].master is None or float(eng.buckets[0].master.max()) <= 6.0
+
+
+def test_flux_loop_switches_forward_precision():
+    """The diffusion run loop: forward in A6W4 until the switch step, then 8-bit forward with a 4-bit backward; the
+    switch is logged and changes the losses against a run that never switches."""
+    import io
+
+    from mlperf_training_b200.trainer.flux import run
+    base = dict(model=dict(preset="tiny-mmdit"), global_batch=8, train_iters=4, lr=1e-3, prompt_dropout=0.0)
+    spec = {"initial": "a6w4", "switch_step": 2, "final": "mxfp8_fwd_mxfp4_bwd",
+            "deosc": {"enabled": True, "start_step": 0, "period": 2, "ratio": 1.0}}
+    buf = io.StringIO()
+    import contextlib
+    with contextlib.redirect_stdout(buf):
+        sw = run(dict(base, precision_schedule=spec), device="cpu", stream=io.StringIO())
+        stay = run(dict(base, precision_schedule={"initial": "a6w4"}), device="cpu", stream=io.StringIO())
+    text = buf.getvalue()
+    assert "step 0: linears run in a6w4" in text and "step 2: linears run in mxfp8_fwd_mxfp4_bwd" in text
+    assert "deosc: on" in text
+    assert all(l == l for l in sw["losses"]) and sw["losses"][:2] == stay["losses"][:2] and sw["losses"][2] != stay["losses"][2]
