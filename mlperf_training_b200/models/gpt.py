@@ -252,15 +252,18 @@ class Block(nn.Module):
         if self.lora_qkv is not None:
             lo = self.lora_qkv
             qkv = qkv + lo.up(T.GatherRows.apply(lo.down(xn), tp))
-        a = F.attention_packed(qkv, B=B, S=S, Hq=self.hq, Hkv=self.hkv, D=cfg.head_dim, cos=cos, sin=sin,
-                               sink=self.sink, causal=True, window=cfg.layer_window(self.layer))
+        if self.cp is not None:
+            a = self._attention_cp(qkv, cos, sin, B, S, self.hq, self.hkv)       # this rank's heads, sequence over the cp group
+        else:
+            a = F.attention_packed(qkv, B=B, S=S, Hq=self.hq, Hkv=self.hkv, D=cfg.head_dim, cos=cos, sin=sin,
+                                   sink=self.sink, causal=True, window=cfg.layer_window(self.layer))
         h = T.row_parallel(a, self.w_proj, tp, residual=x)
         if self.lora_proj is not None:
             lo = self.lora_proj
             h = h + lo.up(T.ScatterRows.apply(lo.down(a), tp))
         return self.mlp(h, self.mlp_norm, cfg.norm_eps)
 
-    def _attention_cp(self, qkv, cos, sin, B, S):
+    def _attention_cp(self, qkv, cos, sin, B, S, Hq=None, Hkv=None):
         """Attention with the sequence sharded over ``self.cp = (group, mode)``: ``S`` is this rank's
         chunk and ``cos`` / ``sin`` its rows of the tables.  ``mode`` "allgather" gathers keys and
         values of the earlier chunks, "ulysses" trades sequence shards for head shards, "ring" passes key / value
@@ -268,7 +271,7 @@ class Block(nn.Module):
         from ..parallel.context import context_parallel_attention, ring_attention, ulysses_attention
         cfg = self.cfg
         group, mode = self.cp
-        Hq, Hkv, D = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        Hq, Hkv, D = Hq or cfg.n_heads, Hkv or cfg.n_kv_heads, cfg.head_dim
         v3 = F.rope_packed(qkv, cos, sin, S=S, Hq=Hq, Hkv=Hkv, D=D).view(B, S, -1)
         q = v3[:, :, :Hq * D].unflatten(-1, (Hq, D))
         k = v3[:, :, Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
@@ -391,8 +394,6 @@ class GPT(nn.Module):
             for blk in self.blocks:
                 blk.cp = None
             return
-        if self.tp is not None:
-            raise NotImplementedError("context parallelism is not combined with tensor parallelism")
         if self.cfg.sink:
             raise NotImplementedError("context parallelism does not carry attention sink logits")
         if mode not in ("allgather", "ulysses", "ring"):

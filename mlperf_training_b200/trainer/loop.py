@@ -207,15 +207,15 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     if pp_size > 1 and (int(rc.dp_replicate) > 1 or cp_size > 1 or world % (pp_size * max(int(rc.tensor_parallel), 1))):
         raise NotImplementedError("pipeline stages combine with data and tensor parallelism here (context_parallel = 1, "
                                   "dp_replicate = 1, world divisible by pipeline_parallel x tensor_parallel)")
-    if cp_size > 1 and (int(rc.tensor_parallel) > 1 or int(rc.dp_replicate) > 1 or world % cp_size):
-        raise NotImplementedError("context parallelism combines with plain data parallelism here (tensor_parallel = 1, "
-                                  "dp_replicate = 1, world divisible by context_parallel)")
+    if cp_size > 1 and (int(rc.dp_replicate) > 1 or world % (cp_size * max(int(rc.tensor_parallel), 1))):
+        raise NotImplementedError("context parallelism combines with data and tensor parallelism here (dp_replicate = 1, "
+                                  "world divisible by context_parallel x tensor_parallel)")
     tp_size = min(int(rc.tensor_parallel), world)
     tp_ctx, dp_group, dp_rank, dp_world, rep_group = None, None, rank, world, None
     replicate = max(int(rc.dp_replicate), 1)
     if tp_size > 1 or (replicate > 1 and world > 1):
         from ..parallel.mesh import Mesh, MeshSpec
-        mesh = Mesh(MeshSpec(tp=tp_size, pp=pp_size, dp_replicate=replicate))
+        mesh = Mesh(MeshSpec(tp=tp_size, pp=pp_size, cp=cp_size if tp_size > 1 else 1, dp_replicate=replicate))
         if replicate > 1:
             rep_group = mesh.group("dp_replicate")
     if tp_size > 1:
@@ -260,8 +260,9 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             mesh = Mesh(MeshSpec(pp=pp_size))
         dp_rank, dp_world = mesh.index("dp"), mesh.size("dp")
     elif cp_size > 1:
-        from ..parallel.mesh import Mesh, MeshSpec
-        mesh = Mesh(MeshSpec(cp=cp_size))
+        if tp_size == 1:
+            from ..parallel.mesh import Mesh, MeshSpec
+            mesh = Mesh(MeshSpec(cp=cp_size))
         dp_rank, dp_world = mesh.index("dp"), mesh.size("dp")
         cp_group, dp_group = mesh.group("cp"), mesh.group("dp_cp")     # gradients are reduced over data x context
     if rc.global_batch % dp_world:

@@ -74,6 +74,17 @@ def test_context_parallel_attention_gloo(world):
     assert "RESULT rank 0 ok=True" in r.stdout
 
 
+def test_tensor_x_context_parallel_matches_plain_trainer_gloo():
+    """Tensor 2 x context 2 on four ranks (all-gather and ring forms, masked labels) against the plain trainer."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+                        "--master-addr", "127.0.0.1", "--master-port", "29677",
+                        os.path.join(ROOT, "tests", "multi", "tp_cp_worker.py")],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("ok=True") == 4
+
+
 def test_bf16_gradient_wire_follows_the_fp32_wire_gloo():
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
