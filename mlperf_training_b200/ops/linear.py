@@ -75,7 +75,7 @@ def hadamard_rows(x: torch.Tensor, block: int) -> torch.Tensor:
             h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)], 0)
         h = _HADAMARD[key] = (h / block ** 0.5).to(device=x.device, dtype=x.dtype)
     T, C = x.shape
-    return torch.matmul(h, x.view(T // block, block, C)).view(T, C)
+    return torch.matmul(h, x.reshape(T // block, block, C)).reshape(T, C)
 
 
 def mx_eligible(rows: int, n_out: int, n_in: int) -> bool:

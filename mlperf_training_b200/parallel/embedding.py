@@ -159,11 +159,13 @@ class ShardedEmbedding:
         self.apply_rowwise_adagrad(rows_l, g_l)
 
     def apply_rowwise_adagrad(self, rows: torch.Tensor, grads: torch.Tensor) -> None:
+        """Row-wise Adagrad on the rows ``rows`` of the local shard (entries outside ``[0, local_rows)`` are skipped);
+        the row width is the shard's own (a column-wise shard holds a slice of the table's width)."""
         if rows.numel() == 0:
             return
         if self.weight.is_cuda and self.weight.dtype == torch.bfloat16:
             _lib.call("b200_rowwise_adagrad", _lib.ptr(self.weight), _lib.ptr(self.state), _lib.ptr(rows.contiguous()),
-                      _lib.ptr(grads.contiguous()), rows.numel(), self.dim, float(self.lr), float(self.eps),
+                      _lib.ptr(grads.contiguous()), rows.numel(), self.weight.shape[1], float(self.lr), float(self.eps),
                       self.local_rows, _lib.stream_ptr())
             return
         ok = (rows >= 0) & (rows < self.local_rows)
@@ -333,13 +335,6 @@ class ColumnShardedEmbedding(ShardedEmbedding):
         srt_l = S.sort_unique(req_ids, S.key_bits_for(max(self.rows, 2)))
         g_l = S.segment_sum(recv, srt_l, out_dtype=torch.float32)
         self.apply_rowwise_adagrad(srt_l.uniq, g_l)
-
-    def apply_rowwise_adagrad(self, rows: torch.Tensor, grads: torch.Tensor) -> None:
-        dim, self.dim = self.dim, self.cols                              # the update runs on this rank's slice
-        try:
-            super().apply_rowwise_adagrad(rows, grads)
-        finally:
-            self.dim = dim
 
     # ------------------------------------------------------------------ state
     def state_dict(self) -> dict:
