@@ -236,3 +236,15 @@ def test_hstu_trainer_steps_with_the_interleaved_preprocessor():
                      data_kw=dict(length_median=12, length_min=4, length_max=24))
     losses = [float(tr.train_step(i)) for i in range(4)]
     assert all(l == l and l < 10 for l in losses)
+
+
+def test_hstu_loop_with_column_wise_tables_resumes_gloo(tmp_path):
+    """Two ranks, the eleven-table set with two tables cut along their width: the loop trains, writes the sharded
+    sparse checkpoint, exits, and the resumed run continues on the straight run's losses."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29678",
+                        os.path.join(ROOT, "tests", "multi", "hstu_loop_worker.py"), str(tmp_path)],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("ok=True") == 2
