@@ -126,6 +126,20 @@ class Deoscillator:
             value[sl] = (r * scale).reshape(-1)[src]
         return tracked, key, code, value
 
+    def state_dict(self) -> dict:
+        """Per-bucket flip state (in bucket order), for this rank's optimizer-shard checkpoint."""
+        per = []
+        for b in self.engine.buckets:
+            st = self.state.get(id(b))
+            per.append(None if st is None else {k: v.detach().cpu() for k, v in st.items()})
+        return {"buckets": per, "snapped": self.snapped, "history": list(self.history)}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.snapped, self.history = int(sd.get("snapped", 0)), [tuple(h) for h in sd.get("history", [])]
+        for b, st in zip(self.engine.buckets, sd.get("buckets", [])):
+            if st is not None:
+                self.state[id(b)] = {k: v.to(b.param_buf.device) for k, v in st.items()}
+
     def after_step(self, step: int, precision: str) -> int:
         """Returns the number of weights snapped at this step (non-zero only at a period end)."""
         from .linear import MX_RECIPES

@@ -356,6 +356,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     if sched is not None and sched.deosc.enabled:
         from ..ops.recipe import Deoscillator
         deosc = Deoscillator(trainer.engine, sched.deosc)
+        if resuming and ck["optim"] is not None and ck["optim"].get("deosc") is not None:
+            deosc.load_state_dict(ck["optim"]["deosc"])        # flip counts of the period the checkpoint fell into
     hb = None
     if rc.heartbeat_timeout_s > 0 and world > 1:
         from ..parallel.health import Heartbeat
@@ -463,7 +465,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                 saver(step + 1,
                                 dense={"param_bufs": [b.param_buf.detach().cpu() for b in trainer.engine.buckets],
                                        "model_config": cfg.to_dict()},
-                                optim_shard=_optim_shard(trainer, per_rank_params),
+                                optim_shard=dict(_optim_shard(trainer, per_rank_params),
+                                                 deosc=deosc.state_dict() if deosc is not None else None),
                                 meta={"samples": samples, "run_started": True, "window": 0, "batch_idx_in_window": -1,
                                       "evals_done": evals_done})
                 last_ckpt_t = time.perf_counter()

@@ -179,3 +179,28 @@ def test_flux_loop_switches_forward_precision():
     assert "step 0: linears run in a6w4" in text and "step 2: linears run in mxfp8_fwd_mxfp4_bwd" in text
     assert "deosc: on" in text
     assert all(l == l for l in sw["losses"]) and sw["losses"][:2] == stay["losses"][:2] and sw["losses"][2] != stay["losses"][2]
+
+
+def test_deoscillator_state_survives_a_resume(tmp_path):
+    """A run under 4-bit weights that exits in the middle of a de-oscillation period and resumes ends on the losses of
+    the uninterrupted run: flip counts travel with the optimizer shard."""
+    import io
+
+    import pytest
+
+    from mlperf_training_b200.trainer.loop import run
+    tiny = dict(n_layers=2, hidden=128, n_heads=2, n_kv_heads=2, head_dim=64, ffn_hidden=256, vocab_size=256, seq_len=128,
+                dtype="fp32", precision="mxfp4")
+    spec = {"initial": "mxfp4", "deosc": {"enabled": True, "start_step": 0, "period": 4, "ratio": 0.5}}
+    base = dict(model=tiny, global_batch=2, micro_batch=2, train_iters=6, lr=5e-3, lr_warmup_iters=1, clip_grad=1.0,
+                precision_schedule=spec)
+    torch.manual_seed(0)
+    ref = run(dict(base), device="cpu", stream=io.StringIO())
+    assert [s for s, _ in ref["deosc_history"]] == [3]
+    e = dict(base, checkpoint_dir=str(tmp_path / "ck"), die_at_step=2)
+    torch.manual_seed(0)
+    with pytest.raises(SystemExit):
+        run(dict(e), device="cpu", stream=io.StringIO())
+    out = run(dict(e, die_at_step=0), device="cpu", stream=io.StringIO())
+    assert out["steps"] == 4 and out["deosc_history"] == ref["deosc_history"]         # same count snapped at the same step
+    assert max(abs(a - b) for a, b in zip(out["losses"], ref["losses"][2:])) < 1e-5
