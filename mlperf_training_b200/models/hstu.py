@@ -390,10 +390,36 @@ class HSTU(nn.Module):
 
     # ------------------------------------------------------------------ dynamic layers
     def get_extra_state(self):
-        return {"sd_iter": self._sd_iter}
+        """What a checkpoint needs beside the parameters: the stochastic-depth counter and the per-tensor FP8 scale
+        state of every linear and attention site (a frozen calibration must not start over after a resume; the
+        reference registers these buffers on the layer for the same reason, modules/stu.py:317-328)."""
+        sites = {}
+        for n, p in self.named_parameters():
+            st = getattr(p, "_fp8_sites", None)
+            if st:
+                sites[n] = {k: v.state_dict() for k, v in st.items()}
+        attn = {n: [s.state_dict() for s in m._attn_fp8_sites] for n, m in self.named_modules()
+                if getattr(m, "_attn_fp8_sites", None) is not None}
+        return {"sd_iter": self._sd_iter, "fp8_sites": sites, "fp8_attn_sites": attn}
 
     def set_extra_state(self, state):
-        self._sd_iter = int((state or {}).get("sd_iter", 0))
+        state = state or {}
+        self._sd_iter = int(state.get("sd_iter", 0))
+        if state.get("fp8_sites") or state.get("fp8_attn_sites"):
+            from ..ops import fp8 as F8
+            from ..ops.linear import _site
+            params, mods = dict(self.named_parameters()), dict(self.named_modules())
+            for n, per in (state.get("fp8_sites") or {}).items():
+                if n in params:
+                    for name, sd in per.items():
+                        _site(params[n], name, sd["fmt"]).load_state_dict(sd)
+            for n, lst in (state.get("fp8_attn_sites") or {}).items():
+                if n in mods:
+                    dev = next(self.parameters()).device
+                    sites = tuple(F8.DelayedScale(sd["fmt"], dev) for sd in lst)
+                    for s_, sd in zip(sites, lst):
+                        s_.load_state_dict(sd)
+                    mods[n]._attn_fp8_sites = sites
 
     def skipped_layers(self, it: int) -> list:
         """Layers that stochastic depth turns into the identity in training forward number ``it``."""

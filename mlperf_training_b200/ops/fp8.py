@@ -26,6 +26,27 @@ FMAX = {"e4m3": 448.0, "e5m2": 57344.0}
 _TORCH = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
 
 
+# How a site's scale follows the tensor, per element format (``set_policy`` changes it for sites created afterwards):
+#   mode "rolling": the factor follows the maximum of the last ``history`` epochs (delayed scaling);
+#   mode "frozen":  ``history`` calibration epochs, then the factor never moves again (the recommender's forward sites:
+#                   4 steps, margin 1.5, generative_recommenders/ops/triton/triton_fp8.py:94-102,694-749);
+#   ``refresh``:    a rolling factor is republished only every ``refresh`` epochs from the maximum collected since
+#                   (the recommender's gradient sites: every 200 calls, margin 8, .../bwd_fp8.py:157-169,1073-1154);
+#   ``margin``:     headroom multiplier on the collected maximum.
+SCALE_POLICY = {"e4m3": dict(mode="rolling", history=4, margin=1.0, refresh=1),
+                "e5m2": dict(mode="rolling", history=4, margin=1.0, refresh=1)}
+
+
+def set_policy(fmt: str, **kw) -> dict:
+    """Change the scale policy of ``fmt`` sites created from now on; returns the previous policy."""
+    old = dict(SCALE_POLICY[fmt])
+    bad = set(kw) - set(old)
+    if bad or kw.get("mode", old["mode"]) not in ("rolling", "frozen"):
+        raise ValueError(f"fp8 scale policy: unknown setting {sorted(bad) or kw.get('mode')}")
+    SCALE_POLICY[fmt].update(kw)
+    return old
+
+
 @dataclass
 class FP8Operand:
     """K-major operand: ``q [rows, k]`` codes (uint8) and ``inv_scale`` (one fp32, on the device):
@@ -49,34 +70,58 @@ class DelayedScale:
     the optimizer has stepped - pushes the collected amax into the history and recomputes ``scale`` =
     ``fmax / (max(history) * 2^margin)``, all on the device."""
 
-    def __init__(self, fmt: str, device, history: int = 4, margin: int = 0):
+    def __init__(self, fmt: str, device, history: int | None = None, margin: int = 0):
+        pol = SCALE_POLICY[fmt]
         self.fmt, self.margin = fmt, margin
-        self.hist = torch.zeros(history, dtype=torch.float32, device=device)
+        self.mode, self.margin_mult, self.refresh = pol["mode"], float(pol["margin"]), max(int(pol["refresh"]), 1)
+        self.hist = torch.zeros(history if history is not None else int(pol["history"]), dtype=torch.float32, device=device)
         self.amax = torch.zeros(1, dtype=torch.int32, device=device)
         self.scale = torch.ones(1, dtype=torch.float32, device=device)
         self.inv_scale = torch.ones(1, dtype=torch.float32, device=device)
         self.epoch = None
         self.pos = 0
         self.primed = False
+        self.frozen = False
 
     def _set_from(self, amax: torch.Tensor) -> None:
-        a = amax.float().clamp_min(1e-30) * (2.0 ** self.margin)
+        a = amax.float().clamp_min(1e-30) * (2.0 ** self.margin) * self.margin_mult
         self.scale.copy_((FMAX[self.fmt] / a).reshape(1))
         self.inv_scale.copy_((a / FMAX[self.fmt]).reshape(1))
 
     def prepare(self, x: torch.Tensor, epoch: int) -> None:
         """Make ``scale`` valid for quantising ``x`` in ``epoch``."""
+        if self.frozen:
+            return
         if not self.primed:
             # no history yet: this tensor's own maximum (one extra pass, first use only)
             self._set_from(x.detach().abs().amax())
             self.primed, self.epoch = True, epoch
             return
         if epoch != self.epoch:
-            self.hist[self.pos % self.hist.numel()] = self.amax.view(torch.float32)[0]
-            self.pos += 1
+            self.epoch = epoch
+            if self.refresh > 1:
+                # the collected maximum keeps growing over the window; it is published at the window's end
+                self.pos += 1
+                if self.pos % self.refresh:
+                    return
+                self.hist[(self.pos // self.refresh) % self.hist.numel()] = self.amax.view(torch.float32)[0]
+            else:
+                self.hist[self.pos % self.hist.numel()] = self.amax.view(torch.float32)[0]
+                self.pos += 1
             self.amax.zero_()
             self._set_from(self.hist.max())
-            self.epoch = epoch
+            if self.mode == "frozen" and self.pos >= self.hist.numel():
+                self.frozen = True                       # calibration complete: the factor stays
+
+    def state_dict(self) -> dict:
+        return {"fmt": self.fmt, "hist": self.hist.detach().cpu(), "amax": self.amax.detach().cpu(), "scale": self.scale.detach().cpu(),
+                "inv_scale": self.inv_scale.detach().cpu(), "epoch": self.epoch, "pos": self.pos, "primed": self.primed,
+                "frozen": self.frozen}
+
+    def load_state_dict(self, sd: dict) -> None:
+        for k in ("hist", "amax", "scale", "inv_scale"):
+            getattr(self, k).copy_(sd[k])
+        self.epoch, self.pos, self.primed, self.frozen = sd["epoch"], int(sd["pos"]), bool(sd["primed"]), bool(sd["frozen"])
 
 
 def quantize(x: torch.Tensor, state: DelayedScale, *, want_row: bool = True, want_col: bool = False):

@@ -415,6 +415,15 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                      contextualized_mlp=str(m.get("contextualized_mlp", "simple")),
                      pmlp_contextual_dropout=float(m.get("pmlp_contextual_dropout", 0.0)),
                      num_positions=int(m.get("num_positions", 8192)), num_time_buckets=int(m.get("num_time_buckets", 2048)))
+    # per-tensor FP8 scale policy: "reference" = the recommender's recipe - forward sites calibrate for 4 steps (margin 1.5)
+    # and freeze, gradient sites republish every 200 steps with margin 8; "rolling" = a 4-step delayed-scaling history
+    policy = str(m.get("fp8_scale_policy", "rolling")).lower()
+    if policy == "reference":
+        from ..ops import fp8 as _F8
+        _F8.set_policy("e4m3", mode="frozen", history=int(m.get("fp8_calibration_steps", 4)), margin=float(m.get("fp8_margin", 1.5)))
+        _F8.set_policy("e5m2", mode="rolling", history=1, refresh=int(m.get("fp8_grad_refresh", 200)), margin=float(m.get("fp8_grad_margin", 8.0)))
+    elif policy != "rolling":
+        raise ValueError(f"fp8_scale_policy '{policy}': 'rolling' or 'reference'")
     emb = exp.get("embedding") or {}
     table_set = emb.get("tables") or None            # "yambda": the benchmark's eleven tables instead of one item table
     if table_set == "yambda":

@@ -62,3 +62,65 @@ def test_schedule_switch_changes_the_numbers():
     assert torch.equal(ys[0], ys[1]) and torch.equal(ys[2], ys[3])
     assert not torch.equal(ys[1], ys[2])
     assert sched.log == [(0, "a6w4"), (2, "fp8")]
+
+
+def test_scale_policies_frozen_calibration_and_refresh_cadence():
+    """"frozen": the factor follows the first ``history`` epochs and then never moves; ``refresh``: a rolling factor is
+    republished only at the end of every window from the maximum collected in it; ``margin`` leaves headroom."""
+    old4, old5 = fp8.set_policy("e4m3", mode="frozen", history=2, margin=1.5), fp8.set_policy("e5m2", refresh=3, history=1, margin=8.0)
+    try:
+        st = fp8.DelayedScale("e4m3", "cpu")
+        x = torch.randn(128, 128).bfloat16()
+        seen = []
+        for epoch, mult in enumerate((1.0, 4.0, 2.0, 100.0, 100.0)):
+            st.prepare(x * mult, epoch)
+            fp8.quantize(x * mult, st)
+            seen.append((float(st.scale), st.frozen))
+        amax = float(x.abs().max())
+        assert not seen[1][1] and seen[2][1] and seen[2][0] == seen[3][0] == seen[4][0]      # frozen after two calibration epochs
+        assert abs(seen[2][0] * amax * 4.0 * 1.5 - 448.0) < 1e-2                            # max of the calibration epochs, margin 1.5
+        sd = st.state_dict()
+        st2 = fp8.DelayedScale("e4m3", "cpu")
+        st2.load_state_dict(sd)
+        st2.prepare(x * 1000, 9)
+        assert st2.frozen and float(st2.scale) == seen[4][0]                                # a resumed site stays frozen
+        g = fp8.DelayedScale("e5m2", "cpu")
+        scales = []
+        for epoch, mult in enumerate((1.0, 1.0, 8.0, 1.0, 1.0, 1.0, 1.0)):
+            g.prepare(x * mult, epoch)
+            fp8.quantize(x * mult, g)
+            scales.append(float(g.scale))
+        # published at epochs 3 and 6 only: the first window's maximum (8 x) rules from epoch 3 on, the second's (1 x) from 6
+        assert scales[0] == scales[1] == scales[2] and scales[3] == scales[4] == scales[5] != scales[2]
+        assert abs(scales[3] * amax * 8.0 * 8.0 - 57344.0) / 57344.0 < 1e-3 and abs(scales[6] * amax * 8.0 - 57344.0) / 57344.0 < 1e-3
+    finally:
+        fp8.set_policy("e4m3", **old4)
+        fp8.set_policy("e5m2", **old5)
+
+
+def test_hstu_run_with_the_reference_fp8_policy_resumes(tmp_path):
+    """HSTU linears in per-tensor FP8 with calibrate-then-freeze factors: the factor state is part of the model's
+    checkpoint, so a run that exits after the calibration and resumes continues on the straight run's losses."""
+    import io
+
+    import pytest
+
+    from mlperf_training_b200.trainer.hstu import run
+    old4, old5 = dict(fp8.SCALE_POLICY["e4m3"]), dict(fp8.SCALE_POLICY["e5m2"])
+    try:
+        e = dict(batch_per_gpu=32, train_steps=8, dense_lr=2e-3, sparse_lr=0.05, eval_interval_steps=0, num_eval_batches=0,
+                 model=dict(layers=1, dim=256, heads=2, d_qk=128, d_v=128, max_seq_len=64, dtype="fp32", precision="fp8",
+                            mlp_hidden=128, num_positions=128, num_time_buckets=32, fp8_scale_policy="reference",
+                            fp8_calibration_steps=2, input_dropout=0.0, linear_dropout=0.0),
+                 embedding=dict(rows=300, dim=128), data=dict(length_median=24, length_min=8, length_max=60))
+        ref = run(dict(e), device="cpu", stream=io.StringIO())
+        sites = [s for p in ref["trainer"].model.parameters() for s in getattr(p, "_fp8_sites", {}).values()]
+        assert sites and all(s.frozen for s in sites if s.fmt == "e4m3") and any(s.fmt == "e5m2" and not s.frozen for s in sites)
+        ck = dict(e, checkpoint_dir=str(tmp_path / "ck"), die_at_step=5)
+        with pytest.raises(SystemExit):
+            run(dict(ck), device="cpu", stream=io.StringIO())
+        out = run(dict(ck, die_at_step=0), device="cpu", stream=io.StringIO())
+        assert max(abs(a - b) for a, b in zip(out["losses"], ref["losses"][5:])) < 1e-5
+    finally:
+        fp8.SCALE_POLICY["e4m3"].update(old4)
+        fp8.SCALE_POLICY["e5m2"].update(old5)
