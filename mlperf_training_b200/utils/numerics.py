@@ -3,11 +3,14 @@ a linear layer (forward, data gradient, weight gradient) computed from MXFP8-qua
 against the same products in fp64.
 
     python -m mlperf_training_b200.utils.numerics [--tokens 512 --in 1024 --out 1024 --outliers 0.001]
+    python -m mlperf_training_b200.utils.numerics --precision mxfp4 a6w4 fp8      # through the training path itself
 
 ``linear_site_report(x, w, dy)`` quantises exactly as the training path does (e4m3 values with one
 power-of-two scale per 32 elements along the contraction dimension of each GEMM: rows of x and w
 for the forward product, columns for the two gradient products), dequantises, multiplies in fp64
-and compares.  Runs on CPU or GPU tensors.  The reference carries the same kind of probe for its FP8
+and compares.  ``recipe_report(x, w, dy, precision)`` runs the linear triple of the training path itself (forward,
+data gradient, weight gradient under ``precision``: any micro-scaled recipe or per-tensor fp8, with its stochastic
+rounding and Hadamard operands) and compares each result with fp64.  Both run on CPU or GPU tensors.  The reference carries the same kind of probe for its FP8
 paths (generative_recommenders/ops/triton/fp8_wgrad_snr.py, preproc_fp8_snr.py: fp64 reference GEMMs,
 SNR and cosine per site).
 """
@@ -60,6 +63,19 @@ def linear_site_report(x: torch.Tensor, w: torch.Tensor, dy: torch.Tensor) -> di
     return {k: {"snr_db": round(snr_db(r, g), 2), "cosine": round(cosine(r, g), 6)} for k, (r, g) in sites.items()}
 
 
+def recipe_report(x: torch.Tensor, w: torch.Tensor, dy: torch.Tensor, precision: str) -> dict:
+    """SNR (dB) and cosine of ``y``, ``dx`` and ``dw`` as the training path computes them under ``precision``."""
+    from ..ops import functional as F
+    dt = torch.bfloat16 if x.is_cuda else torch.float32
+    xq = x.to(dt).detach().clone().requires_grad_(True)
+    wq = w.to(dt).detach().clone().requires_grad_(True)
+    y = F.linear(xq, wq, None, None, precision)
+    y.backward(dy.to(dt))
+    xb, wb, db = (t.to(dt).double() for t in (x, w, dy))
+    sites = {"fwd": (xb @ wb.t(), y.detach()), "dgrad": (db @ wb, xq.grad), "wgrad": (db.t() @ xb, wq.grad)}
+    return {k: {"snr_db": round(snr_db(r, g), 2), "cosine": round(cosine(r, g), 6)} for k, (r, g) in sites.items()}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=512)
@@ -67,6 +83,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", dest="n", type=int, default=1024)
     ap.add_argument("--outliers", type=float, default=0.0, help="fraction of activation entries multiplied by 50")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--precision", nargs="*", default=[], help="recipes to run through the training path (mxfp8 mxfp6 mxfp4 a6w4 fp8 ...)")
     a = ap.parse_args(argv)
     g = torch.Generator().manual_seed(a.seed)
     x = torch.randn(a.tokens, a.k, generator=g)
@@ -75,6 +92,8 @@ def main(argv=None) -> int:
     w = torch.randn(a.n, a.k, generator=g) * 0.02
     dy = torch.randn(a.tokens, a.n, generator=g) * 1e-3
     print(json.dumps({"shape": [a.tokens, a.k, a.n], "outliers": a.outliers, **linear_site_report(x, w, dy)}))
+    for prec in a.precision:
+        print(json.dumps({"precision": prec, **recipe_report(x, w, dy, prec)}))
     return 0
 
 

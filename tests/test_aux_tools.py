@@ -116,6 +116,14 @@ def test_mxfp8_site_probe_reports_snr_and_is_scale_invariant():
     for k in rep:
         assert abs(rep2[k]["snr_db"] - rep[k]["snr_db"]) < 0.05
     assert main(["--tokens", "128", "--in", "128", "--out", "128", "--outliers", "0.01"]) == 0
+    # through the training path: the narrower the elements, the lower the ratio; the bare-operand probe agrees for mxfp8
+    from mlperf_training_b200.utils.numerics import recipe_report
+    torch.manual_seed(0)
+    by = {p: recipe_report(x, w, dy, p) for p in ("mxfp8", "mxfp6", "mxfp4", "fp8")}
+    assert all(abs(by["mxfp8"][k]["snr_db"] - rep[k]["snr_db"]) < 1.0 for k in rep)
+    assert by["mxfp8"]["fwd"]["snr_db"] > by["mxfp6"]["fwd"]["snr_db"] > by["mxfp4"]["fwd"]["snr_db"] > 10.0
+    assert by["fp8"]["fwd"]["snr_db"] > 22.0 and by["mxfp4"]["wgrad"]["cosine"] > 0.95
+    assert main(["--tokens", "128", "--in", "128", "--out", "128", "--precision", "a6w4"]) == 0
 
 
 def test_startup_timeline_phases():
