@@ -22,7 +22,7 @@ def main(argv=None) -> int:
     ap.add_argument("--config", required=True)
     ap.add_argument("--device", default=None)
     ap.add_argument("overrides", nargs="*")
-    args = ap.parse_args(argv)
+    args = ap.parse_intermixed_args(argv)      # key=value overrides may follow the options
 
     if os.environ.get("B200_QUIET", "0") not in ("", "0"):
         from ..mllog import suppress

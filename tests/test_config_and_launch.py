@@ -121,3 +121,18 @@ def test_env_bootstrap_env_wins_and_partial_arm():
     assert env["B_A"] == "1" and env["B_KEEP"] == "7" and env["B_Y"] == "0" and "B_SKIP" not in env
     assert rep.kept == {"B_KEEP": "7"} and rep.partial_arms == {"fp8_forward": {"on": ["x"], "off": ["y"]}}
     assert any("partial arm" in l for l in rep.lines())
+
+
+def test_cli_takes_overrides_after_the_options(tmp_path, capsys):
+    """``cli <mode> --config X --device cpu key=value ...``: the overrides may follow the options."""
+    from mlperf_training_b200.trainer import cli
+    exp = tmp_path / "tiny.yaml"
+    exp.write_text(
+        "modules:\n  pre_trainer:\n    overrides:\n      benchmark: tiny\n      global_batch: 2\n      micro_batch: 1\n"
+        "      train_iters: 5\n      model: {n_layers: 1, hidden: 32, n_heads: 2, n_kv_heads: 1, head_dim: 16, ffn_hidden: 64, "
+        "vocab_size: 64, seq_len: 16, dtype: fp32}\n")
+    rc = cli.main(["pretrain", "--config", str(exp), "--device", "cpu", "modules.pre_trainer.resolved.train_iters=2"])
+    out = capsys.readouterr().out
+    assert rc == 0
+    recs = parse_log(out)
+    assert sum(r["key"] == "train_loss" for r in recs) == 2             # two iterations, not the file's five
