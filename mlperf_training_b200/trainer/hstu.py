@@ -140,7 +140,9 @@ class HSTUTrainer:
             self.table = EmbeddingCollection(tables, group=group, device=self.device, lr=sparse_lr, seed=seed, comm=emb_comm, plan=plan)
             self.ctx_keys = [t.name for t in tables if t.name == "uid" or t.name.startswith("cross_")]
             data_kw.pop("kind", None)
-            self.data = YambdaSyntheticSamples(tables, batch_per_gpu, seed=seed, **data_kw)
+            import inspect
+            known = set(inspect.signature(HSTUSyntheticData.__init__).parameters)
+            self.data = YambdaSyntheticSamples(tables, batch_per_gpu, seed=seed, **{k: v for k, v in data_kw.items() if k in known})
             self.eval_data = None
             data_kw = {"kind": "_done"}
         else:
@@ -157,11 +159,16 @@ class HSTUTrainer:
         elif kind == "yambda":
             # memory-mapped event store: time windows, per-rank slices of each window, user-hash hold-out
             from ..data.yambda import EventStoreDataset
-            root = data_kw.pop("root")
+            root = data_kw.pop("root", None) or data_kw.pop("path")
+            for k in ("path", "length_median", "length_min", "length_max", "zipf_alpha", "balance_world"):   # synthetic-only keys
+                data_kw.pop(k, None)
             self.data = _WorldView(EventStoreDataset(root, batch_per_gpu, split="train", **data_kw), self.world)
             self.eval_data = _WorldView(EventStoreDataset(root, batch_per_gpu, split="eval", **data_kw), self.world)
         elif kind != "_done":
-            self.data = HSTUSyntheticData(table_rows, batch_per_gpu, seed=seed, **data_kw)
+            import inspect
+            known = set(inspect.signature(HSTUSyntheticData.__init__).parameters)
+            # an experiment file names keys of every data kind (paths, hold-out settings): the generator takes its own
+            self.data = HSTUSyntheticData(table_rows, batch_per_gpu, seed=seed, **{k: v for k, v in data_kw.items() if k in known})
             self.eval_data = None
         self.batch_per_gpu = batch_per_gpu
         self.sparse_lr, self.lr_warmup_steps, self.lr_warmup_start_lr = float(sparse_lr), 0, 0.0

@@ -136,3 +136,40 @@ def test_cli_takes_overrides_after_the_options(tmp_path, capsys):
     assert rc == 0
     recs = parse_log(out)
     assert sum(r["key"] == "train_loss" for r in recs) == 2             # two iterations, not the file's five
+
+
+_GPT_TINY = ["model.n_layers=2", "model.hidden=128", "model.n_heads=2", "model.n_kv_heads=2", "model.head_dim=64", "model.vocab_size=256",
+             "model.seq_len=128", "model.dtype=fp32", "train_iters=2", "global_batch=2", "micro_batch=1", "eval_interval=0",
+             "warmup_train_steps=0"]
+_SHIPPED = {
+    "workloads/llama31_8b/conf/llama3.1_8B-pretrain-mxfp8.yaml": ("pretrain", "pre_trainer", _GPT_TINY + ["model.ffn_hidden=256", "comm=nccl"]),
+    "workloads/gpt_oss_20b/conf/gpt_oss_20B-mxfp8-pretrain.yaml": ("pretrain", "pre_trainer", _GPT_TINY + [
+        "model.moe_ffn_hidden=128", "model.n_experts=4", "model.top_k=2", "model.window=64", "expert_parallel=1", "moe_dispatch=nccl"]),
+    "workloads/gpt_oss_20b/conf/gpt_oss_20B-mxfp4-deosc-pretrain.yaml": ("pretrain", "pre_trainer", _GPT_TINY + [
+        "model.moe_ffn_hidden=128", "model.n_experts=4", "model.top_k=2", "model.window=64", "expert_parallel=1", "moe_dispatch=nccl",
+        "precision_schedule.deosc.start_step=0", "precision_schedule.deosc.period=2"]),
+    "workloads/llama2_70b_lora/conf/llama2_70b_lora_posttrain.yaml": ("posttrain", "post_trainer", _GPT_TINY + ["model.ffn_hidden=256", "data.loss_last=32"]),
+    "workloads/flux1/conf/flux.1_schnell_t2i-pretrain.yaml": ("flux", "flux_trainer", [
+        "model.preset=tiny-mmdit", "model.img_size=64", "model.txt_tokens=16", "model.dtype=fp32", "train_iters=2", "global_batch=2",
+        "local_batch=2", "warmup_train_steps=0", "warmup_eval_steps=0", "eval_every_samples=0", "fsdp.comm=nccl"]),
+    "workloads/hstu/conf/hstu_yambda.yaml": ("hstu", "hstu_trainer", [
+        "model.layers=1", "model.dim=64", "model.heads=2", "model.d_qk=32", "model.d_v=32", "model.max_seq_len=64", "model.dtype=fp32",
+        "model.mlp_hidden=32", "model.num_positions=256", "model.num_time_buckets=64", "embedding.rows=300", "embedding.dim=32",
+        "batch_per_gpu=4", "train_steps=2", "eval_interval_steps=0", "num_eval_batches=0", "data.length_median=12", "data.length_min=4",
+        "data.length_max=40"]),
+}
+
+
+def test_every_shipped_experiment_file_is_covered():
+    assert {str(p.relative_to(REPO)) for p in REPO.glob("workloads/*/conf/*.yaml")} == set(_SHIPPED)
+
+
+@pytest.mark.parametrize("path", sorted(_SHIPPED))
+def test_shipped_experiment_runs_through_the_cli_on_cpu(path, capsys):
+    """Every shipped experiment file drives its trainer for two steps on CPU once the model is shrunk by overrides: the
+    keys the file names are the keys the trainer reads."""
+    from mlperf_training_b200.trainer import cli
+    mode, module, over = _SHIPPED[path]
+    rc = cli.main([mode, "--config", str(REPO / path), "--device", "cpu"] + [f"modules.{module}.resolved.{o}" for o in over])
+    out = capsys.readouterr().out
+    assert rc == 0 and "run_stop" in out
