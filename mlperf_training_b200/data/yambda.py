@@ -81,6 +81,7 @@ class EventStoreDataset:
         self.user, self.item, self.ts, self.kind, self.played, self.uoff = (
             np.load(d / f"{n}.npy", mmap_mode="r") for n in ("user", "item", "ts", "kind", "played", "user_offsets"))
         self.batch, self.max_history, self.min_history = batch, max_history, min_history
+        self.num_items = int(np.asarray(self.item).max()) + 1 if len(self.item) else 0     # the table must have this many rows
         self.contract = {"window_seconds": window_seconds, "holdout": holdout, "salt": salt}
         # anchors: listen events with enough history, of users on this side of the split
         pos_in_user = np.arange(len(self.user)) - np.asarray(self.uoff)[np.asarray(self.user)]

@@ -290,8 +290,9 @@ def gelu_bwd(dy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------------------
 def gather_rows(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     if not use_kernels(table):
-        out = table[ids.clamp(min=0)]
-        return torch.where((ids >= 0)[:, None], out, torch.zeros_like(out))
+        # ids outside [0, rows) give zero rows, as in the kernel
+        out = table[ids.clamp(min=0, max=table.shape[0] - 1)]
+        return torch.where(((ids >= 0) & (ids < table.shape[0]))[:, None], out, torch.zeros_like(out))
     ids = ids.to(torch.int64).contiguous()
     table = table.contiguous()
     out = torch.empty((ids.numel(), table.shape[1]), dtype=table.dtype, device=table.device)

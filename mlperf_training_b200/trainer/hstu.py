@@ -164,6 +164,9 @@ class HSTUTrainer:
                 data_kw.pop(k, None)
             self.data = _WorldView(EventStoreDataset(root, batch_per_gpu, split="train", **data_kw), self.world)
             self.eval_data = _WorldView(EventStoreDataset(root, batch_per_gpu, split="eval", **data_kw), self.world)
+            if self.data.ds.num_items > table_rows:
+                raise ValueError(f"the event store under {root} holds item ids up to {self.data.ds.num_items - 1}: "
+                                 f"embedding.rows = {table_rows} is too small")
         elif kind != "_done":
             import inspect
             known = set(inspect.signature(HSTUSyntheticData.__init__).parameters)
