@@ -149,29 +149,32 @@ class HSTUTrainer:
             self.table = ShardedEmbedding(table_rows, cfg.emb_dim, group=group, device=self.device, dtype=cfg.torch_dtype(),
                                           lr=sparse_lr, seed=seed, comm=emb_comm, init_scale=0.05)
         kind = data_kw.pop("kind", "synthetic")
+
+        def only(cls, kw):
+            """The keys of ``kw`` that ``cls`` takes: an experiment file names the keys of every data kind."""
+            import inspect
+            known = set(inspect.signature(cls.__init__).parameters)
+            return {k: v for k, v in kw.items() if k in known}
         if kind == "sequences":
             # per-user sequence files (MovieLens / KuaiRand layout), user-hash hold-out for evaluation
             from ..data.sequences import SequenceFileDataset
             path = data_kw.pop("path")
             fmt = data_kw.pop("format", "movielens")
+            data_kw = only(SequenceFileDataset, data_kw)
             self.data = _WorldView(SequenceFileDataset(path, batch_per_gpu, kind=fmt, split="train", seed=seed, **data_kw), self.world)
             self.eval_data = _WorldView(SequenceFileDataset(path, batch_per_gpu, kind=fmt, split="eval", seed=seed, **data_kw), self.world)
         elif kind == "yambda":
             # memory-mapped event store: time windows, per-rank slices of each window, user-hash hold-out
             from ..data.yambda import EventStoreDataset
             root = data_kw.pop("root", None) or data_kw.pop("path")
-            for k in ("path", "length_median", "length_min", "length_max", "zipf_alpha", "balance_world"):   # synthetic-only keys
-                data_kw.pop(k, None)
+            data_kw = only(EventStoreDataset, data_kw)
             self.data = _WorldView(EventStoreDataset(root, batch_per_gpu, split="train", **data_kw), self.world)
             self.eval_data = _WorldView(EventStoreDataset(root, batch_per_gpu, split="eval", **data_kw), self.world)
             if self.data.ds.num_items > table_rows:
                 raise ValueError(f"the event store under {root} holds item ids up to {self.data.ds.num_items - 1}: "
                                  f"embedding.rows = {table_rows} is too small")
         elif kind != "_done":
-            import inspect
-            known = set(inspect.signature(HSTUSyntheticData.__init__).parameters)
-            # an experiment file names keys of every data kind (paths, hold-out settings): the generator takes its own
-            self.data = HSTUSyntheticData(table_rows, batch_per_gpu, seed=seed, **{k: v for k, v in data_kw.items() if k in known})
+            self.data = HSTUSyntheticData(table_rows, batch_per_gpu, seed=seed, **only(HSTUSyntheticData, data_kw))
             self.eval_data = None
         self.batch_per_gpu = batch_per_gpu
         self.sparse_lr, self.lr_warmup_steps, self.lr_warmup_start_lr = float(sparse_lr), 0, 0.0

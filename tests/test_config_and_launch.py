@@ -173,3 +173,28 @@ def test_shipped_experiment_runs_through_the_cli_on_cpu(path, capsys):
     rc = cli.main([mode, "--config", str(REPO / path), "--device", "cpu"] + [f"modules.{module}.resolved.{o}" for o in over])
     out = capsys.readouterr().out
     assert rc == 0 and "run_stop" in out
+
+
+@pytest.mark.parametrize("kind", ["yambda", "sequences"])
+def test_hstu_experiment_file_with_on_disk_data_kinds(kind, tmp_path, monkeypatch, capsys):
+    """The shipped HSTU experiment file with ``DATA_KIND`` pointing at an event store / per-user sequence files: the
+    keys it names for other data kinds are not handed to the chosen dataset; a table smaller than the store's id
+    range is refused with a message."""
+    from mlperf_training_b200.data.sequences import write_synthetic_sequences
+    from mlperf_training_b200.data.yambda import write_synthetic_event_store
+    from mlperf_training_b200.trainer import cli
+    root = tmp_path / "data"
+    if kind == "yambda":
+        write_synthetic_event_store(str(root), 120, 80, 2000, days=3, seed=1)
+    else:
+        write_synthetic_sequences(str(root), 120, 2000, min_len=20, max_len=60, seed=1)
+    monkeypatch.setenv("DATA_KIND", kind)
+    monkeypatch.setenv("DATADIR", str(root))
+    mode, module, over = _SHIPPED["workloads/hstu/conf/hstu_yambda.yaml"]
+    over = [o for o in over if not o.startswith("embedding.rows")] + ["model.max_seq_len=128", "model.num_positions=512"]
+    args = [mode, "--config", str(REPO / "workloads/hstu/conf/hstu_yambda.yaml"), "--device", "cpu"]
+    assert cli.main(args + [f"modules.{module}.resolved.{o}" for o in over + ["embedding.rows=2000"]]) == 0
+    assert "run_stop" in capsys.readouterr().out
+    if kind == "yambda":
+        with pytest.raises(ValueError, match="too small"):
+            cli.main(args + [f"modules.{module}.resolved.{o}" for o in over + ["embedding.rows=500"]])
