@@ -408,7 +408,11 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         batch = host_batch(data, step)
         if torch.cuda.is_available() and str(device).startswith("cuda"):
             batch = tuple(t.pin_memory() for t in batch) if isinstance(batch, tuple) else batch.pin_memory()
-        loss = trainer.train_step(batch)
+        if prof is not None:
+            with prof.step_range(step):
+                loss = trainer.train_step(batch)
+        else:
+            loss = trainer.train_step(batch)
         if deosc is not None:
             n_snap = deosc.after_step(step, sched.at(step))
             if n_snap and rank == 0:

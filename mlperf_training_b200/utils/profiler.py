@@ -34,6 +34,11 @@ class StepProfiler:
             torch.distributed.barrier()
         self.prof.start()
 
+    def step_range(self, step: int):
+        """Context manager that marks one training step in the trace (``train_step#<n>``): the ranges the trace
+        post-processing cuts the timeline by (``utils.trace_post.step_spans``)."""
+        return torch.profiler.record_function(f"train_step#{int(step)}")
+
     def stop(self) -> Path:
         self.prof.stop()
         self.out_dir.mkdir(parents=True, exist_ok=True)

@@ -54,3 +54,19 @@ def test_passes(tmp_path):
     stats = T.postprocess(p)
     assert stats["lead_in_steps"] == 1 and json.dumps(stats)
     assert T.load(p)["traceEvents"]
+
+
+def test_run_loop_trace_carries_step_ranges(tmp_path):
+    """A trace recorded by the run loop (``profile_step_start`` / ``profile_step_end``) marks every profiled step, so the
+    post-processing finds the steps it reports on."""
+    import glob
+    import io
+
+    from mlperf_training_b200.trainer.loop import run
+    from mlperf_training_b200.utils.trace_post import postprocess
+    tiny = dict(n_layers=1, hidden=32, n_heads=2, n_kv_heads=1, head_dim=16, ffn_hidden=64, vocab_size=64, seq_len=16, dtype="fp32")
+    run(dict(model=tiny, global_batch=2, micro_batch=1, train_iters=5, profile_step_start=1, profile_step_end=4,
+             profile_dir=str(tmp_path)), device="cpu", stream=io.StringIO())
+    rep = postprocess(glob.glob(str(tmp_path / "trace_rank0.json*"))[0], out=str(tmp_path / "fixed.json"), drop_lead_in=False)
+    steps = [s["step"] for s in rep["report"]["steps"]]
+    assert steps and set(steps) <= {1, 2, 3} and rep["report"]["median_wall_us"] > 0
