@@ -251,12 +251,24 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         sched = PrecisionSchedule.from_spec(exp["precision_schedule"])
         if sched.deosc.enabled:
             deosc = Deoscillator(tr.engine, sched.deosc)
+    prof, prof_span = None, (int(exp.get("profile_step_start", 0) or 0), int(exp.get("profile_step_end", 0) or 0))
     for step in range(start_step, iters):
         if sched is not None and sched.apply(tr.model, step) and rank == 0:
             print(f"[precision] step {step}: linears run in {sched.at(step)}; {sched.deosc.status(sched.at(step))}", flush=True)
+        if prof_span[1] > prof_span[0] and step == prof_span[0] and rank == 0:
+            from ..utils.profiler import StepProfiler
+            prof = StepProfiler(exp.get("profile_dir") or ".", rank)
+            prof.start()
         timer.step_start()
-        losses.append(tr.train_step(data.batch(step, dp_rank, local_batch)))
+        if prof is not None:
+            with prof.step_range(step):
+                losses.append(tr.train_step(data.batch(step, dp_rank, local_batch)))
+        else:
+            losses.append(tr.train_step(data.batch(step, dp_rank, local_batch)))
         timer.step_stop()
+        if prof is not None and step + 1 == prof_span[1]:
+            prof.stop()
+            prof = None
         if deosc is not None:
             deosc.after_step(step, sched.at(step))
         samples = (step + 1) * gbs

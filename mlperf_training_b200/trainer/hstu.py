@@ -517,6 +517,9 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     t0 = time.perf_counter()
     window_of = getattr(getattr(tr.data, "ds", tr.data), "window_of_step", None)
     last_window, barrier_debug = None, os.environ.get("WINDOW_BARRIER_DEBUG", "0") == "1"
+    # torch profiler over steps [profile_step_start, profile_step_end) on rank 0, every step marked for the trace
+    # post-processing (generative_recommenders/dlrm_v4/utils.py:451-822)
+    prof, prof_span = None, (int(exp.get("profile_step_start", 0) or 0), int(exp.get("profile_step_end", 0) or 0))
     for step in range(start, steps):
         if window_of is not None:
             w = window_of(step, world)
@@ -528,11 +531,22 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                 if barrier_debug and rank == 0:
                     print(f"[window-barrier] step {step} window {w} waited {waited:.3f} s", flush=True)
                 last_window = w
+        if prof_span[1] > prof_span[0] and step == prof_span[0] and rank == 0:
+            from ..utils.profiler import StepProfiler
+            prof = StepProfiler(exp.get("profile_dir") or ".", rank)
+            prof.start()
         timer.step_start()
-        loss = tr.train_step(step)
+        if prof is not None:
+            with prof.step_range(step):
+                loss = tr.train_step(step)
+        else:
+            loss = tr.train_step(step)
         prev = pending.push(loss)
         fence.step()
         timer.step_stop()
+        if prof is not None and step + 1 == prof_span[1]:
+            prof.stop()
+            prof = None
         if prev is not None:
             losses.append(prev)
             log.event(ml.TRAIN_LOSS, prev, metadata={"samples_count": step * bpg * world})

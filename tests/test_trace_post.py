@@ -70,3 +70,19 @@ def test_run_loop_trace_carries_step_ranges(tmp_path):
     rep = postprocess(glob.glob(str(tmp_path / "trace_rank0.json*"))[0], out=str(tmp_path / "fixed.json"), drop_lead_in=False)
     steps = [s["step"] for s in rep["report"]["steps"]]
     assert steps and set(steps) <= {1, 2, 3} and rep["report"]["median_wall_us"] > 0
+
+
+def test_hstu_loop_trace_carries_step_ranges(tmp_path):
+    import glob
+    import io
+
+    from mlperf_training_b200.trainer.hstu import run
+    from mlperf_training_b200.utils.trace_post import postprocess
+    e = dict(batch_per_gpu=4, train_steps=5, eval_interval_steps=0, num_eval_batches=0, profile_step_start=1, profile_step_end=4,
+             profile_dir=str(tmp_path),
+             model=dict(layers=1, dim=32, heads=2, d_qk=16, d_v=16, max_seq_len=48, dtype="fp32", mlp_hidden=16, num_positions=64,
+                        num_time_buckets=32),
+             embedding=dict(rows=200, dim=16), data=dict(length_median=12, length_min=4, length_max=40))
+    run(e, device="cpu", stream=io.StringIO())
+    rep = postprocess(glob.glob(str(tmp_path / "trace_rank0.json*"))[0], out=str(tmp_path / "fixed.json"), drop_lead_in=False)
+    assert [s["step"] for s in rep["report"]["steps"]] == [2, 3]          # the first profiled step is the lead-in
