@@ -190,6 +190,9 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         mesh = Mesh(MeshSpec(cp=sp_size))
         sp_group, dp_rank, dp_world = mesh.group("cp"), mesh.index("dp"), mesh.size("dp")
     replicate = int((exp.get("fsdp") or {}).get("dp_replicate", 1) or 1)
+    if int((exp.get("fsdp") or {}).get("reshard_after_forward", 0) or 0) and rank == 0:
+        print("[parallel] fsdp.reshard_after_forward: 1 ignored - this trainer shards the optimizer state and keeps the "
+              "parameters gathered (the setting of the reference's submission, reshard_after_forward: 0)", flush=True)
     shard_group = rep_group = None
     if replicate > 1 and world > 1:
         # hybrid sharding: optimizer state sharded inside a group of world / replicate ranks, replicated across groups
