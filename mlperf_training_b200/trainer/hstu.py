@@ -114,7 +114,7 @@ def hstu_bucket_of(name: str) -> str:
 class HSTUTrainer:
     def __init__(self, cfg: HSTUConfig, table_rows: int, batch_per_gpu: int, device, *, dense_lr=1e-3, sparse_lr=1e-2,
                  clip_grad=1.0, emb_comm="nccl", dense_comm="nccl", seed=0, data_kw: dict | None = None, group=None,
-                 table_set: str | None = None, table_scale: int = 1, column_wise: tuple = ()):
+                 table_set: str | None = None, table_scale: int = 1, column_wise: tuple = (), row_wise_min_bytes: int = 1 << 30):
         """``table_set="yambda"``: the multi-table form - an ``EmbeddingCollection`` over the benchmark's eleven tables
         (item / artist / album ids, user id, seven hashed crosses; rows divided by ``table_scale``), batches that carry
         keyed jagged features, a model with the additional-feature branch and the contextual tokens
@@ -136,7 +136,8 @@ class HSTUTrainer:
             if cfg.extra_features != 2 or cfg.contextual != n_ctx:
                 raise ValueError(f"the yambda table set needs a model with extra_features=2 and contextual={n_ctx}")
             from ..parallel.embedding_collection import plan_tables
-            plan = plan_tables(tables, self.world, column_wise=tuple(column_wise)) if column_wise else None
+            # tables of at least row_wise_min_bytes are cut by rows over all ranks, smaller ones go whole to one rank
+            plan = plan_tables(tables, self.world, row_wise_min_bytes=int(row_wise_min_bytes), column_wise=tuple(column_wise))
             self.table = EmbeddingCollection(tables, group=group, device=self.device, lr=sparse_lr, seed=seed, comm=emb_comm, plan=plan)
             self.ctx_keys = [t.name for t in tables if t.name == "uid" or t.name.startswith("cross_")]
             data_kw.pop("kind", None)
@@ -453,7 +454,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                      sparse_lr=float(exp.get("sparse_lr", 1e-2)), clip_grad=float(exp.get("clip_grad", 1.0)),
                      emb_comm=exp.get("emb_a2a", "nccl"), seed=int(exp.get("seed", 0)), data_kw=data_kw,
                      table_set=table_set, table_scale=int(emb.get("table_scale", 1) or 1),
-                     column_wise=tuple(emb.get("column_wise") or ()))
+                     column_wise=tuple(emb.get("column_wise") or ()),
+                     row_wise_min_bytes=int(float(emb.get("row_wise_min_bytes", 1 << 30) or (1 << 30))))
     timeline.mark("model_table_data")
     tr.lr_warmup_steps = int(exp.get("lr_warmup_steps", 0) or 0)
     if hasattr(tr.data, "readahead"):

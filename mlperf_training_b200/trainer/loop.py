@@ -101,6 +101,10 @@ class RunConfig:
     @staticmethod
     def from_dict(d: dict) -> "RunConfig":
         known = {f for f in RunConfig.__dataclass_fields__}
+        unknown = sorted(k for k in d if k not in known)
+        if unknown:
+            import warnings
+            warnings.warn(f"run configuration: keys without a meaning here are ignored: {unknown}", stacklevel=2)
         return RunConfig(**{k: v for k, v in d.items() if k in known})
 
 
