@@ -429,6 +429,28 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
                      contextualized_mlp=str(m.get("contextualized_mlp", "simple")),
                      pmlp_contextual_dropout=float(m.get("pmlp_contextual_dropout", 0.0)),
                      num_positions=int(m.get("num_positions", 8192)), num_time_buckets=int(m.get("num_time_buckets", 2048)))
+    # every other field of the model configuration (stochastic depth, recent-window layers, postprocessor, tasks, dropouts,
+    # ...) can be named in the experiment file as well; keys that mean nothing are reported
+    from dataclasses import fields as _fields
+    _named = {"layers", "dim", "heads", "d_qk", "d_v", "max_seq_len", "dtype", "precision", "attn_precision", "mlp_hidden", "preprocessor",
+              "contextualized_mlp", "pmlp_contextual_dropout", "num_positions", "num_time_buckets"}
+    _policy_keys = {"fp8_scale_policy", "fp8_calibration_steps", "fp8_margin", "fp8_grad_refresh", "fp8_grad_margin"}
+    _types = {f.name: f.type for f in _fields(HSTUConfig)}
+    for k, v in m.items():
+        if k in _named or k in _policy_keys:
+            continue
+        if k not in _types or k in ("emb_dim", "name"):
+            import warnings
+            warnings.warn(f"hstu model configuration: key '{k}' has no meaning here and is ignored", stacklevel=2)
+            continue
+        cur = getattr(cfg, k)
+        if isinstance(cur, tuple):
+            v = tuple(tuple(x) if isinstance(x, list) else x for x in v)
+        elif isinstance(cur, bool):
+            v = bool(int(v)) if not isinstance(v, bool) else v
+        elif isinstance(cur, (int, float)):
+            v = type(cur)(v)
+        setattr(cfg, k, v)
     # per-tensor FP8 scale policy: "reference" = the recommender's recipe - forward sites calibrate for 4 steps (margin 1.5)
     # and freeze, gradient sites republish every 200 steps with margin 8; "rolling" = a 4-step delayed-scaling history
     policy = str(m.get("fp8_scale_policy", "rolling")).lower()

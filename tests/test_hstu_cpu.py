@@ -248,3 +248,20 @@ def test_hstu_loop_with_column_wise_tables_resumes_gloo(tmp_path):
                        env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("ok=True") == 2
+
+
+def test_experiment_file_reaches_every_model_field():
+    """Stochastic depth, recent-window layers, the postprocessor and the task list are set from the ``model`` section of
+    an experiment; a key that means nothing is reported, not silently dropped."""
+    import warnings
+    from mlperf_training_b200.trainer.hstu import run
+    e = _exp(train_steps=3, eval_interval_steps=0, num_eval_batches=0)
+    e["model"] = dict(e["model"], layers=3, sd_ratio=0.5, recent_window=8, recent_window_layers=1, postprocessor="l2",
+                      input_dropout=0.0, tasks=[["listen_plus", 1, "binary"], ["like", 2, "binary"]], bogus=1)
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        out = run(e, device="cpu", stream=io.StringIO())
+    c = out["trainer"].cfg
+    assert (c.sd_ratio, c.recent_window, c.recent_window_layers, c.postprocessor, c.input_dropout) == (0.5, 8, 1, "l2", 0.0)
+    assert c.tasks == (("listen_plus", 1, "binary"), ("like", 2, "binary")) and all(l == l for l in out["losses"])
+    assert any("'bogus'" in str(x.message) for x in w)
