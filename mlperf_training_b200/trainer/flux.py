@@ -177,6 +177,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     spec = dict(exp.get("model") or {})
     cfg = PRESETS[spec.pop("preset", "flux1-schnell")]()
     for k, v in spec.items():
+        if not hasattr(cfg, k):
+            raise KeyError(f"unknown model field '{k}'")
         setattr(cfg, k, tuple(v) if isinstance(v, list) else v)
     ratio = float(exp.get("grad_checkpoint_ratio", 0.0) or 0.0)
     if ratio > 0:
