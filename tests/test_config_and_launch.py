@@ -198,3 +198,21 @@ def test_hstu_experiment_file_with_on_disk_data_kinds(kind, tmp_path, monkeypatc
     if kind == "yambda":
         with pytest.raises(ValueError, match="too small"):
             cli.main(args + [f"modules.{module}.resolved.{o}" for o in over + ["embedding.rows=500"]])
+
+
+def test_launcher_reads_shared_settings_and_keeps_caller_values(tmp_path):
+    """``run_with_docker.sh`` in host mode for the workload whose system file sources a file of shared settings: the
+    shared values (experiment file, trainer mode, seed) arrive, the system file overrides them, the caller overrides
+    both, and the trial log is compliant."""
+    P = "modules.flux_trainer.resolved"
+    over = " ".join(f"{P}.{o}" for o in _SHIPPED["workloads/flux1/conf/flux.1_schnell_t2i-pretrain.yaml"][2])
+    env = dict(os.environ, DGXSYSTEM="B200_1x8x32", NGPU="1", NEXP="1", LOGDIR=str(tmp_path), CUDA_VISIBLE_DEVICES="", LR="1e-3",
+               PYTHONPATH=str(REPO), EXTRA_OVERRIDES="--device cpu " + over)
+    env.pop("SEED", None)
+    res = subprocess.run(["bash", str(REPO / "workloads/flux1/run_with_docker.sh")], env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    assert "compliance: SUCCESS" in res.stdout and "RESULT,flux1,," in res.stdout and "seed 10007" in res.stdout
+    recs = parse_log(res.stdout)
+    lr = [r["value"] for r in recs if r["key"] == "opt_base_learning_rate"]
+    gbs = [r["value"] for r in recs if r["key"] == "global_batch_size"]
+    assert lr == [1e-3] and gbs == [2]            # the caller's LR beats the file's 2.5e-4; the override beats GBS=256

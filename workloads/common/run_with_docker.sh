@@ -22,18 +22,39 @@ WDIR="${REPO}/workloads/${WORKLOAD}"
 CONFIG_FILE="${WDIR}/config_${DGXSYSTEM}.sh"
 [ -f "${CONFIG_FILE}" ] || { echo "missing ${CONFIG_FILE}" >&2; exit 1; }
 
-# config values are defaults: keep anything the caller already exported
-_apply_config_defaults() {
-  local line key val
+# a system file may pull in a file of shared settings (source ".../config_common.sh"): the files to read, in order
+CONFIG_FILES=()
+_collect_config_files() {
+  local line inc
   while IFS= read -r line; do
-    [[ "${line}" =~ ^[[:space:]]*(export[[:space:]]+)?([A-Za-z_][A-Za-z0-9_]*)=(.*)$ ]] || continue
-    key="${BASH_REMATCH[2]}"
-    if [ -z "${!key+x}" ]; then
-      eval "export ${key}=${BASH_REMATCH[3]}"
+    if [[ "${line}" =~ ^[[:space:]]*(source|\.)[[:space:]].*[/\"]([A-Za-z0-9_.-]+\.sh)\"?[[:space:]]*$ ]]; then
+      inc="$(dirname "$1")/${BASH_REMATCH[2]}"
+      [ -f "${inc}" ] && _collect_config_files "${inc}"
     fi
   done < "$1"
+  CONFIG_FILES+=("$1")
 }
-_apply_config_defaults "${CONFIG_FILE}"
+_collect_config_files "${CONFIG_FILE}"
+
+# config values are defaults: keep anything the caller already exported.  A later file (the system file) overrides an
+# earlier one (the shared settings), as it would when sourced.
+_apply_config_defaults() {
+  local line key f
+  declare -A from_caller=()
+  for f in "${CONFIG_FILES[@]}"; do
+    while IFS= read -r line; do
+      [[ "${line}" =~ ^[[:space:]]*(export[[:space:]]+)?([A-Za-z_][A-Za-z0-9_]*)=(.*)$ ]] || continue
+      key="${BASH_REMATCH[2]}"
+      if [ -z "${from_caller[${key}]+x}" ]; then
+        if [ -n "${!key+x}" ] && [ -z "${_set_by_config[${key}]+x}" ]; then from_caller[${key}]=1; continue; fi
+        eval "export ${key}=${BASH_REMATCH[3]}"
+        _set_by_config[${key}]=1
+      fi
+    done < "${f}"
+  done
+}
+declare -A _set_by_config=()
+_apply_config_defaults
 
 : "${NEXP:=1}"
 : "${LOGDIR:=${REPO}/results/${WORKLOAD}}"
@@ -55,9 +76,11 @@ run_in() {  # run a command on the host or inside the container
 _env_args=()
 if [ -n "${CONT}" ]; then
   # forward every variable the config file names plus the launcher's own
-  while IFS= read -r line; do
-    [[ "${line}" =~ ^[[:space:]]*(export[[:space:]]+)?([A-Za-z_][A-Za-z0-9_]*)= ]] && _env_args+=("-e" "${BASH_REMATCH[2]}")
-  done < "${CONFIG_FILE}"
+  for _f in "${CONFIG_FILES[@]}"; do
+    while IFS= read -r line; do
+      [[ "${line}" =~ ^[[:space:]]*(export[[:space:]]+)?([A-Za-z_][A-Za-z0-9_]*)= ]] && _env_args+=("-e" "${BASH_REMATCH[2]}")
+    done < "${_f}"
+  done
   _env_args+=(-e WORKLOAD -e DGXSYSTEM -e SEED -e LOGDIR=/results -e DATADIR=/data)
   docker rm -f "${CONT_NAME}" >/dev/null 2>&1 || true
   docker run --gpus all --rm --detach --name "${CONT_NAME}" --ipc=host --ulimit memlock=-1 --ulimit stack=67108864 \
