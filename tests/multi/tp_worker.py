@@ -25,7 +25,6 @@ def main():
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     device = torch.device("cuda", torch.cuda.current_device()) if gpu else torch.device("cpu")
     dist.init_process_group(backend)
-    me = dist.new_group([rank]) if False else None
     solo = [dist.new_group([r]) for r in range(world)][rank]          # data-parallel group of one
     heads, kv = max(4, world), max(2, world)              # every rank needs at least one query and one kv head
     hd = 64 if gpu else 16
