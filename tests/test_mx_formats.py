@@ -204,3 +204,16 @@ def test_deoscillator_state_survives_a_resume(tmp_path):
     out = run(dict(e, die_at_step=0), device="cpu", stream=io.StringIO())
     assert out["steps"] == 4 and out["deosc_history"] == ref["deosc_history"]         # same count snapped at the same step
     assert max(abs(a - b) for a, b in zip(out["losses"], ref["losses"][2:])) < 1e-5
+
+
+def test_deoscillation_keeps_replicas_identical_gloo():
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29679",
+                        os.path.join(root, "tests", "multi", "deosc_worker.py")], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("ok=True") == 2
