@@ -240,3 +240,18 @@ def load_experiment(path: str | os.PathLike, env: Mapping[str, str] | None = Non
     if overrides:
         apply_cli_overrides(cfg, overrides)
     return cfg
+
+
+def warn_unknown_keys(exp: dict, run_fn, what: str) -> list:
+    """Warn about top-level keys of ``exp`` that ``run_fn`` never looks up (``exp.get("key")`` / ``exp["key"]`` in its
+    source): a misspelt key otherwise falls back to its default without a word.  Returns the unknown keys."""
+    import inspect
+    import re
+    import warnings
+    src = inspect.getsource(run_fn)
+    known = set(re.findall(r'exp\.get\(\s*"(\w+)"', src)) | set(re.findall(r'exp\["(\w+)"\]', src))
+    unknown = sorted(k for k in exp if k not in known)
+    if unknown:
+        warnings.warn(f"{what}: keys without a meaning here are ignored: {unknown}", stacklevel=3)
+    return unknown
+

@@ -163,6 +163,9 @@ class FluxTrainer:
 
 def run(exp: dict, device: str | None = None, stream=None) -> dict:
     rank = dist.get_rank() if dist.is_initialized() else 0
+    if rank == 0:
+        from ..config.loader import warn_unknown_keys
+        warn_unknown_keys(exp, run, "flux experiment")
     world = dist.get_world_size() if dist.is_initialized() else 1
     device = device or ("cuda" if torch.cuda.is_available() else "cpu")
     sync = dist.barrier if world > 1 else None

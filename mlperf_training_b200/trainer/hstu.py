@@ -407,6 +407,9 @@ def _warmup(tr: "HSTUTrainer", steps: int) -> None:
 
 def run(exp: dict, device: str | None = None, stream=None) -> dict:
     rank = dist.get_rank() if dist.is_initialized() else 0
+    if rank == 0:
+        from ..config.loader import warn_unknown_keys
+        warn_unknown_keys(exp, run, "hstu experiment")
     from ..utils.metrics import StartupTimeline
     timeline = StartupTimeline()
     world = dist.get_world_size() if dist.is_initialized() else 1

@@ -216,3 +216,17 @@ def test_launcher_reads_shared_settings_and_keeps_caller_values(tmp_path):
     lr = [r["value"] for r in recs if r["key"] == "opt_base_learning_rate"]
     gbs = [r["value"] for r in recs if r["key"] == "global_batch_size"]
     assert lr == [1e-3] and gbs == [2]            # the caller's LR beats the file's 2.5e-4; the override beats GBS=256
+
+
+def test_misspelt_experiment_keys_are_reported():
+    import warnings
+    from mlperf_training_b200.config.loader import warn_unknown_keys
+    from mlperf_training_b200.trainer import flux, hstu
+    for path, module, fn in (("workloads/hstu/conf/hstu_yambda.yaml", "hstu_trainer", hstu.run),
+                             ("workloads/flux1/conf/flux.1_schnell_t2i-pretrain.yaml", "flux_trainer", flux.run)):
+        resolved = loader.load_experiment(REPO / path, env={})["modules"][module]["resolved"]
+        with warnings.catch_warnings(record=True) as w:
+            warnings.simplefilter("always")
+            assert warn_unknown_keys(resolved, fn, "experiment") == [] and not w          # every shipped key is read
+            assert warn_unknown_keys(dict(resolved, trian_steps=3), fn, "experiment") == ["trian_steps"]
+            assert len(w) == 1 and "trian_steps" in str(w[0].message)
