@@ -3,6 +3,8 @@
     python -m mlperf_training_b200.trainer.cli pretrain  --config <experiment.yaml> [key=value ...]
     python -m mlperf_training_b200.trainer.cli posttrain --config <experiment.yaml> [key=value ...]
     python -m mlperf_training_b200.trainer.cli hstu      --config <experiment.yaml> [key=value ...]
+    python -m mlperf_training_b200.trainer.cli flux      --config <experiment.yaml> [key=value ...]
+    python -m mlperf_training_b200.trainer.cli <mode>    --config <experiment.yaml> --print-config   # what would run
 
 The experiment YAML is resolved with ``${ENV:default}`` substitution and ``key=value`` overrides
 (the reference's ``primus-cli direct -- train pretrain --config $EXP`` surface,
@@ -21,6 +23,7 @@ def main(argv=None) -> int:
     ap.add_argument("mode", choices=["pretrain", "posttrain", "hstu", "flux"])
     ap.add_argument("--config", required=True)
     ap.add_argument("--device", default=None)
+    ap.add_argument("--print-config", action="store_true", help="print the resolved experiment of this trainer and exit")
     ap.add_argument("overrides", nargs="*")
     args = ap.parse_intermixed_args(argv)      # key=value overrides may follow the options
 
@@ -41,6 +44,10 @@ def main(argv=None) -> int:
     exp = load_experiment(args.config, overrides=args.overrides)
     module = {"pretrain": "pre_trainer", "posttrain": "post_trainer", "hstu": "hstu_trainer", "flux": "flux_trainer"}[args.mode]
     resolved = (exp.get("modules") or {}).get(module, {}).get("resolved") or exp
+    if args.print_config:
+        import yaml
+        print(yaml.safe_dump(resolved, sort_keys=False, default_flow_style=False))
+        return 0
     from ..parallel import health
     try:
         if args.mode == "pretrain":

@@ -230,3 +230,13 @@ def test_misspelt_experiment_keys_are_reported():
             assert warn_unknown_keys(resolved, fn, "experiment") == [] and not w          # every shipped key is read
             assert warn_unknown_keys(dict(resolved, trian_steps=3), fn, "experiment") == ["trian_steps"]
             assert len(w) == 1 and "trian_steps" in str(w[0].message)
+
+
+def test_cli_prints_the_resolved_experiment(capsys, monkeypatch):
+    import yaml
+    from mlperf_training_b200.trainer import cli
+    monkeypatch.setenv("GBS", "64")
+    rc = cli.main(["pretrain", "--config", str(REPO / "workloads/llama31_8b/conf/llama3.1_8B-pretrain-mxfp8.yaml"), "--print-config",
+                   "modules.pre_trainer.resolved.lr=0.5"])
+    got = yaml.safe_load(capsys.readouterr().out)
+    assert rc == 0 and got["global_batch"] == 64 and got["lr"] == 0.5 and got["model"]["precision"] == "mxfp8"
