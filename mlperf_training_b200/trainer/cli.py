@@ -48,6 +48,10 @@ def main(argv=None) -> int:
         import yaml
         print(yaml.safe_dump(resolved, sort_keys=False, default_flow_style=False))
         return 0
+    if os.environ.get("SELF_CHECK", "0") not in ("", "0"):
+        # kernels against their eager oracle before anything is timed; a disagreement stops the run here
+        from ..ops.selfcheck import run_selfcheck
+        run_selfcheck(args.device or ("cuda" if torch.cuda.is_available() else "cpu"), verbose=int(os.environ.get("RANK", "0")) == 0)
     from ..parallel import health
     try:
         if args.mode == "pretrain":

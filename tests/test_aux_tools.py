@@ -132,3 +132,23 @@ def test_startup_timeline_phases():
     t = StartupTimeline(clock=lambda: next(ticks))
     assert t.mark("model") == 1.5 and t.mark("warmup") == 2.5
     assert t.report() == {"phases": {"model": 1.5, "warmup": 2.5}, "total_s": 4.0}
+
+
+def test_startup_selfcheck_runs_and_fails_closed(monkeypatch):
+    from mlperf_training_b200.ops import kernels as K
+    from mlperf_training_b200.ops import selfcheck
+    rep = selfcheck.run_selfcheck("cpu")
+    assert set(rep) >= {"gemm", "block-scaled gemm", "attention", "cross entropy"} and max(rep.values()) == 0.0
+    assert selfcheck.main(["--device", "cpu"]) == 0
+    # a kernel that disagrees with its oracle stops the run
+    real = K.swiglu_fwd
+    calls = {"n": 0}
+
+    def broken(gu):
+        calls["n"] += 1
+        out = real(gu)
+        return out * 1.5 if calls["n"] % 2 == 1 else out           # the "device" side is off by 50 %
+    monkeypatch.setattr(K, "swiglu_fwd", broken)
+    import pytest
+    with pytest.raises(RuntimeError, match="swiglu"):
+        selfcheck.run_selfcheck("cpu")
