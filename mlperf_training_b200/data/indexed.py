@@ -97,6 +97,9 @@ class GPTSampleDataset:
         self.total = int(sum(self.per_set))
         if self.total == 0:
             raise ValueError("dataset shorter than one sample")
+        # a prefix shorter than one sample contributes nothing, whatever its weight
+        self.weights = np.where(np.array(self.per_set) > 0, self.weights, 0.0)
+        self.weights = self.weights / self.weights.sum()
         self.seed = seed
         # blended order: set index per sample drawn by weight, then a running cursor per set
         rng = np.random.default_rng(seed)

@@ -142,3 +142,34 @@ def test_embedding_plan_places_every_table_once(world, sizes, cut):
     small = sorted((t.bytes() for t in tabs if world > 1 and t.bytes() < cut * 128), reverse=True)
     if small:
         assert max(load) - min(load) <= small[0]                        # greedy by size: ranks differ by at most the largest table
+
+
+@settings(max_examples=15, deadline=None)
+@given(seed=st.integers(0, 1000), seq=st.sampled_from([8, 16, 33]), n_docs=st.integers(1, 12), world=st.sampled_from([1, 2, 4]))
+def test_blended_token_dataset_properties(tmp_path_factory, seed, seq, n_docs, world):
+    import numpy as np
+    from mlperf_training_b200.data.indexed import GPTSampleDataset, write_indexed_dataset
+    root = tmp_path_factory.mktemp("idx")
+    rng = np.random.default_rng(seed)
+    big = [rng.integers(0, 1000, size=int(rng.integers(seq, 6 * seq))).astype(np.int32) for _ in range(n_docs + 3)]
+    tiny = [np.arange(3, dtype=np.int32)]                                     # shorter than one sample
+    write_indexed_dataset(str(root / "a"), big)
+    write_indexed_dataset(str(root / "b"), tiny)
+    if sum(len(d) for d in big) <= seq:
+        return
+    ds = GPTSampleDataset([str(root / "a"), str(root / "b")], [0.5, 0.5], seq, seed=seed)
+    stream = np.concatenate(big)
+    assert len(ds) == (len(stream) - 1) // seq and set(ds.order_set.tolist()) == {0}     # the short prefix is never drawn
+    seen = set()
+    for i in range(len(ds)):
+        s = ds.sample(i)
+        j = int(ds.order_idx[i])
+        assert s.shape == (seq + 1,) and np.array_equal(s, stream[j * seq:j * seq + seq + 1])
+        seen.add(j)
+    assert seen == set(range(len(ds)))                                       # an epoch visits every window once
+    again = GPTSampleDataset([str(root / "a"), str(root / "b")], [0.5, 0.5], seq, seed=seed)
+    assert np.array_equal(again.order_idx, ds.order_idx)                     # a pure function of the seed
+    # the ranks of a step read consecutive, disjoint samples
+    got = [ds.batch(3, r, world, 2) for r in range(world)]
+    want = [ds.sample((3 * world + r) * 2 + k) for r in range(world) for k in range(2)]
+    assert np.array_equal(np.concatenate([g.numpy() for g in got]), np.stack(want))
