@@ -173,3 +173,40 @@ def test_blended_token_dataset_properties(tmp_path_factory, seed, seq, n_docs, w
     got = [ds.batch(3, r, world, 2) for r in range(world)]
     want = [ds.sample((3 * world + r) * 2 + k) for r in range(world) for k in range(2)]
     assert np.array_equal(np.concatenate([g.numpy() for g in got]), np.stack(want))
+
+
+@settings(max_examples=8, deadline=None)
+@given(seed=st.integers(0, 1000), world=st.sampled_from([1, 2, 3]), batch=st.sampled_from([2, 4]), max_history=st.sampled_from([12, 30]))
+def test_event_store_stream_properties(tmp_path_factory, seed, world, batch, max_history):
+    import numpy as np
+    from mlperf_training_b200.data.yambda import EventStoreDataset, write_synthetic_event_store
+    root = str(tmp_path_factory.mktemp("store"))
+    write_synthetic_event_store(root, 60, 50, 500, days=3, seed=seed)
+    kw = dict(max_history=max_history, min_history=4, holdout=0.2, salt=seed)
+    train, held = EventStoreDataset(root, batch, split="train", **kw), EventStoreDataset(root, batch, split="eval", **kw)
+    users_t, users_e = set(np.asarray(train.user)[train.anchors].tolist()), set(np.asarray(held.user)[held.anchors].tolist())
+    assert not users_t & users_e                                             # a user is on one side of the split
+    ts = np.asarray(train.ts)
+    steps = sum(train.batches_in_window(w, world) for w in range(train.num_windows))
+    if steps == 0:
+        return
+    seen = []
+    last_window = -1
+    for step in range(steps):
+        w = train.window_of_step(step, world)
+        assert w >= last_window                                              # windows are walked in time order
+        last_window = w
+        for rank in range(world):
+            anchors = train.step_anchors(step, rank, world)
+            b = train.batch_at(step, rank, world=world)
+            assert len(anchors) == batch and b["offsets"].numel() == batch + 1 and int(b["offsets"][-1]) == b["total"]
+            seen += anchors.tolist()
+            for i, a in enumerate(anchors.tolist()):
+                lo, hi = int(b["offsets"][i]), int(b["offsets"][i + 1])
+                t = b["timestamps"][lo:hi].numpy()
+                assert 1 <= hi - lo <= max_history + 1 and t[-1] == ts[a]   # the anchor is the sample's last event
+                assert int(np.asarray(train.kind)[a]) == 0                   # anchors are listens
+                u = int(np.asarray(train.user)[a])
+                assert int(train.uoff[u]) + 4 <= a                           # with at least min_history events before them
+    assert len(seen) == len(set(seen))                                       # no anchor is read twice in a pass
+    assert b["rows"] % 128 == 0 and b["rows"] >= b["total"]
