@@ -64,6 +64,8 @@ class ShardedEmbedding:
         self.lr, self.eps = lr, eps
         self.comm = comm if (self.world > 1 and self.device.type == "cuda") else "nccl"
         self.recv = None
+        import os
+        self._verify_left = int(os.environ.get("B200_VERIFY_FUSED_LOOKUP", "0") or 0)     # compare the first N fused lookups
         if self.comm == "fused":
             from .symm import SymmetricBuffer
             self.max_requests = max_requests
@@ -132,6 +134,17 @@ class ShardedEmbedding:
                       _lib.stream_ptr())
             self.recv.barrier()                                   # every owner's rows have landed
             rows_u = self.recv.local[: n_u * self.dim].view(n_u, self.dim).clone()
+            if self._verify_left > 0:
+                # first calls of a run, on request: the same rows through the library all-to-all, compared bit for bit
+                # (the reference arms its fused exchanges the same way: DLRM_HSTU_FP8_SEQ_A2A_FUSED_VERIFY,
+                # generative_recommenders/dlrm_v4/seq_a2a_rowperm.py:752-772)
+                self._verify_left -= 1
+                served = K.gather_rows(self.weight, local_idx)
+                ref = torch.empty_like(rows_u)
+                dist.all_to_all_single(ref, served, in_splits, out_splits, group=self.group)
+                if not torch.equal(ref, rows_u):
+                    raise RuntimeError(f"table {self.name}: the peer-store lookup differs from the all-to-all lookup "
+                                       f"({int((ref != rows_u).any(1).sum())} of {n_u} rows)")
         else:
             served = K.gather_rows(self.weight, local_idx)
             rows_u = torch.empty((uniq.numel(), self.dim), dtype=self.weight.dtype, device=ids.device)
