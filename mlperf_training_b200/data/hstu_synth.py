@@ -88,6 +88,45 @@ class HSTUSyntheticData:
         return {k: (v.to(device, non_blocking=True) if hasattr(v, "to") else v) for k, v in batch.items()}
 
 
+def yambda_features(b: dict, tables: dict, uid: torch.Tensor, artist_of: torch.Tensor | None = None,
+                    album_of: torch.Tensor | None = None) -> dict:
+    """``b`` (item ids, offsets, targets of a batch) plus the keyed jagged features of the Yambda table set: per token the
+    item, its artist and its album (``artist_of`` / ``album_of``: item -> id maps; without them an arithmetic map), per
+    sample the user id and seven hashed crosses of the user with the item / artist / album it met last.  Adds
+    ``samples`` (history features ``uih_*`` and candidate features) and ``token_row`` (row of every token inside the
+    [history rows | candidate rows] concatenation the lookups return).  ``tables``: ``{name: TableConfig}`` - the row
+    counts bound the ids."""
+    from .samples import KeyedJagged, Samples, hashed_cross
+    rows = {n: t.rows for n, t in tables.items()}
+    item = b["item_ids"] % rows["item_id"]
+    artist = (artist_of[b["item_ids"]] % rows["artist_id"] if artist_of is not None else item * 2654435761 % rows["artist_id"]).long()
+    album = (album_of[b["item_ids"]] % rows["album_id"] if album_of is not None else item * 40503 % rows["album_id"]).long()
+    offsets, nt = b["offsets"].long(), b["num_targets"].long()
+    B = nt.numel()
+    lens = offsets[1:] - offsets[:-1]
+    pos = torch.arange(int(b["total"]))
+    seq = torch.repeat_interleave(torch.arange(B), lens)
+    is_cand = (pos - offsets[:-1][seq]) >= (lens - nt)[seq]
+    hist_idx, cand_idx = torch.nonzero(~is_cand)[:, 0], torch.nonzero(is_cand)[:, 0]
+    uid = uid.long() % rows["uid"]
+    last_hist = (offsets[1:] - nt - 1).clamp(min=0)
+    crosses = {}
+    for k, other in enumerate((item, artist, album, item, artist, album, item)):
+        name = f"cross_{k}"
+        if name in rows:
+            crosses[name] = hashed_cross(uid, other[last_hist] + k, rows[name], salt=k)
+    one = torch.ones(B, dtype=torch.int64)
+    uih = KeyedJagged.from_dict({"uih_item_id": (item[hist_idx], lens - nt), "uih_artist_id": (artist[hist_idx], lens - nt),
+                                 "uih_album_id": (album[hist_idx], lens - nt), "uid": (uid, one),
+                                 **{n: (v, one) for n, v in crosses.items()}})
+    cand = KeyedJagged.from_dict({"item_id": (item[cand_idx], nt), "artist_id": (artist[cand_idx], nt),
+                                  "album_id": (album[cand_idx], nt)})
+    tok_row = torch.empty(int(b["total"]), dtype=torch.int64)
+    tok_row[hist_idx] = torch.arange(hist_idx.numel())
+    tok_row[cand_idx] = hist_idx.numel() + torch.arange(cand_idx.numel())
+    return dict(b, samples=Samples(uih, cand, {}), token_row=tok_row)
+
+
 class YambdaSyntheticSamples(HSTUSyntheticData):
     """Synthetic batches with the feature set of the Yambda benchmark tables: per token an item, its artist and its
     album; per sample a user id and hashed crosses of the user with what it listened to last - as a ``Samples`` of two
@@ -100,38 +139,10 @@ class YambdaSyntheticSamples(HSTUSyntheticData):
         super().__init__(self.tables["item_id"].rows, batch, **kw)
 
     def batch_at(self, step: int, rank: int = 0, pin: bool = False) -> dict:
-        from .samples import KeyedJagged, Samples, hashed_cross
         b = super().batch_at(step, rank, pin=False)
-        rows = {n: t.rows for n, t in self.tables.items()}
-        item = b["item_ids"]
-        artist = (item * 2654435761 % rows["artist_id"]).long()        # an item has one artist and one album
-        album = (item * 40503 % rows["album_id"]).long()
-        offsets, nt = b["offsets"].long(), b["num_targets"].long()
-        B = nt.numel()
-        lens = offsets[1:] - offsets[:-1]
-        pos = torch.arange(int(b["total"]))
-        seq = torch.repeat_interleave(torch.arange(B), lens)
-        is_cand = (pos - offsets[:-1][seq]) >= (lens - nt)[seq]
-        hist_idx, cand_idx = torch.nonzero(~is_cand)[:, 0], torch.nonzero(is_cand)[:, 0]
         g = torch.Generator().manual_seed((self.seed * 1000003 + step) * 4099 + rank + 17)
-        uid = torch.randint(0, rows["uid"], (B,), generator=g)
-        last_hist = (offsets[1:] - nt - 1).clamp(min=0)
-        crosses = {}
-        for k, other in enumerate((item, artist, album, item, artist, album, item)):
-            name = f"cross_{k}"
-            if name in rows:
-                crosses[name] = hashed_cross(uid, other[last_hist] + k, rows[name], salt=k)
-        one = torch.ones(B, dtype=torch.int64)
-        uih = KeyedJagged.from_dict({"uih_item_id": (item[hist_idx], lens - nt), "uih_artist_id": (artist[hist_idx], lens - nt),
-                                     "uih_album_id": (album[hist_idx], lens - nt), "uid": (uid, one),
-                                     **{n: (v, one) for n, v in crosses.items()}})
-        cand = KeyedJagged.from_dict({"item_id": (item[cand_idx], nt), "artist_id": (artist[cand_idx], nt),
-                                      "album_id": (album[cand_idx], nt)})
-        # row of every token inside the [history rows | candidate rows] concatenation the lookups return
-        tok_row = torch.empty(int(b["total"]), dtype=torch.int64)
-        tok_row[hist_idx] = torch.arange(hist_idx.numel())
-        tok_row[cand_idx] = hist_idx.numel() + torch.arange(cand_idx.numel())
-        out = dict(b, samples=Samples(uih, cand, {}), token_row=tok_row)
+        uid = torch.randint(0, self.tables["uid"].rows, (b["num_targets"].numel(),), generator=g)
+        out = yambda_features(b, self.tables, uid)
         if pin and torch.cuda.is_available():
             out = {k: (v.pin_memory() if hasattr(v, "pin_memory") else v) for k, v in out.items()}
         return out

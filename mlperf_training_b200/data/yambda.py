@@ -82,6 +82,10 @@ class EventStoreDataset:
             np.load(d / f"{n}.npy", mmap_mode="r") for n in ("user", "item", "ts", "kind", "played", "user_offsets"))
         self.batch, self.max_history, self.min_history = batch, max_history, min_history
         self.num_items = int(np.asarray(self.item).max()) + 1 if len(self.item) else 0     # the table must have this many rows
+        # optional item -> artist / album maps (``item_artist.npy`` / ``item_album.npy``, indexed by item id) for the
+        # multi-table feature set; without them the features fall back to an arithmetic map of the item id
+        self.item_artist = torch.from_numpy(np.load(d / "item_artist.npy").astype(np.int64)) if (d / "item_artist.npy").exists() else None
+        self.item_album = torch.from_numpy(np.load(d / "item_album.npy").astype(np.int64)) if (d / "item_album.npy").exists() else None
         self.contract = {"window_seconds": window_seconds, "holdout": holdout, "salt": salt}
         # anchors: listen events with enough history, of users on this side of the split
         pos_in_user = np.arange(len(self.user)) - np.asarray(self.uoff)[np.asarray(self.user)]
@@ -133,7 +137,8 @@ class EventStoreDataset:
         out = {"offsets": torch.from_numpy(offsets), "num_targets": torch.ones(len(anchors), dtype=torch.int32),
                "timestamps": torch.from_numpy(ts.astype(np.int64)), "actions": torch.from_numpy(actions),
                "item_ids": torch.from_numpy(ids.astype(np.int64)), "total": total, "rows": (total + 127) // 128 * 128,
-               "lengths": torch.from_numpy(lens)}
+               "lengths": torch.from_numpy(lens), "max_targets": 1,
+               "users": torch.from_numpy(np.asarray(self.user)[anchors].astype(np.int64))}
         if pin and torch.cuda.is_available():
             out = {k: (v.pin_memory() if torch.is_tensor(v) else v) for k, v in out.items()}
         return out

@@ -111,6 +111,27 @@ def hstu_bucket_of(name: str) -> str:
     return f"l{int(parts[1]):04d}" if parts[0] == "layers" else "a_misc"
 
 
+class _YambdaStoreView:
+    """An event-store stream whose batches carry the keyed jagged features of the eleven-table set: the store gives the
+    events (items, times, actions) and the user of every sample; artists, albums and the hashed crosses are derived per
+    batch (``data.hstu_synth.yambda_features``)."""
+
+    def __init__(self, inner, tables):
+        self.inner, self.tables = inner, {t.name: t for t in tables}
+        self.ds = inner.ds
+
+    def batch_at(self, step: int, rank: int = 0, pin: bool = False) -> dict:
+        from ..data.hstu_synth import yambda_features
+        b = self.inner.batch_at(step, rank, pin=False)
+        out = yambda_features(b, self.tables, b["users"], self.ds.item_artist, self.ds.item_album)
+        if pin and torch.cuda.is_available():
+            out = {k: (v.pin_memory() if hasattr(v, "pin_memory") else v) for k, v in out.items()}
+        return out
+
+    def __getattr__(self, name):
+        return getattr(self.inner, name)
+
+
 class HSTUTrainer:
     def __init__(self, cfg: HSTUConfig, table_rows: int, batch_per_gpu: int, device, *, dense_lr=1e-3, sparse_lr=1e-2,
                  clip_grad=1.0, emb_comm="nccl", dense_comm="nccl", seed=0, data_kw: dict | None = None, group=None,
@@ -140,12 +161,16 @@ class HSTUTrainer:
             plan = plan_tables(tables, self.world, row_wise_min_bytes=int(row_wise_min_bytes), column_wise=tuple(column_wise))
             self.table = EmbeddingCollection(tables, group=group, device=self.device, lr=sparse_lr, seed=seed, comm=emb_comm, plan=plan)
             self.ctx_keys = [t.name for t in tables if t.name == "uid" or t.name.startswith("cross_")]
-            data_kw.pop("kind", None)
-            import inspect
-            known = set(inspect.signature(HSTUSyntheticData.__init__).parameters)
-            self.data = YambdaSyntheticSamples(tables, batch_per_gpu, seed=seed, **{k: v for k, v in data_kw.items() if k in known})
-            self.eval_data = None
-            data_kw = {"kind": "_done"}
+            self._yambda_tables = tables
+            if data_kw.get("kind", "synthetic") == "synthetic":
+                data_kw.pop("kind", None)
+                import inspect
+                known = set(inspect.signature(HSTUSyntheticData.__init__).parameters)
+                self.data = YambdaSyntheticSamples(tables, batch_per_gpu, seed=seed, **{k: v for k, v in data_kw.items() if k in known})
+                self.eval_data = None
+                data_kw = {"kind": "_done"}
+            elif data_kw.get("kind") != "yambda":
+                raise ValueError("the eleven-table feature set reads synthetic samples or an event store (data.kind: yambda)")
         else:
             self.table = ShardedEmbedding(table_rows, cfg.emb_dim, group=group, device=self.device, dtype=cfg.torch_dtype(),
                                           lr=sparse_lr, seed=seed, comm=emb_comm, init_scale=0.05)
@@ -171,7 +196,10 @@ class HSTUTrainer:
             data_kw = only(EventStoreDataset, data_kw)
             self.data = _WorldView(EventStoreDataset(root, batch_per_gpu, split="train", **data_kw), self.world)
             self.eval_data = _WorldView(EventStoreDataset(root, batch_per_gpu, split="eval", **data_kw), self.world)
-            if self.data.ds.num_items > table_rows:
+            if table_set == "yambda":
+                # ids are folded into the tables' row counts (the benchmark's tables are as large as its id ranges)
+                self.data, self.eval_data = _YambdaStoreView(self.data, self._yambda_tables), _YambdaStoreView(self.eval_data, self._yambda_tables)
+            elif self.data.ds.num_items > table_rows:
                 raise ValueError(f"the event store under {root} holds item ids up to {self.data.ds.num_items - 1}: "
                                  f"embedding.rows = {table_rows} is too small")
         elif kind != "_done":

@@ -265,3 +265,30 @@ def test_experiment_file_reaches_every_model_field():
     assert (c.sd_ratio, c.recent_window, c.recent_window_layers, c.postprocessor, c.input_dropout) == (0.5, 8, 1, "l2", 0.0)
     assert c.tasks == (("listen_plus", 1, "binary"), ("like", 2, "binary")) and all(l == l for l in out["losses"])
     assert any("'bogus'" in str(x.message) for x in w)
+
+
+def test_event_store_feeds_the_eleven_table_feature_set(tmp_path):
+    """Event store + ``embedding.tables: yambda``: every batch carries the keyed jagged features (item / artist / album per
+    token from the store's item maps, user id and hashed crosses per sample) and the loop trains and evaluates on them."""
+    import numpy as np
+    from mlperf_training_b200.data.yambda import write_synthetic_event_store
+    from mlperf_training_b200.trainer.hstu import run
+    root = tmp_path / "store"
+    write_synthetic_event_store(str(root), 80, 60, 3000, days=3, seed=2)
+    rng = np.random.default_rng(0)
+    np.save(root / "item_artist.npy", rng.integers(0, 500, size=3000))
+    np.save(root / "item_album.npy", rng.integers(0, 900, size=3000))
+    e = _exp(train_steps=4, eval_interval_steps=2, num_eval_batches=1, batch_per_gpu=4,
+             embedding=dict(dim=16, tables="yambda", table_scale=2000), data=dict(kind="yambda", path=str(root), min_history=4, max_history=30))
+    out = run(e, device="cpu", stream=io.StringIO())
+    assert len(out["losses"]) >= 3 and all(l == l for l in out["losses"])
+    tr = out["trainer"]
+    b = tr.data.batch_at(0, 0)
+    uih, cand = b["samples"].uih, b["samples"].candidates
+    rows = {t.name: t.rows for t in tr.table.configs}
+    art, alb = torch.from_numpy(np.load(root / "item_artist.npy")), torch.from_numpy(np.load(root / "item_album.npy"))
+    hist = ~torch.isin(torch.arange(b["total"]), b["offsets"][1:].long() - 1)            # one candidate per sample: its last event
+    raw = b["item_ids"]
+    assert torch.equal(uih["uih_item_id"][0], raw[hist] % rows["item_id"]) and torch.equal(cand["item_id"][0], raw[~hist] % rows["item_id"])
+    assert torch.equal(uih["uih_artist_id"][0], art[raw[hist]] % rows["artist_id"]) and torch.equal(cand["album_id"][0], alb[raw[~hist]] % rows["album_id"])
+    assert torch.equal(uih["uid"][0], b["users"] % rows["uid"]) and all(int(uih[f"cross_{k}"][0].max()) < rows[f"cross_{k}"] for k in range(7))
