@@ -1,6 +1,7 @@
 """Dataset preparation utilities (the reference's ``scripts/`` of each workload):
 
     python -m mlperf_training_b200.data.prep convert-sft  <in.jsonl|in.parquet> <out.npy> [--seq-len 8192]
+    python -m mlperf_training_b200.data.prep convert-events <processed_dir> <store_root> [--metadata-dir <dir>]
     python -m mlperf_training_b200.data.prep metadata     <packed.npy> <packed_metadata.jsonl>
     python -m mlperf_training_b200.data.prep hash         <directory>
     python -m mlperf_training_b200.data.prep verify       <directory> <checksums.md5>
@@ -239,6 +240,8 @@ def main(argv=None) -> int:
     q = sub.add_parser("synthetic-sequences"); q.add_argument("path"); q.add_argument("--users", type=int, default=10_000)
     q.add_argument("--items", type=int, default=100_000); q.add_argument("--kind", default="movielens", choices=["movielens", "kuairand"])
     q.add_argument("--min-len", type=int, default=8); q.add_argument("--max-len", type=int, default=200); q.add_argument("--seed", type=int, default=0)
+    cv = sub.add_parser("convert-events"); cv.add_argument("processed_dir"); cv.add_argument("root")
+    cv.add_argument("--metadata-dir", default=None); cv.add_argument("--listen-plus-threshold", type=float, default=50.0)
     d = sub.add_parser("download"); d.add_argument("manifest"); d.add_argument("dest")
     f = sub.add_parser("hf-to-torch-dist"); f.add_argument("hf_dir"); f.add_argument("out_root")
     f.add_argument("--preset", default="llama2-70b"); f.add_argument("--dtype", default="bf16")
@@ -252,6 +255,10 @@ def main(argv=None) -> int:
         from .yambda import write_synthetic_event_store
         n = write_synthetic_event_store(a.root, a.users, a.events_per_user, a.items, days=a.days, seed=a.seed)
         print(f"{n} events of {a.users} users -> {a.root}")
+    elif a.cmd == "convert-events":
+        from .yambda import convert_sessions
+        n = convert_sessions(a.processed_dir, a.metadata_dir, a.root, a.listen_plus_threshold)
+        print(f"{n} events -> {a.root}")
     elif a.cmd == "synthetic-sequences":
         from .sequences import write_synthetic_sequences
         write_synthetic_sequences(a.path, a.users, a.items, min_len=a.min_len, max_len=a.max_len, seed=a.seed, kind=a.kind)

@@ -45,6 +45,36 @@ def write_event_store(root: str, user: np.ndarray, item: np.ndarray, ts: np.ndar
         np.save(d / f"{name}.npy", arr)
 
 
+def convert_sessions(processed_dir: str, metadata_dir: str | None, root: str, listen_plus_threshold: float = 50.0) -> int:
+    """The preprocessed public data of the reference -> an event store under ``root``.
+
+    ``processed_dir/train_sessions.parquet`` holds one row per session with list columns ``item_ids``, ``timestamps``,
+    ``event_types`` (0 listen, 1 like, others), ``played_ratio_pct`` beside ``uid`` / ``session_id``
+    (generative_recommenders/dlrm_v4/datasets/yambda.py:156-212); ``metadata_dir/{artist,album}_item_mapping.parquet`` map an
+    ``item_id`` to its ``artist_id`` / ``album_id`` (``:623-636``).  Events keep their type (listens stay anchors whatever
+    their played ratio); ``played`` is 1 for a listen played for at least ``listen_plus_threshold`` percent - the
+    listen-plus label.  Returns the number of events."""
+    import pandas as pd
+    df = pd.read_parquet(Path(processed_dir) / "train_sessions.parquet").sort_values(["uid", "session_id"], kind="stable")
+    lens = df["item_ids"].map(len).to_numpy()
+    user = np.repeat(df["uid"].to_numpy().astype(np.int64), lens)
+    flat = lambda c, dt: np.concatenate([np.asarray(v) for v in df[c]]).astype(dt) if len(df) else np.zeros(0, dt)
+    item, ts, kind = flat("item_ids", np.int64), flat("timestamps", np.int64), flat("event_types", np.int64)
+    ratio = np.nan_to_num(flat("played_ratio_pct", np.float32), nan=0.0)
+    played = ((kind == 0) & (ratio >= listen_plus_threshold)).astype(np.uint8)
+    write_event_store(root, user, item, ts, kind.clip(0, 255), played)
+    if metadata_dir is not None:
+        n_items = int(item.max()) + 1 if len(item) else 0
+        for name in ("artist", "album"):
+            f = Path(metadata_dir) / f"{name}_item_mapping.parquet"
+            if f.exists():
+                m = pd.read_parquet(f)
+                table = np.zeros(max(n_items, int(m["item_id"].max()) + 1), dtype=np.int64)
+                table[m["item_id"].to_numpy()] = m[f"{name}_id"].to_numpy()
+                np.save(Path(root) / f"item_{name}.npy", table)
+    return int(len(user))
+
+
 def write_synthetic_event_store(root: str, users: int, events_per_user: int, items: int, *, days: int = 7,
                                 zipf_alpha: float = 1.05, seed: int = 0) -> int:
     """A random event store for runs without the real data: item popularity follows a bounded Zipf

@@ -292,3 +292,41 @@ def test_event_store_feeds_the_eleven_table_feature_set(tmp_path):
     assert torch.equal(uih["uih_item_id"][0], raw[hist] % rows["item_id"]) and torch.equal(cand["item_id"][0], raw[~hist] % rows["item_id"])
     assert torch.equal(uih["uih_artist_id"][0], art[raw[hist]] % rows["artist_id"]) and torch.equal(cand["album_id"][0], alb[raw[~hist]] % rows["album_id"])
     assert torch.equal(uih["uid"][0], b["users"] % rows["uid"]) and all(int(uih[f"cross_{k}"][0].max()) < rows[f"cross_{k}"] for k in range(7))
+
+
+def test_preprocessed_sessions_convert_to_an_event_store(tmp_path):
+    """``train_sessions.parquet`` (list columns per session) and the item -> artist / album parquets become an event store
+    whose samples carry the listen-plus label and the item maps."""
+    import numpy as np
+    import pandas as pd
+    from mlperf_training_b200.data import prep
+    from mlperf_training_b200.data.yambda import EventStoreDataset
+    rng = np.random.default_rng(0)
+    rows = []
+    for uid in range(12):
+        t = 1_600_000_000
+        for sess in range(3):
+            n = int(rng.integers(4, 9))
+            ts = t + np.cumsum(rng.integers(1, 300, size=n))
+            t = int(ts[-1]) + 4000
+            rows.append({"uid": uid, "session_id": sess, "item_ids": rng.integers(0, 50, size=n).tolist(), "timestamps": ts.tolist(),
+                         "event_types": rng.choice([0, 0, 0, 1, 2], size=n).tolist(), "is_organic": [1] * n,
+                         "played_ratio_pct": rng.choice([10.0, 49.0, 50.0, 100.0, np.nan], size=n).tolist()})
+    proc, meta = tmp_path / "processed", tmp_path / "meta"
+    proc.mkdir(), meta.mkdir()
+    pd.DataFrame(rows).sample(frac=1.0, random_state=1).to_parquet(proc / "train_sessions.parquet")     # rows in any order
+    pd.DataFrame({"item_id": np.arange(50), "artist_id": np.arange(50) // 5}).to_parquet(meta / "artist_item_mapping.parquet")
+    pd.DataFrame({"item_id": np.arange(50), "album_id": np.arange(50) // 2}).to_parquet(meta / "album_item_mapping.parquet")
+    assert prep.main(["convert-events", str(proc), str(tmp_path / "store"), "--metadata-dir", str(meta)]) == 0
+    ds = EventStoreDataset(str(tmp_path / "store"), 2, min_history=3, max_history=12, holdout=0.0)
+    n_events = sum(len(r["item_ids"]) for r in rows)
+    assert len(ds.item) == n_events and ds.item_artist.tolist() == (np.arange(50) // 5).tolist()
+    user = np.asarray(ds.user)
+    assert (np.diff(user) >= 0).all() and all((np.diff(np.asarray(ds.ts)[user == u]) >= 0).all() for u in range(12))
+    # listen-plus: a listen played for at least half; likes and other events carry no played flag
+    flat_kind = np.concatenate([np.asarray(r["event_types"]) for r in sorted(rows, key=lambda r: (r["uid"], r["session_id"]))])
+    flat_ratio = np.nan_to_num(np.concatenate([np.asarray(r["played_ratio_pct"], dtype=np.float32)
+                                               for r in sorted(rows, key=lambda r: (r["uid"], r["session_id"]))]))
+    assert np.array_equal(np.asarray(ds.kind), flat_kind) and np.array_equal(np.asarray(ds.played), ((flat_kind == 0) & (flat_ratio >= 50)).astype(np.uint8))
+    b = ds.batch_at(0)
+    assert b["item_ids"].numel() == b["total"] and set(b["users"].tolist()) <= set(range(12))
