@@ -128,6 +128,14 @@ class _YambdaStoreView:
             out = {k: (v.pin_memory() if hasattr(v, "pin_memory") else v) for k, v in out.items()}
         return out
 
+    @property
+    def readahead(self) -> int:
+        return self.inner.readahead
+
+    @readahead.setter
+    def readahead(self, n: int) -> None:
+        self.inner.readahead = n             # the store view underneath does the read-ahead
+
     def __getattr__(self, name):
         return getattr(self.inner, name)
 
