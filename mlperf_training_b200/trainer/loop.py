@@ -356,6 +356,9 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     if rc.precision_schedule:
         from ..ops.recipe import PrecisionSchedule
         sched = PrecisionSchedule.from_spec(rc.precision_schedule)
+        if tp_size > 1 and rank == 0:
+            print("[precision] the schedule governs the linears outside the tensor-parallel blocks; the tensor-parallel linears "
+                  f"keep the precision of their context ({tp_ctx.precision})", flush=True)
     deosc = None
     if sched is not None and sched.deosc.enabled:
         from ..ops.recipe import Deoscillator
