@@ -207,8 +207,6 @@ class Block(nn.Module):
         W = self.tp.world if self.tp is not None else 1
         if cfg.n_heads % W or cfg.n_kv_heads % W:
             raise ValueError(f"heads {cfg.n_heads}/{cfg.n_kv_heads} are not divisible by the tensor-parallel size {W}")
-        if self.tp is not None and cfg.n_experts:
-            raise ValueError("tensor parallelism is implemented for dense MLPs; shard experts with expert parallelism")
         self.hq, self.hkv = cfg.n_heads // W, cfg.n_kv_heads // W
         self.attn_norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
         self.w_qkv = nn.Parameter(torch.empty((self.hq + 2 * self.hkv) * hd, d, dtype=dtype, device=device))

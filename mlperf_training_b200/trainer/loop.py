@@ -215,11 +215,13 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         raise NotImplementedError("context parallelism combines with data and tensor parallelism here (dp_replicate = 1, "
                                   "world divisible by context_parallel x tensor_parallel)")
     tp_size = min(int(rc.tensor_parallel), world)
+    ep_size = min(int(rc.expert_parallel), world) if cfg.n_experts else 1
     tp_ctx, dp_group, dp_rank, dp_world, rep_group = None, None, rank, world, None
     replicate = max(int(rc.dp_replicate), 1)
     if tp_size > 1 or (replicate > 1 and world > 1):
         from ..parallel.mesh import Mesh, MeshSpec
-        mesh = Mesh(MeshSpec(tp=tp_size, pp=pp_size, cp=cp_size if tp_size > 1 else 1, dp_replicate=replicate))
+        mesh = Mesh(MeshSpec(tp=tp_size, pp=pp_size, cp=cp_size if tp_size > 1 else 1, ep=ep_size if (tp_size > 1 and pp_size == 1) else 1,
+                             dp_replicate=replicate))
         if replicate > 1:
             rep_group = mesh.group("dp_replicate")
     if tp_size > 1:
@@ -239,12 +241,17 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
         if cfg.precision != "bf16":
             cfg.precision = "bf16"       # everything outside the tensor-parallel linears stays bf16
     cp_group = ep_group = edp_group = None
-    ep_size = min(int(rc.expert_parallel), world) if cfg.n_experts else 1
     if ep_size > 1:
-        if tp_size > 1 or cp_size > 1 or replicate > 1 or (world // pp_size) % ep_size or cfg.n_experts % ep_size:
-            raise NotImplementedError("expert parallelism combines with data and pipeline parallelism here (tensor / context "
-                                      "parallel = 1, dp_replicate = 1; data-parallel size and experts divisible by expert_parallel)")
-        if pp_size > 1:
+        if (tp_size > 1 and pp_size > 1) or cp_size > 1 or replicate > 1 or (world // (pp_size * tp_size)) % ep_size or cfg.n_experts % ep_size:
+            raise NotImplementedError("expert parallelism combines with data parallelism and with ONE of pipeline / tensor "
+                                      "parallelism here (context parallel = 1, dp_replicate = 1; data-parallel size and experts "
+                                      "divisible by expert_parallel)")
+        if tp_size > 1:
+            # experts spread over (a block of) the data-parallel ranks that share a tensor-parallel index; every
+            # tensor-parallel rank routes its own block of token rows through them
+            ep_group = mesh.group("ep")
+            edp_group = mesh.group("edp") if mesh.size("edp") > 1 else None
+        elif pp_size > 1:
             # experts spread over (a block of) the data-parallel replicas of every pipeline stage
             from ..parallel.mesh import Mesh, MeshSpec
             mesh = Mesh(MeshSpec(pp=pp_size, ep=ep_size))
@@ -256,7 +263,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             from ..parallel.mesh import Mesh, MeshSpec
             ep_mesh = Mesh(MeshSpec(ep=ep_size))
             ep_group, edp_group = ep_mesh.group("ep"), ep_mesh.group("edp")
-        fused_ep = str(rc.moe_dispatch).lower() == "fused" and str(device).startswith("cuda") and pp_size == 1
+        fused_ep = str(rc.moe_dispatch).lower() == "fused" and str(device).startswith("cuda") and pp_size == 1 and tp_size == 1
         cfg.ep_comm = "fused" if fused_ep else "nccl"
     if pp_size > 1 and tp_size == 1:
         if ep_size == 1:

@@ -85,6 +85,18 @@ def test_tensor_x_context_parallel_matches_plain_trainer_gloo():
     assert r.stdout.count("ok=True") == 4
 
 
+def test_tensor_x_expert_parallel_follows_the_unsplit_model_gloo():
+    """Tensor 2 x data 2 with the experts spread over the data-parallel ranks: loss and gradient norm of the unsplit
+    mixture-of-experts model, then the run loop on the same mesh."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+                        "--master-addr", "127.0.0.1", "--master-port", "29680",
+                        os.path.join(ROOT, "tests", "multi", "tp_ep_worker.py")],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("ok=True") == 4
+
+
 def test_bf16_gradient_wire_follows_the_fp32_wire_gloo():
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
