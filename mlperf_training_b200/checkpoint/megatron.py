@@ -223,7 +223,7 @@ def sharded_megatron_state(model: GPT, tp_group) -> dict:
         if shard is None and ep is not None and ep_group is not None:
             # stacked experts: this rank's block of the expert dimension, over the expert-parallel group
             n, r = ep
-            dev = f"rank:{r}/{'cpu' if t.device.type == 'cpu' else str(t.device)}"
+            dev = f"rank:{_global_rank(ep_group, r)}/{'cpu' if t.device.type == 'cpu' else str(t.device)}"
             meta = ShardMetadata(shard_offsets=[r * t.shape[0]] + [0] * (t.dim() - 1), shard_sizes=list(t.shape), placement=dev)
             out[key] = init_from_local_shards([Shard(tensor=t.contiguous(), metadata=meta)], *full_shape_of(p),
                                               process_group=ep_group)
@@ -247,11 +247,18 @@ def sharded_megatron_state(model: GPT, tp_group) -> dict:
             pieces = [(t[:h], [r * h] + tail), (t[h:], [full[0] // 2 + r * h] + tail)]
         else:
             raise ValueError(kind)
-        dev = f"rank:{r}/{'cpu' if t.device.type == 'cpu' else str(t.device)}"
+        dev = f"rank:{_global_rank(tp_group, r)}/{'cpu' if t.device.type == 'cpu' else str(t.device)}"
         shards = [Shard(tensor=x.contiguous(), metadata=ShardMetadata(shard_offsets=list(off), shard_sizes=list(x.shape),
                                                                       placement=dev)) for x, off in pieces]
         out[key] = init_from_local_shards(shards, *full, process_group=tp_group)
     return out
+
+
+def _global_rank(group, r: int) -> int:
+    """Global rank of member ``r`` of ``group`` (a shard's placement names global ranks, also inside a sub-group)."""
+    if group is None or group is torch.distributed.group.WORLD:
+        return r
+    return torch.distributed.get_global_rank(group, r)
 
 
 def _tp_group_of(model):

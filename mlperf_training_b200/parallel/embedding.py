@@ -221,7 +221,8 @@ class ShardedEmbedding:
         if self.world == 1:
             return {f"{prefix}embeddings.{self.name}.weight": self.weight,
                     f"{prefix}embeddings.{self.name}.rowwise_adagrad.sum": self.state}
-        dev = f"rank:{self.rank}/{'cpu' if self.device.type == 'cpu' else str(self.device)}"
+        owner = self.rank if (self.group is None or self.group is dist.group.WORLD) else dist.get_global_rank(self.group, self.rank)
+        dev = f"rank:{owner}/{'cpu' if self.device.type == 'cpu' else str(self.device)}"
         out = {}
         for key, t, size in ((f"{prefix}embeddings.{self.name}.weight", self.weight, (self.rows, self.dim)),
                              (f"{prefix}embeddings.{self.name}.rowwise_adagrad.sum", self.state, (self.rows,))):
@@ -369,7 +370,8 @@ class ColumnShardedEmbedding(ShardedEmbedding):
         wkey, skey = f"{prefix}embeddings.{self.name}.weight", f"{prefix}embeddings.{self.name}.rowwise_adagrad.sum"
         if self.world == 1:
             return {wkey: self.weight, skey: self.state}
-        dev = f"rank:{self.rank}/{'cpu' if self.device.type == 'cpu' else str(self.device)}"
+        owner = self.rank if (self.group is None or self.group is dist.group.WORLD) else dist.get_global_rank(self.group, self.rank)
+        dev = f"rank:{owner}/{'cpu' if self.device.type == 'cpu' else str(self.device)}"
         w = Shard(tensor=self.weight, metadata=ShardMetadata(shard_offsets=[0, self.col_lo], shard_sizes=list(self.weight.shape), placement=dev))
         s = Shard(tensor=self.state.view(self.rows, 1), metadata=ShardMetadata(shard_offsets=[0, self.rank], shard_sizes=[self.rows, 1], placement=dev))
         return {wkey: init_from_local_shards([w], self.rows, self.dim, process_group=self.group),
