@@ -88,6 +88,23 @@ class GPTStage(nn.Module):
             self.final_norm.copy_(full.final_norm)
             self.lm_head.copy_(full.lm_head)
 
+    def set_context_parallel(self, group, mode: str = "allgather") -> None:
+        """Shard the sequence over ``group`` inside this stage: ``forward`` then takes the rank's chunk of tokens and
+        labels (chunk ``r`` of ``W``; with ``mode="ring"`` the zig-zag chunks ``r`` and ``2 W - 1 - r``) - see
+        ``models.gpt.GPT.set_context_parallel``."""
+        if group is None or dist.get_world_size(group) == 1:
+            self.cp = None
+            for blk in self.blocks:
+                blk.cp = None
+            return
+        if self.cfg.sink:
+            raise NotImplementedError("context parallelism does not carry attention sink logits")
+        if mode not in ("allgather", "ulysses", "ring"):
+            raise ValueError(f"unknown context-parallel mode '{mode}'")
+        self.cp = (group, dist.get_world_size(group), dist.get_rank(group), mode)
+        for blk in self.blocks:
+            blk.cp = (group, mode)
+
     def rope(self, device):
         if self._rope is None or self._rope[0].device != torch.device(device):
             self._rope = K.rope_tables(self.cfg.seq_len, self.cfg.head_dim, self.cfg.rope_theta, device)
@@ -99,6 +116,13 @@ class GPTStage(nn.Module):
         the token losses divided by ``n_valid`` when that is given)."""
         B, S = tokens.shape
         cos, sin = self.rope(tokens.device)
+        if getattr(self, "cp", None) is not None:
+            _, W, r, mode = self.cp
+            if mode == "ring":
+                from .context import zigzag_chunk
+                cos, sin = zigzag_chunk(cos[:S * W], W, r, dim=0), zigzag_chunk(sin[:S * W], W, r, dim=0)
+            else:
+                cos, sin = cos[r * S:(r + 1) * S].contiguous(), sin[r * S:(r + 1) * S].contiguous()
         ids = tokens.reshape(-1)
         if self.tp is not None:
             # tensor + sequence parallel inside the stage: every rank of the group embeds, passes on and scores its

@@ -208,9 +208,10 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
 
     cfg = build_model_config(rc.model)
     pp_size, cp_size = int(rc.pipeline_parallel), int(rc.context_parallel)
-    if pp_size > 1 and (int(rc.dp_replicate) > 1 or cp_size > 1 or world % (pp_size * max(int(rc.tensor_parallel), 1))):
-        raise NotImplementedError("pipeline stages combine with data and tensor parallelism here (context_parallel = 1, "
-                                  "dp_replicate = 1, world divisible by pipeline_parallel x tensor_parallel)")
+    if pp_size > 1 and (int(rc.dp_replicate) > 1 or (cp_size > 1 and int(rc.tensor_parallel) > 1)
+                        or world % (pp_size * max(int(rc.tensor_parallel), 1) * max(cp_size, 1))):
+        raise NotImplementedError("pipeline stages combine with data parallelism and ONE of tensor / context / expert "
+                                  "parallelism here (dp_replicate = 1, world divisible by the product of the sizes)")
     if cp_size > 1 and (int(rc.dp_replicate) > 1 or world % (cp_size * max(int(rc.tensor_parallel), 1))):
         raise NotImplementedError("context parallelism combines with data and tensor parallelism here (dp_replicate = 1, "
                                   "world divisible by context_parallel x tensor_parallel)")
@@ -268,7 +269,11 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     if pp_size > 1 and tp_size == 1:
         if ep_size == 1:
             from ..parallel.mesh import Mesh, MeshSpec
-            mesh = Mesh(MeshSpec(pp=pp_size))
+            mesh = Mesh(MeshSpec(pp=pp_size, cp=cp_size))
+            if cp_size > 1:
+                cp_group = mesh.group("cp")
+        elif cp_size > 1:
+            raise NotImplementedError("pipeline stages take context OR expert parallelism")
         dp_rank, dp_world = mesh.index("dp"), mesh.size("dp")
     elif cp_size > 1:
         if tp_size == 1:
@@ -290,7 +295,8 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
     if pp_size > 1:
         from .pipeline_train import PipelineTrainer
         trainer = PipelineTrainer(cfg, opt, tc, device, mesh, virtual_stages=rc.virtual_pipeline_parallel or 1,
-                                  freeze_base=cfg.lora_rank > 0, tp=tp_ctx, ep_group=ep_group, expert_dp_group=edp_group)
+                                  freeze_base=cfg.lora_rank > 0, tp=tp_ctx, ep_group=ep_group, expert_dp_group=edp_group,
+                                  cp_group=cp_group, cp_mode=rc.context_parallel_mode)
     else:
         trainer = PretrainTrainer(cfg, opt, tc, device, group=dp_group, ep_group=ep_group, tp=tp_ctx,
                                   freeze_base=cfg.lora_rank > 0, replicate_group=rep_group, cp_group=cp_group,

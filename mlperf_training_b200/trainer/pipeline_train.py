@@ -34,7 +34,7 @@ def _chunk_bucket_of(name: str) -> str:
 
 class PipelineTrainer:
     def __init__(self, model_cfg: GPTConfig, opt: OptimConfig, train: TrainConfig, device, mesh, virtual_stages: int = 1,
-                 freeze_base: bool = False, tp=None, ep_group=None, expert_dp_group=None):
+                 freeze_base: bool = False, tp=None, ep_group=None, expert_dp_group=None, cp_group=None, cp_mode: str = "allgather"):
         self.cfg, self.train_cfg = model_cfg, train
         self.device = torch.device(device)
         self.mesh = mesh
@@ -63,7 +63,19 @@ class PipelineTrainer:
         if freeze_base:
             from ..models.lora import freeze_base as _freeze
             _freeze(self.model)
-        self.engine = ZeroEngine(self.model, opt, group=self.dp_group, comm="nccl", bucket_of=bucket_of, pp_group=self.pp_group,
+        # context parallel stages: the ranks of ``cp_group`` hold chunks of the same sequences; gradients are reduced
+        # over data x context, the loss is the mean of the chunks' losses
+        self.cp_group = cp_group if (cp_group is not None and dist.get_world_size(cp_group) > 1) else None
+        self.cp_world = dist.get_world_size(self.cp_group) if self.cp_group is not None else 1
+        self.cp_rank = dist.get_rank(self.cp_group) if self.cp_group is not None else 0
+        self.cp_mode = cp_mode
+        if self.cp_group is not None:
+            if self.tp is not None:
+                raise NotImplementedError("pipeline stages take tensor OR context parallelism")
+            for chunk in self.chunks:
+                chunk.set_context_parallel(self.cp_group, cp_mode)
+        grad_group = mesh.group("dp_cp") if self.cp_group is not None else self.dp_group
+        self.engine = ZeroEngine(self.model, opt, group=grad_group, comm="nccl", bucket_of=bucket_of, pp_group=self.pp_group,
                                  tp_group=self.tp.group if self.tp is not None else None, expert_dp_group=expert_dp_group)
         if train.local_batch % train.micro_batch:
             raise ValueError("local_batch must be a multiple of micro_batch")
@@ -85,6 +97,18 @@ class PipelineTrainer:
             return tokens[:, :-1].contiguous(), tokens[:, 1:].contiguous()
         return tokens, labels
 
+    def _chunk(self, t: torch.Tensor) -> torch.Tensor:
+        """This rank's part of the sequence dimension (everything without context parallelism)."""
+        if self.cp_group is None:
+            return t
+        if self.cp_mode == "ring":
+            from ..parallel.context import zigzag_chunk
+            return zigzag_chunk(t, self.cp_world, self.cp_rank, dim=1)
+        s = t.shape[1] // self.cp_world
+        if t.shape[1] % self.cp_world:
+            raise ValueError(f"sequence length {t.shape[1]} does not divide over {self.cp_world} context-parallel ranks")
+        return t[:, self.cp_rank * s:(self.cp_rank + 1) * s].contiguous()
+
     def train_step_device(self, tokens: torch.Tensor, labels: torch.Tensor | None = None) -> torch.Tensor:
         """One optimizer step; the mean loss over the micro-batches as a 0-d device tensor on every
         rank of the pipeline."""
@@ -93,8 +117,11 @@ class PipelineTrainer:
         mbs = []
         for i in range(self.n_micro):
             x, y = x_all[i * mb:(i + 1) * mb].contiguous(), y_all[i * mb:(i + 1) * mb].contiguous()
-            # explicit labels mask part of the positions (-100): the mean runs over the labelled ones
-            mbs.append((x, y) if labels is None else (x, y, max(int((y != -100).sum()), 1)))
+            # explicit labels mask part of the positions (-100): the mean runs over the labelled ones (with the sequence
+            # sharded every chunk divides by its share of the count, so the average of the chunks is the mean)
+            n_valid = None if labels is None else max(int((y != -100).sum()), 1) / self.cp_world
+            x, y = self._chunk(x), self._chunk(y)
+            mbs.append((x, y) if labels is None else (x, y, n_valid if self.cp_group is not None else int(n_valid)))
         total = self.runner.run(mbs)
         self.engine.step(self.lr(), grad_scale=1.0 / self.n_micro)
         self.step_idx += 1
@@ -104,6 +131,9 @@ class PipelineTrainer:
         dist.all_reduce(out, group=self.pp_group)
         if self.tp is not None:
             dist.all_reduce(out, group=self.tp.group)          # every rank of a stage scored its own token rows
+        if self.cp_group is not None:
+            dist.all_reduce(out, group=self.cp_group)
+            out = out / self.cp_world
         return out
 
     def _to_device(self, t: torch.Tensor, slot: int) -> torch.Tensor:
@@ -130,7 +160,7 @@ class PipelineTrainer:
         pp_ranks = self.mesh.ranks["pp"]
         prev, nxt = pp_ranks[(self.r - 1) % self.S], pp_ranks[(self.r + 1) % self.S]
         for i in range(0, x_all.shape[0], mb):
-            x, y = x_all[i:i + mb].contiguous(), y_all[i:i + mb].contiguous()
+            x, y = self._chunk(x_all[i:i + mb].contiguous()), self._chunk(y_all[i:i + mb].contiguous())
             tpw = self.tp.world if self.tp is not None else 1
             like = torch.empty((x.numel() // tpw, self.cfg.hidden), dtype=self.cfg.torch_dtype(), device=self.device)
             for chunk in self.chunks:
@@ -149,6 +179,8 @@ class PipelineTrainer:
         dist.all_reduce(acc, group=self.pp_group)        # only the last stage contributed
         if self.tp is not None:
             dist.all_reduce(acc, group=self.tp.group)
+        if self.cp_group is not None:
+            dist.all_reduce(acc, group=self.cp_group)      # sums and counts of the chunks
         if dist.get_world_size(self.dp_group) > 1:
             dist.all_reduce(acc, group=self.dp_group)
         return acc

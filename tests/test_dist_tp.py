@@ -107,6 +107,17 @@ def test_tensor_parallel_stages_checkpoint_round_trips_gloo(tmp_path):
     assert r.stdout.count("ok=True") == 4
 
 
+@pytest.mark.parametrize("virtual", [1, 2])
+def test_pipeline_x_context_parallel_follows_the_unsplit_model_gloo(virtual):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+                        "--master-addr", "127.0.0.1", "--master-port", "29682",
+                        os.path.join(ROOT, "tests", "multi", "pp_cp_worker.py"), str(virtual)],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("ok=True") == 4
+
+
 def test_bf16_gradient_wire_follows_the_fp32_wire_gloo():
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=ROOT)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
