@@ -14,7 +14,8 @@ knobs that are 1 in every shipped configuration
 (llama2_sft/primus/conf/llama2_70b_lora_posttrain.yaml:22; flux1/primus/conf/flux.1_schnell_t2i-pretrain.yaml:48;
 llama2_sft/primus/src/llama2_custom.py:393-397).  In this all-gather form the work per rank grows with ``r``.
 
-``ring_attention`` is the balanced form (Megatron's default ``cp_comm_type`` p2p): the sequence is cut into
+``ring_attention`` is the balanced form (Megatron's default ``cp_comm_type`` p2p, which the reference's provider gets with
+``context_parallel_size > 1``: llama2_sft/primus/src/llama2_custom.py:393-397,501-506): the sequence is cut into
 ``2 W`` chunks and rank ``r`` holds chunks ``r`` and ``2 W - 1 - r`` (zig-zag), key / value blocks travel round
 the ring with point-to-point messages posted before the attention of the block in hand, the partial outputs
 are merged by their log-sum-exp, and every ring step costs every rank the same half block of work.  Memory

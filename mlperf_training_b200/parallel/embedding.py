@@ -280,6 +280,8 @@ class ColumnShardedEmbedding(ShardedEmbedding):
     the requests of all ranks per row there (sorted order, fp32) and applies row-wise Adagrad to the slice.
     The Adagrad sum of a row is kept per column shard (the mean of squares runs over the shard's columns),
     which is how TorchRec's fused optimizer treats a column-wise shard: every shard is a table of its own.
+    (The reference leaves the choice between row-, table- and column-wise placement to TorchRec's planner under its
+    constraints: generative_recommenders/dlrm_v4/train/utils.py:1311-1545.)
     """
 
     def __init__(self, rows: int, dim: int, *, group=None, device="cpu", dtype=torch.bfloat16, lr: float = 1e-2,
