@@ -54,7 +54,7 @@ def group_ranks(spec: MeshSpec, world: int) -> dict[str, list[list[int]]]:
     def rank_of(t, c, d, p):
         return ((p * dp + d) * spec.cp + c) * spec.tp + t
 
-    out = {"tp": [], "cp": [], "dp": [], "pp": [], "ep": [], "edp": [], "dp_shard": [], "dp_replicate": [], "dp_cp": []}
+    out = {"tp": [], "cp": [], "dp": [], "pp": [], "ep": [], "edp": [], "dp_shard": [], "dp_replicate": [], "dp_cp": [], "edp_cp": []}
     for p in range(spec.pp):
         for d in range(dp):
             for c in range(spec.cp):
@@ -82,6 +82,9 @@ def group_ranks(spec: MeshSpec, world: int) -> dict[str, list[list[int]]]:
     for p in range(spec.pp):
         for t in range(spec.tp):
             out["dp_cp"].append([rank_of(t, c, d, p) for d in range(dp) for c in range(spec.cp)])
+            # ... and of the same experts: the same position in the expert-parallel blocks, every context chunk
+            for e in range(spec.ep):
+                out["edp_cp"].append([rank_of(t, c, d, p) for d in range(e, dp, spec.ep) for c in range(spec.cp)])
     return out
 
 

@@ -243,11 +243,19 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             cfg.precision = "bf16"       # everything outside the tensor-parallel linears stays bf16
     cp_group = ep_group = edp_group = None
     if ep_size > 1:
-        if (tp_size > 1 and pp_size > 1) or cp_size > 1 or replicate > 1 or (world // (pp_size * tp_size)) % ep_size or cfg.n_experts % ep_size:
-            raise NotImplementedError("expert parallelism combines with data parallelism and with ONE of pipeline / tensor "
-                                      "parallelism here (context parallel = 1, dp_replicate = 1; data-parallel size and experts "
-                                      "divisible by expert_parallel)")
-        if tp_size > 1:
+        others = (tp_size > 1) + (pp_size > 1) + (cp_size > 1)
+        if others > 1 or replicate > 1 or (world // (pp_size * tp_size * cp_size)) % ep_size or cfg.n_experts % ep_size:
+            raise NotImplementedError("expert parallelism combines with data parallelism and with ONE of pipeline / tensor / "
+                                      "context parallelism here (dp_replicate = 1; data-parallel size and experts divisible by "
+                                      "expert_parallel)")
+        if cp_size > 1:
+            # experts spread over (a block of) the data-parallel ranks that hold the same chunk of the sequences; the copies
+            # of an expert - in the other blocks and in the other chunks - sum their gradients
+            from ..parallel.mesh import Mesh, MeshSpec
+            mesh = Mesh(MeshSpec(cp=cp_size, ep=ep_size))
+            ep_group = mesh.group("ep")
+            edp_group = mesh.group("edp_cp") if mesh.size("edp_cp") > 1 else None
+        elif tp_size > 1:
             # experts spread over (a block of) the data-parallel ranks that share a tensor-parallel index; every
             # tensor-parallel rank routes its own block of token rows through them
             ep_group = mesh.group("ep")
@@ -264,7 +272,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             from ..parallel.mesh import Mesh, MeshSpec
             ep_mesh = Mesh(MeshSpec(ep=ep_size))
             ep_group, edp_group = ep_mesh.group("ep"), ep_mesh.group("edp")
-        fused_ep = str(rc.moe_dispatch).lower() == "fused" and str(device).startswith("cuda") and pp_size == 1 and tp_size == 1
+        fused_ep = str(rc.moe_dispatch).lower() == "fused" and str(device).startswith("cuda") and others == 0
         cfg.ep_comm = "fused" if fused_ep else "nccl"
     if pp_size > 1 and tp_size == 1:
         if ep_size == 1:
@@ -276,7 +284,7 @@ def run(exp: dict, device: str | None = None, stream=None) -> dict:
             raise NotImplementedError("pipeline stages take context OR expert parallelism")
         dp_rank, dp_world = mesh.index("dp"), mesh.size("dp")
     elif cp_size > 1:
-        if tp_size == 1:
+        if tp_size == 1 and ep_size == 1:
             from ..parallel.mesh import Mesh, MeshSpec
             mesh = Mesh(MeshSpec(cp=cp_size))
         dp_rank, dp_world = mesh.index("dp"), mesh.size("dp")

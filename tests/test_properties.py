@@ -24,7 +24,7 @@ def test_mesh_groups_partition_the_world(tp, cp, pp, dp, ep, rep):
     world = tp * cp * pp * dp
     groups = group_ranks(spec, world)
     sizes = {"tp": tp, "cp": cp, "pp": pp, "dp": dp, "ep": ep, "edp": dp // ep, "dp_shard": dp // rep, "dp_replicate": rep,
-             "dp_cp": dp * cp}
+             "dp_cp": dp * cp, "edp_cp": dp // ep * cp}
     for dim, lists in groups.items():
         flat = sorted(r for g in lists for r in g)
         assert flat == list(range(world)), dim                          # every rank in exactly one group of the dimension
