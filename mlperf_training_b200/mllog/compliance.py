@@ -10,6 +10,9 @@ from .core import check_compliance, parse_log
 
 def main(argv=None) -> int:
     argv = sys.argv[1:] if argv is None else argv
+    if len(argv) == 1 and argv[0] in ("-h", "--help"):
+        print("usage: compliance <logfile>   (checks the :::MLLOG lines of one trial log; exit 0 = compliant)")
+        return 0
     if len(argv) != 1:
         print("usage: compliance <logfile>", file=sys.stderr)
         return 2

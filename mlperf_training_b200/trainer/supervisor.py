@@ -96,8 +96,12 @@ def _launch_logged(world: int, cli_args: list[str], env: dict | None) -> int:
 
 def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
+    usage = "usage: supervisor --nproc N [--max-restarts K] [--shrink --min-nproc M] -- <trainer.cli arguments>"
+    if argv and argv[0] in ("-h", "--help"):
+        print(usage)
+        return 0
     if "--" not in argv:
-        print("usage: supervisor --nproc N [--max-restarts K] [--shrink --min-nproc M] -- <trainer.cli arguments>", file=sys.stderr)
+        print(usage, file=sys.stderr)
         return 2
     cut = argv.index("--")
     ap = argparse.ArgumentParser(prog="b200-supervisor")
